@@ -1,0 +1,196 @@
+/*
+ * scn_b200.h -- C ABI of the sm_100a submanifold sparse-convolution inference path.
+ *
+ * This is the drop-in boundary.  The reference (facebookresearch/SparseConvNet) exposes the
+ * same operations through a pybind11 module, `sparseconvnet.SCN`
+ * (sparseconvnet/SCN/pybind.cpp:201-237, prototypes in sparseconvnet/SCN/sparseconvnet.h);
+ * each entry point below names the reference function it replaces.  A binding for the
+ * reference only has to turn `at::Tensor` arguments into the plain pointers and sizes used
+ * here.
+ *
+ * Conventions
+ *  - every function returns an `int` status (SCN_OK == 0); `scn_last_error()` gives a
+ *    thread-local message for the last non-zero status.  Nothing traps or aborts.
+ *  - `stream` is a `cudaStream_t` passed as `void*` (NULL = legacy default stream).
+ *  - spatial sizes, filter sizes and strides are HOST arrays of `dimension` int64 values,
+ *    as in the reference (CPU LongTensors).
+ *  - feature matrices are DEVICE pointers to row-major float32 `[rows, planes]`, owned by
+ *    the caller.  Rows are the active sites of one spatial scale, numbered as
+ *    `scn_md_spatial_locations` reports them.
+ *  - a `scn_metadata` owns the device-side site hash tables, the per-filter-offset
+ *    rulebooks and their cache, exactly the role of the reference's `Metadata<D>`
+ *    (sparseconvnet/SCN/Metadata/Metadata.h:44-167).  It is not thread safe, like the
+ *    reference object.
+ *  - device memory for tables and rulebooks comes from the CUDA stream-ordered allocator
+ *    of the current device.
+ */
+#ifndef SCN_B200_H
+#define SCN_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SCN_ABI_VERSION 1
+#define SCN_MAX_DIMENSION 6
+
+typedef struct scn_metadata scn_metadata;
+
+enum scn_status {
+  SCN_OK = 0,
+  SCN_ERR_BAD_ARG = 1,      /* null pointer, bad dimension, bad mode ...                    */
+  SCN_ERR_CUDA = 2,         /* a CUDA runtime call failed; message has the CUDA string      */
+  SCN_ERR_COORD_RANGE = 3,  /* a coordinate or batch index lies outside its field          */
+  SCN_ERR_KEY_BITS = 4,     /* spatial size x batch does not fit a 63-bit site key          */
+  SCN_ERR_NO_GRID = 5,      /* no active-site grid exists for that spatial size             */
+  SCN_ERR_TABLE_FULL = 6,   /* a bounded hash probe gave up                                 */
+  SCN_ERR_UNSUPPORTED = 7,  /* shape outside what the kernels implement                     */
+  SCN_ERR_SIZE_MISMATCH = 8 /* row / plane counts disagree with the metadata               */
+};
+
+/* arithmetic used inside the convolution kernels */
+enum scn_precision {
+  SCN_PRECISION_FP32 = 0, /* fp32 FMA, fp32 accumulate (matches the reference's float path)  */
+  SCN_PRECISION_TF32 = 1, /* tcgen05 kind::tf32 tensor-core tiles, fp32 accumulate in TMEM   */
+  SCN_PRECISION_BF16 = 2  /* tcgen05 kind::f16 (bf16 operands), fp32 accumulate in TMEM      */
+};
+
+/* which rulebook of a metadata object an export call refers to */
+enum scn_rulebook_kind {
+  SCN_RULES_SUBMANIFOLD = 0, /* key (spatial_size, filter_size)          */
+  SCN_RULES_STRIDED = 1      /* key (input_size, filter_size, stride)    */
+};
+
+int scn_abi_version(void);
+const char *scn_status_string(int status);
+const char *scn_last_error(void);
+
+/* ---- Metadata object ------------------------------------------------------------------ */
+
+/* replaces `Metadata_<D>()` (pybind.cpp:12-14, 204-209).  dimension in 1..SCN_MAX_DIMENSION. */
+int scn_md_create(int dimension, scn_metadata **md);
+int scn_md_destroy(scn_metadata *md);
+/* replaces Metadata<D>::clear (Metadata.cpp:52-66) */
+int scn_md_clear(scn_metadata *md, void *stream);
+
+/* replaces Metadata<D>::inputLayer + inputLayerRules
+ * (Metadata.cpp:413-425, Metadata/IOLayersRules.h:18-121).
+ * coords: int64 [n_rows, n_cols], n_cols == dimension (one sample) or dimension+1 (last
+ * column = batch index); `coords_on_device` says where the pointer lives (host arrays are
+ * copied with one cudaMemcpyAsync).  mode 0..4 as in the reference (0 unique, 1 first,
+ * 2 last, 3 sum, 4 mean).  Builds the site hash of `spatial_size` on the GPU, numbers the
+ * output rows in order of first occurrence in the input, and returns the active-site count.
+ * Coordinates must lie in [0, spatial_size): the reference does not check this, this
+ * library reports SCN_ERR_COORD_RANGE. */
+int scn_md_input_layer(scn_metadata *md, const int64_t *spatial_size, const int64_t *coords,
+                       int coords_on_device, int64_t n_rows, int n_cols, int64_t batch_size,
+                       int mode, void *stream, int64_t *n_active);
+
+/* replaces cpu/cuda_InputLayer_updateOutput's feature pass
+ * (CPU/IOLayers.cpp:11-29,49-72; CUDA/IOLayers.cu:14-41) using the rules stored by the last
+ * scn_md_input_layer call.  in [n_in, n_planes] -> out [n_active, n_planes]. */
+int scn_input_layer_forward(scn_metadata *md, const float *in_features, int64_t n_in,
+                            float *out_features, int64_t n_out, int n_planes, void *stream);
+
+/* replaces Metadata<D>::getNActive / getBatchSize (Metadata.cpp:67-70,171-176) */
+int scn_md_n_active(scn_metadata *md, const int64_t *spatial_size, int64_t *n_active);
+int scn_md_batch_size(scn_metadata *md, const int64_t *spatial_size, int64_t *batch_size);
+
+/* replaces Metadata<D>::getSpatialLocations (Metadata.cpp:149-170):
+ * out_dev int64 [n_active, dimension+1] on the device, row r = coordinates then batch index. */
+int scn_md_spatial_locations(scn_metadata *md, const int64_t *spatial_size, int64_t *out_dev,
+                             void *stream);
+
+/* replaces Metadata<D>::getSubmanifoldRuleBook (Metadata.cpp:437-451,
+ * Metadata/SubmanifoldConvolutionRules.h:26-87).  Builds (or finds in the cache) the
+ * rulebook on the GPU.  n_rules (may be NULL) receives the total rule count over all filter
+ * offsets; asking for it waits for the build. */
+int scn_md_submanifold_rulebook(scn_metadata *md, const int64_t *spatial_size,
+                                const int64_t *filter_size, void *stream, int64_t *n_rules);
+
+/* replaces Metadata<D>::getRuleBook (Metadata.cpp:492-518, Metadata/ConvolutionRules.h:11-105).
+ * Creates the output grid (site hash and row numbering of `output_size`) if this is the
+ * first use, builds the rulebook, and returns the output active-site count, which the
+ * caller needs to size the output of Convolution / MaxPooling. */
+int scn_md_strided_rulebook(scn_metadata *md, const int64_t *input_size,
+                            const int64_t *output_size, const int64_t *filter_size,
+                            const int64_t *filter_stride, void *stream, int64_t *n_active_out,
+                            int64_t *n_rules);
+
+/* Rulebook read-back in the reference's format (RuleBook = one flat list of
+ * (input_row, output_row) int32 pairs per filter offset, Metadata.h:35).  The reference does
+ * not bind this; it exists so parity tests can compare rulebooks bit for bit.
+ * sizes_a / sizes_b / sizes_c: SUBMANIFOLD: (spatial_size, filter_size, NULL);
+ * STRIDED: (input_size, filter_size, filter_stride).  The rulebook must have been built.
+ * counts_host: int64 [n_offsets] rule count per offset.  pairs_dev (may be NULL): int32
+ * [2 * sum(counts)], offsets concatenated in order, rules of one offset ordered by output
+ * row. */
+int scn_md_rulebook_export(scn_metadata *md, int kind, const int64_t *sizes_a,
+                           const int64_t *sizes_b, const int64_t *sizes_c, int64_t *n_offsets,
+                           int64_t *counts_host, int32_t *pairs_dev, void *stream);
+
+/* ---- Feature operators ----------------------------------------------------------------- */
+
+/* replaces SubmanifoldConvolution_updateOutput (sparseconvnet.h:101-104;
+ * CPU/Convolution.cpp:117-150; CUDA/Convolution.cu:57-233,444-521,618-642).
+ * weight [filter_volume, groups, n_in/groups, n_out/groups], bias [n_out] or NULL.
+ * in [n_active, n_in] -> out [n_active, n_out].  macs (may be NULL) receives the
+ * reference's return value (rules x n_in/groups x n_out/groups x groups). */
+int scn_submanifold_convolution_forward(scn_metadata *md, const int64_t *spatial_size,
+                                        const int64_t *filter_size, const float *in_features,
+                                        float *out_features, const float *weight,
+                                        const float *bias, int n_in_planes, int n_out_planes,
+                                        int groups, int precision, void *stream, double *macs);
+
+/* replaces Convolution_updateOutput (sparseconvnet.h:87-92; CPU/Convolution.cpp:45-79).
+ * out must have the n_active_out rows reported by scn_md_strided_rulebook. */
+int scn_convolution_forward(scn_metadata *md, const int64_t *input_size,
+                            const int64_t *output_size, const int64_t *filter_size,
+                            const int64_t *filter_stride, const float *in_features,
+                            float *out_features, const float *weight, const float *bias,
+                            int n_in_planes, int n_out_planes, int groups, int precision,
+                            void *stream, double *macs);
+
+/* replaces Deconvolution_updateOutput (sparseconvnet.h:149-154; CPU/Deconvolution.cpp:7-41):
+ * uses the rulebook of the matching Convolution (output_size -> input_size) with the two
+ * rule columns swapped.  in [n_active(input_size), n_in] -> out [n_active(output_size), n_out]. */
+int scn_deconvolution_forward(scn_metadata *md, const int64_t *input_size,
+                              const int64_t *output_size, const int64_t *filter_size,
+                              const int64_t *filter_stride, const float *in_features,
+                              float *out_features, const float *weight, const float *bias,
+                              int n_in_planes, int n_out_planes, int groups, int precision,
+                              void *stream, double *macs);
+
+/* replaces BatchNormalization_updateOutput (sparseconvnet.h:22-26;
+ * CPU/BatchNormalization.cpp:12-62; CUDA/BatchNormalization.cu:14-122), which fuses the
+ * leaky-ReLU: y = x*w + b, y *= (y > 0 ? 1 : leakiness).  weight / bias may be NULL.
+ * train != 0 computes batch statistics and updates running_mean / running_var in place
+ * (momentum = weight of the old value).  save_mean / save_invstd: [n_planes] outputs. */
+int scn_batchnorm_forward(const float *in_features, float *out_features, int64_t n_rows,
+                          int n_planes, int64_t in_stride, int64_t out_stride, float *save_mean,
+                          float *save_invstd, float *running_mean, float *running_var,
+                          const float *weight, const float *bias, double eps, double momentum,
+                          int train, double leakiness, void *stream);
+
+/* replaces MaxPooling_updateOutput (sparseconvnet.h:198-201; CPU/MaxPooling.cpp:7-60):
+ * out[o] = max(0, max over rules of in[i]) on planes n_features_to_drop .. n_planes_in-1.
+ * out [n_active_out, n_planes_in - n_features_to_drop]. */
+int scn_max_pooling_forward(scn_metadata *md, const int64_t *input_size,
+                            const int64_t *output_size, const int64_t *pool_size,
+                            const int64_t *pool_stride, const float *in_features,
+                            float *out_features, int n_planes_in, int n_features_to_drop,
+                            void *stream);
+
+/* replaces SparseToDense_updateOutput (sparseconvnet.h:220-222; CPU/SparseToDense.cpp:7-64):
+ * out [batch_size, n_planes, *spatial_size] float32, written completely (zeros where
+ * inactive). */
+int scn_sparse_to_dense_forward(scn_metadata *md, const int64_t *spatial_size,
+                                const float *in_features, float *out_dense, int n_planes,
+                                void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SCN_B200_H */
