@@ -33,6 +33,12 @@
 extern "C" {
 #endif
 
+#if defined(__GNUC__)
+#define SCN_API __attribute__((visibility("default")))
+#else
+#define SCN_API
+#endif
+
 #define SCN_ABI_VERSION 1
 #define SCN_MAX_DIMENSION 6
 
@@ -63,17 +69,17 @@ enum scn_rulebook_kind {
   SCN_RULES_STRIDED = 1      /* key (input_size, filter_size, stride)    */
 };
 
-int scn_abi_version(void);
-const char *scn_status_string(int status);
-const char *scn_last_error(void);
+SCN_API int scn_abi_version(void);
+SCN_API const char *scn_status_string(int status);
+SCN_API const char *scn_last_error(void);
 
 /* ---- Metadata object ------------------------------------------------------------------ */
 
 /* replaces `Metadata_<D>()` (pybind.cpp:12-14, 204-209).  dimension in 1..SCN_MAX_DIMENSION. */
-int scn_md_create(int dimension, scn_metadata **md);
-int scn_md_destroy(scn_metadata *md);
+SCN_API int scn_md_create(int dimension, scn_metadata **md);
+SCN_API int scn_md_destroy(scn_metadata *md);
 /* replaces Metadata<D>::clear (Metadata.cpp:52-66) */
-int scn_md_clear(scn_metadata *md, void *stream);
+SCN_API int scn_md_clear(scn_metadata *md, void *stream);
 
 /* replaces Metadata<D>::inputLayer + inputLayerRules
  * (Metadata.cpp:413-425, Metadata/IOLayersRules.h:18-121).
@@ -84,37 +90,37 @@ int scn_md_clear(scn_metadata *md, void *stream);
  * output rows in order of first occurrence in the input, and returns the active-site count.
  * Coordinates must lie in [0, spatial_size): the reference does not check this, this
  * library reports SCN_ERR_COORD_RANGE. */
-int scn_md_input_layer(scn_metadata *md, const int64_t *spatial_size, const int64_t *coords,
+SCN_API int scn_md_input_layer(scn_metadata *md, const int64_t *spatial_size, const int64_t *coords,
                        int coords_on_device, int64_t n_rows, int n_cols, int64_t batch_size,
                        int mode, void *stream, int64_t *n_active);
 
 /* replaces cpu/cuda_InputLayer_updateOutput's feature pass
  * (CPU/IOLayers.cpp:11-29,49-72; CUDA/IOLayers.cu:14-41) using the rules stored by the last
  * scn_md_input_layer call.  in [n_in, n_planes] -> out [n_active, n_planes]. */
-int scn_input_layer_forward(scn_metadata *md, const float *in_features, int64_t n_in,
+SCN_API int scn_input_layer_forward(scn_metadata *md, const float *in_features, int64_t n_in,
                             float *out_features, int64_t n_out, int n_planes, void *stream);
 
 /* replaces Metadata<D>::getNActive / getBatchSize (Metadata.cpp:67-70,171-176) */
-int scn_md_n_active(scn_metadata *md, const int64_t *spatial_size, int64_t *n_active);
-int scn_md_batch_size(scn_metadata *md, const int64_t *spatial_size, int64_t *batch_size);
+SCN_API int scn_md_n_active(scn_metadata *md, const int64_t *spatial_size, int64_t *n_active);
+SCN_API int scn_md_batch_size(scn_metadata *md, const int64_t *spatial_size, int64_t *batch_size);
 
 /* replaces Metadata<D>::getSpatialLocations (Metadata.cpp:149-170):
  * out_dev int64 [n_active, dimension+1] on the device, row r = coordinates then batch index. */
-int scn_md_spatial_locations(scn_metadata *md, const int64_t *spatial_size, int64_t *out_dev,
+SCN_API int scn_md_spatial_locations(scn_metadata *md, const int64_t *spatial_size, int64_t *out_dev,
                              void *stream);
 
 /* replaces Metadata<D>::getSubmanifoldRuleBook (Metadata.cpp:437-451,
  * Metadata/SubmanifoldConvolutionRules.h:26-87).  Builds (or finds in the cache) the
  * rulebook on the GPU.  n_rules (may be NULL) receives the total rule count over all filter
  * offsets; asking for it waits for the build. */
-int scn_md_submanifold_rulebook(scn_metadata *md, const int64_t *spatial_size,
+SCN_API int scn_md_submanifold_rulebook(scn_metadata *md, const int64_t *spatial_size,
                                 const int64_t *filter_size, void *stream, int64_t *n_rules);
 
 /* replaces Metadata<D>::getRuleBook (Metadata.cpp:492-518, Metadata/ConvolutionRules.h:11-105).
  * Creates the output grid (site hash and row numbering of `output_size`) if this is the
  * first use, builds the rulebook, and returns the output active-site count, which the
  * caller needs to size the output of Convolution / MaxPooling. */
-int scn_md_strided_rulebook(scn_metadata *md, const int64_t *input_size,
+SCN_API int scn_md_strided_rulebook(scn_metadata *md, const int64_t *input_size,
                             const int64_t *output_size, const int64_t *filter_size,
                             const int64_t *filter_stride, void *stream, int64_t *n_active_out,
                             int64_t *n_rules);
@@ -127,7 +133,7 @@ int scn_md_strided_rulebook(scn_metadata *md, const int64_t *input_size,
  * counts_host: int64 [n_offsets] rule count per offset.  pairs_dev (may be NULL): int32
  * [2 * sum(counts)], offsets concatenated in order, rules of one offset ordered by output
  * row. */
-int scn_md_rulebook_export(scn_metadata *md, int kind, const int64_t *sizes_a,
+SCN_API int scn_md_rulebook_export(scn_metadata *md, int kind, const int64_t *sizes_a,
                            const int64_t *sizes_b, const int64_t *sizes_c, int64_t *n_offsets,
                            int64_t *counts_host, int32_t *pairs_dev, void *stream);
 
@@ -138,7 +144,7 @@ int scn_md_rulebook_export(scn_metadata *md, int kind, const int64_t *sizes_a,
  * weight [filter_volume, groups, n_in/groups, n_out/groups], bias [n_out] or NULL.
  * in [n_active, n_in] -> out [n_active, n_out].  macs (may be NULL) receives the
  * reference's return value (rules x n_in/groups x n_out/groups x groups). */
-int scn_submanifold_convolution_forward(scn_metadata *md, const int64_t *spatial_size,
+SCN_API int scn_submanifold_convolution_forward(scn_metadata *md, const int64_t *spatial_size,
                                         const int64_t *filter_size, const float *in_features,
                                         float *out_features, const float *weight,
                                         const float *bias, int n_in_planes, int n_out_planes,
@@ -146,7 +152,7 @@ int scn_submanifold_convolution_forward(scn_metadata *md, const int64_t *spatial
 
 /* replaces Convolution_updateOutput (sparseconvnet.h:87-92; CPU/Convolution.cpp:45-79).
  * out must have the n_active_out rows reported by scn_md_strided_rulebook. */
-int scn_convolution_forward(scn_metadata *md, const int64_t *input_size,
+SCN_API int scn_convolution_forward(scn_metadata *md, const int64_t *input_size,
                             const int64_t *output_size, const int64_t *filter_size,
                             const int64_t *filter_stride, const float *in_features,
                             float *out_features, const float *weight, const float *bias,
@@ -156,7 +162,7 @@ int scn_convolution_forward(scn_metadata *md, const int64_t *input_size,
 /* replaces Deconvolution_updateOutput (sparseconvnet.h:149-154; CPU/Deconvolution.cpp:7-41):
  * uses the rulebook of the matching Convolution (output_size -> input_size) with the two
  * rule columns swapped.  in [n_active(input_size), n_in] -> out [n_active(output_size), n_out]. */
-int scn_deconvolution_forward(scn_metadata *md, const int64_t *input_size,
+SCN_API int scn_deconvolution_forward(scn_metadata *md, const int64_t *input_size,
                               const int64_t *output_size, const int64_t *filter_size,
                               const int64_t *filter_stride, const float *in_features,
                               float *out_features, const float *weight, const float *bias,
@@ -168,7 +174,7 @@ int scn_deconvolution_forward(scn_metadata *md, const int64_t *input_size,
  * leaky-ReLU: y = x*w + b, y *= (y > 0 ? 1 : leakiness).  weight / bias may be NULL.
  * train != 0 computes batch statistics and updates running_mean / running_var in place
  * (momentum = weight of the old value).  save_mean / save_invstd: [n_planes] outputs. */
-int scn_batchnorm_forward(const float *in_features, float *out_features, int64_t n_rows,
+SCN_API int scn_batchnorm_forward(const float *in_features, float *out_features, int64_t n_rows,
                           int n_planes, int64_t in_stride, int64_t out_stride, float *save_mean,
                           float *save_invstd, float *running_mean, float *running_var,
                           const float *weight, const float *bias, double eps, double momentum,
@@ -177,7 +183,7 @@ int scn_batchnorm_forward(const float *in_features, float *out_features, int64_t
 /* replaces MaxPooling_updateOutput (sparseconvnet.h:198-201; CPU/MaxPooling.cpp:7-60):
  * out[o] = max(0, max over rules of in[i]) on planes n_features_to_drop .. n_planes_in-1.
  * out [n_active_out, n_planes_in - n_features_to_drop]. */
-int scn_max_pooling_forward(scn_metadata *md, const int64_t *input_size,
+SCN_API int scn_max_pooling_forward(scn_metadata *md, const int64_t *input_size,
                             const int64_t *output_size, const int64_t *pool_size,
                             const int64_t *pool_stride, const float *in_features,
                             float *out_features, int n_planes_in, int n_features_to_drop,
@@ -186,7 +192,7 @@ int scn_max_pooling_forward(scn_metadata *md, const int64_t *input_size,
 /* replaces SparseToDense_updateOutput (sparseconvnet.h:220-222; CPU/SparseToDense.cpp:7-64):
  * out [batch_size, n_planes, *spatial_size] float32, written completely (zeros where
  * inactive). */
-int scn_sparse_to_dense_forward(scn_metadata *md, const int64_t *spatial_size,
+SCN_API int scn_sparse_to_dense_forward(scn_metadata *md, const int64_t *spatial_size,
                                 const float *in_features, float *out_dense, int n_planes,
                                 void *stream);
 

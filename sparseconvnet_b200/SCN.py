@@ -1,0 +1,327 @@
+"""Host-side mirror of the reference's ``sparseconvnet.SCN`` extension module.
+
+Same names, argument order and ownership rules as the functions bound in the reference's
+``sparseconvnet/SCN/pybind.cpp:201-237`` (prototypes in ``sparseconvnet/SCN/sparseconvnet.h``)
+for the inference path: the caller passes an empty output tensor, the callee sizes and
+fills it; an absent bias is a 0-element tensor; spatial sizes are CPU LongTensors;
+convolutions return their multiply-add count as a float.
+
+Every function forwards to the C-ABI library (``include/scn_b200.h``) with raw device
+pointers and torch's current CUDA stream.  Feature tensors must be CUDA float32: there is
+no CPU path.
+"""
+import ctypes as C
+
+import torch
+
+from . import _lib
+from ._lib import check, lib, sizes
+
+PRECISION_FP32, PRECISION_TF32, PRECISION_BF16 = 0, 1, 2
+_precision = PRECISION_FP32
+
+
+def set_precision(p):
+    """Arithmetic of the convolution kernels: 'fp32' (default, reference-exact class),
+    'tf32' or 'bf16' (tensor-core tiles with fp32 accumulation)."""
+    global _precision
+    table = {"fp32": 0, "tf32": 1, "bf16": 2, 0: 0, 1: 1, 2: 2}
+    if p not in table:
+        raise ValueError("precision must be 'fp32', 'tf32' or 'bf16'")
+    _precision = table[p]
+
+
+def get_precision():
+    return ("fp32", "tf32", "bf16")[_precision]
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _features(t, name):
+    if not t.is_cuda:
+        raise RuntimeError("%s must be a CUDA tensor: sparseconvnet_b200 has no CPU path" % name)
+    if t.dtype != torch.float32:
+        raise RuntimeError("%s must be float32, got %s" % (name, t.dtype))
+    if not t.is_contiguous():
+        raise RuntimeError("%s must be contiguous" % name)
+    return t
+
+
+def _ptr(t):
+    return C.c_void_p(t.data_ptr()) if t is not None and t.numel() else C.c_void_p(0)
+
+
+def _optional(t, like, name):
+    """0-element tensor means 'absent' (reference: utils.py:21-22, bias.numel() tests)."""
+    if t is None or t.numel() == 0:
+        return None
+    t = _features(t.detach(), name)
+    if t.device != like.device:
+        raise RuntimeError("%s is on %s, features on %s" % (name, t.device, like.device))
+    return t
+
+
+class _Metadata(object):
+    """Counterpart of the reference's ``Metadata<D>`` Python object (pybind.cpp:12-33): owns
+    the GPU site hash of every spatial scale and the rulebook cache."""
+    dimension = 0
+
+    def __init__(self):
+        self._h = C.c_void_p()
+        check(lib.scn_md_create(self.dimension, C.byref(self._h)))
+        self.device = None
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h and lib is not None:
+            try:
+                lib.scn_md_destroy(h)
+            except Exception:
+                pass
+
+    def clear(self):
+        check(lib.scn_md_clear(self._h, _stream()))
+
+    def getNActive(self, spatial_size):
+        n = C.c_int64()
+        check(lib.scn_md_n_active(self._h, sizes(spatial_size), C.byref(n)))
+        return n.value
+
+    def getBatchSize(self, spatial_size):
+        n = C.c_int64()
+        check(lib.scn_md_batch_size(self._h, sizes(spatial_size), C.byref(n)))
+        return n.value
+
+    def getSpatialLocations(self, spatial_size, device="cpu"):
+        """LongTensor [nActive, D+1]: coordinates then batch index (Metadata.cpp:149-170).
+        Computed on the GPU; returned on the CPU like the reference unless ``device`` says
+        otherwise."""
+        n = self.getNActive(spatial_size)
+        dev = self.device if self.device is not None else torch.device("cuda")
+        out = torch.zeros(n, self.dimension + 1, dtype=torch.int64, device=dev)
+        if n:
+            with torch.cuda.device(dev):
+                check(lib.scn_md_spatial_locations(self._h, sizes(spatial_size), _ptr(out), _stream()))
+        return out.to(device)
+
+    # ---- extensions used by tests and tools (no counterpart in the reference's bindings) ----
+    def rulebook(self, kind, a, b, c=None):
+        """Reads a built rulebook back as the reference stores it: a list with one int32
+        tensor [n_rules, 2] of (input_row, output_row) per filter offset."""
+        dev = self.device if self.device is not None else torch.device("cuda")
+        n_off = C.c_int64()
+        counts = (C.c_int64 * 4096)()
+        sc = sizes(c) if c is not None else None
+        with torch.cuda.device(dev):
+            check(lib.scn_md_rulebook_export(self._h, kind, sizes(a), sizes(b), sc, C.byref(n_off), counts,
+                                             None, _stream()))
+            k = n_off.value
+            cnt = [counts[i] for i in range(k)]
+            pairs = torch.empty(2 * sum(cnt), dtype=torch.int32, device=dev)
+            check(lib.scn_md_rulebook_export(self._h, kind, sizes(a), sizes(b), sc, C.byref(n_off), counts,
+                                             _ptr(pairs), _stream()))
+        pairs = pairs.view(-1, 2)
+        out, pos = [], 0
+        for n in cnt:
+            out.append(pairs[pos:pos + n])
+            pos += n
+        return out
+
+    def _unsupported(self, *a, **k):
+        raise NotImplementedError("outside the inference path implemented by sparseconvnet_b200")
+
+    setInputSpatialSize = batchAddSample = setInputSpatialLocation = setInputSpatialLocations = _unsupported
+    createMetadataForDenseToSparse = sparsifyMetadata = appendMetadata = sparsifyCompare = _unsupported
+    addSampleFromThresholdedTensor = generateRuleBooks3s2 = generateRuleBooks2s2 = _unsupported
+    compareSparseHelper = copyFeaturesHelper = _unsupported
+
+
+def _make_metadata_class(d):
+    return type("Metadata_%d" % d, (_Metadata,), {"dimension": d})
+
+
+Metadata_1, Metadata_2, Metadata_3, Metadata_4, Metadata_5, Metadata_6 = (
+    _make_metadata_class(d) for d in range(1, 7))
+
+
+def n_rulebook_bits():
+    return 32
+
+
+def is_cuda_build():
+    return True
+
+
+# ---------------------------------------------------------------------------------------------
+# operators
+# ---------------------------------------------------------------------------------------------
+
+def InputLayer_updateOutput(m, spatial_size, input_coords, input_features, output_features,
+                            batch_size, mode):
+    """sparseconvnet.h:163-167.  ``input_coords`` may be a CPU or CUDA LongTensor."""
+    f = _features(input_features, "input_features")
+    if input_coords.dtype != torch.int64 or input_coords.dim() != 2:
+        raise RuntimeError("input_coords must be a 2-d LongTensor")
+    if input_coords.size(0) != f.size(0):
+        raise RuntimeError("input_coords and input_features disagree on the row count")
+    coords = input_coords.contiguous()
+    if coords.is_cuda and coords.device != f.device:
+        coords = coords.to(f.device)
+    m.device = f.device
+    n_active = C.c_int64()
+    with torch.cuda.device(f.device):
+        check(lib.scn_md_input_layer(m._h, sizes(spatial_size), _ptr(coords), int(coords.is_cuda),
+                                     coords.size(0), coords.size(1), int(batch_size), int(mode),
+                                     _stream(), C.byref(n_active)))
+        output_features.resize_(n_active.value, f.size(1))
+        check(lib.scn_input_layer_forward(m._h, _ptr(f), f.size(0), _ptr(output_features), n_active.value,
+                                          f.size(1), _stream()))
+
+
+def _conv_args(input_features, weight, bias):
+    f = _features(input_features, "input_features")
+    w = _features(weight.detach(), "weight")
+    if w.dim() != 4:
+        raise RuntimeError("weight must be [filter_volume, groups, nIn/groups, nOut/groups]")
+    if w.device != f.device:
+        raise RuntimeError("weight is on %s, features on %s" % (w.device, f.device))
+    groups, cin, cout = w.size(1), w.size(2), w.size(3)
+    if f.numel() and f.size(1) != groups * cin:
+        raise RuntimeError("features have %d planes, weight expects %d" % (f.size(1), groups * cin))
+    b = _optional(bias, f, "bias")
+    return f, w, b, groups, cin, cout
+
+
+def SubmanifoldConvolution_updateOutput(inputSize, filterSize, m, input_features, output_features,
+                                        weight, bias):
+    """sparseconvnet.h:101-104."""
+    f, w, b, groups, cin, cout = _conv_args(input_features, weight, bias)
+    macs = C.c_double()
+    with torch.cuda.device(f.device):
+        n = m.getNActive(inputSize)
+        if f.size(0) != n:
+            raise RuntimeError("features have %d rows, metadata has %d active sites" % (f.size(0), n))
+        output_features.resize_(n, groups * cout)
+        check(lib.scn_submanifold_convolution_forward(
+            m._h, sizes(inputSize), sizes(filterSize), _ptr(f), _ptr(output_features), _ptr(w), _ptr(b),
+            groups * cin, groups * cout, groups, _precision, _stream(), C.byref(macs)))
+    return macs.value
+
+
+def Convolution_updateOutput(inputSize, outputSize, filterSize, filterStride, m, input_features,
+                             output_features, weight, bias):
+    """sparseconvnet.h:87-92."""
+    f, w, b, groups, cin, cout = _conv_args(input_features, weight, bias)
+    macs = C.c_double()
+    n_out = C.c_int64()
+    with torch.cuda.device(f.device):
+        if f.size(0) != m.getNActive(inputSize):
+            raise RuntimeError("features have %d rows, metadata has %d active sites"
+                               % (f.size(0), m.getNActive(inputSize)))
+        check(lib.scn_md_strided_rulebook(m._h, sizes(inputSize), sizes(outputSize), sizes(filterSize),
+                                          sizes(filterStride), _stream(), C.byref(n_out), None))
+        output_features.resize_(n_out.value, groups * cout)
+        check(lib.scn_convolution_forward(
+            m._h, sizes(inputSize), sizes(outputSize), sizes(filterSize), sizes(filterStride), _ptr(f),
+            _ptr(output_features), _ptr(w), _ptr(b), groups * cin, groups * cout, groups, _precision,
+            _stream(), C.byref(macs)))
+    return macs.value
+
+
+def Deconvolution_updateOutput(inputSize, outputSize, filterSize, filterStride, m, input_features,
+                               output_features, weight, bias):
+    """sparseconvnet.h:149-154."""
+    f, w, b, groups, cin, cout = _conv_args(input_features, weight, bias)
+    macs = C.c_double()
+    with torch.cuda.device(f.device):
+        # same rulebook as the Convolution that made `inputSize` out of `outputSize`
+        check(lib.scn_md_strided_rulebook(m._h, sizes(outputSize), sizes(inputSize), sizes(filterSize),
+                                          sizes(filterStride), _stream(), None, None))
+        if f.size(0) != m.getNActive(inputSize):
+            raise RuntimeError("features have %d rows, metadata has %d active sites"
+                               % (f.size(0), m.getNActive(inputSize)))
+        output_features.resize_(m.getNActive(outputSize), groups * cout)
+        check(lib.scn_deconvolution_forward(
+            m._h, sizes(inputSize), sizes(outputSize), sizes(filterSize), sizes(filterStride), _ptr(f),
+            _ptr(output_features), _ptr(w), _ptr(b), groups * cin, groups * cout, groups, _precision,
+            _stream(), C.byref(macs)))
+    return macs.value
+
+
+def BatchNormalization_updateOutput(input_features, output_features, saveMean, saveInvStd, runningMean,
+                                    runningVar, weight, bias, eps, momentum, train, leakiness):
+    """sparseconvnet.h:22-26.  Accepts a column slice of a wider matrix (row stride > planes),
+    as the reference does (CPU/BatchNormalization.cpp:9-10)."""
+    f = input_features
+    if not f.is_cuda or f.dtype != torch.float32 or f.dim() != 2 or (f.numel() and f.stride(1) != 1):
+        raise RuntimeError("input_features must be a CUDA float32 matrix with unit column stride")
+    n, c = f.size(0), f.size(1)
+    with torch.cuda.device(f.device):
+        output_features.resize_(n, c)
+        saveMean.resize_(c)
+        saveInvStd.resize_(c)
+        if n == 0:
+            return
+        w = _optional(weight, f, "weight")
+        b = _optional(bias, f, "bias")
+        check(lib.scn_batchnorm_forward(
+            _ptr(f), _ptr(output_features), n, c, f.stride(0), output_features.stride(0), _ptr(saveMean),
+            _ptr(saveInvStd), _ptr(_features(runningMean, "runningMean")),
+            _ptr(_features(runningVar, "runningVar")), _ptr(w), _ptr(b), float(eps), float(momentum),
+            int(bool(train)), float(leakiness), _stream()))
+
+
+def MaxPooling_updateOutput(inputSize, outputSize, poolSize, poolStride, m, input_features,
+                            output_features, nFeaturesToDrop):
+    """sparseconvnet.h:198-201."""
+    f = _features(input_features, "input_features")
+    n_out = C.c_int64()
+    with torch.cuda.device(f.device):
+        check(lib.scn_md_strided_rulebook(m._h, sizes(inputSize), sizes(outputSize), sizes(poolSize),
+                                          sizes(poolStride), _stream(), C.byref(n_out), None))
+        output_features.resize_(n_out.value, f.size(1) - int(nFeaturesToDrop))
+        check(lib.scn_max_pooling_forward(
+            m._h, sizes(inputSize), sizes(outputSize), sizes(poolSize), sizes(poolStride), _ptr(f),
+            _ptr(output_features), f.size(1), int(nFeaturesToDrop), _stream()))
+
+
+def SparseToDense_updateOutput(inputSize, m, input_features, output_features, nPlanes):
+    """sparseconvnet.h:220-222.  Output [batch, nPlanes, *inputSize]."""
+    f = _features(input_features, "input_features")
+    with torch.cuda.device(f.device):
+        shape = [m.getBatchSize(inputSize), int(nPlanes)] + [int(v) for v in inputSize]
+        output_features.resize_(*shape)
+        if f.dim() == 2:
+            if f.size(1) != nPlanes:
+                raise RuntimeError("features have %d planes, nPlanes is %d" % (f.size(1), nPlanes))
+            check(lib.scn_sparse_to_dense_forward(m._h, sizes(inputSize), _ptr(f), _ptr(output_features),
+                                                  int(nPlanes), _stream()))
+        else:
+            output_features.zero_()
+
+
+def NetworkInNetwork_updateOutput(input_features, output_features, weight, bias):
+    """sparseconvnet.h:51-53.  The reference itself hands this 1x1 convolution to the dense
+    matrix library (CPU/NetworkInNetwork.cpp:7-23: ``addmm_``); so does this."""
+    f = _features(input_features, "input_features")
+    n, cout = f.size(0), weight.size(1)
+    output_features.resize_(n, cout)
+    if bias is not None and bias.numel():
+        output_features.copy_(bias.detach().expand(n, cout))
+    else:
+        output_features.zero_()
+    if n:
+        output_features.addmm_(f, weight.detach())
+    return float(n * f.size(1) * cout)
+
+
+def _training_only(*a, **k):
+    raise NotImplementedError("backward passes are outside the inference path of sparseconvnet_b200")
+
+
+InputLayer_updateGradInput = SubmanifoldConvolution_backward = Convolution_backward = _training_only
+Deconvolution_backward = BatchNormalization_backward = MaxPooling_updateGradInput = _training_only
+SparseToDense_updateGradInput = NetworkInNetwork_updateGradInput = _training_only
+NetworkInNetwork_accGradParameters = _training_only

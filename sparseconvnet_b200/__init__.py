@@ -1,0 +1,27 @@
+"""sparseconvnet_b200: the inference path of SparseConvNet (InputLayer, SubmanifoldConvolution,
+Convolution, Deconvolution, BatchNormReLU, MaxPooling, SparseToDense and the Metadata object)
+on sm_100a, with the reference package's module API:
+
+    import sparseconvnet_b200 as scn
+    model = scn.Sequential().add(scn.SubmanifoldConvolution(3, 3, 32, 3, False)).add(...)
+
+All compute runs in ``libscn_b200.so`` (C ABI in ``include/scn_b200.h``); there is no CPU path.
+"""
+forward_pass_multiplyAdd_count = 0
+forward_pass_hidden_states = 0
+
+from . import SCN  # noqa: E402  (loads libscn_b200.so; fails loudly if it is missing)
+from .SCN import set_precision, get_precision  # noqa: E402
+from .sparse_tensor import SparseConvNetTensor, to_long_tensor as toLongTensor  # noqa: E402
+
+
+def Metadata(dim):
+    """A fresh Metadata object for `dim` spatial dimensions (reference: sparseconvnet/metadata.py:16-17)."""
+    return getattr(SCN, "Metadata_%d" % dim)()
+
+
+from .layers import (InputLayer, SubmanifoldConvolution, ValidConvolution, Convolution,  # noqa: E402
+                     Deconvolution, BatchNormalization, BatchNormReLU, BatchNormLeakyReLU, MaxPooling,
+                     SparseToDense, NetworkInNetwork, Identity)
+from .containers import Sequential, ConcatTable, JoinTable, AddTable  # noqa: E402
+from .architectures import SparseVggNet, SparseResNet, UNet  # noqa: E402

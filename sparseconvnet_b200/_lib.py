@@ -1,0 +1,82 @@
+"""ctypes binding of ``libscn_b200.so`` (``include/scn_b200.h``).
+
+The library is the only compute path: if it is missing or does not export a symbol the
+import fails loudly.  There is no CPU or PyTorch fallback.
+"""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libscn_b200.so")
+
+_i64p = C.POINTER(C.c_int64)
+_vp = C.c_void_p
+
+# name -> (restype, argtypes); mirrors include/scn_b200.h one to one
+SIGNATURES = {
+    "scn_abi_version": (C.c_int, []),
+    "scn_status_string": (C.c_char_p, [C.c_int]),
+    "scn_last_error": (C.c_char_p, []),
+    "scn_md_create": (C.c_int, [C.c_int, C.POINTER(_vp)]),
+    "scn_md_destroy": (C.c_int, [_vp]),
+    "scn_md_clear": (C.c_int, [_vp, _vp]),
+    "scn_md_input_layer": (C.c_int, [_vp, _i64p, _vp, C.c_int, C.c_int64, C.c_int, C.c_int64,
+                                     C.c_int, _vp, _i64p]),
+    "scn_input_layer_forward": (C.c_int, [_vp, _vp, C.c_int64, _vp, C.c_int64, C.c_int, _vp]),
+    "scn_md_n_active": (C.c_int, [_vp, _i64p, _i64p]),
+    "scn_md_batch_size": (C.c_int, [_vp, _i64p, _i64p]),
+    "scn_md_spatial_locations": (C.c_int, [_vp, _i64p, _vp, _vp]),
+    "scn_md_submanifold_rulebook": (C.c_int, [_vp, _i64p, _i64p, _vp, _i64p]),
+    "scn_md_strided_rulebook": (C.c_int, [_vp, _i64p, _i64p, _i64p, _i64p, _vp, _i64p, _i64p]),
+    "scn_md_rulebook_export": (C.c_int, [_vp, C.c_int, _i64p, _i64p, _i64p, _i64p, _i64p, _vp, _vp]),
+    "scn_submanifold_convolution_forward": (C.c_int, [_vp, _i64p, _i64p, _vp, _vp, _vp, _vp, C.c_int,
+                                                      C.c_int, C.c_int, C.c_int, _vp,
+                                                      C.POINTER(C.c_double)]),
+    "scn_convolution_forward": (C.c_int, [_vp, _i64p, _i64p, _i64p, _i64p, _vp, _vp, _vp, _vp,
+                                          C.c_int, C.c_int, C.c_int, C.c_int, _vp,
+                                          C.POINTER(C.c_double)]),
+    "scn_deconvolution_forward": (C.c_int, [_vp, _i64p, _i64p, _i64p, _i64p, _vp, _vp, _vp, _vp,
+                                            C.c_int, C.c_int, C.c_int, C.c_int, _vp,
+                                            C.POINTER(C.c_double)]),
+    "scn_batchnorm_forward": (C.c_int, [_vp, _vp, C.c_int64, C.c_int, C.c_int64, C.c_int64, _vp, _vp,
+                                        _vp, _vp, _vp, _vp, C.c_double, C.c_double, C.c_int,
+                                        C.c_double, _vp]),
+    "scn_max_pooling_forward": (C.c_int, [_vp, _i64p, _i64p, _i64p, _i64p, _vp, _vp, C.c_int, C.c_int,
+                                          _vp]),
+    "scn_sparse_to_dense_forward": (C.c_int, [_vp, _i64p, _vp, _vp, C.c_int, _vp]),
+}
+
+
+class ScnError(RuntimeError):
+    def __init__(self, status, message):
+        RuntimeError.__init__(self, "scn_b200 status %d: %s" % (status, message))
+        self.status = status
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            "%s is missing: build it with `python -m sparseconvnet_b200.build` "
+            "(there is no CPU fallback)" % LIB_PATH)
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the symbol is not exported
+        fn.restype = res
+        fn.argtypes = args
+    if lib.scn_abi_version() != 1:
+        raise ImportError("libscn_b200.so has ABI version %d, expected 1" % lib.scn_abi_version())
+    return lib
+
+
+lib = _load()
+
+
+def check(status):
+    if status != 0:
+        raise ScnError(status, lib.scn_last_error().decode() or lib.scn_status_string(status).decode())
+
+
+def sizes(seq):
+    """Host int64 array for a spatial size / filter size / stride."""
+    vals = [int(v) for v in seq]
+    return (C.c_int64 * len(vals))(*vals)

@@ -1,0 +1,72 @@
+"""Containers (reference: sparseconvnet/sequential.py:10-33, sparseconvnet/tables.py:13-55)."""
+import torch
+
+from .sparse_tensor import SparseConvNetTensor
+
+
+class Sequential(torch.nn.Sequential):
+    def input_spatial_size(self, out_size):
+        for name in reversed(list(self._modules)):
+            out_size = self._modules[name].input_spatial_size(out_size)
+        return out_size
+
+    def add(self, module):
+        self._modules[str(len(self._modules))] = module
+        return self
+
+    def append(self, module):
+        return self.add(module)
+
+    def insert(self, index, module):
+        for i in range(len(self._modules), index, -1):
+            self._modules[str(i)] = self._modules[str(i - 1)]
+        self._modules[str(index)] = module
+
+    def __add__(self, other):
+        r = Sequential()
+        for m in self:
+            r.add(m)
+        for m in other:
+            r.add(m)
+        return r
+
+
+class ConcatTable(torch.nn.Sequential):
+    """Feeds one input to every child; returns the list of outputs."""
+
+    def forward(self, input):
+        return [module(input) for module in self._modules.values()]
+
+    def add(self, module):
+        self._modules[str(len(self._modules))] = module
+        return self
+
+    def input_spatial_size(self, out_size):
+        return self._modules["0"].input_spatial_size(out_size)
+
+
+class JoinTable(torch.nn.Sequential):
+    """Concatenates the feature planes of a list of tensors that share one set of sites."""
+
+    def forward(self, input):
+        output = SparseConvNetTensor(metadata=input[0].metadata, spatial_size=input[0].spatial_size)
+        if input[0].features.numel():
+            output.features = torch.cat([i.features for i in input], 1)
+        else:
+            output.features = input[0].features
+        return output
+
+    def input_spatial_size(self, out_size):
+        return out_size
+
+
+class AddTable(torch.nn.Sequential):
+    """Sums the features of a list of tensors that share one set of sites."""
+
+    def forward(self, input):
+        output = SparseConvNetTensor(metadata=input[0].metadata, spatial_size=input[0].spatial_size)
+        output.features = sum([i.features for i in input])
+        return output
+
+    def input_spatial_size(self, out_size):
+        return out_size

@@ -1,0 +1,95 @@
+// C-ABI entry points of the three convolution operators: rulebook lookup (built on first use
+// and cached, like the reference's Metadata), shape checks, kernel choice.
+#include "metadata.cuh"
+
+namespace scn {
+int conv_forward_simt(const float *in, long long n_in, float *out, long long n_out, const float *weight,
+                      const float *bias, const int *table, int K, int cin, int cout, int groups,
+                      int *flags, cudaStream_t stream);
+int conv_forward_tc(const float *in, long long n_in, float *out, long long n_out, const float *weight,
+                    const float *bias, const int *table, int K, int cin, int cout, int precision,
+                    int *flags, cudaStream_t stream);
+bool conv_tc_supported(int cin, int cout, int groups, int precision);
+
+static int run_conv(scn_metadata *md, Rulebook &rb, bool transposed, const float *in, float *out,
+                    const float *weight, const float *bias, int n_in_planes, int n_out_planes, int groups,
+                    int precision, cudaStream_t stream, double *macs) {
+  SCN_REQUIRE(groups >= 1 && n_in_planes >= 1 && n_out_planes >= 1 && n_in_planes % groups == 0 &&
+                  n_out_planes % groups == 0,
+              SCN_ERR_BAD_ARG, "planes %d -> %d not divisible into %d groups", n_in_planes, n_out_planes, groups);
+  SCN_REQUIRE(precision >= SCN_PRECISION_FP32 && precision <= SCN_PRECISION_BF16, SCN_ERR_BAD_ARG,
+              "unknown precision %d", precision);
+  SCN_REQUIRE(weight, SCN_ERR_BAD_ARG, "null weight");
+  int cin = n_in_planes / groups, cout = n_out_planes / groups;
+  long long rows_in = transposed ? rb.n_out : rb.n_in;
+  long long rows_out = transposed ? rb.n_in : rb.n_out;
+  const int *table = rb.nbr;
+  if (transposed) {
+    SCN_TRY(rulebook_transposed(rb, stream));
+    table = rb.tnbr;
+  }
+  if (rows_out > 0) {
+    SCN_REQUIRE(out && (in || rows_in == 0), SCN_ERR_BAD_ARG, "null features");
+    if (!md->flags_dev) {
+      SCN_TRY(device_alloc((void **)&md->flags_dev, sizeof(int), stream));
+      SCN_CUDA_CHECK(cudaMemsetAsync(md->flags_dev, 0, sizeof(int), stream));
+    }
+    if (precision != SCN_PRECISION_FP32 && conv_tc_supported(cin, cout, groups, precision))
+      SCN_TRY(conv_forward_tc(in, rows_in, out, rows_out, weight, bias, table, rb.n_offsets, cin, cout,
+                              precision, md->flags_dev, stream));
+    else
+      SCN_TRY(conv_forward_simt(in, rows_in, out, rows_out, weight, bias, table, rb.n_offsets, cin, cout,
+                                groups, md->flags_dev, stream));
+  }
+  if (macs) {  // the reference's return value: rules x ip x op x groups (CPU/Convolution.cpp:141)
+    SCN_TRY(rulebook_counts(rb, stream));
+    *macs = (double)rb.total_rules * cin * cout * groups;
+  }
+  return SCN_OK;
+}
+}  // namespace scn
+
+using namespace scn;
+
+extern "C" {
+
+int scn_submanifold_convolution_forward(scn_metadata *md, const int64_t *spatial_size,
+                                        const int64_t *filter_size, const float *in_features,
+                                        float *out_features, const float *weight, const float *bias,
+                                        int n_in_planes, int n_out_planes, int groups, int precision,
+                                        void *stream_, double *macs) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SCN_REQUIRE(md && spatial_size && filter_size, SCN_ERR_BAD_ARG, "null argument");
+  Rulebook *rb = nullptr;
+  SCN_TRY(get_submanifold_rulebook(md, spatial_size, filter_size, stream, &rb));
+  return run_conv(md, *rb, false, in_features, out_features, weight, bias, n_in_planes, n_out_planes,
+                  groups, precision, stream, macs);
+}
+
+int scn_convolution_forward(scn_metadata *md, const int64_t *input_size, const int64_t *output_size,
+                            const int64_t *filter_size, const int64_t *filter_stride,
+                            const float *in_features, float *out_features, const float *weight,
+                            const float *bias, int n_in_planes, int n_out_planes, int groups,
+                            int precision, void *stream_, double *macs) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SCN_REQUIRE(md && input_size && output_size && filter_size && filter_stride, SCN_ERR_BAD_ARG, "null argument");
+  Rulebook *rb = nullptr;
+  SCN_TRY(get_strided_rulebook(md, input_size, output_size, filter_size, filter_stride, stream, &rb));
+  return run_conv(md, *rb, false, in_features, out_features, weight, bias, n_in_planes, n_out_planes,
+                  groups, precision, stream, macs);
+}
+
+int scn_deconvolution_forward(scn_metadata *md, const int64_t *input_size, const int64_t *output_size,
+                              const int64_t *filter_size, const int64_t *filter_stride,
+                              const float *in_features, float *out_features, const float *weight,
+                              const float *bias, int n_in_planes, int n_out_planes, int groups,
+                              int precision, void *stream_, double *macs) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SCN_REQUIRE(md && input_size && output_size && filter_size && filter_stride, SCN_ERR_BAD_ARG, "null argument");
+  Rulebook *rb = nullptr;
+  // the rulebook of the matching Convolution: fine (this op's output) -> coarse (this op's input)
+  SCN_TRY(get_strided_rulebook(md, output_size, input_size, filter_size, filter_stride, stream, &rb));
+  return run_conv(md, *rb, true, in_features, out_features, weight, bias, n_in_planes, n_out_planes,
+                  groups, precision, stream, macs);
+}
+}

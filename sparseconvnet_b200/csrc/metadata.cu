@@ -1,0 +1,898 @@
+// The Metadata object: GPU site hash per spatial scale and the rulebook builders.
+//
+// Replaces, with device kernels and no host round trip for the rules themselves,
+//   Metadata<D>::inputLayer / inputLayerRules     (Metadata.cpp:413-425, IOLayersRules.h:18-121)
+//   Metadata<D>::getSubmanifoldRuleBook           (Metadata.cpp:437-451,
+//                                                  SubmanifoldConvolutionRules.h:11-87)
+//   Metadata<D>::getRuleBook                      (Metadata.cpp:492-518, ConvolutionRules.h:11-105,
+//                                                  RectangularRegions.h:94-119)
+//   Metadata<D>::getSpatialLocations              (Metadata.cpp:149-170)
+// of the reference.  Only counts (active sites, rules per offset) ever travel to the host.
+#include <algorithm>
+#include <climits>
+
+#include "metadata.cuh"
+
+namespace scn {
+
+// ------------------------------------------------------------------------------------------
+// key layout
+// ------------------------------------------------------------------------------------------
+
+static int make_layout(int dim, const int64_t *size, KeyLayout &L) {
+  L = KeyLayout{};
+  L.dim = dim;
+  int sh = 0;
+  for (int d = dim - 1; d >= 0; --d) {  // last dimension in the lowest bits
+    SCN_REQUIRE(size[d] >= 1 && size[d] <= INT_MAX, SCN_ERR_BAD_ARG,
+                "spatial size[%d]=%lld out of range", d, (long long)size[d]);
+    int bits = std::max(1, bit_length((unsigned long long)size[d] - 1));
+    L.shift[d] = sh;
+    L.bits[d] = bits;
+    L.size[d] = (int)size[d];
+    sh += bits;
+  }
+  SCN_REQUIRE(sh <= 62, SCN_ERR_KEY_BITS, "spatial size needs %d key bits (max 62)", sh);
+  L.batch_shift = sh;
+  L.batch_bits = std::min(31, 63 - sh);
+  return SCN_OK;
+}
+
+std::vector<int64_t> make_key(int dim, const int64_t *a, const int64_t *b, const int64_t *c) {
+  std::vector<int64_t> k(a, a + dim);
+  if (b) k.insert(k.end(), b, b + dim);
+  if (c) k.insert(k.end(), c, c + dim);
+  return k;
+}
+
+Grid *find_grid(scn_metadata *md, const int64_t *spatial_size) {
+  auto it = md->grids.find(make_key(md->dim, spatial_size));
+  return it == md->grids.end() ? nullptr : &it->second;
+}
+
+static int alloc_table(HashTable &T, long long expected_sites, cudaStream_t stream) {
+  unsigned long long slots = next_pow2((unsigned long long)std::max<long long>(64, 2 * expected_sites));
+  SCN_REQUIRE(slots < (1ull << 31), SCN_ERR_UNSUPPORTED, "site table too large (%llu slots)", slots);
+  T.n_buckets = slots / 2;
+  SCN_TRY(device_alloc((void **)&T.slots, slots * sizeof(Slot), stream));
+  // key = all ones (free), row = -1, aux = 0xFFFFFFFF
+  SCN_CUDA_CHECK(cudaMemsetAsync(T.slots, 0xFF, slots * sizeof(Slot), stream));
+  return SCN_OK;
+}
+
+static void free_grid(Grid &g, cudaStream_t stream) {
+  device_free(g.row_keys, stream);
+  device_free(g.table.slots, stream);
+  g = Grid{};
+}
+static void free_rulebook(Rulebook &r, cudaStream_t stream) {
+  device_free(r.nbr, stream);
+  device_free(r.tnbr, stream);
+  device_free(r.counts_dev, stream);
+  r = Rulebook{};
+}
+
+static int ensure_scratch(scn_metadata *md, cudaStream_t stream) {
+  if (!md->flags_dev) {
+    SCN_TRY(device_alloc((void **)&md->flags_dev, sizeof(int), stream));
+    SCN_CUDA_CHECK(cudaMemsetAsync(md->flags_dev, 0, sizeof(int), stream));
+  }
+  if (!md->scalars_dev) SCN_TRY(device_alloc((void **)&md->scalars_dev, 4 * sizeof(int), stream));
+  return SCN_OK;
+}
+
+// Reads (and clears) the device flag word; waits for the stream.
+static int fetch_flags(scn_metadata *md, cudaStream_t stream, int *flags, int *scalars4) {
+  int host[5] = {0, 0, 0, 0, 0};
+  SCN_CUDA_CHECK(cudaMemcpyAsync(&host[0], md->flags_dev, sizeof(int), cudaMemcpyDeviceToHost, stream));
+  if (scalars4)
+    SCN_CUDA_CHECK(cudaMemcpyAsync(&host[1], md->scalars_dev, 4 * sizeof(int), cudaMemcpyDeviceToHost, stream));
+  SCN_CUDA_CHECK(cudaMemsetAsync(md->flags_dev, 0, sizeof(int), stream));
+  SCN_CUDA_CHECK(cudaStreamSynchronize(stream));
+  *flags = host[0];
+  if (scalars4)
+    for (int i = 0; i < 4; ++i) scalars4[i] = host[1 + i];
+  return SCN_OK;
+}
+
+static int flags_to_status(int flags) {
+  if (flags & FLAG_COORD_RANGE) {
+    set_error("a coordinate or batch index lies outside the spatial size");
+    return SCN_ERR_COORD_RANGE;
+  }
+  if (flags & FLAG_TABLE_FULL) {
+    set_error("site hash probe limit reached");
+    return SCN_ERR_TABLE_FULL;
+  }
+  if (flags & FLAG_BAD_ROW) {
+    set_error("a rulebook entry points outside the feature matrix");
+    return SCN_ERR_SIZE_MISMATCH;
+  }
+  return SCN_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// input layer
+// ------------------------------------------------------------------------------------------
+
+// One thread per input row: range-check, pack, insert.  mode 0 keeps the largest row index
+// per site (the reference's serial `mp[p] = i` leaves the last writer, IOLayersRules.h:41,55);
+// the other modes record the first row that touched the site.
+__global__ void k_insert_input(KeyLayout L, HashTable T, const long long *__restrict__ coords,
+                               long long n, int ncols, int mode,
+                               unsigned long long *__restrict__ row_keys, int *__restrict__ slot_of,
+                               int *flags, int *scalars) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const long long *c = coords + i * ncols;
+  int x[kMaxDim];
+  bool ok = true;
+  for (int d = 0; d < L.dim; ++d) {
+    long long v = c[d];
+    ok &= (v >= 0 && v < L.size[d]);
+    x[d] = (int)v;
+  }
+  long long bl = (ncols > L.dim) ? c[L.dim] : 0;
+  ok &= (bl >= 0 && bl < (1ll << L.batch_bits));
+  if (!ok) {
+    atomicOr(flags, FLAG_COORD_RANGE);
+    if (mode == 0) row_keys[i] = kEmptyKey;
+    slot_of[i] = -1;
+    return;
+  }
+  unsigned long long key = pack_key(L, x, (int)bl);
+  long long s = hash_insert(T, key);
+  if (s < 0) {
+    atomicOr(flags, FLAG_TABLE_FULL);
+    if (mode == 0) row_keys[i] = kEmptyKey;
+    slot_of[i] = -1;
+    return;
+  }
+  atomicMax(&scalars[1], (int)bl);
+  slot_of[i] = (int)s;
+  if (mode == 0) {
+    row_keys[i] = key;
+    atomicMax(&T.slots[s].row, (int)i);
+  } else {
+    atomicMin(&T.slots[s].aux, (unsigned)i);
+  }
+}
+
+// Input mode 0 with repeated coordinates: the site belongs to the last row that named it.
+// Earlier rows keep their feature row but are in no map of the reference, so no rule ever
+// touches them and getSpatialLocations leaves them zero; here their key is blanked.
+__global__ void k_blank_overwritten(const Slot *__restrict__ slots, const int *__restrict__ slot_of,
+                                    long long n, unsigned long long *__restrict__ row_keys) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  int s = slot_of[i];
+  if (s >= 0 && slots[s].row != (int)i) row_keys[i] = kEmptyKey;
+}
+
+__global__ void k_flag_first(const Slot *__restrict__ slots, const int *__restrict__ slot_of,
+                             long long n, int *__restrict__ flag) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  int s = slot_of[i];
+  flag[i] = (s >= 0 && slots[s].aux == (unsigned)i) ? 1 : 0;
+}
+
+// Rows that were the first to touch their site give the site its output row number (rank in
+// input order), which is the numbering of the reference (one counter over the whole input,
+// IOLayersRules.h:69-72,84-87).
+__global__ void k_number_input_sites(Slot *slots, const int *__restrict__ slot_of,
+                                     const int *__restrict__ flag, const int *__restrict__ rank,
+                                     long long n, unsigned long long *__restrict__ row_keys) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n || !flag[i]) return;
+  int s = slot_of[i];
+  int r = rank[i];
+  slots[s].row = r;
+  row_keys[r] = slots[s].key;
+}
+
+__global__ void k_count_per_site(const Slot *__restrict__ slots, const int *__restrict__ slot_of,
+                                 long long n, int *cnt) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  int s = slot_of[i];
+  if (s >= 0) atomicAdd(&cnt[slots[s].row], 1);
+}
+
+__global__ void k_fill_per_site(const Slot *__restrict__ slots, const int *__restrict__ slot_of,
+                                long long n, const int *__restrict__ start, int *cursor,
+                                int *__restrict__ csr_rows) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  int s = slot_of[i];
+  if (s < 0) return;
+  int r = slots[s].row;
+  int p = atomicAdd(&cursor[r], 1);
+  csr_rows[start[r] + p] = (int)i;
+}
+
+// Puts the input rows of every site in ascending order (heap sort, in place, one thread per
+// site; sites with duplicates hold a handful of rows).
+__global__ void k_sort_segments(const int *__restrict__ start, long long n_sites, int *csr_rows) {
+  long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= n_sites) return;
+  int *a = csr_rows + start[r];
+  int m = start[r + 1] - start[r];
+  if (m < 2) return;
+  if (m <= 16) {
+    for (int i = 1; i < m; ++i) {
+      int v = a[i], j = i - 1;
+      while (j >= 0 && a[j] > v) {
+        a[j + 1] = a[j];
+        --j;
+      }
+      a[j + 1] = v;
+    }
+    return;
+  }
+  for (int root0 = m / 2 - 1; root0 >= 0; --root0) {
+    int root = root0;
+    for (;;) {
+      int child = 2 * root + 1;
+      if (child >= m) break;
+      if (child + 1 < m && a[child] < a[child + 1]) ++child;
+      if (a[root] >= a[child]) break;
+      int t = a[root]; a[root] = a[child]; a[child] = t;
+      root = child;
+    }
+  }
+  for (int end = m - 1; end > 0; --end) {
+    int t = a[0]; a[0] = a[end]; a[end] = t;
+    int root = 0;
+    for (;;) {
+      int child = 2 * root + 1;
+      if (child >= end) break;
+      if (child + 1 < end && a[child] < a[child + 1]) ++child;
+      if (a[root] >= a[child]) break;
+      int u = a[root]; a[root] = a[child]; a[child] = u;
+      root = child;
+    }
+  }
+}
+
+__global__ void k_init_scalars(int *scalars) {
+  scalars[0] = 0;
+  scalars[1] = -1;
+  scalars[2] = 0;
+  scalars[3] = 0;
+}
+
+static void clear_input_rules(scn_metadata *md, cudaStream_t stream) {
+  device_free(md->input_csr_start, stream);
+  device_free(md->input_csr_rows, stream);
+  md->input_csr_start = md->input_csr_rows = nullptr;
+  md->input_mode = -1;
+  md->input_n_rows = md->input_n_active = 0;
+}
+
+static int md_clear(scn_metadata *md, cudaStream_t stream) {
+  for (auto &g : md->grids) free_grid(g.second, stream);
+  for (auto &r : md->sub_rules) free_rulebook(r.second, stream);
+  for (auto &r : md->strided_rules) free_rulebook(r.second, stream);
+  md->grids.clear();
+  md->sub_rules.clear();
+  md->strided_rules.clear();
+  clear_input_rules(md, stream);
+  return SCN_OK;
+}
+
+static int md_input_layer(scn_metadata *md, const int64_t *spatial_size, const int64_t *coords,
+                          int coords_on_device, int64_t n, int ncols, int64_t batch_size, int mode,
+                          cudaStream_t stream, int64_t *n_active) {
+  SCN_REQUIRE(md && spatial_size && n_active, SCN_ERR_BAD_ARG, "null argument");
+  SCN_REQUIRE(mode >= 0 && mode <= 4, SCN_ERR_BAD_ARG, "input layer mode %d not in 0..4", mode);
+  SCN_REQUIRE(ncols == md->dim || ncols == md->dim + 1, SCN_ERR_BAD_ARG,
+              "coords must have %d or %d columns, got %d", md->dim, md->dim + 1, ncols);
+  SCN_REQUIRE(n >= 0 && n < (1ll << 30), SCN_ERR_UNSUPPORTED, "row count %lld unsupported", (long long)n);
+  SCN_REQUIRE(n == 0 || coords, SCN_ERR_BAD_ARG, "null coords");
+  SCN_TRY(ensure_scratch(md, stream));
+
+  auto key = make_key(md->dim, spatial_size);
+  auto old = md->grids.find(key);
+  if (old != md->grids.end()) {
+    free_grid(old->second, stream);
+    md->grids.erase(old);
+  }
+  clear_input_rules(md, stream);
+
+  Grid g;
+  SCN_TRY(make_layout(md->dim, spatial_size, g.layout));
+  SCN_TRY(alloc_table(g.table, n, stream));
+  SCN_TRY(device_alloc((void **)&g.row_keys, sizeof(unsigned long long) * (size_t)std::max<int64_t>(n, 1), stream));
+
+  const long long *coords_dev = (const long long *)coords;
+  long long *staged = nullptr;
+  if (!coords_on_device && n > 0) {
+    size_t bytes = sizeof(long long) * (size_t)n * ncols;
+    SCN_TRY(device_alloc((void **)&staged, bytes, stream));
+    SCN_CUDA_CHECK(cudaMemcpyAsync(staged, coords, bytes, cudaMemcpyHostToDevice, stream));
+    coords_dev = staged;
+  }
+
+  const int threads = 256;
+  unsigned blocks = (unsigned)ceil_div(std::max<int64_t>(n, 1), threads);
+  k_init_scalars<<<1, 1, 0, stream>>>(md->scalars_dev);
+  int *slot_of = nullptr, *flag = nullptr, *rank = nullptr, *cursor = nullptr;
+  SCN_TRY(device_alloc((void **)&slot_of, sizeof(int) * (size_t)std::max<int64_t>(n, 1), stream));
+  if (n > 0) {
+    k_insert_input<<<blocks, threads, 0, stream>>>(g.layout, g.table, coords_dev, n, ncols, mode,
+                                                   g.row_keys, slot_of, md->flags_dev, md->scalars_dev);
+    if (mode == 0)
+      k_blank_overwritten<<<blocks, threads, 0, stream>>>(g.table.slots, slot_of, n, g.row_keys);
+    SCN_CUDA_CHECK(cudaGetLastError());
+  }
+  if (mode != 0 && n > 0) {
+    SCN_TRY(device_alloc((void **)&flag, sizeof(int) * (size_t)n, stream));
+    SCN_TRY(device_alloc((void **)&rank, sizeof(int) * (size_t)n, stream));
+    k_flag_first<<<blocks, threads, 0, stream>>>(g.table.slots, slot_of, n, flag);
+    SCN_TRY(exclusive_scan_i32(flag, rank, n, &md->scalars_dev[0], stream));
+    k_number_input_sites<<<blocks, threads, 0, stream>>>(g.table.slots, slot_of, flag, rank, n, g.row_keys);
+    SCN_CUDA_CHECK(cudaGetLastError());
+    // CSR of input rows per site
+    SCN_TRY(device_alloc((void **)&md->input_csr_start, sizeof(int) * (size_t)(n + 1), stream));
+    SCN_TRY(device_alloc((void **)&md->input_csr_rows, sizeof(int) * (size_t)n, stream));
+    SCN_TRY(device_alloc((void **)&cursor, sizeof(int) * (size_t)(n + 1), stream));
+    SCN_CUDA_CHECK(cudaMemsetAsync(cursor, 0, sizeof(int) * (size_t)(n + 1), stream));
+    k_count_per_site<<<blocks, threads, 0, stream>>>(g.table.slots, slot_of, n, cursor);
+    SCN_TRY(exclusive_scan_i32(cursor, md->input_csr_start, n + 1, nullptr, stream));
+    SCN_CUDA_CHECK(cudaMemsetAsync(cursor, 0, sizeof(int) * (size_t)(n + 1), stream));
+    k_fill_per_site<<<blocks, threads, 0, stream>>>(g.table.slots, slot_of, n, md->input_csr_start,
+                                                    cursor, md->input_csr_rows);
+    SCN_CUDA_CHECK(cudaGetLastError());
+  }
+
+  int flags = 0, sc[4];
+  SCN_TRY(fetch_flags(md, stream, &flags, sc));
+  long long active = (mode == 0) ? n : (n > 0 ? sc[0] : 0);
+  if (mode != 0 && n > 0 && flags == 0 && active > 0) {
+    unsigned sblocks = (unsigned)ceil_div(active, threads);
+    k_sort_segments<<<sblocks, threads, 0, stream>>>(md->input_csr_start, active, md->input_csr_rows);
+    SCN_CUDA_CHECK(cudaGetLastError());
+  }
+  device_free(staged, stream);
+  device_free(slot_of, stream);
+  device_free(flag, stream);
+  device_free(rank, stream);
+  device_free(cursor, stream);
+  int st = flags_to_status(flags);
+  if (st != SCN_OK) {
+    free_grid(g, stream);
+    clear_input_rules(md, stream);
+    return st;
+  }
+  g.n_active = active;
+  // batch size: IOLayersRules.h:25,35,52-53 -- one sample when there is no batch column,
+  // otherwise max(requested, largest index + 1)
+  if (ncols == md->dim)
+    g.batch_size = 1;
+  else
+    g.batch_size = std::max<long long>(batch_size, (long long)sc[1] + 1);
+  md->input_mode = mode;
+  md->input_n_rows = n;
+  md->input_n_active = active;
+  md->grids[key] = g;
+  *n_active = active;
+  return SCN_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// spatial locations
+// ------------------------------------------------------------------------------------------
+
+// Row r -> (x_0..x_{D-1}, batch).  A row with a blank key (an earlier duplicate under input
+// mode 0) is reported as zeros, as the reference leaves it (Metadata.cpp:154-168 writes only
+// rows reachable from the maps).
+__global__ void k_spatial_locations(KeyLayout L, const unsigned long long *__restrict__ row_keys,
+                                    long long n, long long *__restrict__ out) {
+  long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= n) return;
+  unsigned long long key = row_keys[r];
+  long long *o = out + r * (L.dim + 1);
+  bool live = (key != kEmptyKey);
+  int x[kMaxDim], b = 0;
+  if (live) unpack_key(L, key, x, b);
+  for (int d = 0; d < L.dim; ++d) o[d] = live ? x[d] : 0;
+  o[L.dim] = live ? b : 0;
+}
+
+// ------------------------------------------------------------------------------------------
+// submanifold rulebook
+// ------------------------------------------------------------------------------------------
+
+struct FilterDesc {
+  int f[kMaxDim];  // filter size
+  int s[kMaxDim];  // stride (strided rules only)
+  int out_size[kMaxDim];
+  int tdim[kMaxDim];  // outputs an input can feed per dimension: ceil(f / s)
+  int tmax;
+};
+
+// One thread per output site, looping over this block's range of filter offsets.  Offset k
+// (row-major over the filter, last dimension fastest, RectangularRegions.h:30-38) looks at
+// input = output + delta_k with delta = k_d - f_d / 2 (SubmanifoldConvolutionRules.h:15-19).
+// The neighbour's key is the site's key plus a per-offset constant, so a probe is a bounds
+// check, one 64-bit add and one 32-byte bucket read.
+__global__ void __launch_bounds__(256)
+k_submanifold_rules(KeyLayout L, HashTable T, const unsigned long long *__restrict__ row_keys,
+                    long long n, int K, FilterDesc F, int k_chunk, int *__restrict__ nbr,
+                    unsigned long long *counts) {
+  extern __shared__ long long sh_raw[];
+  long long *sh_keydelta = sh_raw;                         // [k_chunk]
+  int *sh_count = (int *)(sh_keydelta + k_chunk);          // [k_chunk]
+  signed char *sh_delta = (signed char *)(sh_count + k_chunk);  // [k_chunk][dim]
+  int k0 = blockIdx.y * k_chunk;
+  int k1 = min(K, k0 + k_chunk);
+  for (int kk = k0 + threadIdx.x; kk < k1; kk += blockDim.x) {
+    int rem = kk;
+    long long kd = 0;
+    for (int d = L.dim - 1; d >= 0; --d) {
+      int delta = rem % F.f[d] - F.f[d] / 2;
+      rem /= F.f[d];
+      sh_delta[(kk - k0) * L.dim + d] = (signed char)delta;
+      kd += (long long)delta * (1ll << L.shift[d]);
+    }
+    sh_keydelta[kk - k0] = kd;
+    sh_count[kk - k0] = 0;
+  }
+  __syncthreads();
+  long long site = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  bool active = site < n;
+  unsigned long long key = active ? row_keys[site] : kEmptyKey;
+  active = active && (key != kEmptyKey);  // blank key: overwritten duplicate, in no map
+  int x[kMaxDim], b = 0;
+  if (active) unpack_key(L, key, x, b);
+  for (int kk = k0; kk < k1; ++kk) {
+    int row = -1;
+    if (active) {
+      bool ok = true;
+      const signed char *dl = sh_delta + (kk - k0) * L.dim;
+      for (int d = 0; d < L.dim; ++d) {
+        int y = x[d] + dl[d];
+        ok &= ((unsigned)y < (unsigned)L.size[d]);
+      }
+      if (ok) row = hash_find_row(T, key + (unsigned long long)sh_keydelta[kk - k0]);
+    }
+    if (site < n) nbr[(long long)kk * n + site] = row;
+    unsigned hits = __ballot_sync(0xffffffffu, row >= 0);
+    if ((threadIdx.x & 31) == 0 && hits) atomicAdd(&sh_count[kk - k0], __popc(hits));
+  }
+  __syncthreads();
+  for (int kk = k0 + threadIdx.x; kk < k1; kk += blockDim.x)
+    if (sh_count[kk - k0]) atomicAdd(&counts[kk], (unsigned long long)sh_count[kk - k0]);
+}
+
+int get_submanifold_rulebook(scn_metadata *md, const int64_t *spatial_size,
+                             const int64_t *filter_size, cudaStream_t stream, Rulebook **out) {
+  auto key = make_key(md->dim, spatial_size, filter_size);
+  Rulebook &rb = md->sub_rules[key];
+  *out = &rb;
+  if (rb.built) return SCN_OK;
+  Grid *g = find_grid(md, spatial_size);
+  if (!g) {
+    md->sub_rules.erase(key);
+    set_error("submanifold rulebook: no grid for that spatial size");
+    return SCN_ERR_NO_GRID;
+  }
+  long long K = 1;
+  FilterDesc F{};
+  for (int d = 0; d < md->dim; ++d) {
+    SCN_REQUIRE(filter_size[d] >= 1 && filter_size[d] <= 127, SCN_ERR_UNSUPPORTED,
+                "filter size %lld unsupported", (long long)filter_size[d]);
+    F.f[d] = (int)filter_size[d];
+    K *= filter_size[d];
+  }
+  SCN_REQUIRE(K <= 4096, SCN_ERR_UNSUPPORTED, "filter volume %lld unsupported", K);
+  long long n = g->n_active;
+  SCN_REQUIRE(K * std::max<long long>(n, 1) < (1ll << 40), SCN_ERR_UNSUPPORTED, "rulebook too large");
+  rb.n_offsets = (int)K;
+  rb.n_in = rb.n_out = n;
+  SCN_TRY(device_alloc((void **)&rb.nbr, sizeof(int) * (size_t)(K * std::max<long long>(n, 1)), stream));
+  SCN_TRY(device_alloc((void **)&rb.counts_dev, sizeof(unsigned long long) * (size_t)K, stream));
+  SCN_CUDA_CHECK(cudaMemsetAsync(rb.counts_dev, 0, sizeof(unsigned long long) * (size_t)K, stream));
+  if (n > 0) {
+    const int threads = 256;
+    long long bx = ceil_div(n, threads);
+    // enough blocks to fill the machine even for few sites: split the offsets over grid.y
+    long long want_y = std::max<long long>(1, std::min<long long>(K, ceil_div(148 * 16, bx)));
+    int k_chunk = (int)ceil_div(K, want_y);
+    int gy = (int)ceil_div(K, k_chunk);
+    size_t smem = (size_t)k_chunk * (sizeof(long long) + sizeof(int) + md->dim);
+    k_submanifold_rules<<<dim3((unsigned)bx, (unsigned)gy), threads, smem, stream>>>(
+        g->layout, g->table, g->row_keys, n, (int)K, F, k_chunk, rb.nbr, rb.counts_dev);
+    SCN_CUDA_CHECK(cudaGetLastError());
+  }
+  rb.built = true;
+  return SCN_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// strided rulebook (Convolution / MaxPooling; Deconvolution reads it transposed)
+// ------------------------------------------------------------------------------------------
+
+// For input site x and candidate t in [0, tmax): the t-th output (row-major over the output
+// region, last dimension fastest) that x feeds, and the filter offset it feeds it through.
+// Output region per dimension: lb = max(0, (x - f + s) / s), ub = min(out - 1, x / s)
+// (RectangularRegions.h:108-119); offset = sum (x_d - o_d * s_d) * prod_{j>d} f_j
+// (RectangularRegions.h:30-38,94-105).
+__device__ inline bool strided_target(const KeyLayout &L, const FilterDesc &F, const int *x, int t,
+                                      int *o, int &k) {
+  k = 0;
+  int mult = 1;
+  for (int d = L.dim - 1; d >= 0; --d) {
+    int num = x[d] - F.f[d] + F.s[d];
+    int lb = num > 0 ? num / F.s[d] : 0;
+    int ub = min(F.out_size[d] - 1, x[d] / F.s[d]);
+    int j = t % F.tdim[d];
+    t /= F.tdim[d];
+    int od = lb + j;
+    if (od > ub) return false;
+    o[d] = od;
+    k += (x[d] - od * F.s[d]) * mult;
+    mult *= F.f[d];
+  }
+  return true;
+}
+
+__global__ void k_strided_insert(KeyLayout Lin, KeyLayout Lout, FilterDesc F, HashTable Tout,
+                                 const unsigned long long *__restrict__ in_keys, long long n_in,
+                                 int *__restrict__ slot_of, int *flags) {
+  long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (id >= n_in * F.tmax) return;
+  long long i = id / F.tmax;
+  int t = (int)(id % F.tmax);
+  unsigned long long key = in_keys[i];
+  int s_out = -1;
+  if (key != kEmptyKey) {
+    int x[kMaxDim], o[kMaxDim], b, k;
+    unpack_key(Lin, key, x, b);
+    if (strided_target(Lin, F, x, t, o, k)) {
+      long long s = hash_insert(Tout, pack_key(Lout, o, b));
+      if (s < 0)
+        atomicOr(flags, FLAG_TABLE_FULL);
+      else {
+        s_out = (int)s;
+        atomicMin(&Tout.slots[s].aux, (unsigned)id);
+      }
+    }
+  }
+  slot_of[id] = s_out;
+}
+
+__global__ void k_strided_number(Slot *slots, const int *__restrict__ slot_of,
+                                 const int *__restrict__ flag, const int *__restrict__ rank,
+                                 long long n_ids, unsigned long long *__restrict__ out_keys) {
+  long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (id >= n_ids || !flag[id]) return;
+  int s = slot_of[id];
+  int r = rank[id];
+  slots[s].row = r;
+  out_keys[r] = slots[s].key;
+}
+
+__global__ void k_strided_fill(KeyLayout Lin, FilterDesc F, const Slot *__restrict__ slots,
+                               const unsigned long long *__restrict__ in_keys,
+                               const int *__restrict__ slot_of, long long n_in, long long n_out,
+                               int *__restrict__ nbr, unsigned long long *counts) {
+  long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (id >= n_in * F.tmax) return;
+  int s = slot_of[id];
+  if (s < 0) return;
+  long long i = id / F.tmax;
+  int t = (int)(id % F.tmax);
+  int x[kMaxDim], o[kMaxDim], b, k;
+  unpack_key(Lin, in_keys[i], x, b);
+  strided_target(Lin, F, x, t, o, k);
+  int orow = slots[s].row;
+  nbr[(long long)k * n_out + orow] = (int)i;
+  // one counter update per distinct offset in the warp
+  unsigned peers = __match_any_sync(__activemask(), k);
+  if ((int)(threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&counts[k], (unsigned long long)__popc(peers));
+}
+
+int get_strided_rulebook(scn_metadata *md, const int64_t *input_size, const int64_t *output_size,
+                         const int64_t *filter_size, const int64_t *filter_stride,
+                         cudaStream_t stream, Rulebook **out) {
+  auto key = make_key(md->dim, input_size, filter_size, filter_stride);
+  Rulebook &rb = md->strided_rules[key];
+  *out = &rb;
+  if (rb.built) return SCN_OK;
+  Grid *gin = find_grid(md, input_size);
+  if (!gin) {
+    md->strided_rules.erase(key);
+    set_error("strided rulebook: no grid for the input spatial size");
+    return SCN_ERR_NO_GRID;
+  }
+  SCN_TRY(ensure_scratch(md, stream));
+  FilterDesc F{};
+  long long K = 1;
+  F.tmax = 1;
+  for (int d = 0; d < md->dim; ++d) {
+    SCN_REQUIRE(filter_size[d] >= 1 && filter_size[d] <= 127 && filter_stride[d] >= 1 &&
+                    filter_stride[d] <= 127 && output_size[d] >= 1 && output_size[d] <= INT_MAX,
+                SCN_ERR_UNSUPPORTED, "filter/stride/output size unsupported");
+    F.f[d] = (int)filter_size[d];
+    F.s[d] = (int)filter_stride[d];
+    F.out_size[d] = (int)output_size[d];
+    F.tdim[d] = (int)ceil_div(filter_size[d], filter_stride[d]);
+    F.tmax *= F.tdim[d];
+    K *= filter_size[d];
+  }
+  SCN_REQUIRE(K <= 4096 && F.tmax <= 4096, SCN_ERR_UNSUPPORTED, "filter volume unsupported");
+  long long n_in = gin->n_active;
+  long long n_ids = n_in * F.tmax;
+  SCN_REQUIRE(n_ids < (1ll << 31), SCN_ERR_UNSUPPORTED, "too many (site, output) candidates");
+
+  auto okey = make_key(md->dim, output_size);
+  auto old = md->grids.find(okey);
+  if (old != md->grids.end()) {
+    free_grid(old->second, stream);
+    md->grids.erase(old);
+  }
+  Grid gout;
+  SCN_TRY(make_layout(md->dim, output_size, gout.layout));
+  SCN_REQUIRE(gout.layout.batch_bits >= gin->layout.batch_bits ||
+                  gin->batch_size <= (1ll << gout.layout.batch_bits),
+              SCN_ERR_KEY_BITS, "batch index does not fit the output key");
+  gout.batch_size = gin->batch_size;
+
+  const int threads = 256;
+  int *slot_of = nullptr, *flag = nullptr, *rank = nullptr;
+  long long n_out = 0;
+  if (n_ids > 0) {
+    SCN_TRY(device_alloc((void **)&slot_of, sizeof(int) * (size_t)n_ids, stream));
+    SCN_TRY(device_alloc((void **)&flag, sizeof(int) * (size_t)n_ids, stream));
+    SCN_TRY(device_alloc((void **)&rank, sizeof(int) * (size_t)n_ids, stream));
+    unsigned blocks = (unsigned)ceil_div(n_ids, threads);
+    long long expect = n_in;
+    for (int attempt = 0;; ++attempt) {
+      SCN_TRY(alloc_table(gout.table, expect, stream));
+      k_strided_insert<<<blocks, threads, 0, stream>>>(gin->layout, gout.layout, F, gout.table,
+                                                       gin->row_keys, n_in, slot_of, md->flags_dev);
+      k_flag_first<<<blocks, threads, 0, stream>>>(gout.table.slots, slot_of, n_ids, flag);
+      SCN_TRY(exclusive_scan_i32(flag, rank, n_ids, &md->scalars_dev[0], stream));
+      SCN_CUDA_CHECK(cudaGetLastError());
+      int flags = 0, sc[4];
+      SCN_TRY(fetch_flags(md, stream, &flags, sc));
+      if ((flags & FLAG_TABLE_FULL) && attempt < 3) {  // more coarse sites than guessed: grow
+        device_free(gout.table.slots, stream);
+        gout.table = HashTable{};
+        expect *= 4;
+        continue;
+      }
+      int st = flags_to_status(flags);
+      if (st != SCN_OK) {
+        device_free(slot_of, stream);
+        device_free(flag, stream);
+        device_free(rank, stream);
+        free_grid(gout, stream);
+        md->strided_rules.erase(key);
+        return st;
+      }
+      n_out = sc[0];
+      break;
+    }
+  } else {
+    SCN_TRY(alloc_table(gout.table, 0, stream));
+  }
+  gout.n_active = n_out;
+  SCN_TRY(device_alloc((void **)&gout.row_keys, sizeof(unsigned long long) * (size_t)std::max<long long>(n_out, 1), stream));
+  rb.n_offsets = (int)K;
+  rb.n_in = n_in;
+  rb.n_out = n_out;
+  size_t nbr_bytes = sizeof(int) * (size_t)(K * std::max<long long>(n_out, 1));
+  SCN_TRY(device_alloc((void **)&rb.nbr, nbr_bytes, stream));
+  SCN_CUDA_CHECK(cudaMemsetAsync(rb.nbr, 0xFF, nbr_bytes, stream));
+  SCN_TRY(device_alloc((void **)&rb.counts_dev, sizeof(unsigned long long) * (size_t)K, stream));
+  SCN_CUDA_CHECK(cudaMemsetAsync(rb.counts_dev, 0, sizeof(unsigned long long) * (size_t)K, stream));
+  if (n_ids > 0) {
+    unsigned blocks = (unsigned)ceil_div(n_ids, threads);
+    k_strided_number<<<blocks, threads, 0, stream>>>(gout.table.slots, slot_of, flag, rank, n_ids, gout.row_keys);
+    k_strided_fill<<<blocks, threads, 0, stream>>>(gin->layout, F, gout.table.slots, gin->row_keys,
+                                                   slot_of, n_in, n_out, rb.nbr, rb.counts_dev);
+    SCN_CUDA_CHECK(cudaGetLastError());
+  }
+  device_free(slot_of, stream);
+  device_free(flag, stream);
+  device_free(rank, stream);
+  md->grids[okey] = gout;
+  rb.built = true;
+  return SCN_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// rulebook views
+// ------------------------------------------------------------------------------------------
+
+int rulebook_counts(Rulebook &rb, cudaStream_t stream) {
+  if (rb.total_rules >= 0) return SCN_OK;
+  std::vector<unsigned long long> h(rb.n_offsets);
+  SCN_CUDA_CHECK(cudaMemcpyAsync(h.data(), rb.counts_dev, sizeof(unsigned long long) * rb.n_offsets,
+                                 cudaMemcpyDeviceToHost, stream));
+  SCN_CUDA_CHECK(cudaStreamSynchronize(stream));
+  rb.counts_host.assign(h.begin(), h.end());
+  long long t = 0;
+  for (auto c : rb.counts_host) t += c;
+  rb.total_rules = t;
+  return SCN_OK;
+}
+
+__global__ void k_transpose_rules(const int *__restrict__ nbr, long long n_out, long long n_in, int K,
+                                  int *__restrict__ tnbr) {
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)K * n_out) return;
+  int i = nbr[idx];
+  if (i < 0) return;
+  long long k = idx / n_out, o = idx % n_out;
+  tnbr[k * n_in + i] = (int)o;
+}
+
+int rulebook_transposed(Rulebook &rb, cudaStream_t stream) {
+  if (rb.tnbr) return SCN_OK;
+  size_t bytes = sizeof(int) * (size_t)(rb.n_offsets * std::max<long long>(rb.n_in, 1));
+  SCN_TRY(device_alloc((void **)&rb.tnbr, bytes, stream));
+  SCN_CUDA_CHECK(cudaMemsetAsync(rb.tnbr, 0xFF, bytes, stream));
+  long long total = (long long)rb.n_offsets * rb.n_out;
+  if (total > 0) {
+    k_transpose_rules<<<(unsigned)ceil_div(total, 256), 256, 0, stream>>>(rb.nbr, rb.n_out, rb.n_in,
+                                                                          rb.n_offsets, rb.tnbr);
+    SCN_CUDA_CHECK(cudaGetLastError());
+  }
+  return SCN_OK;
+}
+
+__global__ void k_rule_flags(const int *__restrict__ nbr, long long total, int *__restrict__ flag) {
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx < total) flag[idx] = nbr[idx] >= 0;
+}
+__global__ void k_rule_compact(const int *__restrict__ nbr, const int *__restrict__ pos, long long total,
+                               long long n_out, int *__restrict__ pairs) {
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  int i = nbr[idx];
+  if (i < 0) return;
+  long long p = pos[idx];
+  pairs[2 * p] = i;
+  pairs[2 * p + 1] = (int)(idx % n_out);
+}
+
+static int rulebook_export(Rulebook &rb, int64_t *n_offsets, int64_t *counts_host, int32_t *pairs_dev,
+                           cudaStream_t stream) {
+  SCN_TRY(rulebook_counts(rb, stream));
+  if (n_offsets) *n_offsets = rb.n_offsets;
+  if (counts_host)
+    for (int k = 0; k < rb.n_offsets; ++k) counts_host[k] = rb.counts_host[k];
+  if (!pairs_dev) return SCN_OK;
+  long long total = (long long)rb.n_offsets * rb.n_out;
+  if (total == 0) return SCN_OK;
+  SCN_REQUIRE(total < (1ll << 31), SCN_ERR_UNSUPPORTED, "rulebook too large to export");
+  int *flag = nullptr;
+  SCN_TRY(device_alloc((void **)&flag, sizeof(int) * (size_t)total, stream));
+  unsigned blocks = (unsigned)ceil_div(total, 256);
+  k_rule_flags<<<blocks, 256, 0, stream>>>(rb.nbr, total, flag);
+  SCN_TRY(exclusive_scan_i32(flag, flag, total, nullptr, stream));
+  k_rule_compact<<<blocks, 256, 0, stream>>>(rb.nbr, flag, total, rb.n_out, pairs_dev);
+  SCN_CUDA_CHECK(cudaGetLastError());
+  SCN_TRY(device_free(flag, stream));
+  return SCN_OK;
+}
+
+}  // namespace scn
+
+// ------------------------------------------------------------------------------------------
+// C ABI
+// ------------------------------------------------------------------------------------------
+
+using namespace scn;
+
+extern "C" {
+
+int scn_md_create(int dimension, scn_metadata **md) {
+  SCN_REQUIRE(md, SCN_ERR_BAD_ARG, "null output pointer");
+  SCN_REQUIRE(dimension >= 1 && dimension <= SCN_MAX_DIMENSION, SCN_ERR_BAD_ARG,
+              "dimension %d not in 1..%d", dimension, SCN_MAX_DIMENSION);
+  *md = new scn_metadata();
+  (*md)->dim = dimension;
+  return SCN_OK;
+}
+
+int scn_md_clear(scn_metadata *md, void *stream) {
+  SCN_REQUIRE(md, SCN_ERR_BAD_ARG, "null metadata");
+  return md_clear(md, (cudaStream_t)stream);
+}
+
+int scn_md_destroy(scn_metadata *md) {
+  if (!md) return SCN_OK;
+  md_clear(md, 0);
+  device_free(md->flags_dev, 0);
+  device_free(md->scalars_dev, 0);
+  delete md;
+  return SCN_OK;
+}
+
+int scn_md_input_layer(scn_metadata *md, const int64_t *spatial_size, const int64_t *coords,
+                       int coords_on_device, int64_t n_rows, int n_cols, int64_t batch_size,
+                       int mode, void *stream, int64_t *n_active) {
+  return md_input_layer(md, spatial_size, coords, coords_on_device, n_rows, n_cols, batch_size, mode,
+                        (cudaStream_t)stream, n_active);
+}
+
+int scn_md_n_active(scn_metadata *md, const int64_t *spatial_size, int64_t *n_active) {
+  SCN_REQUIRE(md && spatial_size && n_active, SCN_ERR_BAD_ARG, "null argument");
+  Grid *g = find_grid(md, spatial_size);
+  // the reference's unordered_map lookup default-constructs a zero for an unknown size
+  *n_active = g ? g->n_active : 0;
+  return SCN_OK;
+}
+
+int scn_md_batch_size(scn_metadata *md, const int64_t *spatial_size, int64_t *batch_size) {
+  SCN_REQUIRE(md && spatial_size && batch_size, SCN_ERR_BAD_ARG, "null argument");
+  Grid *g = find_grid(md, spatial_size);
+  *batch_size = g ? g->batch_size : 0;
+  return SCN_OK;
+}
+
+int scn_md_spatial_locations(scn_metadata *md, const int64_t *spatial_size, int64_t *out_dev,
+                             void *stream) {
+  SCN_REQUIRE(md && spatial_size, SCN_ERR_BAD_ARG, "null argument");
+  Grid *g = find_grid(md, spatial_size);
+  SCN_REQUIRE(g, SCN_ERR_NO_GRID, "no grid for that spatial size");
+  if (g->n_active == 0) return SCN_OK;
+  SCN_REQUIRE(out_dev, SCN_ERR_BAD_ARG, "null output");
+  k_spatial_locations<<<(unsigned)ceil_div(g->n_active, 256), 256, 0, (cudaStream_t)stream>>>(
+      g->layout, g->row_keys, g->n_active, (long long *)out_dev);
+  SCN_CUDA_CHECK(cudaGetLastError());
+  return SCN_OK;
+}
+
+int scn_md_submanifold_rulebook(scn_metadata *md, const int64_t *spatial_size,
+                                const int64_t *filter_size, void *stream, int64_t *n_rules) {
+  SCN_REQUIRE(md && spatial_size && filter_size, SCN_ERR_BAD_ARG, "null argument");
+  Rulebook *rb = nullptr;
+  SCN_TRY(get_submanifold_rulebook(md, spatial_size, filter_size, (cudaStream_t)stream, &rb));
+  if (n_rules) {
+    SCN_TRY(rulebook_counts(*rb, (cudaStream_t)stream));
+    *n_rules = rb->total_rules;
+  }
+  return SCN_OK;
+}
+
+int scn_md_strided_rulebook(scn_metadata *md, const int64_t *input_size, const int64_t *output_size,
+                            const int64_t *filter_size, const int64_t *filter_stride, void *stream,
+                            int64_t *n_active_out, int64_t *n_rules) {
+  SCN_REQUIRE(md && input_size && output_size && filter_size && filter_stride, SCN_ERR_BAD_ARG,
+              "null argument");
+  Rulebook *rb = nullptr;
+  SCN_TRY(get_strided_rulebook(md, input_size, output_size, filter_size, filter_stride,
+                               (cudaStream_t)stream, &rb));
+  if (n_active_out) *n_active_out = rb->n_out;
+  if (n_rules) {
+    SCN_TRY(rulebook_counts(*rb, (cudaStream_t)stream));
+    *n_rules = rb->total_rules;
+  }
+  return SCN_OK;
+}
+
+int scn_md_rulebook_export(scn_metadata *md, int kind, const int64_t *sizes_a, const int64_t *sizes_b,
+                           const int64_t *sizes_c, int64_t *n_offsets, int64_t *counts_host,
+                           int32_t *pairs_dev, void *stream) {
+  SCN_REQUIRE(md && sizes_a && sizes_b, SCN_ERR_BAD_ARG, "null argument");
+  Rulebook *rb = nullptr;
+  if (kind == SCN_RULES_SUBMANIFOLD) {
+    auto it = md->sub_rules.find(make_key(md->dim, sizes_a, sizes_b));
+    if (it != md->sub_rules.end()) rb = &it->second;
+  } else if (kind == SCN_RULES_STRIDED) {
+    SCN_REQUIRE(sizes_c, SCN_ERR_BAD_ARG, "null stride");
+    auto it = md->strided_rules.find(make_key(md->dim, sizes_a, sizes_b, sizes_c));
+    if (it != md->strided_rules.end()) rb = &it->second;
+  } else {
+    SCN_REQUIRE(false, SCN_ERR_BAD_ARG, "unknown rulebook kind %d", kind);
+  }
+  SCN_REQUIRE(rb && rb->built, SCN_ERR_NO_GRID, "that rulebook has not been built");
+  return rulebook_export(*rb, n_offsets, counts_host, pairs_dev, (cudaStream_t)stream);
+}
+}

@@ -1,0 +1,73 @@
+// Host-side description of what a scn_metadata object owns on the device: one Grid per
+// spatial scale (site hash + row -> key table) and the dense per-filter-offset rulebooks.
+#pragma once
+
+#include <map>
+#include <vector>
+
+#include "common.cuh"
+
+namespace scn {
+
+// Active sites of one spatial scale.
+struct Grid {
+  KeyLayout layout{};
+  long long n_active = 0;
+  long long batch_size = 0;
+  unsigned long long *row_keys = nullptr;  // [n_active] packed key of every feature row
+  HashTable table{};                       // key -> row
+};
+
+// Dense rulebook.  The reference stores, per filter offset k, a compacted list of
+// (input_row, output_row) pairs (Metadata.h:35).  Because every (offset, output row) has at
+// most one rule, the same information is kept here as a table
+//     nbr[k * n_out + o] = input row feeding output row o through filter offset k, or -1
+// which the output-stationary kernels read with coalesced loads and which the builders write
+// without compaction, atomics or a host round trip.  `tnbr` is the transposed view
+//     tnbr[k * n_in + i] = output row fed by input row i through offset k, or -1
+// used by Deconvolution (the reference swaps the two rule columns, CPU/Deconvolution.cpp:35-37);
+// it is valid because every (offset, input row) also has at most one rule.
+struct Rulebook {
+  int n_offsets = 0;  // filter volume K
+  long long n_in = 0, n_out = 0;
+  int *nbr = nullptr;
+  int *tnbr = nullptr;                       // built on first use
+  unsigned long long *counts_dev = nullptr;  // [K] rules per offset
+  std::vector<long long> counts_host;        // filled on first request (waits for the stream)
+  long long total_rules = -1;
+  bool built = false;
+};
+
+int rulebook_counts(Rulebook &rb, cudaStream_t stream);         // fills counts_host/total_rules
+int rulebook_transposed(Rulebook &rb, cudaStream_t stream);     // builds tnbr if missing
+
+}  // namespace scn
+
+struct scn_metadata {
+  int dim = 0;
+  std::map<std::vector<int64_t>, scn::Grid> grids;             // key: spatial size
+  std::map<std::vector<int64_t>, scn::Rulebook> sub_rules;      // key: size | filter
+  std::map<std::vector<int64_t>, scn::Rulebook> strided_rules;  // key: in size | filter | stride
+
+  // input-layer rules of the last scn_md_input_layer call: CSR over output rows of the input
+  // rows that land on each site, ascending (the order the reference sums them in).
+  int input_mode = -1;
+  long long input_n_rows = 0, input_n_active = 0;
+  int *input_csr_start = nullptr;  // [n_active + 1]
+  int *input_csr_rows = nullptr;   // [n_rows]
+
+  int *flags_dev = nullptr;   // device word the kernels OR DeviceFlag bits into
+  int *scalars_dev = nullptr; // small device scratch: [0] count, [1] max batch index
+};
+
+namespace scn {
+std::vector<int64_t> make_key(int dim, const int64_t *a, const int64_t *b = nullptr,
+                              const int64_t *c = nullptr);
+Grid *find_grid(scn_metadata *md, const int64_t *spatial_size);
+// finds or builds
+int get_submanifold_rulebook(scn_metadata *md, const int64_t *spatial_size,
+                             const int64_t *filter_size, cudaStream_t stream, Rulebook **out);
+int get_strided_rulebook(scn_metadata *md, const int64_t *input_size, const int64_t *output_size,
+                         const int64_t *filter_size, const int64_t *filter_stride,
+                         cudaStream_t stream, Rulebook **out);
+}  // namespace scn

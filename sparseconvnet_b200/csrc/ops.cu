@@ -1,0 +1,280 @@
+// Bandwidth-bound feature operators: input-layer duplicate handling, BatchNorm + leaky ReLU,
+// rulebook-driven max pooling and sparse-to-dense.  Each is one pass over its rows.
+#include <algorithm>
+
+#include "metadata.cuh"
+
+namespace scn {
+
+// ------------------------------------------------------------------------------------------
+// InputLayer feature pass (CPU/IOLayers.cpp:11-29): out[row] = sum_i mult * in[r_i], summed in
+// ascending input-row order with separate multiply and add, as the reference's scalar loop
+// does, so modes 1-3 are bit-exact and mode 4 differs only where 1/count is inexact.
+// ------------------------------------------------------------------------------------------
+__global__ void k_input_features(const float *__restrict__ in, float *__restrict__ out,
+                                 const int *__restrict__ start, const int *__restrict__ rows,
+                                 long long n_out, int C, int mode) {
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n_out * C) return;
+  long long r = idx / C;
+  int c = (int)(idx % C);
+  int s = start[r], e = start[r + 1];
+  float acc = 0.f;
+  if (mode == 1) {
+    acc = in[(long long)rows[s] * C + c];
+  } else if (mode == 2) {
+    acc = in[(long long)rows[e - 1] * C + c];
+  } else {
+    float mult = (mode == 4 && e > s) ? 1.0f / (float)(e - s) : 1.0f;
+    for (int j = s; j < e; ++j) acc = __fadd_rn(acc, __fmul_rn(mult, in[(long long)rows[j] * C + c]));
+  }
+  out[idx] = acc;
+}
+
+// ------------------------------------------------------------------------------------------
+// BatchNorm + leaky ReLU (CPU/BatchNormalization.cpp:12-62)
+// ------------------------------------------------------------------------------------------
+
+// per-plane sum and sum of squares; grid.x tiles planes by 32, grid.y splits the rows
+__global__ void __launch_bounds__(256)
+k_bn_stats(const float *__restrict__ in, long long n_rows, int C, long long in_stride,
+           double *__restrict__ sums /* [2][C] */) {
+  __shared__ float sh_s[8][33], sh_q[8][33];
+  int lane = threadIdx.x & 31, wy = threadIdx.x >> 5;
+  int c = blockIdx.x * 32 + lane;
+  float s = 0.f, q = 0.f;
+  if (c < C)
+    for (long long r = (long long)blockIdx.y * 8 + wy; r < n_rows; r += (long long)gridDim.y * 8) {
+      float v = in[r * in_stride + c];
+      s += v;
+      q += v * v;
+    }
+  sh_s[wy][lane] = s;
+  sh_q[wy][lane] = q;
+  __syncthreads();
+  if (wy == 0 && c < C) {
+    double ds = 0, dq = 0;
+    for (int j = 0; j < 8; ++j) {
+      ds += sh_s[j][lane];
+      dq += sh_q[j][lane];
+    }
+    atomicAdd(&sums[c], ds);
+    atomicAdd(&sums[C + c], dq);
+  }
+}
+
+// Turns either running statistics (eval) or batch sums (train) into saveMean / saveInvStd and
+// updates the running statistics in training mode: momentum weighs the OLD value, the
+// normalising variance is biased, the running variance unbiased (CPU/BatchNormalization.cpp:32-46).
+__global__ void k_bn_finalize(int C, long long n_rows, const double *__restrict__ sums,
+                              float *save_mean, float *save_invstd, float *running_mean,
+                              float *running_var, float eps, float momentum, int train) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  if (train) {
+    double mean = sums[c] / (double)n_rows;
+    double ss = sums[C + c] - mean * mean * (double)n_rows;
+    save_mean[c] = (float)mean;
+    running_mean[c] = momentum * running_mean[c] + (1 - momentum) * (float)mean;
+    running_var[c] = momentum * running_var[c] + (1 - momentum) * (float)(ss / (double)(n_rows - 1));
+    save_invstd[c] = powf((float)(ss / (double)n_rows) + eps, -0.5f);
+  } else {
+    save_mean[c] = running_mean[c];
+    save_invstd[c] = powf(running_var[c] + eps, -0.5f);
+  }
+}
+
+// y = x * w + b, y *= (y > 0 ? 1 : leak); four planes per thread when the layout allows.
+template <int VEC>
+__global__ void __launch_bounds__(256)
+k_bn_apply(const float *__restrict__ in, float *__restrict__ out, long long n_rows, int C,
+           long long in_stride, long long out_stride, const float *__restrict__ save_mean,
+           const float *__restrict__ save_invstd, const float *__restrict__ weight,
+           const float *__restrict__ bias, float leak) {
+  extern __shared__ float sh_wb[];  // [2][C]
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float w = save_invstd[c] * (weight ? weight[c] : 1.f);
+    sh_wb[c] = w;
+    sh_wb[C + c] = __fadd_rn(__fmul_rn(-save_mean[c], w), bias ? bias[c] : 0.f);
+  }
+  __syncthreads();
+  int cv = C / VEC;
+  long long total = n_rows * cv;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    long long r = idx / cv;
+    int c = (int)(idx % cv) * VEC;
+    if (VEC == 4) {
+      float4 x = *reinterpret_cast<const float4 *>(in + r * in_stride + c);
+      float4 y;
+      y.x = __fadd_rn(__fmul_rn(x.x, sh_wb[c + 0]), sh_wb[C + c + 0]);
+      y.y = __fadd_rn(__fmul_rn(x.y, sh_wb[c + 1]), sh_wb[C + c + 1]);
+      y.z = __fadd_rn(__fmul_rn(x.z, sh_wb[c + 2]), sh_wb[C + c + 2]);
+      y.w = __fadd_rn(__fmul_rn(x.w, sh_wb[c + 3]), sh_wb[C + c + 3]);
+      y.x *= (y.x > 0.f) ? 1.f : leak;
+      y.y *= (y.y > 0.f) ? 1.f : leak;
+      y.z *= (y.z > 0.f) ? 1.f : leak;
+      y.w *= (y.w > 0.f) ? 1.f : leak;
+      *reinterpret_cast<float4 *>(out + r * out_stride + c) = y;
+    } else {
+      float y = __fadd_rn(__fmul_rn(in[r * in_stride + c], sh_wb[c]), sh_wb[C + c]);
+      out[r * out_stride + c] = y * ((y > 0.f) ? 1.f : leak);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// MaxPooling (CPU/MaxPooling.cpp:7-20,37-60): the reference zero-fills the output and then
+// takes elementwise maxima over the rules, so the result is max(0, max of inputs).  Output
+// stationary here: each output element is written once.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+k_max_pool(const float *__restrict__ in, float *__restrict__ out, const int *__restrict__ nbr,
+           long long n_out, long long n_in, int K, int C_out, int in_stride, int drop, int *flags) {
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n_out * C_out) return;
+  long long o = idx / C_out;
+  int c = (int)(idx % C_out);
+  float m = 0.f;
+  for (int k = 0; k < K; ++k) {
+    int i = nbr[(long long)k * n_out + o];
+    if (i < 0) continue;
+    if (i >= n_in) {
+      atomicOr(flags, FLAG_BAD_ROW);
+      continue;
+    }
+    float v = in[(long long)i * in_stride + drop + c];
+    if (m < v) m = v;
+  }
+  out[idx] = m;
+}
+
+// ------------------------------------------------------------------------------------------
+// SparseToDense (CPU/SparseToDense.cpp:7-19,35-64): dense[b][c][offset(x)] = feat[row][c]
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+k_sparse_to_dense(KeyLayout L, const unsigned long long *__restrict__ row_keys,
+                  const float *__restrict__ in, float *__restrict__ out, long long n_rows, int C,
+                  long long volume) {
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n_rows * C) return;
+  long long r = idx / C;
+  int c = (int)(idx % C);
+  unsigned long long key = row_keys[r];
+  if (key == kEmptyKey) return;
+  int x[kMaxDim], b;
+  unpack_key(L, key, x, b);
+  long long lin = 0;
+  for (int d = 0; d < L.dim; ++d) lin = lin * L.size[d] + x[d];
+  out[((long long)b * C + c) * volume + lin] = in[idx];
+}
+
+}  // namespace scn
+
+using namespace scn;
+
+extern "C" {
+
+int scn_input_layer_forward(scn_metadata *md, const float *in_features, int64_t n_in,
+                            float *out_features, int64_t n_out, int n_planes, void *stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SCN_REQUIRE(md && md->input_mode >= 0, SCN_ERR_BAD_ARG, "scn_md_input_layer has not been called");
+  SCN_REQUIRE(n_in == md->input_n_rows && n_out == md->input_n_active, SCN_ERR_SIZE_MISMATCH,
+              "input layer: got %lld -> %lld rows, metadata has %lld -> %lld", (long long)n_in,
+              (long long)n_out, md->input_n_rows, md->input_n_active);
+  SCN_REQUIRE(n_planes >= 1, SCN_ERR_BAD_ARG, "n_planes must be positive");
+  if (n_out == 0) return SCN_OK;
+  SCN_REQUIRE(in_features && out_features, SCN_ERR_BAD_ARG, "null features");
+  if (md->input_mode == 0) {  // row i <-> input i (CPU/IOLayers.cpp:61-63)
+    if (in_features != out_features)
+      SCN_CUDA_CHECK(cudaMemcpyAsync(out_features, in_features, sizeof(float) * (size_t)n_in * n_planes,
+                                     cudaMemcpyDeviceToDevice, stream));
+    return SCN_OK;
+  }
+  long long total = (long long)n_out * n_planes;
+  k_input_features<<<(unsigned)ceil_div(total, 256), 256, 0, stream>>>(
+      in_features, out_features, md->input_csr_start, md->input_csr_rows, n_out, n_planes, md->input_mode);
+  SCN_CUDA_CHECK(cudaGetLastError());
+  return SCN_OK;
+}
+
+int scn_batchnorm_forward(const float *in_features, float *out_features, int64_t n_rows, int n_planes,
+                          int64_t in_stride, int64_t out_stride, float *save_mean, float *save_invstd,
+                          float *running_mean, float *running_var, const float *weight,
+                          const float *bias, double eps, double momentum, int train, double leakiness,
+                          void *stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SCN_REQUIRE(n_planes >= 1 && n_planes <= 4096, SCN_ERR_UNSUPPORTED, "n_planes %d unsupported", n_planes);
+  SCN_REQUIRE(save_mean && save_invstd && running_mean && running_var, SCN_ERR_BAD_ARG, "null statistics");
+  SCN_REQUIRE(in_stride >= n_planes && out_stride >= n_planes, SCN_ERR_BAD_ARG, "row stride below n_planes");
+  if (n_rows == 0) return SCN_OK;
+  SCN_REQUIRE(in_features && out_features, SCN_ERR_BAD_ARG, "null features");
+  double *sums = nullptr;
+  if (train) {
+    SCN_TRY(device_alloc((void **)&sums, sizeof(double) * 2 * n_planes, stream));
+    SCN_CUDA_CHECK(cudaMemsetAsync(sums, 0, sizeof(double) * 2 * n_planes, stream));
+    unsigned gy = (unsigned)std::min<long long>(ceil_div(n_rows, 64), 1024);
+    k_bn_stats<<<dim3((unsigned)ceil_div(n_planes, 32), gy), 256, 0, stream>>>(in_features, n_rows, n_planes,
+                                                                             in_stride, sums);
+  }
+  k_bn_finalize<<<(unsigned)ceil_div(n_planes, 128), 128, 0, stream>>>(
+      n_planes, n_rows, sums, save_mean, save_invstd, running_mean, running_var, (float)eps,
+      (float)momentum, train);
+  bool vec4 = (n_planes % 4 == 0) && (in_stride % 4 == 0) && (out_stride % 4 == 0) &&
+              ((uintptr_t)in_features % 16 == 0) && ((uintptr_t)out_features % 16 == 0);
+  long long work = n_rows * (vec4 ? n_planes / 4 : n_planes);
+  unsigned blocks = (unsigned)std::min<long long>(ceil_div(work, 256), 148 * 16);
+  size_t smem = sizeof(float) * 2 * n_planes;
+  if (vec4)
+    k_bn_apply<4><<<blocks, 256, smem, stream>>>(in_features, out_features, n_rows, n_planes, in_stride,
+                                                 out_stride, save_mean, save_invstd, weight, bias,
+                                                 (float)leakiness);
+  else
+    k_bn_apply<1><<<blocks, 256, smem, stream>>>(in_features, out_features, n_rows, n_planes, in_stride,
+                                                 out_stride, save_mean, save_invstd, weight, bias,
+                                                 (float)leakiness);
+  SCN_CUDA_CHECK(cudaGetLastError());
+  if (sums) SCN_TRY(device_free(sums, stream));
+  return SCN_OK;
+}
+
+int scn_max_pooling_forward(scn_metadata *md, const int64_t *input_size, const int64_t *output_size,
+                            const int64_t *pool_size, const int64_t *pool_stride,
+                            const float *in_features, float *out_features, int n_planes_in,
+                            int n_features_to_drop, void *stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SCN_REQUIRE(md && input_size && output_size && pool_size && pool_stride, SCN_ERR_BAD_ARG, "null argument");
+  SCN_REQUIRE(n_features_to_drop >= 0 && n_features_to_drop < n_planes_in, SCN_ERR_BAD_ARG,
+              "n_features_to_drop %d not in [0, %d)", n_features_to_drop, n_planes_in);
+  Rulebook *rb = nullptr;
+  SCN_TRY(get_strided_rulebook(md, input_size, output_size, pool_size, pool_stride, stream, &rb));
+  if (rb->n_out == 0) return SCN_OK;
+  SCN_REQUIRE(in_features && out_features, SCN_ERR_BAD_ARG, "null features");
+  int c_out = n_planes_in - n_features_to_drop;
+  long long total = rb->n_out * c_out;
+  k_max_pool<<<(unsigned)ceil_div(total, 256), 256, 0, stream>>>(in_features, out_features, rb->nbr, rb->n_out,
+                                                                 rb->n_in, rb->n_offsets, c_out, n_planes_in,
+                                                                 n_features_to_drop, md->flags_dev);
+  SCN_CUDA_CHECK(cudaGetLastError());
+  return SCN_OK;
+}
+
+int scn_sparse_to_dense_forward(scn_metadata *md, const int64_t *spatial_size, const float *in_features,
+                                float *out_dense, int n_planes, void *stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SCN_REQUIRE(md && spatial_size && out_dense, SCN_ERR_BAD_ARG, "null argument");
+  Grid *g = find_grid(md, spatial_size);
+  SCN_REQUIRE(g, SCN_ERR_NO_GRID, "no grid for that spatial size");
+  long long volume = 1;
+  for (int d = 0; d < md->dim; ++d) volume *= spatial_size[d];
+  size_t bytes = sizeof(float) * (size_t)g->batch_size * n_planes * volume;
+  SCN_CUDA_CHECK(cudaMemsetAsync(out_dense, 0, bytes, stream));
+  if (g->n_active == 0) return SCN_OK;
+  SCN_REQUIRE(in_features, SCN_ERR_BAD_ARG, "null features");
+  long long total = g->n_active * n_planes;
+  k_sparse_to_dense<<<(unsigned)ceil_div(total, 256), 256, 0, stream>>>(g->layout, g->row_keys, in_features,
+                                                                        out_dense, g->n_active, n_planes, volume);
+  SCN_CUDA_CHECK(cudaGetLastError());
+  return SCN_OK;
+}
+}

@@ -1,0 +1,303 @@
+"""The inference-path modules, API-compatible with the reference's ``sparseconvnet`` package:
+same class names, constructor arguments, parameter names and shapes (so reference
+``state_dict``s load), same ``input_spatial_size`` protocol.  Forward only: every module
+runs under ``torch.no_grad`` semantics and calls the ``SCN`` mirror module, which calls the
+C-ABI library.
+
+Reference counterparts: sparseconvnet/ioLayers.py:15-65, submanifoldConvolution.py:14-60,
+convolution.py:13-66, deconvolution.py:13-64, batchNormalization.py:13-91,
+maxPooling.py:71-104, sparseToDense.py:59-75, networkInNetwork.py, identity.py.
+"""
+import torch
+from torch.nn import Module, Parameter
+
+import sparseconvnet_b200 as _pkg
+from . import SCN
+from .sparse_tensor import SparseConvNetTensor, optional_tensor, to_long_tensor
+
+
+def _size_str(t):
+    v = t.tolist()
+    return str(v[0]) if min(v) == max(v) else "(" + ",".join(str(i) for i in v) + ")"
+
+
+class InputLayer(Module):
+    """Takes ``[coords, features]`` or ``[coords, features, batch_size]``.
+
+    coords: LongTensor [N, dimension] (one sample) or [N, dimension+1] (last column = batch
+    index), on the CPU as in the reference or already on the GPU.  features: CUDA float
+    tensor [N, planes].  mode: how repeated coordinates are merged -- 0 none expected,
+    1 keep the first row, 2 keep the last row, 3 sum, 4 mean (what the reference's code does,
+    sparseconvnet/SCN/Metadata/IOLayersRules.h:96-120).
+    """
+
+    def __init__(self, dimension, spatial_size, mode=3):
+        Module.__init__(self)
+        self.dimension = dimension
+        self.spatial_size = to_long_tensor(dimension, spatial_size)
+        self.mode = mode
+        self.device = None
+
+    def to(self, device):
+        self.device = device
+        return self
+
+    def forward(self, input):
+        coords, features = input[0], input[1]
+        if self.device is not None:
+            features = features.to(self.device)
+        elif not features.is_cuda:
+            raise RuntimeError("InputLayer: features must be on a CUDA device (or call .to(device) on "
+                               "the layer): sparseconvnet_b200 has no CPU path")
+        output = SparseConvNetTensor(metadata=_pkg.Metadata(self.dimension), spatial_size=self.spatial_size)
+        output.features = features.new_empty(0)
+        SCN.InputLayer_updateOutput(output.metadata, self.spatial_size, coords.long(),
+                                    features.detach().float().contiguous(), output.features,
+                                    0 if len(input) == 2 else input[2], self.mode)
+        return output
+
+    def input_spatial_size(self, out_size):
+        return out_size
+
+    def __repr__(self):
+        return "InputLayer(mode=%d)" % self.mode
+
+
+class _ConvBase(Module):
+    def _init_weight(self, dimension, nIn, nOut, filter_size, bias, groups):
+        self.dimension = dimension
+        self.groups = groups
+        self.nIn = nIn
+        self.nOut = nOut
+        self.filter_size = to_long_tensor(dimension, filter_size)
+        self.filter_volume = int(self.filter_size.prod().item())
+        std = (2.0 * groups / nIn / self.filter_volume) ** 0.5
+        self.weight = Parameter(torch.empty(self.filter_volume, groups, nIn // groups,
+                                            nOut // groups).normal_(0, std))
+        if bias:
+            self.bias = Parameter(torch.zeros(nOut))
+
+    def _count(self, macs, output_features):
+        _pkg.forward_pass_multiplyAdd_count += macs
+        _pkg.forward_pass_hidden_states += output_features.nelement()
+
+
+class SubmanifoldConvolution(_ConvBase):
+    def __init__(self, dimension, nIn, nOut, filter_size, bias, groups=1):
+        Module.__init__(self)
+        self._init_weight(dimension, nIn, nOut, filter_size, bias, groups)
+
+    def forward(self, input):
+        assert input.features.nelement() == 0 or input.features.size(1) == self.nIn, (self.nIn, self.nOut, input)
+        output = SparseConvNetTensor(metadata=input.metadata, spatial_size=input.spatial_size)
+        output.features = input.features.new_empty(0)
+        macs = SCN.SubmanifoldConvolution_updateOutput(
+            input.spatial_size, self.filter_size, input.metadata, input.features.detach().contiguous(),
+            output.features, self.weight, optional_tensor(self, "bias"))
+        self._count(macs, output.features)
+        return output
+
+    def input_spatial_size(self, out_size):
+        return out_size
+
+    def __repr__(self):
+        return "SubmanifoldConvolution %d->%d C%s" % (self.nIn, self.nOut, _size_str(self.filter_size))
+
+
+class ValidConvolution(SubmanifoldConvolution):
+    pass
+
+
+class Convolution(_ConvBase):
+    def __init__(self, dimension, nIn, nOut, filter_size, filter_stride, bias, groups=1):
+        Module.__init__(self)
+        self._init_weight(dimension, nIn, nOut, filter_size, bias, groups)
+        self.filter_stride = to_long_tensor(dimension, filter_stride)
+
+    def forward(self, input):
+        assert input.features.nelement() == 0 or input.features.size(1) == self.nIn
+        out_size = torch.div(input.spatial_size - self.filter_size, self.filter_stride, rounding_mode="trunc") + 1
+        assert ((out_size - 1) * self.filter_stride + self.filter_size == input.spatial_size).all(), \
+            (input.spatial_size, out_size, self.filter_size, self.filter_stride)
+        output = SparseConvNetTensor(metadata=input.metadata, spatial_size=out_size)
+        output.features = input.features.new_empty(0)
+        macs = SCN.Convolution_updateOutput(
+            input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata,
+            input.features.detach().contiguous(), output.features, self.weight, optional_tensor(self, "bias"))
+        self._count(macs, output.features)
+        return output
+
+    def input_spatial_size(self, out_size):
+        return (out_size - 1) * self.filter_stride + self.filter_size
+
+    def __repr__(self):
+        return "Convolution %d->%d C%s/%s" % (self.nIn, self.nOut, _size_str(self.filter_size),
+                                              _size_str(self.filter_stride))
+
+
+class Deconvolution(_ConvBase):
+    def __init__(self, dimension, nIn, nOut, filter_size, filter_stride, bias, groups=1):
+        Module.__init__(self)
+        self._init_weight(dimension, nIn, nOut, filter_size, bias, groups)
+        self.filter_stride = to_long_tensor(dimension, filter_stride)
+
+    def forward(self, input):
+        assert input.features.nelement() == 0 or input.features.size(1) == self.nIn
+        out_size = (input.spatial_size - 1) * self.filter_stride + self.filter_size
+        output = SparseConvNetTensor(metadata=input.metadata, spatial_size=out_size)
+        output.features = input.features.new_empty(0)
+        macs = SCN.Deconvolution_updateOutput(
+            input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata,
+            input.features.detach().contiguous(), output.features, self.weight, optional_tensor(self, "bias"))
+        self._count(macs, output.features)
+        return output
+
+    def input_spatial_size(self, out_size):
+        return torch.div(out_size - self.filter_size, self.filter_stride, rounding_mode="trunc") + 1
+
+    def __repr__(self):
+        return "Deconvolution %d->%d C%s/%s" % (self.nIn, self.nOut, _size_str(self.filter_size),
+                                                _size_str(self.filter_stride))
+
+
+class BatchNormalization(Module):
+    """Batch normalisation fused with a leaky ReLU: leakiness 1 = no activation, 0 = ReLU.
+    eps 1e-4 and momentum 0.99 (weight of the OLD running value) are the reference's defaults
+    (sparseconvnet/batchNormalization.py:24-30)."""
+
+    def __init__(self, nPlanes, eps=1e-4, momentum=0.99, affine=True, leakiness=1):
+        Module.__init__(self)
+        self.nPlanes = nPlanes
+        self.eps = eps
+        self.momentum = momentum
+        self.affine = affine
+        self.leakiness = leakiness
+        self.register_buffer("running_mean", torch.zeros(nPlanes))
+        self.register_buffer("running_var", torch.ones(nPlanes))
+        if affine:
+            self.weight = Parameter(torch.ones(nPlanes))
+            self.bias = Parameter(torch.zeros(nPlanes))
+
+    def forward(self, input):
+        if input.features.nelement() == 0:
+            return input
+        assert input.features.size(1) == self.nPlanes, (self.nPlanes, input.features.shape)
+        output = SparseConvNetTensor(metadata=input.metadata, spatial_size=input.spatial_size)
+        output.features = input.features.new_empty(0)
+        save_mean = input.features.new_empty(self.nPlanes)
+        save_invstd = input.features.new_empty(self.nPlanes)
+        SCN.BatchNormalization_updateOutput(
+            input.features.detach(), output.features, save_mean, save_invstd, self.running_mean,
+            self.running_var, optional_tensor(self, "weight"), optional_tensor(self, "bias"), self.eps,
+            self.momentum, self.training, self.leakiness)
+        return output
+
+    def input_spatial_size(self, out_size):
+        return out_size
+
+    def __repr__(self):
+        s = "BatchNorm(%d,eps=%g,momentum=%g,affine=%s" % (self.nPlanes, self.eps, self.momentum, self.affine)
+        if self.leakiness > 0:
+            s += ",leakiness=%g" % self.leakiness
+        return s + ")"
+
+
+class BatchNormReLU(BatchNormalization):
+    def __init__(self, nPlanes, eps=1e-4, momentum=0.99):
+        BatchNormalization.__init__(self, nPlanes, eps, momentum, True, 0)
+
+    def __repr__(self):
+        return "BatchNormReLU(%d,eps=%g,momentum=%g,affine=%s)" % (self.nPlanes, self.eps, self.momentum,
+                                                                   self.affine)
+
+
+class BatchNormLeakyReLU(BatchNormalization):
+    def __init__(self, nPlanes, eps=1e-4, momentum=0.99, leakiness=0.333):
+        BatchNormalization.__init__(self, nPlanes, eps, momentum, True, leakiness)
+
+    def __repr__(self):
+        return "BatchNormLeakyReLU(%d,eps=%g,momentum=%g,affine=%s,leakiness=%g)" % (
+            self.nPlanes, self.eps, self.momentum, self.affine, self.leakiness)
+
+
+class MaxPooling(Module):
+    def __init__(self, dimension, pool_size, pool_stride, nFeaturesToDrop=0):
+        Module.__init__(self)
+        self.dimension = dimension
+        self.pool_size = to_long_tensor(dimension, pool_size)
+        self.pool_stride = to_long_tensor(dimension, pool_stride)
+        self.nFeaturesToDrop = nFeaturesToDrop
+
+    def forward(self, input):
+        out_size = torch.div(input.spatial_size - self.pool_size, self.pool_stride, rounding_mode="trunc") + 1
+        assert ((out_size - 1) * self.pool_stride + self.pool_size == input.spatial_size).all()
+        output = SparseConvNetTensor(metadata=input.metadata, spatial_size=out_size)
+        output.features = input.features.new_empty(0)
+        SCN.MaxPooling_updateOutput(input.spatial_size, out_size, self.pool_size, self.pool_stride,
+                                    input.metadata, input.features.detach().contiguous(), output.features,
+                                    self.nFeaturesToDrop)
+        return output
+
+    def input_spatial_size(self, out_size):
+        return (out_size - 1) * self.pool_stride + self.pool_size
+
+    def __repr__(self):
+        return "MaxPooling%s/%s" % (_size_str(self.pool_size), _size_str(self.pool_stride))
+
+
+class SparseToDense(Module):
+    """SparseConvNetTensor -> dense tensor [batch, nPlanes, *spatial_size]."""
+
+    def __init__(self, dimension, nPlanes):
+        Module.__init__(self)
+        self.dimension = dimension
+        self.nPlanes = nPlanes
+
+    def forward(self, input):
+        output = input.features.new_empty(0)
+        SCN.SparseToDense_updateOutput(input.spatial_size, input.metadata,
+                                       input.features.detach().contiguous(), output, self.nPlanes)
+        return output
+
+    def input_spatial_size(self, out_size):
+        return out_size
+
+    def __repr__(self):
+        return "SparseToDense(%d,%d)" % (self.dimension, self.nPlanes)
+
+
+class NetworkInNetwork(Module):
+    """1x1 convolution; weight [nIn, nOut] (reference: sparseconvnet/networkInNetwork.py)."""
+
+    def __init__(self, nIn, nOut, bias):
+        Module.__init__(self)
+        self.nIn = nIn
+        self.nOut = nOut
+        std = (2.0 / nIn) ** 0.5
+        self.weight = Parameter(torch.empty(nIn, nOut).normal_(0, std))
+        if bias:
+            self.bias = Parameter(torch.zeros(nOut))
+
+    def forward(self, input):
+        assert input.features.nelement() == 0 or input.features.size(1) == self.nIn
+        output = SparseConvNetTensor(metadata=input.metadata, spatial_size=input.spatial_size)
+        output.features = input.features.new_empty(0)
+        macs = SCN.NetworkInNetwork_updateOutput(input.features.detach().contiguous(), output.features,
+                                                 self.weight, optional_tensor(self, "bias"))
+        _pkg.forward_pass_multiplyAdd_count += macs
+        _pkg.forward_pass_hidden_states += output.features.nelement()
+        return output
+
+    def input_spatial_size(self, out_size):
+        return out_size
+
+    def __repr__(self):
+        return "NetworkInNetwork%d->%d" % (self.nIn, self.nOut)
+
+
+class Identity(Module):
+    def forward(self, input):
+        return input
+
+    def input_spatial_size(self, out_size):
+        return out_size
