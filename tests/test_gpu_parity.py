@@ -1,0 +1,173 @@
+"""Parity of the CUDA path (called through the Python mirror of the reference API, which calls
+the C ABI) against the golden fixtures made by the reference's CPU build, against the numpy
+restatement, and -- when oracle/_ref travelled with the tree -- the live reference."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import runner, scn_oracle as port
+from tests import helpers
+from tests.golden import cases
+
+pytestmark = pytest.mark.gpu
+
+
+def _exact_rules(a, b, what):
+    assert len(a) == len(b), what
+    for k, (ra, rb) in enumerate(zip(a, b)):
+        assert np.array_equal(np.asarray(ra).reshape(-1, 2), np.asarray(rb).reshape(-1, 2)), "%s offset %d" % (what, k)
+
+
+@pytest.mark.parametrize("name", sorted(cases.OPS_CASES))
+def test_ops_against_golden_and_port(name, cuda):
+    g = helpers.load_golden(name)
+    c = cases.OPS_CASES[name]
+    d = c["dim"]
+    inputs = (g["coords"], g["feats"], int(g["batch_size_arg"]))
+
+    net = cases.ops_modules(name)
+    helpers.load_state(net, g, "state")
+    gpu = helpers.GpuBackend()
+    st = cases.run_ops(net, inputs, gpu.run, gpu.locations)
+
+    # -- golden (reference CPU build): canonical comparison
+    assert gpu.batch_size(st["x0"]) == int(g["batch_size"])
+    for k in ("x0", "x1", "x4"):
+        helpers.assert_features_match(gpu.locations(st[k]), st[k].features, g["loc/" + k], g["feat/" + k],
+                                      helpers.FP32_TOL, same_rows=True, what=name + ":" + k)
+    for k in ("x2", "x3", "x5"):
+        helpers.assert_features_match(gpu.locations(st[k]), st[k].features, g["loc/" + k], g["feat/" + k],
+                                      helpers.FP32_TOL, what=name + ":" + k)
+    assert helpers.rel_err(st["dense"], g["dense"]) <= helpers.FP32_TOL
+    if c["mode"] in (0, 1, 2, 3):
+        assert np.array_equal(st["x0"].features, g["feat/x0"]), "input layer must be bit exact"
+    sub = port.canonical_rules(gpu.submanifold_rulebook(st["x0"], [3] * d), gpu.locations(st["x0"]),
+                               gpu.locations(st["x0"]))
+    helpers.assert_rules_equal(sub, helpers.golden_rules(g, "rules_sub"), name + " submanifold")
+    strided = port.canonical_rules(
+        gpu.strided_rulebook(st["x1"], st["x2"].spatial_size, [c["f"]] * d, [c["s"]] * d),
+        gpu.locations(st["x1"]), gpu.locations(st["x2"]))
+    helpers.assert_rules_equal(strided, helpers.golden_rules(g, "rules_strided"), name + " strided")
+
+    # -- numpy restatement: same deterministic numbering, so everything is compared row for row
+    net_cpu = cases.ops_modules(name)
+    helpers.load_state(net_cpu, g, "state")
+    pb = runner.PortBackend()
+    sp = cases.run_ops(net_cpu, inputs, helpers.oracle_run(pb), pb.locations)
+    for k in ("x0", "x1", "x2", "x3", "x4", "x5"):
+        helpers.assert_features_match(gpu.locations(st[k]), st[k].features, pb.locations(sp[k]), sp[k].features,
+                                      helpers.FP32_TOL, same_rows=True, what=name + ":port:" + k)
+    _exact_rules(gpu.submanifold_rulebook(st["x0"], [3] * d), pb.submanifold_rulebook(sp["x0"], [3] * d),
+                 name + " submanifold rulebook")
+    _exact_rules(gpu.strided_rulebook(st["x1"], st["x2"].spatial_size, [c["f"]] * d, [c["s"]] * d),
+                 pb.strided_rulebook(sp["x1"], sp["x2"].spatial_size, [c["f"]] * d, [c["s"]] * d),
+                 name + " strided rulebook")
+
+
+@pytest.mark.parametrize("name", sorted(cases.NET_CASES))
+def test_networks_against_golden(name, cuda):
+    import sparseconvnet_b200 as scn
+    g = helpers.load_golden(name)
+    inp, net, head = cases.net_modules(name)
+    helpers.load_state(net, g, "state")
+    gpu = helpers.GpuBackend()
+    scn.forward_pass_multiplyAdd_count = 0
+    x0 = gpu.run(inp, [g["coords"], g["feats"]])
+    assert np.array_equal(gpu.locations(x0), g["loc/x0"])
+    assert np.array_equal(x0.features, g["feat/x0"])
+    y = gpu.run(net, x0)
+    assert scn.forward_pass_multiplyAdd_count == float(g["macs"]), "multiply-add count differs"
+    if "dense" in g:
+        assert helpers.rel_err(y, g["dense"]) <= helpers.FP32_TOL
+    else:
+        helpers.assert_features_match(gpu.locations(y), y.features, g["loc/y"], g["feat/y"], helpers.FP32_TOL,
+                                      what=name)
+        if head is not None:
+            helpers.load_state(head, g, "head")
+            p = port.align_rows(gpu.locations(y), g["loc/y"])
+            assert helpers.rel_err(gpu.run(head, y), g["head_out"][p]) <= helpers.FP32_TOL
+
+
+def test_empty_and_tiny_inputs(cuda):
+    import sparseconvnet_b200 as scn
+    dev = cuda
+    sc = scn.SubmanifoldConvolution(3, 4, 6, 3, True).to(dev)
+    cv = scn.Convolution(3, 6, 5, 2, 2, False).to(dev)
+    bn = scn.BatchNormReLU(5).to(dev).eval()
+    for n in (0, 1):
+        x = scn.InputLayer(3, 16, mode=3)([torch.zeros(n, 4, dtype=torch.int64) + 3, torch.ones(n, 4, device=dev)])
+        assert x.features.shape == (n, 4)
+        y = bn(cv(sc(x)))
+        assert y.features.shape == (n, 5)
+        assert x.get_spatial_locations().shape == (n, 4)
+        d = scn.SparseToDense(3, 5)(y)
+        assert tuple(d.shape) == (n, 5, 8, 8, 8)
+    # one site: the only rule is the centre offset
+    x = scn.InputLayer(3, 16, mode=3)([torch.tensor([[3, 4, 5, 0]]), torch.ones(1, 4, device=dev)])
+    out = sc(x)
+    want = torch.ones(1, 4, device=dev) @ sc.weight[13, 0] + sc.bias
+    assert torch.allclose(out.features, want, atol=1e-5)
+
+
+def test_coordinate_range_is_reported(cuda):
+    import sparseconvnet_b200 as scn
+    from sparseconvnet_b200._lib import ScnError
+    with pytest.raises(ScnError):
+        scn.InputLayer(2, 8, mode=3)([torch.tensor([[1, 9, 0]]), torch.ones(1, 1, device=cuda)])
+    with pytest.raises(ScnError):
+        scn.InputLayer(2, 8, mode=0)([torch.tensor([[-1, 2, 0]]), torch.ones(1, 1, device=cuda)])
+    with pytest.raises(RuntimeError):
+        scn.InputLayer(2, 8, mode=0)([torch.tensor([[1, 2, 0]]), torch.ones(1, 1)])  # CPU features: no fallback
+
+
+def test_large_field_needs_64_bit_keys(cuda):
+    """4096^3 x batch does not fit 32 bits; corners of the field must stay distinct sites."""
+    import sparseconvnet_b200 as scn
+    pts = torch.tensor([[0, 0, 0, 0], [4095, 4095, 4095, 7], [4095, 0, 4095, 3], [4094, 4095, 4095, 7],
+                        [0, 0, 1, 0], [2048, 2048, 2048, 5]])
+    x = scn.InputLayer(3, 4096, mode=3)([pts, torch.arange(6.0, device=cuda).view(6, 1)])
+    assert torch.equal(x.get_spatial_locations(), pts)
+    rb = x.metadata
+    scn.SubmanifoldConvolution(3, 1, 1, 3, False).to(cuda)(x)
+    rules = [r.cpu().numpy() for r in rb.rulebook(0, [4096] * 3, [3] * 3)]
+    assert sum(r.shape[0] for r in rules) == 6 + 4   # 6 centre rules + (1<->3) and (0<->4) both ways
+    assert rules[13].shape[0] == 6
+
+
+def test_deterministic_bits(cuda):
+    import sparseconvnet_b200 as scn
+    g = helpers.load_golden("net_unet3d")
+    outs = []
+    for _ in range(2):
+        inp, net, head = cases.net_modules("net_unet3d")
+        helpers.load_state(net, g, "state")
+        gpu = helpers.GpuBackend()
+        y = gpu.run(net, gpu.run(inp, [g["coords"], g["feats"]]))
+        outs.append((gpu.locations(y), y.features))
+    assert np.array_equal(outs[0][0], outs[1][0])
+    assert np.array_equal(outs[0][1], outs[1][1])
+
+
+@pytest.mark.skipif(not runner.reference_available(), reason="oracle/_ref not built")
+def test_against_live_reference_random(cuda):
+    """A fresh random case straight against the compiled reference (not a stored fixture)."""
+    import sparseconvnet_b200 as scn
+    rng = np.random.default_rng(2024)
+    n = 20000
+    coords = np.concatenate([rng.integers(0, 63, (n, 3)) // np.array([1, 1, 8]) + np.array([0, 0, 20]),
+                             rng.integers(0, 5, (n, 1))], axis=1)
+    feats = rng.standard_normal((n, 16)).astype(np.float32)
+    torch.manual_seed(5)
+    inp = scn.InputLayer(3, 63, mode=4)
+    net = scn.Sequential().add(scn.SubmanifoldConvolution(3, 16, 32, 3, False)).add(scn.BatchNormReLU(32)).add(
+        scn.Convolution(3, 32, 48, 3, 2, False)).add(scn.BatchNormLeakyReLU(48, leakiness=0.2)).add(
+        scn.SubmanifoldConvolution(3, 48, 48, 3, True)).add(scn.Deconvolution(3, 48, 24, 3, 2, False))
+    from sparseconvnet_b200 import workloads
+    workloads.randomize(net, 3)
+    net.eval()
+    ref = runner.RefBackend()
+    yr = runner.run_module(net, runner.run_module(inp, [coords, feats], ref), ref)
+    gpu = helpers.GpuBackend()
+    yg = gpu.run(net, gpu.run(inp, [coords, feats]))
+    helpers.assert_features_match(gpu.locations(yg), yg.features, ref.locations(yr), yr.features, helpers.FP32_TOL,
+                                  what="live reference")
