@@ -1,0 +1,385 @@
+"""Benchmark of the submanifold sparse-convolution inference path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Headline workload (BASELINE configuration 3): 3-D submanifold U-Net inference, m=32, reps=2,
+planes 32..224, 4096^3 field, batch of 8 synthetic rooms of ~200 k voxels each per GPU, fp32.
+One step = one forward over the batch with a FRESH Metadata: input-layer hash build, every
+rulebook, every layer, the 20-class linear head and (N > 1) the NCCL gather of the per-voxel
+outputs.  `value` = voxels/s with inputs resident in HBM; `e2e` = the same through the public
+API from pinned host buffers (host->device copy of coordinates and features, device->host
+copy of the scores inside the timed region).  Weak scaling: every rank runs its own 8 rooms.
+
+Also reported on the same line: `submanifold_conv` (BASELINE configuration 1: one 32->32
+3-D submanifold convolution, active sites/s cold / warm / rulebook only), `roofline` of the
+dominant kernel from CUDA-event timing of every operator call, `cpu_baseline` (the reference's
+CPU implementation timed on this box's host cores on a bounded sample) and `clocks`.
+
+`--impl reference` times the reference's own CPU implementation (oracle/_ref, compiled from
+the reference sources; the numpy restatement if that is absent) on one room per step.
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CONFIG = 3
+ROOMS_PER_GPU = 8
+METRIC = "unet3d_voxels_per_sec"
+UNIT = "voxels/s"
+# DRAM bytes per launch of the dominant kernel from the committed ncu capture, as a multiple
+# of the algorithmic bytes of that launch (profiles/); None until a capture is committed.
+TRAFFIC_RATIO = None
+
+
+def workload_name():
+    return ("config3: 3D submanifold U-Net m=32 reps=2 planes[32..224] 4096^3, %d rooms x ~200k voxels "
+            "per GPU, fp32, fresh Metadata per step" % ROOMS_PER_GPU)
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML while a timed region runs
+    (read-only queries)."""
+
+    def __init__(self, index, period=0.02):
+        threading.Thread.__init__(self, daemon=True)
+        self.index, self.period = index, period
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop_flag = threading.Event()
+
+    def run(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            names = {
+                getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+                getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+                getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+                getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+            }
+            get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                nv.nvmlDeviceGetCurrentClocksThrottleReasons
+            while not self._stop_flag.is_set():
+                self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                r = get_reasons(h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+                time.sleep(self.period)
+        except Exception as e:  # clocks are evidence, not a dependency
+            self.reasons.add("unavailable: %s" % type(e).__name__)
+
+    def stop(self):
+        self._stop_flag.set()
+        self.join(timeout=2)
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+def conv_bytes(r):
+    """Algorithmic bytes of one convolution call: one gathered input row and one 8-byte rule
+    per rule, every output row written once, the weights once."""
+    groups = r["groups"]
+    cin, cout = r["cin"] * groups, r["cout"] * groups
+    rules = r["macs"] / max(r["cin"] * r["cout"] * groups, 1)
+    return rules * (cin * 4 + 8) + r["n_out"] * cout * 4 + r["offsets"] * r["cin"] * r["cout"] * groups * 4
+
+
+def op_bytes(r):
+    k = r["kind"]
+    if k == "conv":
+        return conv_bytes(r)
+    if k == "batchnorm":
+        return 2.0 * r["rows"] * r["planes"] * 4
+    if k == "rules_submanifold":
+        # coords in, one slot written at insert time is accounted to input_hash; here: one key
+        # read per site, one 16-byte slot per probe, one 4-byte table entry per (site, offset)
+        return r["sites"] * 8 + r["sites"] * r["offsets"] * (16 + 4)
+    if k == "rules_strided":
+        return r["sites"] * (8 + 16 + 16) + r.get("sites_out", 0) * (16 + 8 + 4 * r["offsets"])
+    if k == "input_hash":
+        return r["rows"] * r["cols"] * 8 + r["rows"] * 16 + r.get("sites", 0) * 8
+    if k == "input_features":
+        return (r["rows"] + r["sites"]) * r["planes"] * 4
+    return 0.0
+
+
+def summarize_profile(rows):
+    agg = {}
+    for r in rows:
+        a = agg.setdefault(r["kind"], {"ms": 0.0, "calls": 0, "bytes": 0.0, "flops": 0.0})
+        a["ms"] += r["ms"]
+        a["calls"] += 1
+        a["bytes"] += op_bytes(r)
+        if r["kind"] == "conv":
+            a["flops"] += 2.0 * r["macs"]
+    return agg
+
+
+def run_reference(args, rank):
+    """The reference's CPU implementation on the host cores: K steps of one room each."""
+    if rank != 0:
+        return
+    import numpy as np
+    import torch
+    from oracle import runner
+    from sparseconvnet_b200 import workloads
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    be, kind = (runner.RefBackend(), "reference") if runner.reference_available() else (runner.PortBackend(), "port")
+    inp, net, head = workloads.build_config(CONFIG)
+    rooms = [workloads.batch_config3([s]) for s in range(max(1, min(args.steps + args.warmup, 4)))]
+
+    def step(i):
+        c, f = rooms[i % len(rooms)]
+        y = runner.run_module(net, runner.run_module(inp, [c, f], be), be)
+        runner.run_module(head, y, be)
+        return c.shape[0]
+
+    for i in range(args.warmup):
+        step(i)
+    t0 = time.perf_counter()
+    vox = 0
+    for i in range(args.steps):
+        vox += step(args.warmup + i)
+    dt = time.perf_counter() - t0
+    v = vox / dt
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(), "sample": "one room (~200k voxels) per step"},
+        "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": kind,
+                         "sample": "one room (~200k voxels) per step, %d steps" % args.steps},
+        "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+def cpu_baseline_sample():
+    """Bounded CPU sample for the default run: the reference CPU build on one room, 1 warm-up +
+    3 timed forwards (about 10 s of CPU work)."""
+    import torch
+    from oracle import runner
+    from sparseconvnet_b200 import workloads
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    ref = runner.reference_available()
+    be, kind = (runner.RefBackend(), "reference") if ref else (runner.PortBackend(), "port")
+    inp, net, head = workloads.build_config(CONFIG)
+    c, f = workloads.batch_config3([0], target_voxels=200000 if ref else 20000)
+    times = []
+    for i in range(4 if ref else 2):
+        t0 = time.perf_counter()
+        y = runner.run_module(net, runner.run_module(inp, [c, f], be), be)
+        runner.run_module(head, y, be)
+        times.append(time.perf_counter() - t0)
+    t = sorted(times[1:])[len(times[1:]) // 2]
+    return {"value": c.shape[0] / t, "unit": UNIT, "cores": cores, "kind": kind,
+            "sample": "one room of %d voxels, median of %d forwards after 1 warm-up" % (c.shape[0], len(times) - 1)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile-out", default=None, help="write the per-operator breakdown to this file")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        return run_reference(args, rank)
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    import sparseconvnet_b200 as scn
+    from sparseconvnet_b200 import SCN, shard, workloads
+
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    inp, net, head = workloads.build_config(CONFIG)
+    net.to(dev)
+    head.to(dev)
+    samples = list(range(rank * ROOMS_PER_GPU, (rank + 1) * ROOMS_PER_GPU))
+    coords_np, feats_np = workloads.make_batch(CONFIG, samples)
+    coords_host = torch.from_numpy(coords_np).pin_memory()
+    feats_host = torch.from_numpy(feats_np).pin_memory()
+    coords_dev, feats_dev = coords_host.to(dev), feats_host.to(dev)
+    n_vox = coords_np.shape[0]
+    out_host = torch.empty(n_vox, 20, dtype=torch.float32).pin_memory()
+
+    def forward(c, f):
+        """Returns this rank's per-voxel scores; with N > 1 every rank also receives all ranks'
+        rows (one padded all_gather over NCCL)."""
+        with torch.no_grad():
+            y = head(net(inp([c, f])).features)
+            if world > 1:
+                shard.gather_rows(y)
+        return y
+
+    def step_resident():
+        return forward(coords_dev, feats_dev)
+
+    def step_e2e():
+        c = coords_host.to(dev, non_blocking=True)
+        f = feats_host.to(dev, non_blocking=True)
+        y = forward(c, f)
+        out_host.copy_(y, non_blocking=True)
+        return y
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = SCN.launch_count()
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        barrier()
+        ms = a.elapsed_time(b)
+        launches = SCN.launch_count() - l0
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, launches
+
+    for _ in range(args.warmup):
+        step_resident()
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms, launches = timed(step_resident, args.steps)
+    clocks = sampler.stop()
+    for _ in range(2):
+        step_e2e()
+    ms_e2e, _ = timed(step_e2e, args.steps)
+
+    total_vox = n_vox
+    if world > 1:
+        t = torch.tensor([n_vox], device=dev, dtype=torch.int64)
+        dist.all_reduce(t)
+        total_vox = int(t.item())
+    value = total_vox * args.steps / (ms / 1e3)
+    e2e = total_vox * args.steps / (ms_e2e / 1e3)
+
+    # ---- per-operator breakdown (CUDA events around every operator call, one extra step) -------
+    with SCN.Profile() as prof:
+        step_resident()
+    agg = summarize_profile(prof.rows())
+    peak, peak_src = peaks()
+    top = max(agg, key=lambda k: agg[k]["ms"])
+    a = agg[top]
+    achieved = a["bytes"] / (a["ms"] / 1e3) / 1e9
+    roofline = {"kernel": {"conv": "k_conv_simt", "batchnorm": "k_bn_apply", "rules_submanifold": "k_submanifold_rules",
+                           "rules_strided": "k_strided_*", "input_hash": "k_insert_input"}.get(top, top),
+                "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "peak_source": peak_src,
+                "traffic": (TRAFFIC_RATIO * a["bytes"] / a["calls"]) if TRAFFIC_RATIO else None,
+                "algorithmic_bytes_per_step": a["bytes"], "launches_per_step": a["calls"], "ms_per_step": a["ms"],
+                "tflops": a["flops"] / (a["ms"] / 1e3) / 1e12 if a["flops"] else None}
+    breakdown = {k: {"ms": round(v["ms"], 4), "calls": v["calls"],
+                     "GBps": round(v["bytes"] / (v["ms"] / 1e3) / 1e9, 1) if v["ms"] > 0 else None}
+                 for k, v in sorted(agg.items(), key=lambda kv: -kv[1]["ms"])}
+
+    # ---- configuration 1: one 3-D submanifold convolution 32->32 ------------------------------
+    sub = None
+    if rank == 0:
+        inp1, net1, _ = workloads.build_config(1)
+        net1.to(dev)
+        c1, f1 = workloads.make_batch(1, [0])
+        c1d, f1d = torch.from_numpy(c1).to(dev), torch.from_numpy(f1).to(dev)
+
+        def ev_time(fn, reps):
+            torch.cuda.synchronize()
+            a_, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a_.record()
+            for _ in range(reps):
+                fn()
+            b_.record()
+            torch.cuda.synchronize()
+            return a_.elapsed_time(b_) / reps
+
+        with torch.no_grad():
+            def cold():
+                return net1(inp1([c1d, f1d]))
+
+            for _ in range(3):
+                x1 = inp1([c1d, f1d])
+                net1(x1)
+            t_cold = ev_time(cold, 10)
+            t_warm = ev_time(lambda: net1(x1), 20)
+
+            def rules_only():
+                x = inp1([c1d, f1d])
+                SCN.lib.scn_md_submanifold_rulebook(x.metadata._h, SCN.sizes([256] * 3), SCN.sizes([3] * 3),
+                                                    SCN._stream(), None)
+            t_rules = ev_time(rules_only, 10)
+        n1 = c1.shape[0]
+        sub = {"workload": "config1: SubmanifoldConvolution 3D f3 32->32 fp32, 256^3, batch 1", "sites": n1,
+               "cold_sites_per_sec": n1 / (t_cold / 1e3), "warm_sites_per_sec": n1 / (t_warm / 1e3),
+               "hash_and_rulebook_sites_per_sec": n1 / (t_rules / 1e3),
+               "ms": {"cold": t_cold, "warm": t_warm, "hash_and_rulebook": t_rules}}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu = cpu_baseline_sample()
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": workload_name(), "voxels_per_step": total_vox,
+                       "l2": "inputs and activations (>200 MB per tensor) exceed the 126 MB L2",
+                       "precision": scn.get_precision(), "parallelism": "dp%d by batch index" % world},
+            "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
+                    "h2d_bytes_per_step": int(coords_host.numel() * 8 + feats_host.numel() * 4),
+                    "d2h_bytes_per_step": int(out_host.numel() * 4)},
+            "gpu_launches": int(launches),
+            "roofline": roofline, "breakdown_ms_per_step": breakdown, "submanifold_conv": sub,
+            "cpu_baseline": cpu, "clocks": clocks,
+        }
+        print(json.dumps(line))
+        if args.profile_out:
+            with open(args.profile_out, "w") as f:
+                json.dump({"breakdown": breakdown, "rows": prof.rows()}, f, indent=1)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

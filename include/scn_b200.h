@@ -72,6 +72,9 @@ enum scn_rulebook_kind {
 SCN_API int scn_abi_version(void);
 SCN_API const char *scn_status_string(int status);
 SCN_API const char *scn_last_error(void);
+/* number of CUDA kernels this library has launched in this process so far (no counterpart in
+ * the reference; used to report how many kernels a timed region ran) */
+SCN_API long long scn_launch_count(void);
 
 /* ---- Metadata object ------------------------------------------------------------------ */
 

@@ -141,8 +141,8 @@ class RefBackend(object):
 
     def nin(self, x, weight, bias):
         out = torch.empty(0)
-        self.SCN.NetworkInNetwork_updateOutput(self._t(x.features), out, self._opt(weight), self._opt(bias))
-        return OTensor(out.numpy(), x.metadata, x.spatial_size)
+        macs = self.SCN.NetworkInNetwork_updateOutput(self._t(x.features), out, self._opt(weight), self._opt(bias))
+        return OTensor(out.numpy(), x.metadata, x.spatial_size), macs
 
 
 class _PortMetadata(object):
@@ -224,7 +224,8 @@ class PortBackend(object):
         out = x.features @ _np(weight)
         if bias is not None:
             out = out + _np(bias)
-        return OTensor(out.astype(np.float32), x.metadata, x.spatial_size)
+        macs = float(x.features.shape[0]) * weight.shape[0] * weight.shape[1]  # CPU/NetworkInNetwork.cpp:22
+        return OTensor(out.astype(np.float32), x.metadata, x.spatial_size), macs
 
 
 def run_module(m, x, be, stats=None):
@@ -277,7 +278,9 @@ def run_module(m, x, be, stats=None):
     if name == "SparseToDense":
         return be.sparse_to_dense(x, m.nPlanes)
     if name == "NetworkInNetwork":
-        return be.nin(x, m.weight, getattr(m, "bias", None))
+        y, macs = be.nin(x, m.weight, getattr(m, "bias", None))
+        count(macs)
+        return y
     if name == "Linear":
         f = x.features if isinstance(x, OTensor) else x
         y = f @ _np(m.weight).T

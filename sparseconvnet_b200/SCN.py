@@ -39,6 +39,50 @@ def _stream():
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+class Profile(object):
+    """Optional per-operator timing: inside ``with SCN.Profile() as p`` every operator call
+    records a pair of CUDA events on the current stream around its kernels, plus the sizes
+    needed to turn the time into algorithmic bytes and FLOPs.  ``p.rows()`` (after a
+    synchronize) lists dicts with ``kind``, ``ms`` and those sizes.  Off by default."""
+    active = None
+
+    def __enter__(self):
+        self.records = []
+        Profile.active = self
+        return self
+
+    def __exit__(self, *exc):
+        Profile.active = None
+
+    def rows(self):
+        torch.cuda.synchronize()
+        return [dict(info, kind=kind, ms=a.elapsed_time(b)) for kind, info, a, b in self.records]
+
+
+class _timed(object):
+    def __init__(self, kind, info):
+        self.kind, self.info = kind, info
+
+    def __enter__(self):
+        p = Profile.active
+        if p is not None:
+            self.a = torch.cuda.Event(enable_timing=True)
+            self.b = torch.cuda.Event(enable_timing=True)
+            self.a.record()
+        return self.info
+
+    def __exit__(self, *exc):
+        p = Profile.active
+        if p is not None and exc[0] is None:
+            self.b.record()
+            p.records.append((self.kind, self.info, self.a, self.b))
+
+
+def launch_count():
+    """Kernels launched by the library in this process so far."""
+    return lib.scn_launch_count()
+
+
 def _features(t, name):
     if not t.is_cuda:
         raise RuntimeError("%s must be a CUDA tensor: sparseconvnet_b200 has no CPU path" % name)
@@ -172,12 +216,15 @@ def InputLayer_updateOutput(m, spatial_size, input_coords, input_features, outpu
     m.device = f.device
     n_active = C.c_int64()
     with torch.cuda.device(f.device):
-        check(lib.scn_md_input_layer(m._h, sizes(spatial_size), _ptr(coords), int(coords.is_cuda),
-                                     coords.size(0), coords.size(1), int(batch_size), int(mode),
-                                     _stream(), C.byref(n_active)))
+        with _timed("input_hash", dict(rows=coords.size(0), cols=coords.size(1), mode=int(mode))) as info:
+            check(lib.scn_md_input_layer(m._h, sizes(spatial_size), _ptr(coords), int(coords.is_cuda),
+                                         coords.size(0), coords.size(1), int(batch_size), int(mode),
+                                         _stream(), C.byref(n_active)))
+            info["sites"] = n_active.value
         output_features.resize_(n_active.value, f.size(1))
-        check(lib.scn_input_layer_forward(m._h, _ptr(f), f.size(0), _ptr(output_features), n_active.value,
-                                          f.size(1), _stream()))
+        with _timed("input_features", dict(rows=coords.size(0), sites=n_active.value, planes=f.size(1))):
+            check(lib.scn_input_layer_forward(m._h, _ptr(f), f.size(0), _ptr(output_features), n_active.value,
+                                              f.size(1), _stream()))
 
 
 def _conv_args(input_features, weight, bias):
@@ -204,9 +251,14 @@ def SubmanifoldConvolution_updateOutput(inputSize, filterSize, m, input_features
         if f.size(0) != n:
             raise RuntimeError("features have %d rows, metadata has %d active sites" % (f.size(0), n))
         output_features.resize_(n, groups * cout)
-        check(lib.scn_submanifold_convolution_forward(
-            m._h, sizes(inputSize), sizes(filterSize), _ptr(f), _ptr(output_features), _ptr(w), _ptr(b),
-            groups * cin, groups * cout, groups, _precision, _stream(), C.byref(macs)))
+        with _timed("rules_submanifold", dict(sites=n, offsets=w.size(0), dim=m.dimension)) as info:
+            check(lib.scn_md_submanifold_rulebook(m._h, sizes(inputSize), sizes(filterSize), _stream(), None))
+        with _timed("conv", dict(op="submanifold", n_in=n, n_out=n, cin=cin, cout=cout, groups=groups,
+                                 offsets=w.size(0), precision=_precision)) as info:
+            check(lib.scn_submanifold_convolution_forward(
+                m._h, sizes(inputSize), sizes(filterSize), _ptr(f), _ptr(output_features), _ptr(w), _ptr(b),
+                groups * cin, groups * cout, groups, _precision, _stream(), C.byref(macs)))
+            info["macs"] = macs.value
     return macs.value
 
 
@@ -220,13 +272,18 @@ def Convolution_updateOutput(inputSize, outputSize, filterSize, filterStride, m,
         if f.size(0) != m.getNActive(inputSize):
             raise RuntimeError("features have %d rows, metadata has %d active sites"
                                % (f.size(0), m.getNActive(inputSize)))
-        check(lib.scn_md_strided_rulebook(m._h, sizes(inputSize), sizes(outputSize), sizes(filterSize),
-                                          sizes(filterStride), _stream(), C.byref(n_out), None))
+        with _timed("rules_strided", dict(sites=f.size(0), offsets=w.size(0), dim=m.dimension)) as info:
+            check(lib.scn_md_strided_rulebook(m._h, sizes(inputSize), sizes(outputSize), sizes(filterSize),
+                                              sizes(filterStride), _stream(), C.byref(n_out), None))
+            info["sites_out"] = n_out.value
         output_features.resize_(n_out.value, groups * cout)
-        check(lib.scn_convolution_forward(
-            m._h, sizes(inputSize), sizes(outputSize), sizes(filterSize), sizes(filterStride), _ptr(f),
-            _ptr(output_features), _ptr(w), _ptr(b), groups * cin, groups * cout, groups, _precision,
-            _stream(), C.byref(macs)))
+        with _timed("conv", dict(op="strided", n_in=f.size(0), n_out=n_out.value, cin=cin, cout=cout,
+                                 groups=groups, offsets=w.size(0), precision=_precision)) as info:
+            check(lib.scn_convolution_forward(
+                m._h, sizes(inputSize), sizes(outputSize), sizes(filterSize), sizes(filterStride), _ptr(f),
+                _ptr(output_features), _ptr(w), _ptr(b), groups * cin, groups * cout, groups, _precision,
+                _stream(), C.byref(macs)))
+            info["macs"] = macs.value
     return macs.value
 
 
@@ -242,11 +299,15 @@ def Deconvolution_updateOutput(inputSize, outputSize, filterSize, filterStride, 
         if f.size(0) != m.getNActive(inputSize):
             raise RuntimeError("features have %d rows, metadata has %d active sites"
                                % (f.size(0), m.getNActive(inputSize)))
-        output_features.resize_(m.getNActive(outputSize), groups * cout)
-        check(lib.scn_deconvolution_forward(
-            m._h, sizes(inputSize), sizes(outputSize), sizes(filterSize), sizes(filterStride), _ptr(f),
-            _ptr(output_features), _ptr(w), _ptr(b), groups * cin, groups * cout, groups, _precision,
-            _stream(), C.byref(macs)))
+        n_fine = m.getNActive(outputSize)
+        output_features.resize_(n_fine, groups * cout)
+        with _timed("conv", dict(op="deconvolution", n_in=f.size(0), n_out=n_fine, cin=cin, cout=cout,
+                                 groups=groups, offsets=w.size(0), precision=_precision)) as info:
+            check(lib.scn_deconvolution_forward(
+                m._h, sizes(inputSize), sizes(outputSize), sizes(filterSize), sizes(filterStride), _ptr(f),
+                _ptr(output_features), _ptr(w), _ptr(b), groups * cin, groups * cout, groups, _precision,
+                _stream(), C.byref(macs)))
+            info["macs"] = macs.value
     return macs.value
 
 
@@ -266,11 +327,12 @@ def BatchNormalization_updateOutput(input_features, output_features, saveMean, s
             return
         w = _optional(weight, f, "weight")
         b = _optional(bias, f, "bias")
-        check(lib.scn_batchnorm_forward(
-            _ptr(f), _ptr(output_features), n, c, f.stride(0), output_features.stride(0), _ptr(saveMean),
-            _ptr(saveInvStd), _ptr(_features(runningMean, "runningMean")),
-            _ptr(_features(runningVar, "runningVar")), _ptr(w), _ptr(b), float(eps), float(momentum),
-            int(bool(train)), float(leakiness), _stream()))
+        with _timed("batchnorm", dict(rows=n, planes=c)):
+            check(lib.scn_batchnorm_forward(
+                _ptr(f), _ptr(output_features), n, c, f.stride(0), output_features.stride(0), _ptr(saveMean),
+                _ptr(saveInvStd), _ptr(_features(runningMean, "runningMean")),
+                _ptr(_features(runningVar, "runningVar")), _ptr(w), _ptr(b), float(eps), float(momentum),
+                int(bool(train)), float(leakiness), _stream()))
 
 
 def MaxPooling_updateOutput(inputSize, outputSize, poolSize, poolStride, m, input_features,

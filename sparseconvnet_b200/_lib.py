@@ -17,6 +17,7 @@ SIGNATURES = {
     "scn_abi_version": (C.c_int, []),
     "scn_status_string": (C.c_char_p, [C.c_int]),
     "scn_last_error": (C.c_char_p, []),
+    "scn_launch_count": (C.c_longlong, []),
     "scn_md_create": (C.c_int, [C.c_int, C.POINTER(_vp)]),
     "scn_md_destroy": (C.c_int, [_vp]),
     "scn_md_clear": (C.c_int, [_vp, _vp]),
@@ -56,7 +57,7 @@ class ScnError(RuntimeError):
 def _load():
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            "%s is missing: build it with `python -m sparseconvnet_b200.build` "
+            "%s is missing: build it with `python sparseconvnet_b200/build.py` "
             "(there is no CPU fallback)" % LIB_PATH)
     lib = C.CDLL(LIB_PATH)
     for name, (res, args) in SIGNATURES.items():

@@ -4,7 +4,8 @@ Every ``csrc/*.cu`` is compiled for sm_100a only
 (``-gencode arch=compute_100a,code=sm_100a``) and linked into one shared library next to
 this file.  nvcc cross-compiles without a GPU.
 
-Usage:  python -m sparseconvnet_b200.build [--force] [--verbose]
+Usage:  python sparseconvnet_b200/build.py [--force] [--verbose]
+(run as a script: importing the package needs the library this builds)
 """
 import concurrent.futures as cf
 import glob

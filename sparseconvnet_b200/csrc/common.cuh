@@ -40,6 +40,15 @@ void set_error(const char *fmt, ...);
     }                                                                                          \
   } while (0)
 
+// Every kernel launch of the library goes through this macro so that the number of launches
+// can be read back (scn_launch_count), e.g. to state how many kernels a timed region ran.
+void note_launch();
+#define SCN_LAUNCH(kernel, grid, block, smem, stream, ...)                                      \
+  do {                                                                                         \
+    scn::note_launch();                                                                        \
+    kernel<<<(grid), (block), (smem), (stream)>>>(__VA_ARGS__);                                \
+  } while (0)
+
 // Kernels report problems by OR-ing a bit into a device word; the host reads it at the next
 // point where it waits for the stream anyway.  Nothing on the device traps.
 enum DeviceFlag : int {

@@ -214,9 +214,7 @@ static int launch_simt(const float *in, int ld_in, long long n_in, float *out, i
   int vec_in = (ld_in % 4 == 0) && (cin % 4 == 0) && ((uintptr_t)in % 16 == 0);
   int vec_w = (cout % 4 == 0) && ((uintptr_t)weight % 16 == 0) && (((long long)cin * cout) % 4 == 0);
   dim3 grid((unsigned)ceil_div(n_out, kTileRows), (unsigned)ceil_div(cout, BN), (unsigned)groups);
-  k_conv_simt<BN><<<grid, kThreads, smem, stream>>>(in, ld_in, n_in, out, ld_out, n_out, weight,
-                                                   (long long)groups * cin * cout, (long long)cin * cout,
-                                                   bias, table, K, cin, cout, vec_in, vec_w, flags);
+  SCN_LAUNCH(k_conv_simt<BN>, grid, kThreads, smem, stream, in, ld_in, n_in, out, ld_out, n_out, weight, (long long)groups * cin * cout, (long long)cin * cout, bias, table, K, cin, cout, vec_in, vec_w, flags);
   SCN_CUDA_CHECK(cudaGetLastError());
   return SCN_OK;
 }

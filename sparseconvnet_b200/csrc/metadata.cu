@@ -316,33 +316,31 @@ static int md_input_layer(scn_metadata *md, const int64_t *spatial_size, const i
 
   const int threads = 256;
   unsigned blocks = (unsigned)ceil_div(std::max<int64_t>(n, 1), threads);
-  k_init_scalars<<<1, 1, 0, stream>>>(md->scalars_dev);
+  SCN_LAUNCH(k_init_scalars, 1, 1, 0, stream, md->scalars_dev);
   int *slot_of = nullptr, *flag = nullptr, *rank = nullptr, *cursor = nullptr;
   SCN_TRY(device_alloc((void **)&slot_of, sizeof(int) * (size_t)std::max<int64_t>(n, 1), stream));
   if (n > 0) {
-    k_insert_input<<<blocks, threads, 0, stream>>>(g.layout, g.table, coords_dev, n, ncols, mode,
-                                                   g.row_keys, slot_of, md->flags_dev, md->scalars_dev);
+    SCN_LAUNCH(k_insert_input, blocks, threads, 0, stream, g.layout, g.table, coords_dev, n, ncols, mode, g.row_keys, slot_of, md->flags_dev, md->scalars_dev);
     if (mode == 0)
-      k_blank_overwritten<<<blocks, threads, 0, stream>>>(g.table.slots, slot_of, n, g.row_keys);
+      SCN_LAUNCH(k_blank_overwritten, blocks, threads, 0, stream, g.table.slots, slot_of, n, g.row_keys);
     SCN_CUDA_CHECK(cudaGetLastError());
   }
   if (mode != 0 && n > 0) {
     SCN_TRY(device_alloc((void **)&flag, sizeof(int) * (size_t)n, stream));
     SCN_TRY(device_alloc((void **)&rank, sizeof(int) * (size_t)n, stream));
-    k_flag_first<<<blocks, threads, 0, stream>>>(g.table.slots, slot_of, n, flag);
+    SCN_LAUNCH(k_flag_first, blocks, threads, 0, stream, g.table.slots, slot_of, n, flag);
     SCN_TRY(exclusive_scan_i32(flag, rank, n, &md->scalars_dev[0], stream));
-    k_number_input_sites<<<blocks, threads, 0, stream>>>(g.table.slots, slot_of, flag, rank, n, g.row_keys);
+    SCN_LAUNCH(k_number_input_sites, blocks, threads, 0, stream, g.table.slots, slot_of, flag, rank, n, g.row_keys);
     SCN_CUDA_CHECK(cudaGetLastError());
     // CSR of input rows per site
     SCN_TRY(device_alloc((void **)&md->input_csr_start, sizeof(int) * (size_t)(n + 1), stream));
     SCN_TRY(device_alloc((void **)&md->input_csr_rows, sizeof(int) * (size_t)n, stream));
     SCN_TRY(device_alloc((void **)&cursor, sizeof(int) * (size_t)(n + 1), stream));
     SCN_CUDA_CHECK(cudaMemsetAsync(cursor, 0, sizeof(int) * (size_t)(n + 1), stream));
-    k_count_per_site<<<blocks, threads, 0, stream>>>(g.table.slots, slot_of, n, cursor);
+    SCN_LAUNCH(k_count_per_site, blocks, threads, 0, stream, g.table.slots, slot_of, n, cursor);
     SCN_TRY(exclusive_scan_i32(cursor, md->input_csr_start, n + 1, nullptr, stream));
     SCN_CUDA_CHECK(cudaMemsetAsync(cursor, 0, sizeof(int) * (size_t)(n + 1), stream));
-    k_fill_per_site<<<blocks, threads, 0, stream>>>(g.table.slots, slot_of, n, md->input_csr_start,
-                                                    cursor, md->input_csr_rows);
+    SCN_LAUNCH(k_fill_per_site, blocks, threads, 0, stream, g.table.slots, slot_of, n, md->input_csr_start, cursor, md->input_csr_rows);
     SCN_CUDA_CHECK(cudaGetLastError());
   }
 
@@ -351,7 +349,7 @@ static int md_input_layer(scn_metadata *md, const int64_t *spatial_size, const i
   long long active = (mode == 0) ? n : (n > 0 ? sc[0] : 0);
   if (mode != 0 && n > 0 && flags == 0 && active > 0) {
     unsigned sblocks = (unsigned)ceil_div(active, threads);
-    k_sort_segments<<<sblocks, threads, 0, stream>>>(md->input_csr_start, active, md->input_csr_rows);
+    SCN_LAUNCH(k_sort_segments, sblocks, threads, 0, stream, md->input_csr_start, active, md->input_csr_rows);
     SCN_CUDA_CHECK(cudaGetLastError());
   }
   device_free(staged, stream);
@@ -502,8 +500,7 @@ int get_submanifold_rulebook(scn_metadata *md, const int64_t *spatial_size,
     int k_chunk = (int)ceil_div(K, want_y);
     int gy = (int)ceil_div(K, k_chunk);
     size_t smem = (size_t)k_chunk * (sizeof(long long) + sizeof(int) + md->dim);
-    k_submanifold_rules<<<dim3((unsigned)bx, (unsigned)gy), threads, smem, stream>>>(
-        g->layout, g->table, g->row_keys, n, (int)K, F, k_chunk, rb.nbr, rb.counts_dev);
+    SCN_LAUNCH(k_submanifold_rules, dim3((unsigned)bx, (unsigned)gy), threads, smem, stream, g->layout, g->table, g->row_keys, n, (int)K, F, k_chunk, rb.nbr, rb.counts_dev);
     SCN_CUDA_CHECK(cudaGetLastError());
   }
   rb.built = true;
@@ -651,9 +648,8 @@ int get_strided_rulebook(scn_metadata *md, const int64_t *input_size, const int6
     long long expect = n_in;
     for (int attempt = 0;; ++attempt) {
       SCN_TRY(alloc_table(gout.table, expect, stream));
-      k_strided_insert<<<blocks, threads, 0, stream>>>(gin->layout, gout.layout, F, gout.table,
-                                                       gin->row_keys, n_in, slot_of, md->flags_dev);
-      k_flag_first<<<blocks, threads, 0, stream>>>(gout.table.slots, slot_of, n_ids, flag);
+      SCN_LAUNCH(k_strided_insert, blocks, threads, 0, stream, gin->layout, gout.layout, F, gout.table, gin->row_keys, n_in, slot_of, md->flags_dev);
+      SCN_LAUNCH(k_flag_first, blocks, threads, 0, stream, gout.table.slots, slot_of, n_ids, flag);
       SCN_TRY(exclusive_scan_i32(flag, rank, n_ids, &md->scalars_dev[0], stream));
       SCN_CUDA_CHECK(cudaGetLastError());
       int flags = 0, sc[4];
@@ -691,9 +687,8 @@ int get_strided_rulebook(scn_metadata *md, const int64_t *input_size, const int6
   SCN_CUDA_CHECK(cudaMemsetAsync(rb.counts_dev, 0, sizeof(unsigned long long) * (size_t)K, stream));
   if (n_ids > 0) {
     unsigned blocks = (unsigned)ceil_div(n_ids, threads);
-    k_strided_number<<<blocks, threads, 0, stream>>>(gout.table.slots, slot_of, flag, rank, n_ids, gout.row_keys);
-    k_strided_fill<<<blocks, threads, 0, stream>>>(gin->layout, F, gout.table.slots, gin->row_keys,
-                                                   slot_of, n_in, n_out, rb.nbr, rb.counts_dev);
+    SCN_LAUNCH(k_strided_number, blocks, threads, 0, stream, gout.table.slots, slot_of, flag, rank, n_ids, gout.row_keys);
+    SCN_LAUNCH(k_strided_fill, blocks, threads, 0, stream, gin->layout, F, gout.table.slots, gin->row_keys, slot_of, n_in, n_out, rb.nbr, rb.counts_dev);
     SCN_CUDA_CHECK(cudaGetLastError());
   }
   device_free(slot_of, stream);
@@ -738,8 +733,7 @@ int rulebook_transposed(Rulebook &rb, cudaStream_t stream) {
   SCN_CUDA_CHECK(cudaMemsetAsync(rb.tnbr, 0xFF, bytes, stream));
   long long total = (long long)rb.n_offsets * rb.n_out;
   if (total > 0) {
-    k_transpose_rules<<<(unsigned)ceil_div(total, 256), 256, 0, stream>>>(rb.nbr, rb.n_out, rb.n_in,
-                                                                          rb.n_offsets, rb.tnbr);
+    SCN_LAUNCH(k_transpose_rules, (unsigned)ceil_div(total, 256), 256, 0, stream, rb.nbr, rb.n_out, rb.n_in, rb.n_offsets, rb.tnbr);
     SCN_CUDA_CHECK(cudaGetLastError());
   }
   return SCN_OK;
@@ -773,9 +767,9 @@ static int rulebook_export(Rulebook &rb, int64_t *n_offsets, int64_t *counts_hos
   int *flag = nullptr;
   SCN_TRY(device_alloc((void **)&flag, sizeof(int) * (size_t)total, stream));
   unsigned blocks = (unsigned)ceil_div(total, 256);
-  k_rule_flags<<<blocks, 256, 0, stream>>>(rb.nbr, total, flag);
+  SCN_LAUNCH(k_rule_flags, blocks, 256, 0, stream, rb.nbr, total, flag);
   SCN_TRY(exclusive_scan_i32(flag, flag, total, nullptr, stream));
-  k_rule_compact<<<blocks, 256, 0, stream>>>(rb.nbr, flag, total, rb.n_out, pairs_dev);
+  SCN_LAUNCH(k_rule_compact, blocks, 256, 0, stream, rb.nbr, flag, total, rb.n_out, pairs_dev);
   SCN_CUDA_CHECK(cudaGetLastError());
   SCN_TRY(device_free(flag, stream));
   return SCN_OK;
@@ -843,8 +837,7 @@ int scn_md_spatial_locations(scn_metadata *md, const int64_t *spatial_size, int6
   SCN_REQUIRE(g, SCN_ERR_NO_GRID, "no grid for that spatial size");
   if (g->n_active == 0) return SCN_OK;
   SCN_REQUIRE(out_dev, SCN_ERR_BAD_ARG, "null output");
-  k_spatial_locations<<<(unsigned)ceil_div(g->n_active, 256), 256, 0, (cudaStream_t)stream>>>(
-      g->layout, g->row_keys, g->n_active, (long long *)out_dev);
+  SCN_LAUNCH(k_spatial_locations, (unsigned)ceil_div(g->n_active, 256), 256, 0, (cudaStream_t)stream, g->layout, g->row_keys, g->n_active, (long long *)out_dev);
   SCN_CUDA_CHECK(cudaGetLastError());
   return SCN_OK;
 }

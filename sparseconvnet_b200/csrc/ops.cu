@@ -192,8 +192,7 @@ int scn_input_layer_forward(scn_metadata *md, const float *in_features, int64_t 
     return SCN_OK;
   }
   long long total = (long long)n_out * n_planes;
-  k_input_features<<<(unsigned)ceil_div(total, 256), 256, 0, stream>>>(
-      in_features, out_features, md->input_csr_start, md->input_csr_rows, n_out, n_planes, md->input_mode);
+  SCN_LAUNCH(k_input_features, (unsigned)ceil_div(total, 256), 256, 0, stream, in_features, out_features, md->input_csr_start, md->input_csr_rows, n_out, n_planes, md->input_mode);
   SCN_CUDA_CHECK(cudaGetLastError());
   return SCN_OK;
 }
@@ -214,25 +213,18 @@ int scn_batchnorm_forward(const float *in_features, float *out_features, int64_t
     SCN_TRY(device_alloc((void **)&sums, sizeof(double) * 2 * n_planes, stream));
     SCN_CUDA_CHECK(cudaMemsetAsync(sums, 0, sizeof(double) * 2 * n_planes, stream));
     unsigned gy = (unsigned)std::min<long long>(ceil_div(n_rows, 64), 1024);
-    k_bn_stats<<<dim3((unsigned)ceil_div(n_planes, 32), gy), 256, 0, stream>>>(in_features, n_rows, n_planes,
-                                                                             in_stride, sums);
+    SCN_LAUNCH(k_bn_stats, dim3((unsigned)ceil_div(n_planes, 32), gy), 256, 0, stream, in_features, n_rows, n_planes, in_stride, sums);
   }
-  k_bn_finalize<<<(unsigned)ceil_div(n_planes, 128), 128, 0, stream>>>(
-      n_planes, n_rows, sums, save_mean, save_invstd, running_mean, running_var, (float)eps,
-      (float)momentum, train);
+  SCN_LAUNCH(k_bn_finalize, (unsigned)ceil_div(n_planes, 128), 128, 0, stream, n_planes, n_rows, sums, save_mean, save_invstd, running_mean, running_var, (float)eps, (float)momentum, train);
   bool vec4 = (n_planes % 4 == 0) && (in_stride % 4 == 0) && (out_stride % 4 == 0) &&
               ((uintptr_t)in_features % 16 == 0) && ((uintptr_t)out_features % 16 == 0);
   long long work = n_rows * (vec4 ? n_planes / 4 : n_planes);
   unsigned blocks = (unsigned)std::min<long long>(ceil_div(work, 256), 148 * 16);
   size_t smem = sizeof(float) * 2 * n_planes;
   if (vec4)
-    k_bn_apply<4><<<blocks, 256, smem, stream>>>(in_features, out_features, n_rows, n_planes, in_stride,
-                                                 out_stride, save_mean, save_invstd, weight, bias,
-                                                 (float)leakiness);
+    SCN_LAUNCH(k_bn_apply<4>, blocks, 256, smem, stream, in_features, out_features, n_rows, n_planes, in_stride, out_stride, save_mean, save_invstd, weight, bias, (float)leakiness);
   else
-    k_bn_apply<1><<<blocks, 256, smem, stream>>>(in_features, out_features, n_rows, n_planes, in_stride,
-                                                 out_stride, save_mean, save_invstd, weight, bias,
-                                                 (float)leakiness);
+    SCN_LAUNCH(k_bn_apply<1>, blocks, 256, smem, stream, in_features, out_features, n_rows, n_planes, in_stride, out_stride, save_mean, save_invstd, weight, bias, (float)leakiness);
   SCN_CUDA_CHECK(cudaGetLastError());
   if (sums) SCN_TRY(device_free(sums, stream));
   return SCN_OK;
@@ -252,9 +244,7 @@ int scn_max_pooling_forward(scn_metadata *md, const int64_t *input_size, const i
   SCN_REQUIRE(in_features && out_features, SCN_ERR_BAD_ARG, "null features");
   int c_out = n_planes_in - n_features_to_drop;
   long long total = rb->n_out * c_out;
-  k_max_pool<<<(unsigned)ceil_div(total, 256), 256, 0, stream>>>(in_features, out_features, rb->nbr, rb->n_out,
-                                                                 rb->n_in, rb->n_offsets, c_out, n_planes_in,
-                                                                 n_features_to_drop, md->flags_dev);
+  SCN_LAUNCH(k_max_pool, (unsigned)ceil_div(total, 256), 256, 0, stream, in_features, out_features, rb->nbr, rb->n_out, rb->n_in, rb->n_offsets, c_out, n_planes_in, n_features_to_drop, md->flags_dev);
   SCN_CUDA_CHECK(cudaGetLastError());
   return SCN_OK;
 }
@@ -272,8 +262,7 @@ int scn_sparse_to_dense_forward(scn_metadata *md, const int64_t *spatial_size, c
   if (g->n_active == 0) return SCN_OK;
   SCN_REQUIRE(in_features, SCN_ERR_BAD_ARG, "null features");
   long long total = g->n_active * n_planes;
-  k_sparse_to_dense<<<(unsigned)ceil_div(total, 256), 256, 0, stream>>>(g->layout, g->row_keys, in_features,
-                                                                        out_dense, g->n_active, n_planes, volume);
+  SCN_LAUNCH(k_sparse_to_dense, (unsigned)ceil_div(total, 256), 256, 0, stream, g->layout, g->row_keys, in_features, out_dense, g->n_active, n_planes, volume);
   SCN_CUDA_CHECK(cudaGetLastError());
   return SCN_OK;
 }

@@ -2,6 +2,7 @@
 // rulebook builders.
 #include <stdarg.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
@@ -9,6 +10,9 @@
 namespace scn {
 
 static thread_local char g_last_error[512] = "";
+static std::atomic<long long> g_launches{0};
+
+void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 void set_error(const char *fmt, ...) {
   va_list ap;
@@ -115,21 +119,21 @@ __global__ void k_set_zero(int *p) { *p = 0; }
 int exclusive_scan_i32(const int *in, int *out, long long n, int *total_dev,
                        cudaStream_t stream) {
   if (n <= 0) {
-    if (total_dev) k_set_zero<<<1, 1, 0, stream>>>(total_dev);
+    if (total_dev) SCN_LAUNCH(k_set_zero, 1, 1, 0, stream, total_dev);
     return SCN_OK;
   }
   long long tiles = ceil_div(n, kScanTile);
   if (tiles == 1) {
-    k_scan_tiles<<<1, kScanThreads, 0, stream>>>(in, out, nullptr, n, total_dev);
+    SCN_LAUNCH(k_scan_tiles, 1, kScanThreads, 0, stream, in, out, nullptr, n, total_dev);
     SCN_CUDA_CHECK(cudaGetLastError());
     return SCN_OK;
   }
   int *sums = nullptr;
   SCN_TRY(device_alloc((void **)&sums, sizeof(int) * (size_t)tiles, stream));
-  k_scan_tile_sums<<<(unsigned)tiles, kScanThreads, 0, stream>>>(in, sums, n);
+  SCN_LAUNCH(k_scan_tile_sums, (unsigned)tiles, kScanThreads, 0, stream, in, sums, n);
   SCN_CUDA_CHECK(cudaGetLastError());
   SCN_TRY(exclusive_scan_i32(sums, sums, tiles, nullptr, stream));
-  k_scan_tiles<<<(unsigned)tiles, kScanThreads, 0, stream>>>(in, out, sums, n, total_dev);
+  SCN_LAUNCH(k_scan_tiles, (unsigned)tiles, kScanThreads, 0, stream, in, out, sums, n, total_dev);
   SCN_CUDA_CHECK(cudaGetLastError());
   SCN_TRY(device_free(sums, stream));
   return SCN_OK;
@@ -140,6 +144,8 @@ int exclusive_scan_i32(const int *in, int *out, long long n, int *total_dev,
 extern "C" {
 
 int scn_abi_version(void) { return SCN_ABI_VERSION; }
+
+long long scn_launch_count(void) { return scn::g_launches.load(std::memory_order_relaxed); }
 
 const char *scn_last_error(void) { return scn::g_last_error; }
 

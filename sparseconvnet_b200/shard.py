@@ -1,0 +1,54 @@
+"""Data-parallel inference: the minibatch shards by batch index, one process per GPU.
+
+Each rank keeps a contiguous range of samples, builds its own Metadata (site hash and
+rulebooks never cross ranks: no operator mixes rows of different samples, and inference-mode
+BatchNorm uses running statistics), and the per-row results are gathered at the end with one
+collective.  The reference has no multi-GPU path; this follows its per-sample structure
+(one hash map per sample, sparseconvnet/SCN/Metadata/Metadata.h:34)."""
+import torch
+import torch.distributed as dist
+
+
+def shard_range(n_samples, rank, world):
+    """Contiguous sample range [lo, hi) of `rank`: the first n % world ranks get one extra."""
+    base, extra = divmod(int(n_samples), int(world))
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def shard_batch(coords, features, rank, world, n_samples=None):
+    """Rows of this rank's samples, batch index renumbered from 0.  coords [n, D+1] (last
+    column = batch index) and features [n, C] are torch tensors or numpy arrays."""
+    b = coords[:, -1]
+    if n_samples is None:
+        n_samples = int(b.max()) + 1 if len(b) else 0
+    lo, hi = shard_range(n_samples, rank, world)
+    keep = (b >= lo) & (b < hi)
+    c = coords[keep].copy() if hasattr(coords, "copy") else coords[keep].clone()
+    c[:, -1] -= lo
+    return c, features[keep], (lo, hi)
+
+
+def gather_rows(rows, group=None):
+    """All ranks' row blocks concatenated in rank order (= batch order when every rank's rows
+    are in batch order).  Blocks may have different row counts: counts are exchanged first,
+    blocks padded to the largest, gathered with one all_gather, and trimmed.
+    Returns (gathered [sum n_r, C], counts list)."""
+    if not dist.is_available() or not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return rows, [rows.shape[0]]
+    world = dist.get_world_size(group)
+    n = torch.tensor([rows.shape[0]], dtype=torch.int64, device=rows.device)
+    counts = torch.empty(world, dtype=torch.int64, device=rows.device)
+    dist.all_gather_into_tensor(counts, n, group=group)
+    counts = counts.tolist()
+    width = rows.shape[1:]
+    biggest = max(counts)
+    padded = rows
+    if rows.shape[0] < biggest:
+        padded = rows.new_zeros((biggest,) + tuple(width))
+        padded[:rows.shape[0]] = rows
+    out = rows.new_empty((world * biggest,) + tuple(width))
+    dist.all_gather_into_tensor(out, padded.contiguous(), group=group)
+    if all(c == biggest for c in counts):
+        return out, counts
+    return torch.cat([out[r * biggest:r * biggest + counts[r]] for r in range(world)]), counts
