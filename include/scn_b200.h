@@ -60,8 +60,12 @@ enum scn_status {
 enum scn_precision {
   SCN_PRECISION_FP32 = 0, /* fp32 FMA, fp32 accumulate (matches the reference's float path)  */
   SCN_PRECISION_TF32 = 1, /* tcgen05 kind::tf32 tensor-core tiles, fp32 accumulate in TMEM   */
-  SCN_PRECISION_BF16 = 2  /* tcgen05 kind::f16 (bf16 operands), fp32 accumulate in TMEM      */
+  SCN_PRECISION_BF16 = 2, /* tcgen05 kind::f16 (bf16 operands), fp32 accumulate in TMEM      */
+  SCN_PRECISION_TF32X3 = 3 /* tcgen05 kind::tf32, three passes over the hi/lo split of both
+                             operands, fp32 accumulate in TMEM: fp32-class accuracy          */
 };
+/* The tensor-core modes need groups == 1, n_in_planes % 32 == 0, n_out_planes % 16 == 0 and
+ * n_out_planes <= 256; other shapes run the fp32 kernel whatever the precision says. */
 
 /* which rulebook of a metadata object an export call refers to */
 enum scn_rulebook_kind {
@@ -102,6 +106,11 @@ SCN_API int scn_md_input_layer(scn_metadata *md, const int64_t *spatial_size, co
  * scn_md_input_layer call.  in [n_in, n_planes] -> out [n_active, n_planes]. */
 SCN_API int scn_input_layer_forward(scn_metadata *md, const float *in_features, int64_t n_in,
                             float *out_features, int64_t n_out, int n_planes, void *stream);
+
+/* Kernels never trap: they raise a flag in device memory (a rulebook entry outside the feature
+ * matrix, an expired bounded wait ...).  This waits for `stream`, reads and clears the flags
+ * and returns the matching status.  No counterpart in the reference (which checks nothing). */
+SCN_API int scn_md_poll_errors(scn_metadata *md, void *stream);
 
 /* replaces Metadata<D>::getNActive / getBatchSize (Metadata.cpp:67-70,171-176) */
 SCN_API int scn_md_n_active(scn_metadata *md, const int64_t *spatial_size, int64_t *n_active);

@@ -17,22 +17,23 @@ import torch
 from . import _lib
 from ._lib import check, lib, sizes
 
-PRECISION_FP32, PRECISION_TF32, PRECISION_BF16 = 0, 1, 2
+PRECISION_FP32, PRECISION_TF32, PRECISION_BF16, PRECISION_TF32X3 = 0, 1, 2, 3
 _precision = PRECISION_FP32
 
 
 def set_precision(p):
-    """Arithmetic of the convolution kernels: 'fp32' (default, reference-exact class),
-    'tf32' or 'bf16' (tensor-core tiles with fp32 accumulation)."""
+    """Arithmetic of the convolution kernels: 'fp32' (default; fp32 FMA), 'tf32x3' (tensor-core
+    tiles over the hi/lo split of both operands: fp32-class accuracy), 'tf32' or 'bf16'
+    (single-pass tensor-core tiles, fp32 accumulation)."""
     global _precision
-    table = {"fp32": 0, "tf32": 1, "bf16": 2, 0: 0, 1: 1, 2: 2}
+    table = {"fp32": 0, "tf32": 1, "bf16": 2, "tf32x3": 3, 0: 0, 1: 1, 2: 2, 3: 3}
     if p not in table:
-        raise ValueError("precision must be 'fp32', 'tf32' or 'bf16'")
+        raise ValueError("precision must be 'fp32', 'tf32x3', 'tf32' or 'bf16'")
     _precision = table[p]
 
 
 def get_precision():
-    return ("fp32", "tf32", "bf16")[_precision]
+    return ("fp32", "tf32", "bf16", "tf32x3")[_precision]
 
 
 def _stream():
@@ -127,6 +128,12 @@ class _Metadata(object):
 
     def clear(self):
         check(lib.scn_md_clear(self._h, _stream()))
+
+    def poll_errors(self):
+        """Waits for the current stream and raises if a kernel flagged a problem."""
+        dev = self.device if self.device is not None else torch.device("cuda")
+        with torch.cuda.device(dev):
+            check(lib.scn_md_poll_errors(self._h, _stream()))
 
     def getNActive(self, spatial_size):
         n = C.c_int64()

@@ -55,6 +55,7 @@ enum DeviceFlag : int {
   FLAG_COORD_RANGE = 1,
   FLAG_TABLE_FULL = 2,
   FLAG_BAD_ROW = 4,
+  FLAG_TC_TIMEOUT = 8,
 };
 
 // ---- packed site key ----------------------------------------------------------------------

@@ -17,7 +17,7 @@ static int run_conv(scn_metadata *md, Rulebook &rb, bool transposed, const float
   SCN_REQUIRE(groups >= 1 && n_in_planes >= 1 && n_out_planes >= 1 && n_in_planes % groups == 0 &&
                   n_out_planes % groups == 0,
               SCN_ERR_BAD_ARG, "planes %d -> %d not divisible into %d groups", n_in_planes, n_out_planes, groups);
-  SCN_REQUIRE(precision >= SCN_PRECISION_FP32 && precision <= SCN_PRECISION_BF16, SCN_ERR_BAD_ARG,
+  SCN_REQUIRE(precision >= SCN_PRECISION_FP32 && precision <= SCN_PRECISION_TF32X3, SCN_ERR_BAD_ARG,
               "unknown precision %d", precision);
   SCN_REQUIRE(weight, SCN_ERR_BAD_ARG, "null weight");
   int cin = n_in_planes / groups, cout = n_out_planes / groups;

@@ -104,6 +104,10 @@ static int flags_to_status(int flags) {
     set_error("site hash probe limit reached");
     return SCN_ERR_TABLE_FULL;
   }
+  if (flags & FLAG_TC_TIMEOUT) {
+    set_error("a bounded wait inside the tensor-core convolution kernel expired");
+    return SCN_ERR_CUDA;
+  }
   if (flags & FLAG_BAD_ROW) {
     set_error("a rulebook entry points outside the feature matrix");
     return SCN_ERR_SIZE_MISMATCH;
@@ -813,6 +817,14 @@ int scn_md_input_layer(scn_metadata *md, const int64_t *spatial_size, const int6
                        int mode, void *stream, int64_t *n_active) {
   return md_input_layer(md, spatial_size, coords, coords_on_device, n_rows, n_cols, batch_size, mode,
                         (cudaStream_t)stream, n_active);
+}
+
+int scn_md_poll_errors(scn_metadata *md, void *stream) {
+  SCN_REQUIRE(md, SCN_ERR_BAD_ARG, "null metadata");
+  if (!md->flags_dev) return SCN_OK;
+  int flags = 0;
+  SCN_TRY(fetch_flags(md, (cudaStream_t)stream, &flags, nullptr));
+  return flags_to_status(flags);
 }
 
 int scn_md_n_active(scn_metadata *md, const int64_t *spatial_size, int64_t *n_active) {

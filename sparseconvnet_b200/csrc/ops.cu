@@ -252,12 +252,14 @@ int scn_max_pooling_forward(scn_metadata *md, const int64_t *input_size, const i
 int scn_sparse_to_dense_forward(scn_metadata *md, const int64_t *spatial_size, const float *in_features,
                                 float *out_dense, int n_planes, void *stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
-  SCN_REQUIRE(md && spatial_size && out_dense, SCN_ERR_BAD_ARG, "null argument");
+  SCN_REQUIRE(md && spatial_size, SCN_ERR_BAD_ARG, "null argument");
   Grid *g = find_grid(md, spatial_size);
   SCN_REQUIRE(g, SCN_ERR_NO_GRID, "no grid for that spatial size");
   long long volume = 1;
   for (int d = 0; d < md->dim; ++d) volume *= spatial_size[d];
   size_t bytes = sizeof(float) * (size_t)g->batch_size * n_planes * volume;
+  if (bytes == 0) return SCN_OK;
+  SCN_REQUIRE(out_dense, SCN_ERR_BAD_ARG, "null output");
   SCN_CUDA_CHECK(cudaMemsetAsync(out_dense, 0, bytes, stream));
   if (g->n_active == 0) return SCN_OK;
   SCN_REQUIRE(in_features, SCN_ERR_BAD_ARG, "null features");

@@ -1,0 +1,94 @@
+"""The tcgen05 / TMEM convolution path against the fp32 kernel (itself checked against the
+reference in test_gpu_parity.py) and against the numpy restatement.
+
+Tolerances (relative to the largest output magnitude): 1e-2 for single-pass tf32 and bf16
+tensor-core arithmetic, 1e-4 -- the fp32 bar -- for the three-pass tf32 split."""
+import numpy as np
+import pytest
+import torch
+
+from tests import helpers
+
+pytestmark = pytest.mark.gpu
+
+MODES = [("tf32", helpers.TC_TOL), ("bf16", helpers.TC_TOL), ("tf32x3", helpers.FP32_TOL)]
+
+
+def _surface(n, size, batch, seed):
+    rng = np.random.default_rng(seed)
+    pts = rng.integers(0, size, (n, 2))
+    z = (size / 2 + size / 5 * np.sin(pts[:, 0] / 6.0) + size / 8 * np.cos(pts[:, 1] / 4.0)).astype(np.int64)
+    return np.concatenate([pts, z[:, None], rng.integers(0, batch, (n, 1))], axis=1)
+
+
+@pytest.fixture
+def restore_precision():
+    import sparseconvnet_b200 as scn
+    yield
+    scn.set_precision("fp32")
+
+
+@pytest.mark.parametrize("mode,tol", MODES)
+@pytest.mark.parametrize("cin,cout", [(32, 32), (64, 64), (32, 16), (96, 160), (224, 224), (256, 128)])
+def test_submanifold_conv_tensor_core(mode, tol, cin, cout, cuda, restore_precision):
+    import sparseconvnet_b200 as scn
+    coords = _surface(5000, 40, 2, 1)
+    rng = np.random.default_rng(2)
+    torch.manual_seed(cin * 1000 + cout)
+    inp = scn.InputLayer(3, 40, mode=3)
+    sc = scn.SubmanifoldConvolution(3, cin, cout, 3, True).to(cuda)
+    sc.bias.data.normal_()
+    feats = torch.from_numpy(rng.standard_normal((coords.shape[0], cin)).astype(np.float32)).to(cuda)
+    with torch.no_grad():
+        x = inp([torch.from_numpy(coords), feats])
+        scn.set_precision("fp32")
+        want = sc(x).features
+        scn.set_precision(mode)
+        got = sc(x).features
+        x.metadata.poll_errors()
+    err = helpers.rel_err(got.cpu().numpy(), want.cpu().numpy())
+    assert err <= tol, "%s %d->%d: relative error %.3g" % (mode, cin, cout, err)
+    assert err > 0 or mode == "tf32x3", "tensor-core result identical to fp32: the path did not run"
+
+
+@pytest.mark.parametrize("mode,tol", MODES)
+def test_strided_and_transposed_tensor_core(mode, tol, cuda, restore_precision):
+    import sparseconvnet_b200 as scn
+    coords = _surface(6000, 48, 3, 3)
+    rng = np.random.default_rng(4)
+    torch.manual_seed(7)
+    inp = scn.InputLayer(3, 48, mode=4)
+    down = scn.Convolution(3, 32, 64, 2, 2, False).to(cuda)
+    up = scn.Deconvolution(3, 64, 32, 2, 2, False).to(cuda)
+    down3 = scn.Convolution(3, 32, 48, 3, 2, False).to(cuda)
+    feats = torch.from_numpy(rng.standard_normal((coords.shape[0], 32)).astype(np.float32)).to(cuda)
+    outs = {}
+    with torch.no_grad():
+        for m in ("fp32", mode):
+            scn.set_precision(m)
+            x = inp([torch.from_numpy(coords), feats])
+            y = down(x)
+            z = up(y)
+            x47 = scn.InputLayer(3, 47, mode=4)([torch.from_numpy(np.minimum(coords, [46, 46, 46, 9])), feats])
+            w = down3(x47)
+            x.metadata.poll_errors()
+            x47.metadata.poll_errors()
+            outs[m] = [t.features.cpu().numpy() for t in (y, z, w)]
+    for a, b, name in zip(outs[mode], outs["fp32"], ("conv 2/2", "deconv 2/2", "conv 3/2")):
+        err = helpers.rel_err(a, b)
+        assert err <= tol, "%s %s: relative error %.3g" % (mode, name, err)
+
+
+@pytest.mark.parametrize("mode,tol", MODES)
+def test_unet_tensor_core_against_golden(mode, tol, cuda, restore_precision):
+    """Whole small U-Net (planes 8..32: only the 32-plane layers take the tensor path, the
+    rest fall back to the fp32 kernel) against the reference's stored output."""
+    import sparseconvnet_b200 as scn
+    from tests.golden import cases
+    g = helpers.load_golden("net_unet3d")
+    inp, net, head = cases.net_modules("net_unet3d")
+    helpers.load_state(net, g, "state")
+    gpu = helpers.GpuBackend()
+    scn.set_precision(mode)
+    y = gpu.run(net, gpu.run(inp, [g["coords"], g["feats"]]))
+    helpers.assert_features_match(gpu.locations(y), y.features, g["loc/y"], g["feat/y"], tol, what=mode)
