@@ -13,7 +13,9 @@
 //        bulk-copy (cp.async.bulk, completion on an mbarrier) brings the whole slab;
 //   D += A * B  issued by one elected thread: Cin-slice/8 (tf32) or /16 (bf16) tcgen05.mma
 //        instructions of shape 128 x Cout x 8|16, completion tracked with tcgen05.commit.
-// Gather of step s+1 overlaps the MMAs of step s (multi-stage ring of shared-memory buffers).
+// The gather runs up to three steps ahead of the tensor core through a ring of shared-memory
+// stages; producer warps and the MMA-issuing warp meet only on mbarriers (no block-wide sync in
+// the main loop).
 //
 // Arithmetic modes:
 //   TF32    one pass, operands truncated to tf32 by the tensor core            (1e-2 class)
@@ -26,6 +28,8 @@
 // issuing work, drains its own copies, frees its tensor memory and returns.
 #include <cuda_bf16.h>
 
+#include <stdlib.h>
+
 #include <algorithm>
 
 #include "metadata.cuh"
@@ -35,7 +39,7 @@ namespace scn {
 enum TcMode : int { TC_TF32 = 0, TC_BF16 = 1, TC_TF32X3 = 2 };
 
 constexpr int kTcRows = 128;     // M of the MMA tile = TMEM lanes
-constexpr int kTcThreads = 256;
+constexpr int kTcThreads = 160;  // 4 producer/epilogue warps + 1 MMA warp
 constexpr int kTcMaxOffsets = 128;
 constexpr unsigned kWaitLimit = 1u << 20;
 
@@ -189,12 +193,35 @@ struct TcParams {
   int K, cin, cout;
   int kc;          // input planes per step (32 or 16)
   int n_stages;
+  int lookahead;   // steps the gather runs ahead of the tensor core (< n_stages)
   int tmem_cols;   // power of two >= cout, >= 32
   int *flags;
 };
 
+__device__ __forceinline__ void mbar_arrive(unsigned long long *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_dyn(int n) {
+  switch (n) {
+    case 0: cp_async_wait<0>(); break;
+    case 1: cp_async_wait<1>(); break;
+    case 2: cp_async_wait<2>(); break;
+    default: cp_async_wait<3>(); break;
+  }
+}
+
+// Warp roles.  Warps 0-3 (128 threads, one per tile row in the epilogue) are the gather
+// producers; warp 4 owns tensor memory, streams the weight slabs and issues the MMAs.  The
+// roles meet only on mbarriers:
+//   full_a[s]  128 producer arrivals: the rows of stage s are in shared memory (and fenced for
+//              the async proxy)
+//   full_w[s]  transaction barrier of the weight slab's bulk copy
+//   empty[s]   tcgen05.commit: the MMAs that read stage s have finished
+//   acc_full   tcgen05.commit after the last MMA of the tile
+constexpr int kProducerThreads = 128;
+
 template <int MODE>
-__global__ void __launch_bounds__(kTcThreads, 1) k_conv_tc(TcParams P) {
+__global__ void __launch_bounds__(kTcThreads) k_conv_tc(TcParams P) {
   constexpr bool kBf16 = (MODE == TC_BF16);
   constexpr bool kSplit = (MODE == TC_TF32X3);
   constexpr int kEsize = kBf16 ? 2 : 4;
@@ -204,7 +231,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_conv_tc(TcParams P) {
   extern __shared__ __align__(128) unsigned char smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const long long row0 = (long long)blockIdx.x * kTcRows;
-  const int K = P.K, kc = P.kc, NS = P.n_stages;
+  const int K = P.K, kc = P.kc, NS = P.n_stages, L = P.lookahead;
   const int n_slices = P.cin / kc;
   const int pieces_per_row = kc / kPerPiece;
   const unsigned a_bytes = kTcRows * kc * kEsize;
@@ -216,26 +243,28 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_conv_tc(TcParams P) {
   unsigned char *stage_base = smem;
   int *sh_idx = reinterpret_cast<int *>(smem + (size_t)NS * stage_bytes);
   unsigned long long *bars = reinterpret_cast<unsigned long long *>(sh_idx + (size_t)K * kTcRows);
-  unsigned long long *w_full = bars;          // [NS]
-  unsigned long long *mma_done = bars + NS;   // [NS]
-  unsigned long long *acc_full = bars + 2 * NS;
-  int *sh_steps = reinterpret_cast<int *>(bars + 2 * NS + 1);  // [K] offsets with at least one rule
+  unsigned long long *full_a = bars;            // [NS]
+  unsigned long long *full_w = bars + NS;       // [NS]
+  unsigned long long *empty = bars + 2 * NS;    // [NS]
+  unsigned long long *acc_full = bars + 3 * NS;
+  int *sh_steps = reinterpret_cast<int *>(bars + 3 * NS + 1);  // [K] offsets with at least one rule
   int *sh_has = sh_steps + kTcMaxOffsets;                       // [K]
   unsigned *sh_tmem = reinterpret_cast<unsigned *>(sh_has + kTcMaxOffsets);
   int *sh_nk = reinterpret_cast<int *>(sh_tmem + 1);
-  int *sh_abort = sh_nk + 1;
+  volatile int *sh_abort = sh_nk + 1;
 
   // ---- prologue: barriers, tensor memory, rulebook columns of this tile ----------------------
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
-      mbar_init(&w_full[s], 1);
-      mbar_init(&mma_done[s], 1);
+      mbar_init(&full_a[s], kProducerThreads);
+      mbar_init(&full_w[s], 1);
+      mbar_init(&empty[s], 1);
     }
     mbar_init(acc_full, 1);
     *sh_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 0) tmem_alloc(sh_tmem, (unsigned)P.tmem_cols);
+  if (warp == 4) tmem_alloc(sh_tmem, (unsigned)P.tmem_cols);
   for (int k = warp; k < K; k += kTcThreads / 32) {
     bool any = false;
 #pragma unroll
@@ -264,133 +293,106 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_conv_tc(TcParams P) {
   }
   __syncthreads();
   const unsigned tmem_base = *sh_tmem;
-  const int n_active_k = *sh_nk;
-  const int S = n_active_k * n_slices;
-  const unsigned idesc = instr_desc(kBf16, P.cout);
-  bool ok = true;
+  const int S = *sh_nk * n_slices;
 
-  // stage s gets step `step`: W slab by bulk copy (one thread), A rows by cp.async (all threads)
-  auto produce = [&](int step) {
-    const int st = step % NS, use = step / NS;
-    const int k = sh_steps[step / n_slices], slice = step % n_slices;
-    unsigned char *sa = stage_base + (size_t)st * stage_bytes;
-    if (use > 0 && ok) ok = mbar_wait(&mma_done[st], (unsigned)((use - 1) & 1));
-    if (!ok) return;
-    if (tid == 0) {
-      unsigned char *sw = sa + (kSplit ? 2 * a_bytes : a_bytes);
-      const unsigned total_w = w_bytes * (kSplit ? 2 : 1);
-      mbar_expect_tx(&w_full[st], total_w);
-      bulk_copy_g2s(smem_u32(sw), P.wprep + ((size_t)k * n_slices + slice) * total_w, total_w, &w_full[st]);
-    }
-    const int *idx = sh_idx + k * kTcRows;
-    const int total_pieces = kTcRows * pieces_per_row;
-    if (!kBf16) {
-      for (int p = tid; p < total_pieces; p += kTcThreads) {
-        int r = (p & 7) + 8 * (p / (8 * pieces_per_row));
-        int j = (p >> 3) % pieces_per_row;
-        int src_row = idx[r];
-        const float *src = P.in + (long long)(src_row < 0 ? 0 : src_row) * P.ld_in + slice * kc + j * 4;
-        unsigned dst = smem_u32(sa) + (r >> 3) * sbo + j * 128 + (r & 7) * 16;
-        cp_async16(dst, src, src_row < 0 ? 0u : 16u);
-      }
-    } else {
-      // bf16: 8 input floats -> one 16-byte piece of 8 bf16, converted in registers
-      for (int p = tid; p < total_pieces; p += kTcThreads) {
-        int r = (p & 7) + 8 * (p / (8 * pieces_per_row));
-        int j = (p >> 3) % pieces_per_row;
-        int src_row = idx[r];
-        uint4 packed = make_uint4(0, 0, 0, 0);
-        if (src_row >= 0) {
-          const float4 *src =
-              reinterpret_cast<const float4 *>(P.in + (long long)src_row * P.ld_in + slice * kc + j * 8);
-          float4 x = __ldg(src), y = __ldg(src + 1);
-          __nv_bfloat162 b0 = __floats2bfloat162_rn(x.x, x.y), b1 = __floats2bfloat162_rn(x.z, x.w);
-          __nv_bfloat162 b2 = __floats2bfloat162_rn(y.x, y.y), b3 = __floats2bfloat162_rn(y.z, y.w);
-          packed.x = *reinterpret_cast<unsigned *>(&b0);
-          packed.y = *reinterpret_cast<unsigned *>(&b1);
-          packed.z = *reinterpret_cast<unsigned *>(&b2);
-          packed.w = *reinterpret_cast<unsigned *>(&b3);
+  if (warp < 4) {
+    // =================================== gather producers =====================================
+    // Piece p = tid + 128 i of a stage is the 16-byte piece j of tile row r with
+    //   r = (p & 7) + 8 * (p / (8 * pieces_per_row)),  j = (p >> 3) % pieces_per_row,
+    // so a quarter warp fills one 128-byte core matrix and a warp reads 64 contiguous bytes of
+    // 8 rows.  pieces_per_row is a power of two (2, 4 or 8): j is fixed per thread and the rows
+    // step by 16 * 8 / pieces_per_row.
+    const int lg = 31 - __clz(pieces_per_row);
+    const int j = (tid >> 3) & (pieces_per_row - 1);
+    const int r_base = (tid & 7) + 8 * (tid >> (3 + lg));
+    const int r_step = 8 * (16 >> lg);
+    const unsigned off_base = (unsigned)(r_base >> 3) * sbo + j * 128 + (r_base & 7) * 16;
+    const unsigned off_step = (unsigned)(r_step >> 3) * sbo;
+    const int n_mine = pieces_per_row;  // pieces of this thread per stage
+    for (int s = 0; s < S + L; ++s) {
+      if (*sh_abort) break;
+      if (s < S) {
+        const int st = s % NS, use = s / NS;
+        if (use > 0 && !mbar_wait(&empty[st], (unsigned)((use - 1) & 1))) {
+          *sh_abort = 1;
+          break;
         }
-        *reinterpret_cast<uint4 *>(sa + (r >> 3) * sbo + j * 128 + (r & 7) * 16) = packed;
-      }
-    }
-  };
-
-  if (S > 0) produce(0);
-  cp_async_commit();
-
-  for (int step = 0; step < S; ++step) {
-    if (step + 1 < S) produce(step + 1);
-    cp_async_commit();
-    cp_async_wait<1>();  // everything but the newest group has landed: this step's rows
-    const int st = step % NS;
-    unsigned char *sa = stage_base + (size_t)st * stage_bytes;
-    if (kSplit) {
-      // low parts of the pieces this thread copied: a_lo = a - trunc_tf32(a)
-      const int total_pieces = kTcRows * pieces_per_row;
-      for (int p = tid; p < total_pieces; p += kTcThreads) {
-        int r = (p & 7) + 8 * (p / (8 * pieces_per_row));
-        int j = (p >> 3) % pieces_per_row;
-        unsigned off = (r >> 3) * sbo + j * 128 + (r & 7) * 16;
-        float4 a = *reinterpret_cast<const float4 *>(sa + off);
-        float4 lo;
-        lo.x = a.x - __uint_as_float(__float_as_uint(a.x) & 0xFFFFE000u);
-        lo.y = a.y - __uint_as_float(__float_as_uint(a.y) & 0xFFFFE000u);
-        lo.z = a.z - __uint_as_float(__float_as_uint(a.z) & 0xFFFFE000u);
-        lo.w = a.w - __uint_as_float(__float_as_uint(a.w) & 0xFFFFE000u);
-        *reinterpret_cast<float4 *>(sa + a_bytes + off) = lo;
-      }
-    }
-    fence_proxy_async_smem();  // make this thread's shared-memory writes visible to the tensor core
-    if (!ok) atomicExch(sh_abort, 1);
-    __syncthreads();
-    if (*sh_abort) break;
-    if (tid == 0) {
-      if (mbar_wait(&w_full[st], (unsigned)((step / NS) & 1))) {
-        tc_fence_after();
-        const unsigned a_addr = smem_u32(sa);
-        const unsigned w_addr = a_addr + (kSplit ? 2 * a_bytes : a_bytes);
-        const int n_mma = kc / kMmaK;
-        for (int j = 0; j < n_mma; ++j) {
-          unsigned long long da = smem_desc(a_addr + j * 256, 128, sbo);
-          unsigned long long db = smem_desc(w_addr + j * 256, 128, sbo);
-          tc_mma<kBf16>(tmem_base, da, db, idesc, (step > 0 || j > 0) ? 1u : 0u);
-          if (kSplit) {
-            unsigned long long da_lo = smem_desc(a_addr + a_bytes + j * 256, 128, sbo);
-            unsigned long long db_lo = smem_desc(w_addr + w_bytes + j * 256, 128, sbo);
-            tc_mma<kBf16>(tmem_base, da_lo, db, idesc, 1u);
-            tc_mma<kBf16>(tmem_base, da, db_lo, idesc, 1u);
+        const int k = sh_steps[s / n_slices], slice = s % n_slices;
+        unsigned char *sa = stage_base + (size_t)st * stage_bytes;
+        const unsigned sa_u32 = smem_u32(sa);
+        const int *idx = sh_idx + k * kTcRows + r_base;
+        const float *col = P.in + slice * kc + j * kPerPiece;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          if (i < n_mine) {
+            const int src_row = idx[i * r_step];
+            const unsigned off = off_base + i * off_step;
+            if (!kBf16) {
+              cp_async16(sa_u32 + off, col + (long long)(src_row < 0 ? 0 : src_row) * P.ld_in, src_row < 0 ? 0u : 16u);
+            } else {
+              // bf16: 8 input floats -> one 16-byte piece of 8 bf16, converted in registers
+              uint4 packed = make_uint4(0, 0, 0, 0);
+              if (src_row >= 0) {
+                const float4 *src = reinterpret_cast<const float4 *>(col + (long long)src_row * P.ld_in);
+                float4 x = __ldg(src), y = __ldg(src + 1);
+                __nv_bfloat162 b0 = __floats2bfloat162_rn(x.x, x.y), b1 = __floats2bfloat162_rn(x.z, x.w);
+                __nv_bfloat162 b2 = __floats2bfloat162_rn(y.x, y.y), b3 = __floats2bfloat162_rn(y.z, y.w);
+                packed.x = *reinterpret_cast<unsigned *>(&b0);
+                packed.y = *reinterpret_cast<unsigned *>(&b1);
+                packed.z = *reinterpret_cast<unsigned *>(&b2);
+                packed.w = *reinterpret_cast<unsigned *>(&b3);
+              }
+              *reinterpret_cast<uint4 *>(sa + off) = packed;
+            }
           }
         }
-        tc_commit(&mma_done[st]);
-        if (step == S - 1) tc_commit(acc_full);
-      } else {
-        atomicExch(sh_abort, 1);
+      }
+      cp_async_commit();
+      if (s >= L) {
+        const int c = s - L;  // the step whose rows have landed once only L groups are pending
+        cp_async_wait_dyn(L);
+        unsigned char *sa = stage_base + (size_t)(c % NS) * stage_bytes;
+        if (kSplit) {
+          // low parts of the pieces this thread copied: a_lo = a - trunc_tf32(a)
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            if (i < n_mine) {
+              const unsigned off = off_base + i * off_step;
+              float4 a = *reinterpret_cast<const float4 *>(sa + off);
+              float4 lo;
+              lo.x = a.x - __uint_as_float(__float_as_uint(a.x) & 0xFFFFE000u);
+              lo.y = a.y - __uint_as_float(__float_as_uint(a.y) & 0xFFFFE000u);
+              lo.z = a.z - __uint_as_float(__float_as_uint(a.z) & 0xFFFFE000u);
+              lo.w = a.w - __uint_as_float(__float_as_uint(a.w) & 0xFFFFE000u);
+              *reinterpret_cast<float4 *>(sa + a_bytes + off) = lo;
+            }
+          }
+        }
+        fence_proxy_async_smem();  // this thread's shared-memory writes -> visible to the tensor core
+        mbar_arrive(&full_a[c % NS]);
       }
     }
-  }
-  cp_async_wait<0>();
+    cp_async_wait<0>();
 
-  // ---- epilogue: TMEM -> registers -> (+bias) -> HBM, each row once ---------------------------
-  bool have_acc = false;
-  if (S > 0 && !*sh_abort) {
-    have_acc = mbar_wait(acc_full, 0);
-    if (!have_acc) atomicExch(sh_abort, 1);
-  }
-  have_acc = __all_sync(0xffffffffu, have_acc);  // tcgen05.ld below is warp-collective
-  tc_fence_after();
-  {
-    const int q = warp & 3, half = warp >> 2;
-    const long long row = row0 + q * 32 + lane;
-    for (int c0 = half * 16; c0 < P.cout; c0 += 32) {
+    // ================================ epilogue (same 4 warps) ==================================
+    bool have_acc = false;
+    if (S > 0 && !*sh_abort) {
+      have_acc = mbar_wait(acc_full, 0);
+      if (!have_acc) *sh_abort = 1;
+    }
+    have_acc = __all_sync(0xffffffffu, have_acc);  // tcgen05.ld below is warp-collective
+    tc_fence_after();
+    const long long row = row0 + warp * 32 + lane;
+    const bool store = row < P.n_out && (S == 0 || have_acc);
+    for (int c0 = 0; c0 < P.cout; c0 += 16) {
       float v[16];
       if (have_acc) {
-        tmem_ld16(tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)c0, v);
+        tmem_ld16(tmem_base + ((unsigned)(warp * 32) << 16) + (unsigned)c0, v);
       } else {
 #pragma unroll
         for (int i = 0; i < 16; ++i) v[i] = 0.f;
       }
-      if (row < P.n_out && !(S > 0 && !have_acc)) {
+      if (store) {
         float *dst = P.out + row * P.ld_out + c0;
 #pragma unroll
         for (int i = 0; i < 16; i += 4) {
@@ -403,11 +405,57 @@ __global__ void __launch_bounds__(kTcThreads, 1) k_conv_tc(TcParams P) {
         }
       }
     }
+  } else if (warp == 4 && lane == 0) {
+    // ============================ weight slabs + MMA issue (one thread) =======================
+    const unsigned idesc = instr_desc(kBf16, P.cout);
+    const unsigned total_w = w_bytes * (kSplit ? 2 : 1);
+    bool ok = true;
+    auto load_w = [&](int s) {
+      const int st = s % NS, use = s / NS;
+      if (use > 0 && !mbar_wait(&empty[st], (unsigned)((use - 1) & 1))) {
+        ok = false;
+        return;
+      }
+      const int k = sh_steps[s / n_slices], slice = s % n_slices;
+      unsigned char *sw = stage_base + (size_t)st * stage_bytes + (kSplit ? 2 * a_bytes : a_bytes);
+      mbar_expect_tx(&full_w[st], total_w);
+      bulk_copy_g2s(smem_u32(sw), P.wprep + ((size_t)k * n_slices + slice) * total_w, total_w, &full_w[st]);
+    };
+    const int Lw = L > 0 ? L : 1;  // the weight slabs always run at least one step ahead
+    for (int s = 0; s < Lw && s < S && ok; ++s) load_w(s);
+    for (int step = 0; step < S && ok; ++step) {
+      if (*sh_abort) break;
+      if (step + Lw < S) load_w(step + Lw);
+      const int st = step % NS;
+      const unsigned ph = (unsigned)((step / NS) & 1);
+      if (!ok || !mbar_wait(&full_w[st], ph) || !mbar_wait(&full_a[st], ph)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const unsigned a_addr = smem_u32(stage_base + (size_t)st * stage_bytes);
+      const unsigned w_addr = a_addr + (kSplit ? 2 * a_bytes : a_bytes);
+      const int n_mma = kc / kMmaK;
+      for (int j = 0; j < n_mma; ++j) {
+        unsigned long long da = smem_desc(a_addr + j * 256, 128, sbo);
+        unsigned long long db = smem_desc(w_addr + j * 256, 128, sbo);
+        tc_mma<kBf16>(tmem_base, da, db, idesc, (step > 0 || j > 0) ? 1u : 0u);
+        if (kSplit) {
+          unsigned long long da_lo = smem_desc(a_addr + a_bytes + j * 256, 128, sbo);
+          unsigned long long db_lo = smem_desc(w_addr + w_bytes + j * 256, 128, sbo);
+          tc_mma<kBf16>(tmem_base, da_lo, db, idesc, 1u);
+          tc_mma<kBf16>(tmem_base, da, db_lo, idesc, 1u);
+        }
+      }
+      tc_commit(&empty[st]);
+      if (step == S - 1) tc_commit(acc_full);
+    }
+    if (!ok) *sh_abort = 1;
   }
-  if (*sh_abort && tid == 0) atomicOr(P.flags, FLAG_TC_TIMEOUT);
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem_base, (unsigned)P.tmem_cols);
+  if (*sh_abort && tid == 0) atomicOr(P.flags, FLAG_TC_TIMEOUT);
+  if (warp == 4) tmem_dealloc(tmem_base, (unsigned)P.tmem_cols);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -428,25 +476,45 @@ bool conv_tc_supported(int cin, int cout, int groups, int precision) {
 }
 
 struct TcPlan {
-  int kc, stages;
+  int kc, stages, lookahead;
   size_t smem;
 };
 
+static int env_int(const char *name, int dflt) {
+  const char *v = getenv(name);
+  return v ? atoi(v) : dflt;
+}
+
+// Picks the slice width, ring depth and lookahead.  Two CTAs per SM are preferred (one tile's
+// prologue and epilogue then overlap the other's main loop) as long as the ring keeps at least
+// three stages; otherwise one CTA with a deeper ring.  SCN_TC_STAGES / SCN_TC_KC /
+// SCN_TC_LOOKAHEAD override the choice (tuning knobs).
 static bool plan(int mode, int K, int cin, int cout, TcPlan &pl) {
-  const size_t budget = 200 * 1024;
   const int esize = mode == TC_BF16 ? 2 : 4;
   const size_t control = (size_t)K * kTcRows * 4 + 16 * 8 + 2 * kTcMaxOffsets * 4 + 64;
+  const size_t one_cta = 200 * 1024, two_ctas = 110 * 1024;
+  int force_kc = env_int("SCN_TC_KC", 0), force_ns = env_int("SCN_TC_STAGES", 0);
   for (int kc : {32, 16}) {
     if (cin % kc) continue;
+    if (force_kc && kc != force_kc) continue;
     if (mode == TC_BF16 && kc == 16) continue;
     size_t stage = ((size_t)kTcRows * kc * esize + (size_t)cout * kc * esize) * (mode == TC_TF32X3 ? 2 : 1);
-    int stages = (int)std::min<size_t>(4, (budget - control) / stage);
-    if (stages >= 3 || (kc == 16 && stages >= 2) || (mode == TC_BF16 && stages >= 2)) {
-      pl.kc = kc;
-      pl.stages = stages;
-      pl.smem = (size_t)stages * stage + control;
-      return true;
-    }
+    if (control + 2 * stage > one_cta) continue;
+    int stages = (int)std::min<size_t>(4, (two_ctas - std::min(control, two_ctas)) / stage);
+    if (stages < 3) stages = (int)std::min<size_t>(4, (one_cta - control) / stage);
+    if (force_ns) stages = force_ns;
+    if (stages < 2 || control + (size_t)stages * stage > 220 * 1024) continue;
+    if (stages < 3 && kc == 32 && cin % 16 == 0 && mode != TC_BF16 && !force_kc && !force_ns) continue;
+    pl.kc = kc;
+    pl.stages = stages;
+    // bf16 converts in registers with blocking loads, so running ahead buys nothing there
+    // The gather may run `lookahead` steps ahead; a stage is refilled only after its MMAs have
+    // finished, so the ring needs lookahead + 2 stages to keep the producers from waiting on the
+    // tensor core's round trip every step.  bf16 converts in registers with blocking loads, so
+    // running ahead buys nothing there.
+    pl.lookahead = mode == TC_BF16 ? 0 : std::max(1, std::min(env_int("SCN_TC_LOOKAHEAD", stages - 2), stages - 1));
+    pl.smem = (size_t)stages * stage + control;
+    return true;
   }
   return false;
 }
@@ -484,6 +552,7 @@ int conv_forward_tc(const float *in, long long n_in, float *out, long long n_out
   P.cout = cout;
   P.kc = pl.kc;
   P.n_stages = pl.stages;
+  P.lookahead = pl.lookahead;
   P.tmem_cols = (int)std::max<unsigned long long>(32, next_pow2((unsigned long long)cout));
   P.flags = flags;
   unsigned grid = (unsigned)ceil_div(n_out, kTcRows);
