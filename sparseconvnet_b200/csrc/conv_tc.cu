@@ -1,27 +1,35 @@
 // Tensor-core sparse convolution for sm_100a: tcgen05.mma with the accumulator in TMEM.
 //
-// Output stationary, like the fp32 kernel: a CTA owns 128 consecutive output rows for the whole
-// filter, so the accumulator tile D[128 x Cout] (fp32) lives in tensor memory from the first
-// filter offset to the last and every output row is written to HBM exactly once.  For every
-// filter offset k for which the tile has at least one rule, and every 32-plane slice of the
-// input planes:
-//   A  = the 128 input rows named by the dense rulebook column (offset k, rows of the tile),
+// Output stationary, like the fp32 kernel: a CTA owns 256 consecutive output rows for the whole
+// filter, so their accumulators live in tensor memory from the first filter offset to the last
+// and every output row is written to HBM exactly once.
+//
+// Orientation.  A tcgen05.mma instruction costs about the same ~150 cycles whatever its N
+// (measured: 152 cycles per instruction for N = 32 ... 256, tf32 and bf16 alike), so the wide
+// dimension has to be N.  Channel counts are small (32 ... 224) while rows are plentiful, hence
+// the product is computed transposed:
+//     D^T[Cout x 256 rows] += W[k]^T[Cout x Cin-slice] * G^T[Cin-slice x 256 rows]
+// i.e. the MMA's A operand (M = 128 TMEM lanes) is the weight slab, its B operand (N = 256) the
+// gathered input rows.  TMEM lane = output plane, TMEM column = row of the tile.
+//
+// For every filter offset k for which the tile has at least one rule, and every slice of 32
+// (or 16) input planes:
+//   G  = the 256 input rows named by the dense rulebook column (offset k, rows of the tile),
 //        gathered with 16-byte cp.async copies straight into the tensor core's K-major
 //        core-matrix layout in shared memory; a row without a rule is zero-filled by the copy
 //        itself (src-size 0), so it contributes nothing;
-//   B  = W[k][slice][:] -- prepared once per call in exactly that shared-memory image, so one
-//        bulk-copy (cp.async.bulk, completion on an mbarrier) brings the whole slab;
-//   D += A * B  issued by one elected thread: Cin-slice/8 (tf32) or /16 (bf16) tcgen05.mma
-//        instructions of shape 128 x Cout x 8|16, completion tracked with tcgen05.commit.
-// The gather runs up to three steps ahead of the tensor core through a ring of shared-memory
-// stages; producer warps and the MMA-issuing warp meet only on mbarriers (no block-wide sync in
-// the main loop).
+//   W  = W[k][slice][:] -- prepared once per call in exactly its shared-memory image, so one
+//        bulk copy (cp.async.bulk, completion on an mbarrier) brings the whole slab;
+//   one elected thread issues slice/8 (tf32) or slice/16 (bf16) tcgen05.mma instructions of
+//   shape 128 x 256 x 8|16 per 128 output planes; completion is tracked with tcgen05.commit.
+// The gather runs ahead of the tensor core through a ring of shared-memory stages; producer
+// warps and the MMA-issuing warp meet only on mbarriers (no block-wide sync in the main loop).
 //
 // Arithmetic modes:
 //   TF32    one pass, operands truncated to tf32 by the tensor core            (1e-2 class)
 //   BF16    operands rounded to bf16 while staging, fp32 accumulate            (1e-2 class)
-//   TF32X3  split a = a_hi + a_lo (both tf32-representable): D += A_hi*B_hi + A_lo*B_hi +
-//           A_hi*B_lo, fp32 accumulate -- recovers fp32-class accuracy (error ~2^-21 per
+//   TF32X3  split a = a_hi + a_lo (both tf32-representable): D += W_hi*G_hi + W_hi*G_lo +
+//           W_lo*G_hi, fp32 accumulate -- recovers fp32-class accuracy (error ~2^-21 per
 //           product) on the tensor pipe, for the reference's fp32 parity bar.
 //
 // Every wait on an mbarrier is bounded; on expiry the kernel raises FLAG_TC_TIMEOUT, stops
@@ -38,8 +46,11 @@ namespace scn {
 
 enum TcMode : int { TC_TF32 = 0, TC_BF16 = 1, TC_TF32X3 = 2 };
 
-constexpr int kTcRows = 128;     // M of the MMA tile = TMEM lanes
-constexpr int kTcThreads = 160;  // 4 producer/epilogue warps + 1 MMA warp
+constexpr int kTcRows = 256;     // output rows per CTA = N of the MMA = TMEM columns per plane tile
+constexpr int kTcPlanes = 128;   // output planes per MMA = M = TMEM lanes
+constexpr int kTcThreads = 288;  // 8 producer/epilogue warps + 1 MMA warp
+constexpr int kProducerThreads = 256;
+constexpr int kMmaWarp = kProducerThreads / 32;
 constexpr int kTcMaxOffsets = 128;
 constexpr unsigned kWaitLimit = 1u << 20;
 
@@ -140,16 +151,16 @@ __device__ __forceinline__ unsigned long long smem_desc(unsigned addr, unsigned 
   d |= 1ull << 46;
   return d;
 }
-// Instruction descriptor: D fp32, A/B both tf32 or both bf16, both K-major, M = 128, N = n.
-__host__ __device__ inline unsigned instr_desc(bool bf16, int n) {
+// Instruction descriptor: D fp32, A/B both tf32 or both bf16, both K-major, M = 128, N = 256.
+__host__ __device__ inline unsigned instr_desc(bool bf16) {
   unsigned fmt = bf16 ? 1u : 2u;
-  return (1u << 4) | (fmt << 7) | (fmt << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(kTcRows >> 4) << 24);
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | ((unsigned)(kTcRows >> 3) << 17) | ((unsigned)(kTcPlanes >> 4) << 24);
 }
 
 // ---------------------------------------------------------------------------------------------
 // weight preparation: W [K][Cin][Cout] fp32 -> per (offset, slice) the shared-memory image of the
-// B operand (N = Cout rows, K-major core matrices), high part and -- for TF32X3 -- low part.
-// image(k, c) at ((k * n_slices + c) * parts + part) * cout * kc * esize bytes.
+// weight operand (Cout rows, K-major core matrices over the slice's input planes), high part
+// and -- for TF32X3 -- low part.  image(k, c) at ((k * n_slices + c) * parts + part) * tile bytes.
 // ---------------------------------------------------------------------------------------------
 __global__ void k_prepare_weights(const float *__restrict__ w, unsigned char *__restrict__ out, int K, int cin,
                                   int cout, int kc, int mode) {
@@ -193,8 +204,8 @@ struct TcParams {
   int K, cin, cout;
   int kc;          // input planes per step (32 or 16)
   int n_stages;
-  int lookahead;   // steps the gather runs ahead of the tensor core (< n_stages)
-  int tmem_cols;   // power of two >= cout, >= 32
+  int lookahead;   // steps the gather runs ahead of the tensor core (<= n_stages - 1)
+  int tmem_cols;   // 256 per 128 output planes
   int *flags;
 };
 
@@ -210,16 +221,14 @@ __device__ __forceinline__ void cp_async_wait_dyn(int n) {
   }
 }
 
-// Warp roles.  Warps 0-3 (128 threads, one per tile row in the epilogue) are the gather
-// producers; warp 4 owns tensor memory, streams the weight slabs and issues the MMAs.  The
-// roles meet only on mbarriers:
-//   full_a[s]  128 producer arrivals: the rows of stage s are in shared memory (and fenced for
-//              the async proxy)
+// Warp roles.  Warps 0-7 are the gather producers (and, afterwards, the epilogue); warp 8
+// owns tensor memory, streams the weight slabs and issues the MMAs.  The roles meet only on
+// mbarriers:
+//   full_g[s]  one arrival per producer warp: the rows of stage s are in shared memory (and
+//              fenced for the async proxy)
 //   full_w[s]  transaction barrier of the weight slab's bulk copy
 //   empty[s]   tcgen05.commit: the MMAs that read stage s have finished
 //   acc_full   tcgen05.commit after the last MMA of the tile
-constexpr int kProducerThreads = 128;
-
 template <int MODE>
 __global__ void __launch_bounds__(kTcThreads) k_conv_tc(TcParams P) {
   constexpr bool kBf16 = (MODE == TC_BF16);
@@ -227,6 +236,9 @@ __global__ void __launch_bounds__(kTcThreads) k_conv_tc(TcParams P) {
   constexpr int kEsize = kBf16 ? 2 : 4;
   constexpr int kPerPiece = 16 / kEsize;  // elements per 16-byte piece
   constexpr int kMmaK = 32 / kEsize;      // K per instruction (32 bytes)
+  // plain tf32 needs no pass over the gathered rows, so the copies themselves can signal the
+  // barrier when they land (cp.async.mbarrier.arrive.noinc): the producers never wait for data
+  constexpr bool kAsyncArrive = (MODE == TC_TF32);
 
   extern __shared__ __align__(128) unsigned char smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -234,16 +246,20 @@ __global__ void __launch_bounds__(kTcThreads) k_conv_tc(TcParams P) {
   const int K = P.K, kc = P.kc, NS = P.n_stages, L = P.lookahead;
   const int n_slices = P.cin / kc;
   const int pieces_per_row = kc / kPerPiece;
-  const unsigned a_bytes = kTcRows * kc * kEsize;
+  const unsigned g_bytes = kTcRows * kc * kEsize;
   const unsigned w_bytes = P.cout * kc * kEsize;
-  const unsigned stage_bytes = (a_bytes + w_bytes) * (kSplit ? 2 : 1);
+  const unsigned stage_bytes = (g_bytes + w_bytes) * (kSplit ? 2 : 1);
   const unsigned sbo = pieces_per_row * 128;
+  const int n_mt = (P.cout + kTcPlanes - 1) / kTcPlanes;  // plane tiles of 128
 
-  // shared memory carve-up: [stages][A | A_lo | W | W_lo] | idx [K][128] | control
+  // shared memory carve-up: [stages][W | W_lo | G | G_lo] | idx [K][256] | control.  The weight
+  // slab comes first: an MMA always reads 128 weight rows, and when Cout is not a multiple of
+  // 128 the rows past the slab are whatever follows it -- the gathered rows of the same stage,
+  // in bounds and harmless (they only reach TMEM lanes that are never read back).
   unsigned char *stage_base = smem;
   int *sh_idx = reinterpret_cast<int *>(smem + (size_t)NS * stage_bytes);
   unsigned long long *bars = reinterpret_cast<unsigned long long *>(sh_idx + (size_t)K * kTcRows);
-  unsigned long long *full_a = bars;            // [NS]
+  unsigned long long *full_g = bars;            // [NS]
   unsigned long long *full_w = bars + NS;       // [NS]
   unsigned long long *empty = bars + 2 * NS;    // [NS]
   unsigned long long *acc_full = bars + 3 * NS;
@@ -252,11 +268,12 @@ __global__ void __launch_bounds__(kTcThreads) k_conv_tc(TcParams P) {
   unsigned *sh_tmem = reinterpret_cast<unsigned *>(sh_has + kTcMaxOffsets);
   int *sh_nk = reinterpret_cast<int *>(sh_tmem + 1);
   volatile int *sh_abort = sh_nk + 1;
+  const unsigned w_off = 0, g_off = w_bytes * (kSplit ? 2 : 1);
 
   // ---- prologue: barriers, tensor memory, rulebook columns of this tile ----------------------
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
-      mbar_init(&full_a[s], kProducerThreads);
+      mbar_init(&full_g[s], kAsyncArrive ? kProducerThreads : kProducerThreads / 32);
       mbar_init(&full_w[s], 1);
       mbar_init(&empty[s], 1);
     }
@@ -264,7 +281,7 @@ __global__ void __launch_bounds__(kTcThreads) k_conv_tc(TcParams P) {
     *sh_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 4) tmem_alloc(sh_tmem, (unsigned)P.tmem_cols);
+  if (warp == kMmaWarp) tmem_alloc(sh_tmem, (unsigned)P.tmem_cols);
   for (int k = warp; k < K; k += kTcThreads / 32) {
     bool any = false;
 #pragma unroll
@@ -295,29 +312,37 @@ __global__ void __launch_bounds__(kTcThreads) k_conv_tc(TcParams P) {
   const unsigned tmem_base = *sh_tmem;
   const int S = *sh_nk * n_slices;
 
-  if (warp < 4) {
+  if (warp < kMmaWarp) {
     // =================================== gather producers =====================================
-    // Piece p = tid + 128 i of a stage is the 16-byte piece j of tile row r with
+    // Piece p = tid + 256 i of a stage is the 16-byte piece j of tile row r with
     //   r = (p & 7) + 8 * (p / (8 * pieces_per_row)),  j = (p >> 3) % pieces_per_row,
     // so a quarter warp fills one 128-byte core matrix and a warp reads 64 contiguous bytes of
     // 8 rows.  pieces_per_row is a power of two (2, 4 or 8): j is fixed per thread and the rows
-    // step by 16 * 8 / pieces_per_row.
+    // step by 32 * 8 / pieces_per_row; a thread owns pieces_per_row pieces of every stage.
     const int lg = 31 - __clz(pieces_per_row);
     const int j = (tid >> 3) & (pieces_per_row - 1);
     const int r_base = (tid & 7) + 8 * (tid >> (3 + lg));
-    const int r_step = 8 * (16 >> lg);
-    const unsigned off_base = (unsigned)(r_base >> 3) * sbo + j * 128 + (r_base & 7) * 16;
+    const int r_step = 8 * ((kProducerThreads / 8) >> lg);
+    const unsigned off_base = g_off + (unsigned)(r_base >> 3) * sbo + j * 128 + (r_base & 7) * 16;
     const unsigned off_step = (unsigned)(r_step >> 3) * sbo;
-    const int n_mine = pieces_per_row;  // pieces of this thread per stage
+    const int n_mine = pieces_per_row;
+    // running counters instead of divisions: ring stage / round of the step being issued (s)
+    // and of the step being completed (c = s - L), offset index and slice of step s
+    int st = 0, round = 0, ki = 0, slice = 0;
+    int st_c = 0;
     for (int s = 0; s < S + L; ++s) {
       if (*sh_abort) break;
       if (s < S) {
-        const int st = s % NS, use = s / NS;
-        if (use > 0 && !mbar_wait(&empty[st], (unsigned)((use - 1) & 1))) {
-          *sh_abort = 1;
-          break;
+        if (round > 0) {  // one lane polls, the warp follows
+          int freed = 1;
+          if (lane == 0) freed = mbar_wait(&empty[st], (unsigned)((round - 1) & 1)) ? 1 : 0;
+          freed = __shfl_sync(0xffffffffu, freed, 0);
+          if (!freed) {
+            *sh_abort = 1;
+            break;
+          }
         }
-        const int k = sh_steps[s / n_slices], slice = s % n_slices;
+        const int k = sh_steps[ki];
         unsigned char *sa = stage_base + (size_t)st * stage_bytes;
         const unsigned sa_u32 = smem_u32(sa);
         const int *idx = sh_idx + k * kTcRows + r_base;
@@ -346,14 +371,25 @@ __global__ void __launch_bounds__(kTcThreads) k_conv_tc(TcParams P) {
             }
           }
         }
+        if (kAsyncArrive)
+          asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&full_g[st])) : "memory");
+        if (++slice == n_slices) {
+          slice = 0;
+          ++ki;
+        }
+        if (++st == NS) {
+          st = 0;
+          ++round;
+        }
       }
+      if (kAsyncArrive) continue;
       cp_async_commit();
       if (s >= L) {
-        const int c = s - L;  // the step whose rows have landed once only L groups are pending
+        // step c = s - L: its rows have landed once only L groups are still pending
         cp_async_wait_dyn(L);
-        unsigned char *sa = stage_base + (size_t)(c % NS) * stage_bytes;
+        unsigned char *sa = stage_base + (size_t)st_c * stage_bytes;
         if (kSplit) {
-          // low parts of the pieces this thread copied: a_lo = a - trunc_tf32(a)
+          // low parts of the pieces this thread copied: g_lo = g - trunc_tf32(g)
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             if (i < n_mine) {
@@ -364,17 +400,23 @@ __global__ void __launch_bounds__(kTcThreads) k_conv_tc(TcParams P) {
               lo.y = a.y - __uint_as_float(__float_as_uint(a.y) & 0xFFFFE000u);
               lo.z = a.z - __uint_as_float(__float_as_uint(a.z) & 0xFFFFE000u);
               lo.w = a.w - __uint_as_float(__float_as_uint(a.w) & 0xFFFFE000u);
-              *reinterpret_cast<float4 *>(sa + a_bytes + off) = lo;
+              *reinterpret_cast<float4 *>(sa + g_bytes + off) = lo;
             }
           }
         }
-        fence_proxy_async_smem();  // this thread's shared-memory writes -> visible to the tensor core
-        mbar_arrive(&full_a[c % NS]);
+        // No proxy fence here: with copies of later steps still in flight it would wait for all
+        // of them and serialise the gather.  The consumer fences after it has acquired the barrier.
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full_g[st_c]);  // one arrival per warp (release)
+        if (++st_c == NS) st_c = 0;
       }
     }
     cp_async_wait<0>();
 
-    // ================================ epilogue (same 4 warps) ==================================
+    // ================================ epilogue (same 8 warps) ==================================
+    // TMEM lane = output plane, column = tile row.  A warp may read only the 32 lanes of its
+    // quadrant (warp id mod 4); the two warps of a quadrant take alternate 16-row chunks.  The 32
+    // lanes of a warp hold 32 consecutive planes of one row: a 128-byte coalesced store.
     bool have_acc = false;
     if (S > 0 && !*sh_abort) {
       have_acc = mbar_wait(acc_full, 0);
@@ -382,80 +424,104 @@ __global__ void __launch_bounds__(kTcThreads) k_conv_tc(TcParams P) {
     }
     have_acc = __all_sync(0xffffffffu, have_acc);  // tcgen05.ld below is warp-collective
     tc_fence_after();
-    const long long row = row0 + warp * 32 + lane;
-    const bool store = row < P.n_out && (S == 0 || have_acc);
-    for (int c0 = 0; c0 < P.cout; c0 += 16) {
-      float v[16];
-      if (have_acc) {
-        tmem_ld16(tmem_base + ((unsigned)(warp * 32) << 16) + (unsigned)c0, v);
-      } else {
+    const int quad = warp & 3;
+    if (S == 0 || have_acc) {
+      for (int mt = 0; mt < n_mt; ++mt) {
+        const int plane0 = mt * kTcPlanes + quad * 32;
+        if (plane0 >= P.cout) break;
+        const int plane = plane0 + lane;
+        const bool plane_ok = plane < P.cout;
+        const float b = (P.bias && plane_ok) ? P.bias[plane] : 0.f;
+        for (int n0 = (warp >> 2) * 16; n0 < kTcRows; n0 += 32) {
+          if (row0 + n0 >= P.n_out) break;
+          float v[16];
+          if (have_acc) {
+            tmem_ld16(tmem_base + ((unsigned)(quad * 32) << 16) + (unsigned)(mt * kTcRows + n0), v);
+          } else {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) v[i] = 0.f;
-      }
-      if (store) {
-        float *dst = P.out + row * P.ld_out + c0;
+            for (int i = 0; i < 16; ++i) v[i] = 0.f;
+          }
+          if (plane_ok) {
+            float *dst = P.out + (row0 + n0) * P.ld_out + plane;
 #pragma unroll
-        for (int i = 0; i < 16; i += 4) {
-          float4 o;
-          o.x = v[i] + (P.bias ? P.bias[c0 + i] : 0.f);
-          o.y = v[i + 1] + (P.bias ? P.bias[c0 + i + 1] : 0.f);
-          o.z = v[i + 2] + (P.bias ? P.bias[c0 + i + 2] : 0.f);
-          o.w = v[i + 3] + (P.bias ? P.bias[c0 + i + 3] : 0.f);
-          *reinterpret_cast<float4 *>(dst + i) = o;
+            for (int i = 0; i < 16; ++i)
+              if (row0 + n0 + i < P.n_out) dst[(long long)i * P.ld_out] = v[i] + b;
+          }
         }
       }
     }
-  } else if (warp == 4 && lane == 0) {
+  } else if (warp == kMmaWarp && lane == 0) {
     // ============================ weight slabs + MMA issue (one thread) =======================
-    const unsigned idesc = instr_desc(kBf16, P.cout);
+    const unsigned idesc = instr_desc(kBf16);
     const unsigned total_w = w_bytes * (kSplit ? 2 : 1);
     bool ok = true;
-    auto load_w = [&](int s) {
-      const int st = s % NS, use = s / NS;
-      if (use > 0 && !mbar_wait(&empty[st], (unsigned)((use - 1) & 1))) {
+    // running counters (no divisions): weight-slab loader and MMA issuer each walk the steps
+    int w_st = 0, w_round = 0, w_ki = 0, w_slice = 0;
+    auto load_next_w = [&]() {
+      if (w_round > 0 && !mbar_wait(&empty[w_st], (unsigned)((w_round - 1) & 1))) {
         ok = false;
         return;
       }
-      const int k = sh_steps[s / n_slices], slice = s % n_slices;
-      unsigned char *sw = stage_base + (size_t)st * stage_bytes + (kSplit ? 2 * a_bytes : a_bytes);
-      mbar_expect_tx(&full_w[st], total_w);
-      bulk_copy_g2s(smem_u32(sw), P.wprep + ((size_t)k * n_slices + slice) * total_w, total_w, &full_w[st]);
+      const int k = sh_steps[w_ki];
+      unsigned char *sw = stage_base + (size_t)w_st * stage_bytes + w_off;
+      mbar_expect_tx(&full_w[w_st], total_w);
+      bulk_copy_g2s(smem_u32(sw), P.wprep + ((size_t)k * n_slices + w_slice) * total_w, total_w, &full_w[w_st]);
+      if (++w_slice == n_slices) {
+        w_slice = 0;
+        ++w_ki;
+      }
+      if (++w_st == NS) {
+        w_st = 0;
+        ++w_round;
+      }
     };
     const int Lw = L > 0 ? L : 1;  // the weight slabs always run at least one step ahead
-    for (int s = 0; s < Lw && s < S && ok; ++s) load_w(s);
+    for (int s = 0; s < Lw && s < S && ok; ++s) load_next_w();
+    int st = 0, round = 0;
+    const int n_mma = kc / kMmaK;
     for (int step = 0; step < S && ok; ++step) {
       if (*sh_abort) break;
-      if (step + Lw < S) load_w(step + Lw);
-      const int st = step % NS;
-      const unsigned ph = (unsigned)((step / NS) & 1);
-      if (!ok || !mbar_wait(&full_w[st], ph) || !mbar_wait(&full_a[st], ph)) {
+      if (step + Lw < S) load_next_w();
+      const unsigned ph = (unsigned)(round & 1);
+      if (!ok || !mbar_wait(&full_w[st], ph) || !mbar_wait(&full_g[st], ph)) {
         ok = false;
         break;
       }
+      // the producers' generic-proxy writes were acquired through full_g; order them before the
+      // tensor core's async-proxy reads
+      fence_proxy_async_smem();
       tc_fence_after();
-      const unsigned a_addr = smem_u32(stage_base + (size_t)st * stage_bytes);
-      const unsigned w_addr = a_addr + (kSplit ? 2 * a_bytes : a_bytes);
-      const int n_mma = kc / kMmaK;
-      for (int j = 0; j < n_mma; ++j) {
-        unsigned long long da = smem_desc(a_addr + j * 256, 128, sbo);
-        unsigned long long db = smem_desc(w_addr + j * 256, 128, sbo);
-        tc_mma<kBf16>(tmem_base, da, db, idesc, (step > 0 || j > 0) ? 1u : 0u);
-        if (kSplit) {
-          unsigned long long da_lo = smem_desc(a_addr + a_bytes + j * 256, 128, sbo);
-          unsigned long long db_lo = smem_desc(w_addr + w_bytes + j * 256, 128, sbo);
-          tc_mma<kBf16>(tmem_base, da_lo, db, idesc, 1u);
-          tc_mma<kBf16>(tmem_base, da, db_lo, idesc, 1u);
+      const unsigned w_addr = smem_u32(stage_base + (size_t)st * stage_bytes) + w_off;
+      const unsigned g_addr = smem_u32(stage_base + (size_t)st * stage_bytes) + g_off;
+      for (int jj = 0; jj < n_mma; ++jj) {
+        const unsigned long long dg = smem_desc(g_addr + jj * 256, 128, sbo);
+        const unsigned long long dg_lo = smem_desc(g_addr + g_bytes + jj * 256, 128, sbo);
+        const unsigned acc = (step > 0 || jj > 0) ? 1u : 0u;
+        for (int mt = 0; mt < n_mt; ++mt) {
+          const unsigned d = tmem_base + (unsigned)(mt * kTcRows);
+          const unsigned w_mt = w_addr + (unsigned)mt * (kTcPlanes / 8) * sbo + jj * 256;
+          const unsigned long long dw = smem_desc(w_mt, 128, sbo);
+          tc_mma<kBf16>(d, dw, dg, idesc, acc);
+          if (kSplit) {
+            const unsigned long long dw_lo = smem_desc(w_mt + w_bytes, 128, sbo);
+            tc_mma<kBf16>(d, dw, dg_lo, idesc, 1u);
+            tc_mma<kBf16>(d, dw_lo, dg, idesc, 1u);
+          }
         }
       }
       tc_commit(&empty[st]);
       if (step == S - 1) tc_commit(acc_full);
+      if (++st == NS) {
+        st = 0;
+        ++round;
+      }
     }
     if (!ok) *sh_abort = 1;
   }
   tc_fence_before();
   __syncthreads();
   if (*sh_abort && tid == 0) atomicOr(P.flags, FLAG_TC_TIMEOUT);
-  if (warp == 4) tmem_dealloc(tmem_base, (unsigned)P.tmem_cols);
+  if (warp == kMmaWarp) tmem_dealloc(tmem_base, (unsigned)P.tmem_cols);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -472,7 +538,7 @@ static int tc_mode_of(int precision) {
 
 bool conv_tc_supported(int cin, int cout, int groups, int precision) {
   if (tc_mode_of(precision) < 0) return false;
-  return groups == 1 && cin % 32 == 0 && cout % 16 == 0 && cout >= 16 && cout <= 256;
+  return groups == 1 && cin % 16 == 0 && cout % 8 == 0 && cout >= 8 && cout <= 256;
 }
 
 struct TcPlan {
@@ -486,37 +552,44 @@ static int env_int(const char *name, int dflt) {
 }
 
 // Picks the slice width, ring depth and lookahead.  Two CTAs per SM are preferred (one tile's
-// prologue and epilogue then overlap the other's main loop) as long as the ring keeps at least
-// three stages; otherwise one CTA with a deeper ring.  SCN_TC_STAGES / SCN_TC_KC /
-// SCN_TC_LOOKAHEAD override the choice (tuning knobs).
+// prologue and epilogue then overlap the other's main loop) when tensor memory allows it
+// (Cout <= 128: 256 columns each) and the ring keeps at least three stages; otherwise one CTA
+// with a deeper ring.  SCN_TC_STAGES / SCN_TC_KC / SCN_TC_LOOKAHEAD override the choice.
 static bool plan(int mode, int K, int cin, int cout, TcPlan &pl) {
   const int esize = mode == TC_BF16 ? 2 : 4;
   const size_t control = (size_t)K * kTcRows * 4 + 16 * 8 + 2 * kTcMaxOffsets * 4 + 64;
   const size_t one_cta = 200 * 1024, two_ctas = 110 * 1024;
-  int force_kc = env_int("SCN_TC_KC", 0), force_ns = env_int("SCN_TC_STAGES", 0);
-  for (int kc : {32, 16}) {
-    if (cin % kc) continue;
-    if (force_kc && kc != force_kc) continue;
-    if (mode == TC_BF16 && kc == 16) continue;
-    size_t stage = ((size_t)kTcRows * kc * esize + (size_t)cout * kc * esize) * (mode == TC_TF32X3 ? 2 : 1);
-    if (control + 2 * stage > one_cta) continue;
-    int stages = (int)std::min<size_t>(4, (two_ctas - std::min(control, two_ctas)) / stage);
-    if (stages < 3) stages = (int)std::min<size_t>(4, (one_cta - control) / stage);
-    if (force_ns) stages = force_ns;
-    if (stages < 2 || control + (size_t)stages * stage > 220 * 1024) continue;
-    if (stages < 3 && kc == 32 && cin % 16 == 0 && mode != TC_BF16 && !force_kc && !force_ns) continue;
-    pl.kc = kc;
-    pl.stages = stages;
-    // bf16 converts in registers with blocking loads, so running ahead buys nothing there
-    // The gather may run `lookahead` steps ahead; a stage is refilled only after its MMAs have
-    // finished, so the ring needs lookahead + 2 stages to keep the producers from waiting on the
-    // tensor core's round trip every step.  bf16 converts in registers with blocking loads, so
-    // running ahead buys nothing there.
-    pl.lookahead = mode == TC_BF16 ? 0 : std::max(1, std::min(env_int("SCN_TC_LOOKAHEAD", stages - 2), stages - 1));
-    pl.smem = (size_t)stages * stage + control;
-    return true;
+  const int force_kc = env_int("SCN_TC_KC", 0), force_ns = env_int("SCN_TC_STAGES", 0);
+  TcPlan best{};
+  bool found = false;
+  for (int pass = 0; pass < 2 && !found; ++pass) {  // pass 0: two CTAs per SM, pass 1: one
+    if (pass == 0 && (cout > kTcPlanes || force_ns)) continue;
+    const size_t budget = pass == 0 ? two_ctas : one_cta;
+    for (int kc : {32, 16}) {
+      if (cin % kc) continue;
+      if (force_kc && kc != force_kc) continue;
+      size_t stage = ((size_t)kTcRows * kc * esize + (size_t)cout * kc * esize) * (mode == TC_TF32X3 ? 2 : 1);
+      if (control + 2 * stage > budget) continue;
+      int stages = force_ns ? force_ns : (int)std::min<size_t>(4, (budget - control) / stage);
+      if (control + (size_t)stages * stage > 220 * 1024) continue;
+      if (stages < 3 && !force_ns && (pass == 0 || (kc == 32 && cin % 16 == 0 && !force_kc))) continue;
+      best.kc = kc;
+      best.stages = stages;
+      best.smem = (size_t)stages * stage + control;
+      found = true;
+      break;
+    }
   }
-  return false;
+  if (!found) return false;
+  // The gather may run `lookahead` steps ahead; a stage is refilled only after its MMAs have
+  // finished, so the ring needs lookahead + 2 stages to keep the producers from waiting on the
+  // tensor core's round trip every step.  bf16 converts in registers with blocking loads, so
+  // running ahead buys nothing there.
+  best.lookahead = mode == TC_BF16
+                       ? 0
+                       : std::max(1, std::min(env_int("SCN_TC_LOOKAHEAD", best.stages - 2), best.stages - 1));
+  pl = best;
+  return true;
 }
 
 int conv_forward_tc(const float *in, long long n_in, float *out, long long n_out, const float *weight,
@@ -525,8 +598,7 @@ int conv_forward_tc(const float *in, long long n_in, float *out, long long n_out
   if (n_out == 0) return SCN_OK;
   int mode = tc_mode_of(precision);
   SCN_REQUIRE(mode >= 0 && K <= kTcMaxOffsets, SCN_ERR_UNSUPPORTED, "tensor-core path: unsupported precision/filter");
-  SCN_REQUIRE(((uintptr_t)in % 16 == 0) && ((uintptr_t)out % 16 == 0), SCN_ERR_BAD_ARG,
-              "tensor-core path needs 16-byte aligned feature matrices");
+  SCN_REQUIRE((uintptr_t)in % 16 == 0, SCN_ERR_BAD_ARG, "tensor-core path needs a 16-byte aligned input matrix");
   TcPlan pl;
   SCN_REQUIRE(plan(mode, K, cin, cout, pl), SCN_ERR_UNSUPPORTED, "tensor-core path: tile does not fit shared memory");
   const int esize = mode == TC_BF16 ? 2 : 4;
@@ -553,15 +625,15 @@ int conv_forward_tc(const float *in, long long n_in, float *out, long long n_out
   P.kc = pl.kc;
   P.n_stages = pl.stages;
   P.lookahead = pl.lookahead;
-  P.tmem_cols = (int)std::max<unsigned long long>(32, next_pow2((unsigned long long)cout));
+  P.tmem_cols = kTcRows * (int)ceil_div(cout, kTcPlanes);
   P.flags = flags;
   unsigned grid = (unsigned)ceil_div(n_out, kTcRows);
-  static bool configured[3] = {false, false, false};
-  if (!configured[mode]) {
+  static bool configured = false;
+  if (!configured) {
     SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_tc<TC_TF32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
     SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_tc<TC_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
     SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_tc<TC_TF32X3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-    configured[0] = configured[1] = configured[2] = true;
+    configured = true;
   }
   if (mode == TC_TF32)
     SCN_LAUNCH(k_conv_tc<TC_TF32>, grid, kTcThreads, pl.smem, stream, P);
