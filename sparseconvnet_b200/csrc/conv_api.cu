@@ -34,7 +34,11 @@ static int run_conv(scn_metadata *md, Rulebook &rb, bool transposed, const float
       SCN_TRY(device_alloc((void **)&md->flags_dev, sizeof(int), stream));
       SCN_CUDA_CHECK(cudaMemsetAsync(md->flags_dev, 0, sizeof(int), stream));
     }
-    if (precision != SCN_PRECISION_FP32 && conv_tc_supported(cin, cout, groups, precision))
+    // TF32X3 is the fp32-accuracy mode: each shape runs whichever fp32-class kernel is faster.
+    // Below ~96 output planes the three-pass tensor-core tile (cost per 8 input planes and 256
+    // rows is fixed, whatever Cout) does not beat the fp32 FMA kernel, so narrow layers keep it.
+    const bool narrow_x3 = precision == SCN_PRECISION_TF32X3 && cout <= 64;
+    if (precision != SCN_PRECISION_FP32 && !narrow_x3 && conv_tc_supported(cin, cout, groups, precision))
       SCN_TRY(conv_forward_tc(in, rows_in, out, rows_out, weight, bias, table, rb.n_offsets, cin, cout,
                               precision, md->flags_dev, stream));
     else
