@@ -101,7 +101,7 @@ def test_empty_and_tiny_inputs(cuda):
         assert y.features.shape == (n, 5)
         assert x.get_spatial_locations().shape == (n, 4)
         d = scn.SparseToDense(3, 5)(y)
-        assert tuple(d.shape) == (n, 5, 8, 8, 8)
+        assert tuple(d.shape) == (4 if n else 0, 5, 8, 8, 8)   # batch index 3 -> four samples
     # one site: the only rule is the centre offset
     x = scn.InputLayer(3, 16, mode=3)([torch.tensor([[3, 4, 5, 0]]), torch.ones(1, 4, device=dev)])
     out = sc(x)
