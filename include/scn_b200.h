@@ -162,6 +162,35 @@ SCN_API int scn_submanifold_convolution_forward(scn_metadata *md, const int64_t 
                                         const float *bias, int n_in_planes, int n_out_planes,
                                         int groups, int precision, void *stream, double *macs);
 
+/* Allocation-free SubmanifoldConvolution.  No counterpart in the reference.
+ *
+ * scn_submanifold_convolution_forward takes a temporary buffer for the prepared weight image
+ * from the CUDA allocator on every call.  A caller that must not allocate where it runs the
+ * layer -- a fixed launch sequence that is replayed, a latency-critical loop that may not enter
+ * the driver's allocator, a process with a pre-assigned memory budget -- uses this entry point
+ * instead: the same tensor-core kernels with the image kept in an 8 MiB array that is part of
+ * the library (every GPU that loads the library holds those 8 MiB until the process exits).
+ * It calls no cudaMalloc / cudaFree and no allocating library routine.
+ *
+ *  - precision must be SCN_PRECISION_TF32, _BF16 or _TF32X3, groups == 1, and the shape one the
+ *    tensor-core path takes (see scn_precision); anything else is SCN_ERR_UNSUPPORTED.
+ *  - limit: filter_volume * n_in_planes * n_out_planes * (4 for tf32, 2 for bf16, 8 for tf32x3)
+ *    bytes <= 8 MiB, otherwise SCN_ERR_UNSUPPORTED with the sizes in scn_last_error().
+ *  - the rulebook of (spatial_size, filter_size) must already exist
+ *    (scn_md_submanifold_rulebook, which does allocate); otherwise SCN_ERR_NO_GRID.
+ *  - the first call on each device looks up the array's device address; make that call with
+ *    the device current and before starting any stream capture.
+ *  - all calls share the one array and it keeps the last call's image: nothing in it needs
+ *    clearing (each call rewrites what it reads), but two calls that overlap on the GPU (other
+ *    streams, other threads) race on it -- serialise them.
+ *  in [n_active, n_in_planes] -> out [n_active, n_out_planes]; bias [n_out_planes] or NULL. */
+SCN_API int scn_submanifold_convolution_forward_static(scn_metadata *md, const int64_t *spatial_size,
+                                                       const int64_t *filter_size,
+                                                       const float *in_features, float *out_features,
+                                                       const float *weight, const float *bias,
+                                                       int n_in_planes, int n_out_planes,
+                                                       int precision, void *stream);
+
 /* replaces Convolution_updateOutput (sparseconvnet.h:87-92; CPU/Convolution.cpp:45-79).
  * out must have the n_active_out rows reported by scn_md_strided_rulebook. */
 SCN_API int scn_convolution_forward(scn_metadata *md, const int64_t *input_size,

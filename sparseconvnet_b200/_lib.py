@@ -34,6 +34,8 @@ SIGNATURES = {
     "scn_submanifold_convolution_forward": (C.c_int, [_vp, _i64p, _i64p, _vp, _vp, _vp, _vp, C.c_int,
                                                       C.c_int, C.c_int, C.c_int, _vp,
                                                       C.POINTER(C.c_double)]),
+    "scn_submanifold_convolution_forward_static": (C.c_int, [_vp, _i64p, _i64p, _vp, _vp, _vp, _vp, C.c_int,
+                                                             C.c_int, C.c_int, _vp]),
     "scn_convolution_forward": (C.c_int, [_vp, _i64p, _i64p, _i64p, _i64p, _vp, _vp, _vp, _vp,
                                           C.c_int, C.c_int, C.c_int, C.c_int, _vp,
                                           C.POINTER(C.c_double)]),

@@ -646,4 +646,108 @@ int conv_forward_tc(const float *in, long long n_in, float *out, long long n_out
   return SCN_OK;
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant
+// ---------------------------------------------------------------------------------------------
+// conv_forward_tc stages the prepared weight image in memory it takes from the stream-ordered
+// allocator.  Some hosts cannot do that at the point where they run the convolution: code
+// that is replaying a fixed sequence of launches, a real-time loop that must not enter the
+// driver's allocator, a process whose memory budget was handed out up front.  For them the
+// same kernel pair runs with the image in a fixed array that is part of the library image:
+// every GPU that loads the library carries these 8 MiB until the process exits.
+constexpr size_t kStaticWeightBytes = 8u << 20;
+static __device__ __align__(256) unsigned char g_static_weight_image[kStaticWeightBytes];
+
+// In host code the array's name is only a handle; the device address comes from the runtime,
+// once per device, with that device current.
+static void *g_static_weight_ptr[64] = {nullptr};
+
+static int static_weight_image(void **ptr) {
+  int dev = 0;
+  SCN_CUDA_CHECK(cudaGetDevice(&dev));
+  SCN_REQUIRE(dev >= 0 && dev < 64, SCN_ERR_UNSUPPORTED, "device index %d unsupported", dev);
+  if (!g_static_weight_ptr[dev]) {
+    void *p = nullptr;
+    SCN_CUDA_CHECK(cudaGetSymbolAddress(&p, g_static_weight_image));
+    SCN_REQUIRE(p, SCN_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+    g_static_weight_ptr[dev] = p;
+  }
+  *ptr = g_static_weight_ptr[dev];
+  return SCN_OK;
+}
+
 }  // namespace scn
+
+extern "C" int scn_submanifold_convolution_forward_static(scn_metadata *md, const int64_t *spatial_size,
+                                                          const int64_t *filter_size, const float *in_features,
+                                                          float *out_features, const float *weight,
+                                                          const float *bias, int n_in_planes, int n_out_planes,
+                                                          int precision, void *stream_) {
+  using namespace scn;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SCN_REQUIRE(md && spatial_size && filter_size && weight, SCN_ERR_BAD_ARG, "null argument");
+  const int mode = tc_mode_of(precision);
+  SCN_REQUIRE(mode >= 0 && conv_tc_supported(n_in_planes, n_out_planes, 1, precision), SCN_ERR_UNSUPPORTED,
+              "the allocation-free entry point runs the tensor-core kernel only: precision tf32 / bf16 / tf32x3, "
+              "n_in_planes %% 16 == 0, n_out_planes %% 8 == 0, n_out_planes <= 256 (got %d -> %d, precision %d)",
+              n_in_planes, n_out_planes, precision);
+  // the rulebook must exist already: building it would allocate
+  auto it = md->sub_rules.find(make_key(md->dim, spatial_size, filter_size));
+  SCN_REQUIRE(it != md->sub_rules.end() && it->second.built, SCN_ERR_NO_GRID,
+              "rulebook not built yet: call scn_md_submanifold_rulebook (which allocates) beforehand");
+  SCN_REQUIRE(md->flags_dev, SCN_ERR_NO_GRID, "metadata has no device state yet");
+  Rulebook &rb = it->second;
+  const int K = rb.n_offsets, cin = n_in_planes, cout = n_out_planes;
+  if (rb.n_out == 0) return SCN_OK;
+  SCN_REQUIRE(in_features && out_features, SCN_ERR_BAD_ARG, "null features");
+  SCN_REQUIRE(K <= kTcMaxOffsets && (uintptr_t)in_features % 16 == 0, SCN_ERR_UNSUPPORTED,
+              "filter volume above %d or input matrix not 16-byte aligned", kTcMaxOffsets);
+  TcPlan pl;
+  SCN_REQUIRE(plan(mode, K, cin, cout, pl), SCN_ERR_UNSUPPORTED, "tile does not fit shared memory");
+  const int esize = mode == TC_BF16 ? 2 : 4;
+  const size_t wbytes = (size_t)K * cin * cout * esize * (mode == TC_TF32X3 ? 2 : 1);
+  SCN_REQUIRE(wbytes <= kStaticWeightBytes, SCN_ERR_UNSUPPORTED,
+              "prepared weights need %zu bytes, the built-in buffer holds %zu (filter volume x n_in x n_out x %d)",
+              wbytes, kStaticWeightBytes, esize * (mode == TC_TF32X3 ? 2 : 1));
+  void *image = nullptr;
+  SCN_TRY(static_weight_image(&image));
+  // the image is rewritten in full for this call's shape; nothing in it has to start at zero
+  const long long total = (long long)K * cin * cout;
+  SCN_LAUNCH(k_prepare_weights, (unsigned)ceil_div(total, 256), 256, 0, stream, weight, (unsigned char *)image, K, cin,
+             cout, pl.kc, mode);
+  TcParams P;
+  P.in = in_features;
+  P.n_in = rb.n_in;
+  P.ld_in = cin;
+  P.out = out_features;
+  P.n_out = rb.n_out;
+  P.ld_out = cout;
+  P.wprep = (const unsigned char *)image;
+  P.bias = bias;
+  P.nbr = rb.nbr;
+  P.K = K;
+  P.cin = cin;
+  P.cout = cout;
+  P.kc = pl.kc;
+  P.n_stages = pl.stages;
+  P.lookahead = pl.lookahead;
+  P.tmem_cols = kTcRows * (int)ceil_div(cout, kTcPlanes);
+  P.flags = md->flags_dev;
+  const unsigned grid = (unsigned)ceil_div(rb.n_out, kTcRows);
+  static bool configured = false;
+  if (!configured) {  // attribute calls: no allocation
+    SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_tc<TC_TF32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+    SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_tc<TC_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+    SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_tc<TC_TF32X3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+    configured = true;
+  }
+  if (mode == TC_TF32)
+    SCN_LAUNCH(k_conv_tc<TC_TF32>, grid, kTcThreads, pl.smem, stream, P);
+  else if (mode == TC_BF16)
+    SCN_LAUNCH(k_conv_tc<TC_BF16>, grid, kTcThreads, pl.smem, stream, P);
+  else
+    SCN_LAUNCH(k_conv_tc<TC_TF32X3>, grid, kTcThreads, pl.smem, stream, P);
+  SCN_CUDA_CHECK(cudaGetLastError());
+  return SCN_OK;
+}
