@@ -37,9 +37,9 @@ UNIT = "voxels/s"
 TRAFFIC_RATIO = None
 
 
-def workload_name():
+def workload_name(rooms=ROOMS_PER_GPU):
     return ("config3: 3D submanifold U-Net m=32 reps=2 planes[32..224] 4096^3, %d rooms x ~200k voxels "
-            "per GPU, fp32, fresh Metadata per step" % ROOMS_PER_GPU)
+            "per GPU, fp32, fresh Metadata per step" % rooms)
 
 
 def peaks():
@@ -207,6 +207,9 @@ def main():
                     help="convolution arithmetic of the headline number (tf32x3 and fp32 meet the fp32 parity bar)")
     ap.add_argument("--no-variants", action="store_true", help="skip timing the other arithmetic modes")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-config1", action="store_true", help="skip the single-convolution (configuration 1) numbers")
+    ap.add_argument("--rooms", type=int, default=ROOMS_PER_GPU,
+                    help="rooms per GPU; the benchmark is 8, smaller values are for profiler captures of a small case")
     ap.add_argument("--profile-out", default=None, help="write the per-operator breakdown to this file")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -231,7 +234,7 @@ def main():
     inp, net, head = workloads.build_config(CONFIG)
     net.to(dev)
     head.to(dev)
-    samples = list(range(rank * ROOMS_PER_GPU, (rank + 1) * ROOMS_PER_GPU))
+    samples = list(range(rank * args.rooms, (rank + 1) * args.rooms))
     coords_np, feats_np = workloads.make_batch(CONFIG, samples)
     coords_host = torch.from_numpy(coords_np).pin_memory()
     feats_host = torch.from_numpy(feats_np).pin_memory()
@@ -321,7 +324,7 @@ def main():
 
     # ---- configuration 1: one 3-D submanifold convolution 32->32 ------------------------------
     sub = None
-    if rank == 0:
+    if rank == 0 and not args.no_config1:
         inp1, net1, _ = workloads.build_config(1)
         net1.to(dev)
         c1, f1 = workloads.make_batch(1, [0])
@@ -381,7 +384,7 @@ def main():
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": {"fp32": "f32", "tf32x3": "f32 (3-pass tf32 split on tcgen05, fp32 accumulate)",
                       "tf32": "tf32", "bf16": "bf16"}[args.precision], "data": "synthetic",
-            "config": {"workload": workload_name(), "voxels_per_step": total_vox,
+            "config": {"workload": workload_name(args.rooms), "voxels_per_step": total_vox,
                        "l2": "inputs and activations (>200 MB per tensor) exceed the 126 MB L2",
                        "precision": scn.get_precision(), "parallelism": "dp%d by batch index" % world},
             "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
