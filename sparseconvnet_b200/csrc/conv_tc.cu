@@ -353,7 +353,13 @@ __global__ void __launch_bounds__(kTcThreads) k_conv_tc(TcParams P) {
             const int src_row = idx[i * r_step];
             const unsigned off = off_base + i * off_step;
             if (!kBf16) {
-              cp_async16(sa_u32 + off, col + (long long)(src_row < 0 ? 0 : src_row) * P.ld_in, src_row < 0 ? 0u : 16u);
+              // The copy pipe moves one 16-byte lane request per cycle, so a zero-filling copy
+              // costs as much as a real one; a missing row is zeroed with a plain 128-bit store
+              // (32 lanes per 4 cycles) instead and only real rows go through cp.async.
+              if (src_row >= 0)
+                cp_async16(sa_u32 + off, col + (long long)src_row * P.ld_in, 16u);
+              else
+                *reinterpret_cast<uint4 *>(sa + off) = make_uint4(0, 0, 0, 0);
             } else {
               // bf16: 8 input floats -> one 16-byte piece of 8 bf16, converted in registers
               uint4 packed = make_uint4(0, 0, 0, 0);
