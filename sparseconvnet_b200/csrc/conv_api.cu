@@ -10,6 +10,10 @@ int conv_forward_tc(const float *in, long long n_in, float *out, long long n_out
                     const float *bias, const int *table, int K, int cin, int cout, int precision,
                     int *flags, cudaStream_t stream);
 bool conv_tc_supported(int cin, int cout, int groups, int precision);
+int conv_forward_tma(const float *in, long long n_in, float *out, long long n_out, const float *weight,
+                     const float *bias, const int *table, int K, int cin, int cout, int precision, int *flags,
+                     cudaStream_t stream);
+bool conv_tma_supported(int K, int cin, int cout, int groups, int precision, long long n_in);
 
 static int run_conv(scn_metadata *md, Rulebook &rb, bool transposed, const float *in, float *out,
                     const float *weight, const float *bias, int n_in_planes, int n_out_planes, int groups,
@@ -38,7 +42,10 @@ static int run_conv(scn_metadata *md, Rulebook &rb, bool transposed, const float
     // Below ~96 output planes the three-pass tensor-core tile (cost per 8 input planes and 256
     // rows is fixed, whatever Cout) does not beat the fp32 FMA kernel, so narrow layers keep it.
     const bool narrow_x3 = precision == SCN_PRECISION_TF32X3 && cout <= 64;
-    if (precision != SCN_PRECISION_FP32 && !narrow_x3 && conv_tc_supported(cin, cout, groups, precision))
+    if (precision != SCN_PRECISION_FP32 && !narrow_x3 && conv_tma_supported(rb.n_offsets, cin, cout, groups, precision, rows_in))
+      SCN_TRY(conv_forward_tma(in, rows_in, out, rows_out, weight, bias, table, rb.n_offsets, cin, cout,
+                               precision, md->flags_dev, stream));
+    else if (precision != SCN_PRECISION_FP32 && !narrow_x3 && conv_tc_supported(cin, cout, groups, precision))
       SCN_TRY(conv_forward_tc(in, rows_in, out, rows_out, weight, bias, table, rb.n_offsets, cin, cout,
                               precision, md->flags_dev, stream));
     else

@@ -41,10 +41,10 @@
 #include <algorithm>
 
 #include "metadata.cuh"
+#include "tc_ptx.cuh"
 
 namespace scn {
 
-enum TcMode : int { TC_TF32 = 0, TC_BF16 = 1, TC_TF32X3 = 2 };
 
 constexpr int kTcRows = 256;     // output rows per CTA = N of the MMA = TMEM columns per plane tile
 constexpr int kTcPlanes = 128;   // output planes per MMA = M = TMEM lanes
@@ -52,105 +52,7 @@ constexpr int kTcThreads = 288;  // 8 producer/epilogue warps + 1 MMA warp
 constexpr int kProducerThreads = 256;
 constexpr int kMmaWarp = kProducerThreads / 32;
 constexpr int kTcMaxOffsets = 128;
-constexpr unsigned kWaitLimit = 1u << 20;
 
-// ---------------------------------------------------------------------------------------------
-// PTX wrappers
-// ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(unsigned long long *bar, unsigned count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned long long *bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-// Bounded wait: returns false if the phase did not complete within the iteration limit.
-__device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned parity) {
-  unsigned addr = smem_u32(bar);
-  for (unsigned it = 0; it < kWaitLimit; ++it) {
-    unsigned done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(addr), "r"(parity)
-        : "memory");
-    if (done) return true;
-  }
-  return false;
-}
-__device__ __forceinline__ void cp_async16(unsigned dst, const void *src, unsigned src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void bulk_copy_g2s(unsigned dst, const void *src, unsigned bytes, unsigned long long *bar) {
-  asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-               "l"(src), "r"(bytes), "r"(smem_u32(bar))
-               : "memory");
-}
-__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tmem_alloc(unsigned *dst_smem, unsigned ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols)
-               : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(unsigned taddr, unsigned ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tc_commit(unsigned long long *bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
-}
-template <bool BF16>
-__device__ __forceinline__ void tc_mma(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc,
-                                       unsigned idesc, unsigned accumulate) {
-  if (BF16)
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-  else
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// 32 lanes x 16 consecutive 32-bit columns: thread t of the warp gets lane (base lane + t).
-__device__ __forceinline__ void tmem_ld16(unsigned taddr, float *v) {
-  unsigned r[16];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, "
-      "[%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// Shared-memory matrix descriptor, K-major, no swizzle: 8-row x 16-byte core matrices stored as
-// contiguous 128-byte blocks; `lbo` = byte step between core matrices along K, `sbo` = byte
-// step between 8-row groups along M/N; version field 1 (Blackwell).
-__device__ __forceinline__ unsigned long long smem_desc(unsigned addr, unsigned lbo, unsigned sbo) {
-  unsigned long long d = 0;
-  d |= (unsigned long long)((addr >> 4) & 0x3FFF);
-  d |= (unsigned long long)((lbo >> 4) & 0x3FFF) << 16;
-  d |= (unsigned long long)((sbo >> 4) & 0x3FFF) << 32;
-  d |= 1ull << 46;
-  return d;
-}
 // Instruction descriptor: D fp32, A/B both tf32 or both bf16, both K-major, M = 128, N = 256.
 __host__ __device__ inline unsigned instr_desc(bool bf16) {
   unsigned fmt = bf16 ? 1u : 2u;
@@ -188,6 +90,14 @@ __global__ void k_prepare_weights(const float *__restrict__ w, unsigned char *__
   }
 }
 
+int prepare_weights(const float *w, unsigned char *out, int K, int cin, int cout, int kc, int mode,
+                    cudaStream_t stream) {
+  long long total = (long long)K * cin * cout;
+  SCN_LAUNCH(k_prepare_weights, (unsigned)ceil_div(total, 256), 256, 0, stream, w, out, K, cin, cout, kc, mode);
+  SCN_CUDA_CHECK(cudaGetLastError());
+  return SCN_OK;
+}
+
 // ---------------------------------------------------------------------------------------------
 // main kernel
 // ---------------------------------------------------------------------------------------------
@@ -209,9 +119,6 @@ struct TcParams {
   int *flags;
 };
 
-__device__ __forceinline__ void mbar_arrive(unsigned long long *bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
 __device__ __forceinline__ void cp_async_wait_dyn(int n) {
   switch (n) {
     case 0: cp_async_wait<0>(); break;

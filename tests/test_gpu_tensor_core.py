@@ -51,6 +51,34 @@ def test_submanifold_conv_tensor_core(mode, tol, cin, cout, cuda, restore_precis
     assert err > 0 or mode == "tf32x3", "tensor-core result identical to fp32: the path did not run"
 
 
+@pytest.mark.parametrize("gather", ["cp.async", "tma"])
+@pytest.mark.parametrize("mode,tol", MODES)
+def test_persistent_kernel_both_gathers(mode, tol, gather, cuda, restore_precision, monkeypatch):
+    """The persistent kernel (double-buffered TMEM accumulators, one CTA per SM) forced on for
+    every arithmetic mode, with its cp.async gather and with the TMA tile::gather4 gather
+    (rows without a rule are out-of-bounds coordinates that the TMA unit zero-fills)."""
+    import sparseconvnet_b200 as scn
+    monkeypatch.setenv("SCN_TC_PERSISTENT", "1")
+    monkeypatch.setenv("SCN_TC_TMA_GATHER", "1" if gather == "tma" else "0")
+    coords = _surface(9000, 64, 3, 21)
+    rng = np.random.default_rng(22)
+    for cin, cout in ((32, 32), (64, 96), (128, 64)):
+        torch.manual_seed(cin + cout)
+        inp = scn.InputLayer(3, 64, mode=3)
+        sc = scn.SubmanifoldConvolution(3, cin, cout, 3, True).to(cuda)
+        sc.bias.data.normal_()
+        feats = torch.from_numpy(rng.standard_normal((coords.shape[0], cin)).astype(np.float32)).to(cuda)
+        with torch.no_grad():
+            x = inp([torch.from_numpy(coords), feats])
+            scn.set_precision("fp32")
+            want = sc(x).features
+            scn.set_precision(mode)
+            got = sc(x).features
+            x.metadata.poll_errors()
+        err = helpers.rel_err(got.cpu().numpy(), want.cpu().numpy())
+        assert err <= tol, "%s %s %d->%d: relative error %.3g" % (gather, mode, cin, cout, err)
+
+
 @pytest.mark.parametrize("mode,tol", MODES)
 def test_strided_and_transposed_tensor_core(mode, tol, cuda, restore_precision):
     import sparseconvnet_b200 as scn
