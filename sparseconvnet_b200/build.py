@@ -61,7 +61,7 @@ def build(force=False, verbose=False):
     with cf.ThreadPoolExecutor(max(1, min(8, os.cpu_count() or 1))) as ex:
         objs = list(ex.map(lambda s: _compile(s, verbose), _sources()))
     cmd = [NVCC, "-shared", "-o", LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a",
-                                                   "-lcudart", "-lcuda"]
+                                                   "-lcudart"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError("link failed:\n%s" % r.stderr[-4000:])

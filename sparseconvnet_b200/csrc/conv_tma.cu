@@ -607,9 +607,22 @@ int conv_forward_tma(const float *in, long long n_in, float *out, long long n_ou
   cuuint64_t gstride[1] = {(cuuint64_t)cin * sizeof(float)};
   cuuint32_t box[2] = {(cuuint32_t)kSlice, 1};
   cuuint32_t estr[2] = {1, 1};
-  CUresult cr = cuTensorMapEncodeTiled(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(in), gdim, gstride,
-                                       box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                       CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  // The encoder is a driver entry point; it is looked up through the runtime so that the library
+  // does not link against libcuda (and still loads on a machine without a driver).
+  typedef CUresult (*EncodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeTiled encode = nullptr;
+  if (!encode) {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    SCN_CUDA_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+    SCN_REQUIRE(fn && qres == cudaDriverEntryPointSuccess, SCN_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+    encode = (EncodeTiled)fn;
+  }
+  CUresult cr = encode(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(in), gdim, gstride, box, estr,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   SCN_REQUIRE(cr == CUDA_SUCCESS, SCN_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)cr);
 
   const int esize = mode == TC_BF16 ? 2 : 4;
