@@ -123,9 +123,12 @@ def op_bytes(r):
 
 
 def summarize_profile(rows):
+    """Per kernel class: time, calls, algorithmic bytes and FLOPs of one step.  Convolution calls
+    are split by the kernel that ran them."""
     agg = {}
     for r in rows:
-        a = agg.setdefault(r["kind"], {"ms": 0.0, "calls": 0, "bytes": 0.0, "flops": 0.0})
+        name = r.get("kernel", r["kind"]) if r["kind"] == "conv" else r["kind"]
+        a = agg.setdefault(name, {"ms": 0.0, "calls": 0, "bytes": 0.0, "flops": 0.0})
         a["ms"] += r["ms"]
         a["calls"] += 1
         a["bytes"] += op_bytes(r)
@@ -311,7 +314,7 @@ def main():
     top = max(agg, key=lambda k: agg[k]["ms"])
     a = agg[top]
     achieved = a["bytes"] / (a["ms"] / 1e3) / 1e9
-    roofline = {"kernel": {"conv": "k_conv_simt" if args.precision == "fp32" else "k_conv_tc", "batchnorm": "k_bn_apply", "rules_submanifold": "k_submanifold_rules",
+    roofline = {"kernel": {"batchnorm": "k_bn_apply", "rules_submanifold": "k_submanifold_rules",
                            "rules_strided": "k_strided_*", "input_hash": "k_insert_input"}.get(top, top),
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "peak_source": peak_src,

@@ -64,6 +64,12 @@ enum scn_precision {
   SCN_PRECISION_TF32X3 = 3 /* tcgen05 kind::tf32, three passes over the hi/lo split of both
                              operands, fp32 accumulate in TMEM: fp32-class accuracy          */
 };
+/* which convolution kernel the last convolution call of this thread ran (for profiling) */
+enum scn_conv_kernel {
+  SCN_KERNEL_CONV_SIMT = 0,          /* k_conv_simt: fp32 FMA                                 */
+  SCN_KERNEL_CONV_TC = 1,            /* k_conv_tc: tcgen05, one tile per CTA                  */
+  SCN_KERNEL_CONV_TC_PERSISTENT = 2  /* k_conv_tma: tcgen05, persistent, double-buffered TMEM */
+};
 /* The tensor-core modes need groups == 1, n_in_planes % 32 == 0, n_out_planes % 16 == 0 and
  * n_out_planes <= 256; other shapes run the fp32 kernel whatever the precision says. */
 
@@ -156,6 +162,10 @@ SCN_API int scn_md_rulebook_export(scn_metadata *md, int kind, const int64_t *si
  * weight [filter_volume, groups, n_in/groups, n_out/groups], bias [n_out] or NULL.
  * in [n_active, n_in] -> out [n_active, n_out].  macs (may be NULL) receives the
  * reference's return value (rules x n_in/groups x n_out/groups x groups). */
+/* -1 before the first convolution, else an scn_conv_kernel value.  No counterpart in the
+ * reference; lets a profiler attribute a call's time to the kernel that ran it. */
+SCN_API int scn_last_conv_kernel(void);
+
 SCN_API int scn_submanifold_convolution_forward(scn_metadata *md, const int64_t *spatial_size,
                                         const int64_t *filter_size, const float *in_features,
                                         float *out_features, const float *weight,

@@ -18,6 +18,7 @@ SIGNATURES = {
     "scn_status_string": (C.c_char_p, [C.c_int]),
     "scn_last_error": (C.c_char_p, []),
     "scn_launch_count": (C.c_longlong, []),
+    "scn_last_conv_kernel": (C.c_int, []),
     "scn_md_create": (C.c_int, [C.c_int, C.POINTER(_vp)]),
     "scn_md_destroy": (C.c_int, [_vp]),
     "scn_md_clear": (C.c_int, [_vp, _vp]),

@@ -15,6 +15,8 @@ int conv_forward_tma(const float *in, long long n_in, float *out, long long n_ou
                      cudaStream_t stream);
 bool conv_tma_supported(int K, int cin, int cout, int groups, int precision, long long n_in);
 
+static thread_local int g_last_kernel = -1;
+
 static int run_conv(scn_metadata *md, Rulebook &rb, bool transposed, const float *in, float *out,
                     const float *weight, const float *bias, int n_in_planes, int n_out_planes, int groups,
                     int precision, cudaStream_t stream, double *macs) {
@@ -43,14 +45,20 @@ static int run_conv(scn_metadata *md, Rulebook &rb, bool transposed, const float
     // rows is fixed, whatever Cout) does not beat the fp32 FMA kernel, so narrow layers keep it.
     const bool narrow_x3 = precision == SCN_PRECISION_TF32X3 && cout <= 64;
     if (precision != SCN_PRECISION_FP32 && !narrow_x3 && conv_tma_supported(rb.n_offsets, cin, cout, groups, precision, rows_in))
+    {
       SCN_TRY(conv_forward_tma(in, rows_in, out, rows_out, weight, bias, table, rb.n_offsets, cin, cout,
                                precision, md->flags_dev, stream));
-    else if (precision != SCN_PRECISION_FP32 && !narrow_x3 && conv_tc_supported(cin, cout, groups, precision))
+      g_last_kernel = SCN_KERNEL_CONV_TC_PERSISTENT;
+    } else if (precision != SCN_PRECISION_FP32 && !narrow_x3 && conv_tc_supported(cin, cout, groups, precision))
+    {
       SCN_TRY(conv_forward_tc(in, rows_in, out, rows_out, weight, bias, table, rb.n_offsets, cin, cout,
                               precision, md->flags_dev, stream));
-    else
+      g_last_kernel = SCN_KERNEL_CONV_TC;
+    } else {
       SCN_TRY(conv_forward_simt(in, rows_in, out, rows_out, weight, bias, table, rb.n_offsets, cin, cout,
                                 groups, md->flags_dev, stream));
+      g_last_kernel = SCN_KERNEL_CONV_SIMT;
+    }
   }
   if (macs) {  // the reference's return value: rules x ip x op x groups (CPU/Convolution.cpp:141)
     SCN_TRY(rulebook_counts(rb, stream));
@@ -63,6 +71,8 @@ static int run_conv(scn_metadata *md, Rulebook &rb, bool transposed, const float
 using namespace scn;
 
 extern "C" {
+
+int scn_last_conv_kernel(void) { return g_last_kernel; }
 
 int scn_submanifold_convolution_forward(scn_metadata *md, const int64_t *spatial_size,
                                         const int64_t *filter_size, const float *in_features,
