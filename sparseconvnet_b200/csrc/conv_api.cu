@@ -1,5 +1,7 @@
 // C-ABI entry points of the three convolution operators: rulebook lookup (built on first use
 // and cached, like the reference's Metadata), shape checks, kernel choice.
+#include <stdlib.h>
+
 #include "metadata.cuh"
 
 namespace scn {
@@ -43,7 +45,8 @@ static int run_conv(scn_metadata *md, Rulebook &rb, bool transposed, const float
     // TF32X3 is the fp32-accuracy mode: each shape runs whichever fp32-class kernel is faster.
     // Below ~96 output planes the three-pass tensor-core tile (cost per 8 input planes and 256
     // rows is fixed, whatever Cout) does not beat the fp32 FMA kernel, so narrow layers keep it.
-    const bool narrow_x3 = precision == SCN_PRECISION_TF32X3 && cout <= 64;
+    static const int x3_min_cout = getenv("SCN_X3_MIN_COUT") ? atoi(getenv("SCN_X3_MIN_COUT")) : 64;
+    const bool narrow_x3 = precision == SCN_PRECISION_TF32X3 && cout < x3_min_cout;
     if (precision != SCN_PRECISION_FP32 && !narrow_x3 && conv_tma_supported(rb.n_offsets, cin, cout, groups, precision, rows_in))
     {
       SCN_TRY(conv_forward_tma(in, rows_in, out, rows_out, weight, bias, table, rb.n_offsets, cin, cout,
