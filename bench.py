@@ -274,12 +274,17 @@ def main():
         barrier()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         l0 = SCN.launch_count()
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps - 1)]
         a.record()
-        for _ in range(steps):
+        for i in range(steps):
             fn()
+            if i < steps - 1:
+                marks[i].record()
         b.record()
         barrier()
         ms = a.elapsed_time(b)
+        edges = [a] + marks + [b]
+        timed.per_step = [round(edges[i].elapsed_time(edges[i + 1]), 3) for i in range(steps)]
         launches = SCN.launch_count() - l0
         if world > 1:
             t = torch.tensor([ms], device=dev)
@@ -293,6 +298,7 @@ def main():
     sampler = ClockSampler(local)
     sampler.start()
     ms, launches = timed(step_resident, args.steps)
+    per_step = timed.per_step
     clocks = sampler.stop()
     for _ in range(2):
         step_e2e()
@@ -393,7 +399,7 @@ def main():
             "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": int(coords_host.numel() * 8 + feats_host.numel() * 4),
                     "d2h_bytes_per_step": int(out_host.numel() * 4)},
-            "gpu_launches": int(launches),
+            "gpu_launches": int(launches), "ms_each_step": per_step,
             "roofline": roofline, "breakdown_ms_per_step": breakdown, "submanifold_conv": sub,
             "variants_voxels_per_sec": variants,
             "cpu_baseline": cpu, "clocks": clocks,

@@ -47,13 +47,16 @@ static int run_conv(scn_metadata *md, Rulebook &rb, bool transposed, const float
     // rows is fixed, whatever Cout) does not beat the fp32 FMA kernel, so narrow layers keep it.
     static const int x3_min_cout = getenv("SCN_X3_MIN_COUT") ? atoi(getenv("SCN_X3_MIN_COUT")) : 64;
     const bool narrow_x3 = precision == SCN_PRECISION_TF32X3 && cout < x3_min_cout;
-    if (precision != SCN_PRECISION_FP32 && !narrow_x3 && conv_tma_supported(rb.n_offsets, cin, cout, groups, precision, rows_in))
-    {
+    // The persistent kernel runs one CTA per SM over whole tiles; with fewer tiles than SMs the
+    // per-tile kernel is used instead, which splits a tile's filter offsets over several CTAs.
+    static const bool force_persistent = getenv("SCN_TC_PERSISTENT") && atoi(getenv("SCN_TC_PERSISTENT")) != 0;
+    const bool few_tiles = rows_out <= 148 * 256 && !force_persistent;
+    if (precision != SCN_PRECISION_FP32 && !narrow_x3 && !few_tiles &&
+        conv_tma_supported(rb.n_offsets, cin, cout, groups, precision, rows_in)) {
       SCN_TRY(conv_forward_tma(in, rows_in, out, rows_out, weight, bias, table, rb.n_offsets, cin, cout,
                                precision, md->flags_dev, stream));
       g_last_kernel = SCN_KERNEL_CONV_TC_PERSISTENT;
-    } else if (precision != SCN_PRECISION_FP32 && !narrow_x3 && conv_tc_supported(cin, cout, groups, precision))
-    {
+    } else if (precision != SCN_PRECISION_FP32 && !narrow_x3 && conv_tc_supported(cin, cout, groups, precision)) {
       SCN_TRY(conv_forward_tc(in, rows_in, out, rows_out, weight, bias, table, rb.n_offsets, cin, cout,
                               precision, md->flags_dev, stream));
       g_last_kernel = SCN_KERNEL_CONV_TC;

@@ -12,11 +12,20 @@
 //
 // The same kernel serves SubmanifoldConvolution, Convolution (table nbr) and Deconvolution
 // (table tnbr): the table maps (offset, output row) to an input row or -1.
+#include <stdlib.h>
+
 #include <algorithm>
 
 #include "metadata.cuh"
 
 namespace scn {
+
+// conv_pipe.cu: the software-pipelined variant for 16-byte aligned rows and <= 32 filter offsets.
+bool conv_pipe_supported(const float *in, const float *out, const float *weight, const float *bias, int K, int cin,
+                         int cout);
+int conv_forward_pipe(const float *in, long long n_in, float *out, long long n_out, const float *weight,
+                      const float *bias, const int *table, int K, int cin, int cout, int groups, int *flags,
+                      cudaStream_t stream);
 
 constexpr int kTileRows = 128;  // output rows per CTA
 constexpr int kChunk = 32;      // input planes staged per step
@@ -224,6 +233,9 @@ int conv_forward_simt(const float *in, long long n_in, float *out, long long n_o
                       const float *bias, const int *table, int K, int cin, int cout, int groups,
                       int *flags, cudaStream_t stream) {
   if (n_out == 0) return SCN_OK;
+  static const bool block_kernel_only = getenv("SCN_SIMT_BLOCK") && atoi(getenv("SCN_SIMT_BLOCK")) != 0;
+  if (!block_kernel_only && conv_pipe_supported(in, out, weight, bias, K, cin, cout))
+    return conv_forward_pipe(in, n_in, out, n_out, weight, bias, table, K, cin, cout, groups, flags, stream);
   int ld_in = cin * groups, ld_out = cout * groups;
   if (cout <= 16)
     return launch_simt<16>(in, ld_in, n_in, out, ld_out, n_out, weight, bias, table, K, cin, cout, groups, flags, stream);

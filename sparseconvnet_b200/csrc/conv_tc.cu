@@ -116,6 +116,8 @@ struct TcParams {
   int n_stages;
   int lookahead;   // steps the gather runs ahead of the tensor core (<= n_stages - 1)
   int tmem_cols;   // 256 per 128 output planes
+  int n_split;     // CTAs per tile (grid.y): each takes a contiguous range of the filter offsets
+  float *partial;  // [n_split][n_out][cout] partial sums when n_split > 1 (k_sum_partials adds them up)
   int *flags;
 };
 
@@ -158,6 +160,11 @@ __global__ void __launch_bounds__(kTcThreads) k_conv_tc(TcParams P) {
   const unsigned stage_bytes = (g_bytes + w_bytes) * (kSplit ? 2 : 1);
   const unsigned sbo = pieces_per_row * 128;
   const int n_mt = (P.cout + kTcPlanes - 1) / kTcPlanes;  // plane tiles of 128
+  // offsets of this CTA; with n_split > 1 the tile's sum over offsets is finished by k_sum_partials
+  const int k_begin = (int)(((long long)blockIdx.y * K) / P.n_split);
+  const int k_end = (int)(((long long)(blockIdx.y + 1) * K) / P.n_split);
+  float *const out_base = P.partial ? P.partial + (size_t)blockIdx.y * P.n_out * P.ld_out : P.out;
+  const float *const bias_base = P.partial ? nullptr : P.bias;
 
   // shared memory carve-up: [stages][W | W_lo | G | G_lo] | idx [K][256] | control.  The weight
   // slab comes first: an MMA always reads 128 weight rows, and when Cout is not a multiple of
@@ -189,7 +196,7 @@ __global__ void __launch_bounds__(kTcThreads) k_conv_tc(TcParams P) {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == kMmaWarp) tmem_alloc(sh_tmem, (unsigned)P.tmem_cols);
-  for (int k = warp; k < K; k += kTcThreads / 32) {
+  for (int k = k_begin + warp; k < k_end; k += kTcThreads / 32) {
     bool any = false;
 #pragma unroll
     for (int i = 0; i < kTcRows / 32; ++i) {
@@ -211,7 +218,7 @@ __global__ void __launch_bounds__(kTcThreads) k_conv_tc(TcParams P) {
   tc_fence_after();
   if (tid == 0) {
     int n = 0;
-    for (int k = 0; k < K; ++k)
+    for (int k = k_begin; k < k_end; ++k)
       if (sh_has[k]) sh_steps[n++] = k;
     *sh_nk = n;
   }
@@ -344,7 +351,7 @@ __global__ void __launch_bounds__(kTcThreads) k_conv_tc(TcParams P) {
         if (plane0 >= P.cout) break;
         const int plane = plane0 + lane;
         const bool plane_ok = plane < P.cout;
-        const float b = (P.bias && plane_ok) ? P.bias[plane] : 0.f;
+        const float b = (bias_base && plane_ok) ? bias_base[plane] : 0.f;
         for (int n0 = (warp >> 2) * 16; n0 < kTcRows; n0 += 32) {
           if (row0 + n0 >= P.n_out) break;
           float v[16];
@@ -355,7 +362,7 @@ __global__ void __launch_bounds__(kTcThreads) k_conv_tc(TcParams P) {
             for (int i = 0; i < 16; ++i) v[i] = 0.f;
           }
           if (plane_ok) {
-            float *dst = P.out + (row0 + n0) * P.ld_out + plane;
+            float *dst = out_base + (row0 + n0) * P.ld_out + plane;
 #pragma unroll
             for (int i = 0; i < 16; ++i)
               if (row0 + n0 + i < P.n_out) dst[(long long)i * P.ld_out] = v[i] + b;
@@ -437,6 +444,24 @@ __global__ void __launch_bounds__(kTcThreads) k_conv_tc(TcParams P) {
   if (warp == kMmaWarp) tmem_dealloc(tmem_base, (unsigned)P.tmem_cols);
 }
 
+// out[i] = bias[i % cout] + sum over s of partial[s][i], in the fixed order s = 0, 1, ...: the result
+// does not depend on which CTA finished first.
+__global__ void k_sum_partials(const float4 *__restrict__ partial, int n_split, long long n4, const float *__restrict__ bias,
+                               int cout, float4 *__restrict__ out) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n4) return;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (bias) acc = __ldg(reinterpret_cast<const float4 *>(bias + (int)((i * 4) % cout)));
+  for (int s = 0; s < n_split; ++s) {
+    const float4 v = partial[(long long)s * n4 + i];
+    acc.x += v.x;
+    acc.y += v.y;
+    acc.z += v.z;
+    acc.w += v.w;
+  }
+  out[i] = acc;
+}
+
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
@@ -462,6 +487,30 @@ struct TcPlan {
 static int env_int(const char *name, int dflt) {
   const char *v = getenv(name);
   return v ? atoi(v) : dflt;
+}
+
+// A tile costs K * Cin/8 (x3) tensor-core instructions of ~150 cycles however few rows it holds,
+// so a level with fewer tiles than the GPU has SMs leaves most tensor cores idle for the whole
+// call.  Such calls split every tile's filter offsets over n CTAs; the CTAs write partial sums
+// and k_sum_partials adds them in a fixed order.  n minimises (waves of CTAs) x (offsets per
+// CTA + a fixed cost of about 1.5 offsets for a CTA's prologue and epilogue).
+// SCN_TC_SPLIT forces the factor (1 = never split).
+static int split_factor(long long n_out, int K, int cout) {
+  const int forced = env_int("SCN_TC_SPLIT", 0);
+  if (forced > 0) return std::max(1, std::min(forced, K));
+  const long long tiles = ceil_div(n_out, kTcRows);
+  const long long slots = 148 * (cout <= kTcPlanes ? 2 : 1);  // tensor memory: 256 columns per 128 planes
+  if (tiles >= 4 * slots) return 1;
+  int best = 1;
+  double best_cost = 1e30;
+  for (int n = 1; n <= K; ++n) {
+    const double cost = (double)ceil_div(tiles * n, slots) * ((double)ceil_div(K, n) + 1.5);
+    if (cost < best_cost - 1e-9) {
+      best_cost = cost;
+      best = n;
+    }
+  }
+  return best;
 }
 
 // Picks the slice width, ring depth and lookahead.  Two CTAs per SM are preferred (one tile's
@@ -540,7 +589,11 @@ int conv_forward_tc(const float *in, long long n_in, float *out, long long n_out
   P.lookahead = pl.lookahead;
   P.tmem_cols = kTcRows * (int)ceil_div(cout, kTcPlanes);
   P.flags = flags;
-  unsigned grid = (unsigned)ceil_div(n_out, kTcRows);
+  const bool vec_ok = (uintptr_t)out % 16 == 0 && (uintptr_t)bias % 16 == 0;  // k_sum_partials moves float4
+  P.n_split = vec_ok ? split_factor(n_out, K, cout) : 1;
+  P.partial = nullptr;
+  if (P.n_split > 1) SCN_TRY(device_alloc((void **)&P.partial, (size_t)P.n_split * n_out * cout * sizeof(float), stream));
+  dim3 grid((unsigned)ceil_div(n_out, kTcRows), (unsigned)P.n_split);
   static bool configured = false;
   if (!configured) {
     SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_tc<TC_TF32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
@@ -555,6 +608,12 @@ int conv_forward_tc(const float *in, long long n_in, float *out, long long n_out
   else
     SCN_LAUNCH(k_conv_tc<TC_TF32X3>, grid, kTcThreads, pl.smem, stream, P);
   SCN_CUDA_CHECK(cudaGetLastError());
+  if (P.n_split > 1) {
+    const long long n4 = n_out * cout / 4;  // cout is a multiple of 8
+    SCN_LAUNCH(k_sum_partials, (unsigned)ceil_div(n4, 256), 256, 0, stream, reinterpret_cast<const float4 *>(P.partial), P.n_split, n4, bias, cout, reinterpret_cast<float4 *>(out));
+    SCN_CUDA_CHECK(cudaGetLastError());
+    SCN_TRY(device_free(P.partial, stream));
+  }
   SCN_TRY(device_free(wprep, stream));
   return SCN_OK;
 }
@@ -646,6 +705,8 @@ extern "C" int scn_submanifold_convolution_forward_static(scn_metadata *md, cons
   P.n_stages = pl.stages;
   P.lookahead = pl.lookahead;
   P.tmem_cols = kTcRows * (int)ceil_div(cout, kTcPlanes);
+  P.n_split = 1;  // splitting needs scratch for the partial sums
+  P.partial = nullptr;
   P.flags = md->flags_dev;
   const unsigned grid = (unsigned)ceil_div(rb.n_out, kTcRows);
   static bool configured = false;
