@@ -271,6 +271,17 @@ def main():
         torch.cuda.synchronize()
 
     def timed(fn, steps):
+        # a cyclic-GC pass of the interpreter in the middle of a step stalls the launch thread for
+        # tens of ms (seen as one 70 ms step among 31 ms ones): collect before, not during
+        import gc
+        gc.collect()
+        gc.disable()
+        try:
+            return _timed(fn, steps)
+        finally:
+            gc.enable()
+
+    def _timed(fn, steps):
         barrier()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         l0 = SCN.launch_count()

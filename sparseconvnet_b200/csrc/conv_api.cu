@@ -43,13 +43,14 @@ static int run_conv(scn_metadata *md, Rulebook &rb, bool transposed, const float
       SCN_CUDA_CHECK(cudaMemsetAsync(md->flags_dev, 0, sizeof(int), stream));
     }
     // TF32X3 is the fp32-accuracy mode: each shape runs whichever fp32-class kernel is faster.
-    // Below ~96 output planes the three-pass tensor-core tile (cost per 8 input planes and 256
-    // rows is fixed, whatever Cout) does not beat the fp32 FMA kernel, so narrow layers keep it.
-    static const int x3_min_cout = getenv("SCN_X3_MIN_COUT") ? atoi(getenv("SCN_X3_MIN_COUT")) : 64;
+    // Below 64 output planes the three-pass tensor-core tile (its cost per 8 input planes and 256
+    // rows is fixed, whatever Cout) does not beat the fp32 FMA kernel, so narrow layers keep it
+    // (SCN_X3_MIN_COUT moves the threshold).
+    const int x3_min_cout = getenv("SCN_X3_MIN_COUT") ? atoi(getenv("SCN_X3_MIN_COUT")) : 64;
     const bool narrow_x3 = precision == SCN_PRECISION_TF32X3 && cout < x3_min_cout;
     // The persistent kernel runs one CTA per SM over whole tiles; with fewer tiles than SMs the
     // per-tile kernel is used instead, which splits a tile's filter offsets over several CTAs.
-    static const bool force_persistent = getenv("SCN_TC_PERSISTENT") && atoi(getenv("SCN_TC_PERSISTENT")) != 0;
+    const bool force_persistent = getenv("SCN_TC_PERSISTENT") && atoi(getenv("SCN_TC_PERSISTENT")) != 0;
     const bool few_tiles = rows_out <= 148 * 256 && !force_persistent;
     if (precision != SCN_PRECISION_FP32 && !narrow_x3 && !few_tiles &&
         conv_tma_supported(rb.n_offsets, cin, cout, groups, precision, rows_in)) {

@@ -80,21 +80,6 @@ __device__ __forceinline__ unsigned long long smem_desc_sw128(unsigned addr) {
   d |= 2ull << 61;                             // SWIZZLE_128B
   return d;
 }
-__device__ __forceinline__ void tmem_ld32(unsigned taddr, float *v) {
-  unsigned r[32];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
 __host__ __device__ inline unsigned instr_desc_tma(bool bf16) {
   unsigned fmt = bf16 ? 1u : 2u;
   return (1u << 4) | (fmt << 7) | (fmt << 10) | ((unsigned)(kRows >> 3) << 17) | ((unsigned)(kPlanes >> 4) << 24);
@@ -174,6 +159,17 @@ k_conv_tma(const __grid_constant__ CUtensorMap in_map, TmaParams P) {
     int st = 0, round = 0;
     bool ok = true;
     auto producer_sync = [] { asm volatile("bar.sync 1, %0;" ::"n"(N_PRODUCER_WARPS * 32) : "memory"); };
+    // barrier + OR over the producers: every producer thread gets the same answer, so they leave
+    // the loop together (a warp that left alone would strand the others at the next barrier)
+    auto producer_vote = [](bool x) -> bool {
+      unsigned r;
+      asm volatile(
+          "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.or.pred q, 1, %2, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+          : "=r"(r)
+          : "r"((unsigned)x), "n"(N_PRODUCER_WARPS * 32)
+          : "memory");
+      return r != 0;
+    };
     // one ring slot: wait until it is free, weight slab (or nothing for a marker), flags
     auto open_stage = [&](int k, int slice, int flags, bool marker) -> unsigned char * {
       if (round > 0) {
@@ -225,12 +221,13 @@ k_conv_tma(const __grid_constant__ CUtensorMap in_map, TmaParams P) {
     advance(tile_c, k_c);
     int v0 = entry(tile_a, k_a), v1 = entry(tile_b, k_b), v2;
     int issued_in_tile = 0;
-    for (long long t = 0; t < my_tiles && ok && !*sh_abort;) {
+    for (long long t = 0; t < my_tiles;) {
       v2 = entry(tile_c, k_c);
       const bool hit = (unsigned)v0 < (unsigned)P.n_in;
       if (v0 >= 0 && !hit) atomicOr(P.flags, FLAG_BAD_ROW);
       const unsigned hits = __ballot_sync(0xffffffffu, hit);
-      producer_sync();  // everybody is done with the previous offset's lists
+      // everybody is done with the previous offset's lists; stop together on a failure
+      if (producer_vote(!ok || *sh_abort)) break;
       if (lane == 0) warp_cnt[warp] = __popc(hits);
       producer_sync();
       int base = 0, total = 0;
