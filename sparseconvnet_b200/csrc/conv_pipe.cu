@@ -8,9 +8,10 @@
 //   prologue  the four warps compact the tile's rules of every filter offset (ballots over
 //             coalesced reads of the dense rulebook) into per-offset pair lists in shared memory;
 //             offsets without a rule in the tile disappear from the step list
-//   steps     one step = (offset, batch of <= 64 pairs, 32-plane chunk).  The input rows of the
-//             batch and the W[k] slab of the chunk travel with 16-byte cp.async into a ring of
-//             three stages, two steps ahead of the arithmetic; there is ONE block barrier per step
+//   steps     one step = (offset, batch of <= 64 pairs, 32-plane chunk), listed once per tile.  The
+//             input rows of the batch and the W[k] slab of the chunk travel with 16-byte cp.async
+//             into a ring of three stages, two steps ahead of the arithmetic; there is ONE block
+//             barrier per step and no per-step bookkeeping beyond two counters
 //   compute   thread = (pair group 0..15) x (plane group 0..7): PM pairs x NPL planes in registers,
 //             PM = ceil(pairs / 16) chosen per step, so every thread works whatever the fill of
 //             the tile; input values are broadcast float4 reads, W values float4 reads
@@ -31,16 +32,21 @@ constexpr int kPThreads = 128;
 constexpr int kPCap = 64;                // pairs per step
 constexpr int kPChunk = 32;              // input planes per step
 constexpr int kPAStride = kPChunk + 4;   // stage row stride (floats): 4 pair groups of a warp hit 4 bank quads
-constexpr int kPStages = 3;               // ring of gathered-row stages (rows run two steps ahead)
-constexpr int kPWStages = 2;              // ring of weight-slab stages (slabs run one step ahead)
+#ifndef SCN_PIPE_STAGES
+#define SCN_PIPE_STAGES 3
+#endif
+constexpr int kPStages = SCN_PIPE_STAGES;  // ring of stages: copies run kPStages - 1 steps ahead of the arithmetic
 constexpr int kPMaxK = 32;
+constexpr int kPMaxGroups = 2 * kPMaxK;  // (offset, batch of <= 64 pairs) groups of a tile
 
 template <int NPL>
 struct PipeSmem {
   float acc[kPRows][NPL * 8];                // tile accumulator
   float a[kPStages][kPCap][kPAStride];       // gathered input rows of a step: [pair][plane]
-  float w[kPWStages][kPChunk][NPL * 8];      // W[k][c0 .. c0+32][n0 .. n0+BN]
+  float w[kPStages][kPChunk][NPL * 8];       // W[k][c0 .. c0+32][n0 .. n0+BN]
   int cnt[kPMaxK];                           // pairs per offset
+  int groups[kPMaxGroups];                   // offset | first pair << 8 | pairs << 16, in execution order
+  int n_groups;
   // followed by: int pin[K][128] (pair -> input row), unsigned char prow[K][128] (pair -> local output row)
 };
 
@@ -48,11 +54,6 @@ static size_t pipe_smem_bytes(int npl, int K) {
   size_t fixed = npl == 4 ? sizeof(PipeSmem<4>) : sizeof(PipeSmem<8>);
   return fixed + (size_t)K * kPRows * 5;
 }
-
-struct PipeStep {
-  int k, base, c;  // offset, first pair of the batch, chunk
-  bool valid;
-};
 
 template <int PM, int NPL>
 __device__ __forceinline__ void pipe_chunk(float (&acc)[4][NPL], const float *a_thr, const float *w_thr, int kmax) {
@@ -155,92 +156,97 @@ k_conv_pipe(const float *__restrict__ in, int ld_in, long long n_in, float *__re
   }
   __syncthreads();
 
-  // ---- step list: (offset with rules, batch of <= 64 pairs, chunk), same order on both sides ------
-  const int nch = (cin + kPChunk - 1) / kPChunk;
-  auto first_step = [&]() {
-    PipeStep st{0, 0, 0, true};
-    while (st.k < K && S.cnt[st.k] == 0) ++st.k;
-    st.valid = st.k < K;
-    return st;
-  };
-  auto next_step = [&](PipeStep &st) {
-    if (!st.valid) return;
-    if (++st.c < nch) return;
-    st.c = 0;
-    st.base += kPCap;
-    if (st.base < S.cnt[st.k]) return;
-    st.base = 0;
-    ++st.k;
-    while (st.k < K && S.cnt[st.k] == 0) ++st.k;
-    st.valid = st.k < K;
-  };
-  // Two cp.async groups per call, empty or not, so wait_group's count stays fixed: the weight slab
-  // of `sw` (one step ahead of the arithmetic), then the gathered rows of `sa` (two steps ahead).
-  auto issue_w = [&](const PipeStep &st, int stage) {
-    if (st.valid) {
-      const float *wk = weight + (long long)st.k * w_offset_stride;
-      for (int q = tid; q < kPChunk * (BN / 4); q += kPThreads) {
-        const int r = q / (BN / 4), cc = (q % (BN / 4)) * 4;
-        const int ci = st.c * kPChunk + r, n = n0 + cc;
-        const bool ok = ci < cin && n < cout;
-        cp_async16(smem_u32(&S.w[stage][r][cc]), ok ? wk + (long long)ci * cout + n : weight, ok ? 16u : 0u);
-      }
+  // ---- group list: (offset with rules, batch of <= 64 pairs); lane k of warp 0 places offset k ------
+  if (warp == 0) {
+    const int c = lane < K ? S.cnt[lane] : 0;
+    const int nb = (c + kPCap - 1) / kPCap;  // 0, 1 or 2 batches
+    int incl = nb;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int o = __shfl_up_sync(kFull, incl, d);
+      if (lane >= d) incl += o;
     }
-    cp_async_commit();
-  };
-  auto issue_a = [&](const PipeStep &st, int stage) {
-    if (st.valid) {
-      const int P = min(kPCap, S.cnt[st.k] - st.base);
-      const int c = st.c * kPChunk + tx * 4;
-      if (c < cin) {
-        const int *pk = &pin[st.k][st.base];
-        for (int p = ty; p < P; p += 16)
-          cp_async16(smem_u32(&S.a[stage][p][tx * 4]), in + (long long)pk[p] * ld_in + c, 16u);
-      }
-    }
-    cp_async_commit();
-  };
+    const int first = incl - nb;
+    for (int b = 0; b < nb; ++b) S.groups[first + b] = lane | (b * kPCap) << 8 | min(kPCap, c - b * kPCap) << 16;
+    if (lane == 31) S.n_groups = incl;
+  }
+  __syncthreads();
 
-  // cp.async groups, oldest first: W(0) A(0) A(1) | W(1) A(2) | W(2) A(3) | ...  (one pair per
-  // iteration).  When step s is about to be computed the newest group is A(s+1); everything older,
-  // W(s) and A(s) included, must have landed: wait_group 1.
-  PipeStep sc = first_step(), sw = sc, sa = sc;
-  issue_w(sw, 0);  // W(0)
-  next_step(sw);
-  issue_a(sa, 0);  // A(0)
-  next_step(sa);
-  issue_a(sa, 1);  // A(1)
-  next_step(sa);
+  // ---- steps: (group, 32-plane chunk), flattened; copies of step s+2 are issued during step s ------
+  const int nch = (cin + kPChunk - 1) / kPChunk;
+  const int n_steps = S.n_groups * nch;
+  constexpr int PPR = BN / 4;               // 16-byte pieces per W row
+  constexpr int RSTEP = kPThreads / PPR;    // W rows per pass of the CTA
+  const int w_cc = (tid % PPR) * 4, w_r0 = tid / PPR;
+  const bool w_col_ok = n0 + w_cc < cout;
+  const long long w_thr = (long long)w_r0 * cout + n0 + w_cc;
+  // one cp.async group per call, empty or not, so wait_group's count stays fixed
+  auto issue = [&](int g, int c, int stage) {
+    if (g < S.n_groups) {
+      const int d = S.groups[g];
+      const int k = d & 0xFF, base = (d >> 8) & 0xFF, P = d >> 16;
+      const float *wk = weight + (long long)k * w_offset_stride + (long long)c * kPChunk * cout + w_thr;
+      const int rows_left = cin - c * kPChunk;  // W rows of this chunk that exist
+#pragma unroll
+      for (int i = 0; i < kPChunk / RSTEP; ++i) {
+        const int r = w_r0 + i * RSTEP;
+        const bool ok = w_col_ok && r < rows_left;
+        cp_async16(smem_u32(&S.w[stage][r][w_cc]), ok ? wk + (long long)i * RSTEP * cout : weight, ok ? 16u : 0u);
+      }
+      const int c0 = c * kPChunk + tx * 4;
+      if (c0 < cin) {
+        const int *pk = &pin[k][base];
+        const float *col = in + c0;
+#pragma unroll
+        for (int i = 0; i < kPCap / 16; ++i) {
+          const int p = ty + 16 * i;
+          if (p < P) cp_async16(smem_u32(&S.a[stage][p][tx * 4]), col + (long long)pk[p] * ld_in, 16u);
+        }
+      }
+    }
+    cp_async_commit();
+  };
+  int gi = 0, ci = 0;  // next step to issue
+  auto advance_issue = [&] {
+    if (++ci == nch) {
+      ci = 0;
+      ++gi;
+    }
+  };
+#pragma unroll
+  for (int st = 0; st < kPStages - 1; ++st) {
+    issue(gi, ci, st);
+    advance_issue();
+  }
 
   float acc[4][NPL];
-  int stage = 0, wstage = 0;
-  while (sc.valid) {
-    cp_async_wait<1>();
-    __syncthreads();  // the step's data has landed for every thread; the previous step is consumed
-    issue_w(sw, wstage ^ 1);
-    next_step(sw);
-    issue_a(sa, stage == 0 ? kPStages - 1 : stage - 1);
-    next_step(sa);
+  int stage = 0, gc = 0, c = 0;  // stage, group and chunk of the step being computed
+  for (int s = 0; s < n_steps; ++s) {
+    cp_async_wait<kPStages - 2>();  // all but the newest kPStages - 2 groups: the copies of step s have landed
+    __syncthreads();     // ... for every thread; and the previous step is consumed
+    issue(gi, ci, stage == 0 ? kPStages - 1 : stage - 1);
+    advance_issue();
 
-    const int P = min(kPCap, S.cnt[sc.k] - sc.base);
+    const int d = S.groups[gc];
+    const int k = d & 0xFF, base = (d >> 8) & 0xFF, P = d >> 16;
     const int pm = (P + 15) >> 4;
-    const int kmax = min(kPChunk, cin - sc.c * kPChunk);
-    if (sc.c == 0) {
+    const int kmax = min(kPChunk, cin - c * kPChunk);
+    if (c == 0) {
 #pragma unroll
       for (int j = 0; j < 4; ++j)
 #pragma unroll
         for (int e = 0; e < NPL; ++e) acc[j][e] = 0.f;
     }
     const float *a_thr = &S.a[stage][ty][0];
-    const float *w_thr = &S.w[wstage][0][tx * 4];
+    const float *w_thr_s = &S.w[stage][0][tx * 4];
     switch (pm) {
-      case 1: pipe_chunk<1, NPL>(acc, a_thr, w_thr, kmax); break;
-      case 2: pipe_chunk<2, NPL>(acc, a_thr, w_thr, kmax); break;
-      case 3: pipe_chunk<3, NPL>(acc, a_thr, w_thr, kmax); break;
-      default: pipe_chunk<4, NPL>(acc, a_thr, w_thr, kmax); break;
+      case 1: pipe_chunk<1, NPL>(acc, a_thr, w_thr_s, kmax); break;
+      case 2: pipe_chunk<2, NPL>(acc, a_thr, w_thr_s, kmax); break;
+      case 3: pipe_chunk<3, NPL>(acc, a_thr, w_thr_s, kmax); break;
+      default: pipe_chunk<4, NPL>(acc, a_thr, w_thr_s, kmax); break;
     }
-    if (sc.c == nch - 1) {
-      const unsigned char *pr = &prow[sc.k][sc.base];
+    if (c == nch - 1) {
+      const unsigned char *pr = &prow[k][base];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int p = j * 16 + ty;
@@ -258,9 +264,11 @@ k_conv_pipe(const float *__restrict__ in, int ld_in, long long n_in, float *__re
         }
       }
     }
-    next_step(sc);
+    if (++c == nch) {
+      c = 0;
+      ++gc;
+    }
     stage = stage + 1 == kPStages ? 0 : stage + 1;
-    wstage ^= 1;
   }
   cp_async_wait<0>();
   __syncthreads();
