@@ -228,12 +228,86 @@ static int launch_simt(const float *in, int ld_in, long long n_in, float *out, i
   return SCN_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Thin layers (Cin <= 3, e.g. the first layer of a network: 1 or 3 input planes).  A tile of
+// gathered rows would be almost empty, so there is no tile: one thread owns one output row and
+// 32 output planes in registers.  A warp reads its 32 rows' rulebook entries coalesced (one
+// 128-byte load per filter offset), then walks the offsets in lockstep: a thread whose row has a
+// rule loads the Cin input values and adds x_c * W[k][c][:] with W read from shared memory at a
+// warp-uniform address (broadcast).
+// ---------------------------------------------------------------------------------------------
+constexpr int kThinMaxK = 32;
+constexpr int kThinPlanes = 32;
+
+__global__ void __launch_bounds__(128)
+k_conv_thin(const float *__restrict__ in, int ld_in, long long n_in, float *__restrict__ out, int ld_out,
+            long long n_out, const float *__restrict__ weight, const float *__restrict__ bias,
+            const int *__restrict__ nbr, int K, int cin, int cout, int *flags) {
+  extern __shared__ __align__(16) float w_s[];  // [K][cin][32]: planes n0 .. n0+31 of this CTA, zero padded
+  const int n0 = blockIdx.y * kThinPlanes;
+  for (int i = threadIdx.x; i < K * cin * kThinPlanes; i += blockDim.x) {
+    const int n = n0 + i % kThinPlanes, kc = i / kThinPlanes;
+    w_s[i] = n < cout ? __ldg(weight + (long long)kc * cout + n) : 0.f;
+  }
+  __syncthreads();
+  const long long row = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const bool row_ok = row < n_out;
+  int v[kThinMaxK];
+#pragma unroll
+  for (int k = 0; k < kThinMaxK; ++k) v[k] = (k < K && row_ok) ? __ldg(nbr + (long long)k * n_out + row) : -1;
+  float acc[kThinPlanes];
+#pragma unroll
+  for (int n = 0; n < kThinPlanes; ++n) acc[n] = (bias && n0 + n < cout) ? __ldg(bias + n0 + n) : 0.f;
+#pragma unroll
+  for (int k = 0; k < kThinMaxK; ++k) {
+    if (k >= K) break;
+    int idx = v[k];
+    if (idx >= n_in) {
+      atomicOr(flags, FLAG_BAD_ROW);
+      idx = -1;
+    }
+    if (idx < 0) continue;
+    const float *src = in + (long long)idx * ld_in;
+    for (int c = 0; c < cin; ++c) {
+      const float x = __ldg(src + c);
+      const float4 *w4 = reinterpret_cast<const float4 *>(w_s + (k * cin + c) * kThinPlanes);
+#pragma unroll
+      for (int q = 0; q < kThinPlanes / 4; ++q) {
+        const float4 w = w4[q];
+        acc[4 * q + 0] = fmaf(x, w.x, acc[4 * q + 0]);
+        acc[4 * q + 1] = fmaf(x, w.y, acc[4 * q + 1]);
+        acc[4 * q + 2] = fmaf(x, w.z, acc[4 * q + 2]);
+        acc[4 * q + 3] = fmaf(x, w.w, acc[4 * q + 3]);
+      }
+    }
+  }
+  if (!row_ok) return;
+  float *dst = out + row * ld_out + n0;
+#pragma unroll
+  for (int n = 0; n < kThinPlanes; ++n)
+    if (n0 + n < cout) dst[n] = acc[n];
+}
+
+static bool conv_thin_supported(int K, int cin, int groups) { return cin <= 3 && K <= kThinMaxK && groups == 1; }
+
+static int conv_forward_thin(const float *in, long long n_in, float *out, long long n_out, const float *weight,
+                             const float *bias, const int *table, int K, int cin, int cout, int *flags,
+                             cudaStream_t stream) {
+  const size_t smem = (size_t)K * cin * kThinPlanes * sizeof(float);  // <= 16 KB
+  dim3 grid((unsigned)ceil_div(n_out, 128), (unsigned)ceil_div(cout, kThinPlanes));
+  SCN_LAUNCH(k_conv_thin, grid, 128, smem, stream, in, cin, n_in, out, cout, n_out, weight, bias, table, K, cin, cout, flags);
+  SCN_CUDA_CHECK(cudaGetLastError());
+  return SCN_OK;
+}
+
 // out [n_out, groups*cout] = bias + sum_k in[table[k][.]] @ W[k]; cin / cout are per group.
 int conv_forward_simt(const float *in, long long n_in, float *out, long long n_out, const float *weight,
                       const float *bias, const int *table, int K, int cin, int cout, int groups,
                       int *flags, cudaStream_t stream) {
   if (n_out == 0) return SCN_OK;
-  static const bool block_kernel_only = getenv("SCN_SIMT_BLOCK") && atoi(getenv("SCN_SIMT_BLOCK")) != 0;
+  const bool block_kernel_only = getenv("SCN_SIMT_BLOCK") && atoi(getenv("SCN_SIMT_BLOCK")) != 0;
+  if (!block_kernel_only && conv_thin_supported(K, cin, groups))
+    return conv_forward_thin(in, n_in, out, n_out, weight, bias, table, K, cin, cout, flags, stream);
   if (!block_kernel_only && conv_pipe_supported(in, out, weight, bias, K, cin, cout))
     return conv_forward_pipe(in, n_in, out, n_out, weight, bias, table, K, cin, cout, groups, flags, stream);
   int ld_in = cin * groups, ld_out = cout * groups;
