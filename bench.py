@@ -32,9 +32,11 @@ CONFIG = 3
 ROOMS_PER_GPU = 8
 METRIC = "unet3d_voxels_per_sec"
 UNIT = "voxels/s"
-# DRAM bytes per launch of the dominant kernel from the committed ncu capture, as a multiple
-# of the algorithmic bytes of that launch (profiles/); None until a capture is committed.
-TRAFFIC_RATIO = None
+# DRAM bytes per launch of the dominant kernel (k_conv_tma) as a multiple of the algorithmic bytes
+# of that launch: 75 MB measured against 343 MB counted per launch in the 4-room capture
+# (profiles/k_conv_tma_tf32x3_unet3d_4rooms.md); the traffic grows with the rows, like the
+# algorithmic bytes.  Only applied when that kernel is the dominant one.
+TRAFFIC_RATIO = 0.22
 
 
 def workload_name(rooms=ROOMS_PER_GPU):
@@ -335,7 +337,7 @@ def main():
                            "rules_strided": "k_strided_*", "input_hash": "k_insert_input"}.get(top, top),
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "peak_source": peak_src,
-                "traffic": (TRAFFIC_RATIO * a["bytes"] / a["calls"]) if TRAFFIC_RATIO else None,
+                "traffic": (TRAFFIC_RATIO * a["bytes"] / a["calls"]) if (TRAFFIC_RATIO and top == "k_conv_tma") else None,
                 "algorithmic_bytes_per_step": a["bytes"], "launches_per_step": a["calls"], "ms_per_step": a["ms"],
                 "tflops": a["flops"] / (a["ms"] / 1e3) / 1e12 if a["flops"] else None}
     breakdown = {k: {"ms": round(v["ms"], 4), "calls": v["calls"],
