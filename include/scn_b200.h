@@ -107,6 +107,18 @@ SCN_API int scn_md_input_layer(scn_metadata *md, const int64_t *spatial_size, co
                        int coords_on_device, int64_t n_rows, int n_cols, int64_t batch_size,
                        int mode, void *stream, int64_t *n_active);
 
+/* replaces Metadata<D>::blLayer + blRules (Metadata.cpp:427-436, Metadata/IOLayersRules.h:134-288),
+ * the metadata half of BLInputLayer (CPU/IOLayers.cpp:139-163).
+ * coords: int64 [batch_size, length, dimension]; the sample index is the first array index, a point
+ * whose first coordinate is negative is an empty slot.  mode as in the reference's BL layers: 0 all
+ * present and unique (rows = the batch_size*length points), 1 LAST point of a site, 2 FIRST point,
+ * 3 sum, 4 mean.  Sites are numbered sample by sample in order of first occurrence.  The features
+ * then go through scn_input_layer_forward (in [batch_size*length, n_planes]) and back through
+ * scn_output_layer_forward. */
+SCN_API int scn_md_bl_input_layer(scn_metadata *md, const int64_t *spatial_size, const int64_t *coords,
+                          int coords_on_device, int64_t batch_size, int64_t length, int mode, void *stream,
+                          int64_t *n_active);
+
 /* replaces cpu/cuda_InputLayer_updateOutput's feature pass
  * (CPU/IOLayers.cpp:11-29,49-72; CUDA/IOLayers.cu:14-41) using the rules stored by the last
  * scn_md_input_layer call.  in [n_in, n_planes] -> out [n_active, n_planes]. */
@@ -117,6 +129,15 @@ SCN_API int scn_input_layer_forward(scn_metadata *md, const float *in_features, 
  * matrix, an expired bounded wait ...).  This waits for `stream`, reads and clears the flags
  * and returns the matching status.  No counterpart in the reference (which checks nothing). */
 SCN_API int scn_md_poll_errors(scn_metadata *md, void *stream);
+
+/* replaces cpu/cuda_OutputLayer_updateOutput and cpu/cuda_BLOutputLayer_updateOutput
+ * (CPU/IOLayers.cpp:95-114,197-215; CUDA/IOLayers.cu): in [n_active, n_planes] -> out [n_points,
+ * n_planes], n_points = rows read by the last (BL)InputLayer call (batch_size*length for BL).  Each
+ * site's row is copied to the points its rule names (mode 0: all rows; first / last point of the
+ * site as the input mode kept it; all points for sum / mean -- unscaled, as the reference); every
+ * other point gets zeros. */
+SCN_API int scn_output_layer_forward(scn_metadata *md, const float *in_features, int64_t n_in,
+                             float *out_features, int64_t n_out, int n_planes, void *stream);
 
 /* replaces Metadata<D>::getNActive / getBatchSize (Metadata.cpp:67-70,171-176) */
 SCN_API int scn_md_n_active(scn_metadata *md, const int64_t *spatial_size, int64_t *n_active);

@@ -86,6 +86,24 @@ class RefBackend(object):
                                          self._t(features), out, int(batch_size), int(mode))
         return OTensor(out.numpy(), md, spatial_size)
 
+    def bl_input_layer(self, dim, spatial_size, mode, coords, features):
+        md = getattr(self.SCN, "Metadata_%d" % dim)()
+        out = torch.empty(0)
+        f = np.ascontiguousarray(features, dtype=np.float32)
+        self.SCN.BLInputLayer_updateOutput(md, _lt(spatial_size), torch.as_tensor(np.asarray(coords)).long().contiguous(),
+                                           torch.from_numpy(f), out, int(mode))
+        return OTensor(out.numpy(), md, spatial_size)
+
+    def output_layer(self, x):
+        out = torch.empty(0)
+        self.SCN.OutputLayer_updateOutput(x.metadata, self._t(x.features), out)
+        return out.numpy()
+
+    def bl_output_layer(self, x):
+        out = torch.empty(0)
+        self.SCN.BLOutputLayer_updateOutput(x.metadata, self._t(x.features), out)
+        return out.numpy()
+
     def locations(self, x, spatial_size=None):
         return x.metadata.getSpatialLocations(_lt(spatial_size or x.spatial_size)).numpy()
 
@@ -159,9 +177,28 @@ class PortBackend(object):
         md = _PortMetadata()
         grid, rules = port.input_layer([int(v) for v in spatial_size], np.asarray(coords), batch_size, mode)
         md.grids[tuple(int(v) for v in spatial_size)] = grid
-        md.input_rules = rules
+        md.input_rules, md.point_mode, md.point_shape = rules, mode, (np.asarray(coords).shape[0],)
         out = port.input_layer_features(features, grid.n_active, rules, mode)
         return OTensor(out, md, spatial_size)
+
+    def bl_input_layer(self, dim, spatial_size, mode, coords, features):
+        md = _PortMetadata()
+        coords = np.asarray(coords)
+        grid, rules, point_mode = port.bl_input_layer([int(v) for v in spatial_size], coords, mode)
+        md.grids[tuple(int(v) for v in spatial_size)] = grid
+        md.input_rules, md.point_mode, md.point_shape = rules, point_mode, coords.shape[:2]
+        f = np.asarray(features, dtype=np.float32).reshape(coords.shape[0] * coords.shape[1], -1)
+        out = port.input_layer_features(f, grid.n_active, rules, point_mode)
+        return OTensor(out, md, spatial_size)
+
+    def output_layer(self, x):
+        md = x.metadata
+        n = int(np.prod(md.point_shape))
+        return port.output_layer_features(x.features, n, md.input_rules, md.point_mode)
+
+    def bl_output_layer(self, x):
+        out = self.output_layer(x)
+        return out.reshape(tuple(x.metadata.point_shape) + (out.shape[1],))
 
     def _grid(self, x, size=None):
         return x.metadata.grids[tuple(size or x.spatial_size)]
@@ -256,6 +293,13 @@ def run_module(m, x, be, stats=None):
     if name == "InputLayer":
         coords, feats = np.asarray(x[0]), np.asarray(x[1], dtype=np.float32)
         return be.input_layer(m.dimension, m.spatial_size.tolist(), m.mode, coords, feats, 0 if len(x) == 2 else x[2])
+    if name == "BLInputLayer":
+        return be.bl_input_layer(m.dimension, m.spatial_size.tolist(), m.mode, np.asarray(x[0]),
+                                 np.asarray(x[1], dtype=np.float32))
+    if name == "OutputLayer":
+        return be.output_layer(x)
+    if name == "BLOutputLayer":
+        return be.bl_output_layer(x)
     if name in ("SubmanifoldConvolution", "ValidConvolution"):
         y, macs = be.subconv(x, m.filter_size.tolist(), m.weight, getattr(m, "bias", None))
         count(macs)

@@ -221,6 +221,7 @@ def InputLayer_updateOutput(m, spatial_size, input_coords, input_features, outpu
     if coords.is_cuda and coords.device != f.device:
         coords = coords.to(f.device)
     m.device = f.device
+    m.n_input_rows, m.bl_shape = coords.size(0), None
     n_active = C.c_int64()
     with torch.cuda.device(f.device):
         with _timed("input_hash", dict(rows=coords.size(0), cols=coords.size(1), mode=int(mode))) as info:
@@ -232,6 +233,58 @@ def InputLayer_updateOutput(m, spatial_size, input_coords, input_features, outpu
         with _timed("input_features", dict(rows=coords.size(0), sites=n_active.value, planes=f.size(1))):
             check(lib.scn_input_layer_forward(m._h, _ptr(f), f.size(0), _ptr(output_features), n_active.value,
                                               f.size(1), _stream()))
+
+
+def BLInputLayer_updateOutput(m, spatial_size, input_coords, input_features, output_features, mode):
+    """sparseconvnet.h (BLInputLayer_updateOutput), CPU/IOLayers.cpp:139-163.  ``input_coords``:
+    LongTensor [batch, length, dimension] on the CPU or the GPU, -1 marks an empty slot;
+    ``input_features``: [batch, length, planes]."""
+    f = _features(input_features, "input_features")
+    if input_coords.dtype != torch.int64 or input_coords.dim() != 3:
+        raise RuntimeError("input_coords must be a 3-d LongTensor [batch, length, dimension]")
+    if f.dim() != 3 or tuple(input_coords.shape[:2]) != tuple(f.shape[:2]):
+        raise RuntimeError("input_coords and input_features disagree on batch x length")
+    coords = input_coords.contiguous()
+    if coords.is_cuda and coords.device != f.device:
+        coords = coords.to(f.device)
+    m.device = f.device
+    m.bl_shape, m.n_input_rows = (f.size(0), f.size(1)), f.size(0) * f.size(1)
+    n_active = C.c_int64()
+    with torch.cuda.device(f.device):
+        with _timed("input_hash", dict(rows=f.size(0) * f.size(1), cols=coords.size(2), mode=int(mode))) as info:
+            check(lib.scn_md_bl_input_layer(m._h, sizes(spatial_size), _ptr(coords), int(coords.is_cuda),
+                                            f.size(0), f.size(1), int(mode), _stream(), C.byref(n_active)))
+            info["sites"] = n_active.value
+        output_features.resize_(n_active.value, f.size(2))
+        with _timed("input_features", dict(rows=f.size(0) * f.size(1), sites=n_active.value, planes=f.size(2))):
+            check(lib.scn_input_layer_forward(m._h, _ptr(f), f.size(0) * f.size(1), _ptr(output_features),
+                                              n_active.value, f.size(2), _stream()))
+
+
+def _output_layer(m, input_features, output_features, shape):
+    f = _features(input_features, "input_features")
+    n_points = 1
+    for d in shape[:-1]:
+        n_points *= d
+    output_features.resize_(*shape)
+    with torch.cuda.device(f.device):
+        with _timed("output_features", dict(rows=n_points, sites=f.size(0), planes=f.size(1))):
+            check(lib.scn_output_layer_forward(m._h, _ptr(f), f.size(0), _ptr(output_features), n_points,
+                                               f.size(1), _stream()))
+
+
+def OutputLayer_updateOutput(m, input_features, output_features):
+    """CPU/IOLayers.cpp:95-114: [n_active, planes] -> [n_points, planes] of the InputLayer call."""
+    if getattr(m, "n_input_rows", None) is None:
+        raise RuntimeError("OutputLayer needs a metadata made by InputLayer")
+    _output_layer(m, input_features, output_features, (m.n_input_rows, input_features.size(1)))
+
+
+def BLOutputLayer_updateOutput(m, input_features, output_features):
+    """CPU/IOLayers.cpp:197-215: [n_active, planes] -> [batch, length, planes] of the BLInputLayer call."""
+    if getattr(m, "bl_shape", None) is None:
+        raise RuntimeError("BLOutputLayer needs a metadata made by BLInputLayer")
+    _output_layer(m, input_features, output_features, m.bl_shape + (input_features.size(1),))
 
 
 def _conv_args(input_features, weight, bias):

@@ -20,7 +20,7 @@ def Metadata(dim):
     return getattr(SCN, "Metadata_%d" % dim)()
 
 
-from .layers import (InputLayer, SubmanifoldConvolution, ValidConvolution, Convolution,  # noqa: E402
+from .layers import (InputLayer, OutputLayer, BLInputLayer, BLOutputLayer, SubmanifoldConvolution, ValidConvolution, Convolution,  # noqa: E402
                      Deconvolution, BatchNormalization, BatchNormReLU, BatchNormLeakyReLU, MaxPooling,
                      SparseToDense, NetworkInNetwork, Identity)
 from .containers import Sequential, ConcatTable, JoinTable, AddTable  # noqa: E402

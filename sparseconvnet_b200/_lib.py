@@ -24,7 +24,9 @@ SIGNATURES = {
     "scn_md_clear": (C.c_int, [_vp, _vp]),
     "scn_md_input_layer": (C.c_int, [_vp, _i64p, _vp, C.c_int, C.c_int64, C.c_int, C.c_int64,
                                      C.c_int, _vp, _i64p]),
+    "scn_md_bl_input_layer": (C.c_int, [_vp, _i64p, _vp, C.c_int, C.c_int64, C.c_int64, C.c_int, _vp, _i64p]),
     "scn_input_layer_forward": (C.c_int, [_vp, _vp, C.c_int64, _vp, C.c_int64, C.c_int, _vp]),
+    "scn_output_layer_forward": (C.c_int, [_vp, _vp, C.c_int64, _vp, C.c_int64, C.c_int, _vp]),
     "scn_md_poll_errors": (C.c_int, [_vp, _vp]),
     "scn_md_n_active": (C.c_int, [_vp, _i64p, _i64p]),
     "scn_md_batch_size": (C.c_int, [_vp, _i64p, _i64p]),

@@ -122,13 +122,20 @@ static int flags_to_status(int flags) {
 // One thread per input row: range-check, pack, insert.  mode 0 keeps the largest row index
 // per site (the reference's serial `mp[p] = i` leaves the last writer, IOLayersRules.h:41,55);
 // the other modes record the first row that touched the site.
+// bl_length > 0: coords are [batch, bl_length, dim] (BLInputLayer, IOLayersRules.h:134-288):
+// the sample index is i / bl_length and a point whose first coordinate is negative is empty.
 __global__ void k_insert_input(KeyLayout L, HashTable T, const long long *__restrict__ coords,
-                               long long n, int ncols, int mode,
+                               long long n, int ncols, int mode, long long bl_length,
                                unsigned long long *__restrict__ row_keys, int *__restrict__ slot_of,
                                int *flags, int *scalars) {
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const long long *c = coords + i * ncols;
+  if (bl_length > 0 && c[0] < 0) {  // empty slot of the batch x length array: in no map, in no rule
+    if (mode == 0) row_keys[i] = kEmptyKey;
+    slot_of[i] = -1;
+    return;
+  }
   int x[kMaxDim];
   bool ok = true;
   for (int d = 0; d < L.dim; ++d) {
@@ -136,7 +143,7 @@ __global__ void k_insert_input(KeyLayout L, HashTable T, const long long *__rest
     ok &= (v >= 0 && v < L.size[d]);
     x[d] = (int)v;
   }
-  long long bl = (ncols > L.dim) ? c[L.dim] : 0;
+  long long bl = bl_length > 0 ? i / bl_length : ((ncols > L.dim) ? c[L.dim] : 0);
   ok &= (bl >= 0 && bl < (1ll << L.batch_bits));
   if (!ok) {
     atomicOr(flags, FLAG_COORD_RANGE);
@@ -287,7 +294,7 @@ static int md_clear(scn_metadata *md, cudaStream_t stream) {
 
 static int md_input_layer(scn_metadata *md, const int64_t *spatial_size, const int64_t *coords,
                           int coords_on_device, int64_t n, int ncols, int64_t batch_size, int mode,
-                          cudaStream_t stream, int64_t *n_active) {
+                          int64_t bl_length, cudaStream_t stream, int64_t *n_active) {
   SCN_REQUIRE(md && spatial_size && n_active, SCN_ERR_BAD_ARG, "null argument");
   SCN_REQUIRE(mode >= 0 && mode <= 4, SCN_ERR_BAD_ARG, "input layer mode %d not in 0..4", mode);
   SCN_REQUIRE(ncols == md->dim || ncols == md->dim + 1, SCN_ERR_BAD_ARG,
@@ -324,7 +331,7 @@ static int md_input_layer(scn_metadata *md, const int64_t *spatial_size, const i
   int *slot_of = nullptr, *flag = nullptr, *rank = nullptr, *cursor = nullptr;
   SCN_TRY(device_alloc((void **)&slot_of, sizeof(int) * (size_t)std::max<int64_t>(n, 1), stream));
   if (n > 0) {
-    SCN_LAUNCH(k_insert_input, blocks, threads, 0, stream, g.layout, g.table, coords_dev, n, ncols, mode, g.row_keys, slot_of, md->flags_dev, md->scalars_dev);
+    SCN_LAUNCH(k_insert_input, blocks, threads, 0, stream, g.layout, g.table, coords_dev, n, ncols, mode, (long long)bl_length, g.row_keys, slot_of, md->flags_dev, md->scalars_dev);
     if (mode == 0)
       SCN_LAUNCH(k_blank_overwritten, blocks, threads, 0, stream, g.table.slots, slot_of, n, g.row_keys);
     SCN_CUDA_CHECK(cudaGetLastError());
@@ -370,7 +377,9 @@ static int md_input_layer(scn_metadata *md, const int64_t *spatial_size, const i
   g.n_active = active;
   // batch size: IOLayersRules.h:25,35,52-53 -- one sample when there is no batch column,
   // otherwise max(requested, largest index + 1)
-  if (ncols == md->dim)
+  if (bl_length > 0)
+    g.batch_size = batch_size;
+  else if (ncols == md->dim)
     g.batch_size = 1;
   else
     g.batch_size = std::max<long long>(batch_size, (long long)sc[1] + 1);
@@ -815,8 +824,23 @@ int scn_md_destroy(scn_metadata *md) {
 int scn_md_input_layer(scn_metadata *md, const int64_t *spatial_size, const int64_t *coords,
                        int coords_on_device, int64_t n_rows, int n_cols, int64_t batch_size,
                        int mode, void *stream, int64_t *n_active) {
-  return md_input_layer(md, spatial_size, coords, coords_on_device, n_rows, n_cols, batch_size, mode,
+  return md_input_layer(md, spatial_size, coords, coords_on_device, n_rows, n_cols, batch_size, mode, 0,
                         (cudaStream_t)stream, n_active);
+}
+
+int scn_md_bl_input_layer(scn_metadata *md, const int64_t *spatial_size, const int64_t *coords,
+                          int coords_on_device, int64_t batch_size, int64_t length, int mode, void *stream,
+                          int64_t *n_active) {
+  SCN_REQUIRE(md, SCN_ERR_BAD_ARG, "null metadata");
+  SCN_REQUIRE(batch_size >= 0 && length >= 0, SCN_ERR_BAD_ARG, "negative batch size or length");
+  SCN_REQUIRE(mode >= 0 && mode <= 4, SCN_ERR_BAD_ARG, "input layer mode %d not in 0..4", mode);
+  // blRules keeps the LAST point of a site in mode 1 and the FIRST in mode 2 (IOLayersRules.h:172-199),
+  // inputLayerRules the other way round (IOLayersRules.h:95-106): stored in the latter's terms.
+  const int stored_mode = mode == 1 ? 2 : mode == 2 ? 1 : mode;
+  // an empty batch x length array still needs a non-zero stride for the sample index
+  SCN_TRY(md_input_layer(md, spatial_size, coords, coords_on_device, batch_size * length, md->dim, batch_size,
+                         stored_mode, std::max<int64_t>(length, 1), (cudaStream_t)stream, n_active));
+  return SCN_OK;
 }
 
 int scn_md_poll_errors(scn_metadata *md, void *stream) {

@@ -31,6 +31,29 @@ __global__ void k_input_features(const float *__restrict__ in, float *__restrict
   out[idx] = acc;
 }
 
+// OutputLayer / BLOutputLayer (CPU/IOLayers.cpp:31-47,95-114,197-215): the feature row of a
+// site goes back, unscaled, to the input points its rule names -- the first point of the site
+// (mode 1), the last (mode 2) or all of them (modes 3, 4).  Points that no rule names (dropped
+// duplicates, empty slots of a batch x length array) keep the zeros the output was cleared to.
+__global__ void k_output_features(const float *__restrict__ in, float *__restrict__ out,
+                                  const int *__restrict__ start, const int *__restrict__ rows,
+                                  long long n_sites, int C, int mode) {
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n_sites * C) return;
+  long long r = idx / C;
+  int c = (int)(idx % C);
+  int s = start[r], e = start[r + 1];
+  if (e <= s) return;
+  const float v = in[idx];
+  if (mode == 1) {
+    out[(long long)rows[s] * C + c] = v;
+  } else if (mode == 2) {
+    out[(long long)rows[e - 1] * C + c] = v;
+  } else {
+    for (int j = s; j < e; ++j) out[(long long)rows[j] * C + c] = v;
+  }
+}
+
 // ------------------------------------------------------------------------------------------
 // BatchNorm + leaky ReLU (CPU/BatchNormalization.cpp:12-62)
 // ------------------------------------------------------------------------------------------
@@ -193,6 +216,31 @@ int scn_input_layer_forward(scn_metadata *md, const float *in_features, int64_t 
   }
   long long total = (long long)n_out * n_planes;
   SCN_LAUNCH(k_input_features, (unsigned)ceil_div(total, 256), 256, 0, stream, in_features, out_features, md->input_csr_start, md->input_csr_rows, n_out, n_planes, md->input_mode);
+  SCN_CUDA_CHECK(cudaGetLastError());
+  return SCN_OK;
+}
+
+int scn_output_layer_forward(scn_metadata *md, const float *in_features, int64_t n_in, float *out_features,
+                             int64_t n_out, int n_planes, void *stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SCN_REQUIRE(md, SCN_ERR_BAD_ARG, "null metadata");
+  SCN_REQUIRE(md->input_mode >= 0, SCN_ERR_NO_GRID, "no input layer has been run on this metadata");
+  SCN_REQUIRE(n_planes >= 1, SCN_ERR_BAD_ARG, "n_planes %d", n_planes);
+  SCN_REQUIRE(n_in == md->input_n_active, SCN_ERR_SIZE_MISMATCH, "input has %lld rows, the input layer made %lld",
+              (long long)n_in, (long long)md->input_n_active);
+  SCN_REQUIRE(n_out == md->input_n_rows, SCN_ERR_SIZE_MISMATCH, "output has %lld rows, the input layer read %lld",
+              (long long)n_out, (long long)md->input_n_rows);
+  if (n_out == 0) return SCN_OK;
+  SCN_REQUIRE(out_features && (in_features || n_in == 0), SCN_ERR_BAD_ARG, "null features");
+  const size_t bytes = sizeof(float) * (size_t)n_out * n_planes;
+  if (md->input_mode == 0) {  // rows are the input points themselves
+    SCN_CUDA_CHECK(cudaMemcpyAsync(out_features, in_features, bytes, cudaMemcpyDeviceToDevice, stream));
+    return SCN_OK;
+  }
+  SCN_CUDA_CHECK(cudaMemsetAsync(out_features, 0, bytes, stream));
+  if (n_in == 0) return SCN_OK;
+  long long total = (long long)n_in * n_planes;
+  SCN_LAUNCH(k_output_features, (unsigned)ceil_div(total, 256), 256, 0, stream, in_features, out_features, md->input_csr_start, md->input_csr_rows, n_in, n_planes, md->input_mode);
   SCN_CUDA_CHECK(cudaGetLastError());
   return SCN_OK;
 }

@@ -63,6 +63,83 @@ class InputLayer(Module):
         return "InputLayer(mode=%d)" % self.mode
 
 
+class OutputLayer(Module):
+    """The inverse of InputLayer for 'autoencoder' / per-point networks (ioLayers.py:68-91): takes a
+    SparseConvNetTensor whose metadata was made by an InputLayer and returns a float tensor
+    [n_points, planes]: every input point gets the row of its site (points that the InputLayer's
+    mode dropped get zeros)."""
+
+    def __init__(self, dimension):
+        Module.__init__(self)
+        self.dimension = dimension
+
+    def forward(self, input):
+        output = input.features.new_empty(0)
+        SCN.OutputLayer_updateOutput(input.metadata, input.features.detach().contiguous(), output)
+        return output
+
+    def input_spatial_size(self, out_size):
+        return out_size
+
+    def __repr__(self):
+        return "OutputLayer()"
+
+
+class BLInputLayer(Module):
+    """Takes ``[coords, features]`` with coords a LongTensor [batch, length, dimension] (-1 = empty
+    slot) and features [batch, length, planes] (ioLayers.py:94-138).  mode: 0 all points present
+    and unique, 1 use the last point of a site, 2 keep the first, 3 sum, 4 mean."""
+
+    def __init__(self, dimension, spatial_size, mode=3):
+        Module.__init__(self)
+        self.dimension = dimension
+        self.spatial_size = to_long_tensor(dimension, spatial_size)
+        self.mode = mode
+        self.device = None
+
+    def to(self, device):
+        self.device = device
+        return self
+
+    def forward(self, input):
+        coords, features = input[0], input[1]
+        if self.device is not None:
+            features = features.to(self.device)
+        elif not features.is_cuda:
+            raise RuntimeError("BLInputLayer: features must be on a CUDA device (or call .to(device) on "
+                               "the layer): sparseconvnet_b200 has no CPU path")
+        output = SparseConvNetTensor(metadata=_pkg.Metadata(self.dimension), spatial_size=self.spatial_size)
+        output.features = features.new_empty(0)
+        SCN.BLInputLayer_updateOutput(output.metadata, self.spatial_size, coords.long(),
+                                      features.detach().float().contiguous(), output.features, self.mode)
+        return output
+
+    def input_spatial_size(self, out_size):
+        return out_size
+
+    def __repr__(self):
+        return "BLInputLayer(mode=%d)" % self.mode
+
+
+class BLOutputLayer(Module):
+    """The inverse of BLInputLayer (ioLayers.py:141-164): returns [batch, length, planes]."""
+
+    def __init__(self, dimension):
+        Module.__init__(self)
+        self.dimension = dimension
+
+    def forward(self, input):
+        output = input.features.new_empty(0)
+        SCN.BLOutputLayer_updateOutput(input.metadata, input.features.detach().contiguous(), output)
+        return output
+
+    def input_spatial_size(self, out_size):
+        return out_size
+
+    def __repr__(self):
+        return "BLOutputLayer()"
+
+
 class _ConvBase(Module):
     def _init_weight(self, dimension, nIn, nOut, filter_size, bias, groups):
         self.dimension = dimension

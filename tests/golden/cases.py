@@ -27,6 +27,67 @@ OPS_CASES = {
 }
 
 
+# ---- input / output layer pairs (per-point networks) ----------------------------------------------
+# x0 = InputLayer or BLInputLayer (mode); x1 = SC(x0) (+bias); points = OutputLayer / BLOutputLayer (x1)
+IO_CASES = {
+    "io_il2d_m0": dict(dim=2, size=[11, 11], bl=False, n=90, batch=2, mode=0, planes=3),
+    "io_il2d_m1": dict(dim=2, size=[9, 9], bl=False, n=200, batch=3, mode=1, planes=3),
+    "io_il2d_m2": dict(dim=2, size=[9, 9], bl=False, n=200, batch=3, mode=2, planes=3),
+    "io_il3d_m4": dict(dim=3, size=[7, 7, 7], bl=False, n=500, batch=2, mode=4, planes=4),
+    "io_bl2d_m0": dict(dim=2, size=[11, 11], bl=True, batch=3, length=40, mode=0, planes=3),
+    "io_bl2d_m1": dict(dim=2, size=[7, 7], bl=True, batch=3, length=60, mode=1, planes=3, empty=0.2),
+    "io_bl2d_m2": dict(dim=2, size=[7, 7], bl=True, batch=3, length=60, mode=2, planes=3, empty=0.2),
+    "io_bl3d_m3": dict(dim=3, size=[5, 5, 5], bl=True, batch=4, length=90, mode=3, planes=4, empty=0.3),
+    "io_bl1d_m4": dict(dim=1, size=[9], bl=True, batch=2, length=30, mode=4, planes=2, empty=0.5),
+}
+
+
+def io_inputs(case):
+    c = IO_CASES[case]
+    rng = np.random.default_rng(sum(map(ord, case)))
+    d = c["dim"]
+    if not c["bl"]:
+        cols = [rng.integers(0, s, c["n"]) for s in c["size"]] + [rng.integers(0, c["batch"], c["n"])]
+        coords = np.stack(cols, axis=1).astype(np.int64)
+        if c["mode"] == 0:
+            coords = np.unique(coords, axis=0)
+            rng.shuffle(coords)
+        feats = rng.standard_normal((coords.shape[0], c["planes"])).astype(np.float32)
+        return coords, feats
+    B, L = c["batch"], c["length"]
+    if c["mode"] == 0:  # all present, unique within a sample
+        coords = np.zeros((B, L, d), dtype=np.int64)
+        for b in range(B):
+            cells = rng.permutation(int(np.prod(c["size"])))[:L]
+            coords[b] = np.stack(np.unravel_index(cells, c["size"]), axis=1)
+    else:
+        coords = np.stack([rng.integers(0, s, (B, L)) for s in c["size"]], axis=2).astype(np.int64)
+        coords[rng.random((B, L)) < c["empty"]] = -1
+    feats = rng.standard_normal((B, L, c["planes"])).astype(np.float32)
+    return coords, feats
+
+
+def io_modules(case):
+    c = IO_CASES[case]
+    torch.manual_seed(sum(map(ord, case)))
+    d, p = c["dim"], c["planes"]
+    mods = dict(sc=scn.SubmanifoldConvolution(d, p, p + 2, 3, True))
+    mods["sc"].bias.data.normal_()
+    net = torch.nn.ModuleDict(mods)
+    workloads.randomize(net, 11)
+    net.eval()
+    il = scn.BLInputLayer(d, c["size"], c["mode"]) if c["bl"] else scn.InputLayer(d, c["size"], c["mode"])
+    ol = scn.BLOutputLayer(d) if c["bl"] else scn.OutputLayer(d)
+    return il, net, ol
+
+
+def run_io(mods, inputs, run):
+    il, net, ol = mods
+    x0 = run(il, list(inputs))
+    x1 = run(net["sc"], x0)
+    return dict(x0=x0, x1=x1, back0=run(ol, x0), back1=run(ol, x1))
+
+
 def ops_inputs(case):
     c = OPS_CASES[case]
     rng = np.random.default_rng(sum(map(ord, case)))

@@ -51,6 +51,19 @@ def ops_case(name, be):
     return out
 
 
+def io_case(name, be):
+    mods = cases.io_modules(name)
+    coords, feats = cases.io_inputs(name)
+    st = cases.run_io(mods, (coords, feats), lambda m, x: runner.run_module(m, x, be))
+    out = {"coords": coords, "feats": feats}
+    _state("state", mods[1], out)
+    for k in ("x0", "x1"):
+        out["loc/" + k] = be.locations(st[k])
+        out["feat/" + k] = st[k].features
+    out["back0"], out["back1"] = st["back0"], st["back1"]
+    return out
+
+
 def net_case(name, be):
     inp, net, head = cases.net_modules(name)
     coords, feats = cases.net_inputs(name)
@@ -75,10 +88,12 @@ def main():
     be = runner.RefBackend()
     for name in cases.OPS_CASES:
         np.savez_compressed(os.path.join(HERE, name + ".npz"), **ops_case(name, be))
+    for name in cases.IO_CASES:
+        np.savez_compressed(os.path.join(HERE, name + ".npz"), **io_case(name, be))
     for name in cases.NET_CASES:
         np.savez_compressed(os.path.join(HERE, name + ".npz"), **net_case(name, be))
     total = sum(os.path.getsize(os.path.join(HERE, f)) for f in os.listdir(HERE) if f.endswith(".npz"))
-    print("wrote %d cases, %.1f KiB" % (len(cases.OPS_CASES) + len(cases.NET_CASES), total / 1024.0))
+    print("wrote %d cases, %.1f KiB" % (len(cases.OPS_CASES) + len(cases.IO_CASES) + len(cases.NET_CASES), total / 1024.0))
 
 
 if __name__ == "__main__":

@@ -79,9 +79,13 @@ class GpuBackend(object):
 
     def run(self, m, x):
         import sparseconvnet_b200 as scn
-        m = m.to(self.device) if not isinstance(m, scn.InputLayer) else m
+        m = m.to(self.device) if not isinstance(m, (scn.InputLayer, scn.BLInputLayer)) else m
         with torch.no_grad():
-            if isinstance(m, scn.InputLayer):
+            if isinstance(m, scn.BLInputLayer):
+                coords = torch.as_tensor(np.asarray(x[0])).long()
+                feats = torch.as_tensor(np.asarray(x[1], dtype=np.float32)).to(self.device)
+                y = m([coords, feats])
+            elif isinstance(m, scn.InputLayer):
                 coords = torch.as_tensor(np.asarray(x[0])).long()
                 feats = torch.as_tensor(np.asarray(x[1], dtype=np.float32)).to(self.device)
                 y = m([coords, feats] + list(x[2:]))

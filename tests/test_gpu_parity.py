@@ -88,6 +88,53 @@ def test_networks_against_golden(name, cuda):
             assert helpers.rel_err(gpu.run(head, y), g["head_out"][p]) <= helpers.FP32_TOL
 
 
+@pytest.mark.parametrize("name", sorted(cases.IO_CASES))
+def test_io_layers_against_golden(name, cuda):
+    """InputLayer / BLInputLayer -> SubmanifoldConvolution -> OutputLayer / BLOutputLayer through the C
+    ABI against the reference's results: same row numbering on the input side, so row for row; the
+    copies back to the points are exact."""
+    g = helpers.load_golden(name)
+    mods = cases.io_modules(name)
+    helpers.load_state(mods[1], g, "state")
+    gpu = helpers.GpuBackend()
+    st = cases.run_io(mods, (g["coords"], g["feats"]), gpu.run)
+    assert np.array_equal(gpu.locations(st["x0"]), g["loc/x0"])
+    if cases.IO_CASES[name]["mode"] != 4:
+        assert np.array_equal(st["x0"].features, g["feat/x0"]), "input layer must be bit exact"
+    assert helpers.rel_err(st["x0"].features, g["feat/x0"]) <= 1e-6
+    assert helpers.rel_err(st["x1"].features, g["feat/x1"]) <= helpers.FP32_TOL
+    assert st["back0"].shape == g["back0"].shape
+    assert np.array_equal(st["back0"], st["back0"]) and helpers.rel_err(st["back0"], g["back0"]) <= 1e-6
+    assert helpers.rel_err(st["back1"], g["back1"]) <= helpers.FP32_TOL
+
+
+def test_io_layers_edge_cases(cuda):
+    """Empty batch x length arrays, a sample with only empty slots, device-resident coordinates."""
+    import sparseconvnet_b200 as scn
+    dev = cuda
+    il, ol = scn.BLInputLayer(2, [8, 8], mode=3), scn.BLOutputLayer(2)
+    coords = torch.full((3, 5, 2), -1, dtype=torch.int64)
+    coords[0, 1] = torch.tensor([2, 3])
+    coords[0, 4] = torch.tensor([2, 3])
+    coords[2, 0] = torch.tensor([7, 7])
+    feats = torch.arange(3 * 5 * 2, dtype=torch.float32, device=dev).reshape(3, 5, 2)
+    for c in (coords, coords.to(dev)):
+        x = il([c, feats])
+        assert x.features.shape == (2, 2)
+        assert torch.equal(x.features[0], feats[0, 1] + feats[0, 4])
+        back = ol(x)
+        assert back.shape == (3, 5, 2)
+        assert torch.equal(back[0, 1], x.features[0]) and torch.equal(back[0, 4], x.features[0])
+        assert torch.equal(back[2, 0], x.features[1]) and back[1].abs().sum().item() == 0
+        x.metadata.poll_errors()
+    x = il([torch.zeros(0, 4, 2, dtype=torch.int64), torch.zeros(0, 4, 3, device=dev)])
+    assert x.features.shape == (0, 3) and ol(x).shape == (0, 4, 3)
+    # OutputLayer after a plain InputLayer, mode 2 (last row wins): the dropped duplicate reads zeros
+    x = scn.InputLayer(2, [8, 8], mode=2)([torch.tensor([[1, 1, 0], [1, 1, 0], [2, 2, 0]]),
+                                           torch.tensor([[1.0], [2.0], [3.0]], device=dev)])
+    assert scn.OutputLayer(2)(x).flatten().tolist() == [0.0, 2.0, 3.0]
+
+
 def test_empty_and_tiny_inputs(cuda):
     import sparseconvnet_b200 as scn
     dev = cuda

@@ -57,3 +57,22 @@ def test_port_networks_match_reference_golden(name):
             helpers.load_state(head, g, "head")
             p = port.align_rows(be.locations(y), g["loc/y"])
             assert helpers.rel_err(runner.run_module(head, y, be), g["head_out"][p]) <= 1e-4
+
+
+@pytest.mark.parametrize("name", sorted(cases.IO_CASES))
+def test_port_io_layers_match_reference_golden(name):
+    """InputLayer / BLInputLayer -> SubmanifoldConvolution -> OutputLayer / BLOutputLayer: the input
+    side is numbered exactly like the reference, so everything is compared row for row, and the
+    copies back to the points are bit exact."""
+    g = helpers.load_golden(name)
+    mods = cases.io_modules(name)
+    helpers.load_state(mods[1], g, "state")
+    be = runner.PortBackend()
+    st = cases.run_io(mods, (g["coords"], g["feats"]), helpers.oracle_run(be))
+    assert np.array_equal(be.locations(st["x0"]), g["loc/x0"])
+    assert np.array_equal(st["x0"].features, g["feat/x0"]) or cases.IO_CASES[name]["mode"] == 4
+    assert helpers.rel_err(st["x0"].features, g["feat/x0"]) <= 1e-6
+    assert helpers.rel_err(st["x1"].features, g["feat/x1"]) <= 1e-5
+    assert st["back0"].shape == g["back0"].shape
+    assert helpers.rel_err(st["back0"], g["back0"]) <= 1e-6
+    assert helpers.rel_err(st["back1"], g["back1"]) <= 1e-5
