@@ -261,6 +261,23 @@ SCN_API int scn_max_pooling_forward(scn_metadata *md, const int64_t *input_size,
                             float *out_features, int n_planes_in, int n_features_to_drop,
                             void *stream);
 
+/* replaces cpu/cuda_AveragePooling_updateOutput (CPU/AveragePooling.cpp:38-61, CUDA/AveragePooling.cu):
+ * same arguments as scn_max_pooling_forward; out[o] = sum over the rules of o of in[i] / filter volume
+ * (the divisor is the pool volume whatever the number of rules, as in the reference). */
+SCN_API int scn_average_pooling_forward(scn_metadata *md, const int64_t *input_size, const int64_t *output_size,
+                                const int64_t *pool_size, const int64_t *pool_stride,
+                                const float *in_features, float *out_features, int n_planes_in,
+                                int n_features_to_drop, void *stream);
+
+/* replaces cpu/cuda_UnPooling_updateOutput (CPU/UnPooling.cpp:35-59, CUDA/UnPooling.cu).  input_size is
+ * the coarse scale, output_size = (input_size - 1) * pool_stride + pool_size the fine one, whose grid must
+ * already exist in the metadata (SCN_ERR_NO_GRID otherwise; the reference would produce zero rows).
+ * in [n_active(input_size), n_planes_in] -> out [n_active(output_size), n_planes_in - n_features_to_drop]:
+ * every fine site gets the sum of the coarse sites whose pooling window holds it. */
+SCN_API int scn_unpooling_forward(scn_metadata *md, const int64_t *input_size, const int64_t *output_size,
+                          const int64_t *pool_size, const int64_t *pool_stride, const float *in_features,
+                          float *out_features, int n_planes_in, int n_features_to_drop, void *stream);
+
 /* replaces SparseToDense_updateOutput (sparseconvnet.h:220-222; CPU/SparseToDense.cpp:7-64):
  * out [batch_size, n_planes, *spatial_size] float32, written completely (zeros where
  * inactive). */

@@ -152,6 +152,18 @@ class RefBackend(object):
                                          self._t(x.features), out, int(drop))
         return OTensor(out.numpy(), x.metadata, out_size)
 
+    def avgpool(self, x, out_size, pool_size, stride, drop):
+        out = torch.empty(0)
+        self.SCN.AveragePooling_updateOutput(_lt(x.spatial_size), _lt(out_size), _lt(pool_size), _lt(stride),
+                                             x.metadata, self._t(x.features), out, int(drop))
+        return OTensor(out.numpy(), x.metadata, out_size)
+
+    def unpool(self, x, out_size, pool_size, stride, drop):
+        out = torch.empty(0)
+        self.SCN.UnPooling_updateOutput(_lt(x.spatial_size), _lt(out_size), _lt(pool_size), _lt(stride),
+                                        x.metadata, self._t(x.features), out, int(drop))
+        return OTensor(out.numpy(), x.metadata, out_size)
+
     def sparse_to_dense(self, x, n_planes):
         out = torch.empty(0)
         self.SCN.SparseToDense_updateOutput(_lt(x.spatial_size), x.metadata, self._t(x.features), out, int(n_planes))
@@ -254,6 +266,17 @@ class PortBackend(object):
         n_out = x.metadata.grids[tuple(int(v) for v in out_size)].n_active
         return OTensor(port.max_pooling(x.features, n_out, rules, drop), x.metadata, out_size)
 
+    def avgpool(self, x, out_size, pool_size, stride, drop):
+        rules = self.strided_rulebook(x, out_size, pool_size, stride)
+        n_out = x.metadata.grids[tuple(int(v) for v in out_size)].n_active
+        return OTensor(port.average_pooling(x.features, n_out, rules, drop), x.metadata, out_size)
+
+    def unpool(self, x, out_size, pool_size, stride, drop):
+        fine = OTensor(None, x.metadata, out_size)   # the fine grid must exist already
+        rules = self.strided_rulebook(fine, [int(v) for v in x.spatial_size], pool_size, stride)
+        n_fine = x.metadata.grids[tuple(int(v) for v in out_size)].n_active
+        return OTensor(port.unpooling(x.features, n_fine, rules, drop), x.metadata, out_size)
+
     def sparse_to_dense(self, x, n_planes):
         return port.sparse_to_dense(self._grid(x), x.features, n_planes)
 
@@ -319,6 +342,12 @@ def run_module(m, x, be, stats=None):
     if name == "MaxPooling":
         out_size = [(i - f) // s + 1 for i, f, s in zip(x.spatial_size, m.pool_size.tolist(), m.pool_stride.tolist())]
         return be.maxpool(x, out_size, m.pool_size.tolist(), m.pool_stride.tolist(), m.nFeaturesToDrop)
+    if name == "AveragePooling":
+        out_size = [(i - f) // s + 1 for i, f, s in zip(x.spatial_size, m.pool_size.tolist(), m.pool_stride.tolist())]
+        return be.avgpool(x, out_size, m.pool_size.tolist(), m.pool_stride.tolist(), m.nFeaturesToDrop)
+    if name == "UnPooling":
+        out_size = [(i - 1) * s + f for i, f, s in zip(x.spatial_size, m.pool_size.tolist(), m.pool_stride.tolist())]
+        return be.unpool(x, out_size, m.pool_size.tolist(), m.pool_stride.tolist(), m.nFeaturesToDrop)
     if name == "SparseToDense":
         return be.sparse_to_dense(x, m.nPlanes)
     if name == "NetworkInNetwork":

@@ -412,6 +412,32 @@ def MaxPooling_updateOutput(inputSize, outputSize, poolSize, poolStride, m, inpu
             _ptr(output_features), f.size(1), int(nFeaturesToDrop), _stream()))
 
 
+def AveragePooling_updateOutput(inputSize, outputSize, poolSize, poolStride, m, input_features,
+                                output_features, nFeaturesToDrop):
+    """sparseconvnet.h (AveragePooling_updateOutput), CPU/AveragePooling.cpp:38-61."""
+    f = _features(input_features, "input_features")
+    n_out = C.c_int64()
+    with torch.cuda.device(f.device):
+        check(lib.scn_md_strided_rulebook(m._h, sizes(inputSize), sizes(outputSize), sizes(poolSize),
+                                          sizes(poolStride), _stream(), C.byref(n_out), None))
+        output_features.resize_(n_out.value, f.size(1) - int(nFeaturesToDrop))
+        check(lib.scn_average_pooling_forward(
+            m._h, sizes(inputSize), sizes(outputSize), sizes(poolSize), sizes(poolStride), _ptr(f),
+            _ptr(output_features), f.size(1), int(nFeaturesToDrop), _stream()))
+
+
+def UnPooling_updateOutput(inputSize, outputSize, poolSize, poolStride, m, input_features, output_features,
+                           nFeaturesToDrop):
+    """sparseconvnet.h (UnPooling_updateOutput), CPU/UnPooling.cpp:35-59: inputSize is the coarse scale,
+    outputSize the fine one (its grid must exist already)."""
+    f = _features(input_features, "input_features")
+    with torch.cuda.device(f.device):
+        output_features.resize_(m.getNActive(outputSize), f.size(1) - int(nFeaturesToDrop))
+        check(lib.scn_unpooling_forward(
+            m._h, sizes(inputSize), sizes(outputSize), sizes(poolSize), sizes(poolStride), _ptr(f),
+            _ptr(output_features), f.size(1), int(nFeaturesToDrop), _stream()))
+
+
 def SparseToDense_updateOutput(inputSize, m, input_features, output_features, nPlanes):
     """sparseconvnet.h:220-222.  Output [batch, nPlanes, *inputSize]."""
     f = _features(input_features, "input_features")

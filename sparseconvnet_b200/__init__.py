@@ -21,7 +21,7 @@ def Metadata(dim):
 
 
 from .layers import (InputLayer, OutputLayer, BLInputLayer, BLOutputLayer, SubmanifoldConvolution, ValidConvolution, Convolution,  # noqa: E402
-                     Deconvolution, BatchNormalization, BatchNormReLU, BatchNormLeakyReLU, MaxPooling,
+                     Deconvolution, BatchNormalization, BatchNormReLU, BatchNormLeakyReLU, MaxPooling, AveragePooling, UnPooling,
                      SparseToDense, NetworkInNetwork, Identity)
 from .containers import Sequential, ConcatTable, JoinTable, AddTable  # noqa: E402
-from .architectures import SparseVggNet, SparseResNet, UNet  # noqa: E402
+from .architectures import SparseVggNet, SparseResNet, UNet, FullyConvolutionalNet  # noqa: E402

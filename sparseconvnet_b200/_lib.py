@@ -50,6 +50,10 @@ SIGNATURES = {
                                         C.c_double, _vp]),
     "scn_max_pooling_forward": (C.c_int, [_vp, _i64p, _i64p, _i64p, _i64p, _vp, _vp, C.c_int, C.c_int,
                                           _vp]),
+    "scn_average_pooling_forward": (C.c_int, [_vp, _i64p, _i64p, _i64p, _i64p, _vp, _vp, C.c_int, C.c_int,
+                                          _vp]),
+    "scn_unpooling_forward": (C.c_int, [_vp, _i64p, _i64p, _i64p, _i64p, _vp, _vp, C.c_int, C.c_int,
+                                          _vp]),
     "scn_sparse_to_dense_forward": (C.c_int, [_vp, _i64p, _vp, _vp, C.c_int, _vp]),
 }
 

@@ -130,3 +130,37 @@ def UNet(dimension, reps, nPlanes, residual_blocks=False, downsample=[2, 2], lea
         return m
 
     return level(nPlanes, n_input_planes)
+
+
+def FullyConvolutionalNet(dimension, reps, nPlanes, residual_blocks=False, downsample=[2, 2]):
+    """Fully-convolutional network for per-voxel prediction (reference:
+    networkArchitectures.py:259-312): `reps` blocks per level, a strided Convolution down, the
+    deeper levels, then UnPooling back to this level's sites; the coarse result is concatenated to
+    the level's own features, so the output has sum(nPlanes) planes at the input's sites."""
+
+    def block(m, a, b):
+        if residual_blocks:
+            shortcut = scn.Identity() if a == b else scn.NetworkInNetwork(a, b, False)
+            body = (scn.Sequential()
+                    .add(scn.BatchNormReLU(a)).add(scn.SubmanifoldConvolution(dimension, a, b, 3, False))
+                    .add(scn.BatchNormReLU(b)).add(scn.SubmanifoldConvolution(dimension, b, b, 3, False)))
+            m.add(scn.ConcatTable().add(shortcut).add(body)).add(scn.AddTable())
+        else:
+            m.add(scn.Sequential().add(scn.BatchNormReLU(a))
+                  .add(scn.SubmanifoldConvolution(dimension, a, b, 3, False)))
+
+    def level(planes):
+        m = scn.Sequential()
+        for _ in range(reps):
+            block(m, planes[0], planes[0])
+        if len(planes) > 1:
+            deeper = (scn.Sequential()
+                      .add(scn.BatchNormReLU(planes[0]))
+                      .add(scn.Convolution(dimension, planes[0], planes[1], downsample[0], downsample[1], False))
+                      .add(level(planes[1:]))
+                      .add(scn.UnPooling(dimension, downsample[0], downsample[1])))
+            m.add(scn.ConcatTable().add(scn.Identity()).add(deeper))
+            m.add(scn.JoinTable())
+        return m
+
+    return level(nPlanes)

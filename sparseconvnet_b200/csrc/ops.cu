@@ -173,6 +173,36 @@ k_max_pool(const float *__restrict__ in, float *__restrict__ out, const int *__r
 }
 
 // ------------------------------------------------------------------------------------------
+// AveragePooling (CPU/AveragePooling.cpp:7-20,38-61): out[o] = sum over the rules of o, in
+// ascending filter-offset order, of in[i] / filterVolume -- the divisor is the filter volume, not
+// the number of rules, and every term is divided before it is added, as the reference does.
+// UnPooling (CPU/UnPooling.cpp:7-19,35-59): the rulebook of (fine -> coarse) read backwards:
+// out[fine] = sum over offsets of in[coarse]; `nbr` is then the transposed table [K][n fine].
+// ------------------------------------------------------------------------------------------
+template <bool AVERAGE>
+__global__ void __launch_bounds__(256)
+k_sum_pool(const float *__restrict__ in, float *__restrict__ out, const int *__restrict__ nbr,
+           long long n_out, long long n_in, int K, int C_out, int in_stride, int drop, int *flags) {
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n_out * C_out) return;
+  long long o = idx / C_out;
+  int c = (int)(idx % C_out);
+  const float fv = (float)K;
+  float acc = 0.f;
+  for (int k = 0; k < K; ++k) {
+    int i = nbr[(long long)k * n_out + o];
+    if (i < 0) continue;
+    if (i >= n_in) {
+      atomicOr(flags, FLAG_BAD_ROW);
+      continue;
+    }
+    float v = in[(long long)i * in_stride + drop + c];
+    acc = __fadd_rn(acc, AVERAGE ? __fdiv_rn(v, fv) : v);
+  }
+  out[idx] = acc;
+}
+
+// ------------------------------------------------------------------------------------------
 // SparseToDense (CPU/SparseToDense.cpp:7-19,35-64): dense[b][c][offset(x)] = feat[row][c]
 // ------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
@@ -293,6 +323,46 @@ int scn_max_pooling_forward(scn_metadata *md, const int64_t *input_size, const i
   int c_out = n_planes_in - n_features_to_drop;
   long long total = rb->n_out * c_out;
   SCN_LAUNCH(k_max_pool, (unsigned)ceil_div(total, 256), 256, 0, stream, in_features, out_features, rb->nbr, rb->n_out, rb->n_in, rb->n_offsets, c_out, n_planes_in, n_features_to_drop, md->flags_dev);
+  SCN_CUDA_CHECK(cudaGetLastError());
+  return SCN_OK;
+}
+
+int scn_average_pooling_forward(scn_metadata *md, const int64_t *input_size, const int64_t *output_size,
+                                const int64_t *pool_size, const int64_t *pool_stride,
+                                const float *in_features, float *out_features, int n_planes_in,
+                                int n_features_to_drop, void *stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SCN_REQUIRE(md && input_size && output_size && pool_size && pool_stride, SCN_ERR_BAD_ARG, "null argument");
+  SCN_REQUIRE(n_features_to_drop >= 0 && n_features_to_drop < n_planes_in, SCN_ERR_BAD_ARG,
+              "n_features_to_drop %d not in [0, %d)", n_features_to_drop, n_planes_in);
+  Rulebook *rb = nullptr;
+  SCN_TRY(get_strided_rulebook(md, input_size, output_size, pool_size, pool_stride, stream, &rb));
+  if (rb->n_out == 0) return SCN_OK;
+  SCN_REQUIRE(in_features && out_features, SCN_ERR_BAD_ARG, "null features");
+  int c_out = n_planes_in - n_features_to_drop;
+  long long total = rb->n_out * c_out;
+  SCN_LAUNCH(k_sum_pool<true>, (unsigned)ceil_div(total, 256), 256, 0, stream, in_features, out_features, rb->nbr, rb->n_out, rb->n_in, rb->n_offsets, c_out, n_planes_in, n_features_to_drop, md->flags_dev);
+  SCN_CUDA_CHECK(cudaGetLastError());
+  return SCN_OK;
+}
+
+int scn_unpooling_forward(scn_metadata *md, const int64_t *input_size, const int64_t *output_size,
+                          const int64_t *pool_size, const int64_t *pool_stride, const float *in_features,
+                          float *out_features, int n_planes_in, int n_features_to_drop, void *stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SCN_REQUIRE(md && input_size && output_size && pool_size && pool_stride, SCN_ERR_BAD_ARG, "null argument");
+  SCN_REQUIRE(n_features_to_drop >= 0 && n_features_to_drop < n_planes_in, SCN_ERR_BAD_ARG,
+              "n_features_to_drop %d not in [0, %d)", n_features_to_drop, n_planes_in);
+  // the fine grid (output_size) must exist: its sites are what gets un-pooled onto
+  SCN_REQUIRE(find_grid(md, output_size), SCN_ERR_NO_GRID, "UnPooling: no grid for the output spatial size");
+  Rulebook *rb = nullptr;  // rulebook of fine (output_size) -> coarse (input_size)
+  SCN_TRY(get_strided_rulebook(md, output_size, input_size, pool_size, pool_stride, stream, &rb));
+  if (rb->n_in == 0) return SCN_OK;
+  SCN_REQUIRE(out_features && (in_features || rb->n_out == 0), SCN_ERR_BAD_ARG, "null features");
+  SCN_TRY(rulebook_transposed(*rb, stream));
+  int c_out = n_planes_in - n_features_to_drop;
+  long long total = rb->n_in * c_out;
+  SCN_LAUNCH(k_sum_pool<false>, (unsigned)ceil_div(total, 256), 256, 0, stream, in_features, out_features, rb->tnbr, rb->n_in, rb->n_out, rb->n_offsets, c_out, n_planes_in, n_features_to_drop, md->flags_dev);
   SCN_CUDA_CHECK(cudaGetLastError());
   return SCN_OK;
 }

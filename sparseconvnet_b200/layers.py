@@ -322,6 +322,61 @@ class MaxPooling(Module):
         return "MaxPooling%s/%s" % (_size_str(self.pool_size), _size_str(self.pool_stride))
 
 
+class AveragePooling(Module):
+    """averagePooling.py: like MaxPooling, but every output site gets the sum of its inputs divided
+    by the pool volume (not by the number of active inputs)."""
+
+    def __init__(self, dimension, pool_size, pool_stride, nFeaturesToDrop=0):
+        Module.__init__(self)
+        self.dimension = dimension
+        self.pool_size = to_long_tensor(dimension, pool_size)
+        self.pool_stride = to_long_tensor(dimension, pool_stride)
+        self.nFeaturesToDrop = nFeaturesToDrop
+
+    def forward(self, input):
+        out_size = torch.div(input.spatial_size - self.pool_size, self.pool_stride, rounding_mode="trunc") + 1
+        assert ((out_size - 1) * self.pool_stride + self.pool_size == input.spatial_size).all()
+        output = SparseConvNetTensor(metadata=input.metadata, spatial_size=out_size)
+        output.features = input.features.new_empty(0)
+        SCN.AveragePooling_updateOutput(input.spatial_size, out_size, self.pool_size, self.pool_stride,
+                                        input.metadata, input.features.detach().contiguous(), output.features,
+                                        self.nFeaturesToDrop)
+        return output
+
+    def input_spatial_size(self, out_size):
+        return (out_size - 1) * self.pool_stride + self.pool_size
+
+    def __repr__(self):
+        return "AveragePooling%s/%s" % (_size_str(self.pool_size), _size_str(self.pool_stride))
+
+
+class UnPooling(Module):
+    """unPooling.py: the inverse geometry of a pooling layer -- every site of the fine scale (which
+    must already exist in the metadata) gets the sum of the coarse sites whose window holds it."""
+
+    def __init__(self, dimension, pool_size, pool_stride, nFeaturesToDrop=0):
+        Module.__init__(self)
+        self.dimension = dimension
+        self.pool_size = to_long_tensor(dimension, pool_size)
+        self.pool_stride = to_long_tensor(dimension, pool_stride)
+        self.nFeaturesToDrop = nFeaturesToDrop
+
+    def forward(self, input):
+        out_size = (input.spatial_size - 1) * self.pool_stride + self.pool_size
+        output = SparseConvNetTensor(metadata=input.metadata, spatial_size=out_size)
+        output.features = input.features.new_empty(0)
+        SCN.UnPooling_updateOutput(input.spatial_size, out_size, self.pool_size, self.pool_stride,
+                                   input.metadata, input.features.detach().contiguous(), output.features,
+                                   self.nFeaturesToDrop)
+        return output
+
+    def input_spatial_size(self, out_size):
+        return torch.div(out_size - self.pool_size, self.pool_stride, rounding_mode="trunc") + 1
+
+    def __repr__(self):
+        return "UnPooling%s/%s" % (_size_str(self.pool_size), _size_str(self.pool_stride))
+
+
 class SparseToDense(Module):
     """SparseConvNetTensor -> dense tensor [batch, nPlanes, *spatial_size]."""
 

@@ -10,7 +10,7 @@ from sparseconvnet_b200 import workloads
 
 # ---- operator chains ---------------------------------------------------------------------------
 # x0 = InputLayer(mode); x1 = SC(x0) (+bias); x2 = Conv f/s (x1); x3 = BNReLU(x2); x4 = Deconv(x3) (+bias);
-# x5 = MaxPool f/s (x1); dense = SparseToDense(x5)
+# x5 = MaxPool f/s (x1); dense = SparseToDense(x5); x6 = AveragePool f/s (x1); x7 = UnPool f/s (x6)
 OPS_CASES = {
     "ops1d_m3": dict(dim=1, size=[33], n=40, batch=2, mode=3, planes=3, f=3, s=2, groups=1),
     "ops2d_m0": dict(dim=2, size=[17, 17], n=150, batch=3, mode=0, planes=5, f=3, s=2, groups=1),
@@ -117,6 +117,8 @@ def ops_modules(case):
         dc=scn.Deconvolution(d, 6 * g, 4 * g, c["f"], c["s"], True, g),
         mp=scn.MaxPooling(d, c["f"], c["s"], 1),
         sd=scn.SparseToDense(d, 2 * p - 1),
+        ap=scn.AveragePooling(d, c["f"], c["s"], 1),
+        up=scn.UnPooling(d, c["f"], c["s"]),
     )
     mods["sc"].bias.data.normal_()
     mods["dc"].bias.data.normal_()
@@ -137,7 +139,9 @@ def run_ops(net, inputs, run, locations):
     x4 = run(net["dc"], x3)
     x5 = run(net["mp"], x1)
     dense = run(net["sd"], x5)
-    return dict(x0=x0, x1=x1, x2=x2, x3=x3, x4=x4, x5=x5, dense=dense)
+    x6 = run(net["ap"], x1)
+    x7 = run(net["up"], x6)
+    return dict(x0=x0, x1=x1, x2=x2, x3=x3, x4=x4, x5=x5, dense=dense, x6=x6, x7=x7)
 
 
 # ---- small networks ------------------------------------------------------------------------------
@@ -156,6 +160,16 @@ def _mini_unet():
     net = scn.Sequential().add(scn.SubmanifoldConvolution(3, 3, 8, 3, False)).add(
         scn.UNet(3, 2, [8, 16, 24, 32], False)).add(scn.BatchNormReLU(8))
     return inp, net, torch.nn.Linear(8, 5)
+
+
+def _mini_fcn():
+    # per-point network: residual FullyConvolutionalNet (UnPooling back to the input sites), then
+    # OutputLayer hands every input point its site's features
+    inp = scn.InputLayer(3, 64, mode=3)
+    net = scn.Sequential().add(scn.SubmanifoldConvolution(3, 3, 8, 3, False)).add(
+        scn.FullyConvolutionalNet(3, 1, [8, 12, 16], residual_blocks=True)).add(scn.BatchNormReLU(36)).add(
+        scn.OutputLayer(3))
+    return inp, net, None
 
 
 def _mini_resnet():
@@ -180,14 +194,14 @@ def _mini_4d():
 
 
 NET_CASES = {"net_vgg2d": _mini_vgg, "net_unet3d": _mini_unet, "net_resnet3d": _mini_resnet,
-             "net_vggplus2d": _mini_vgg_plus, "net_stack4d": _mini_4d}
+             "net_vggplus2d": _mini_vgg_plus, "net_stack4d": _mini_4d, "net_fcn3d": _mini_fcn}
 
 
 def net_inputs(case):
     rng = np.random.default_rng(sum(map(ord, case)))
     if case == "net_vgg2d":
         return workloads.batch_config2([0, 1, 2, 3])
-    if case == "net_unet3d":
+    if case in ("net_unet3d", "net_fcn3d"):
         n = 3000
         pts = rng.integers(0, 64, (n, 2))
         z = (20 + 10 * np.sin(pts[:, 0] / 9.0) + 6 * np.cos(pts[:, 1] / 7.0)).astype(np.int64)

@@ -35,7 +35,7 @@ def ops_case(name, be):
     c = cases.OPS_CASES[name]
     out = {"coords": coords, "feats": feats, "batch_size_arg": np.int64(bs)}
     _state("state", net, out)
-    for k in ("x0", "x1", "x2", "x3", "x4", "x5"):
+    for k in ("x0", "x1", "x2", "x3", "x4", "x5", "x6", "x7"):
         out["loc/" + k] = be.locations(st[k])
         out["feat/" + k] = st[k].features
     out["dense"] = st["dense"]

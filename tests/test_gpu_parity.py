@@ -32,10 +32,10 @@ def test_ops_against_golden_and_port(name, cuda):
 
     # -- golden (reference CPU build): canonical comparison
     assert gpu.batch_size(st["x0"]) == int(g["batch_size"])
-    for k in ("x0", "x1", "x4"):
+    for k in ("x0", "x1", "x4", "x7"):
         helpers.assert_features_match(gpu.locations(st[k]), st[k].features, g["loc/" + k], g["feat/" + k],
                                       helpers.FP32_TOL, same_rows=True, what=name + ":" + k)
-    for k in ("x2", "x3", "x5"):
+    for k in ("x2", "x3", "x5", "x6"):
         helpers.assert_features_match(gpu.locations(st[k]), st[k].features, g["loc/" + k], g["feat/" + k],
                                       helpers.FP32_TOL, what=name + ":" + k)
     assert helpers.rel_err(st["dense"], g["dense"]) <= helpers.FP32_TOL
@@ -54,7 +54,7 @@ def test_ops_against_golden_and_port(name, cuda):
     helpers.load_state(net_cpu, g, "state")
     pb = runner.PortBackend()
     sp = cases.run_ops(net_cpu, inputs, helpers.oracle_run(pb), pb.locations)
-    for k in ("x0", "x1", "x2", "x3", "x4", "x5"):
+    for k in ("x0", "x1", "x2", "x3", "x4", "x5", "x6", "x7"):
         helpers.assert_features_match(gpu.locations(st[k]), st[k].features, pb.locations(sp[k]), sp[k].features,
                                       helpers.FP32_TOL, same_rows=True, what=name + ":port:" + k)
     _exact_rules(gpu.submanifold_rulebook(st["x0"], [3] * d), pb.submanifold_rulebook(sp["x0"], [3] * d),

@@ -20,11 +20,11 @@ def test_port_ops_match_reference_golden(name):
     d = c["dim"]
     assert be.batch_size(st["x0"]) == int(g["batch_size"])
     # input-level stages share the reference's row numbering exactly
-    for k in ("x0", "x1", "x4"):
+    for k in ("x0", "x1", "x4", "x7"):
         helpers.assert_features_match(be.locations(st[k]), st[k].features, g["loc/" + k], g["feat/" + k],
                                       1e-5, same_rows=True, what=name + ":" + k)
     assert np.array_equal(st["x0"].features, g["feat/x0"]), "input layer features must be bit exact"
-    for k in ("x2", "x3", "x5"):
+    for k in ("x2", "x3", "x5", "x6"):
         helpers.assert_features_match(be.locations(st[k]), st[k].features, g["loc/" + k], g["feat/" + k],
                                       1e-5, what=name + ":" + k)
     assert helpers.rel_err(st["dense"], g["dense"]) <= 1e-5
