@@ -53,6 +53,18 @@ def peaks():
     return 6650.0, "fallback"
 
 
+def tensor_peak_tflops():
+    """Dense tf32 peak used for the tensor-pipe utilisation figure: half of the measured sustained
+    bf16 cuBLAS figure (there is no tf32 entry in MEASURED_PEAKS.json), else half of the
+    fallback 1400."""
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return 0.5 * float(d.get("bf16_tflops_sustained", d.get("bf16_tflops", 1400.0))), "0.5 x measured bf16 sustained"
+    return 700.0, "0.5 x fallback bf16 sustained"
+
+
 class ClockSampler(threading.Thread):
     """Samples SM clock and throttle reasons of one GPU through NVML while a timed region runs
     (read-only queries)."""
@@ -386,10 +398,18 @@ def main():
     roofline = {"kernel": {"batchnorm": "k_bn_apply", "rules_submanifold": "k_submanifold_rules",
                            "rules_strided": "k_strided_*", "input_hash": "k_insert_input"}.get(top, top),
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "peak_source": peak_src,
+                "peak_source": peak_src, "frac_of_nominal_7700": achieved / 7700.0,
                 "traffic": (TRAFFIC_RATIO * a["bytes"] / a["calls"]) if (TRAFFIC_RATIO and top == "k_conv_tma") else None,
                 "algorithmic_bytes_per_step": a["bytes"], "launches_per_step": a["calls"], "ms_per_step": a["ms"],
                 "tflops": a["flops"] / (a["ms"] / 1e3) / 1e12 if a["flops"] else None}
+    if a["flops"]:
+        # the same kernel against the tensor pipe: algorithmic FLOPs (2 x rules x Cin x Cout; the
+        # three-pass mode issues three times as many) over the dense tf32 peak
+        tpeak, tsrc = tensor_peak_tflops()
+        roofline["tensor"] = {"achieved": roofline["tflops"], "peak": tpeak, "unit": "TFLOP/s",
+                              "frac": roofline["tflops"] / tpeak, "peak_source": tsrc}
+    roofline["limiter"] = ("shared-memory data pipe (ncu: 77 % busy, tensor pipe 40-46 %), see "
+                           "profiles/k_conv_tma_tf32x3_unet3d_4rooms.md") if top == "k_conv_tma" else None
     breakdown = {k: {"ms": round(v["ms"], 4), "calls": v["calls"],
                      "GBps": round(v["bytes"] / (v["ms"] / 1e3) / 1e9, 1) if v["ms"] > 0 else None}
                  for k, v in sorted(agg.items(), key=lambda kv: -kv[1]["ms"])}
