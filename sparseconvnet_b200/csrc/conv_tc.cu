@@ -554,6 +554,19 @@ static bool plan(int mode, int K, int cin, int cout, TcPlan &pl) {
   return true;
 }
 
+// cudaFuncSetAttribute is per device: done once for every device the library is used on.
+static int configure_tc_kernels() {
+  static bool configured[64] = {false};
+  int dev = 0;
+  SCN_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && configured[dev]) return SCN_OK;
+  SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_tc<TC_TF32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+  SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_tc<TC_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+  SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_tc<TC_TF32X3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+  if (dev >= 0 && dev < 64) configured[dev] = true;
+  return SCN_OK;
+}
+
 int conv_forward_tc(const float *in, long long n_in, float *out, long long n_out, const float *weight,
                     const float *bias, const int *table, int K, int cin, int cout, int precision, int *flags,
                     cudaStream_t stream) {
@@ -594,13 +607,7 @@ int conv_forward_tc(const float *in, long long n_in, float *out, long long n_out
   P.partial = nullptr;
   if (P.n_split > 1) SCN_TRY(device_alloc((void **)&P.partial, (size_t)P.n_split * n_out * cout * sizeof(float), stream));
   dim3 grid((unsigned)ceil_div(n_out, kTcRows), (unsigned)P.n_split);
-  static bool configured = false;
-  if (!configured) {
-    SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_tc<TC_TF32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-    SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_tc<TC_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-    SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_tc<TC_TF32X3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-    configured = true;
-  }
+  SCN_TRY(configure_tc_kernels());
   if (mode == TC_TF32)
     SCN_LAUNCH(k_conv_tc<TC_TF32>, grid, kTcThreads, pl.smem, stream, P);
   else if (mode == TC_BF16)
@@ -709,13 +716,7 @@ extern "C" int scn_submanifold_convolution_forward_static(scn_metadata *md, cons
   P.partial = nullptr;
   P.flags = md->flags_dev;
   const unsigned grid = (unsigned)ceil_div(rb.n_out, kTcRows);
-  static bool configured = false;
-  if (!configured) {  // attribute calls: no allocation
-    SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_tc<TC_TF32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-    SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_tc<TC_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-    SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_tc<TC_TF32X3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-    configured = true;
-  }
+  SCN_TRY(configure_tc_kernels());  // attribute calls: no allocation
   if (mode == TC_TF32)
     SCN_LAUNCH(k_conv_tc<TC_TF32>, grid, kTcThreads, pl.smem, stream, P);
   else if (mode == TC_BF16)
