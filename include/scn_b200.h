@@ -178,15 +178,15 @@ SCN_API int scn_md_rulebook_export(scn_metadata *md, int kind, const int64_t *si
 
 /* ---- Feature operators ----------------------------------------------------------------- */
 
+/* -1 before the first convolution, else an scn_conv_kernel value.  No counterpart in the
+ * reference; lets a profiler attribute a call's time to the kernel that ran it. */
+SCN_API int scn_last_conv_kernel(void);
+
 /* replaces SubmanifoldConvolution_updateOutput (sparseconvnet.h:101-104;
  * CPU/Convolution.cpp:117-150; CUDA/Convolution.cu:57-233,444-521,618-642).
  * weight [filter_volume, groups, n_in/groups, n_out/groups], bias [n_out] or NULL.
  * in [n_active, n_in] -> out [n_active, n_out].  macs (may be NULL) receives the
  * reference's return value (rules x n_in/groups x n_out/groups x groups). */
-/* -1 before the first convolution, else an scn_conv_kernel value.  No counterpart in the
- * reference; lets a profiler attribute a call's time to the kernel that ran it. */
-SCN_API int scn_last_conv_kernel(void);
-
 SCN_API int scn_submanifold_convolution_forward(scn_metadata *md, const int64_t *spatial_size,
                                         const int64_t *filter_size, const float *in_features,
                                         float *out_features, const float *weight,
@@ -241,6 +241,33 @@ SCN_API int scn_deconvolution_forward(scn_metadata *md, const int64_t *input_siz
                               int n_in_planes, int n_out_planes, int groups, int precision,
                               void *stream, double *macs);
 
+/* ---- Backward passes (training) ---------------------------------------------------------------
+ * fp32.  Every gradient buffer is overwritten (not accumulated into); d_bias and d_in_features may
+ * be NULL when not wanted.  Sums are formed in a fixed order: results are bit-reproducible. */
+
+/* replaces SubmanifoldConvolution_backward (sparseconvnet.h:106-114; CPU/Convolution.cpp:152-190;
+ * CUDA/Convolution.cu dConvolution_KMxKN_backward_dW*).  in [n_active, n_in], d_out [n_active, n_out]
+ * -> d_in [n_active, n_in], d_weight like weight, d_bias [n_out]. */
+SCN_API int scn_submanifold_convolution_backward(scn_metadata *md, const int64_t *spatial_size,
+                                         const int64_t *filter_size, const float *in_features,
+                                         float *d_in_features, const float *d_out_features,
+                                         const float *weight, float *d_weight, float *d_bias,
+                                         int n_in_planes, int n_out_planes, int groups, void *stream);
+
+/* replaces Convolution_backward (sparseconvnet.h:94-104; CPU/Convolution.cpp:80-115). */
+SCN_API int scn_convolution_backward(scn_metadata *md, const int64_t *input_size, const int64_t *output_size,
+                             const int64_t *filter_size, const int64_t *filter_stride,
+                             const float *in_features, float *d_in_features, const float *d_out_features,
+                             const float *weight, float *d_weight, float *d_bias, int n_in_planes,
+                             int n_out_planes, int groups, void *stream);
+
+/* replaces Deconvolution_backward (sparseconvnet.h:156-166; CPU/Deconvolution.cpp). */
+SCN_API int scn_deconvolution_backward(scn_metadata *md, const int64_t *input_size, const int64_t *output_size,
+                               const int64_t *filter_size, const int64_t *filter_stride,
+                               const float *in_features, float *d_in_features, const float *d_out_features,
+                               const float *weight, float *d_weight, float *d_bias, int n_in_planes,
+                               int n_out_planes, int groups, void *stream);
+
 /* replaces BatchNormalization_updateOutput (sparseconvnet.h:22-26;
  * CPU/BatchNormalization.cpp:12-62; CUDA/BatchNormalization.cu:14-122), which fuses the
  * leaky-ReLU: y = x*w + b, y *= (y > 0 ? 1 : leakiness).  weight / bias may be NULL.
@@ -251,6 +278,16 @@ SCN_API int scn_batchnorm_forward(const float *in_features, float *out_features,
                           float *save_invstd, float *running_mean, float *running_var,
                           const float *weight, const float *bias, double eps, double momentum,
                           int train, double leakiness, void *stream);
+
+/* replaces BatchNormalization_backward (sparseconvnet.h:28-38; CPU/BatchNormalization.cpp:64-107,
+ * CUDA/BatchNormalization.cu).  in / d_in share in_stride, out / d_out share out_stride; save_mean and
+ * save_invstd are what the forward call left there.  d_weight / d_bias [n_planes] may be NULL; weight
+ * may be NULL (no affine).  d_out is not modified (the reference scales it in place). */
+SCN_API int scn_batchnorm_backward(const float *in_features, float *d_in_features, const float *out_features,
+                           const float *d_out_features, int64_t n_rows, int n_planes, int64_t in_stride,
+                           int64_t out_stride, const float *save_mean, const float *save_invstd,
+                           const float *weight, float *d_weight, float *d_bias, double leakiness,
+                           void *stream);
 
 /* replaces MaxPooling_updateOutput (sparseconvnet.h:198-201; CPU/MaxPooling.cpp:7-60):
  * out[o] = max(0, max over rules of in[i]) on planes n_features_to_drop .. n_planes_in-1.
@@ -284,6 +321,42 @@ SCN_API int scn_unpooling_forward(scn_metadata *md, const int64_t *input_size, c
 SCN_API int scn_sparse_to_dense_forward(scn_metadata *md, const int64_t *spatial_size,
                                 const float *in_features, float *out_dense, int n_planes,
                                 void *stream);
+
+/* replaces InputLayer_updateGradInput / BLInputLayer_updateGradInput (CPU/IOLayers.cpp:74-93,165-186):
+ * d_out [n_active, n_planes] -> d_in [n_points, n_planes]; the points a rule names get the site's
+ * gradient (1/count of it in mode 4), the others zero. */
+SCN_API int scn_input_layer_backward(scn_metadata *md, float *d_in_features, int64_t n_points,
+                             const float *d_out_features, int64_t n_sites, int n_planes, void *stream);
+
+/* replaces OutputLayer_updateGradInput / BLOutputLayer_updateGradInput (CPU/IOLayers.cpp:116-136,217-237):
+ * d_out [n_points, n_planes] -> d_in [n_active, n_planes], every site the unscaled sum over its points. */
+SCN_API int scn_output_layer_backward(scn_metadata *md, float *d_in_features, int64_t n_sites,
+                              const float *d_out_features, int64_t n_points, int n_planes, void *stream);
+
+/* replaces MaxPooling_updateGradInput (sparseconvnet.h:203-212; CPU/MaxPooling.cpp:22-35,61-84): d_out flows
+ * to every input that equals the pooled maximum.  d_in [n_active(input_size), n_planes_in] (the dropped
+ * planes get zeros), out / d_out [n_active(output_size), n_planes_in - n_features_to_drop]. */
+SCN_API int scn_max_pooling_backward(scn_metadata *md, const int64_t *input_size, const int64_t *output_size,
+                             const int64_t *pool_size, const int64_t *pool_stride, const float *in_features,
+                             float *d_in_features, const float *out_features, const float *d_out_features,
+                             int n_planes_in, int n_features_to_drop, void *stream);
+
+/* replaces AveragePooling_updateGradInput (sparseconvnet.h:81-92; CPU/AveragePooling.cpp:21-35,62-85). */
+SCN_API int scn_average_pooling_backward(scn_metadata *md, const int64_t *input_size, const int64_t *output_size,
+                                 const int64_t *pool_size, const int64_t *pool_stride, float *d_in_features,
+                                 const float *d_out_features, int n_planes_in, int n_features_to_drop,
+                                 void *stream);
+
+/* replaces UnPooling_updateGradInput (sparseconvnet.h:235-242; CPU/UnPooling.cpp:20-32,60-80): input_size is
+ * the coarse scale as in scn_unpooling_forward; d_in [n_active(input_size), n_planes_in]. */
+SCN_API int scn_unpooling_backward(scn_metadata *md, const int64_t *input_size, const int64_t *output_size,
+                           const int64_t *pool_size, const int64_t *pool_stride, float *d_in_features,
+                           const float *d_out_features, int n_planes_in, int n_features_to_drop, void *stream);
+
+/* replaces SparseToDense_updateGradInput (sparseconvnet.h:224-228; CPU/SparseToDense.cpp:20-33,66-85):
+ * d_out_dense [batch, n_planes, *spatial_size] -> d_in [n_active, n_planes]. */
+SCN_API int scn_sparse_to_dense_backward(scn_metadata *md, const int64_t *spatial_size, float *d_in_features,
+                                 const float *d_out_dense, int n_planes, void *stream);
 
 #ifdef __cplusplus
 }

@@ -398,6 +398,52 @@ def BatchNormalization_updateOutput(input_features, output_features, saveMean, s
                 int(bool(train)), float(leakiness), _stream()))
 
 
+def _conv_backward_args(input_features, d_input_features, d_output_features, weight, d_weight, d_bias):
+    f, w, _, groups, cin, cout = _conv_args(input_features, weight, torch.empty(0))
+    go = _features(d_output_features, "d_output_features")
+    dw = _features(d_weight, "d_weight")
+    if dw.shape != w.shape:
+        raise RuntimeError("d_weight must have the shape of weight")
+    db = _features(d_bias, "d_bias") if d_bias is not None and d_bias.numel() else None
+    d_input_features.resize_(f.size(0), groups * cin)
+    return f, w, go, dw, db, groups, cin, cout
+
+
+def SubmanifoldConvolution_backward(inputSize, filterSize, m, input_features, d_input_features,
+                                    d_output_features, weight, d_weight, d_bias):
+    """sparseconvnet.h:106-114.  fp32; gradients are overwritten."""
+    f, w, go, dw, db, groups, cin, cout = _conv_backward_args(input_features, d_input_features,
+                                                             d_output_features, weight, d_weight, d_bias)
+    with torch.cuda.device(f.device):
+        check(lib.scn_submanifold_convolution_backward(
+            m._h, sizes(inputSize), sizes(filterSize), _ptr(f), _ptr(d_input_features), _ptr(go), _ptr(w),
+            _ptr(dw), _ptr(db), groups * cin, groups * cout, groups, _stream()))
+
+
+def Convolution_backward(inputSize, outputSize, filterSize, filterStride, m, input_features, d_input_features,
+                         d_output_features, weight, d_weight, d_bias):
+    """sparseconvnet.h:94-104."""
+    f, w, go, dw, db, groups, cin, cout = _conv_backward_args(input_features, d_input_features,
+                                                             d_output_features, weight, d_weight, d_bias)
+    with torch.cuda.device(f.device):
+        check(lib.scn_convolution_backward(
+            m._h, sizes(inputSize), sizes(outputSize), sizes(filterSize), sizes(filterStride), _ptr(f),
+            _ptr(d_input_features), _ptr(go), _ptr(w), _ptr(dw), _ptr(db), groups * cin, groups * cout, groups,
+            _stream()))
+
+
+def Deconvolution_backward(inputSize, outputSize, filterSize, filterStride, m, input_features, d_input_features,
+                           d_output_features, weight, d_weight, d_bias):
+    """sparseconvnet.h:156-166."""
+    f, w, go, dw, db, groups, cin, cout = _conv_backward_args(input_features, d_input_features,
+                                                             d_output_features, weight, d_weight, d_bias)
+    with torch.cuda.device(f.device):
+        check(lib.scn_deconvolution_backward(
+            m._h, sizes(inputSize), sizes(outputSize), sizes(filterSize), sizes(filterStride), _ptr(f),
+            _ptr(d_input_features), _ptr(go), _ptr(w), _ptr(dw), _ptr(db), groups * cin, groups * cout, groups,
+            _stream()))
+
+
 def MaxPooling_updateOutput(inputSize, outputSize, poolSize, poolStride, m, input_features,
                             output_features, nFeaturesToDrop):
     """sparseconvnet.h:198-201."""
@@ -468,11 +514,82 @@ def NetworkInNetwork_updateOutput(input_features, output_features, weight, bias)
     return float(n * f.size(1) * cout)
 
 
+def BatchNormalization_backward(input_features, d_input_features, output_features, d_output_features, saveMean,
+                                saveInvStd, runningMean, runningVar, weight, bias, d_weight, d_bias, leakiness):
+    """sparseconvnet.h:28-38.  d_output_features is left untouched (the reference scales it in place)."""
+    f = input_features
+    n, c = f.size(0), f.size(1)
+    d_input_features.resize_(n, c)
+    w = _optional(weight, f, "weight")
+    with torch.cuda.device(f.device):
+        check(lib.scn_batchnorm_backward(
+            _ptr(f), _ptr(d_input_features), _ptr(output_features), _ptr(d_output_features), n, c,
+            f.stride(0) if n else c, output_features.stride(0) if n else c, _ptr(saveMean), _ptr(saveInvStd),
+            _ptr(w), _ptr(d_weight), _ptr(d_bias), float(leakiness), _stream()))
+
+
+def InputLayer_updateGradInput(m, d_input_features, d_output_features):
+    """CPU/IOLayers.cpp:74-93 (and BLInputLayer_updateGradInput, :165-186, reshaped by the caller)."""
+    go = _features(d_output_features, "d_output_features")
+    d_input_features.resize_(m.n_input_rows, go.size(1))
+    with torch.cuda.device(go.device):
+        check(lib.scn_input_layer_backward(m._h, _ptr(d_input_features), m.n_input_rows, _ptr(go), go.size(0),
+                                           go.size(1), _stream()))
+
+
+def OutputLayer_updateGradInput(m, d_input_features, d_output_features):
+    """CPU/IOLayers.cpp:116-136 (and BLOutputLayer_updateGradInput): d_output [points..., planes];
+    d_input_features must already have its [n_active, planes] shape."""
+    go = _features(d_output_features, "d_output_features")
+    with torch.cuda.device(go.device):
+        check(lib.scn_output_layer_backward(m._h, _ptr(d_input_features), d_input_features.size(0), _ptr(go),
+                                            m.n_input_rows, go.size(-1), _stream()))
+
+
+def MaxPooling_updateGradInput(inputSize, outputSize, poolSize, poolStride, m, input_features, d_input_features,
+                               output_features, d_output_features, nFeaturesToDrop):
+    """sparseconvnet.h:203-212."""
+    f = _features(input_features, "input_features")
+    d_input_features.resize_(f.size(0), f.size(1))
+    with torch.cuda.device(f.device):
+        check(lib.scn_max_pooling_backward(
+            m._h, sizes(inputSize), sizes(outputSize), sizes(poolSize), sizes(poolStride), _ptr(f),
+            _ptr(d_input_features), _ptr(_features(output_features, "output_features")),
+            _ptr(_features(d_output_features, "d_output_features")), f.size(1), int(nFeaturesToDrop), _stream()))
+
+
+def AveragePooling_updateGradInput(inputSize, outputSize, poolSize, poolStride, m, input_features,
+                                   d_input_features, d_output_features, nFeaturesToDrop):
+    """sparseconvnet.h:81-92."""
+    f = _features(input_features, "input_features")
+    d_input_features.resize_(f.size(0), f.size(1))
+    with torch.cuda.device(f.device):
+        check(lib.scn_average_pooling_backward(
+            m._h, sizes(inputSize), sizes(outputSize), sizes(poolSize), sizes(poolStride), _ptr(d_input_features),
+            _ptr(_features(d_output_features, "d_output_features")), f.size(1), int(nFeaturesToDrop), _stream()))
+
+
+def UnPooling_updateGradInput(inputSize, outputSize, poolSize, poolStride, m, d_input_features, d_output_features,
+                              nFeaturesToDrop):
+    """sparseconvnet.h:235-242: d_input_features must already have the input's shape."""
+    go = _features(d_output_features, "d_output_features")
+    with torch.cuda.device(go.device):
+        check(lib.scn_unpooling_backward(
+            m._h, sizes(inputSize), sizes(outputSize), sizes(poolSize), sizes(poolStride), _ptr(d_input_features),
+            _ptr(go), d_input_features.size(1), int(nFeaturesToDrop), _stream()))
+
+
+def SparseToDense_updateGradInput(inputSize, m, input_features, d_input_features, d_output_features):
+    """sparseconvnet.h:224-228."""
+    go = _features(d_output_features, "d_output_features")
+    d_input_features.resize_(input_features.size(0), input_features.size(1))
+    with torch.cuda.device(go.device):
+        check(lib.scn_sparse_to_dense_backward(m._h, sizes(inputSize), _ptr(d_input_features), _ptr(go),
+                                               input_features.size(1), _stream()))
+
+
 def _training_only(*a, **k):
-    raise NotImplementedError("backward passes are outside the inference path of sparseconvnet_b200")
+    raise NotImplementedError("this backward pass is not part of sparseconvnet_b200 yet")
 
 
-InputLayer_updateGradInput = SubmanifoldConvolution_backward = Convolution_backward = _training_only
-Deconvolution_backward = BatchNormalization_backward = MaxPooling_updateGradInput = _training_only
-SparseToDense_updateGradInput = NetworkInNetwork_updateGradInput = _training_only
-NetworkInNetwork_accGradParameters = _training_only
+NetworkInNetwork_updateGradInput = NetworkInNetwork_accGradParameters = _training_only  # torch autograd does these

@@ -45,6 +45,21 @@ SIGNATURES = {
     "scn_deconvolution_forward": (C.c_int, [_vp, _i64p, _i64p, _i64p, _i64p, _vp, _vp, _vp, _vp,
                                             C.c_int, C.c_int, C.c_int, C.c_int, _vp,
                                             C.POINTER(C.c_double)]),
+    "scn_submanifold_convolution_backward": (C.c_int, [_vp, _i64p, _i64p, _vp, _vp, _vp, _vp, _vp, _vp,
+                                                       C.c_int, C.c_int, C.c_int, _vp]),
+    "scn_convolution_backward": (C.c_int, [_vp, _i64p, _i64p, _i64p, _i64p, _vp, _vp, _vp, _vp, _vp, _vp,
+                                           C.c_int, C.c_int, C.c_int, _vp]),
+    "scn_deconvolution_backward": (C.c_int, [_vp, _i64p, _i64p, _i64p, _i64p, _vp, _vp, _vp, _vp, _vp, _vp,
+                                             C.c_int, C.c_int, C.c_int, _vp]),
+    "scn_input_layer_backward": (C.c_int, [_vp, _vp, C.c_int64, _vp, C.c_int64, C.c_int, _vp]),
+    "scn_output_layer_backward": (C.c_int, [_vp, _vp, C.c_int64, _vp, C.c_int64, C.c_int, _vp]),
+    "scn_max_pooling_backward": (C.c_int, [_vp, _i64p, _i64p, _i64p, _i64p, _vp, _vp, _vp, _vp, C.c_int, C.c_int,
+                                           _vp]),
+    "scn_average_pooling_backward": (C.c_int, [_vp, _i64p, _i64p, _i64p, _i64p, _vp, _vp, C.c_int, C.c_int, _vp]),
+    "scn_unpooling_backward": (C.c_int, [_vp, _i64p, _i64p, _i64p, _i64p, _vp, _vp, C.c_int, C.c_int, _vp]),
+    "scn_sparse_to_dense_backward": (C.c_int, [_vp, _i64p, _vp, _vp, C.c_int, _vp]),
+    "scn_batchnorm_backward": (C.c_int, [_vp, _vp, _vp, _vp, C.c_int64, C.c_int, C.c_int64, C.c_int64, _vp, _vp,
+                                         _vp, _vp, _vp, C.c_double, _vp]),
     "scn_batchnorm_forward": (C.c_int, [_vp, _vp, C.c_int64, C.c_int, C.c_int64, C.c_int64, _vp, _vp,
                                         _vp, _vp, _vp, _vp, C.c_double, C.c_double, C.c_int,
                                         C.c_double, _vp]),

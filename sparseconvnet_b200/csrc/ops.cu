@@ -37,14 +37,15 @@ __global__ void k_input_features(const float *__restrict__ in, float *__restrict
 // duplicates, empty slots of a batch x length array) keep the zeros the output was cleared to.
 __global__ void k_output_features(const float *__restrict__ in, float *__restrict__ out,
                                   const int *__restrict__ start, const int *__restrict__ rows,
-                                  long long n_sites, int C, int mode) {
+                                  long long n_sites, int C, int mode, int scale_mean) {
   long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= n_sites * C) return;
   long long r = idx / C;
   int c = (int)(idx % C);
   int s = start[r], e = start[r + 1];
   if (e <= s) return;
-  const float v = in[idx];
+  // scale_mean: the backward pass of a mode-4 InputLayer hands every point 1/count of the site's row
+  const float v = scale_mean ? __fmul_rn(1.0f / (float)(e - s), in[idx]) : in[idx];
   if (mode == 1) {
     out[(long long)rows[s] * C + c] = v;
   } else if (mode == 2) {
@@ -147,6 +148,80 @@ k_bn_apply(const float *__restrict__ in, float *__restrict__ out, long long n_ro
 }
 
 // ------------------------------------------------------------------------------------------
+// BatchNorm + leaky ReLU, backward (CPU/BatchNormalization.cpp:64-107).  With d = d_out * (out > 0
+// ? 1 : leakiness):  d_bias = sum d,  dotp = sum (x - mean) d,  d_weight = dotp * invstd,
+//   d_in = (d - d_bias / n - (x - mean) * dotp * invstd^2 / n) * invstd * weight.
+// The reference applies this formula in eval mode too (with the running statistics in mean /
+// invstd); so does this.  The two sums are accumulated in double, chunk by chunk, and the chunks
+// are added in a fixed order.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+k_bn_back_sums(const float *__restrict__ in, const float *__restrict__ out, const float *__restrict__ d_out,
+               long long n_rows, int C, long long in_stride, long long out_stride,
+               const float *__restrict__ mean, float leak, long long chunk_rows,
+               double *__restrict__ partial /* [chunks][2][C] */) {
+  __shared__ double sh_s[8][33], sh_q[8][33];
+  const int lane = threadIdx.x & 31, wy = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
+  const long long r0 = (long long)blockIdx.y * chunk_rows, r1 = min(n_rows, r0 + chunk_rows);
+  double s = 0.0, q = 0.0;
+  if (c < C) {
+    const float m = mean[c];
+    for (long long r = r0 + wy; r < r1; r += 8) {
+      float d = d_out[r * out_stride + c];
+      if (!(out[r * out_stride + c] > 0.f)) d *= leak;
+      s += d;
+      q += (double)(in[r * in_stride + c] - m) * d;
+    }
+  }
+  sh_s[wy][lane] = s;
+  sh_q[wy][lane] = q;
+  __syncthreads();
+  if (wy == 0 && c < C) {
+    double ts = 0.0, tq = 0.0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      ts += sh_s[i][lane];
+      tq += sh_q[i][lane];
+    }
+    partial[((long long)blockIdx.y * 2 + 0) * C + c] = ts;
+    partial[((long long)blockIdx.y * 2 + 1) * C + c] = tq;
+  }
+}
+
+__global__ void k_bn_back_finalize(const double *__restrict__ partial, int chunks, int C, long long n_rows,
+                                   const float *__restrict__ invstd, float *__restrict__ d_weight,
+                                   float *__restrict__ d_bias, float *__restrict__ coef /* [2][C] */) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  double s = 0.0, q = 0.0;
+  for (int i = 0; i < chunks; ++i) {
+    s += partial[((long long)i * 2 + 0) * C + c];
+    q += partial[((long long)i * 2 + 1) * C + c];
+  }
+  const float is = invstd[c];
+  if (d_bias) d_bias[c] = (float)s;
+  if (d_weight) d_weight[c] = (float)q * is;
+  coef[c] = (float)(s / (double)n_rows);                      // gradMean
+  coef[C + c] = (float)(q * (double)is * (double)is / (double)n_rows);  // k
+}
+
+__global__ void __launch_bounds__(256)
+k_bn_back_apply(const float *__restrict__ in, float *__restrict__ d_in, const float *__restrict__ out,
+                const float *__restrict__ d_out, long long n_rows, int C, long long in_stride,
+                long long out_stride, const float *__restrict__ mean, const float *__restrict__ invstd,
+                const float *__restrict__ weight, const float *__restrict__ coef, float leak) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n_rows * C) return;
+  const long long r = idx / C;
+  const int c = (int)(idx % C);
+  float d = d_out[r * out_stride + c];
+  if (!(out[r * out_stride + c] > 0.f)) d *= leak;
+  const float x = in[r * in_stride + c] - mean[c];
+  d_in[r * in_stride + c] = (d - coef[c] - x * coef[C + c]) * invstd[c] * (weight ? weight[c] : 1.f);
+}
+
+// ------------------------------------------------------------------------------------------
 // MaxPooling (CPU/MaxPooling.cpp:7-20,37-60): the reference zero-fills the output and then
 // takes elementwise maxima over the rules, so the result is max(0, max of inputs).  Output
 // stationary here: each output element is written once.
@@ -222,6 +297,72 @@ k_sparse_to_dense(KeyLayout L, const unsigned long long *__restrict__ row_keys,
   out[((long long)b * C + c) * volume + lin] = in[idx];
 }
 
+// ------------------------------------------------------------------------------------------
+// Backward passes of the pooling operators, input stationary (each d_in element is written once,
+// sums in ascending filter-offset order).  `table` maps (offset, d_in row) to the d_out row.
+//   OP 0  MaxPooling (CPU/MaxPooling.cpp:22-35): d_out flows to every input equal to the pooled
+//         maximum
+//   OP 1  AveragePooling (CPU/AveragePooling.cpp:21-35): d_out / pool volume
+//   OP 2  UnPooling (CPU/UnPooling.cpp:20-32): plain sum
+// The first `drop` planes of d_in (features the forward pass ignored) are zero.
+// ------------------------------------------------------------------------------------------
+template <int OP>
+__global__ void __launch_bounds__(256)
+k_pool_backward(const float *__restrict__ in, float *__restrict__ d_in, const float *__restrict__ out,
+                const float *__restrict__ d_out, const int *__restrict__ table, long long n_rows,
+                long long n_other, int K, int C_in, int drop, int *flags) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n_rows * C_in) return;
+  const long long i = idx / C_in;
+  const int c = (int)(idx % C_in) - drop;
+  if (c < 0) {
+    d_in[idx] = 0.f;
+    return;
+  }
+  const int C_out = C_in - drop;
+  const float fv = (float)K;
+  const float x = OP == 0 ? in[idx] : 0.f;
+  float acc = 0.f;
+  for (int k = 0; k < K; ++k) {
+    const int o = table[(long long)k * n_rows + i];
+    if (o < 0) continue;
+    if (o >= n_other) {
+      atomicOr(flags, FLAG_BAD_ROW);
+      continue;
+    }
+    const float g = d_out[(long long)o * C_out + c];
+    if (OP == 0) {
+      if (out[(long long)o * C_out + c] == x) acc = __fadd_rn(acc, g);
+    } else if (OP == 1) {
+      acc = __fadd_rn(acc, __fdiv_rn(g, fv));
+    } else {
+      acc = __fadd_rn(acc, g);
+    }
+  }
+  d_in[idx] = acc;
+}
+
+// SparseToDense backward (CPU/SparseToDense.cpp:20-33): d_in[row][c] = d_dense[b][c][offset(x)]
+__global__ void __launch_bounds__(256)
+k_dense_to_sparse_grad(KeyLayout L, const unsigned long long *__restrict__ row_keys,
+                       const float *__restrict__ d_dense, float *__restrict__ d_in, long long n_rows, int C,
+                       long long volume) {
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n_rows * C) return;
+  long long r = idx / C;
+  int c = (int)(idx % C);
+  unsigned long long key = row_keys[r];
+  if (key == kEmptyKey) {
+    d_in[idx] = 0.f;
+    return;
+  }
+  int x[kMaxDim], b;
+  unpack_key(L, key, x, b);
+  long long lin = 0;
+  for (int d = 0; d < L.dim; ++d) lin = lin * L.size[d] + x[d];
+  d_in[idx] = d_dense[((long long)b * C + c) * volume + lin];
+}
+
 }  // namespace scn
 
 using namespace scn;
@@ -270,7 +411,7 @@ int scn_output_layer_forward(scn_metadata *md, const float *in_features, int64_t
   SCN_CUDA_CHECK(cudaMemsetAsync(out_features, 0, bytes, stream));
   if (n_in == 0) return SCN_OK;
   long long total = (long long)n_in * n_planes;
-  SCN_LAUNCH(k_output_features, (unsigned)ceil_div(total, 256), 256, 0, stream, in_features, out_features, md->input_csr_start, md->input_csr_rows, n_in, n_planes, md->input_mode);
+  SCN_LAUNCH(k_output_features, (unsigned)ceil_div(total, 256), 256, 0, stream, in_features, out_features, md->input_csr_start, md->input_csr_rows, n_in, n_planes, md->input_mode, 0);
   SCN_CUDA_CHECK(cudaGetLastError());
   return SCN_OK;
 }
@@ -305,6 +446,35 @@ int scn_batchnorm_forward(const float *in_features, float *out_features, int64_t
     SCN_LAUNCH(k_bn_apply<1>, blocks, 256, smem, stream, in_features, out_features, n_rows, n_planes, in_stride, out_stride, save_mean, save_invstd, weight, bias, (float)leakiness);
   SCN_CUDA_CHECK(cudaGetLastError());
   if (sums) SCN_TRY(device_free(sums, stream));
+  return SCN_OK;
+}
+
+int scn_batchnorm_backward(const float *in_features, float *d_in_features, const float *out_features,
+                           const float *d_out_features, int64_t n_rows, int n_planes, int64_t in_stride,
+                           int64_t out_stride, const float *save_mean, const float *save_invstd,
+                           const float *weight, float *d_weight, float *d_bias, double leakiness, void *stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SCN_REQUIRE(n_planes >= 1 && n_planes <= 4096, SCN_ERR_UNSUPPORTED, "n_planes %d unsupported", n_planes);
+  SCN_REQUIRE(save_mean && save_invstd, SCN_ERR_BAD_ARG, "null statistics");
+  SCN_REQUIRE(in_stride >= n_planes && out_stride >= n_planes, SCN_ERR_BAD_ARG, "row stride below n_planes");
+  if (n_rows == 0) {
+    if (d_weight) SCN_CUDA_CHECK(cudaMemsetAsync(d_weight, 0, sizeof(float) * n_planes, stream));
+    if (d_bias) SCN_CUDA_CHECK(cudaMemsetAsync(d_bias, 0, sizeof(float) * n_planes, stream));
+    return SCN_OK;
+  }
+  SCN_REQUIRE(in_features && d_in_features && out_features && d_out_features, SCN_ERR_BAD_ARG, "null features");
+  const int chunks = (int)std::max<long long>(1, std::min<long long>(128, n_rows / 2048));
+  const long long chunk_rows = ceil_div(n_rows, chunks);
+  double *partial = nullptr;
+  float *coef = nullptr;
+  SCN_TRY(device_alloc((void **)&partial, sizeof(double) * 2 * (size_t)chunks * n_planes, stream));
+  SCN_TRY(device_alloc((void **)&coef, sizeof(float) * 2 * (size_t)n_planes, stream));
+  SCN_LAUNCH(k_bn_back_sums, dim3((unsigned)ceil_div(n_planes, 32), (unsigned)chunks), 256, 0, stream, in_features, out_features, d_out_features, n_rows, n_planes, in_stride, out_stride, save_mean, (float)leakiness, chunk_rows, partial);
+  SCN_LAUNCH(k_bn_back_finalize, (unsigned)ceil_div(n_planes, 128), 128, 0, stream, partial, chunks, n_planes, n_rows, save_invstd, d_weight, d_bias, coef);
+  SCN_LAUNCH(k_bn_back_apply, (unsigned)ceil_div(n_rows * n_planes, 256), 256, 0, stream, in_features, d_in_features, out_features, d_out_features, n_rows, n_planes, in_stride, out_stride, save_mean, save_invstd, weight, coef, (float)leakiness);
+  SCN_CUDA_CHECK(cudaGetLastError());
+  SCN_TRY(device_free(partial, stream));
+  SCN_TRY(device_free(coef, stream));
   return SCN_OK;
 }
 
@@ -383,6 +553,130 @@ int scn_sparse_to_dense_forward(scn_metadata *md, const int64_t *spatial_size, c
   SCN_REQUIRE(in_features, SCN_ERR_BAD_ARG, "null features");
   long long total = g->n_active * n_planes;
   SCN_LAUNCH(k_sparse_to_dense, (unsigned)ceil_div(total, 256), 256, 0, stream, g->layout, g->row_keys, in_features, out_dense, g->n_active, n_planes, volume);
+  SCN_CUDA_CHECK(cudaGetLastError());
+  return SCN_OK;
+}
+
+/* ---- backward passes of the feature operators ------------------------------------------------ */
+
+int scn_input_layer_backward(scn_metadata *md, float *d_in_features, int64_t n_points,
+                             const float *d_out_features, int64_t n_sites, int n_planes, void *stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SCN_REQUIRE(md && md->input_mode >= 0, SCN_ERR_NO_GRID, "no input layer has been run on this metadata");
+  SCN_REQUIRE(n_points == md->input_n_rows && n_sites == md->input_n_active, SCN_ERR_SIZE_MISMATCH,
+              "input layer backward: got %lld points, %lld sites; metadata has %lld, %lld", (long long)n_points,
+              (long long)n_sites, md->input_n_rows, md->input_n_active);
+  SCN_REQUIRE(n_planes >= 1, SCN_ERR_BAD_ARG, "n_planes must be positive");
+  if (n_points == 0) return SCN_OK;
+  SCN_REQUIRE(d_in_features && (d_out_features || n_sites == 0), SCN_ERR_BAD_ARG, "null features");
+  const size_t bytes = sizeof(float) * (size_t)n_points * n_planes;
+  if (md->input_mode == 0) {
+    SCN_CUDA_CHECK(cudaMemcpyAsync(d_in_features, d_out_features, bytes, cudaMemcpyDeviceToDevice, stream));
+    return SCN_OK;
+  }
+  SCN_CUDA_CHECK(cudaMemsetAsync(d_in_features, 0, bytes, stream));
+  if (n_sites == 0) return SCN_OK;
+  long long total = (long long)n_sites * n_planes;
+  SCN_LAUNCH(k_output_features, (unsigned)ceil_div(total, 256), 256, 0, stream, d_out_features, d_in_features, md->input_csr_start, md->input_csr_rows, n_sites, n_planes, md->input_mode, md->input_mode == 4 ? 1 : 0);
+  SCN_CUDA_CHECK(cudaGetLastError());
+  return SCN_OK;
+}
+
+int scn_output_layer_backward(scn_metadata *md, float *d_in_features, int64_t n_sites,
+                              const float *d_out_features, int64_t n_points, int n_planes, void *stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SCN_REQUIRE(md && md->input_mode >= 0, SCN_ERR_NO_GRID, "no input layer has been run on this metadata");
+  SCN_REQUIRE(n_points == md->input_n_rows && n_sites == md->input_n_active, SCN_ERR_SIZE_MISMATCH,
+              "output layer backward: got %lld points, %lld sites; metadata has %lld, %lld", (long long)n_points,
+              (long long)n_sites, md->input_n_rows, md->input_n_active);
+  SCN_REQUIRE(n_planes >= 1, SCN_ERR_BAD_ARG, "n_planes must be positive");
+  if (n_sites == 0) return SCN_OK;
+  SCN_REQUIRE(d_in_features && d_out_features, SCN_ERR_BAD_ARG, "null features");
+  if (md->input_mode == 0) {
+    SCN_CUDA_CHECK(cudaMemcpyAsync(d_in_features, d_out_features, sizeof(float) * (size_t)n_sites * n_planes,
+                                   cudaMemcpyDeviceToDevice, stream));
+    return SCN_OK;
+  }
+  // every site collects, unscaled, the gradients of the points its rule names (CPU/IOLayers.cpp:116-136)
+  const int mode = md->input_mode == 4 ? 3 : md->input_mode;
+  long long total = (long long)n_sites * n_planes;
+  SCN_LAUNCH(k_input_features, (unsigned)ceil_div(total, 256), 256, 0, stream, d_out_features, d_in_features, md->input_csr_start, md->input_csr_rows, n_sites, n_planes, mode);
+  SCN_CUDA_CHECK(cudaGetLastError());
+  return SCN_OK;
+}
+
+static int pool_backward(scn_metadata *md, int op, const int64_t *input_size, const int64_t *output_size,
+                         const int64_t *pool_size, const int64_t *pool_stride, const float *in_features,
+                         float *d_in_features, const float *out_features, const float *d_out_features,
+                         int n_planes_in, int n_features_to_drop, cudaStream_t stream) {
+  SCN_REQUIRE(md && input_size && output_size && pool_size && pool_stride, SCN_ERR_BAD_ARG, "null argument");
+  SCN_REQUIRE(n_features_to_drop >= 0 && n_features_to_drop < n_planes_in, SCN_ERR_BAD_ARG,
+              "n_features_to_drop %d not in [0, %d)", n_features_to_drop, n_planes_in);
+  Rulebook *rb = nullptr;
+  const int *table = nullptr;
+  long long n_rows = 0, n_other = 0;
+  if (op == 2) {  // UnPooling: input = coarse; rulebook of (fine = output_size) -> (coarse = input_size)
+    SCN_TRY(get_strided_rulebook(md, output_size, input_size, pool_size, pool_stride, stream, &rb));
+    table = rb->nbr;
+    n_rows = rb->n_out;
+    n_other = rb->n_in;
+  } else {
+    SCN_TRY(get_strided_rulebook(md, input_size, output_size, pool_size, pool_stride, stream, &rb));
+    SCN_TRY(rulebook_transposed(*rb, stream));
+    table = rb->tnbr;
+    n_rows = rb->n_in;
+    n_other = rb->n_out;
+  }
+  if (n_rows == 0) return SCN_OK;
+  SCN_REQUIRE(d_in_features && (d_out_features || n_other == 0), SCN_ERR_BAD_ARG, "null gradient");
+  SCN_REQUIRE(op != 0 || (in_features && (out_features || n_other == 0)), SCN_ERR_BAD_ARG, "null features");
+  long long total = n_rows * n_planes_in;
+  unsigned blocks = (unsigned)ceil_div(total, 256);
+  if (op == 0)
+    SCN_LAUNCH(k_pool_backward<0>, blocks, 256, 0, stream, in_features, d_in_features, out_features, d_out_features, table, n_rows, n_other, rb->n_offsets, n_planes_in, n_features_to_drop, md->flags_dev);
+  else if (op == 1)
+    SCN_LAUNCH(k_pool_backward<1>, blocks, 256, 0, stream, in_features, d_in_features, out_features, d_out_features, table, n_rows, n_other, rb->n_offsets, n_planes_in, n_features_to_drop, md->flags_dev);
+  else
+    SCN_LAUNCH(k_pool_backward<2>, blocks, 256, 0, stream, in_features, d_in_features, out_features, d_out_features, table, n_rows, n_other, rb->n_offsets, n_planes_in, n_features_to_drop, md->flags_dev);
+  SCN_CUDA_CHECK(cudaGetLastError());
+  return SCN_OK;
+}
+
+int scn_max_pooling_backward(scn_metadata *md, const int64_t *input_size, const int64_t *output_size,
+                             const int64_t *pool_size, const int64_t *pool_stride, const float *in_features,
+                             float *d_in_features, const float *out_features, const float *d_out_features,
+                             int n_planes_in, int n_features_to_drop, void *stream) {
+  return pool_backward(md, 0, input_size, output_size, pool_size, pool_stride, in_features, d_in_features,
+                       out_features, d_out_features, n_planes_in, n_features_to_drop, (cudaStream_t)stream);
+}
+
+int scn_average_pooling_backward(scn_metadata *md, const int64_t *input_size, const int64_t *output_size,
+                                 const int64_t *pool_size, const int64_t *pool_stride, float *d_in_features,
+                                 const float *d_out_features, int n_planes_in, int n_features_to_drop,
+                                 void *stream) {
+  return pool_backward(md, 1, input_size, output_size, pool_size, pool_stride, nullptr, d_in_features, nullptr,
+                       d_out_features, n_planes_in, n_features_to_drop, (cudaStream_t)stream);
+}
+
+int scn_unpooling_backward(scn_metadata *md, const int64_t *input_size, const int64_t *output_size,
+                           const int64_t *pool_size, const int64_t *pool_stride, float *d_in_features,
+                           const float *d_out_features, int n_planes_in, int n_features_to_drop, void *stream) {
+  return pool_backward(md, 2, input_size, output_size, pool_size, pool_stride, nullptr, d_in_features, nullptr,
+                       d_out_features, n_planes_in, n_features_to_drop, (cudaStream_t)stream);
+}
+
+int scn_sparse_to_dense_backward(scn_metadata *md, const int64_t *spatial_size, float *d_in_features,
+                                 const float *d_out_dense, int n_planes, void *stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SCN_REQUIRE(md && spatial_size, SCN_ERR_BAD_ARG, "null argument");
+  Grid *g = find_grid(md, spatial_size);
+  SCN_REQUIRE(g, SCN_ERR_NO_GRID, "no grid for that spatial size");
+  if (g->n_active == 0) return SCN_OK;
+  SCN_REQUIRE(d_in_features && d_out_dense, SCN_ERR_BAD_ARG, "null gradient");
+  long long volume = 1;
+  for (int d = 0; d < md->dim; ++d) volume *= spatial_size[d];
+  long long total = g->n_active * n_planes;
+  SCN_LAUNCH(k_dense_to_sparse_grad, (unsigned)ceil_div(total, 256), 256, 0, stream, g->layout, g->row_keys, d_out_dense, d_in_features, g->n_active, n_planes, volume);
   SCN_CUDA_CHECK(cudaGetLastError());
   return SCN_OK;
 }

@@ -12,7 +12,7 @@ import torch
 from torch.nn import Module, Parameter
 
 import sparseconvnet_b200 as _pkg
-from . import SCN
+from . import SCN, autograd
 from .sparse_tensor import SparseConvNetTensor, optional_tensor, to_long_tensor
 
 
@@ -50,10 +50,18 @@ class InputLayer(Module):
             raise RuntimeError("InputLayer: features must be on a CUDA device (or call .to(device) on "
                                "the layer): sparseconvnet_b200 has no CPU path")
         output = SparseConvNetTensor(metadata=_pkg.Metadata(self.dimension), spatial_size=self.spatial_size)
-        output.features = features.new_empty(0)
-        SCN.InputLayer_updateOutput(output.metadata, self.spatial_size, coords.long(),
-                                    features.detach().float().contiguous(), output.features,
-                                    0 if len(input) == 2 else input[2], self.mode)
+        batch_size = 0 if len(input) == 2 else input[2]
+
+        def run(f):
+            out = f.new_empty(0)
+            SCN.InputLayer_updateOutput(output.metadata, self.spatial_size, coords.long(),
+                                        f.detach().float().contiguous(), out, batch_size, self.mode)
+            return out
+
+        if autograd.needs_grad(features):
+            output.features = autograd.input_features(features, output.metadata, run)
+        else:
+            output.features = run(features)
         return output
 
     def input_spatial_size(self, out_size):
@@ -74,6 +82,8 @@ class OutputLayer(Module):
         self.dimension = dimension
 
     def forward(self, input):
+        if autograd.needs_grad(input.features):
+            return autograd.output_features(input.features, input.metadata, False)
         output = input.features.new_empty(0)
         SCN.OutputLayer_updateOutput(input.metadata, input.features.detach().contiguous(), output)
         return output
@@ -109,9 +119,16 @@ class BLInputLayer(Module):
             raise RuntimeError("BLInputLayer: features must be on a CUDA device (or call .to(device) on "
                                "the layer): sparseconvnet_b200 has no CPU path")
         output = SparseConvNetTensor(metadata=_pkg.Metadata(self.dimension), spatial_size=self.spatial_size)
-        output.features = features.new_empty(0)
-        SCN.BLInputLayer_updateOutput(output.metadata, self.spatial_size, coords.long(),
-                                      features.detach().float().contiguous(), output.features, self.mode)
+        def run(f):
+            out = f.new_empty(0)
+            SCN.BLInputLayer_updateOutput(output.metadata, self.spatial_size, coords.long(),
+                                          f.detach().float().contiguous(), out, self.mode)
+            return out
+
+        if autograd.needs_grad(features):
+            output.features = autograd.input_features(features, output.metadata, run)
+        else:
+            output.features = run(features)
         return output
 
     def input_spatial_size(self, out_size):
@@ -129,6 +146,8 @@ class BLOutputLayer(Module):
         self.dimension = dimension
 
     def forward(self, input):
+        if autograd.needs_grad(input.features):
+            return autograd.output_features(input.features, input.metadata, True)
         output = input.features.new_empty(0)
         SCN.BLOutputLayer_updateOutput(input.metadata, input.features.detach().contiguous(), output)
         return output
@@ -167,10 +186,16 @@ class SubmanifoldConvolution(_ConvBase):
     def forward(self, input):
         assert input.features.nelement() == 0 or input.features.size(1) == self.nIn, (self.nIn, self.nOut, input)
         output = SparseConvNetTensor(metadata=input.metadata, spatial_size=input.spatial_size)
-        output.features = input.features.new_empty(0)
-        macs = SCN.SubmanifoldConvolution_updateOutput(
-            input.spatial_size, self.filter_size, input.metadata, input.features.detach().contiguous(),
-            output.features, self.weight, optional_tensor(self, "bias"))
+        bias = optional_tensor(self, "bias")
+        if autograd.needs_grad(input.features, self.weight, bias):
+            output.features, macs = autograd.convolution(
+                autograd.SUBMANIFOLD, input.features, self.weight, bias.to(self.weight.device), input.metadata,
+                input.spatial_size, None, self.filter_size, None)
+        else:
+            output.features = input.features.new_empty(0)
+            macs = SCN.SubmanifoldConvolution_updateOutput(
+                input.spatial_size, self.filter_size, input.metadata, input.features.detach().contiguous(),
+                output.features, self.weight, bias)
         self._count(macs, output.features)
         return output
 
@@ -197,10 +222,16 @@ class Convolution(_ConvBase):
         assert ((out_size - 1) * self.filter_stride + self.filter_size == input.spatial_size).all(), \
             (input.spatial_size, out_size, self.filter_size, self.filter_stride)
         output = SparseConvNetTensor(metadata=input.metadata, spatial_size=out_size)
-        output.features = input.features.new_empty(0)
-        macs = SCN.Convolution_updateOutput(
-            input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata,
-            input.features.detach().contiguous(), output.features, self.weight, optional_tensor(self, "bias"))
+        bias = optional_tensor(self, "bias")
+        if autograd.needs_grad(input.features, self.weight, bias):
+            output.features, macs = autograd.convolution(
+                autograd.STRIDED, input.features, self.weight, bias.to(self.weight.device), input.metadata,
+                input.spatial_size, out_size, self.filter_size, self.filter_stride)
+        else:
+            output.features = input.features.new_empty(0)
+            macs = SCN.Convolution_updateOutput(
+                input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata,
+                input.features.detach().contiguous(), output.features, self.weight, bias)
         self._count(macs, output.features)
         return output
 
@@ -222,10 +253,16 @@ class Deconvolution(_ConvBase):
         assert input.features.nelement() == 0 or input.features.size(1) == self.nIn
         out_size = (input.spatial_size - 1) * self.filter_stride + self.filter_size
         output = SparseConvNetTensor(metadata=input.metadata, spatial_size=out_size)
-        output.features = input.features.new_empty(0)
-        macs = SCN.Deconvolution_updateOutput(
-            input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata,
-            input.features.detach().contiguous(), output.features, self.weight, optional_tensor(self, "bias"))
+        bias = optional_tensor(self, "bias")
+        if autograd.needs_grad(input.features, self.weight, bias):
+            output.features, macs = autograd.convolution(
+                autograd.TRANSPOSED, input.features, self.weight, bias.to(self.weight.device), input.metadata,
+                input.spatial_size, out_size, self.filter_size, self.filter_stride)
+        else:
+            output.features = input.features.new_empty(0)
+            macs = SCN.Deconvolution_updateOutput(
+                input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata,
+                input.features.detach().contiguous(), output.features, self.weight, bias)
         self._count(macs, output.features)
         return output
 
@@ -260,6 +297,13 @@ class BatchNormalization(Module):
             return input
         assert input.features.size(1) == self.nPlanes, (self.nPlanes, input.features.shape)
         output = SparseConvNetTensor(metadata=input.metadata, spatial_size=input.spatial_size)
+        weight, bias = optional_tensor(self, "weight"), optional_tensor(self, "bias")
+        if autograd.needs_grad(input.features, weight, bias):
+            dev = input.features.device
+            output.features = autograd.batchnorm(input.features, weight.to(dev), bias.to(dev), self.running_mean,
+                                                 self.running_var, self.eps, self.momentum, self.training,
+                                                 self.leakiness)
+            return output
         output.features = input.features.new_empty(0)
         save_mean = input.features.new_empty(self.nPlanes)
         save_invstd = input.features.new_empty(self.nPlanes)
@@ -309,6 +353,10 @@ class MaxPooling(Module):
         out_size = torch.div(input.spatial_size - self.pool_size, self.pool_stride, rounding_mode="trunc") + 1
         assert ((out_size - 1) * self.pool_stride + self.pool_size == input.spatial_size).all()
         output = SparseConvNetTensor(metadata=input.metadata, spatial_size=out_size)
+        if autograd.needs_grad(input.features):
+            output.features = autograd.pooling("max", input.features, input.metadata, input.spatial_size, out_size,
+                                               self.pool_size, self.pool_stride, self.nFeaturesToDrop)
+            return output
         output.features = input.features.new_empty(0)
         SCN.MaxPooling_updateOutput(input.spatial_size, out_size, self.pool_size, self.pool_stride,
                                     input.metadata, input.features.detach().contiguous(), output.features,
@@ -337,6 +385,10 @@ class AveragePooling(Module):
         out_size = torch.div(input.spatial_size - self.pool_size, self.pool_stride, rounding_mode="trunc") + 1
         assert ((out_size - 1) * self.pool_stride + self.pool_size == input.spatial_size).all()
         output = SparseConvNetTensor(metadata=input.metadata, spatial_size=out_size)
+        if autograd.needs_grad(input.features):
+            output.features = autograd.pooling("avg", input.features, input.metadata, input.spatial_size, out_size,
+                                               self.pool_size, self.pool_stride, self.nFeaturesToDrop)
+            return output
         output.features = input.features.new_empty(0)
         SCN.AveragePooling_updateOutput(input.spatial_size, out_size, self.pool_size, self.pool_stride,
                                         input.metadata, input.features.detach().contiguous(), output.features,
@@ -364,6 +416,10 @@ class UnPooling(Module):
     def forward(self, input):
         out_size = (input.spatial_size - 1) * self.pool_stride + self.pool_size
         output = SparseConvNetTensor(metadata=input.metadata, spatial_size=out_size)
+        if autograd.needs_grad(input.features):
+            output.features = autograd.pooling("unpool", input.features, input.metadata, input.spatial_size, out_size,
+                                               self.pool_size, self.pool_stride, self.nFeaturesToDrop)
+            return output
         output.features = input.features.new_empty(0)
         SCN.UnPooling_updateOutput(input.spatial_size, out_size, self.pool_size, self.pool_stride,
                                    input.metadata, input.features.detach().contiguous(), output.features,
@@ -386,6 +442,8 @@ class SparseToDense(Module):
         self.nPlanes = nPlanes
 
     def forward(self, input):
+        if autograd.needs_grad(input.features):
+            return autograd.sparse_to_dense(input.features, input.metadata, input.spatial_size, self.nPlanes)
         output = input.features.new_empty(0)
         SCN.SparseToDense_updateOutput(input.spatial_size, input.metadata,
                                        input.features.detach().contiguous(), output, self.nPlanes)
@@ -413,6 +471,15 @@ class NetworkInNetwork(Module):
     def forward(self, input):
         assert input.features.nelement() == 0 or input.features.size(1) == self.nIn
         output = SparseConvNetTensor(metadata=input.metadata, spatial_size=input.spatial_size)
+        if autograd.needs_grad(input.features, self.weight):
+            # a dense matrix product: torch's own autograd covers it (the reference calls addmm as well)
+            output.features = input.features @ self.weight
+            if hasattr(self, "bias"):
+                output.features = output.features + self.bias
+            macs = float(input.features.size(0) * self.nIn * self.nOut)
+            _pkg.forward_pass_multiplyAdd_count += macs
+            _pkg.forward_pass_hidden_states += output.features.nelement()
+            return output
         output.features = input.features.new_empty(0)
         macs = SCN.NetworkInNetwork_updateOutput(input.features.detach().contiguous(), output.features,
                                                  self.weight, optional_tensor(self, "bias"))
