@@ -32,11 +32,11 @@ CONFIG = 3
 ROOMS_PER_GPU = 8
 METRIC = "unet3d_voxels_per_sec"
 UNIT = "voxels/s"
-# DRAM bytes per launch of the dominant kernel (k_conv_tma) as a multiple of the algorithmic bytes
-# of that launch: 75 MB measured against 343 MB counted per launch in the 4-room capture
-# (profiles/k_conv_tma_tf32x3_unet3d_4rooms.md); the traffic grows with the rows, like the
-# algorithmic bytes.  Only applied when that kernel is the dominant one.
-TRAFFIC_RATIO = 0.22
+# DRAM bytes per launch of the dominant kernel as a multiple of the algorithmic bytes of that
+# launch, from the committed ncu captures (profiles/): k_conv_tma 75 MB against 343 MB per launch
+# (4-room case, 18 launches); k_conv_pipe 553 MB against 2.18 GB (32->32) and 768 MB against
+# 4.03 GB (64->32) at 8 rooms.  The traffic grows with the rows, like the algorithmic bytes.
+TRAFFIC_RATIO = {"k_conv_tma": 0.22, "k_conv_pipe_mma": 0.22, "k_conv_simt": 0.25}
 
 
 def workload_name(rooms=ROOMS_PER_GPU):
@@ -399,7 +399,7 @@ def main():
                            "rules_strided": "k_strided_*", "input_hash": "k_insert_input"}.get(top, top),
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "peak_source": peak_src, "frac_of_nominal_7700": achieved / 7700.0,
-                "traffic": (TRAFFIC_RATIO * a["bytes"] / a["calls"]) if (TRAFFIC_RATIO and top == "k_conv_tma") else None,
+                "traffic": (TRAFFIC_RATIO[top] * a["bytes"] / a["calls"]) if top in TRAFFIC_RATIO else None,
                 "algorithmic_bytes_per_step": a["bytes"], "launches_per_step": a["calls"], "ms_per_step": a["ms"],
                 "tflops": a["flops"] / (a["ms"] / 1e3) / 1e12 if a["flops"] else None}
     if a["flops"]:
@@ -408,8 +408,11 @@ def main():
         tpeak, tsrc = tensor_peak_tflops()
         roofline["tensor"] = {"achieved": roofline["tflops"], "peak": tpeak, "unit": "TFLOP/s",
                               "frac": roofline["tflops"] / tpeak, "peak_source": tsrc}
-    roofline["limiter"] = ("shared-memory data pipe (ncu: 77 % busy, tensor pipe 40-46 %), see "
-                           "profiles/k_conv_tma_tf32x3_unet3d_4rooms.md") if top == "k_conv_tma" else None
+    roofline["limiter"] = {
+        "k_conv_tma": "shared-memory data pipe (ncu: 77 % busy, tensor pipe 40-46 %), see "
+                      "profiles/k_conv_tma_tf32x3_unet3d_4rooms.md",
+        "k_conv_pipe_mma": "instruction issue and shared-memory data pipe of small (offset, 128-row) steps, see "
+                           "profiles/k_conv_pipe_unet3d_8rooms.md"}.get(top)
     breakdown = {k: {"ms": round(v["ms"], 4), "calls": v["calls"],
                      "GBps": round(v["bytes"] / (v["ms"] / 1e3) / 1e9, 1) if v["ms"] > 0 else None}
                  for k, v in sorted(agg.items(), key=lambda kv: -kv[1]["ms"])}

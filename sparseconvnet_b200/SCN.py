@@ -319,7 +319,7 @@ def SubmanifoldConvolution_updateOutput(inputSize, filterSize, m, input_features
                 m._h, sizes(inputSize), sizes(filterSize), _ptr(f), _ptr(output_features), _ptr(w), _ptr(b),
                 groups * cin, groups * cout, groups, _precision, _stream(), C.byref(macs)))
             info["macs"] = macs.value
-            info["kernel"] = ("k_conv_simt", "k_conv_tc", "k_conv_tma")[lib.scn_last_conv_kernel()]
+            info["kernel"] = ("k_conv_simt", "k_conv_tc", "k_conv_tma", "k_conv_pipe_mma")[lib.scn_last_conv_kernel()]
     return macs.value
 
 
@@ -345,7 +345,7 @@ def Convolution_updateOutput(inputSize, outputSize, filterSize, filterStride, m,
                 _ptr(output_features), _ptr(w), _ptr(b), groups * cin, groups * cout, groups, _precision,
                 _stream(), C.byref(macs)))
             info["macs"] = macs.value
-            info["kernel"] = ("k_conv_simt", "k_conv_tc", "k_conv_tma")[lib.scn_last_conv_kernel()]
+            info["kernel"] = ("k_conv_simt", "k_conv_tc", "k_conv_tma", "k_conv_pipe_mma")[lib.scn_last_conv_kernel()]
     return macs.value
 
 
@@ -370,7 +370,7 @@ def Deconvolution_updateOutput(inputSize, outputSize, filterSize, filterStride, 
                 _ptr(output_features), _ptr(w), _ptr(b), groups * cin, groups * cout, groups, _precision,
                 _stream(), C.byref(macs)))
             info["macs"] = macs.value
-            info["kernel"] = ("k_conv_simt", "k_conv_tc", "k_conv_tma")[lib.scn_last_conv_kernel()]
+            info["kernel"] = ("k_conv_simt", "k_conv_tc", "k_conv_tma", "k_conv_pipe_mma")[lib.scn_last_conv_kernel()]
     return macs.value
 
 

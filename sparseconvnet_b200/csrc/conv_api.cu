@@ -16,6 +16,11 @@ int conv_forward_tma(const float *in, long long n_in, float *out, long long n_ou
                      const float *bias, const int *table, int K, int cin, int cout, int precision, int *flags,
                      cudaStream_t stream);
 bool conv_tma_supported(int K, int cin, int cout, int groups, int precision, long long n_in);
+bool conv_pipe_supported(const float *in, const float *out, const float *weight, const float *bias, int K, int cin,
+                         int cout);
+int conv_forward_pipe(const float *in, long long n_in, float *out, long long n_out, const float *weight,
+                      const float *bias, const int *table, int K, int cin, int cout, int groups, int three_pass_mma,
+                      int *flags, cudaStream_t stream);
 
 static thread_local int g_last_kernel = -1;
 
@@ -42,17 +47,23 @@ static int run_conv(scn_metadata *md, Rulebook &rb, bool transposed, const float
       SCN_TRY(device_alloc((void **)&md->flags_dev, sizeof(int), stream));
       SCN_CUDA_CHECK(cudaMemsetAsync(md->flags_dev, 0, sizeof(int), stream));
     }
-    // TF32X3 is the fp32-accuracy mode: each shape runs whichever fp32-class kernel is faster.
-    // Below 64 output planes the three-pass tensor-core tile (its cost per 8 input planes and 256
-    // rows is fixed, whatever Cout) does not beat the fp32 FMA kernel, so narrow layers keep it
-    // (SCN_X3_MIN_COUT moves the threshold).
-    const int x3_min_cout = getenv("SCN_X3_MIN_COUT") ? atoi(getenv("SCN_X3_MIN_COUT")) : 64;
+    // TF32X3 is the fp32-accuracy mode: each shape runs whichever fp32-class kernel is fastest.
+    // Up to 64 output planes that is the pipelined kernel of conv_pipe.cu with its arithmetic on
+    // the warp-level tensor path (three tf32 mma.sync passes on compacted 16-pair tiles): the
+    // tcgen05 tile costs the same per 8 input planes and 256 rows whatever Cout and however few
+    // of the rows have a rule.  SCN_X3_MIN_COUT moves the threshold (layers with fewer output
+    // planes than it stay off tcgen05).
+    const int x3_min_cout = getenv("SCN_X3_MIN_COUT") ? atoi(getenv("SCN_X3_MIN_COUT")) : 65;
     const bool narrow_x3 = precision == SCN_PRECISION_TF32X3 && cout < x3_min_cout;
     // The persistent kernel runs one CTA per SM over whole tiles; with fewer tiles than SMs the
     // per-tile kernel is used instead, which splits a tile's filter offsets over several CTAs.
     const bool force_persistent = getenv("SCN_TC_PERSISTENT") && atoi(getenv("SCN_TC_PERSISTENT")) != 0;
     const bool few_tiles = rows_out <= 148 * 256 && !force_persistent;
-    if (precision != SCN_PRECISION_FP32 && !narrow_x3 && !few_tiles &&
+    if (narrow_x3 && cin % 8 == 0 && conv_pipe_supported(in, out, weight, bias, rb.n_offsets, cin, cout)) {
+      SCN_TRY(conv_forward_pipe(in, rows_in, out, rows_out, weight, bias, table, rb.n_offsets, cin, cout, groups, 1,
+                                md->flags_dev, stream));
+      g_last_kernel = SCN_KERNEL_CONV_PIPE_MMA;
+    } else if (precision != SCN_PRECISION_FP32 && !narrow_x3 && !few_tiles &&
         conv_tma_supported(rb.n_offsets, cin, cout, groups, precision, rows_in)) {
       SCN_TRY(conv_forward_tma(in, rows_in, out, rows_out, weight, bias, table, rb.n_offsets, cin, cout,
                                precision, md->flags_dev, stream));

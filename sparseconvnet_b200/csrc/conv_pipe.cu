@@ -20,6 +20,8 @@
 //
 // Output rows are written once, bias added.  Needs 16-byte aligned rows (cin, cout multiples of
 // 4) and at most 32 filter offsets; conv_simt.cu keeps the general kernel.
+#include <stdlib.h>
+
 #include <algorithm>
 
 #include "metadata.cuh"
@@ -41,9 +43,9 @@ constexpr int kPMaxGroups = 2 * kPMaxK;  // (offset, batch of <= 64 pairs) group
 
 template <int NPL>
 struct PipeSmem {
-  float acc[kPRows][NPL * 8];                // tile accumulator
+  float acc[kPRows][NPL * 8 + 4];            // tile accumulator; +4: the rows a warp folds into spread over the banks
   float a[kPStages][kPCap][kPAStride];       // gathered input rows of a step: [pair][plane]
-  float w[kPStages][kPChunk][NPL * 8];       // W[k][c0 .. c0+32][n0 .. n0+BN]
+  float w[kPStages][kPChunk][NPL * 8];       // W[k][c0 .. c0+32][n0 .. n0+BN], column n of row r at n ^ ((r & 3) << 3)
   int cnt[kPMaxK];                           // pairs per offset
   int groups[kPMaxGroups];                   // offset | first pair << 8 | pairs << 16, in execution order
   int n_groups;
@@ -56,7 +58,8 @@ static size_t pipe_smem_bytes(int npl, int K) {
 }
 
 template <int PM, int NPL>
-__device__ __forceinline__ void pipe_chunk(float (&acc)[4][NPL], const float *a_thr, const float *w_thr, int kmax) {
+__device__ __forceinline__ void pipe_chunk(float (&acc)[4][NPL], const float *a_thr, const float *w_row0, int col0,
+                                           int kmax) {
   constexpr int WS = NPL * 8;
 #pragma unroll 2
   for (int kk = 0; kk < kmax; kk += 4) {
@@ -64,7 +67,8 @@ __device__ __forceinline__ void pipe_chunk(float (&acc)[4][NPL], const float *a_
 #pragma unroll
     for (int q = 0; q < 4; ++q)
 #pragma unroll
-      for (int h = 0; h < NPL / 4; ++h) w[q][h] = *reinterpret_cast<const float4 *>(w_thr + (kk + q) * WS + h * 32);
+      for (int h = 0; h < NPL / 4; ++h)  // columns of row r are stored at col ^ ((r & 3) << 3); kk % 4 == 0
+        w[q][h] = *reinterpret_cast<const float4 *>(w_row0 + (kk + q) * WS + ((h * 32 + col0) ^ (q << 3)));
 #pragma unroll
     for (int j = 0; j < PM; ++j) {
       const float4 a4 = *reinterpret_cast<const float4 *>(a_thr + j * 16 * kPAStride + kk);
@@ -92,7 +96,61 @@ __device__ __forceinline__ void pipe_chunk(float (&acc)[4][NPL], const float *a_
   }
 }
 
-template <int NPL>
+// ---- warp-level tensor path (three tf32 passes) on the same pipeline ---------------------------
+// D(16x8, fp32) += A(16x8, tf32, row) * B(8x8, tf32, col); lane = 4 g + t holds
+//   a0 A[g][t] a1 A[g+8][t] a2 A[g][t+4] a3 A[g+8][t+4], b0 B[t][g] b1 B[t+4][g],
+//   d0 D[g][2t] d1 D[g][2t+1] d2 D[g+8][2t] d3 D[g+8][2t+1].
+__device__ __forceinline__ void mma_m16n8k8_tf32(float (&d)[4], const unsigned (&a)[4], const unsigned (&b)[2]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+__device__ __forceinline__ void split_tf32(float x, unsigned &hi, unsigned &lo) {
+  hi = __float_as_uint(x) & 0xFFFFE000u;
+  lo = __float_as_uint(x - __uint_as_float(hi));
+}
+
+// One chunk: MT tiles of 16 pairs x the warp's NT tiles of 8 planes (planes n_w .. n_w + 8 NT).
+template <int MT, int NT>
+__device__ __forceinline__ void pipe_chunk_mma(float (&d)[4][NT][4], const float *a_stage, const float *w_row0,
+                                               int WS, int n_w, int kmax, int lane) {
+  const int g = lane >> 2, t = lane & 3;
+  for (int k0 = 0; k0 < kmax; k0 += 8) {
+    unsigned bh[NT][2], bl[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int col = (n_w + nt * 8 + g) ^ (t << 3);  // rows k0+t and k0+t+4 share (r & 3) = t
+      split_tf32(w_row0[(k0 + t) * WS + col], bh[nt][0], bl[nt][0]);
+      split_tf32(w_row0[(k0 + t + 4) * WS + col], bh[nt][1], bl[nt][1]);
+    }
+    // all fragments first, then the three passes tile by tile: consecutive instructions write
+    // different accumulators
+    unsigned ah[MT][4], al[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      const float *ap = a_stage + (mt * 16 + g) * kPAStride + k0 + t;
+      split_tf32(ap[0], ah[mt][0], al[mt][0]);
+      split_tf32(ap[8 * kPAStride], ah[mt][1], al[mt][1]);
+      split_tf32(ap[4], ah[mt][2], al[mt][2]);
+      split_tf32(ap[8 * kPAStride + 4], ah[mt][3], al[mt][3]);
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) mma_m16n8k8_tf32(d[mt][nt], al[mt], bh[nt]);
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) mma_m16n8k8_tf32(d[mt][nt], ah[mt], bl[nt]);
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) mma_m16n8k8_tf32(d[mt][nt], ah[mt], bh[nt]);
+  }
+}
+
+template <int NPL, bool MMA>
 __global__ void __launch_bounds__(kPThreads)
 k_conv_pipe(const float *__restrict__ in, int ld_in, long long n_in, float *__restrict__ out, int ld_out,
             long long n_out, const float *__restrict__ weight, long long w_offset_stride,
@@ -117,7 +175,7 @@ k_conv_pipe(const float *__restrict__ in, int ld_in, long long n_in, float *__re
   if (bias) bias += (long long)g * cout;
 
   // ---- prologue: pair lists of every offset ---------------------------------------------------
-  for (int i = tid; i < kPRows * BN / 4; i += kPThreads)
+  for (int i = tid; i < kPRows * (BN + 4) / 4; i += kPThreads)
     reinterpret_cast<float4 *>(&S.acc[0][0])[i] = make_float4(0.f, 0.f, 0.f, 0.f);
   {
     constexpr int kPer = kPMaxK / 4;  // offsets per warp
@@ -191,7 +249,7 @@ k_conv_pipe(const float *__restrict__ in, int ld_in, long long n_in, float *__re
       for (int i = 0; i < kPChunk / RSTEP; ++i) {
         const int r = w_r0 + i * RSTEP;
         const bool ok = w_col_ok && r < rows_left;
-        cp_async16(smem_u32(&S.w[stage][r][w_cc]), ok ? wk + (long long)i * RSTEP * cout : weight, ok ? 16u : 0u);
+        cp_async16(smem_u32(&S.w[stage][r][w_cc ^ ((r & 3) << 3)]), ok ? wk + (long long)i * RSTEP * cout : weight, ok ? 16u : 0u);
       }
       const int c0 = c * kPChunk + tx * 4;
       if (c0 < cin) {
@@ -219,7 +277,8 @@ k_conv_pipe(const float *__restrict__ in, int ld_in, long long n_in, float *__re
     advance_issue();
   }
 
-  float acc[4][NPL];
+  float acc[4][NPL];          // FMA micro-tile
+  float dm[4][BN / 32][4];    // MMA fragments
   int stage = 0, gc = 0, c = 0;  // stage, group and chunk of the step being computed
   for (int s = 0; s < n_steps; ++s) {
     cp_async_wait<kPStages - 2>();  // all but the newest kPStages - 2 groups: the copies of step s have landed
@@ -231,35 +290,75 @@ k_conv_pipe(const float *__restrict__ in, int ld_in, long long n_in, float *__re
     const int k = d & 0xFF, base = (d >> 8) & 0xFF, P = d >> 16;
     const int pm = (P + 15) >> 4;
     const int kmax = min(kPChunk, cin - c * kPChunk);
-    if (c == 0) {
+    if (!MMA) {
+      if (c == 0) {
+  #pragma unroll
+        for (int j = 0; j < 4; ++j)
+  #pragma unroll
+          for (int e = 0; e < NPL; ++e) acc[j][e] = 0.f;
+      }
+      const float *a_thr = &S.a[stage][ty][0];
+      const float *w_row0 = &S.w[stage][0][0];
+      switch (pm) {
+        case 1: pipe_chunk<1, NPL>(acc, a_thr, w_row0, tx * 4, kmax); break;
+        case 2: pipe_chunk<2, NPL>(acc, a_thr, w_row0, tx * 4, kmax); break;
+        case 3: pipe_chunk<3, NPL>(acc, a_thr, w_row0, tx * 4, kmax); break;
+        default: pipe_chunk<4, NPL>(acc, a_thr, w_row0, tx * 4, kmax); break;
+      }
+      if (c == nch - 1) {
+        const unsigned char *pr = &prow[k][base];
+  #pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int p = j * 16 + ty;
+          if (p < P) {
+            float *dst = &S.acc[pr[p]][tx * 4];
+  #pragma unroll
+            for (int h = 0; h < NPL / 4; ++h) {
+              float4 t = *reinterpret_cast<float4 *>(dst + h * 32);
+              t.x += acc[j][h * 4 + 0];
+              t.y += acc[j][h * 4 + 1];
+              t.z += acc[j][h * 4 + 2];
+              t.w += acc[j][h * 4 + 3];
+              *reinterpret_cast<float4 *>(dst + h * 32) = t;
+            }
+          }
+        }
+      }
+    } else {
+      constexpr int NT = BN / 32;
+      if (c == 0) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
+        for (int mt = 0; mt < 4; ++mt)
 #pragma unroll
-        for (int e = 0; e < NPL; ++e) acc[j][e] = 0.f;
-    }
-    const float *a_thr = &S.a[stage][ty][0];
-    const float *w_thr_s = &S.w[stage][0][tx * 4];
-    switch (pm) {
-      case 1: pipe_chunk<1, NPL>(acc, a_thr, w_thr_s, kmax); break;
-      case 2: pipe_chunk<2, NPL>(acc, a_thr, w_thr_s, kmax); break;
-      case 3: pipe_chunk<3, NPL>(acc, a_thr, w_thr_s, kmax); break;
-      default: pipe_chunk<4, NPL>(acc, a_thr, w_thr_s, kmax); break;
-    }
-    if (c == nch - 1) {
-      const unsigned char *pr = &prow[k][base];
+          for (int nt = 0; nt < NT; ++nt) dm[mt][nt][0] = dm[mt][nt][1] = dm[mt][nt][2] = dm[mt][nt][3] = 0.f;
+      }
+      const float *a_stage = &S.a[stage][0][0];
+      const float *w_row0 = &S.w[stage][0][0];
+      const int n_w = warp * NT * 8;
+      switch (pm) {
+        case 1: pipe_chunk_mma<1, NT>(dm, a_stage, w_row0, BN, n_w, kmax, lane); break;
+        case 2: pipe_chunk_mma<2, NT>(dm, a_stage, w_row0, BN, n_w, kmax, lane); break;
+        case 3: pipe_chunk_mma<3, NT>(dm, a_stage, w_row0, BN, n_w, kmax, lane); break;
+        default: pipe_chunk_mma<4, NT>(dm, a_stage, w_row0, BN, n_w, kmax, lane); break;
+      }
+      if (c == nch - 1) {
+        const unsigned char *pr = &prow[k][base];
+        const int gq = lane >> 2, t2 = (lane & 3) * 2;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int p = j * 16 + ty;
-        if (p < P) {
-          float *dst = &S.acc[pr[p]][tx * 4];
+        for (int mt = 0; mt < 4; ++mt) {
 #pragma unroll
-          for (int h = 0; h < NPL / 4; ++h) {
-            float4 t = *reinterpret_cast<float4 *>(dst + h * 32);
-            t.x += acc[j][h * 4 + 0];
-            t.y += acc[j][h * 4 + 1];
-            t.z += acc[j][h * 4 + 2];
-            t.w += acc[j][h * 4 + 3];
-            *reinterpret_cast<float4 *>(dst + h * 32) = t;
+          for (int half = 0; half < 2; ++half) {
+            const int p = mt * 16 + half * 8 + gq;
+            if (mt < pm && p < P) {
+              float *dst = &S.acc[pr[p]][n_w + t2];
+#pragma unroll
+              for (int nt = 0; nt < NT; ++nt) {
+                float2 v = *reinterpret_cast<float2 *>(dst + nt * 8);
+                v.x += dm[mt][nt][half * 2 + 0];
+                v.y += dm[mt][nt][half * 2 + 1];
+                *reinterpret_cast<float2 *>(dst + nt * 8) = v;
+              }
+            }
           }
         }
       }
@@ -291,7 +390,7 @@ k_conv_pipe(const float *__restrict__ in, int ld_in, long long n_in, float *__re
   }
 }
 
-template <int NPL>
+template <int NPL, bool MMA>
 static int launch_pipe(const float *in, int ld_in, long long n_in, float *out, int ld_out, long long n_out,
                        const float *weight, const float *bias, const int *table, int K, int cin, int cout,
                        int groups, int *flags, cudaStream_t stream) {
@@ -300,11 +399,11 @@ static int launch_pipe(const float *in, int ld_in, long long n_in, float *out, i
   SCN_CUDA_CHECK(cudaGetDevice(&dev));
   const size_t smem = pipe_smem_bytes(NPL, K);
   if (dev >= 64 || configured[dev] < (int)smem) {
-    SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_pipe<NPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_pipe<NPL, MMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     if (dev < 64) configured[dev] = (int)smem;
   }
   dim3 grid((unsigned)ceil_div(n_out, (long long)kPRows), (unsigned)ceil_div(cout, NPL * 8), (unsigned)groups);
-  auto kernel = k_conv_pipe<NPL>;
+  auto kernel = k_conv_pipe<NPL, MMA>;
   SCN_LAUNCH(kernel, grid, kPThreads, smem, stream, in, ld_in, n_in, out, ld_out, n_out, weight, (long long)groups * cin * cout, (long long)cin * cout, bias, table, K, cin, cout, flags);
   SCN_CUDA_CHECK(cudaGetLastError());
   return SCN_OK;
@@ -317,14 +416,18 @@ bool conv_pipe_supported(const float *in, const float *out, const float *weight,
 }
 
 // out [n_out, groups*cout] = bias + sum_k in[table[k][.]] @ W[k]; cin / cout are per group.
+// three_pass_mma: the arithmetic runs as three tf32 mma.sync passes (fp32-class accuracy) instead of fp32 FMA.
 int conv_forward_pipe(const float *in, long long n_in, float *out, long long n_out, const float *weight,
-                      const float *bias, const int *table, int K, int cin, int cout, int groups, int *flags,
-                      cudaStream_t stream) {
+                      const float *bias, const int *table, int K, int cin, int cout, int groups, int three_pass_mma,
+                      int *flags, cudaStream_t stream) {
   if (n_out == 0) return SCN_OK;
   const int ld_in = cin * groups, ld_out = cout * groups;
+  const bool mma = three_pass_mma && cin % 8 == 0;
   if (cout <= 32)
-    return launch_pipe<4>(in, ld_in, n_in, out, ld_out, n_out, weight, bias, table, K, cin, cout, groups, flags, stream);
-  return launch_pipe<8>(in, ld_in, n_in, out, ld_out, n_out, weight, bias, table, K, cin, cout, groups, flags, stream);
+    return mma ? launch_pipe<4, true>(in, ld_in, n_in, out, ld_out, n_out, weight, bias, table, K, cin, cout, groups, flags, stream)
+               : launch_pipe<4, false>(in, ld_in, n_in, out, ld_out, n_out, weight, bias, table, K, cin, cout, groups, flags, stream);
+  return mma ? launch_pipe<8, true>(in, ld_in, n_in, out, ld_out, n_out, weight, bias, table, K, cin, cout, groups, flags, stream)
+             : launch_pipe<8, false>(in, ld_in, n_in, out, ld_out, n_out, weight, bias, table, K, cin, cout, groups, flags, stream);
 }
 
 }  // namespace scn

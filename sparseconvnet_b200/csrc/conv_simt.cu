@@ -24,8 +24,8 @@ namespace scn {
 bool conv_pipe_supported(const float *in, const float *out, const float *weight, const float *bias, int K, int cin,
                          int cout);
 int conv_forward_pipe(const float *in, long long n_in, float *out, long long n_out, const float *weight,
-                      const float *bias, const int *table, int K, int cin, int cout, int groups, int *flags,
-                      cudaStream_t stream);
+                      const float *bias, const int *table, int K, int cin, int cout, int groups, int three_pass_mma,
+                      int *flags, cudaStream_t stream);
 
 constexpr int kTileRows = 128;  // output rows per CTA
 constexpr int kChunk = 32;      // input planes staged per step
@@ -309,7 +309,7 @@ int conv_forward_simt(const float *in, long long n_in, float *out, long long n_o
   if (!block_kernel_only && conv_thin_supported(K, cin, groups))
     return conv_forward_thin(in, n_in, out, n_out, weight, bias, table, K, cin, cout, flags, stream);
   if (!block_kernel_only && conv_pipe_supported(in, out, weight, bias, K, cin, cout))
-    return conv_forward_pipe(in, n_in, out, n_out, weight, bias, table, K, cin, cout, groups, flags, stream);
+    return conv_forward_pipe(in, n_in, out, n_out, weight, bias, table, K, cin, cout, groups, 0, flags, stream);
   int ld_in = cin * groups, ld_out = cout * groups;
   if (cout <= 16)
     return launch_simt<16>(in, ld_in, n_in, out, ld_out, n_out, weight, bias, table, K, cin, cout, groups, flags, stream);
