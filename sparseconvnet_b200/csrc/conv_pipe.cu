@@ -116,7 +116,11 @@ template <int MT, int NT>
 __device__ __forceinline__ void pipe_chunk_mma(float (&d)[4][NT][4], const float *a_stage, const float *w_row0,
                                                int WS, int n_w, int kmax, int lane) {
   const int g = lane >> 2, t = lane & 3;
-  for (int k0 = 0; k0 < kmax; k0 += 8) {
+  // a whole 32-plane chunk is the common case: unrolled, so that the loads of the next 8 planes
+  // are issued ahead of this block's instructions
+#pragma unroll
+  for (int k0 = 0; k0 < kPChunk; k0 += 8) {
+    if (k0 >= kmax) break;
     unsigned bh[NT][2], bl[NT][2];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
