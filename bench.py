@@ -412,7 +412,7 @@ def main():
         "k_conv_tma": "shared-memory data pipe (ncu: 77 % busy, tensor pipe 40-46 %), see "
                       "profiles/k_conv_tma_tf32x3_unet3d_4rooms.md",
         "k_conv_pipe_mma": "instruction issue and shared-memory data pipe of small (offset, 128-row) steps, see "
-                           "profiles/k_conv_pipe_unet3d_8rooms.md"}.get(top)
+                           "profiles/k_conv_pipe_mma_unet3d_4and8rooms.md"}.get(top)
     breakdown = {k: {"ms": round(v["ms"], 4), "calls": v["calls"],
                      "GBps": round(v["bytes"] / (v["ms"] / 1e3) / 1e9, 1) if v["ms"] > 0 else None}
                  for k, v in sorted(agg.items(), key=lambda kv: -kv[1]["ms"])}
