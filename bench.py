@@ -35,8 +35,9 @@ UNIT = "voxels/s"
 # DRAM bytes per launch of the dominant kernel as a multiple of the algorithmic bytes of that
 # launch, from the committed ncu captures (profiles/): k_conv_tma 75 MB against 343 MB per launch
 # (4-room case, 18 launches); k_conv_pipe 553 MB against 2.18 GB (32->32) and 768 MB against
-# 4.03 GB (64->32) at 8 rooms.  The traffic grows with the rows, like the algorithmic bytes.
-TRAFFIC_RATIO = {"k_conv_tma": 0.22, "k_conv_pipe_mma": 0.22, "k_conv_simt": 0.25}
+# 4.03 GB (64->32) at 8 rooms; k_conv_rows 263 MB against 1.08 GB (32->32, 4 rooms).  The traffic
+# grows with the rows, like the algorithmic bytes.
+TRAFFIC_RATIO = {"k_conv_tma": 0.22, "k_conv_pipe_mma": 0.22, "k_conv_rows": 0.24, "k_conv_simt": 0.25}
 
 
 def workload_name(rooms=ROOMS_PER_GPU):
@@ -412,7 +413,9 @@ def main():
         "k_conv_tma": "shared-memory data pipe (ncu: 77 % busy, tensor pipe 40-46 %), see "
                       "profiles/k_conv_tma_tf32x3_unet3d_4rooms.md",
         "k_conv_pipe_mma": "instruction issue and shared-memory data pipe of small (offset, 128-row) steps, see "
-                           "profiles/k_conv_pipe_mma_unet3d_4and8rooms.md"}.get(top)
+                           "profiles/k_conv_pipe_mma_unet3d_4and8rooms.md",
+        "k_conv_rows": "warp-level tensor pipe 50 % busy; the rest is latency of the weight-fragment loads "
+                       "(L1 hit rate 41 %) and dependent issue, see profiles/k_conv_rows_unet3d_4rooms.md"}.get(top)
     breakdown = {k: {"ms": round(v["ms"], 4), "calls": v["calls"],
                      "GBps": round(v["bytes"] / (v["ms"] / 1e3) / 1e9, 1) if v["ms"] > 0 else None}
                  for k, v in sorted(agg.items(), key=lambda kv: -kv[1]["ms"])}

@@ -69,7 +69,8 @@ enum scn_conv_kernel {
   SCN_KERNEL_CONV_SIMT = 0,          /* k_conv_pipe / k_conv_simt / k_conv_thin: fp32 FMA     */
   SCN_KERNEL_CONV_TC = 1,            /* k_conv_tc: tcgen05, one tile per CTA                  */
   SCN_KERNEL_CONV_TC_PERSISTENT = 2, /* k_conv_tma: tcgen05, persistent, double-buffered TMEM */
-  SCN_KERNEL_CONV_PIPE_MMA = 3       /* k_conv_pipe with three tf32 mma.sync passes           */
+  SCN_KERNEL_CONV_PIPE_MMA = 3,      /* k_conv_pipe with three tf32 mma.sync passes           */
+  SCN_KERNEL_CONV_ROWS = 4           /* k_conv_rows: row-stationary, three tf32 mma.sync passes */
 };
 /* The tensor-core modes need groups == 1, n_in_planes % 32 == 0, n_out_planes % 16 == 0 and
  * n_out_planes <= 256; other shapes run the fp32 kernel whatever the precision says. */

@@ -17,6 +17,9 @@ import torch
 from . import _lib
 from ._lib import check, lib, sizes
 
+# scn_last_conv_kernel() -> name (enum scn_conv_kernel of include/scn_b200.h)
+_KERNEL_NAMES = ("k_conv_simt", "k_conv_tc", "k_conv_tma", "k_conv_pipe_mma", "k_conv_rows")
+
 PRECISION_FP32, PRECISION_TF32, PRECISION_BF16, PRECISION_TF32X3 = 0, 1, 2, 3
 _precision = PRECISION_FP32
 
@@ -319,7 +322,7 @@ def SubmanifoldConvolution_updateOutput(inputSize, filterSize, m, input_features
                 m._h, sizes(inputSize), sizes(filterSize), _ptr(f), _ptr(output_features), _ptr(w), _ptr(b),
                 groups * cin, groups * cout, groups, _precision, _stream(), C.byref(macs)))
             info["macs"] = macs.value
-            info["kernel"] = ("k_conv_simt", "k_conv_tc", "k_conv_tma", "k_conv_pipe_mma")[lib.scn_last_conv_kernel()]
+            info["kernel"] = _KERNEL_NAMES[lib.scn_last_conv_kernel()]
     return macs.value
 
 
@@ -345,7 +348,7 @@ def Convolution_updateOutput(inputSize, outputSize, filterSize, filterStride, m,
                 _ptr(output_features), _ptr(w), _ptr(b), groups * cin, groups * cout, groups, _precision,
                 _stream(), C.byref(macs)))
             info["macs"] = macs.value
-            info["kernel"] = ("k_conv_simt", "k_conv_tc", "k_conv_tma", "k_conv_pipe_mma")[lib.scn_last_conv_kernel()]
+            info["kernel"] = _KERNEL_NAMES[lib.scn_last_conv_kernel()]
     return macs.value
 
 
@@ -370,7 +373,7 @@ def Deconvolution_updateOutput(inputSize, outputSize, filterSize, filterStride, 
                 _ptr(output_features), _ptr(w), _ptr(b), groups * cin, groups * cout, groups, _precision,
                 _stream(), C.byref(macs)))
             info["macs"] = macs.value
-            info["kernel"] = ("k_conv_simt", "k_conv_tc", "k_conv_tma", "k_conv_pipe_mma")[lib.scn_last_conv_kernel()]
+            info["kernel"] = _KERNEL_NAMES[lib.scn_last_conv_kernel()]
     return macs.value
 
 

@@ -1,0 +1,291 @@
+// Sparse convolution with fp32-class accuracy on the warp-level tensor path, accumulators in
+// registers: the kernel for narrow layers (32 or 64 output planes) with many rows.
+//
+// Same mathematics and the same dense rulebook as the other convolution kernels (the reference's
+// per-offset gather / GEMM / scatter-add is CPU/Convolution.cpp:137-148 and
+// CUDA/Convolution.cu:57-233,618-642).  The work is laid out by OUTPUT ROW, not by rule:
+//
+//   warp      32 consecutive output rows as two 16-row tiles of mma.sync.m16n8k8, their 32 x Cout
+//             accumulators in registers for the whole filter.  For every filter offset the warp
+//             gathers the input rows of its rows (16-byte cp.async into a private ring of stages,
+//             zero fill where the rulebook has no rule) and multiplies them with the offset's
+//             weights.  A 16-row tile without a rule for the offset is skipped: rows come sorted by
+//             coordinate, so the rules of an offset cluster (54 % of the (offset, 16-row tile) slots
+//             of an indoor scan hold a rule, at 62 % fill)
+//   weights   prepared once per call as the per-lane fragment image of (offset, 32-plane chunk)
+//             slabs, hi and lo parts already split (8 or 16 KB); every warp reads its B fragments
+//             straight from that image with 128-bit loads through L1 (the gathers bypass L1, the
+//             output is written with streaming stores), one prefetch per step ahead
+//   nothing   is shared between warps: no barrier, no shared-memory accumulator, no pair lists.
+//             A CTA is one warp; 20 of them are resident per SM
+//   arithmetic x = hi + lo with hi = x truncated to tf32; D += A_lo B_hi + A_hi B_lo + A_hi B_hi
+//             in fp32 accumulators (1e-5 of max against fp32)
+//
+// Against the compacting kernel of conv_pipe.cu this issues 1.4 to 1.6 times the tensor
+// instructions (the zero rows inside a tile) but half the instructions around each of them.
+#include <stdlib.h>
+
+#include "metadata.cuh"
+#include "tc_ptx.cuh"
+
+namespace scn {
+
+constexpr int kRChunk = 32;                    // input planes per step
+constexpr int kRAStride = kRChunk + 4;         // floats; rows g and g + 1 land on different bank quads
+#ifndef SCN_ROWS_A_STAGES
+#define SCN_ROWS_A_STAGES 2
+#endif
+constexpr int kRAStages = SCN_ROWS_A_STAGES;   // per-warp ring of gathered rows
+constexpr int kRMaxK = 32;
+constexpr int kRStageFloats = 32 * kRAStride;  // one stage: [row][plane]
+
+__device__ __forceinline__ void rows_mma(float (&d)[4], const unsigned (&a)[4], const unsigned (&b)[2]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+__device__ __forceinline__ void rows_split(float x, unsigned &hi, unsigned &lo) {
+  hi = __float_as_uint(x) & 0xFFFFE000u;
+  lo = __float_as_uint(x - __uint_as_float(hi));
+}
+
+// W [K][cin][cout] -> image [K][cin / 32][4][cout / 8][32] of (b0 hi, b1 hi, b0 lo, b1 lo): the B
+// fragments of lane (g, t) for k-block kb of the chunk and output planes 8 nt .. 8 nt + 7, already
+// split (see the layout note above)
+__global__ void k_rows_prepare(const float *__restrict__ w, uint4 *__restrict__ img, int K, int cin, int cout) {
+  const int nt_n = cout / 8, nch = cin / kRChunk;
+  const long long total = (long long)K * nch * 4 * nt_n * 32;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int lane = (int)(i & 31);
+  long long r = i >> 5;
+  const int nt = (int)(r % nt_n);
+  r /= nt_n;
+  const int kb = (int)(r & 3);
+  r >>= 2;
+  const int c = (int)(r % nch);
+  const int k = (int)(r / nch);
+  const int g = lane >> 2, t = lane & 3;
+  const int p0 = c * kRChunk + kb * 8 + t, n = nt * 8 + g;
+  const float *wk = w + ((long long)k * cin + p0) * cout + n;
+  uint4 o;
+  rows_split(wk[0], o.x, o.z);
+  rows_split(wk[4 * (long long)cout], o.y, o.w);
+  img[i] = o;
+}
+
+// One (offset, 32-plane chunk) step of a warp: its two 16-row tiles times the slab.
+// D fragment: d[mt][nt] = rows (g, g + 8) of tile mt x planes 8 nt + 2 t, + 1.
+// The A values are read with scalar loads in fragment order.  (Reading a lane's eight planes of a
+// row with two 128-bit loads and picking the fragments out of them makes the compiler move every
+// value into place: 2.2 register moves per tensor instruction, measured on this kernel and on a
+// probe; with scalar loads there are none.)
+// A 16-row tile without a rule for the offset (m0 / m1 = 0, warp-uniform) is left out.  Tried and
+// not kept: always multiplying both tiles (16 % more tensor instructions; faster by 5 % for 32
+// output planes, slower by 12 % for 64); accumulators of their own for the two small terms (more
+// accurate, 2e-6, but the registers cost more warps than the shorter dependency chains gain);
+// weight fragments held two k-blocks ahead in registers (same).
+template <int NT>
+__device__ __forceinline__ void rows_chunk(float (&d)[2][NT][4], const float *a_stage, const uint4 *w_slab,
+                                           int lane, unsigned m0, unsigned m1) {
+  const int g = lane >> 2, t = lane & 3;
+  const float *a_lane = a_stage + g * kRAStride + t;
+#pragma unroll
+  for (int kb = 0; kb < 4; ++kb) {
+    unsigned bh[NT][2], bl[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const uint4 b = __ldg(w_slab + (kb * NT + nt) * 32 + lane);
+      bh[nt][0] = b.x, bh[nt][1] = b.y, bl[nt][0] = b.z, bl[nt][1] = b.w;
+    }
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt) {
+      if ((mt == 0 ? m0 : m1) == 0) continue;
+      const float *ap = a_lane + mt * 16 * kRAStride + kb * 8;
+      unsigned ah[4], al[4];
+      rows_split(ap[0], ah[0], al[0]);
+      rows_split(ap[8 * kRAStride], ah[1], al[1]);
+      rows_split(ap[4], ah[2], al[2]);
+      rows_split(ap[8 * kRAStride + 4], ah[3], al[3]);
+      // the small terms first; consecutive instructions write different accumulators
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) rows_mma(d[mt][nt], al, bh[nt]);
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) rows_mma(d[mt][nt], ah, bl[nt]);
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) rows_mma(d[mt][nt], ah, bh[nt]);
+    }
+  }
+}
+
+__device__ __forceinline__ void prefetch_l1(const void *p) {
+  asm volatile("prefetch.global.L1 [%0];" ::"l"(p));
+}
+
+template <int NT>
+__global__ void __launch_bounds__(32)
+k_conv_rows(const float *__restrict__ in, int ld_in, long long n_in, float *__restrict__ out, int ld_out,
+            long long n_out, const uint4 *__restrict__ img, const float *__restrict__ bias,
+            const int *__restrict__ nbr, int K, int nch, int *flags) {
+  constexpr unsigned kFull = 0xffffffffu;
+  constexpr int kSlab = 4 * NT * 32;  // uint4 per (offset, chunk) slab
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  const int lane = threadIdx.x;
+  float *a_ring = reinterpret_cast<float *>(smem_raw);
+  const long long row0 = (long long)blockIdx.x * 32;
+  if (row0 >= n_out) return;
+  const long long my_row = row0 + lane;
+
+  // ---- which offsets have a rule for any of the warp's rows ---------------------------------------
+  unsigned wmask = 0;
+  for (int k0 = 0; k0 < K; k0 += 8) {
+    int v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int k = k0 + u;
+      v[u] = (k < K && my_row < n_out) ? __ldg(nbr + (long long)k * n_out + my_row) : -1;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (v[u] >= n_in) atomicOr(flags, FLAG_BAD_ROW);
+      if (__any_sync(kFull, v[u] >= 0 && v[u] < n_in)) wmask |= 1u << (k0 + u);
+    }
+  }
+
+  float d[2][NT][4];
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) d[mt][nt][0] = d[mt][nt][1] = d[mt][nt][2] = d[mt][nt][3] = 0.f;
+
+  // Gathers run kRAStages - 1 steps ahead of the arithmetic; the rulebook entries of the rows (one
+  // per lane) are read one offset ahead of the gather that needs them and handed to the copying
+  // lanes by shuffles.
+  unsigned irem = wmask;  // offsets whose gathers are still to be issued
+  auto load_entry = [&](unsigned rem) -> int {
+    if (!rem || my_row >= n_out) return -1;
+    const int v = __ldg(nbr + (long long)(__ffs(rem) - 1) * n_out + my_row);
+    return v < n_in ? v : -1;
+  };
+  int vcur = load_entry(irem), vnext = load_entry(irem & (irem - 1));
+  int ic = 0, istage = 0;
+  const int piece = (lane & 7) * 4, prow = lane >> 3;
+  unsigned mk_q[kRAStages];  // which rows of the steps in flight have a rule
+#pragma unroll
+  for (int s = 0; s < kRAStages; ++s) mk_q[s] = 0;
+  auto issue = [&] {
+#pragma unroll
+    for (int s = 0; s < kRAStages - 1; ++s) mk_q[s] = mk_q[s + 1];
+    mk_q[kRAStages - 1] = 0;
+    if (irem) {
+      const unsigned mk = __ballot_sync(kFull, vcur >= 0);
+      mk_q[kRAStages - 1] = mk;
+      float *dst = a_ring + istage * kRStageFloats + piece;
+      const float *col = in + ic * kRChunk + piece;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if ((i < 4 ? (mk & 0xFFFFu) : (mk >> 16)) == 0) continue;  // such a tile is not read
+        const int rr = prow + 4 * i;
+        const int v = __shfl_sync(kFull, vcur, rr);
+        cp_async16(smem_u32(dst + rr * kRAStride), v >= 0 ? col + (long long)v * ld_in : in, v >= 0 ? 16u : 0u);
+      }
+      // the slab this step will multiply with: towards L1 while the rows travel
+#pragma unroll
+      for (int q = 0; q < NT / 2; ++q)  // 128 bytes per lane and instruction
+        prefetch_l1(img + ((long long)(__ffs(irem) - 1) * nch + ic) * kSlab + q * 256 + lane * 8);
+      if (++ic == nch) {
+        ic = 0;
+        irem &= irem - 1;
+        vcur = vnext;
+        vnext = load_entry(irem & (irem - 1));
+      }
+    }
+    cp_async_commit();  // one group per call, empty or not: wait_group's count stays fixed
+    istage = istage + 1 == kRAStages ? 0 : istage + 1;
+  };
+#pragma unroll
+  for (int s = 0; s < kRAStages - 1; ++s) issue();
+
+  int cstage = 0;
+  for (unsigned rem = wmask; rem; rem &= rem - 1) {
+    const int k = __ffs(rem) - 1;
+    for (int c = 0; c < nch; ++c) {
+      cp_async_wait<kRAStages - 2>();  // the rows of this step have landed (this lane's copies)
+      __syncwarp();                    // ... every lane's; and the previous step's reads are done
+      issue();
+      rows_chunk<NT>(d, a_ring + cstage * kRStageFloats, img + ((long long)k * nch + c) * kSlab, lane,
+                           mk_q[0] & 0xFFFFu, mk_q[0] >> 16);
+      cstage = cstage + 1 == kRAStages ? 0 : cstage + 1;
+    }
+  }
+  cp_async_wait<0>();
+
+  // ---- the warp's rows, written once ---------------------------------------------------------------
+  const int g = lane >> 2, t2 = (lane & 3) * 2;
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const long long r = row0 + mt * 16 + h * 8 + g;
+      if (r >= n_out) continue;
+      float *dst = out + r * ld_out + t2;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        float2 v = make_float2(d[mt][nt][h * 2], d[mt][nt][h * 2 + 1]);
+        if (bias) {
+          const float2 b = __ldg(reinterpret_cast<const float2 *>(bias + nt * 8 + t2));
+          v.x += b.x;
+          v.y += b.y;
+        }
+        __stcs(reinterpret_cast<float2 *>(dst + nt * 8), v);
+      }
+    }
+}
+
+template <int NT>
+static int launch_rows(const float *in, int ld_in, long long n_in, float *out, int ld_out, long long n_out,
+                       const uint4 *img, const float *bias, const int *table, int K, int nch, int *flags,
+                       cudaStream_t stream) {
+  static bool configured[64] = {false};
+  int dev = 0;
+  SCN_CUDA_CHECK(cudaGetDevice(&dev));
+  const size_t smem = (size_t)kRAStages * kRStageFloats * sizeof(float);
+  auto kernel = k_conv_rows<NT>;
+  if (dev >= 64 || !configured[dev]) {
+    SCN_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    // 9 KB of shared memory per warp: a carve-out of 80 % holds 20 warps per SM (the registers allow
+    // more with 32 output planes), the rest of the 256 KB stays L1 for the weight image
+    SCN_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 80));
+    if (dev < 64) configured[dev] = true;
+  }
+  SCN_LAUNCH(kernel, (unsigned)ceil_div(n_out, 32LL), 32, smem, stream, in, ld_in, n_in, out, ld_out, n_out, img, bias,
+             table, K, nch, flags);
+  SCN_CUDA_CHECK(cudaGetLastError());
+  return SCN_OK;
+}
+
+bool conv_rows_supported(const float *in, const float *out, const float *weight, const float *bias, int K, int cin,
+                         int cout, int groups) {
+  return groups == 1 && K <= kRMaxK && cin % kRChunk == 0 && (cout == 32 || cout == 64) &&
+         (uintptr_t)in % 16 == 0 && (uintptr_t)out % 8 == 0 && (uintptr_t)bias % 8 == 0 && (uintptr_t)weight % 4 == 0;
+}
+
+// out [n_out, cout] = bias + sum_k in[table[k][.]] @ W[k], three tf32 passes (fp32-class accuracy)
+int conv_forward_rows(const float *in, long long n_in, float *out, long long n_out, const float *weight,
+                      const float *bias, const int *table, int K, int cin, int cout, int *flags,
+                      cudaStream_t stream) {
+  if (n_out == 0) return SCN_OK;
+  const int nch = cin / kRChunk;
+  uint4 *img = nullptr;
+  const long long total = (long long)K * nch * 4 * (cout / 8) * 32;
+  SCN_TRY(device_alloc((void **)&img, (size_t)total * sizeof(uint4), stream));
+  SCN_LAUNCH(k_rows_prepare, (unsigned)ceil_div(total, 256LL), 256, 0, stream, weight, img, K, cin, cout);
+  const int rc = cout == 32
+                     ? launch_rows<4>(in, cin, n_in, out, cout, n_out, img, bias, table, K, nch, flags, stream)
+                     : launch_rows<8>(in, cin, n_in, out, cout, n_out, img, bias, table, K, nch, flags, stream);
+  const int rf = device_free(img, stream);
+  return rc != SCN_OK ? rc : rf;
+}
+
+}  // namespace scn

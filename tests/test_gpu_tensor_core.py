@@ -51,6 +51,41 @@ def test_submanifold_conv_tensor_core(mode, tol, cin, cout, cuda, restore_precis
     assert err > 0 or mode == "tf32x3", "tensor-core result identical to fp32: the path did not run"
 
 
+@pytest.mark.parametrize("rows", ["1", "0"])
+@pytest.mark.parametrize("cin,cout", [(32, 32), (64, 32), (64, 64), (128, 64)])
+def test_narrow_three_pass_kernels(cin, cout, rows, cuda, restore_precision, monkeypatch):
+    """Layers with 32 or 64 output planes in the fp32-accuracy mode: the row-stationary kernel
+    (default) and the compacting pipelined kernel (SCN_X3_ROWS=0), on a row count that is not a
+    multiple of the 32-row warp tile, for a submanifold, a strided and a transposed rulebook."""
+    import sparseconvnet_b200 as scn
+    from sparseconvnet_b200._lib import lib
+    monkeypatch.setenv("SCN_X3_ROWS", rows)
+    coords = _surface(7001, 56, 2, 31)
+    rng = np.random.default_rng(32)
+    torch.manual_seed(cin + 7 * cout)
+    inp = scn.InputLayer(3, 56, mode=3)
+    layers = [scn.SubmanifoldConvolution(3, cin, cout, 3, True).to(cuda),
+              scn.Convolution(3, cin, cout, 2, 2, False).to(cuda)]
+    feats = torch.from_numpy(rng.standard_normal((coords.shape[0], cin)).astype(np.float32)).to(cuda)
+    with torch.no_grad():
+        x = inp([torch.from_numpy(coords), feats])
+        assert x.features.size(0) % 32 != 0
+        for layer in layers + [None]:
+            if layer is None:  # transposed rulebook: back from the coarse grid
+                layer = scn.Deconvolution(3, cout, cout, 2, 2, False).to(cuda)
+                scn.set_precision("fp32")
+                x = layers[1](x)
+            scn.set_precision("fp32")
+            want = layer(x).features
+            scn.set_precision("tf32x3")
+            got = layer(x).features
+            kernel = lib.scn_last_conv_kernel()
+            x.metadata.poll_errors()
+            assert kernel == (4 if rows == "1" else 3), "kernel %d ran" % kernel
+            err = helpers.rel_err(got.cpu().numpy(), want.cpu().numpy())
+            assert err <= helpers.FP32_TOL, "%d->%d rows=%s: relative error %.3g" % (cin, cout, rows, err)
+
+
 @pytest.mark.parametrize("gather", ["cp.async", "tma"])
 @pytest.mark.parametrize("mode,tol", MODES)
 def test_persistent_kernel_both_gathers(mode, tol, gather, cuda, restore_precision, monkeypatch):
