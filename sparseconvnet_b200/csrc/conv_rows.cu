@@ -14,8 +14,9 @@
 //             of an indoor scan hold a rule, at 62 % fill)
 //   weights   prepared once per call as the per-lane fragment image of (offset, 32-plane chunk)
 //             slabs, hi and lo parts already split (8 or 16 KB); every warp reads its B fragments
-//             straight from that image with 128-bit loads through L1 (the gathers bypass L1, the
-//             output is written with streaming stores), one prefetch per step ahead
+//             straight from that image with 128-bit loads; they come from L2 (the slabs of the 20
+//             warps of an SM do not fit L1 beside the shared memory, hit rate 9 %; an L1 prefetch a
+//             step ahead made it slower), and the other warps cover the latency
 //   nothing   is shared between warps: no barrier, no shared-memory accumulator, no pair lists.
 //             A CTA is one warp; 20 of them are resident per SM
 //   arithmetic x = hi + lo with hi = x truncated to tf32; D += A_lo B_hi + A_hi B_lo + A_hi B_hi
@@ -32,10 +33,7 @@ namespace scn {
 
 constexpr int kRChunk = 32;                    // input planes per step
 constexpr int kRAStride = kRChunk + 4;         // floats; rows g and g + 1 land on different bank quads
-#ifndef SCN_ROWS_A_STAGES
-#define SCN_ROWS_A_STAGES 2
-#endif
-constexpr int kRAStages = SCN_ROWS_A_STAGES;   // per-warp ring of gathered rows
+constexpr int kRAStages = 2;                   // per-warp ring of gathered rows (three: slower, fewer warps fit)
 constexpr int kRMaxK = 32;
 constexpr int kRStageFloats = 32 * kRAStride;  // one stage: [row][plane]
 
@@ -85,7 +83,8 @@ __global__ void k_rows_prepare(const float *__restrict__ w, uint4 *__restrict__ 
 // not kept: always multiplying both tiles (16 % more tensor instructions; faster by 5 % for 32
 // output planes, slower by 12 % for 64); accumulators of their own for the two small terms (more
 // accurate, 2e-6, but the registers cost more warps than the shorter dependency chains gain);
-// weight fragments held two k-blocks ahead in registers (same).
+// weight fragments held two k-blocks ahead in registers (same); the image without the split,
+// hi and lo made in registers (half the L2 traffic, 6 % slower).
 template <int NT>
 __device__ __forceinline__ void rows_chunk(float (&d)[2][NT][4], const float *a_stage, const uint4 *w_slab,
                                            int lane, unsigned m0, unsigned m1) {
@@ -99,28 +98,49 @@ __device__ __forceinline__ void rows_chunk(float (&d)[2][NT][4], const float *a_
       const uint4 b = __ldg(w_slab + (kb * NT + nt) * 32 + lane);
       bh[nt][0] = b.x, bh[nt][1] = b.y, bl[nt][0] = b.z, bl[nt][1] = b.w;
     }
+    if (NT <= 4 && m0 != 0 && m1 != 0) {
+      // both tiles: their instructions interleaved, an accumulator comes round every 2 NT instructions
+      unsigned ah[2][4], al[2][4];
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt) {
-      if ((mt == 0 ? m0 : m1) == 0) continue;
-      const float *ap = a_lane + mt * 16 * kRAStride + kb * 8;
-      unsigned ah[4], al[4];
-      rows_split(ap[0], ah[0], al[0]);
-      rows_split(ap[8 * kRAStride], ah[1], al[1]);
-      rows_split(ap[4], ah[2], al[2]);
-      rows_split(ap[8 * kRAStride + 4], ah[3], al[3]);
-      // the small terms first; consecutive instructions write different accumulators
+      for (int mt = 0; mt < 2; ++mt) {
+        const float *ap = a_lane + mt * 16 * kRAStride + kb * 8;
+        rows_split(ap[0], ah[mt][0], al[mt][0]);
+        rows_split(ap[8 * kRAStride], ah[mt][1], al[mt][1]);
+        rows_split(ap[4], ah[mt][2], al[mt][2]);
+        rows_split(ap[8 * kRAStride + 4], ah[mt][3], al[mt][3]);
+      }
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt) rows_mma(d[mt][nt], al, bh[nt]);
+      for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt) rows_mma(d[mt][nt], ah, bl[nt]);
+        for (int nt = 0; nt < NT; ++nt) rows_mma(d[mt][nt], al[mt], bh[nt]);
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt) rows_mma(d[mt][nt], ah, bh[nt]);
+      for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) rows_mma(d[mt][nt], ah[mt], bl[nt]);
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) rows_mma(d[mt][nt], ah[mt], bh[nt]);
+    } else {
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        if ((mt == 0 ? m0 : m1) == 0) continue;
+        const float *ap = a_lane + mt * 16 * kRAStride + kb * 8;
+        unsigned ah[4], al[4];
+        rows_split(ap[0], ah[0], al[0]);
+        rows_split(ap[8 * kRAStride], ah[1], al[1]);
+        rows_split(ap[4], ah[2], al[2]);
+        rows_split(ap[8 * kRAStride + 4], ah[3], al[3]);
+        // the small terms first; consecutive instructions write different accumulators
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) rows_mma(d[mt][nt], al, bh[nt]);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) rows_mma(d[mt][nt], ah, bl[nt]);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) rows_mma(d[mt][nt], ah, bh[nt]);
+      }
     }
   }
-}
-
-__device__ __forceinline__ void prefetch_l1(const void *p) {
-  asm volatile("prefetch.global.L1 [%0];" ::"l"(p));
 }
 
 template <int NT>
@@ -190,10 +210,6 @@ k_conv_rows(const float *__restrict__ in, int ld_in, long long n_in, float *__re
         const int v = __shfl_sync(kFull, vcur, rr);
         cp_async16(smem_u32(dst + rr * kRAStride), v >= 0 ? col + (long long)v * ld_in : in, v >= 0 ? 16u : 0u);
       }
-      // the slab this step will multiply with: towards L1 while the rows travel
-#pragma unroll
-      for (int q = 0; q < NT / 2; ++q)  // 128 bytes per lane and instruction
-        prefetch_l1(img + ((long long)(__ffs(irem) - 1) * nch + ic) * kSlab + q * 256 + lane * 8);
       if (++ic == nch) {
         ic = 0;
         irem &= irem - 1;
