@@ -184,6 +184,22 @@ SCN_API int scn_md_rulebook_export(scn_metadata *md, int kind, const int64_t *si
  * reference; lets a profiler attribute a call's time to the kernel that ran it. */
 SCN_API int scn_last_conv_kernel(void);
 
+/* The convolution operators return the reference's multiply-add count (rules x planes in x planes
+ * out, CPU/Convolution.cpp:141) through `macs`.  The reference knows the rule totals on the host;
+ * here they are counted on the device, and fetching them where the operator is called makes the
+ * host wait for the stream once per rulebook, with the GPU idle until the next launch.
+ * scn_set_deferred_counts(1) lifts that wait for callers that can take the number later: while a
+ * rulebook's totals are still on their way the operator stores -(planes in x planes out x groups)
+ * in *macs, and scn_md_take_count_ticket hands out a ticket (or NULL) for the total of the last
+ * such answer on that metadata object.  scn_count_ticket_total waits for that one copy only (not
+ * for the stream) and returns the number of rules; the ticket stays valid after the metadata
+ * object is gone and is given back with scn_count_ticket_release.  Off by default: *macs is then
+ * always the count.  No counterpart in the reference. */
+SCN_API int scn_set_deferred_counts(int on);
+SCN_API int scn_md_take_count_ticket(scn_metadata *md, void **ticket);
+SCN_API int scn_count_ticket_total(void *ticket, int64_t *total);
+SCN_API int scn_count_ticket_release(void *ticket);
+
 /* replaces SubmanifoldConvolution_updateOutput (sparseconvnet.h:101-104;
  * CPU/Convolution.cpp:117-150; CUDA/Convolution.cu:57-233,444-521,618-642).
  * weight [filter_volume, groups, n_in/groups, n_out/groups], bias [n_out] or NULL.

@@ -17,6 +17,94 @@ import torch
 from . import _lib
 from ._lib import check, lib, sizes
 
+class DeferredCount(object):
+    """Multiply-add count of a convolution whose rule totals were still on their way to the host
+    when the operator returned (``scn_set_deferred_counts`` in ``include/scn_b200.h``).  Acts as
+    the number: ``float(x)``, ``x + y``, ``x * y`` wait for that one copy and give the count the
+    reference's operator would have returned (CPU/Convolution.cpp:141)."""
+    __slots__ = ("_ticket", "_factor", "_value")
+
+    def __init__(self, ticket, factor):
+        self._ticket, self._factor, self._value = ticket, factor, None
+
+    def resolve(self):
+        if self._value is None:
+            total = C.c_int64()
+            check(lib.scn_count_ticket_total(self._ticket, C.byref(total)))
+            self._value = float(total.value) * self._factor
+            lib.scn_count_ticket_release(self._ticket)
+            self._ticket = None
+        return self._value
+
+    def __del__(self):
+        if getattr(self, "_ticket", None) is not None and lib is not None:
+            lib.scn_count_ticket_release(self._ticket)
+            self._ticket = None
+
+    __float__ = resolve
+
+    def __int__(self):
+        return int(self.resolve())
+
+    def __add__(self, other):
+        return self.resolve() + other
+
+    __radd__ = __add__
+
+    def __mul__(self, other):
+        return self.resolve() * other
+
+    __rmul__ = __mul__
+
+    def __eq__(self, other):
+        return self.resolve() == other
+
+    def __repr__(self):
+        return "DeferredCount(%r)" % (self._value if self._value is not None else "pending")
+
+
+class _FlopCounter(object):
+    """``forward_pass_multiplyAdd_count`` of the package: counts still in flight are kept aside
+    and folded in when the number is read (or when many have piled up, long after they landed)."""
+
+    def __init__(self):
+        self.base, self.pending = 0, []
+
+    def add(self, macs):
+        if isinstance(macs, DeferredCount):
+            self.pending.append(macs)
+            if len(self.pending) > 512:
+                self.fold()
+        else:
+            self.base += macs
+
+    def fold(self):
+        pending, self.pending = self.pending, []
+        for p in pending:
+            self.base += p.resolve()
+
+    def value(self):
+        self.fold()
+        return self.base
+
+    def reset(self, value=0):
+        self.base, self.pending = value, []
+
+
+flop_counter = _FlopCounter()
+check(lib.scn_set_deferred_counts(1))
+
+
+def _macs_result(m, macs):
+    if macs.value >= 0:
+        return macs.value
+    ticket = C.c_void_p()
+    check(lib.scn_md_take_count_ticket(m._h, C.byref(ticket)))
+    if not ticket.value:
+        raise RuntimeError("count pending but no ticket")
+    return DeferredCount(ticket.value, -macs.value)
+
+
 # scn_last_conv_kernel() -> name (enum scn_conv_kernel of include/scn_b200.h)
 _KERNEL_NAMES = ("k_conv_simt", "k_conv_tc", "k_conv_tma", "k_conv_pipe_mma", "k_conv_rows")
 
@@ -321,9 +409,11 @@ def SubmanifoldConvolution_updateOutput(inputSize, filterSize, m, input_features
             check(lib.scn_submanifold_convolution_forward(
                 m._h, sizes(inputSize), sizes(filterSize), _ptr(f), _ptr(output_features), _ptr(w), _ptr(b),
                 groups * cin, groups * cout, groups, _precision, _stream(), C.byref(macs)))
-            info["macs"] = macs.value
+            result = _macs_result(m, macs)
+            if Profile.active is not None:
+                info["macs"] = float(result)
             info["kernel"] = _KERNEL_NAMES[lib.scn_last_conv_kernel()]
-    return macs.value
+    return result
 
 
 def Convolution_updateOutput(inputSize, outputSize, filterSize, filterStride, m, input_features,
@@ -347,9 +437,11 @@ def Convolution_updateOutput(inputSize, outputSize, filterSize, filterStride, m,
                 m._h, sizes(inputSize), sizes(outputSize), sizes(filterSize), sizes(filterStride), _ptr(f),
                 _ptr(output_features), _ptr(w), _ptr(b), groups * cin, groups * cout, groups, _precision,
                 _stream(), C.byref(macs)))
-            info["macs"] = macs.value
+            result = _macs_result(m, macs)
+            if Profile.active is not None:
+                info["macs"] = float(result)
             info["kernel"] = _KERNEL_NAMES[lib.scn_last_conv_kernel()]
-    return macs.value
+    return result
 
 
 def Deconvolution_updateOutput(inputSize, outputSize, filterSize, filterStride, m, input_features,
@@ -372,9 +464,11 @@ def Deconvolution_updateOutput(inputSize, outputSize, filterSize, filterStride, 
                 m._h, sizes(inputSize), sizes(outputSize), sizes(filterSize), sizes(filterStride), _ptr(f),
                 _ptr(output_features), _ptr(w), _ptr(b), groups * cin, groups * cout, groups, _precision,
                 _stream(), C.byref(macs)))
-            info["macs"] = macs.value
+            result = _macs_result(m, macs)
+            if Profile.active is not None:
+                info["macs"] = float(result)
             info["kernel"] = _KERNEL_NAMES[lib.scn_last_conv_kernel()]
-    return macs.value
+    return result
 
 
 def BatchNormalization_updateOutput(input_features, output_features, saveMean, saveInvStd, runningMean,

@@ -7,12 +7,31 @@ on sm_100a, with the reference package's module API:
 
 All compute runs in ``libscn_b200.so`` (C ABI in ``include/scn_b200.h``); there is no CPU path.
 """
-forward_pass_multiplyAdd_count = 0
+import sys as _sys
+import types as _types
+
 forward_pass_hidden_states = 0
 
 from . import SCN  # noqa: E402  (loads libscn_b200.so; fails loudly if it is missing)
 from .SCN import set_precision, get_precision  # noqa: E402
 from .sparse_tensor import SparseConvNetTensor, to_long_tensor as toLongTensor  # noqa: E402
+
+
+class _Package(_types.ModuleType):
+    """``forward_pass_multiplyAdd_count`` (reference: sparseconvnet/__init__.py) is read and reset
+    like the reference's module attribute; reading it folds in the counts of convolutions whose
+    rule totals were still travelling to the host when they returned (SCN.DeferredCount)."""
+
+    @property
+    def forward_pass_multiplyAdd_count(self):
+        return SCN.flop_counter.value()
+
+    @forward_pass_multiplyAdd_count.setter
+    def forward_pass_multiplyAdd_count(self, value):
+        SCN.flop_counter.reset(value)
+
+
+_sys.modules[__name__].__class__ = _Package
 
 
 def Metadata(dim):

@@ -19,6 +19,10 @@ SIGNATURES = {
     "scn_last_error": (C.c_char_p, []),
     "scn_launch_count": (C.c_longlong, []),
     "scn_last_conv_kernel": (C.c_int, []),
+    "scn_set_deferred_counts": (C.c_int, [C.c_int]),
+    "scn_md_take_count_ticket": (C.c_int, [_vp, C.POINTER(_vp)]),
+    "scn_count_ticket_total": (C.c_int, [_vp, _i64p]),
+    "scn_count_ticket_release": (C.c_int, [_vp]),
     "scn_md_create": (C.c_int, [C.c_int, C.POINTER(_vp)]),
     "scn_md_destroy": (C.c_int, [_vp]),
     "scn_md_clear": (C.c_int, [_vp, _vp]),

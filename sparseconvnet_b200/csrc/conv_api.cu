@@ -2,6 +2,8 @@
 // and cached, like the reference's Metadata), shape checks, kernel choice.
 #include <stdlib.h>
 
+#include <atomic>
+
 #include "metadata.cuh"
 
 namespace scn {
@@ -29,6 +31,7 @@ int conv_forward_rows(const float *in, long long n_in, float *out, long long n_o
                       cudaStream_t stream);
 
 static thread_local int g_last_kernel = -1;
+static std::atomic<int> g_deferred_counts{0};
 
 static int run_conv(scn_metadata *md, Rulebook &rb, bool transposed, const float *in, float *out,
                     const float *weight, const float *bias, int n_in_planes, int n_out_planes, int groups,
@@ -90,7 +93,19 @@ static int run_conv(scn_metadata *md, Rulebook &rb, bool transposed, const float
     }
   }
   if (macs) {  // the reference's return value: rules x ip x op x groups (CPU/Convolution.cpp:141)
-    SCN_TRY(rulebook_counts(rb, stream));
+    if (g_deferred_counts.load()) {
+      // do not wait for the rule totals here: -(ip x op x groups) and a ticket for the total
+      SCN_TRY(rulebook_counts_async(rb, stream));
+      if (rb.total_rules < 0) {
+        count_ticket_release(md->last_ticket);
+        md->last_ticket = rb.ticket;
+        rb.ticket->refs.fetch_add(1);
+        *macs = -(double)cin * cout * groups;
+        return SCN_OK;
+      }
+    } else {
+      SCN_TRY(rulebook_counts(rb, stream));
+    }
     *macs = (double)rb.total_rules * cin * cout * groups;
   }
   return SCN_OK;
@@ -102,6 +117,31 @@ using namespace scn;
 extern "C" {
 
 int scn_last_conv_kernel(void) { return g_last_kernel; }
+
+int scn_set_deferred_counts(int on) {
+  g_deferred_counts.store(on ? 1 : 0);
+  return SCN_OK;
+}
+
+int scn_md_take_count_ticket(scn_metadata *md, void **ticket) {
+  SCN_REQUIRE(md && ticket, SCN_ERR_BAD_ARG, "null argument");
+  *ticket = md->last_ticket;  // the reference held for the caller moves to the caller
+  md->last_ticket = nullptr;
+  return SCN_OK;
+}
+
+int scn_count_ticket_total(void *ticket, int64_t *total) {
+  SCN_REQUIRE(ticket && total, SCN_ERR_BAD_ARG, "null argument");
+  long long t = 0;
+  SCN_TRY(count_ticket_total((CountTicket *)ticket, &t));
+  *total = t;
+  return SCN_OK;
+}
+
+int scn_count_ticket_release(void *ticket) {
+  count_ticket_release((CountTicket *)ticket);
+  return SCN_OK;
+}
 
 int scn_submanifold_convolution_forward(scn_metadata *md, const int64_t *spatial_size,
                                         const int64_t *filter_size, const float *in_features,

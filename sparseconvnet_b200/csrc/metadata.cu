@@ -11,6 +11,8 @@
 #include <algorithm>
 #include <climits>
 
+#include <mutex>
+
 #include "metadata.cuh"
 
 namespace scn {
@@ -66,6 +68,7 @@ static void free_grid(Grid &g, cudaStream_t stream) {
   g = Grid{};
 }
 static void free_rulebook(Rulebook &r, cudaStream_t stream) {
+  count_ticket_release(r.ticket);
   device_free(r.nbr, stream);
   device_free(r.tnbr, stream);
   device_free(r.counts_dev, stream);
@@ -716,16 +719,110 @@ int get_strided_rulebook(scn_metadata *md, const int64_t *input_size, const int6
 // rulebook views
 // ------------------------------------------------------------------------------------------
 
-int rulebook_counts(Rulebook &rb, cudaStream_t stream) {
-  if (rb.total_rules >= 0) return SCN_OK;
-  std::vector<unsigned long long> h(rb.n_offsets);
-  SCN_CUDA_CHECK(cudaMemcpyAsync(h.data(), rb.counts_dev, sizeof(unsigned long long) * rb.n_offsets,
+// ---- rule counts: pinned chunks and events are pooled per device, never given back to the driver
+namespace {
+struct TicketPool {
+  std::mutex mu;
+  std::vector<unsigned long long *> chunks[64];  // kRMaxCounts values each
+  std::vector<cudaEvent_t> events[64];
+};
+constexpr int kTicketValues = 256;  // filter volumes up to 256 offsets
+TicketPool &ticket_pool() {
+  static TicketPool *p = new TicketPool();  // leaked on purpose: tickets may be released at exit
+  return *p;
+}
+}  // namespace
+
+static int count_ticket_start(Rulebook &rb, cudaStream_t stream) {
+  if (rb.ticket) return SCN_OK;
+  SCN_REQUIRE(rb.n_offsets <= kTicketValues, SCN_ERR_UNSUPPORTED, "%d filter offsets", rb.n_offsets);
+  int dev = 0;
+  SCN_CUDA_CHECK(cudaGetDevice(&dev));
+  SCN_REQUIRE(dev < 64, SCN_ERR_UNSUPPORTED, "device %d", dev);
+  CountTicket *t = new CountTicket();
+  t->n = rb.n_offsets;
+  t->device = dev;
+  {
+    TicketPool &P = ticket_pool();
+    std::lock_guard<std::mutex> lock(P.mu);
+    if (!P.chunks[dev].empty()) {
+      t->host = P.chunks[dev].back();
+      P.chunks[dev].pop_back();
+    }
+    if (!P.events[dev].empty()) {
+      t->event = P.events[dev].back();
+      P.events[dev].pop_back();
+    }
+  }
+  if (!t->host) {  // a slab of 64 chunks at a time
+    unsigned long long *slab = nullptr;
+    if (cudaHostAlloc((void **)&slab, sizeof(unsigned long long) * kTicketValues * 64, cudaHostAllocDefault) != cudaSuccess) {
+      cudaGetLastError();
+      delete t;
+      SCN_REQUIRE(false, SCN_ERR_CUDA, "pinned allocation failed");
+    }
+    t->host = slab;
+    TicketPool &P = ticket_pool();
+    std::lock_guard<std::mutex> lock(P.mu);
+    for (int i = 1; i < 64; ++i) P.chunks[dev].push_back(slab + (size_t)i * kTicketValues);
+  }
+  if (!t->event && cudaEventCreateWithFlags(&t->event, cudaEventDisableTiming) != cudaSuccess) {
+    cudaGetLastError();
+    t->event = nullptr;
+    count_ticket_release(t);
+    SCN_REQUIRE(false, SCN_ERR_CUDA, "event creation failed");
+  }
+  rb.ticket = t;
+  SCN_CUDA_CHECK(cudaMemcpyAsync(t->host, rb.counts_dev, sizeof(unsigned long long) * rb.n_offsets,
                                  cudaMemcpyDeviceToHost, stream));
-  SCN_CUDA_CHECK(cudaStreamSynchronize(stream));
-  rb.counts_host.assign(h.begin(), h.end());
+  SCN_CUDA_CHECK(cudaEventRecord(t->event, stream));
+  return SCN_OK;
+}
+
+void count_ticket_release(CountTicket *t) {
+  if (!t || t->refs.fetch_sub(1) != 1) return;
+  if (t->event) cudaEventSynchronize(t->event);  // the copy must not land in a chunk that was handed on
+  TicketPool &P = ticket_pool();
+  {
+    std::lock_guard<std::mutex> lock(P.mu);
+    if (t->host) P.chunks[t->device].push_back(t->host);
+    if (t->event) P.events[t->device].push_back(t->event);
+  }
+  delete t;
+}
+
+int count_ticket_total(CountTicket *t, long long *total) {
+  SCN_CUDA_CHECK(cudaEventSynchronize(t->event));
+  long long s = 0;
+  for (int k = 0; k < t->n; ++k) s += (long long)t->host[k];
+  *total = s;
+  return SCN_OK;
+}
+
+static void counts_from_ticket(Rulebook &rb) {
+  rb.counts_host.assign(rb.ticket->host, rb.ticket->host + rb.n_offsets);
   long long t = 0;
   for (auto c : rb.counts_host) t += c;
   rb.total_rules = t;
+}
+
+int rulebook_counts_async(Rulebook &rb, cudaStream_t stream) {
+  if (rb.total_rules >= 0) return SCN_OK;
+  SCN_TRY(count_ticket_start(rb, stream));
+  cudaError_t q = cudaEventQuery(rb.ticket->event);
+  if (q == cudaSuccess) {
+    counts_from_ticket(rb);
+  } else if (q != cudaErrorNotReady) {
+    SCN_CUDA_CHECK(q);
+  }
+  return SCN_OK;
+}
+
+int rulebook_counts(Rulebook &rb, cudaStream_t stream) {
+  if (rb.total_rules >= 0) return SCN_OK;
+  SCN_TRY(count_ticket_start(rb, stream));
+  SCN_CUDA_CHECK(cudaEventSynchronize(rb.ticket->event));
+  counts_from_ticket(rb);
   return SCN_OK;
 }
 
@@ -814,6 +911,8 @@ int scn_md_clear(scn_metadata *md, void *stream) {
 
 int scn_md_destroy(scn_metadata *md) {
   if (!md) return SCN_OK;
+  count_ticket_release(md->last_ticket);
+  md->last_ticket = nullptr;
   md_clear(md, 0);
   device_free(md->flags_dev, 0);
   device_free(md->scalars_dev, 0);

@@ -2,6 +2,7 @@
 // spatial scale (site hash + row -> key table) and the dense per-filter-offset rulebooks.
 #pragma once
 
+#include <atomic>
 #include <map>
 #include <vector>
 
@@ -27,6 +28,20 @@ struct Grid {
 //     tnbr[k * n_in + i] = output row fed by input row i through offset k, or -1
 // used by Deconvolution (the reference swaps the two rule columns, CPU/Deconvolution.cpp:35-37);
 // it is valid because every (offset, input row) also has at most one rule.
+// A rulebook's per-offset rule counts on their way to the host: an asynchronous copy into pinned
+// memory and the event recorded behind it.  The multiply-add count the reference's operators
+// return needs these totals (CPU/Convolution.cpp:141), and waiting for them where the operator is
+// called would leave the GPU idle once per rulebook; a caller that can take the number later is
+// handed the ticket instead.  Reference counted: the ticket outlives its rulebook and metadata.
+struct CountTicket {
+  unsigned long long *host = nullptr;  // [n] pinned
+  cudaEvent_t event = nullptr;
+  int n = 0, device = 0;
+  std::atomic<int> refs{1};
+};
+void count_ticket_release(CountTicket *t);
+int count_ticket_total(CountTicket *t, long long *total);  // waits for the event only
+
 struct Rulebook {
   int n_offsets = 0;  // filter volume K
   long long n_in = 0, n_out = 0;
@@ -35,10 +50,14 @@ struct Rulebook {
   unsigned long long *counts_dev = nullptr;  // [K] rules per offset
   std::vector<long long> counts_host;        // filled on first request (waits for the stream)
   long long total_rules = -1;
+  CountTicket *ticket = nullptr;             // counts in flight (rulebook_counts_async)
   bool built = false;
 };
 
-int rulebook_counts(Rulebook &rb, cudaStream_t stream);         // fills counts_host/total_rules
+int rulebook_counts(Rulebook &rb, cudaStream_t stream);         // fills counts_host/total_rules (waits)
+// Starts the copy of the counts if it has not been started; fills counts_host/total_rules without
+// waiting if the copy has already landed.  total_rules stays -1 while the copy is in flight.
+int rulebook_counts_async(Rulebook &rb, cudaStream_t stream);
 int rulebook_transposed(Rulebook &rb, cudaStream_t stream);     // builds tnbr if missing
 
 }  // namespace scn
@@ -55,6 +74,8 @@ struct scn_metadata {
   long long input_n_rows = 0, input_n_active = 0;
   int *input_csr_start = nullptr;  // [n_active + 1]
   int *input_csr_rows = nullptr;   // [n_rows]
+
+  scn::CountTicket *last_ticket = nullptr;  // of the last operator that answered "count pending"
 
   int *flags_dev = nullptr;   // device word the kernels OR DeviceFlag bits into
   int *scalars_dev = nullptr; // small device scratch: [0] count, [1] max batch index

@@ -174,7 +174,7 @@ class _ConvBase(Module):
             self.bias = Parameter(torch.zeros(nOut))
 
     def _count(self, macs, output_features):
-        _pkg.forward_pass_multiplyAdd_count += macs
+        SCN.flop_counter.add(macs)
         _pkg.forward_pass_hidden_states += output_features.nelement()
 
 
@@ -477,13 +477,13 @@ class NetworkInNetwork(Module):
             if hasattr(self, "bias"):
                 output.features = output.features + self.bias
             macs = float(input.features.size(0) * self.nIn * self.nOut)
-            _pkg.forward_pass_multiplyAdd_count += macs
+            SCN.flop_counter.add(macs)
             _pkg.forward_pass_hidden_states += output.features.nelement()
             return output
         output.features = input.features.new_empty(0)
         macs = SCN.NetworkInNetwork_updateOutput(input.features.detach().contiguous(), output.features,
                                                  self.weight, optional_tensor(self, "bias"))
-        _pkg.forward_pass_multiplyAdd_count += macs
+        SCN.flop_counter.add(macs)
         _pkg.forward_pass_hidden_states += output.features.nelement()
         return output
 

@@ -218,3 +218,33 @@ def test_against_live_reference_random(cuda):
     yg = gpu.run(net, gpu.run(inp, [coords, feats]))
     helpers.assert_features_match(gpu.locations(yg), yg.features, ref.locations(yr), yr.features, helpers.FP32_TOL,
                                   what="live reference")
+
+
+def test_deferred_multiply_add_count(cuda):
+    """A convolution on a fresh rulebook answers with a ticket instead of waiting for the rule totals;
+    resolved later (even after the metadata object is gone) it is the count the blocking call gives."""
+    import sparseconvnet_b200 as scn
+    from sparseconvnet_b200 import SCN
+    from sparseconvnet_b200._lib import lib
+    rng = np.random.default_rng(5)
+    coords = np.concatenate([rng.integers(0, 24, (3000, 3)), rng.integers(0, 2, (3000, 1))], axis=1)
+    feats = torch.from_numpy(rng.standard_normal((3000, 8)).astype(np.float32)).to(cuda)
+    conv = scn.SubmanifoldConvolution(3, 8, 16, 3, False).to(cuda)
+    counts = []
+    try:
+        for deferred in (0, 1):
+            lib.scn_set_deferred_counts(deferred)
+            x = scn.InputLayer(3, 24, mode=3)([torch.from_numpy(coords), feats])
+            out = torch.empty(0, device=cuda)
+            with torch.no_grad():
+                macs = SCN.SubmanifoldConvolution_updateOutput(x.spatial_size, conv.filter_size, x.metadata,
+                                                               x.features, out, conv.weight, torch.empty(0))
+            if deferred:
+                assert isinstance(macs, SCN.DeferredCount) or macs >= 0
+                del x  # the ticket outlives the metadata object
+            else:
+                assert isinstance(macs, float) and macs > 0
+            counts.append(float(macs))
+    finally:
+        lib.scn_set_deferred_counts(1)
+    assert counts[0] == counts[1] and counts[0] % (8 * 16) == 0
