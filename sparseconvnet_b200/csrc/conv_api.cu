@@ -30,6 +30,11 @@ int conv_forward_rows(const float *in, long long n_in, float *out, long long n_o
                       const float *bias, const int *table, int K, int cin, int cout, int *flags,
                       cudaStream_t stream);
 
+bool conv_rows_thin_supported(const float *out, const float *bias, int cin, int cout, int groups);
+int conv_forward_rows_thin(const float *in, long long n_in, float *out, long long n_out, const float *weight,
+                           const float *bias, const int *table, int K, int cin, int cout, int *flags,
+                           cudaStream_t stream);
+
 static thread_local int g_last_kernel = -1;
 static std::atomic<int> g_deferred_counts{0};
 
@@ -69,7 +74,11 @@ static int run_conv(scn_metadata *md, Rulebook &rb, bool transposed, const float
     const bool force_persistent = getenv("SCN_TC_PERSISTENT") && atoi(getenv("SCN_TC_PERSISTENT")) != 0;
     const bool few_tiles = rows_out <= 148 * 256 && !force_persistent;
     const bool use_rows = !(getenv("SCN_X3_ROWS") && atoi(getenv("SCN_X3_ROWS")) == 0);
-    if (narrow_x3 && use_rows && conv_rows_supported(in, out, weight, bias, rb.n_offsets, cin, cout, groups)) {
+    if (narrow_x3 && use_rows && conv_rows_thin_supported(out, bias, cin, cout, groups)) {
+      SCN_TRY(conv_forward_rows_thin(in, rows_in, out, rows_out, weight, bias, table, rb.n_offsets, cin, cout,
+                                     md->flags_dev, stream));
+      g_last_kernel = SCN_KERNEL_CONV_ROWS;
+    } else if (narrow_x3 && use_rows && conv_rows_supported(in, out, weight, bias, rb.n_offsets, cin, cout, groups)) {
       SCN_TRY(conv_forward_rows(in, rows_in, out, rows_out, weight, bias, table, rb.n_offsets, cin, cout,
                                 md->flags_dev, stream));
       g_last_kernel = SCN_KERNEL_CONV_ROWS;

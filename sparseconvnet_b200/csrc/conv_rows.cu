@@ -281,6 +281,144 @@ static int launch_rows(const float *in, int ld_in, long long n_in, float *out, i
   return SCN_OK;
 }
 
+// ---- first layers: at most four input planes --------------------------------------------------------
+// The same row-stationary scheme without shared memory: a lane's A fragment of m16n8k4 is one
+// input value of two rows, read straight from the feature matrix (the rows are 4 to 16 bytes long,
+// too short and too misaligned for 16-byte copies), the B fragments come from a 2 KB-per-offset
+// image that stays in L1.  Four offsets are in flight at a time.
+__device__ __forceinline__ void rows_mma_k4(float (&d)[4], const unsigned (&a)[2], unsigned b) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k4.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(b));
+}
+
+// W [K][cin][cout] -> image [K][cout / 8][32] of (hi, lo) of W[k][t][8 nt + g], zero for t >= cin
+__global__ void k_rows_thin_prepare(const float *__restrict__ w, uint2 *__restrict__ img, int K, int cin, int cout) {
+  const int nt_n = cout / 8;
+  const long long total = (long long)K * nt_n * 32;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int lane = (int)(i & 31), nt = (int)((i >> 5) % nt_n), k = (int)((i >> 5) / nt_n);
+  const int g = lane >> 2, t = lane & 3;
+  uint2 o = make_uint2(0u, 0u);
+  if (t < cin) rows_split(w[((long long)k * cin + t) * cout + nt * 8 + g], o.x, o.y);
+  img[i] = o;
+}
+
+template <int NT>
+__global__ void __launch_bounds__(128)
+k_conv_rows_thin(const float *__restrict__ in, long long n_in, float *__restrict__ out, long long n_out,
+                 const uint2 *__restrict__ img, const float *__restrict__ bias, const int *__restrict__ nbr,
+                 int K, int cin, int *flags) {
+  constexpr unsigned kFull = 0xffffffffu;
+  constexpr int kGroup = 4;  // offsets in flight
+  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const long long row0 = ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 32;
+  if (row0 >= n_out) return;
+  const long long my_row = row0 + lane;
+  const bool t_ok = t < cin;
+  float d[2][NT][4];
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) d[mt][nt][0] = d[mt][nt][1] = d[mt][nt][2] = d[mt][nt][3] = 0.f;
+
+  for (int k0 = 0; k0 < K; k0 += kGroup) {
+    int v[kGroup];
+#pragma unroll
+    for (int u = 0; u < kGroup; ++u) {
+      const int k = k0 + u;
+      v[u] = (k < K && my_row < n_out) ? __ldg(nbr + (long long)k * n_out + my_row) : -1;
+    }
+    float x[kGroup][2][2];  // [offset][tile][row g / g + 8]: plane t of the input row
+#pragma unroll
+    for (int u = 0; u < kGroup; ++u) {
+      if (v[u] >= n_in) {
+        atomicOr(flags, FLAG_BAD_ROW);
+        v[u] = -1;
+      }
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int idx = __shfl_sync(kFull, v[u], mt * 16 + h * 8 + g);
+          x[u][mt][h] = (idx >= 0 && t_ok) ? __ldg(in + (long long)idx * cin + t) : 0.f;
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < kGroup; ++u) {
+      const unsigned mk = __ballot_sync(kFull, v[u] >= 0);
+      if (mk == 0) continue;
+      unsigned bh[NT], bl[NT];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const uint2 b = __ldg(img + ((long long)(k0 + u) * NT + nt) * 32 + lane);
+        bh[nt] = b.x, bl[nt] = b.y;
+      }
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        if (((mt == 0) ? (mk & 0xFFFFu) : (mk >> 16)) == 0) continue;
+        unsigned ah[2], al[2];
+        rows_split(x[u][mt][0], ah[0], al[0]);
+        rows_split(x[u][mt][1], ah[1], al[1]);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) rows_mma_k4(d[mt][nt], al, bh[nt]);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) rows_mma_k4(d[mt][nt], ah, bl[nt]);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) rows_mma_k4(d[mt][nt], ah, bh[nt]);
+      }
+    }
+  }
+
+  const int t2 = t * 2;
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const long long r = row0 + mt * 16 + h * 8 + g;
+      if (r >= n_out) continue;
+      float *dst = out + r * (NT * 8) + t2;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        float2 y = make_float2(d[mt][nt][h * 2], d[mt][nt][h * 2 + 1]);
+        if (bias) {
+          const float2 b = __ldg(reinterpret_cast<const float2 *>(bias + nt * 8 + t2));
+          y.x += b.x;
+          y.y += b.y;
+        }
+        __stcs(reinterpret_cast<float2 *>(dst + nt * 8), y);
+      }
+    }
+}
+
+bool conv_rows_thin_supported(const float *out, const float *bias, int cin, int cout, int groups) {
+  return groups == 1 && cin >= 1 && cin <= 4 && (cout == 16 || cout == 32 || cout == 64) &&
+         (uintptr_t)out % 8 == 0 && (uintptr_t)bias % 8 == 0;
+}
+
+int conv_forward_rows_thin(const float *in, long long n_in, float *out, long long n_out, const float *weight,
+                           const float *bias, const int *table, int K, int cin, int cout, int *flags,
+                           cudaStream_t stream) {
+  if (n_out == 0) return SCN_OK;
+  uint2 *img = nullptr;
+  const long long total = (long long)K * (cout / 8) * 32;
+  SCN_TRY(device_alloc((void **)&img, (size_t)total * sizeof(uint2), stream));
+  SCN_LAUNCH(k_rows_thin_prepare, (unsigned)ceil_div(total, 256LL), 256, 0, stream, weight, img, K, cin, cout);
+  const unsigned grid = (unsigned)ceil_div(n_out, 128LL);
+  if (cout == 16)
+    SCN_LAUNCH(k_conv_rows_thin<2>, grid, 128, 0, stream, in, n_in, out, n_out, img, bias, table, K, cin, flags);
+  else if (cout == 32)
+    SCN_LAUNCH(k_conv_rows_thin<4>, grid, 128, 0, stream, in, n_in, out, n_out, img, bias, table, K, cin, flags);
+  else
+    SCN_LAUNCH(k_conv_rows_thin<8>, grid, 128, 0, stream, in, n_in, out, n_out, img, bias, table, K, cin, flags);
+  const cudaError_t e = cudaGetLastError();
+  const int rf = device_free(img, stream);
+  SCN_CUDA_CHECK(e);
+  return rf;
+}
+
 bool conv_rows_supported(const float *in, const float *out, const float *weight, const float *bias, int K, int cin,
                          int cout, int groups) {
   return groups == 1 && K <= kRMaxK && cin % kRChunk == 0 && (cout == 32 || cout == 64) &&

@@ -109,17 +109,32 @@ __global__ void k_bn_finalize(int C, long long n_rows, const double *__restrict_
 }
 
 // y = x * w + b, y *= (y > 0 ? 1 : leak); four planes per thread when the layout allows.
+// With `running_var` (eval mode) the statistics are the running ones: every CTA derives mean and
+// inverse deviation from them (the same expressions as k_bn_finalize), and the first one also
+// stores them in save_mean / save_invstd as the reference does; no separate launch.
 template <int VEC>
 __global__ void __launch_bounds__(256)
 k_bn_apply(const float *__restrict__ in, float *__restrict__ out, long long n_rows, int C,
-           long long in_stride, long long out_stride, const float *__restrict__ save_mean,
-           const float *__restrict__ save_invstd, const float *__restrict__ weight,
-           const float *__restrict__ bias, float leak) {
+           long long in_stride, long long out_stride, float *save_mean, float *save_invstd,
+           const float *__restrict__ running_mean, const float *__restrict__ running_var, float eps,
+           const float *__restrict__ weight, const float *__restrict__ bias, float leak) {
   extern __shared__ float sh_wb[];  // [2][C]
   for (int c = threadIdx.x; c < C; c += blockDim.x) {
-    float w = save_invstd[c] * (weight ? weight[c] : 1.f);
+    float mean, invstd;
+    if (running_var) {
+      mean = running_mean[c];
+      invstd = powf(running_var[c] + eps, -0.5f);
+      if (blockIdx.x == 0) {
+        save_mean[c] = mean;
+        save_invstd[c] = invstd;
+      }
+    } else {
+      mean = save_mean[c];
+      invstd = save_invstd[c];
+    }
+    float w = invstd * (weight ? weight[c] : 1.f);
     sh_wb[c] = w;
-    sh_wb[C + c] = __fadd_rn(__fmul_rn(-save_mean[c], w), bias ? bias[c] : 0.f);
+    sh_wb[C + c] = __fadd_rn(__fmul_rn(-mean, w), bias ? bias[c] : 0.f);
   }
   __syncthreads();
   int cv = C / VEC;
@@ -434,16 +449,18 @@ int scn_batchnorm_forward(const float *in_features, float *out_features, int64_t
     unsigned gy = (unsigned)std::min<long long>(ceil_div(n_rows, 64), 1024);
     SCN_LAUNCH(k_bn_stats, dim3((unsigned)ceil_div(n_planes, 32), gy), 256, 0, stream, in_features, n_rows, n_planes, in_stride, sums);
   }
-  SCN_LAUNCH(k_bn_finalize, (unsigned)ceil_div(n_planes, 128), 128, 0, stream, n_planes, n_rows, sums, save_mean, save_invstd, running_mean, running_var, (float)eps, (float)momentum, train);
+  if (train)
+    SCN_LAUNCH(k_bn_finalize, (unsigned)ceil_div(n_planes, 128), 128, 0, stream, n_planes, n_rows, sums, save_mean, save_invstd, running_mean, running_var, (float)eps, (float)momentum, train);
+  const float *rm = train ? nullptr : running_mean, *rv = train ? nullptr : running_var;
   bool vec4 = (n_planes % 4 == 0) && (in_stride % 4 == 0) && (out_stride % 4 == 0) &&
               ((uintptr_t)in_features % 16 == 0) && ((uintptr_t)out_features % 16 == 0);
   long long work = n_rows * (vec4 ? n_planes / 4 : n_planes);
   unsigned blocks = (unsigned)std::min<long long>(ceil_div(work, 256), 148 * 16);
   size_t smem = sizeof(float) * 2 * n_planes;
   if (vec4)
-    SCN_LAUNCH(k_bn_apply<4>, blocks, 256, smem, stream, in_features, out_features, n_rows, n_planes, in_stride, out_stride, save_mean, save_invstd, weight, bias, (float)leakiness);
+    SCN_LAUNCH(k_bn_apply<4>, blocks, 256, smem, stream, in_features, out_features, n_rows, n_planes, in_stride, out_stride, save_mean, save_invstd, rm, rv, (float)eps, weight, bias, (float)leakiness);
   else
-    SCN_LAUNCH(k_bn_apply<1>, blocks, 256, smem, stream, in_features, out_features, n_rows, n_planes, in_stride, out_stride, save_mean, save_invstd, weight, bias, (float)leakiness);
+    SCN_LAUNCH(k_bn_apply<1>, blocks, 256, smem, stream, in_features, out_features, n_rows, n_planes, in_stride, out_stride, save_mean, save_invstd, rm, rv, (float)eps, weight, bias, (float)leakiness);
   SCN_CUDA_CHECK(cudaGetLastError());
   if (sums) SCN_TRY(device_free(sums, stream));
   return SCN_OK;

@@ -86,6 +86,34 @@ def test_narrow_three_pass_kernels(cin, cout, rows, cuda, restore_precision, mon
             assert err <= helpers.FP32_TOL, "%d->%d rows=%s: relative error %.3g" % (cin, cout, rows, err)
 
 
+@pytest.mark.parametrize("cin,cout", [(3, 32), (1, 16), (4, 64), (2, 32)])
+def test_first_layer_three_pass_kernel(cin, cout, cuda, restore_precision):
+    """First layers (at most four input planes) in the fp32-accuracy mode run on the warp-level
+    tensor path too; other plane counts keep the fp32 kernel."""
+    import sparseconvnet_b200 as scn
+    from sparseconvnet_b200._lib import lib
+    coords = _surface(6007, 48, 3, 41)
+    rng = np.random.default_rng(42)
+    torch.manual_seed(cin + 11 * cout)
+    inp = scn.InputLayer(3, 48, mode=3)
+    sc = scn.SubmanifoldConvolution(3, cin, cout, 3, True).to(cuda)
+    sc.bias.data.normal_()
+    down = scn.Convolution(3, cin, cout, 2, 2, False).to(cuda)
+    feats = torch.from_numpy(rng.standard_normal((coords.shape[0], cin)).astype(np.float32)).to(cuda)
+    with torch.no_grad():
+        x = inp([torch.from_numpy(coords), feats])
+        for layer in (sc, down):
+            scn.set_precision("fp32")
+            want = layer(x).features
+            assert lib.scn_last_conv_kernel() == 0
+            scn.set_precision("tf32x3")
+            got = layer(x).features
+            assert lib.scn_last_conv_kernel() == 4
+            x.metadata.poll_errors()
+            err = helpers.rel_err(got.cpu().numpy(), want.cpu().numpy())
+            assert err <= helpers.FP32_TOL, "%d->%d: relative error %.3g" % (cin, cout, err)
+
+
 @pytest.mark.parametrize("gather", ["cp.async", "tma"])
 @pytest.mark.parametrize("mode,tol", MODES)
 def test_persistent_kernel_both_gathers(mode, tol, gather, cuda, restore_precision, monkeypatch):
