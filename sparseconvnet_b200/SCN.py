@@ -56,8 +56,28 @@ class DeferredCount(object):
 
     __rmul__ = __mul__
 
+    def __truediv__(self, other):
+        return self.resolve() / other
+
+    def __rtruediv__(self, other):
+        return other / self.resolve()
+
+    def __sub__(self, other):
+        return self.resolve() - other
+
+    def __rsub__(self, other):
+        return other - self.resolve()
+
     def __eq__(self, other):
         return self.resolve() == other
+
+    def __lt__(self, other):
+        return self.resolve() < other
+
+    def __gt__(self, other):
+        return self.resolve() > other
+
+    __hash__ = None
 
     def __repr__(self):
         return "DeferredCount(%r)" % (self._value if self._value is not None else "pending")

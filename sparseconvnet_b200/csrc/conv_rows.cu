@@ -48,29 +48,57 @@ __device__ __forceinline__ void rows_split(float x, unsigned &hi, unsigned &lo) 
   lo = __float_as_uint(x - __uint_as_float(hi));
 }
 
-// W [K][cin][cout] -> image [K][cin / 32][4][cout / 8][32] of (b0 hi, b1 hi, b0 lo, b1 lo): the B
-// fragments of lane (g, t) for k-block kb of the chunk and output planes 8 nt .. 8 nt + 7, already
-// split (see the layout note above)
+__device__ __forceinline__ void rows_mma_bf16(float (&d)[4], const unsigned (&a)[4], const unsigned (&b)[2]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+// two values as a bf16 pair, `first` in the low half (the lower k index of the fragment register)
+__device__ __forceinline__ unsigned rows_pack_bf16(float first, float second) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(first, second);
+  return *reinterpret_cast<const unsigned *>(&v);
+}
+
+// The product of 16 input planes is four tensor instructions: the large term hi x hi as two tf32
+// m16n8k8, the two small terms lo x W and x x W_lo as one bf16 m16n8k16 each (a bf16 instruction
+// takes the issue slot of a tf32 one and covers twice the planes; the small terms are 2^-11 of
+// the result, so bf16's 2^-9 leaves 2^-20).  Lane (g, t) feeds planes P+t, P+t+4 (the first tf32
+// instruction's k = t, t+4) and P+8+t, P+12+t (the second's) into k slots 2t, 2t+1 and 2t+8, 2t+9
+// of the bf16 instructions, the same assignment on the A and the B side.
+//
+// W [K][cin][cout] -> image [K][cin / 32][2][cout / 8][32][2] of uint4:
+//   [0] = tf32 hi of W[P+t][n], W[P+t+4][n], W[P+8+t][n], W[P+12+t][n]       (n = 8 nt + g)
+//   [1] = bf16 pairs (W[P+t], W[P+t+4]), (W[P+8+t], W[P+12+t]), then the same of W - hi
 __global__ void k_rows_prepare(const float *__restrict__ w, uint4 *__restrict__ img, int K, int cin, int cout) {
   const int nt_n = cout / 8, nch = cin / kRChunk;
-  const long long total = (long long)K * nch * 4 * nt_n * 32;
+  const long long total = (long long)K * nch * 2 * nt_n * 32;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const int lane = (int)(i & 31);
   long long r = i >> 5;
   const int nt = (int)(r % nt_n);
   r /= nt_n;
-  const int kb = (int)(r & 3);
-  r >>= 2;
+  const int kp = (int)(r & 1);
+  r >>= 1;
   const int c = (int)(r % nch);
   const int k = (int)(r / nch);
   const int g = lane >> 2, t = lane & 3;
-  const int p0 = c * kRChunk + kb * 8 + t, n = nt * 8 + g;
+  const int p0 = c * kRChunk + kp * 16 + t, n = nt * 8 + g;
   const float *wk = w + ((long long)k * cin + p0) * cout + n;
-  uint4 o;
-  rows_split(wk[0], o.x, o.z);
-  rows_split(wk[4 * (long long)cout], o.y, o.w);
-  img[i] = o;
+  const float x0 = wk[0], x1 = wk[4 * (long long)cout], x2 = wk[8 * (long long)cout], x3 = wk[12 * (long long)cout];
+  uint4 hi, lo;
+  rows_split(x0, hi.x, lo.x);
+  rows_split(x1, hi.y, lo.y);
+  rows_split(x2, hi.z, lo.z);
+  rows_split(x3, hi.w, lo.w);
+  uint4 pk;
+  pk.x = rows_pack_bf16(x0, x1);
+  pk.y = rows_pack_bf16(x2, x3);
+  pk.z = rows_pack_bf16(__uint_as_float(lo.x), __uint_as_float(lo.y));
+  pk.w = rows_pack_bf16(__uint_as_float(lo.z), __uint_as_float(lo.w));
+  img[2 * i] = hi;
+  img[2 * i + 1] = pk;
 }
 
 // One (offset, 32-plane chunk) step of a warp: its two 16-row tiles times the slab.
@@ -86,60 +114,70 @@ __global__ void k_rows_prepare(const float *__restrict__ w, uint4 *__restrict__ 
 // weight fragments held two k-blocks ahead in registers (same); the image without the split,
 // hi and lo made in registers (half the L2 traffic, 6 % slower).
 template <int NT>
+__device__ __forceinline__ void rows_tile16(float (&d)[NT][4], const float *ap, const unsigned (&bh)[NT][4],
+                                            const unsigned (&bp)[NT][4]) {
+  // planes P+t, P+t+4, P+8+t, P+12+t of rows g and g + 8
+  const float x00 = ap[0], x01 = ap[4], x02 = ap[8], x03 = ap[12];
+  const float x10 = ap[8 * kRAStride], x11 = ap[8 * kRAStride + 4], x12 = ap[8 * kRAStride + 8],
+              x13 = ap[8 * kRAStride + 12];
+  unsigned h0[4], h1[4], l[8];
+  rows_split(x00, h0[0], l[0]);
+  rows_split(x10, h0[1], l[1]);
+  rows_split(x01, h0[2], l[2]);
+  rows_split(x11, h0[3], l[3]);
+  rows_split(x02, h1[0], l[4]);
+  rows_split(x12, h1[1], l[5]);
+  rows_split(x03, h1[2], l[6]);
+  rows_split(x13, h1[3], l[7]);
+  unsigned alo[4], ax[4];
+  alo[0] = rows_pack_bf16(__uint_as_float(l[0]), __uint_as_float(l[2]));  // row g:     planes P+t, P+t+4
+  alo[1] = rows_pack_bf16(__uint_as_float(l[1]), __uint_as_float(l[3]));  // row g + 8
+  alo[2] = rows_pack_bf16(__uint_as_float(l[4]), __uint_as_float(l[6]));  // row g:     planes P+8+t, P+12+t
+  alo[3] = rows_pack_bf16(__uint_as_float(l[5]), __uint_as_float(l[7]));
+  ax[0] = rows_pack_bf16(x00, x01);
+  ax[1] = rows_pack_bf16(x10, x11);
+  ax[2] = rows_pack_bf16(x02, x03);
+  ax[3] = rows_pack_bf16(x12, x13);
+  // the small terms first; consecutive instructions write different accumulators
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    const unsigned b[2] = {bp[nt][0], bp[nt][1]};
+    rows_mma_bf16(d[nt], alo, b);
+  }
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    const unsigned b[2] = {bp[nt][2], bp[nt][3]};
+    rows_mma_bf16(d[nt], ax, b);
+  }
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    const unsigned b[2] = {bh[nt][0], bh[nt][1]};
+    rows_mma(d[nt], h0, b);
+  }
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    const unsigned b[2] = {bh[nt][2], bh[nt][3]};
+    rows_mma(d[nt], h1, b);
+  }
+}
+
+template <int NT>
 __device__ __forceinline__ void rows_chunk(float (&d)[2][NT][4], const float *a_stage, const uint4 *w_slab,
                                            int lane, unsigned m0, unsigned m1) {
   const int g = lane >> 2, t = lane & 3;
   const float *a_lane = a_stage + g * kRAStride + t;
 #pragma unroll
-  for (int kb = 0; kb < 4; ++kb) {
-    unsigned bh[NT][2], bl[NT][2];
+  for (int kp = 0; kp < 2; ++kp) {
+    unsigned bh[NT][4], bp[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-      const uint4 b = __ldg(w_slab + (kb * NT + nt) * 32 + lane);
-      bh[nt][0] = b.x, bh[nt][1] = b.y, bl[nt][0] = b.z, bl[nt][1] = b.w;
+      const uint4 q0 = __ldg(w_slab + ((kp * NT + nt) * 32 + lane) * 2);
+      const uint4 q1 = __ldg(w_slab + ((kp * NT + nt) * 32 + lane) * 2 + 1);
+      bh[nt][0] = q0.x, bh[nt][1] = q0.y, bh[nt][2] = q0.z, bh[nt][3] = q0.w;
+      bp[nt][0] = q1.x, bp[nt][1] = q1.y, bp[nt][2] = q1.z, bp[nt][3] = q1.w;
     }
-    if (NT <= 4 && m0 != 0 && m1 != 0) {
-      // both tiles: their instructions interleaved, an accumulator comes round every 2 NT instructions
-      unsigned ah[2][4], al[2][4];
-#pragma unroll
-      for (int mt = 0; mt < 2; ++mt) {
-        const float *ap = a_lane + mt * 16 * kRAStride + kb * 8;
-        rows_split(ap[0], ah[mt][0], al[mt][0]);
-        rows_split(ap[8 * kRAStride], ah[mt][1], al[mt][1]);
-        rows_split(ap[4], ah[mt][2], al[mt][2]);
-        rows_split(ap[8 * kRAStride + 4], ah[mt][3], al[mt][3]);
-      }
-#pragma unroll
-      for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) rows_mma(d[mt][nt], al[mt], bh[nt]);
-#pragma unroll
-      for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) rows_mma(d[mt][nt], ah[mt], bl[nt]);
-#pragma unroll
-      for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) rows_mma(d[mt][nt], ah[mt], bh[nt]);
-    } else {
-#pragma unroll
-      for (int mt = 0; mt < 2; ++mt) {
-        if ((mt == 0 ? m0 : m1) == 0) continue;
-        const float *ap = a_lane + mt * 16 * kRAStride + kb * 8;
-        unsigned ah[4], al[4];
-        rows_split(ap[0], ah[0], al[0]);
-        rows_split(ap[8 * kRAStride], ah[1], al[1]);
-        rows_split(ap[4], ah[2], al[2]);
-        rows_split(ap[8 * kRAStride + 4], ah[3], al[3]);
-        // the small terms first; consecutive instructions write different accumulators
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) rows_mma(d[mt][nt], al, bh[nt]);
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) rows_mma(d[mt][nt], ah, bl[nt]);
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) rows_mma(d[mt][nt], ah, bh[nt]);
-      }
-    }
+    if (m0 != 0) rows_tile16<NT>(d[0], a_lane + kp * 16, bh, bp);
+    if (m1 != 0) rows_tile16<NT>(d[1], a_lane + 16 * kRAStride + kp * 16, bh, bp);
   }
 }
 
