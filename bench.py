@@ -414,8 +414,8 @@ def main():
                       "profiles/k_conv_tma_tf32x3_unet3d_4rooms.md",
         "k_conv_pipe_mma": "instruction issue and shared-memory data pipe of small (offset, 128-row) steps, see "
                            "profiles/k_conv_pipe_mma_unet3d_4and8rooms.md",
-        "k_conv_rows": "warp-level tensor pipe 50 % busy; the rest is latency of the weight-fragment loads "
-                       "(L1 hit rate 41 %) and dependent issue, see profiles/k_conv_rows_unet3d_4rooms.md"}.get(top)
+        "k_conv_rows": "LSU data pipe 75 % busy (fragment loads, weight fragments from L2), warp-level tensor pipe "
+                       "43-50 %, see profiles/k_conv_rows_unet3d_4rooms.md"}.get(top)
     breakdown = {k: {"ms": round(v["ms"], 4), "calls": v["calls"],
                      "GBps": round(v["bytes"] / (v["ms"] / 1e3) / 1e9, 1) if v["ms"] > 0 else None}
                  for k, v in sorted(agg.items(), key=lambda kv: -kv[1]["ms"])}
