@@ -162,7 +162,13 @@ __global__ void k_insert_input(KeyLayout L, HashTable T, const long long *__rest
     slot_of[i] = -1;
     return;
   }
-  atomicMax(&scalars[1], (int)bl);
+  // largest batch index: one atomic per warp, and none once the word already holds the value
+  {
+    const unsigned peers = __activemask();
+    const int warp_max = __reduce_max_sync(peers, (int)bl);
+    if ((threadIdx.x & 31) == __ffs(peers) - 1 && warp_max > *(volatile int *)&scalars[1])
+      atomicMax(&scalars[1], warp_max);
+  }
   slot_of[i] = (int)s;
   if (mode == 0) {
     row_keys[i] = key;
