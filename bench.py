@@ -472,6 +472,33 @@ def main():
             variants[mode] = total_vox * max(2, args.steps // 2) / (ms_v / 1e3)
         scn.set_precision(args.precision)
 
+    # ---- training step of the same network (forward + backward + SGD), two rooms -----------------
+    training = None
+    if rank == 0 and world == 1 and not args.no_variants:
+        inp_t, net_t, head_t = workloads.build_config(CONFIG)
+        net_t.to(dev).train()
+        head_t.to(dev).train()
+        ct_np, ft_np = workloads.make_batch(CONFIG, [0, 1])
+        ct, ft = torch.from_numpy(ct_np), torch.from_numpy(ft_np).to(dev)
+        params = list(net_t.parameters()) + list(head_t.parameters())
+        opt = torch.optim.SGD(params, lr=1e-3)
+        labels = torch.randint(0, 20, (ct_np.shape[0],), device=dev, generator=torch.Generator(dev).manual_seed(1))
+
+        def train_step():
+            logits = head_t(net_t(inp_t([ct, ft])).features)
+            loss = torch.nn.functional.cross_entropy(logits, labels[:logits.size(0)])
+            opt.zero_grad(set_to_none=True)
+            loss.backward()
+            opt.step()
+            return loss
+
+        train_step()
+        ms_t, _ = timed(train_step, 3)
+        training = {"workload": workload_name(2), "voxels_per_step": int(ct_np.shape[0]), "ms_per_step": ms_t / 3,
+                    "voxels_per_sec": ct_np.shape[0] * 3 / (ms_t / 1e3), "forward": scn.get_precision(),
+                    "backward": "fp32", "optimizer": "SGD"}
+        del net_t, head_t, params, opt
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline_sample()
@@ -490,7 +517,7 @@ def main():
                     "d2h_bytes_per_step": int(out_host.numel() * 4)},
             "gpu_launches": int(launches), "ms_each_step": per_step,
             "roofline": roofline, "breakdown_ms_per_step": breakdown, "submanifold_conv": sub,
-            "variants_voxels_per_sec": variants,
+            "variants_voxels_per_sec": variants, "training_step": training,
             "cpu_baseline": cpu, "clocks": clocks,
         }
         print(json.dumps(line))
