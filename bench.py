@@ -492,11 +492,15 @@ def main():
             opt.step()
             return loss
 
-        train_step()
-        ms_t, _ = timed(train_step, 3)
+        scn.set_backward_precision(args.precision)  # input gradients on the forward's kernels
+        try:
+            train_step()
+            ms_t, _ = timed(train_step, 3)
+        finally:
+            scn.set_backward_precision("fp32")
         training = {"workload": workload_name(2), "voxels_per_step": int(ct_np.shape[0]), "ms_per_step": ms_t / 3,
                     "voxels_per_sec": ct_np.shape[0] * 3 / (ms_t / 1e3), "forward": scn.get_precision(),
-                    "backward": "fp32", "optimizer": "SGD"}
+                    "backward": "input gradients %s, weight gradients fp32" % args.precision, "optimizer": "SGD"}
         del net_t, head_t, params, opt
 
     cpu = None

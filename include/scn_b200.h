@@ -196,6 +196,13 @@ SCN_API int scn_last_conv_kernel(void);
  * object is gone and is given back with scn_count_ticket_release.  Off by default: *macs is then
  * always the count.  No counterpart in the reference. */
 SCN_API int scn_set_deferred_counts(int on);
+
+/* Arithmetic (an scn_precision value) of the input-gradient pass of the three convolution backward
+ * entry points, which runs the forward kernels on the opposite rulebook table with transposed
+ * weights.  Default SCN_PRECISION_FP32; SCN_PRECISION_TF32X3 keeps fp32-class gradients on the tensor
+ * paths.  The weight and bias gradients are always reduced in fp32, in a fixed order.  No
+ * counterpart in the reference. */
+SCN_API int scn_set_backward_precision(int precision);
 SCN_API int scn_md_take_count_ticket(scn_metadata *md, void **ticket);
 SCN_API int scn_count_ticket_total(void *ticket, int64_t *total);
 SCN_API int scn_count_ticket_release(void *ticket);

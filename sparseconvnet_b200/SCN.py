@@ -147,6 +147,25 @@ def get_precision():
     return ("fp32", "tf32", "bf16", "tf32x3")[_precision]
 
 
+_backward_precision = PRECISION_FP32
+
+
+def set_backward_precision(p):
+    """Arithmetic of the input-gradient pass of the convolutions' backward (the forward kernels on
+    the opposite rulebook table): 'fp32' (default) or 'tf32x3' keep fp32-class gradients, 'tf32' /
+    'bf16' are single-pass.  Weight and bias gradients are always reduced in fp32."""
+    global _backward_precision
+    table = {"fp32": 0, "tf32": 1, "bf16": 2, "tf32x3": 3, 0: 0, 1: 1, 2: 2, 3: 3}
+    if p not in table:
+        raise ValueError("precision must be 'fp32', 'tf32x3', 'tf32' or 'bf16'")
+    check(lib.scn_set_backward_precision(table[p]))
+    _backward_precision = table[p]
+
+
+def get_backward_precision():
+    return ("fp32", "tf32", "bf16", "tf32x3")[_backward_precision]
+
+
 def _stream():
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 

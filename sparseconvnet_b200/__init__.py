@@ -13,7 +13,7 @@ import types as _types
 forward_pass_hidden_states = 0
 
 from . import SCN  # noqa: E402  (loads libscn_b200.so; fails loudly if it is missing)
-from .SCN import set_precision, get_precision  # noqa: E402
+from .SCN import set_precision, get_precision, set_backward_precision, get_backward_precision  # noqa: E402
 from .sparse_tensor import SparseConvNetTensor, to_long_tensor as toLongTensor  # noqa: E402
 
 

@@ -20,6 +20,7 @@ SIGNATURES = {
     "scn_launch_count": (C.c_longlong, []),
     "scn_last_conv_kernel": (C.c_int, []),
     "scn_set_deferred_counts": (C.c_int, [C.c_int]),
+    "scn_set_backward_precision": (C.c_int, [C.c_int]),
     "scn_md_take_count_ticket": (C.c_int, [_vp, C.POINTER(_vp)]),
     "scn_count_ticket_total": (C.c_int, [_vp, _i64p]),
     "scn_count_ticket_release": (C.c_int, [_vp]),

@@ -37,6 +37,54 @@ int conv_forward_rows_thin(const float *in, long long n_in, float *out, long lon
 
 static thread_local int g_last_kernel = -1;
 static std::atomic<int> g_deferred_counts{0};
+std::atomic<int> g_backward_precision{SCN_PRECISION_FP32};  // arithmetic of the input-gradient pass
+
+// Kernel choice for out [rows_out, groups * cout] = bias + sum_k in[table[k][.]] @ W[k]; shared by the
+// forward operators and by the input-gradient pass of the backward ones (same kernels, opposite table).
+int conv_forward_dispatch(const float *in, long long rows_in, float *out, long long rows_out, const float *weight,
+                          const float *bias, const int *table, int K, int cin, int cout, int groups, int precision,
+                          int *flags, cudaStream_t stream) {
+  // TF32X3 is the fp32-accuracy mode: each shape runs whichever fp32-class kernel is fastest.
+  // With 32 or 64 output planes (and first layers) that is the row-stationary kernel of
+  // conv_rows.cu on the warp-level tensor path; other narrow shapes take the pipelined kernel of
+  // conv_pipe.cu with three tf32 mma.sync passes on compacted 16-pair tiles.  The tcgen05 tile costs
+  // the same per 8 input planes and 256 rows whatever Cout and however few of the rows have a
+  // rule, so it only pays from SCN_X3_MIN_COUT output planes on.
+  const int x3_min_cout = getenv("SCN_X3_MIN_COUT") ? atoi(getenv("SCN_X3_MIN_COUT")) : 65;
+  const bool narrow_x3 = precision == SCN_PRECISION_TF32X3 && cout < x3_min_cout;
+  // The persistent kernel runs one CTA per SM over whole tiles; with fewer tiles than SMs the
+  // per-tile kernel is used instead, which splits a tile's filter offsets over several CTAs.
+  const bool force_persistent = getenv("SCN_TC_PERSISTENT") && atoi(getenv("SCN_TC_PERSISTENT")) != 0;
+  const bool few_tiles = rows_out <= 148 * 256 && !force_persistent;
+  const bool use_rows = !(getenv("SCN_X3_ROWS") && atoi(getenv("SCN_X3_ROWS")) == 0);
+  if (narrow_x3 && use_rows && conv_rows_thin_supported(out, bias, cin, cout, groups)) {
+    SCN_TRY(conv_forward_rows_thin(in, rows_in, out, rows_out, weight, bias, table, K, cin, cout,
+                                   flags, stream));
+    g_last_kernel = SCN_KERNEL_CONV_ROWS;
+  } else if (narrow_x3 && use_rows && conv_rows_supported(in, out, weight, bias, K, cin, cout, groups)) {
+    SCN_TRY(conv_forward_rows(in, rows_in, out, rows_out, weight, bias, table, K, cin, cout,
+                              flags, stream));
+    g_last_kernel = SCN_KERNEL_CONV_ROWS;
+  } else if (narrow_x3 && cin % 8 == 0 && conv_pipe_supported(in, out, weight, bias, K, cin, cout)) {
+    SCN_TRY(conv_forward_pipe(in, rows_in, out, rows_out, weight, bias, table, K, cin, cout, groups, 1,
+                              flags, stream));
+    g_last_kernel = SCN_KERNEL_CONV_PIPE_MMA;
+  } else if (precision != SCN_PRECISION_FP32 && !narrow_x3 && !few_tiles &&
+      conv_tma_supported(K, cin, cout, groups, precision, rows_in)) {
+    SCN_TRY(conv_forward_tma(in, rows_in, out, rows_out, weight, bias, table, K, cin, cout,
+                             precision, flags, stream));
+    g_last_kernel = SCN_KERNEL_CONV_TC_PERSISTENT;
+  } else if (precision != SCN_PRECISION_FP32 && !narrow_x3 && conv_tc_supported(cin, cout, groups, precision)) {
+    SCN_TRY(conv_forward_tc(in, rows_in, out, rows_out, weight, bias, table, K, cin, cout,
+                            precision, flags, stream));
+    g_last_kernel = SCN_KERNEL_CONV_TC;
+  } else {
+    SCN_TRY(conv_forward_simt(in, rows_in, out, rows_out, weight, bias, table, K, cin, cout,
+                              groups, flags, stream));
+    g_last_kernel = SCN_KERNEL_CONV_SIMT;
+  }
+  return SCN_OK;
+}
 
 static int run_conv(scn_metadata *md, Rulebook &rb, bool transposed, const float *in, float *out,
                     const float *weight, const float *bias, int n_in_planes, int n_out_planes, int groups,
@@ -61,45 +109,8 @@ static int run_conv(scn_metadata *md, Rulebook &rb, bool transposed, const float
       SCN_TRY(device_alloc((void **)&md->flags_dev, sizeof(int), stream));
       SCN_CUDA_CHECK(cudaMemsetAsync(md->flags_dev, 0, sizeof(int), stream));
     }
-    // TF32X3 is the fp32-accuracy mode: each shape runs whichever fp32-class kernel is fastest.
-    // Up to 64 output planes that is the pipelined kernel of conv_pipe.cu with its arithmetic on
-    // the warp-level tensor path (three tf32 mma.sync passes on compacted 16-pair tiles): the
-    // tcgen05 tile costs the same per 8 input planes and 256 rows whatever Cout and however few
-    // of the rows have a rule.  SCN_X3_MIN_COUT moves the threshold (layers with fewer output
-    // planes than it stay off tcgen05).
-    const int x3_min_cout = getenv("SCN_X3_MIN_COUT") ? atoi(getenv("SCN_X3_MIN_COUT")) : 65;
-    const bool narrow_x3 = precision == SCN_PRECISION_TF32X3 && cout < x3_min_cout;
-    // The persistent kernel runs one CTA per SM over whole tiles; with fewer tiles than SMs the
-    // per-tile kernel is used instead, which splits a tile's filter offsets over several CTAs.
-    const bool force_persistent = getenv("SCN_TC_PERSISTENT") && atoi(getenv("SCN_TC_PERSISTENT")) != 0;
-    const bool few_tiles = rows_out <= 148 * 256 && !force_persistent;
-    const bool use_rows = !(getenv("SCN_X3_ROWS") && atoi(getenv("SCN_X3_ROWS")) == 0);
-    if (narrow_x3 && use_rows && conv_rows_thin_supported(out, bias, cin, cout, groups)) {
-      SCN_TRY(conv_forward_rows_thin(in, rows_in, out, rows_out, weight, bias, table, rb.n_offsets, cin, cout,
-                                     md->flags_dev, stream));
-      g_last_kernel = SCN_KERNEL_CONV_ROWS;
-    } else if (narrow_x3 && use_rows && conv_rows_supported(in, out, weight, bias, rb.n_offsets, cin, cout, groups)) {
-      SCN_TRY(conv_forward_rows(in, rows_in, out, rows_out, weight, bias, table, rb.n_offsets, cin, cout,
-                                md->flags_dev, stream));
-      g_last_kernel = SCN_KERNEL_CONV_ROWS;
-    } else if (narrow_x3 && cin % 8 == 0 && conv_pipe_supported(in, out, weight, bias, rb.n_offsets, cin, cout)) {
-      SCN_TRY(conv_forward_pipe(in, rows_in, out, rows_out, weight, bias, table, rb.n_offsets, cin, cout, groups, 1,
-                                md->flags_dev, stream));
-      g_last_kernel = SCN_KERNEL_CONV_PIPE_MMA;
-    } else if (precision != SCN_PRECISION_FP32 && !narrow_x3 && !few_tiles &&
-        conv_tma_supported(rb.n_offsets, cin, cout, groups, precision, rows_in)) {
-      SCN_TRY(conv_forward_tma(in, rows_in, out, rows_out, weight, bias, table, rb.n_offsets, cin, cout,
-                               precision, md->flags_dev, stream));
-      g_last_kernel = SCN_KERNEL_CONV_TC_PERSISTENT;
-    } else if (precision != SCN_PRECISION_FP32 && !narrow_x3 && conv_tc_supported(cin, cout, groups, precision)) {
-      SCN_TRY(conv_forward_tc(in, rows_in, out, rows_out, weight, bias, table, rb.n_offsets, cin, cout,
-                              precision, md->flags_dev, stream));
-      g_last_kernel = SCN_KERNEL_CONV_TC;
-    } else {
-      SCN_TRY(conv_forward_simt(in, rows_in, out, rows_out, weight, bias, table, rb.n_offsets, cin, cout,
-                                groups, md->flags_dev, stream));
-      g_last_kernel = SCN_KERNEL_CONV_SIMT;
-    }
+    SCN_TRY(conv_forward_dispatch(in, rows_in, out, rows_out, weight, bias, table, rb.n_offsets, cin, cout, groups,
+                                  precision, md->flags_dev, stream));
   }
   if (macs) {  // the reference's return value: rules x ip x op x groups (CPU/Convolution.cpp:141)
     if (g_deferred_counts.load()) {
@@ -126,6 +137,13 @@ using namespace scn;
 extern "C" {
 
 int scn_last_conv_kernel(void) { return g_last_kernel; }
+
+int scn_set_backward_precision(int precision) {
+  SCN_REQUIRE(precision >= SCN_PRECISION_FP32 && precision <= SCN_PRECISION_TF32X3, SCN_ERR_BAD_ARG,
+              "unknown precision %d", precision);
+  g_backward_precision.store(precision);
+  return SCN_OK;
+}
 
 int scn_set_deferred_counts(int on) {
   g_deferred_counts.store(on ? 1 : 0);

@@ -12,10 +12,16 @@
 //   d_bias    column sums of d_out, the same two steps.
 #include <algorithm>
 
+#include <atomic>
+
 #include "metadata.cuh"
 
 namespace scn {
 
+extern std::atomic<int> g_backward_precision;
+int conv_forward_dispatch(const float *in, long long rows_in, float *out, long long rows_out, const float *weight,
+                          const float *bias, const int *table, int K, int cin, int cout, int groups, int precision,
+                          int *flags, cudaStream_t stream);
 int conv_forward_simt(const float *in, long long n_in, float *out, long long n_out, const float *weight,
                       const float *bias, const int *table, int K, int cin, int cout, int groups, int *flags,
                       cudaStream_t stream);
@@ -189,8 +195,8 @@ static int run_conv_backward(scn_metadata *md, Rulebook &rb, bool transposed, co
       SCN_TRY(rulebook_transposed(rb, stream));
       table = rb.tnbr;
     }
-    SCN_TRY(conv_forward_simt(d_out, rows_out, d_in, rows_in, wt, nullptr, table, K, cout, cin, groups,
-                              md->flags_dev, stream));
+    SCN_TRY(conv_forward_dispatch(d_out, rows_out, d_in, rows_in, wt, nullptr, table, K, cout, cin, groups,
+                                  g_backward_precision.load(), md->flags_dev, stream));
     SCN_TRY(device_free(wt, stream));
   }
   return SCN_OK;

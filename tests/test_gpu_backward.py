@@ -48,7 +48,18 @@ def _ref_input(ref, dim, size, coords, feats, mode=3):
                                                             (3, [16, 16, 16], 32, 32, 1, False),
                                                             (3, [16, 16, 16], 64, 48, 1, True)])
 @pytest.mark.parametrize("kind", ["sub", "conv", "deconv"])
-def test_convolution_gradients(ref, cuda, dim, size, cin, cout, groups, bias, kind):
+@pytest.mark.parametrize("bwd", ["fp32", "tf32x3"])
+def test_convolution_gradients(ref, cuda, dim, size, cin, cout, groups, bias, kind, bwd):
+    """`bwd`: arithmetic of the input-gradient pass (fp32 FMA, or the fp32-class tensor kernels)."""
+    import sparseconvnet_b200 as scn
+    scn.set_backward_precision(bwd)
+    try:
+        _convolution_gradients(ref, cuda, dim, size, cin, cout, groups, bias, kind)
+    finally:
+        scn.set_backward_precision("fp32")
+
+
+def _convolution_gradients(ref, cuda, dim, size, cin, cout, groups, bias, kind):
     import sparseconvnet_b200 as scn
     rng = np.random.default_rng(dim * 100 + cin)
     coords = _cloud(rng, size, 500, 2)
