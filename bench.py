@@ -248,6 +248,7 @@ def main():
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
+    count_group = shard.host_group() if world > 1 else None  # row counts travel on the host, not through the stream
 
     inp, net, head = workloads.build_config(CONFIG)
     net.to(dev)
@@ -266,7 +267,7 @@ def main():
         with torch.no_grad():
             y = head(net(inp([c, f])).features)
             if world > 1:
-                shard.gather_rows(y)
+                shard.gather_rows(y, count_group=count_group)
         return y
 
     def step_resident():

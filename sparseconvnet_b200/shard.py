@@ -29,17 +29,40 @@ def shard_batch(coords, features, rank, world, n_samples=None):
     return c, features[keep], (lo, hi)
 
 
-def gather_rows(rows, group=None):
+_host_groups = {}
+
+
+def host_group(group=None):
+    """A gloo group over the ranks of `group`, made on first use (every rank must call this at the
+    same point): row counts are exchanged through it, on the host."""
+    key = id(group)
+    if key not in _host_groups:
+        ranks = None if group is None else dist.get_process_group_ranks(group)
+        _host_groups[key] = dist.new_group(ranks=ranks, backend="gloo")
+    return _host_groups[key]
+
+
+def gather_rows(rows, group=None, count_group=None):
     """All ranks' row blocks concatenated in rank order (= batch order when every rank's rows
     are in batch order).  Blocks may have different row counts: counts are exchanged first,
     blocks padded to the largest, gathered with one all_gather, and trimmed.
+    `count_group` (see host_group): the counts, which every rank knows on the host, travel through
+    this CPU group; nothing then waits for the GPU, so the launches of the next step keep running
+    ahead.  Without it the counts go through `group` itself and are read back from the device,
+    which waits for the stream.
     Returns (gathered [sum n_r, C], counts list)."""
     if not dist.is_available() or not dist.is_initialized() or dist.get_world_size(group) == 1:
         return rows, [rows.shape[0]]
     world = dist.get_world_size(group)
-    n = torch.tensor([rows.shape[0]], dtype=torch.int64, device=rows.device)
-    counts = torch.empty(world, dtype=torch.int64, device=rows.device)
-    dist.all_gather_into_tensor(counts, n, group=group)
+    if count_group is not None:
+        n = torch.tensor([rows.shape[0]], dtype=torch.int64)
+        parts = [torch.empty(1, dtype=torch.int64) for _ in range(world)]
+        dist.all_gather(parts, n, group=count_group)
+        counts = torch.cat(parts)
+    else:
+        n = torch.tensor([rows.shape[0]], dtype=torch.int64, device=rows.device)
+        counts = torch.empty(world, dtype=torch.int64, device=rows.device)
+        dist.all_gather_into_tensor(counts, n, group=group)
     counts = counts.tolist()
     width = rows.shape[1:]
     biggest = max(counts)
