@@ -267,8 +267,18 @@ def main():
         with torch.no_grad():
             y = head(net(inp([c, f])).features)
             if world > 1:
-                shard.gather_rows(y, count_group=count_group)
+                # the gather of step i runs beside the kernels of step i+1; its result is taken one
+                # step later (and after the last step, inside the timed region: drain_gather)
+                pending.append(shard.gather_rows(y, count_group=count_group, async_op=True))
+                if len(pending) > 1:
+                    pending.pop(0).result()
         return y
+
+    pending = []
+
+    def drain_gather():
+        while pending:
+            pending.pop(0).result()
 
     def step_resident():
         return forward(coords_dev, feats_dev)
@@ -355,6 +365,7 @@ def main():
                 marks[i].record()
         if end:
             end()
+        drain_gather()
         b.record()
         barrier()
         ms = a.elapsed_time(b)

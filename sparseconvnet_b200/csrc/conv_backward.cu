@@ -12,6 +12,8 @@
 //   d_bias    column sums of d_out, the same two steps.
 #include <algorithm>
 
+#include <stdlib.h>
+
 #include <atomic>
 
 #include "metadata.cuh"
@@ -102,6 +104,142 @@ k_conv_dweight(const float *__restrict__ in, int ld_in, long long n_in_rows, con
     }
 }
 
+// The same partial sums on the warp-level tensor path, for groups = 1 and plane counts that are
+// multiples of 32: grid = (chunks, K, c-tiles * n-tiles), four warps.  Each warp takes a contiguous
+// quarter of the chunk's rulebook entries, keeps only the entries that hold a rule (a third of them
+// on surface data: the FMA kernel above multiplies the empty ones as zeros), and accumulates the
+// 32 x 32 tile  in^T [32 x 8 rules] x d_out [8 rules x 32]  per block of eight rules with
+// mma.sync.m16n8k8 on the hi/lo split of both operands (hi x hi + hi x lo + lo x hi, fp32
+// accumulate: fp32-class accuracy).  The four warps' tiles are added in warp order, so the result
+// does not depend on timing.
+__device__ __forceinline__ void dw_mma(float (&d)[4], const unsigned (&a)[4], const unsigned (&b)[2]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+__device__ __forceinline__ void dw_split(float x, unsigned &hi, unsigned &lo) {
+  hi = __float_as_uint(x) & 0xFFFFE000u;
+  lo = __float_as_uint(x - __uint_as_float(hi));
+}
+
+__global__ void __launch_bounds__(128)
+k_conv_dweight_mma(const float *__restrict__ in, int ld_in, long long n_in_rows, const float *__restrict__ dout,
+                   int ld_out, long long n_out_rows, const int *__restrict__ nbr, long long n_entries, int swap,
+                   int cin, int cout, long long chunk_rows, float *__restrict__ partial, int *flags) {
+  constexpr unsigned kFull = 0xffffffffu;
+  __shared__ int q_in[4][64], q_out[4][64];  // per warp: rules waiting for a block of eight
+  __shared__ float tile[4][32][33];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int k = blockIdx.y;
+  const int tiles_n = cout / 32;
+  const int c0 = (blockIdx.z / tiles_n) * 32, n0 = (blockIdx.z % tiles_n) * 32;
+  const long long j0 = (long long)blockIdx.x * chunk_rows;
+  const long long j1 = min(n_entries, j0 + chunk_rows);
+  const long long per_warp = ((j1 - j0 + 3) / 4 + 31) / 32 * 32;
+  const long long w0 = min(j1, j0 + warp * per_warp), w1 = min(j1, w0 + per_warp);
+  const int *col = nbr + (long long)k * n_entries;
+
+  float d[2][4][4];
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) d[mt][nt][0] = d[mt][nt][1] = d[mt][nt][2] = d[mt][nt][3] = 0.f;
+
+  // one block of eight rules starting at queue position `head`; `count` (< 8 only at the end) are real
+  auto block = [&](int head, int count) {
+    const int p0 = (head + t) & 63, p1 = (head + t + 4) & 63;
+    const bool ok0 = t < count, ok1 = t + 4 < count;
+    const long long ri0 = ok0 ? q_in[warp][p0] : 0, ri1 = ok1 ? q_in[warp][p1] : 0;
+    const long long ro0 = ok0 ? q_out[warp][p0] : 0, ro1 = ok1 ? q_out[warp][p1] : 0;
+    const float *a0p = in + ri0 * ld_in + c0 + g, *a1p = in + ri1 * ld_in + c0 + g;
+    const float *b0p = dout + ro0 * ld_out + n0 + g, *b1p = dout + ro1 * ld_out + n0 + g;
+    float av[2][4], bv[4][2];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt) {  // A[m = plane][k = rule]: a0 (g, t), a1 (g + 8, t), a2 (g, t + 4), a3 (g + 8, t + 4)
+      av[mt][0] = ok0 ? __ldg(a0p + mt * 16) : 0.f;
+      av[mt][1] = ok0 ? __ldg(a0p + mt * 16 + 8) : 0.f;
+      av[mt][2] = ok1 ? __ldg(a1p + mt * 16) : 0.f;
+      av[mt][3] = ok1 ? __ldg(a1p + mt * 16 + 8) : 0.f;
+    }
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {  // B[k = rule][n = plane]: b0 (t, g), b1 (t + 4, g)
+      bv[nt][0] = ok0 ? __ldg(b0p + nt * 8) : 0.f;
+      bv[nt][1] = ok1 ? __ldg(b1p + nt * 8) : 0.f;
+    }
+    unsigned ah[2][4], al[2][4], bh[4][2], bl[4][2];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) dw_split(av[mt][e], ah[mt][e], al[mt][e]);
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      dw_split(bv[nt][0], bh[nt][0], bl[nt][0]);
+      dw_split(bv[nt][1], bh[nt][1], bl[nt][1]);
+    }
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) dw_mma(d[mt][nt], al[mt], bh[nt]);
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) dw_mma(d[mt][nt], ah[mt], bl[nt]);
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) dw_mma(d[mt][nt], ah[mt], bh[nt]);
+  };
+
+  int head = 0, tail = 0;  // queue positions (not wrapped)
+  for (long long jb = w0; jb < w1; jb += 32) {
+    const long long j = jb + lane;
+    int ri = -1, ro = -1;
+    if (j < w1) {
+      const int a = __ldg(col + j);
+      if (a >= 0) {
+        ri = swap ? (int)j : a;
+        ro = swap ? a : (int)j;
+        if (ri >= n_in_rows || ro >= n_out_rows) {
+          atomicOr(flags, FLAG_BAD_ROW);
+          ri = ro = -1;
+        }
+      }
+    }
+    const unsigned m = __ballot_sync(kFull, ri >= 0);
+    if (ri >= 0) {
+      const int p = (tail + __popc(m & ((1u << lane) - 1u))) & 63;
+      q_in[warp][p] = ri;
+      q_out[warp][p] = ro;
+    }
+    tail += __popc(m);
+    __syncwarp();
+    while (tail - head >= 8) {
+      block(head, 8);
+      head += 8;
+    }
+    __syncwarp();  // the blocks' reads of the queue come before the next group's writes
+  }
+  if (tail > head) block(head, tail - head);
+
+  // ---- the four warps' tiles, added in warp order ------------------------------------------------
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {  // d0 (g, 2t), d1 (g, 2t + 1), d2 (g + 8, 2t), d3 (g + 8, 2t + 1)
+      tile[warp][mt * 16 + g][nt * 8 + 2 * t] = d[mt][nt][0];
+      tile[warp][mt * 16 + g][nt * 8 + 2 * t + 1] = d[mt][nt][1];
+      tile[warp][mt * 16 + g + 8][nt * 8 + 2 * t] = d[mt][nt][2];
+      tile[warp][mt * 16 + g + 8][nt * 8 + 2 * t + 1] = d[mt][nt][3];
+    }
+  __syncthreads();
+  float *dst = partial + ((long long)blockIdx.x * gridDim.y + k) * cin * cout;
+  for (int i = threadIdx.x; i < 32 * 32; i += 128) {
+    const int c = i >> 5, n = i & 31;
+    dst[(long long)(c0 + c) * cout + n0 + n] = ((tile[0][c][n] + tile[1][c][n]) + tile[2][c][n]) + tile[3][c][n];
+  }
+}
+
 // partial[chunk][p] = sum over the chunk's rows of x[row][p]; grid = (plane tiles of 32, chunks)
 __global__ void __launch_bounds__(256)
 k_column_sums(const float *__restrict__ x, long long n_rows, int planes, long long chunk_rows,
@@ -179,7 +317,11 @@ static int run_conv_backward(scn_metadata *md, Rulebook &rb, bool transposed, co
     float *partial = nullptr;
     SCN_TRY(device_alloc((void **)&partial, sizeof(float) * (size_t)chunks * w_elems, stream));
     const int tiles = groups * (int)ceil_div(cin, 32) * (int)ceil_div(cout, 32);
-    SCN_LAUNCH(k_conv_dweight, dim3((unsigned)chunks, (unsigned)K, (unsigned)tiles), 256, 0, stream, in, n_in_planes, rows_in, d_out, n_out_planes, rows_out, rb.nbr, n_entries, transposed ? 1 : 0, cin, cout, groups, chunk_rows, partial, md->flags_dev);
+    const bool fma_only = getenv("SCN_DWEIGHT_FMA") && atoi(getenv("SCN_DWEIGHT_FMA")) != 0;
+    if (groups == 1 && cin % 32 == 0 && cout % 32 == 0 && !fma_only)
+      SCN_LAUNCH(k_conv_dweight_mma, dim3((unsigned)chunks, (unsigned)K, (unsigned)tiles), 128, 0, stream, in, n_in_planes, rows_in, d_out, n_out_planes, rows_out, rb.nbr, n_entries, transposed ? 1 : 0, cin, cout, chunk_rows, partial, md->flags_dev);
+    else
+      SCN_LAUNCH(k_conv_dweight, dim3((unsigned)chunks, (unsigned)K, (unsigned)tiles), 256, 0, stream, in, n_in_planes, rows_in, d_out, n_out_planes, rows_out, rb.nbr, n_entries, transposed ? 1 : 0, cin, cout, groups, chunk_rows, partial, md->flags_dev);
     SCN_LAUNCH(k_sum_chunks, (unsigned)ceil_div(w_elems, 256), 256, 0, stream, partial, chunks, w_elems, d_weight);
     SCN_CUDA_CHECK(cudaGetLastError());
     SCN_TRY(device_free(partial, stream));

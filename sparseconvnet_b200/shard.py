@@ -42,7 +42,24 @@ def host_group(group=None):
     return _host_groups[key]
 
 
-def gather_rows(rows, group=None, count_group=None):
+class PendingGather(object):
+    """A gather_rows(..., async_op=True) in flight: `result()` makes the current stream wait for the
+    collective and returns what gather_rows returns."""
+
+    def __init__(self, out, keep, counts, biggest, work):
+        self.out, self.keep, self.counts, self.biggest, self.work = out, keep, counts, biggest, work
+
+    def result(self):
+        if self.work is not None:
+            self.work.wait()
+            self.work = None
+        counts, biggest, out = self.counts, self.biggest, self.out
+        if all(c == biggest for c in counts):
+            return out, counts
+        return torch.cat([out[r * biggest:r * biggest + counts[r]] for r in range(len(counts))]), counts
+
+
+def gather_rows(rows, group=None, count_group=None, async_op=False):
     """All ranks' row blocks concatenated in rank order (= batch order when every rank's rows
     are in batch order).  Blocks may have different row counts: counts are exchanged first,
     blocks padded to the largest, gathered with one all_gather, and trimmed.
@@ -50,9 +67,12 @@ def gather_rows(rows, group=None, count_group=None):
     this CPU group; nothing then waits for the GPU, so the launches of the next step keep running
     ahead.  Without it the counts go through `group` itself and are read back from the device,
     which waits for the stream.
+    `async_op`: returns a PendingGather right after the collective has been enqueued; kernels
+    launched afterwards (the next batch) run beside it.
     Returns (gathered [sum n_r, C], counts list)."""
     if not dist.is_available() or not dist.is_initialized() or dist.get_world_size(group) == 1:
-        return rows, [rows.shape[0]]
+        done = (rows, [rows.shape[0]])
+        return PendingGather(rows, None, done[1], rows.shape[0], None) if async_op else done
     world = dist.get_world_size(group)
     if count_group is not None:
         n = torch.tensor([rows.shape[0]], dtype=torch.int64)
@@ -70,8 +90,8 @@ def gather_rows(rows, group=None, count_group=None):
     if rows.shape[0] < biggest:
         padded = rows.new_zeros((biggest,) + tuple(width))
         padded[:rows.shape[0]] = rows
+    padded = padded.contiguous()
     out = rows.new_empty((world * biggest,) + tuple(width))
-    dist.all_gather_into_tensor(out, padded.contiguous(), group=group)
-    if all(c == biggest for c in counts):
-        return out, counts
-    return torch.cat([out[r * biggest:r * biggest + counts[r]] for r in range(world)]), counts
+    work = dist.all_gather_into_tensor(out, padded, group=group, async_op=async_op)
+    pending = PendingGather(out, padded, counts, biggest, work if async_op else None)
+    return pending if async_op else pending.result()

@@ -46,7 +46,8 @@ def _ref_input(ref, dim, size, coords, feats, mode=3):
 
 @pytest.mark.parametrize("dim,size,cin,cout,groups,bias", [(2, [17, 17], 6, 8, 2, True), (3, [15, 15, 15], 5, 7, 1, True),
                                                             (3, [16, 16, 16], 32, 32, 1, False),
-                                                            (3, [16, 16, 16], 64, 48, 1, True)])
+                                                            (3, [16, 16, 16], 64, 48, 1, True),
+                                                            (3, [16, 16, 16], 64, 96, 1, True)])
 @pytest.mark.parametrize("kind", ["sub", "conv", "deconv"])
 @pytest.mark.parametrize("bwd", ["fp32", "tf32x3"])
 def test_convolution_gradients(ref, cuda, dim, size, cin, cout, groups, bias, kind, bwd):

@@ -34,6 +34,8 @@ def _worker(rank, world, port_no, tmp):
     # the same with the counts exchanged through a host group of their own (what the GPU driver uses)
     gathered2, counts2 = shard.gather_rows(torch.from_numpy(y), count_group=shard.host_group())
     assert counts2 == counts and torch.equal(gathered2, gathered)
+    gathered3, counts3 = shard.gather_rows(torch.from_numpy(y), count_group=shard.host_group(), async_op=True).result()
+    assert counts3 == counts and torch.equal(gathered3, gathered)
     if rank == 0:
         full = runner.run_module(head, runner.run_module(net, runner.run_module(inp, [coords, feats], be), be), be)
         np.save(os.path.join(tmp, "ok.npy"), np.array([np.abs(gathered.numpy() - full).max(), full.shape[0],
