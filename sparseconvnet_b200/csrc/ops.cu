@@ -182,7 +182,23 @@ k_bn_back_sums(const float *__restrict__ in, const float *__restrict__ out, cons
   double s = 0.0, q = 0.0;
   if (c < C) {
     const float m = mean[c];
-    for (long long r = r0 + wy; r < r1; r += 8) {
+    long long r = r0 + wy;
+    for (; r + 24 < r1; r += 32) {  // four rows in flight per thread
+      float d[4], o[4], x[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        d[u] = d_out[(r + 8 * u) * out_stride + c];
+        o[u] = out[(r + 8 * u) * out_stride + c];
+        x[u] = in[(r + 8 * u) * in_stride + c];
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (!(o[u] > 0.f)) d[u] *= leak;
+        s += d[u];
+        q += (double)(x[u] - m) * d[u];
+      }
+    }
+    for (; r < r1; r += 8) {
       float d = d_out[r * out_stride + c];
       if (!(out[r * out_stride + c] > 0.f)) d *= leak;
       s += d;
@@ -480,7 +496,7 @@ int scn_batchnorm_backward(const float *in_features, float *d_in_features, const
     return SCN_OK;
   }
   SCN_REQUIRE(in_features && d_in_features && out_features && d_out_features, SCN_ERR_BAD_ARG, "null features");
-  const int chunks = (int)std::max<long long>(1, std::min<long long>(128, n_rows / 2048));
+  const int chunks = (int)std::max<long long>(1, std::min<long long>(1024, n_rows / 256));
   const long long chunk_rows = ceil_div(n_rows, chunks);
   double *partial = nullptr;
   float *coef = nullptr;
