@@ -112,7 +112,9 @@ __global__ void k_rows_prepare(const float *__restrict__ w, uint4 *__restrict__ 
 // output planes, slower by 12 % for 64); accumulators of their own for the two small terms (more
 // accurate, 2e-6, but the registers cost more warps than the shorter dependency chains gain);
 // weight fragments held two k-blocks ahead in registers (same); the image without the split,
-// hi and lo made in registers (half the L2 traffic, 6 % slower).
+// hi and lo made in registers (half the L2 traffic, 6 % slower); both tiles' instructions interleaved
+// in the tf32 + bf16 form (5 % slower: registers); no shared memory at all, the A values read straight
+// from the feature matrix one half-step ahead (27 % slower: registers, and the loads' latency).
 template <int NT>
 __device__ __forceinline__ void rows_tile16(float (&d)[NT][4], const float *ap, const unsigned (&bh)[NT][4],
                                             const unsigned (&bp)[NT][4]) {
