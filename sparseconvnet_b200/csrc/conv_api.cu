@@ -57,24 +57,28 @@ int conv_forward_dispatch(const float *in, long long rows_in, float *out, long l
   const bool force_persistent = getenv("SCN_TC_PERSISTENT") && atoi(getenv("SCN_TC_PERSISTENT")) != 0;
   const bool few_tiles = rows_out <= 148 * 256 && !force_persistent;
   const bool use_rows = !(getenv("SCN_X3_ROWS") && atoi(getenv("SCN_X3_ROWS")) == 0);
-  if (narrow_x3 && use_rows && conv_rows_thin_supported(out, bias, cin, cout, groups)) {
+  const bool rows_thin = narrow_x3 && use_rows && conv_rows_thin_supported(out, bias, cin, cout, groups);
+  const bool rows = narrow_x3 && use_rows && conv_rows_supported(in, out, weight, bias, K, cin, cout, groups);
+  const bool pipe_mma = narrow_x3 && cin % 8 == 0 && conv_pipe_supported(in, out, weight, bias, K, cin, cout);
+  // a narrow shape none of the three takes (more than 32 filter offsets, groups ...) goes on to tcgen05
+  const bool tensor = precision != SCN_PRECISION_FP32 && !(rows_thin || rows || pipe_mma);
+  if (rows_thin) {
     SCN_TRY(conv_forward_rows_thin(in, rows_in, out, rows_out, weight, bias, table, K, cin, cout,
                                    flags, stream));
     g_last_kernel = SCN_KERNEL_CONV_ROWS;
-  } else if (narrow_x3 && use_rows && conv_rows_supported(in, out, weight, bias, K, cin, cout, groups)) {
+  } else if (rows) {
     SCN_TRY(conv_forward_rows(in, rows_in, out, rows_out, weight, bias, table, K, cin, cout,
                               flags, stream));
     g_last_kernel = SCN_KERNEL_CONV_ROWS;
-  } else if (narrow_x3 && cin % 8 == 0 && conv_pipe_supported(in, out, weight, bias, K, cin, cout)) {
+  } else if (pipe_mma) {
     SCN_TRY(conv_forward_pipe(in, rows_in, out, rows_out, weight, bias, table, K, cin, cout, groups, 1,
                               flags, stream));
     g_last_kernel = SCN_KERNEL_CONV_PIPE_MMA;
-  } else if (precision != SCN_PRECISION_FP32 && !narrow_x3 && !few_tiles &&
-      conv_tma_supported(K, cin, cout, groups, precision, rows_in)) {
+  } else if (tensor && !few_tiles && conv_tma_supported(K, cin, cout, groups, precision, rows_in)) {
     SCN_TRY(conv_forward_tma(in, rows_in, out, rows_out, weight, bias, table, K, cin, cout,
                              precision, flags, stream));
     g_last_kernel = SCN_KERNEL_CONV_TC_PERSISTENT;
-  } else if (precision != SCN_PRECISION_FP32 && !narrow_x3 && conv_tc_supported(cin, cout, groups, precision)) {
+  } else if (tensor && conv_tc_supported(cin, cout, groups, precision)) {
     SCN_TRY(conv_forward_tc(in, rows_in, out, rows_out, weight, bias, table, K, cin, cout,
                             precision, flags, stream));
     g_last_kernel = SCN_KERNEL_CONV_TC;
