@@ -35,6 +35,10 @@ int conv_forward_rows_thin(const float *in, long long n_in, float *out, long lon
                            const float *bias, const int *table, int K, int cin, int cout, int *flags,
                            cudaStream_t stream);
 
+int conv_forward_rows_scatter(const float *in, long long n_in, float *out, long long n_out, const float *weight,
+                              const float *bias, const int *child_of, int K, int cin, int cout, int *flags,
+                              cudaStream_t stream);
+
 static thread_local int g_last_kernel = -1;
 static std::atomic<int> g_deferred_counts{0};
 std::atomic<int> g_backward_precision{SCN_PRECISION_FP32};  // arithmetic of the input-gradient pass
@@ -90,9 +94,10 @@ int conv_forward_dispatch(const float *in, long long rows_in, float *out, long l
   return SCN_OK;
 }
 
+// `disjoint` (only with `transposed`): every output row has exactly one rule (filter = stride).
 static int run_conv(scn_metadata *md, Rulebook &rb, bool transposed, const float *in, float *out,
                     const float *weight, const float *bias, int n_in_planes, int n_out_planes, int groups,
-                    int precision, cudaStream_t stream, double *macs) {
+                    int precision, cudaStream_t stream, double *macs, bool disjoint = false) {
   SCN_REQUIRE(groups >= 1 && n_in_planes >= 1 && n_out_planes >= 1 && n_in_planes % groups == 0 &&
                   n_out_planes % groups == 0,
               SCN_ERR_BAD_ARG, "planes %d -> %d not divisible into %d groups", n_in_planes, n_out_planes, groups);
@@ -103,7 +108,12 @@ static int run_conv(scn_metadata *md, Rulebook &rb, bool transposed, const float
   long long rows_in = transposed ? rb.n_out : rb.n_in;
   long long rows_out = transposed ? rb.n_in : rb.n_out;
   const int *table = rb.nbr;
-  if (transposed) {
+  // the transposed layer with one rule per output row runs from its input side, on the table as built
+  const bool scatter = transposed && disjoint && precision == SCN_PRECISION_TF32X3 && rows_in > 0 &&
+                       !(getenv("SCN_X3_ROWS") && atoi(getenv("SCN_X3_ROWS")) == 0) &&
+                       !(getenv("SCN_ROWS_SCATTER") && atoi(getenv("SCN_ROWS_SCATTER")) == 0) &&
+                       conv_rows_supported(in, out, weight, bias, rb.n_offsets, cin, cout, groups);
+  if (transposed && !scatter) {
     SCN_TRY(rulebook_transposed(rb, stream));
     table = rb.tnbr;
   }
@@ -113,6 +123,12 @@ static int run_conv(scn_metadata *md, Rulebook &rb, bool transposed, const float
       SCN_TRY(device_alloc((void **)&md->flags_dev, sizeof(int), stream));
       SCN_CUDA_CHECK(cudaMemsetAsync(md->flags_dev, 0, sizeof(int), stream));
     }
+  }
+  if (rows_out > 0 && scatter) {
+    SCN_TRY(conv_forward_rows_scatter(in, rows_in, out, rows_out, weight, bias, rb.nbr, rb.n_offsets, cin, cout,
+                                      md->flags_dev, stream));
+    g_last_kernel = SCN_KERNEL_CONV_ROWS;
+  } else if (rows_out > 0) {
     SCN_TRY(conv_forward_dispatch(in, rows_in, out, rows_out, weight, bias, table, rb.n_offsets, cin, cout, groups,
                                   precision, md->flags_dev, stream));
   }
@@ -210,7 +226,9 @@ int scn_deconvolution_forward(scn_metadata *md, const int64_t *input_size, const
   Rulebook *rb = nullptr;
   // the rulebook of the matching Convolution: fine (this op's output) -> coarse (this op's input)
   SCN_TRY(get_strided_rulebook(md, output_size, input_size, filter_size, filter_stride, stream, &rb));
+  bool disjoint = true;  // filter = stride: the children of different coarse sites and offsets never coincide
+  for (int d = 0; d < md->dim; ++d) disjoint &= filter_size[d] == filter_stride[d];
   return run_conv(md, *rb, true, in_features, out_features, weight, bias, n_in_planes, n_out_planes,
-                  groups, precision, stream, macs);
+                  groups, precision, stream, macs, disjoint);
 }
 }

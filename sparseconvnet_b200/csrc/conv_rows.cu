@@ -116,12 +116,22 @@ __global__ void k_rows_prepare(const float *__restrict__ w, uint4 *__restrict__ 
 // in the tf32 + bf16 form (5 % slower: registers); no shared memory at all, the A values read straight
 // from the feature matrix one half-step ahead (27 % slower: registers, and the loads' latency).
 template <int NT>
+__device__ __forceinline__ void rows_tile16v(float (&d)[NT][4], const float (&x)[8], const unsigned (&bh)[NT][4],
+                                             const unsigned (&bp)[NT][4]);
+
+template <int NT>
 __device__ __forceinline__ void rows_tile16(float (&d)[NT][4], const float *ap, const unsigned (&bh)[NT][4],
                                             const unsigned (&bp)[NT][4]) {
-  // planes P+t, P+t+4, P+8+t, P+12+t of rows g and g + 8
-  const float x00 = ap[0], x01 = ap[4], x02 = ap[8], x03 = ap[12];
-  const float x10 = ap[8 * kRAStride], x11 = ap[8 * kRAStride + 4], x12 = ap[8 * kRAStride + 8],
-              x13 = ap[8 * kRAStride + 12];
+  const float x[8] = {ap[0], ap[4], ap[8], ap[12],
+                      ap[8 * kRAStride], ap[8 * kRAStride + 4], ap[8 * kRAStride + 8], ap[8 * kRAStride + 12]};
+  rows_tile16v<NT>(d, x, bh, bp);
+}
+
+// x[0..3]: planes P+t, P+t+4, P+8+t, P+12+t of row g; x[4..7]: the same of row g + 8
+template <int NT>
+__device__ __forceinline__ void rows_tile16v(float (&d)[NT][4], const float (&x)[8], const unsigned (&bh)[NT][4],
+                                             const unsigned (&bp)[NT][4]) {
+  const float x00 = x[0], x01 = x[1], x02 = x[2], x03 = x[3], x10 = x[4], x11 = x[5], x12 = x[6], x13 = x[7];
   unsigned h0[4], h1[4], l[8];
   rows_split(x00, h0[0], l[0]);
   rows_split(x10, h0[1], l[1]);
@@ -453,6 +463,116 @@ int conv_forward_rows_thin(const float *in, long long n_in, float *out, long lon
     SCN_LAUNCH(k_conv_rows_thin<4>, grid, 128, 0, stream, in, n_in, out, n_out, img, bias, table, K, cin, flags);
   else
     SCN_LAUNCH(k_conv_rows_thin<8>, grid, 128, 0, stream, in, n_in, out, n_out, img, bias, table, K, cin, flags);
+  const cudaError_t e = cudaGetLastError();
+  const int rf = device_free(img, stream);
+  SCN_CUDA_CHECK(e);
+  return rf;
+}
+
+// ---- transposed rulebooks whose output rows have one rule each (Deconvolution with filter = stride) --------
+// Run from the output side, the children of a coarse site sit at different filter offsets, so a 16-row tile of
+// fine rows meets several offsets with a few rows each.  Run from the input side a warp takes 32 consecutive
+// COARSE rows (dense, no gather, no transposed table), multiplies them with W[k] for every offset k at which
+// any of them has a child, and stores each product row at the child's row: every fine row is written exactly
+// once (filter = stride makes the children of different sites and offsets disjoint and covers every fine
+// site), so nothing is accumulated in memory.  Measured 10 % faster than the gather form (64 -> 32 planes,
+// 1.59 M fine rows: 0.33 against 0.37 ms; rows sorted by coordinate keep the gather form's tiles to two offsets).
+template <int NT>
+__global__ void __launch_bounds__(32)
+k_conv_rows_scatter(const float *__restrict__ in, int ld_in, long long n_in, float *__restrict__ out, int ld_out,
+                    long long n_out, const uint4 *__restrict__ img, const float *__restrict__ bias,
+                    const int *__restrict__ child_of /* [K][n_in] -> output row */, int K, int nch, int *flags) {
+  constexpr unsigned kFull = 0xffffffffu;
+  constexpr int kSlab = 4 * NT * 32;
+  const int lane = threadIdx.x, g = lane >> 2, t = lane & 3;
+  const long long row0 = (long long)blockIdx.x * 32;
+  if (row0 >= n_in) return;
+  const long long my_row = row0 + lane;
+  const float *ap[2][2];  // rows g / g + 8 of the two tiles; rows past the end are read as zeros
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const long long r = row0 + mt * 16 + h * 8 + g;
+      ap[mt][h] = r < n_in ? in + r * ld_in + t : nullptr;
+    }
+  for (int k = 0; k < K; ++k) {
+    int child = my_row < n_in ? __ldg(child_of + (long long)k * n_in + my_row) : -1;
+    if (child >= n_out) {
+      atomicOr(flags, FLAG_BAD_ROW);
+      child = -1;
+    }
+    const unsigned mk = __ballot_sync(kFull, child >= 0);
+    if (mk == 0) continue;
+    float d[2][NT][4];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) d[mt][nt][0] = d[mt][nt][1] = d[mt][nt][2] = d[mt][nt][3] = 0.f;
+    for (int c = 0; c < nch; ++c) {
+      const uint4 *w_slab = img + ((long long)k * nch + c) * kSlab;
+#pragma unroll
+      for (int kp = 0; kp < 2; ++kp) {
+        unsigned bh[NT][4], bp[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const uint4 q0 = __ldg(w_slab + ((kp * NT + nt) * 32 + lane) * 2);
+          const uint4 q1 = __ldg(w_slab + ((kp * NT + nt) * 32 + lane) * 2 + 1);
+          bh[nt][0] = q0.x, bh[nt][1] = q0.y, bh[nt][2] = q0.z, bh[nt][3] = q0.w;
+          bp[nt][0] = q1.x, bp[nt][1] = q1.y, bp[nt][2] = q1.z, bp[nt][3] = q1.w;
+        }
+        const int off = c * kRChunk + kp * 16;
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+          if ((mt == 0 ? (mk & 0xFFFFu) : (mk >> 16)) == 0) continue;
+          float x[8];
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) x[h * 4 + e] = ap[mt][h] ? __ldg(ap[mt][h] + off + 4 * e) : 0.f;
+          rows_tile16v<NT>(d[mt], x, bh, bp);
+        }
+      }
+    }
+    // each product row to its child's row
+    const int t2 = t * 2;
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int dst_row = __shfl_sync(kFull, child, mt * 16 + h * 8 + g);
+        if (dst_row < 0) continue;
+        float *dst = out + (long long)dst_row * ld_out + t2;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          float2 v = make_float2(d[mt][nt][h * 2], d[mt][nt][h * 2 + 1]);
+          if (bias) {
+            const float2 bb = __ldg(reinterpret_cast<const float2 *>(bias + nt * 8 + t2));
+            v.x += bb.x;
+            v.y += bb.y;
+          }
+          __stcs(reinterpret_cast<float2 *>(dst + nt * 8), v);
+        }
+      }
+  }
+}
+
+// out [n_out, cout]: row child_of[k][i] = bias + in[i] @ W[k] for every rule; every output row must have exactly
+// one rule (the caller's promise).  Same shapes as conv_forward_rows.
+int conv_forward_rows_scatter(const float *in, long long n_in, float *out, long long n_out, const float *weight,
+                              const float *bias, const int *child_of, int K, int cin, int cout, int *flags,
+                              cudaStream_t stream) {
+  if (n_out == 0 || n_in == 0) return SCN_OK;
+  const int nch = cin / kRChunk;
+  uint4 *img = nullptr;
+  const long long total = (long long)K * nch * 2 * (cout / 8) * 32;
+  SCN_TRY(device_alloc((void **)&img, (size_t)total * 2 * sizeof(uint4), stream));
+  SCN_LAUNCH(k_rows_prepare, (unsigned)ceil_div(total, 256LL), 256, 0, stream, weight, img, K, cin, cout);
+  const unsigned grid = (unsigned)ceil_div(n_in, 32LL);
+  if (cout == 32)
+    SCN_LAUNCH(k_conv_rows_scatter<4>, grid, 32, 0, stream, in, cin, n_in, out, cout, n_out, img, bias, child_of, K, nch, flags);
+  else
+    SCN_LAUNCH(k_conv_rows_scatter<8>, grid, 32, 0, stream, in, cin, n_in, out, cout, n_out, img, bias, child_of, K, nch, flags);
   const cudaError_t e = cudaGetLastError();
   const int rf = device_free(img, stream);
   SCN_CUDA_CHECK(e);
