@@ -13,14 +13,17 @@
 //             coordinate, so the rules of an offset cluster (54 % of the (offset, 16-row tile) slots
 //             of an indoor scan hold a rule, at 62 % fill)
 //   weights   prepared once per call as the per-lane fragment image of (offset, 32-plane chunk)
-//             slabs, hi and lo parts already split (8 or 16 KB); every warp reads its B fragments
+//             slabs, tf32 and bf16 parts ready (8 or 16 KB); every warp reads its B fragments
 //             straight from that image with 128-bit loads; they come from L2 (the slabs of the 20
 //             warps of an SM do not fit L1 beside the shared memory, hit rate 9 %; an L1 prefetch a
 //             step ahead made it slower), and the other warps cover the latency
 //   nothing   is shared between warps: no barrier, no shared-memory accumulator, no pair lists.
-//             A CTA is one warp; 20 of them are resident per SM
-//   arithmetic x = hi + lo with hi = x truncated to tf32; D += A_lo B_hi + A_hi B_lo + A_hi B_hi
-//             in fp32 accumulators (1e-5 of max against fp32)
+//             A CTA is one warp; 12 to 21 of them are resident per SM
+//   arithmetic x = hi + lo with hi = x truncated to tf32; D += A_lo B + A B_lo + A_hi B_hi in fp32
+//             accumulators, the large term as tf32 m16n8k8, the two small ones as bf16 m16n8k16
+//             (see k_rows_prepare); 5e-6 of max against fp32
+//   also here k_conv_rows_thin (first layers, at most four input planes) and k_conv_rows_scatter
+//             (Deconvolution with filter = stride, run from its input side)
 //
 // Against the compacting kernel of conv_pipe.cu this issues 1.4 to 1.6 times the tensor
 // instructions (the zero rows inside a tile) but half the instructions around each of them.
