@@ -8,6 +8,8 @@
 //                                                  RectangularRegions.h:94-119)
 //   Metadata<D>::getSpatialLocations              (Metadata.cpp:149-170)
 // of the reference.  Only counts (active sites, rules per offset) ever travel to the host.
+#include <stdlib.h>
+
 #include <algorithm>
 #include <climits>
 
@@ -440,13 +442,17 @@ struct FilterDesc {
 __global__ void __launch_bounds__(256)
 k_submanifold_rules(KeyLayout L, HashTable T, const unsigned long long *__restrict__ row_keys,
                     long long n, int K, FilterDesc F, int k_chunk, int *__restrict__ nbr,
-                    unsigned long long *counts) {
+                    unsigned long long *counts, int mirrored) {
   extern __shared__ long long sh_raw[];
   long long *sh_keydelta = sh_raw;                         // [k_chunk]
   int *sh_count = (int *)(sh_keydelta + k_chunk);          // [k_chunk]
   signed char *sh_delta = (signed char *)(sh_count + k_chunk);  // [k_chunk][dim]
+  // mirrored (all filter sizes odd): offset K-1-k is offset k seen from the neighbour, so only the
+  // offsets up to the centre are looked up; a hit also fills the neighbour's entry at the mirrored
+  // offset (pre-set to -1 by the caller), and the centre is the site itself.
+  const int k_end = mirrored ? K / 2 + 1 : K;
   int k0 = blockIdx.y * k_chunk;
-  int k1 = min(K, k0 + k_chunk);
+  int k1 = min(k_end, k0 + k_chunk);
   for (int kk = k0 + threadIdx.x; kk < k1; kk += blockDim.x) {
     int rem = kk;
     long long kd = 0;
@@ -475,15 +481,22 @@ k_submanifold_rules(KeyLayout L, HashTable T, const unsigned long long *__restri
         int y = x[d] + dl[d];
         ok &= ((unsigned)y < (unsigned)L.size[d]);
       }
-      if (ok) row = hash_find_row(T, key + (unsigned long long)sh_keydelta[kk - k0]);
+      if (mirrored && kk == K / 2)
+        row = (int)site;
+      else if (ok)
+        row = hash_find_row(T, key + (unsigned long long)sh_keydelta[kk - k0]);
     }
     if (site < n) nbr[(long long)kk * n + site] = row;
+    if (mirrored && kk < K / 2 && row >= 0) nbr[(long long)(K - 1 - kk) * n + row] = (int)site;
     unsigned hits = __ballot_sync(0xffffffffu, row >= 0);
     if ((threadIdx.x & 31) == 0 && hits) atomicAdd(&sh_count[kk - k0], __popc(hits));
   }
   __syncthreads();
   for (int kk = k0 + threadIdx.x; kk < k1; kk += blockDim.x)
-    if (sh_count[kk - k0]) atomicAdd(&counts[kk], (unsigned long long)sh_count[kk - k0]);
+    if (sh_count[kk - k0]) {
+      atomicAdd(&counts[kk], (unsigned long long)sh_count[kk - k0]);
+      if (mirrored && kk < K / 2) atomicAdd(&counts[K - 1 - kk], (unsigned long long)sh_count[kk - k0]);
+    }
 }
 
 int get_submanifold_rulebook(scn_metadata *md, const int64_t *spatial_size,
@@ -517,12 +530,17 @@ int get_submanifold_rulebook(scn_metadata *md, const int64_t *spatial_size,
   if (n > 0) {
     const int threads = 256;
     long long bx = ceil_div(n, threads);
+    bool mirrored = K > 1 && !(getenv("SCN_RULES_MIRROR") && atoi(getenv("SCN_RULES_MIRROR")) == 0);
+    for (int d = 0; d < md->dim; ++d) mirrored &= (filter_size[d] % 2 == 1);
+    const long long k_end = mirrored ? K / 2 + 1 : K;  // offsets that are looked up
+    if (mirrored)  // the mirrored half starts out empty
+      SCN_CUDA_CHECK(cudaMemsetAsync(rb.nbr + k_end * n, 0xFF, sizeof(int) * (size_t)((K - k_end) * n), stream));
     // enough blocks to fill the machine even for few sites: split the offsets over grid.y
-    long long want_y = std::max<long long>(1, std::min<long long>(K, ceil_div(148 * 16, bx)));
-    int k_chunk = (int)ceil_div(K, want_y);
-    int gy = (int)ceil_div(K, k_chunk);
+    long long want_y = std::max<long long>(1, std::min<long long>(k_end, ceil_div(148 * 16, bx)));
+    int k_chunk = (int)ceil_div(k_end, want_y);
+    int gy = (int)ceil_div(k_end, k_chunk);
     size_t smem = (size_t)k_chunk * (sizeof(long long) + sizeof(int) + md->dim);
-    SCN_LAUNCH(k_submanifold_rules, dim3((unsigned)bx, (unsigned)gy), threads, smem, stream, g->layout, g->table, g->row_keys, n, (int)K, F, k_chunk, rb.nbr, rb.counts_dev);
+    SCN_LAUNCH(k_submanifold_rules, dim3((unsigned)bx, (unsigned)gy), threads, smem, stream, g->layout, g->table, g->row_keys, n, (int)K, F, k_chunk, rb.nbr, rb.counts_dev, mirrored ? 1 : 0);
     SCN_CUDA_CHECK(cudaGetLastError());
   }
   rb.built = true;
