@@ -27,7 +27,7 @@ int conv_forward_pipe(const float *in, long long n_in, float *out, long long n_o
 bool conv_rows_supported(const float *in, const float *out, const float *weight, const float *bias, int K, int cin,
                          int cout, int groups);
 int conv_forward_rows(const float *in, long long n_in, float *out, long long n_out, const float *weight,
-                      const float *bias, const int *table, int K, int cin, int cout, int *flags,
+                      const float *bias, const int *table, int K, int cin, int cout, int precision, int *flags,
                       cudaStream_t stream);
 
 bool conv_rows_thin_supported(const float *out, const float *bias, int cin, int cout, int groups);
@@ -62,7 +62,9 @@ int conv_forward_dispatch(const float *in, long long rows_in, float *out, long l
   const bool few_tiles = rows_out <= 148 * 256 && !force_persistent;
   const bool use_rows = !(getenv("SCN_X3_ROWS") && atoi(getenv("SCN_X3_ROWS")) == 0);
   const bool rows_thin = narrow_x3 && use_rows && conv_rows_thin_supported(out, bias, cin, cout, groups);
-  const bool rows = narrow_x3 && use_rows && conv_rows_supported(in, out, weight, bias, K, cin, cout, groups);
+  // the row-stationary kernel also has the single-pass modes (32 / 64 output planes)
+  const bool rows = (narrow_x3 || precision == SCN_PRECISION_TF32 || precision == SCN_PRECISION_BF16) && use_rows &&
+                    conv_rows_supported(in, out, weight, bias, K, cin, cout, groups);
   const bool pipe_mma = narrow_x3 && cin % 8 == 0 && conv_pipe_supported(in, out, weight, bias, K, cin, cout);
   // a narrow shape none of the three takes (more than 32 filter offsets, groups ...) goes on to tcgen05
   const bool tensor = precision != SCN_PRECISION_FP32 && !(rows_thin || rows || pipe_mma);
@@ -71,7 +73,7 @@ int conv_forward_dispatch(const float *in, long long rows_in, float *out, long l
                                    flags, stream));
     g_last_kernel = SCN_KERNEL_CONV_ROWS;
   } else if (rows) {
-    SCN_TRY(conv_forward_rows(in, rows_in, out, rows_out, weight, bias, table, K, cin, cout,
+    SCN_TRY(conv_forward_rows(in, rows_in, out, rows_out, weight, bias, table, K, cin, cout, precision,
                               flags, stream));
     g_last_kernel = SCN_KERNEL_CONV_ROWS;
   } else if (pipe_mma) {

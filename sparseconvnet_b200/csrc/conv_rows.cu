@@ -118,23 +118,54 @@ __global__ void k_rows_prepare(const float *__restrict__ w, uint4 *__restrict__ 
 // hi and lo made in registers (half the L2 traffic, 6 % slower); both tiles' instructions interleaved
 // in the tf32 + bf16 form (5 % slower: registers); no shared memory at all, the A values read straight
 // from the feature matrix one half-step ahead (27 % slower: registers, and the loads' latency).
-template <int NT>
+// MODE (a TcMode): TC_TF32X3 as described above; TC_TF32 only the two tf32 instructions, on the values as
+// they are (the tensor core drops the low mantissa bits); TC_BF16 only the bf16 instruction x x W.  The
+// single-pass modes read only their half of the weight image.
+template <int NT, int MODE = TC_TF32X3>
 __device__ __forceinline__ void rows_tile16v(float (&d)[NT][4], const float (&x)[8], const unsigned (&bh)[NT][4],
                                              const unsigned (&bp)[NT][4]);
 
-template <int NT>
+template <int NT, int MODE = TC_TF32X3>
 __device__ __forceinline__ void rows_tile16(float (&d)[NT][4], const float *ap, const unsigned (&bh)[NT][4],
                                             const unsigned (&bp)[NT][4]) {
   const float x[8] = {ap[0], ap[4], ap[8], ap[12],
                       ap[8 * kRAStride], ap[8 * kRAStride + 4], ap[8 * kRAStride + 8], ap[8 * kRAStride + 12]};
-  rows_tile16v<NT>(d, x, bh, bp);
+  rows_tile16v<NT, MODE>(d, x, bh, bp);
 }
 
 // x[0..3]: planes P+t, P+t+4, P+8+t, P+12+t of row g; x[4..7]: the same of row g + 8
-template <int NT>
+template <int NT, int MODE>
 __device__ __forceinline__ void rows_tile16v(float (&d)[NT][4], const float (&x)[8], const unsigned (&bh)[NT][4],
                                              const unsigned (&bp)[NT][4]) {
   const float x00 = x[0], x01 = x[1], x02 = x[2], x03 = x[3], x10 = x[4], x11 = x[5], x12 = x[6], x13 = x[7];
+  if (MODE == TC_BF16) {
+    unsigned ax[4];
+    ax[0] = rows_pack_bf16(x00, x01);
+    ax[1] = rows_pack_bf16(x10, x11);
+    ax[2] = rows_pack_bf16(x02, x03);
+    ax[3] = rows_pack_bf16(x12, x13);
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const unsigned b[2] = {bp[nt][0], bp[nt][1]};
+      rows_mma_bf16(d[nt], ax, b);
+    }
+    return;
+  }
+  if (MODE == TC_TF32) {
+    const unsigned h0[4] = {__float_as_uint(x00), __float_as_uint(x10), __float_as_uint(x01), __float_as_uint(x11)};
+    const unsigned h1[4] = {__float_as_uint(x02), __float_as_uint(x12), __float_as_uint(x03), __float_as_uint(x13)};
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const unsigned b[2] = {bh[nt][0], bh[nt][1]};
+      rows_mma(d[nt], h0, b);
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const unsigned b[2] = {bh[nt][2], bh[nt][3]};
+      rows_mma(d[nt], h1, b);
+    }
+    return;
+  }
   unsigned h0[4], h1[4], l[8];
   rows_split(x00, h0[0], l[0]);
   rows_split(x10, h0[1], l[1]);
@@ -176,7 +207,7 @@ __device__ __forceinline__ void rows_tile16v(float (&d)[NT][4], const float (&x)
   }
 }
 
-template <int NT>
+template <int NT, int MODE>
 __device__ __forceinline__ void rows_chunk(float (&d)[2][NT][4], const float *a_stage, const uint4 *w_slab,
                                            int lane, unsigned m0, unsigned m1) {
   const int g = lane >> 2, t = lane & 3;
@@ -186,17 +217,24 @@ __device__ __forceinline__ void rows_chunk(float (&d)[2][NT][4], const float *a_
     unsigned bh[NT][4], bp[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-      const uint4 q0 = __ldg(w_slab + ((kp * NT + nt) * 32 + lane) * 2);
-      const uint4 q1 = __ldg(w_slab + ((kp * NT + nt) * 32 + lane) * 2 + 1);
-      bh[nt][0] = q0.x, bh[nt][1] = q0.y, bh[nt][2] = q0.z, bh[nt][3] = q0.w;
-      bp[nt][0] = q1.x, bp[nt][1] = q1.y, bp[nt][2] = q1.z, bp[nt][3] = q1.w;
+      if (MODE != TC_BF16) {
+        const uint4 q0 = __ldg(w_slab + ((kp * NT + nt) * 32 + lane) * 2);
+        bh[nt][0] = q0.x, bh[nt][1] = q0.y, bh[nt][2] = q0.z, bh[nt][3] = q0.w;
+      }
+      if (MODE == TC_BF16) {  // only the pair of bf16 W
+        const uint2 q1 = __ldg(reinterpret_cast<const uint2 *>(w_slab + ((kp * NT + nt) * 32 + lane) * 2 + 1));
+        bp[nt][0] = q1.x, bp[nt][1] = q1.y;
+      } else if (MODE == TC_TF32X3) {
+        const uint4 q1 = __ldg(w_slab + ((kp * NT + nt) * 32 + lane) * 2 + 1);
+        bp[nt][0] = q1.x, bp[nt][1] = q1.y, bp[nt][2] = q1.z, bp[nt][3] = q1.w;
+      }
     }
-    if (m0 != 0) rows_tile16<NT>(d[0], a_lane + kp * 16, bh, bp);
-    if (m1 != 0) rows_tile16<NT>(d[1], a_lane + 16 * kRAStride + kp * 16, bh, bp);
+    if (m0 != 0) rows_tile16<NT, MODE>(d[0], a_lane + kp * 16, bh, bp);
+    if (m1 != 0) rows_tile16<NT, MODE>(d[1], a_lane + 16 * kRAStride + kp * 16, bh, bp);
   }
 }
 
-template <int NT>
+template <int NT, int MODE>
 __global__ void __launch_bounds__(32)
 k_conv_rows(const float *__restrict__ in, int ld_in, long long n_in, float *__restrict__ out, int ld_out,
             long long n_out, const uint4 *__restrict__ img, const float *__restrict__ bias,
@@ -283,7 +321,7 @@ k_conv_rows(const float *__restrict__ in, int ld_in, long long n_in, float *__re
       cp_async_wait<kRAStages - 2>();  // the rows of this step have landed (this lane's copies)
       __syncwarp();                    // ... every lane's; and the previous step's reads are done
       issue();
-      rows_chunk<NT>(d, a_ring + cstage * kRStageFloats, img + ((long long)k * nch + c) * kSlab, lane,
+      rows_chunk<NT, MODE>(d, a_ring + cstage * kRStageFloats, img + ((long long)k * nch + c) * kSlab, lane,
                            mk_q[0] & 0xFFFFu, mk_q[0] >> 16);
       cstage = cstage + 1 == kRAStages ? 0 : cstage + 1;
     }
@@ -312,7 +350,7 @@ k_conv_rows(const float *__restrict__ in, int ld_in, long long n_in, float *__re
     }
 }
 
-template <int NT>
+template <int NT, int MODE>
 static int launch_rows(const float *in, int ld_in, long long n_in, float *out, int ld_out, long long n_out,
                        const uint4 *img, const float *bias, const int *table, int K, int nch, int *flags,
                        cudaStream_t stream) {
@@ -320,7 +358,7 @@ static int launch_rows(const float *in, int ld_in, long long n_in, float *out, i
   int dev = 0;
   SCN_CUDA_CHECK(cudaGetDevice(&dev));
   const size_t smem = (size_t)kRAStages * kRStageFloats * sizeof(float);
-  auto kernel = k_conv_rows<NT>;
+  auto kernel = k_conv_rows<NT, MODE>;
   if (dev >= 64 || !configured[dev]) {
     SCN_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     // 9 KB of shared memory per warp: a carve-out of 80 % holds 20 warps per SM (the registers allow
@@ -588,9 +626,10 @@ bool conv_rows_supported(const float *in, const float *out, const float *weight,
          (uintptr_t)in % 16 == 0 && (uintptr_t)out % 8 == 0 && (uintptr_t)bias % 8 == 0 && (uintptr_t)weight % 4 == 0;
 }
 
-// out [n_out, cout] = bias + sum_k in[table[k][.]] @ W[k], three tf32 passes (fp32-class accuracy)
+// out [n_out, cout] = bias + sum_k in[table[k][.]] @ W[k]; precision: SCN_PRECISION_TF32X3 (fp32-class accuracy),
+// SCN_PRECISION_TF32 or SCN_PRECISION_BF16 (single pass)
 int conv_forward_rows(const float *in, long long n_in, float *out, long long n_out, const float *weight,
-                      const float *bias, const int *table, int K, int cin, int cout, int *flags,
+                      const float *bias, const int *table, int K, int cin, int cout, int precision, int *flags,
                       cudaStream_t stream) {
   if (n_out == 0) return SCN_OK;
   const int nch = cin / kRChunk;
@@ -598,9 +637,15 @@ int conv_forward_rows(const float *in, long long n_in, float *out, long long n_o
   const long long total = (long long)K * nch * 4 * (cout / 8) * 32;
   SCN_TRY(device_alloc((void **)&img, (size_t)total * sizeof(uint4), stream));
   SCN_LAUNCH(k_rows_prepare, (unsigned)ceil_div(total, 256LL), 256, 0, stream, weight, img, K, cin, cout);
-  const int rc = cout == 32
-                     ? launch_rows<4>(in, cin, n_in, out, cout, n_out, img, bias, table, K, nch, flags, stream)
-                     : launch_rows<8>(in, cin, n_in, out, cout, n_out, img, bias, table, K, nch, flags, stream);
+  int rc;
+#define SCN_ROWS_CALL(NT, MODE) launch_rows<NT, MODE>(in, cin, n_in, out, cout, n_out, img, bias, table, K, nch, flags, stream)
+  if (precision == SCN_PRECISION_BF16)
+    rc = cout == 32 ? SCN_ROWS_CALL(4, TC_BF16) : SCN_ROWS_CALL(8, TC_BF16);
+  else if (precision == SCN_PRECISION_TF32)
+    rc = cout == 32 ? SCN_ROWS_CALL(4, TC_TF32) : SCN_ROWS_CALL(8, TC_TF32);
+  else
+    rc = cout == 32 ? SCN_ROWS_CALL(4, TC_TF32X3) : SCN_ROWS_CALL(8, TC_TF32X3);
+#undef SCN_ROWS_CALL
   const int rf = device_free(img, stream);
   return rc != SCN_OK ? rc : rf;
 }
