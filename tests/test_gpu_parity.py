@@ -248,3 +248,26 @@ def test_deferred_multiply_add_count(cuda):
     finally:
         lib.scn_set_deferred_counts(1)
     assert counts[0] == counts[1] and counts[0] % (8 * 16) == 0
+
+
+def test_mirrored_rulebook_build_equals_full_lookup(cuda, monkeypatch):
+    """Odd filter sizes: the rulebook built from half the lookups (each hit also fills the neighbour's
+    mirrored entry) is the rulebook built from all of them, rule for rule; a 3 x 5 filter and blanked
+    duplicate rows (input mode 0) included."""
+    import sparseconvnet_b200 as scn
+    rng = np.random.default_rng(11)
+    coords = np.concatenate([rng.integers(0, 20, (4000, 3)), rng.integers(0, 3, (4000, 1))], axis=1)
+    feats = torch.from_numpy(rng.standard_normal((4000, 4)).astype(np.float32)).to(cuda)
+    for mode in (0, 3):
+        for filt in ([3, 3, 3], [3, 5, 1]):
+            books = []
+            for mirror in ("1", "0"):
+                monkeypatch.setenv("SCN_RULES_MIRROR", mirror)
+                x = scn.InputLayer(3, 20, mode=mode)([torch.from_numpy(coords), feats])
+                conv = scn.SubmanifoldConvolution(3, 4, 4, filt, False).to(cuda)
+                with torch.no_grad():
+                    conv(x)
+                books.append(x.metadata.rulebook(0, x.spatial_size, conv.filter_size))
+            assert len(books[0]) == len(books[1]) == int(np.prod(filt))
+            for k, (a, b) in enumerate(zip(*books)):
+                assert torch.equal(a, b), "filter %s mode %d offset %d" % (filt, mode, k)
