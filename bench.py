@@ -248,7 +248,13 @@ def main():
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
-    count_group = shard.host_group() if world > 1 else None  # row counts travel on the host, not through the stream
+    count_group = None
+    if world > 1:  # row counts travel on the host, not through the stream
+        os.environ.setdefault("GLOO_SOCKET_IFNAME", "lo")  # one node: the loopback interface always resolves
+        try:
+            count_group = shard.host_group()
+        except Exception as e:  # no host group: the counts go through NCCL and are read back from the device
+            sys.stderr.write("host group for the row counts unavailable (%s); using the device path\n" % e)
 
     inp, net, head = workloads.build_config(CONFIG)
     net.to(dev)
