@@ -830,8 +830,22 @@ static void counts_from_ticket(Rulebook &rb) {
   rb.total_rules = t;
 }
 
+// filter volumes beyond a ticket's chunk: plain copy and wait
+static int rulebook_counts_blocking(Rulebook &rb, cudaStream_t stream) {
+  std::vector<unsigned long long> h(rb.n_offsets);
+  SCN_CUDA_CHECK(cudaMemcpyAsync(h.data(), rb.counts_dev, sizeof(unsigned long long) * rb.n_offsets,
+                                 cudaMemcpyDeviceToHost, stream));
+  SCN_CUDA_CHECK(cudaStreamSynchronize(stream));
+  rb.counts_host.assign(h.begin(), h.end());
+  long long t = 0;
+  for (auto c : rb.counts_host) t += c;
+  rb.total_rules = t;
+  return SCN_OK;
+}
+
 int rulebook_counts_async(Rulebook &rb, cudaStream_t stream) {
   if (rb.total_rules >= 0) return SCN_OK;
+  if (rb.n_offsets > kTicketValues) return rulebook_counts_blocking(rb, stream);
   SCN_TRY(count_ticket_start(rb, stream));
   cudaError_t q = cudaEventQuery(rb.ticket->event);
   if (q == cudaSuccess) {
@@ -844,6 +858,7 @@ int rulebook_counts_async(Rulebook &rb, cudaStream_t stream) {
 
 int rulebook_counts(Rulebook &rb, cudaStream_t stream) {
   if (rb.total_rules >= 0) return SCN_OK;
+  if (rb.n_offsets > kTicketValues) return rulebook_counts_blocking(rb, stream);
   SCN_TRY(count_ticket_start(rb, stream));
   SCN_CUDA_CHECK(cudaEventSynchronize(rb.ticket->event));
   counts_from_ticket(rb);

@@ -271,3 +271,23 @@ def test_mirrored_rulebook_build_equals_full_lookup(cuda, monkeypatch):
             assert len(books[0]) == len(books[1]) == int(np.prod(filt))
             for k, (a, b) in enumerate(zip(*books)):
                 assert torch.equal(a, b), "filter %s mode %d offset %d" % (filt, mode, k)
+
+
+def test_large_filter_volume_counts(cuda):
+    """A 4-D filter of size 5 has 625 offsets, more than a count ticket holds: the multiply-add count then comes
+    back as a plain number, and equals rules x planes."""
+    import sparseconvnet_b200 as scn
+    from sparseconvnet_b200 import SCN
+    rng = np.random.default_rng(13)
+    coords = np.concatenate([rng.integers(0, 9, (600, 4)), np.zeros((600, 1), np.int64)], axis=1)
+    feats = torch.from_numpy(rng.standard_normal((600, 2)).astype(np.float32)).to(cuda)
+    x = scn.InputLayer(4, 9, mode=3)([torch.from_numpy(coords), feats])
+    conv = scn.SubmanifoldConvolution(4, 2, 3, 5, False).to(cuda)
+    out = torch.empty(0, device=cuda)
+    with torch.no_grad():
+        macs = SCN.SubmanifoldConvolution_updateOutput(x.spatial_size, conv.filter_size, x.metadata, x.features, out,
+                                                       conv.weight, torch.empty(0))
+    book = x.metadata.rulebook(0, x.spatial_size, conv.filter_size)
+    assert len(book) == 625
+    assert float(macs) == float(sum(b.shape[0] for b in book)) * 2 * 3
+    x.metadata.poll_errors()
