@@ -363,9 +363,10 @@ static int launch_rows(const float *in, int ld_in, long long n_in, float *out, i
     SCN_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     // 9 KB of shared memory per warp: a carve-out of 80 % holds 20 warps per SM (the registers allow
     // more with 32 output planes), the rest of the 256 KB stays L1 for the weight image
-    // with 64 output planes the registers hold the SM to 12 warps (110 KB of rings): half the SM's memory is
-    // enough and the other half serves the weight fragments as L1 (3 % faster)
-    SCN_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, NT > 4 ? 50 : 80));
+    // with 64 output planes the registers of the three-term mode hold the SM to 12 warps (110 KB of rings): half
+    // the SM's memory is enough and the other half serves the weight fragments as L1 (3 % faster)
+    SCN_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                        NT > 4 && MODE == TC_TF32X3 ? 50 : 80));
     if (dev < 64) configured[dev] = true;
   }
   SCN_LAUNCH(kernel, (unsigned)ceil_div(n_out, 32LL), 32, smem, stream, in, ld_in, n_in, out, ld_out, n_out, img, bias,
