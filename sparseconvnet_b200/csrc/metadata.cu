@@ -86,14 +86,60 @@ static int ensure_scratch(scn_metadata *md, cudaStream_t stream) {
   return SCN_OK;
 }
 
+// ---- host mailboxes -------------------------------------------------------------------------------
+// The few integers the host has to wait for (flag word, site counts) are written by a one-thread
+// kernel into pinned host memory that is mapped into the device's address space, not copied by
+// cudaMemcpy: a device-to-host copy queues on the copy engine behind whatever the application is
+// copying at the time (a previous batch's 127 MB of results held every such read-back up for 2 ms,
+// seven times per U-Net forward).  Slots of 32 bytes from slabs that are never given back.
+namespace {
+struct MailboxPool {
+  std::mutex mu;
+  std::vector<int *> free_slots;
+};
+MailboxPool &mailbox_pool() {
+  static MailboxPool *p = new MailboxPool();
+  return *p;
+}
+}  // namespace
+
+static int mailbox_acquire(int **slot) {
+  MailboxPool &P = mailbox_pool();
+  std::lock_guard<std::mutex> lock(P.mu);
+  if (P.free_slots.empty()) {
+    int *slab = nullptr;
+    SCN_CUDA_CHECK(cudaHostAlloc((void **)&slab, 4096, cudaHostAllocMapped | cudaHostAllocPortable));
+    for (int i = 0; i < 4096 / 32; ++i) P.free_slots.push_back(slab + i * 8);
+  }
+  *slot = P.free_slots.back();
+  P.free_slots.pop_back();
+  return SCN_OK;
+}
+
+static void mailbox_release(int *slot) {
+  if (!slot) return;
+  MailboxPool &P = mailbox_pool();
+  std::lock_guard<std::mutex> lock(P.mu);
+  P.free_slots.push_back(slot);
+}
+
+__global__ void k_post_scalars(int *flags_dev, const int *scalars_dev, volatile int *mailbox) {
+  mailbox[0] = *flags_dev;
+  *flags_dev = 0;
+  if (scalars_dev)
+    for (int i = 0; i < 4; ++i) mailbox[1 + i] = scalars_dev[i];
+  __threadfence_system();
+}
+
 // Reads (and clears) the device flag word; waits for the stream.
 static int fetch_flags(scn_metadata *md, cudaStream_t stream, int *flags, int *scalars4) {
-  int host[5] = {0, 0, 0, 0, 0};
-  SCN_CUDA_CHECK(cudaMemcpyAsync(&host[0], md->flags_dev, sizeof(int), cudaMemcpyDeviceToHost, stream));
-  if (scalars4)
-    SCN_CUDA_CHECK(cudaMemcpyAsync(&host[1], md->scalars_dev, 4 * sizeof(int), cudaMemcpyDeviceToHost, stream));
-  SCN_CUDA_CHECK(cudaMemsetAsync(md->flags_dev, 0, sizeof(int), stream));
+  if (!md->mailbox) SCN_TRY(mailbox_acquire(&md->mailbox));
+  int *mailbox_dev = nullptr;
+  SCN_CUDA_CHECK(cudaHostGetDevicePointer((void **)&mailbox_dev, md->mailbox, 0));
+  SCN_LAUNCH(k_post_scalars, 1, 1, 0, stream, md->flags_dev, scalars4 ? md->scalars_dev : nullptr, mailbox_dev);
+  SCN_CUDA_CHECK(cudaGetLastError());
   SCN_CUDA_CHECK(cudaStreamSynchronize(stream));
+  const volatile int *host = md->mailbox;
   *flags = host[0];
   if (scalars4)
     for (int i = 0; i < 4; ++i) scalars4[i] = host[1 + i];
@@ -757,6 +803,11 @@ TicketPool &ticket_pool() {
 }
 }  // namespace
 
+__global__ void k_post_counts(const unsigned long long *__restrict__ counts, volatile unsigned long long *host, int n) {
+  for (int i = threadIdx.x; i < n; i += blockDim.x) host[i] = counts[i];
+  __threadfence_system();
+}
+
 static int count_ticket_start(Rulebook &rb, cudaStream_t stream) {
   if (rb.ticket) return SCN_OK;
   SCN_REQUIRE(rb.n_offsets <= kTicketValues, SCN_ERR_UNSUPPORTED, "%d filter offsets", rb.n_offsets);
@@ -780,7 +831,8 @@ static int count_ticket_start(Rulebook &rb, cudaStream_t stream) {
   }
   if (!t->host) {  // a slab of 64 chunks at a time
     unsigned long long *slab = nullptr;
-    if (cudaHostAlloc((void **)&slab, sizeof(unsigned long long) * kTicketValues * 64, cudaHostAllocDefault) != cudaSuccess) {
+    if (cudaHostAlloc((void **)&slab, sizeof(unsigned long long) * kTicketValues * 64,
+                      cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) {
       cudaGetLastError();
       delete t;
       SCN_REQUIRE(false, SCN_ERR_CUDA, "pinned allocation failed");
@@ -797,8 +849,12 @@ static int count_ticket_start(Rulebook &rb, cudaStream_t stream) {
     SCN_REQUIRE(false, SCN_ERR_CUDA, "event creation failed");
   }
   rb.ticket = t;
-  SCN_CUDA_CHECK(cudaMemcpyAsync(t->host, rb.counts_dev, sizeof(unsigned long long) * rb.n_offsets,
-                                 cudaMemcpyDeviceToHost, stream));
+  // posted by a kernel into mapped host memory, not copied: a copy on this stream would hold the stream's next
+  // kernels until the copy engine has finished whatever the application is copying (see the mailboxes above)
+  unsigned long long *host_dev = nullptr;
+  SCN_CUDA_CHECK(cudaHostGetDevicePointer((void **)&host_dev, t->host, 0));
+  SCN_LAUNCH(k_post_counts, 1, 256, 0, stream, rb.counts_dev, host_dev, rb.n_offsets);
+  SCN_CUDA_CHECK(cudaGetLastError());
   SCN_CUDA_CHECK(cudaEventRecord(t->event, stream));
   return SCN_OK;
 }
@@ -950,6 +1006,8 @@ int scn_md_clear(scn_metadata *md, void *stream) {
 
 int scn_md_destroy(scn_metadata *md) {
   if (!md) return SCN_OK;
+  mailbox_release(md->mailbox);
+  md->mailbox = nullptr;
   count_ticket_release(md->last_ticket);
   md->last_ticket = nullptr;
   md_clear(md, 0);

@@ -78,6 +78,7 @@ struct scn_metadata {
   scn::CountTicket *last_ticket = nullptr;  // of the last operator that answered "count pending"
 
   int *flags_dev = nullptr;   // device word the kernels OR DeviceFlag bits into
+  int *mailbox = nullptr;     // pinned, device-mapped host slot (8 ints) the waited-for integers are posted to
   int *scalars_dev = nullptr; // small device scratch: [0] count, [1] max batch index
 };
 
