@@ -250,7 +250,6 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     count_group = None
     if world > 1:  # row counts travel on the host, not through the stream
-        os.environ.setdefault("GLOO_SOCKET_IFNAME", "lo")  # one node: the loopback interface always resolves
         try:
             count_group = shard.host_group()
         except Exception as e:  # no host group: the counts go through NCCL and are read back from the device

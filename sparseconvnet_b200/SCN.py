@@ -85,7 +85,7 @@ class DeferredCount(object):
 
 class _FlopCounter(object):
     """``forward_pass_multiplyAdd_count`` of the package: counts still in flight are kept aside
-    and folded in when the number is read (or when many have piled up, long after they landed)."""
+    and folded in when the number is read (or when about two forward passes' worth have piled up)."""
 
     def __init__(self):
         self.base, self.pending = 0, []
@@ -93,8 +93,12 @@ class _FlopCounter(object):
     def add(self, macs):
         if isinstance(macs, DeferredCount):
             self.pending.append(macs)
-            if len(self.pending) > 512:
-                self.fold()
+            if len(self.pending) > 96:
+                # the oldest ones landed a forward pass ago: folding them waits for nothing and gives
+                # their tickets (pinned memory, an event) back to the library's pool
+                old, self.pending = self.pending[:48], self.pending[48:]
+                for p in old:
+                    self.base += p.resolve()
         else:
             self.base += macs
 
