@@ -2,21 +2,25 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Headline workload (BASELINE configuration 3): 3-D submanifold U-Net inference, m=32, reps=2,
-planes 32..224, 4096^3 field, batch of 8 synthetic rooms of ~200 k voxels each per GPU, fp32.
+Headline workload (benchmark configuration 3): 3-D submanifold U-Net inference, m=32, reps=2,
+planes 32..224, 4096^3 field, batch of 8 synthetic rooms of ~200 k voxels each per GPU.
 One step = one forward over the batch with a FRESH Metadata: input-layer hash build, every
 rulebook, every layer, the 20-class linear head and (N > 1) the NCCL gather of the per-voxel
-outputs.  `value` = voxels/s with inputs resident in HBM; `e2e` = the same through the public
-API from pinned host buffers (host->device copy of coordinates and features, device->host
-copy of the scores inside the timed region).  Weak scaling: every rank runs its own 8 rooms.
+scores to rank 0.  `value` = voxels/s with inputs resident in HBM; `e2e` = the same through the
+public API from pinned host buffers (host->device copy of coordinates and features,
+device->host copy of the scores inside the timed region).  `scaling` "weak": every rank runs its
+own 8 rooms; with N > 1 the line also carries `strong_scaling` (the same 8 rooms split over the
+ranks by batch index) and `gather_check` (what the gather delivered, checked untimed).
 
-Also reported on the same line: `submanifold_conv` (BASELINE configuration 1: one 32->32
-3-D submanifold convolution, active sites/s cold / warm / rulebook only), `roofline` of the
-dominant kernel from CUDA-event timing of every operator call, `cpu_baseline` (the reference's
-CPU implementation timed on this box's host cores on a bounded sample) and `clocks`.
+Also on the line: `roofline` of the convolution kernel with the largest share of the step and
+`breakdown_ms_per_step` (CUDA events around every operator call), `configs` (voxels/s of
+configurations 1, 2, 4 and 5 with the reference's CPU figure beside each), `submanifold_conv`
+(configuration 1 cold / warm / rulebook only), `variants_voxels_per_sec`, `training_step`,
+`cpu_baseline` (the reference's own Python package and CPU extension on this box's host cores, the
+same batch) and `clocks`.
 
-`--impl reference` times the reference's own CPU implementation (oracle/_ref, compiled from
-the reference sources; the numpy restatement if that is absent) on one room per step.
+`--impl reference` times that reference CPU path on the same 8-room batch per step; it imports
+neither this package nor its library.  `--probe-mma` prints the measured cost of tcgen05.mma.
 """
 import argparse
 import json
@@ -32,12 +36,33 @@ CONFIG = 3
 ROOMS_PER_GPU = 8
 METRIC = "unet3d_voxels_per_sec"
 UNIT = "voxels/s"
-# DRAM bytes per launch of the dominant kernel as a multiple of the algorithmic bytes of that
-# launch, from the committed ncu captures (profiles/): k_conv_tma 75 MB against 343 MB per launch
-# (4-room case, 18 launches); k_conv_pipe 553 MB against 2.18 GB (32->32) and 768 MB against
-# 4.03 GB (64->32) at 8 rooms; k_conv_rows 263 MB against 1.08 GB (32->32, 4 rooms).  The traffic
-# grows with the rows, like the algorithmic bytes.
+# DRAM bytes per launch of a convolution kernel as a multiple of the algorithmic bytes of that
+# launch, from ncu captures of a 4-room case (dram__bytes_read + dram__bytes_write of consecutive
+# launches against their algorithmic bytes).  The traffic grows with the rows, like the
+# algorithmic bytes: DRAM sees input, rulebook and output about once, the gather's re-reads
+# (which the algorithmic figure counts per rule) hit L2.
 TRAFFIC_RATIO = {"k_conv_tma": 0.22, "k_conv_pipe_mma": 0.22, "k_conv_rows": 0.24, "k_conv_simt": 0.25}
+# (bound reported for the kernel, what the ncu captures show as its limiter)
+LIMITS = {
+    "k_conv_tma": ("hbm", "shared-memory data pipe 77 % busy, tensor pipe 40-46 % (ncu, 4-room case)"),
+    "k_conv_pipe_mma": ("hbm", "instruction issue and the shared-memory data pipe of small (offset, 128-row) steps"),
+    "k_conv_rows": ("hbm", "LSU data pipe 75 % busy (fragment loads, weight fragments from L2), warp-level tensor "
+                           "pipe 43-50 %; DRAM sees 0.24 of the algorithmic bytes, the gather's re-reads hit L2"),
+}
+# what `dtype` says for each arithmetic mode: the type the path computes in, kernel by kernel
+DTYPE_LABEL = {
+    "fp32": "f32 (fp32 FMA in every convolution)",
+    "tf32x3": "f32-class split arithmetic, fp32 accumulate: warp-level mma.sync (tf32 hi x hi + two bf16 cross "
+              "terms) for 32/64 output planes, tcgen05 three-term tf32 split in TMEM for wider layers",
+    "tf32": "tf32 (single pass, fp32 accumulate)",
+    "bf16": "bf16 (single pass, fp32 accumulate)",
+}
+CONFIG_NAMES = {
+    1: "config1: SubmanifoldConvolution 3D f3 32->32, 256^3 shells and planes, batch 1, fresh Metadata per step",
+    2: "config2: 2D stroke classifier (VGG stack -> SparseToDense 10x10x32), batch 100, field 87x87",
+    4: "config4: 3D SparseResNet on 127^3, batch 16 superquadric surfaces, 50-class head",
+    5: "config5: 4D stack 4 x (SubmanifoldConvolution 64->64 f3 = 81 offsets + BatchNormReLU), 4 sequences x 8 frames",
+}
 
 
 def workload_name(rooms=ROOMS_PER_GPU):
@@ -139,11 +164,18 @@ def op_bytes(r):
 
 def summarize_profile(rows):
     """Per kernel class: time, calls, algorithmic bytes and FLOPs of one step.  Convolution calls
-    are split by the kernel that ran them."""
+    are split by the kernel that ran them.  A rulebook lookup that was served from the Metadata's
+    cache is counted as a call but gets no bytes: only the call that built the rulebook moved them."""
     agg = {}
     for r in rows:
         name = r.get("kernel", r["kind"]) if r["kind"] == "conv" else r["kind"]
         a = agg.setdefault(name, {"ms": 0.0, "calls": 0, "bytes": 0.0, "flops": 0.0})
+        if r["kind"].startswith("rules_"):
+            a["built"] = a.get("built", 0) + (1 if r.get("built", True) else 0)
+            if not r.get("built", True):
+                a["calls"] += 1
+                a["cached_ms"] = a.get("cached_ms", 0.0) + r["ms"]
+                continue
         a["ms"] += r["ms"]
         a["calls"] += 1
         a["bytes"] += op_bytes(r)
@@ -152,71 +184,136 @@ def summarize_profile(rows):
     return agg
 
 
+def load_workloads():
+    """The workload generators, loaded by path: importing the package would load the CUDA library,
+    which the reference arm must not do."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("scn_workloads", os.path.join(ROOT, "sparseconvnet_b200", "workloads.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+class ReferenceCpu(object):
+    """The reference's own stock path on the host cores: its unmodified Python package
+    (scn.InputLayer, scn.UNet, scn.SparseResNet ... from sparseconvnet/*.py) on its own CPU
+    extension, both staged under oracle/_ref by oracle/build_ref.py.  Falls back to the numpy
+    restatement only where that build is absent (kind "port")."""
+
+    def __init__(self, workloads):
+        import torch
+        from oracle import refpkg
+        self.workloads, self.torch = workloads, torch
+        self.cores = os.cpu_count() or 1
+        torch.set_num_threads(self.cores)
+        self.kind = "reference" if refpkg.available("cpu") else "port"
+        self.scn = refpkg.load("cpu") if self.kind == "reference" else None
+
+    def prepare(self, config, samples):
+        """Returns (step function, voxels per step); one step = one forward over the whole batch with a
+        fresh Metadata, as in the GPU arm."""
+        torch, wl = self.torch, self.workloads
+        coords, feats = wl.make_batch(config, samples)
+        if self.kind == "reference":
+            inp, net, head = wl.build_config(config, scn=self.scn)
+            c, f = torch.from_numpy(coords), torch.from_numpy(feats)
+
+            def step():
+                with torch.no_grad():
+                    y = net(inp([c, f]))
+                    return head(y.features) if head is not None else y
+        else:
+            from oracle import runner
+            inp, net, head = wl.build_config(config)
+            be = runner.PortBackend()
+
+            def step():
+                y = runner.run_module(net, runner.run_module(inp, [coords, feats], be), be)
+                return runner.run_module(head, y, be) if head is not None else y
+        return step, coords.shape[0]
+
+    def time(self, config, samples, warmup, steps):
+        step, n = self.prepare(config, samples)
+        for _ in range(warmup):
+            step()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            step()
+        dt = time.perf_counter() - t0
+        return n * steps / dt, dt / steps, n
+
+
 def run_reference(args, rank):
-    """The reference's CPU implementation on the host cores: K steps of one room each."""
+    """The reference's CPU implementation on the host cores, on the same batch as rank 0 of the GPU
+    arm: K steps of all 8 rooms each."""
     if rank != 0:
         return
-    import numpy as np
-    import torch
-    from oracle import runner
-    from sparseconvnet_b200 import workloads
-    cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
-    be, kind = (runner.RefBackend(), "reference") if runner.reference_available() else (runner.PortBackend(), "port")
-    inp, net, head = workloads.build_config(CONFIG)
-    rooms = [workloads.batch_config3([s]) for s in range(max(1, min(args.steps + args.warmup, 4)))]
-
-    def step(i):
-        c, f = rooms[i % len(rooms)]
-        y = runner.run_module(net, runner.run_module(inp, [c, f], be), be)
-        runner.run_module(head, y, be)
-        return c.shape[0]
-
-    for i in range(args.warmup):
-        step(i)
-    t0 = time.perf_counter()
-    vox = 0
-    for i in range(args.steps):
-        vox += step(args.warmup + i)
-    dt = time.perf_counter() - t0
-    v = vox / dt
+    cpu = ReferenceCpu(load_workloads())
+    samples = list(range(args.rooms)) if cpu.kind == "reference" else [0]
+    v, sec, n = cpu.time(CONFIG, samples, args.warmup, args.steps)
+    sample = "the whole batch of rank 0 (%d rooms, %d voxels) per step, %d steps" % (len(samples), n, args.steps)
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sec,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload_name(), "sample": "one room (~200k voxels) per step"},
-        "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": kind,
-                         "sample": "one room (~200k voxels) per step, %d steps" % args.steps},
+        "config": {"workload": workload_name(len(samples)), "voxels_per_step": n, "sample": sample,
+                   "path": "the reference's own Python package and CPU extension" if cpu.kind == "reference"
+                   else "numpy restatement (the compiled reference is absent)"},
+        "cpu_baseline": {"value": v, "unit": UNIT, "cores": cpu.cores, "kind": cpu.kind, "sample": sample},
         "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }))
 
 
-def cpu_baseline_sample():
-    """Bounded CPU sample for the default run: the reference CPU build on one room, 1 warm-up +
-    3 timed forwards (about 10 s of CPU work)."""
+def cpu_baseline_sample(workloads, rooms):
+    """Bounded CPU sample for the default run: the reference on the same batch as the GPU arm,
+    1 warm-up + 2 timed forwards."""
+    cpu = ReferenceCpu(workloads)
+    samples = list(range(rooms)) if cpu.kind == "reference" else [0]
+    v, sec, n = cpu.time(CONFIG, samples, 1, 2)
+    return cpu, {"value": v, "unit": UNIT, "cores": cpu.cores, "kind": cpu.kind, "ms_per_step": 1e3 * sec,
+                 "sample": "%d rooms, %d voxels per forward, mean of 2 forwards after 1 warm-up" % (len(samples), n)}
+
+
+def run_probe_mma(args):
+    """Cycles per tcgen05.mma for every legal (M, N, kind) the kernels could issue, measured by the
+    library's own probe entry point: one CTA (clock64 figures) and one CTA per SM (CUDA-event
+    figure), 2048 instructions each."""
+    import ctypes as C
     import torch
-    from oracle import runner
-    from sparseconvnet_b200 import workloads
-    cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
-    ref = runner.reference_available()
-    be, kind = (runner.RefBackend(), "reference") if ref else (runner.PortBackend(), "port")
-    inp, net, head = workloads.build_config(CONFIG)
-    c, f = workloads.batch_config3([0], target_voxels=200000 if ref else 20000)
-    times = []
-    for i in range(4 if ref else 2):
-        t0 = time.perf_counter()
-        y = runner.run_module(net, runner.run_module(inp, [c, f], be), be)
-        runner.run_module(head, y, be)
-        times.append(time.perf_counter() - t0)
-    t = sorted(times[1:])[len(times[1:]) // 2]
-    return {"value": c.shape[0] / t, "unit": UNIT, "cores": cores, "kind": kind,
-            "sample": "one room of %d voxels, median of %d forwards after 1 warm-up" % (c.shape[0], len(times) - 1)}
+    from sparseconvnet_b200 import SCN
+    torch.cuda.set_device(0)
+    torch.zeros(1, device="cuda")
+    sampler = ClockSampler(0)
+    sampler.start()
+    rows = []
+    n_mma = 2048
+    n_sm = torch.cuda.get_device_properties(0).multi_processor_count
+    for a_tmem in (0, 1):
+        for m in (128, 64):
+            if a_tmem and m != 128:
+                continue
+            for bf16 in (0, 1):
+                for n in (8, 16, 32, 48, 64, 96, 128, 192, 256):
+                    if n < (16 if m == 128 else 8):
+                        continue
+                    rec = {"M": m, "N": n, "kind": "bf16 k16" if bf16 else "tf32 k8", "A": "tmem" if a_tmem else "smem"}
+                    for ctas, tag in ((1, "one_cta"), (n_sm, "all_sms")):
+                        ci, ct, ms = C.c_double(), C.c_double(), C.c_double()
+                        SCN.check(SCN.lib.scn_tc_probe_mma(m, n, bf16, a_tmem, n_mma, ctas, SCN._stream(),
+                                                           C.byref(ci), C.byref(ct), C.byref(ms)))
+                        rec[tag] = {"cycles_issue": round(ci.value, 1), "cycles_complete": round(ct.value, 1),
+                                    "event_us": round(1e3 * ms.value, 1)}
+                    rows.append(rec)
+    clocks = sampler.stop()
+    print(json.dumps({"probe": "tcgen05.mma cycles per instruction", "instructions_per_cta": n_mma,
+                      "clocks": clocks, "rows": rows}))
 
 
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--probe-mma", action="store_true",
+                    help="print the measured cost of one tcgen05.mma per shape and exit (1 GPU)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
@@ -236,6 +333,8 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         return run_reference(args, rank)
+    if args.probe_mma:
+        return run_probe_mma(args)
 
     import numpy as np
     import torch
@@ -258,86 +357,51 @@ def main():
     inp, net, head = workloads.build_config(CONFIG)
     net.to(dev)
     head.to(dev)
-    samples = list(range(rank * args.rooms, (rank + 1) * args.rooms))
-    coords_np, feats_np = workloads.make_batch(CONFIG, samples)
-    coords_host = torch.from_numpy(coords_np).pin_memory()
-    feats_host = torch.from_numpy(feats_np).pin_memory()
-    coords_dev, feats_dev = coords_host.to(dev), feats_host.to(dev)
-    n_vox = coords_np.shape[0]
-    out_host = torch.empty(n_vox, 20, dtype=torch.float32).pin_memory()
+    head_wt = head.weight.detach().t().contiguous()
 
-    def forward(c, f):
-        """Returns this rank's per-voxel scores; with N > 1 every rank also receives all ranks'
-        rows (one padded all_gather over NCCL)."""
-        with torch.no_grad():
-            y = head(net(inp([c, f])).features)
+    class Job(object):
+        """One rank's share of a batch: resident and pinned copies of its inputs, the gather buffers."""
+
+        def __init__(self, samples):
+            self.samples = list(samples)
+            if self.samples:
+                c, f = workloads.make_batch(CONFIG, self.samples)
+            else:  # more ranks than rooms: an empty shard still takes part in the collectives
+                c, f = np.zeros((0, 4), np.int64), np.zeros((0, 3), np.float32)
+            self.coords_host = torch.from_numpy(c).pin_memory()
+            self.feats_host = torch.from_numpy(f).pin_memory()
+            self.coords_dev, self.feats_dev = self.coords_host.to(dev), self.feats_host.to(dev)
+            self.n_vox = c.shape[0]
+            self.total_vox = self.n_vox
+            self.gather = None
             if world > 1:
-                # the gather of step i runs beside the kernels of step i+1; its result is taken one
-                # step later (and after the last step, inside the timed region: drain_gather)
-                pending.append(shard.gather_rows(y, count_group=count_group, async_op=True))
-                if len(pending) > 1:
-                    pending.pop(0).result()
-        return y
+                t = torch.tensor([self.n_vox, self.n_vox], device=dev, dtype=torch.int64)
+                tmax = t.clone()
+                dist.all_reduce(t)
+                dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+                self.total_vox = int(t[0].item())
+                # rank 0 receives every rank's scores; the head writes them into the gather buffer
+                self.gather = shard.RowGather(20, int(tmax[0].item()), dev, count_group=count_group, dst=0)
+            self.pending = []
 
-    pending = []
-
-    def drain_gather():
-        while pending:
-            pending.pop(0).result()
-
-    def step_resident():
-        return forward(coords_dev, feats_dev)
-
-    # End to end: every step copies its inputs from pinned host memory and its scores back to pinned
-    # host memory.  As in a serving loop, the copies run on two copy streams and overlap the
-    # neighbouring steps' kernels: the inputs of step i+1 travel while step i computes (two device
-    # input buffers), the scores of step i travel while step i+1 computes (two host output buffers).
-    main = torch.cuda.current_stream()
-    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
-    c_buf = [torch.empty_like(coords_dev) for _ in range(2)]
-    f_buf = [torch.empty_like(feats_dev) for _ in range(2)]
-    out_buf = [out_host, torch.empty_like(out_host).pin_memory()]
-    in_ready = [torch.cuda.Event() for _ in range(2)]
-    in_free = [torch.cuda.Event() for _ in range(2)]
-    out_free = [torch.cuda.Event() for _ in range(2)]
-
-    def fetch_inputs(b):
-        with torch.cuda.stream(s_in):
-            s_in.wait_event(in_free[b])      # the step that last read this buffer has finished
-            c_buf[b].copy_(coords_host, non_blocking=True)
-            f_buf[b].copy_(feats_host, non_blocking=True)
-            in_ready[b].record(s_in)
-
-    class E2E:
-        def begin(self, steps):
-            self.i, self.steps = 0, steps
-            for b in range(2):
-                in_free[b].record(main)
-                out_free[b].record(main)
-            fetch_inputs(0)
-
-        def step(self):
-            b = self.i & 1
-            if self.i + 1 < self.steps:
-                fetch_inputs(b ^ 1)
-            main.wait_event(in_ready[b])
-            y = forward(c_buf[b], f_buf[b])
-            in_free[b].record(main)
-            done = torch.cuda.Event()
-            done.record(main)
-            with torch.cuda.stream(s_out):
-                s_out.wait_event(done)
-                s_out.wait_event(out_free[b])
-                out_buf[b].copy_(y, non_blocking=True)
-                out_free[b].record(s_out)
-            y.record_stream(s_out)
-            self.i += 1
+        def forward(self, c, f):
+            """This rank's per-voxel scores.  With N > 1 the head writes them into this rank's block of
+            the gather buffer and one NCCL gather (to rank 0) is enqueued; it runs beside the kernels of
+            the next step and is taken one step later (after the last step: drain, inside the timed region)."""
+            with torch.no_grad():
+                x = net(inp([c, f])).features
+                if self.gather is None:
+                    return head(x)
+                y = self.gather.block(x.shape[0])
+                torch.addmm(head.bias, x, head_wt, out=y)
+                self.pending.append(self.gather.start(x.shape[0]))
+                if len(self.pending) > 1:
+                    self.pending.pop(0).wait()
             return y
 
-        def end(self):
-            main.wait_stream(s_out)          # the last scores have reached the host inside the timed region
-
-    e2e_loop = E2E()
+        def drain(self):
+            while self.pending:
+                self.pending.pop(0).wait()
 
     def barrier():
         torch.cuda.synchronize()
@@ -345,18 +409,18 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps, begin=None, end=None):
+    def timed(fn, steps, begin=None, end=None, drain=None):
         # a cyclic-GC pass of the interpreter in the middle of a step stalls the launch thread for
         # tens of ms (seen as one 70 ms step among 31 ms ones): collect before, not during
         import gc
         gc.collect()
         gc.disable()
         try:
-            return _timed(fn, steps, begin, end)
+            return _timed(fn, steps, begin, end, drain)
         finally:
             gc.enable()
 
-    def _timed(fn, steps, begin, end):
+    def _timed(fn, steps, begin, end, drain):
         barrier()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         l0 = SCN.launch_count()
@@ -370,7 +434,8 @@ def main():
                 marks[i].record()
         if end:
             end()
-        drain_gather()
+        if drain:
+            drain()
         b.record()
         barrier()
         ms = a.elapsed_time(b)
@@ -383,98 +448,229 @@ def main():
             ms = float(t.item())
         return ms, launches
 
-    scn.set_precision(args.precision)
-    for _ in range(args.warmup):
-        step_resident()
-    sampler = ClockSampler(local)
-    sampler.start()
-    ms, launches = timed(step_resident, args.steps)
-    per_step = timed.per_step
-    clocks = sampler.stop()
-    for _ in range(2):
-        e2e_loop.begin(1)
-        e2e_loop.step()
-        e2e_loop.end()
-    ms_e2e, _ = timed(e2e_loop.step, args.steps, e2e_loop.begin, e2e_loop.end)
+    class E2E(object):
+        """End to end: every step copies its inputs from pinned host memory and its scores back to pinned
+        host memory.  As in a serving loop, the copies run on two copy streams and overlap the
+        neighbouring steps' kernels: the inputs of step i+1 travel while step i computes (two device
+        input buffers), the scores of step i travel while step i+1 computes (two host output buffers)."""
 
-    total_vox = n_vox
-    if world > 1:
-        t = torch.tensor([n_vox], device=dev, dtype=torch.int64)
-        dist.all_reduce(t)
-        total_vox = int(t.item())
+        def __init__(self, job):
+            self.job = job
+            self.main = torch.cuda.current_stream()
+            self.s_in, self.s_out = torch.cuda.Stream(), torch.cuda.Stream()
+            self.c_buf = [torch.empty_like(job.coords_dev) for _ in range(2)]
+            self.f_buf = [torch.empty_like(job.feats_dev) for _ in range(2)]
+            self.out_buf = [torch.empty(job.n_vox, 20, dtype=torch.float32).pin_memory() for _ in range(2)]
+            self.in_ready = [torch.cuda.Event() for _ in range(2)]
+            self.in_free = [torch.cuda.Event() for _ in range(2)]
+            self.out_free = [torch.cuda.Event() for _ in range(2)]
+
+        def fetch_inputs(self, b):
+            with torch.cuda.stream(self.s_in):
+                self.s_in.wait_event(self.in_free[b])      # the step that last read this buffer has finished
+                self.c_buf[b].copy_(self.job.coords_host, non_blocking=True)
+                self.f_buf[b].copy_(self.job.feats_host, non_blocking=True)
+                self.in_ready[b].record(self.s_in)
+
+        def begin(self, steps):
+            self.i, self.steps = 0, steps
+            for b in range(2):
+                self.in_free[b].record(self.main)
+                self.out_free[b].record(self.main)
+            self.fetch_inputs(0)
+
+        def step(self):
+            b = self.i & 1
+            if self.i + 1 < self.steps:
+                self.fetch_inputs(b ^ 1)
+            self.main.wait_event(self.in_ready[b])
+            self.main.wait_event(self.out_free[b])     # the scores of two steps ago have left their buffer
+            y = self.job.forward(self.c_buf[b], self.f_buf[b])
+            self.in_free[b].record(self.main)
+            done = torch.cuda.Event()
+            done.record(self.main)
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(done)
+                self.out_buf[b].copy_(y, non_blocking=True)
+                self.out_free[b].record(self.s_out)
+            y.record_stream(self.s_out)
+            self.i += 1
+            return y
+
+        def end(self):
+            self.main.wait_stream(self.s_out)          # the last scores have reached the host inside the timed region
+
+    def measure(job, steps, warmup):
+        """(ms resident, launches, per-step ms, clocks, ms end to end) of `steps` forwards of `job`."""
+        for _ in range(warmup):
+            job.forward(job.coords_dev, job.feats_dev)
+        job.drain()
+        sampler = ClockSampler(local)
+        sampler.start()
+        ms, launches = timed(lambda: job.forward(job.coords_dev, job.feats_dev), steps, drain=job.drain)
+        per_step = timed.per_step
+        clocks = sampler.stop()
+        loop = E2E(job)
+        for _ in range(2):
+            loop.begin(1)
+            loop.step()
+            loop.end()
+        job.drain()
+        ms_e2e, _ = timed(loop.step, steps, loop.begin, loop.end, drain=job.drain)
+        return ms, launches, per_step, clocks, ms_e2e
+
+    scn.set_precision(args.precision)
+    job = Job(range(rank * args.rooms, (rank + 1) * args.rooms))
+    ms, launches, per_step, clocks, ms_e2e = measure(job, args.steps, args.warmup)
+    total_vox, n_vox = job.total_vox, job.n_vox
     value = total_vox * args.steps / (ms / 1e3)
     e2e = total_vox * args.steps / (ms_e2e / 1e3)
 
+    # ---- N > 1: what the gather delivered, checked outside the timed region ------------------------------
+    gather_check = None
+    strong = None
+    if world > 1:
+        with torch.no_grad():
+            y_ref = head(net(inp([job.coords_dev, job.feats_dev])).features)       # the plain path, own rows
+            check = shard.RowGather(20, job.gather.capacity, dev, count_group=count_group, dst=None, depth=1)
+            torch.addmm(head.bias, net(inp([job.coords_dev, job.feats_dev])).features, head_wt,
+                        out=check.block(y_ref.shape[0]))
+            views, counts = check.start(y_ref.shape[0]).blocks()
+            torch.cuda.synchronize()
+        # every rank: its own block of the gathered buffer holds exactly the bits of its plain result;
+        # rank 0: every block's checksum equals the checksum its sender computed from its own result
+        own_equal = bool(torch.equal(views[rank], y_ref))
+        sums = torch.stack([v.double().sum() for v in views])
+        mine = torch.zeros(world, dtype=torch.float64, device=dev)
+        mine[rank] = y_ref.double().sum()
+        dist.all_reduce(mine)
+        flags = torch.tensor([1 if own_equal else 0, 1 if torch.equal(sums, mine) else 0], device=dev)
+        dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+        gather_check = {"own_block_bit_equal_on_every_rank": bool(flags[0].item()),
+                        "block_checksums_match_senders": bool(flags[1].item()),
+                        "counts": counts, "counts_add_up": sum(counts) == total_vox}
+        del check, views, y_ref
+        # strong scaling of the batch the metric names: the same 8 rooms split over the ranks by batch index
+        lo, hi = shard.shard_range(ROOMS_PER_GPU, rank, world)
+        sjob = Job(range(lo, hi))
+        s_ms, _, s_per_step, _, s_ms_e2e = measure(sjob, args.steps, args.warmup)
+        strong = {"workload": workload_name(ROOMS_PER_GPU).replace("per GPU", "in all, split over %d GPUs" % world),
+                  "voxels_per_step": sjob.total_vox, "rooms_per_rank": [len(range(*shard.shard_range(ROOMS_PER_GPU, r, world)))
+                                                                         for r in range(world)],
+                  "value": sjob.total_vox * args.steps / (s_ms / 1e3), "unit": UNIT, "ms_per_step": s_ms / args.steps,
+                  "e2e_value": sjob.total_vox * args.steps / (s_ms_e2e / 1e3), "e2e_ms_per_step": s_ms_e2e / args.steps,
+                  "scaling": "strong"}
+        del sjob
+
     # ---- per-operator breakdown (CUDA events around every operator call, one extra step) -------
     with SCN.Profile() as prof:
-        step_resident()
+        job.forward(job.coords_dev, job.feats_dev)
+    job.drain()
     agg = summarize_profile(prof.rows())
     peak, peak_src = peaks()
-    top = max(agg, key=lambda k: agg[k]["ms"])
+    tpeak, tsrc = tensor_peak_tflops()
+    conv_classes = [k for k in agg if agg[k]["flops"]]
+    top = max(conv_classes or agg, key=lambda k: agg[k]["ms"])
     a = agg[top]
     achieved = a["bytes"] / (a["ms"] / 1e3) / 1e9
-    roofline = {"kernel": {"batchnorm": "k_bn_apply", "rules_submanifold": "k_submanifold_rules",
-                           "rules_strided": "k_strided_*", "input_hash": "k_insert_input"}.get(top, top),
-                "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "peak_source": peak_src, "frac_of_nominal_7700": achieved / 7700.0,
+    roofline = {"kernel": top, "bound": LIMITS.get(top, ("hbm", None))[0], "achieved": achieved, "peak": peak,
+                "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
+                "frac_of_nominal_7700": achieved / 7700.0,
                 "traffic": (TRAFFIC_RATIO[top] * a["bytes"] / a["calls"]) if top in TRAFFIC_RATIO else None,
-                "algorithmic_bytes_per_step": a["bytes"], "launches_per_step": a["calls"], "ms_per_step": a["ms"],
-                "tflops": a["flops"] / (a["ms"] / 1e3) / 1e12 if a["flops"] else None}
+                "algorithmic_bytes_per_launch": a["bytes"] / a["calls"], "launches_per_step": a["calls"],
+                "ms_per_step": a["ms"], "tflops": a["flops"] / (a["ms"] / 1e3) / 1e12 if a["flops"] else None,
+                "limiter": LIMITS.get(top, (None, None))[1]}
     if a["flops"]:
         # the same kernel against the tensor pipe: algorithmic FLOPs (2 x rules x Cin x Cout; the
-        # three-pass mode issues three times as many) over the dense tf32 peak
-        tpeak, tsrc = tensor_peak_tflops()
+        # split mode issues three products per FLOP counted) over the dense tf32 peak
         roofline["tensor"] = {"achieved": roofline["tflops"], "peak": tpeak, "unit": "TFLOP/s",
                               "frac": roofline["tflops"] / tpeak, "peak_source": tsrc}
-    roofline["limiter"] = {
-        "k_conv_tma": "shared-memory data pipe (ncu: 77 % busy, tensor pipe 40-46 %), see "
-                      "profiles/k_conv_tma_tf32x3_unet3d_4rooms.md",
-        "k_conv_pipe_mma": "instruction issue and shared-memory data pipe of small (offset, 128-row) steps, see "
-                           "profiles/k_conv_pipe_mma_unet3d_4and8rooms.md",
-        "k_conv_rows": "LSU data pipe 75 % busy (fragment loads, weight fragments from L2), warp-level tensor pipe "
-                       "43-50 %, see profiles/k_conv_rows_unet3d_4rooms.md"}.get(top)
-    breakdown = {k: {"ms": round(v["ms"], 4), "calls": v["calls"],
-                     "GBps": round(v["bytes"] / (v["ms"] / 1e3) / 1e9, 1) if v["ms"] > 0 else None}
-                 for k, v in sorted(agg.items(), key=lambda kv: -kv[1]["ms"])}
+    breakdown = {}
+    for k, v in sorted(agg.items(), key=lambda kv: -kv[1]["ms"]):
+        gbps = v["bytes"] / (v["ms"] / 1e3) / 1e9 if v["ms"] > 0 else None
+        breakdown[k] = {"ms": round(v["ms"], 4), "calls": v["calls"], "GBps": round(gbps, 1) if gbps else None,
+                        "frac_of_hbm_peak": round(gbps / peak, 3) if gbps else None}
+        if v["flops"]:
+            tf = v["flops"] / (v["ms"] / 1e3) / 1e12
+            breakdown[k]["TFLOPs"] = round(tf, 1)
+            breakdown[k]["frac_of_tf32_peak"] = round(tf / tpeak, 3)
+        if "built" in v:
+            breakdown[k]["built"] = v["built"]
 
-    # ---- configuration 1: one 3-D submanifold convolution 32->32 ------------------------------
+    # ---- the other configurations (rank 0, one GPU): voxels/s and the reference CPU beside each -----------
+    configs = None
     sub = None
-    if rank == 0 and not args.no_config1:
-        inp1, net1, _ = workloads.build_config(1)
-        net1.to(dev)
-        c1, f1 = workloads.make_batch(1, [0])
-        c1d, f1d = torch.from_numpy(c1).to(dev), torch.from_numpy(f1).to(dev)
+    cpu_ref = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu_ref, cpu = cpu_baseline_sample(workloads, args.rooms)
+    else:
+        cpu = None
+    if rank == 0 and world == 1 and not args.no_config1:
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)   # larger than the 126 MB L2
 
-        def ev_time(fn, reps):
-            torch.cuda.synchronize()
-            a_, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a_.record()
+        def ev_each(fn, reps):
+            """Mean CUDA-event time of `reps` calls, L2 flushed (a 256 MB write) before each."""
+            tot = 0.0
             for _ in range(reps):
+                flush.fill_(1)
+                a_, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a_.record()
                 fn()
-            b_.record()
-            torch.cuda.synchronize()
-            return a_.elapsed_time(b_) / reps
+                b_.record()
+                torch.cuda.synchronize()
+                tot += a_.elapsed_time(b_)
+            return tot / reps
 
-        with torch.no_grad():
-            def cold():
-                return net1(inp1([c1d, f1d]))
+        configs = {}
+        table = [(1, [0], ("fp32", "tf32x3")), (2, list(range(100)), ("fp32", "tf32x3")),
+                 (4, list(range(16)), ("fp32", "tf32x3")), (5, list(range(4)), ("bf16", "tf32x3"))]
+        for cfg, samples, modes in table:
+            inp_c, net_c, head_c = workloads.build_config(cfg)
+            net_c.to(dev)
+            if head_c is not None:
+                head_c.to(dev)
+            c_np, f_np = workloads.make_batch(cfg, samples)
+            c_d, f_d = torch.from_numpy(c_np).to(dev), torch.from_numpy(f_np).to(dev)
 
-            for _ in range(3):
-                x1 = inp1([c1d, f1d])
-                net1(x1)
-            t_cold = ev_time(cold, 10)
-            t_warm = ev_time(lambda: net1(x1), 20)
+            def fwd():
+                with torch.no_grad():
+                    y = net_c(inp_c([c_d, f_d]))
+                    return head_c(y.features) if head_c is not None else y
 
-            def rules_only():
-                x = inp1([c1d, f1d])
-                SCN.lib.scn_md_submanifold_rulebook(x.metadata._h, SCN.sizes([256] * 3), SCN.sizes([3] * 3),
-                                                    SCN._stream(), None)
-            t_rules = ev_time(rules_only, 10)
-        n1 = c1.shape[0]
-        sub = {"workload": "config1: SubmanifoldConvolution 3D f3 32->32 fp32, 256^3, batch 1", "sites": n1,
-               "cold_sites_per_sec": n1 / (t_cold / 1e3), "warm_sites_per_sec": n1 / (t_warm / 1e3),
-               "hash_and_rulebook_sites_per_sec": n1 / (t_rules / 1e3),
-               "ms": {"cold": t_cold, "warm": t_warm, "hash_and_rulebook": t_rules}}
+            rec = {"workload": CONFIG_NAMES[cfg], "voxels_per_step": int(c_np.shape[0]),
+                   "l2": "flushed before every timed forward"}
+            for mode in modes:
+                scn.set_precision(mode)
+                for _ in range(3):
+                    fwd()
+                t = ev_each(fwd, max(3, args.steps // 2))
+                rec[mode] = {"ms_per_step": round(t, 4), "voxels_per_sec": c_np.shape[0] / (t / 1e3)}
+            scn.set_precision(args.precision)
+            if cfg == 1:
+                # cold = hash + rulebook + convolution (fresh Metadata); warm = cached rulebook; rules only
+                with torch.no_grad():
+                    x1 = inp_c([c_d, f_d])
+                    net_c(x1)
+                    t_warm = ev_each(lambda: net_c(x1), 10)
+
+                    def rules_only():
+                        x = inp_c([c_d, f_d])
+                        SCN.lib.scn_md_submanifold_rulebook(x.metadata._h, SCN.sizes([256] * 3), SCN.sizes([3] * 3),
+                                                            SCN._stream(), None)
+                    t_rules = ev_each(rules_only, 10)
+                n1 = c_np.shape[0]
+                t_cold = rec[args.precision if args.precision in rec else "tf32x3"]["ms_per_step"]
+                sub = {"workload": CONFIG_NAMES[1], "sites": n1, "precision": args.precision,
+                       "cold_sites_per_sec": n1 / (t_cold / 1e3), "warm_sites_per_sec": n1 / (t_warm / 1e3),
+                       "hash_and_rulebook_sites_per_sec": n1 / (t_rules / 1e3),
+                       "ms": {"cold": t_cold, "warm": t_warm, "hash_and_rulebook": t_rules}}
+            if cpu_ref is not None:
+                v_cpu, sec_cpu, _ = cpu_ref.time(cfg, samples, 0 if cfg == 5 else 1, 1 if cfg == 5 else 2)
+                rec["reference_cpu"] = {"voxels_per_sec": v_cpu, "ms_per_step": 1e3 * sec_cpu, "cores": cpu_ref.cores,
+                                        "kind": cpu_ref.kind}
+            configs["config%d" % cfg] = rec
+            del net_c, c_d, f_d
+        del flush
 
     # ---- the other arithmetic modes on the same workload (resident inputs, fewer steps) ---------
     variants = {args.precision: value}
@@ -484,8 +680,9 @@ def main():
                 continue
             scn.set_precision(mode)
             for _ in range(3):  # the mode's first steps grow the allocator's pool for its scratch buffers
-                step_resident()
-            ms_v, _ = timed(step_resident, max(2, args.steps // 2))
+                job.forward(job.coords_dev, job.feats_dev)
+            job.drain()
+            ms_v, _ = timed(lambda: job.forward(job.coords_dev, job.feats_dev), max(2, args.steps // 2), drain=job.drain)
             variants[mode] = total_vox * max(2, args.steps // 2) / (ms_v / 1e3)
         scn.set_precision(args.precision)
 
@@ -520,27 +717,25 @@ def main():
                     "backward": "input gradients %s, weight gradients fp32" % args.precision, "optimizer": "SGD"}
         del net_t, head_t, params, opt
 
-    cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cpu = cpu_baseline_sample()
-
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": {"fp32": "f32", "tf32x3": "f32 (3-pass tf32 split on tcgen05, fp32 accumulate)",
-                      "tf32": "tf32", "bf16": "bf16"}[args.precision], "data": "synthetic",
+            "vs_baseline": None, "dtype": DTYPE_LABEL[args.precision], "data": "synthetic",
             "config": {"workload": workload_name(args.rooms), "voxels_per_step": total_vox,
                        "l2": "inputs and activations (>200 MB per tensor) exceed the 126 MB L2",
                        "precision": scn.get_precision(), "parallelism": "dp%d by batch index" % world},
             "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
-                    "h2d_bytes_per_step": int(coords_host.numel() * 8 + feats_host.numel() * 4),
-                    "d2h_bytes_per_step": int(out_host.numel() * 4)},
+                    "h2d_bytes_per_step": int(job.coords_host.numel() * 8 + job.feats_host.numel() * 4),
+                    "d2h_bytes_per_step": int(n_vox * 20 * 4)},
             "gpu_launches": int(launches), "ms_each_step": per_step,
-            "roofline": roofline, "breakdown_ms_per_step": breakdown, "submanifold_conv": sub,
+            "roofline": roofline, "breakdown_ms_per_step": breakdown, "submanifold_conv": sub, "configs": configs,
             "variants_voxels_per_sec": variants, "training_step": training,
             "cpu_baseline": cpu, "clocks": clocks,
         }
+        if world > 1:
+            line["gather_check"] = gather_check
+            line["strong_scaling"] = strong
         print(json.dumps(line))
         if args.profile_out:
             with open(args.profile_out, "w") as f:

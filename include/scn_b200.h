@@ -87,6 +87,10 @@ SCN_API const char *scn_last_error(void);
 /* number of CUDA kernels this library has launched in this process so far (no counterpart in
  * the reference; used to report how many kernels a timed region ran) */
 SCN_API long long scn_launch_count(void);
+/* number of rulebooks this process has CONSTRUCTED so far (a lookup served from a metadata
+ * object's cache does not count).  No counterpart in the reference; lets a profiler credit the
+ * bytes of a rulebook build only to the call that built it. */
+SCN_API long long scn_rulebook_build_count(void);
 
 /* ---- Metadata object ------------------------------------------------------------------ */
 
@@ -183,6 +187,17 @@ SCN_API int scn_md_rulebook_export(scn_metadata *md, int kind, const int64_t *si
 /* -1 before the first convolution, else an scn_conv_kernel value.  No counterpart in the
  * reference; lets a profiler attribute a call's time to the kernel that ran it. */
 SCN_API int scn_last_conv_kernel(void);
+
+/* Self-calibration of the tensor path.  No counterpart in the reference.  Issues `n_mma`
+ * tcgen05.mma instructions of shape M x N (x 8 tf32 / 16 bf16 along K) back to back from one
+ * thread of each of `n_ctas` CTAs onto disjoint accumulator ranges of TMEM, one commit at the end,
+ * and reports SM cycles per instruction (until the last one was issued / until all completed,
+ * clock64, averaged over the CTAs) and the CUDA-event duration of the whole launch.
+ * a_in_tmem != 0 reads the A operand from TMEM instead of shared memory (M = 128 only).
+ * Allocates a few KB for the duration of the call and waits for the stream. */
+SCN_API int scn_tc_probe_mma(int m, int n, int kind_bf16, int a_in_tmem, int n_mma, int n_ctas,
+                             void *stream, double *cycles_issue, double *cycles_total,
+                             double *event_ms);
 
 /* The convolution operators return the reference's multiply-add count (rules x planes in x planes
  * out, CPU/Convolution.cpp:141) through `macs`.  The reference knows the rule totals on the host;

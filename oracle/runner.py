@@ -23,10 +23,18 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _REF = os.path.join(_HERE, "_ref")
 
 
+_EXTENSION_KEY = "_scn_reference_cpu_extension"  # shared with the staged package (oracle/build_ref.py)
+
+
 def _load(name):
+    import sys
+    if name == "SCN" and _EXTENSION_KEY in sys.modules:
+        return sys.modules[_EXTENSION_KEY]
     spec = importlib.util.spec_from_file_location(name, os.path.join(_REF, name + ".so"))
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
+    if name == "SCN":
+        sys.modules[_EXTENSION_KEY] = mod
     return mod
 
 

@@ -446,7 +446,9 @@ def SubmanifoldConvolution_updateOutput(inputSize, filterSize, m, input_features
             raise RuntimeError("features have %d rows, metadata has %d active sites" % (f.size(0), n))
         output_features.resize_(n, groups * cout)
         with _timed("rules_submanifold", dict(sites=n, offsets=w.size(0), dim=m.dimension)) as info:
+            builds = lib.scn_rulebook_build_count()
             check(lib.scn_md_submanifold_rulebook(m._h, sizes(inputSize), sizes(filterSize), _stream(), None))
+            info["built"] = lib.scn_rulebook_build_count() > builds  # False: served from the cache
         with _timed("conv", dict(op="submanifold", n_in=n, n_out=n, cin=cin, cout=cout, groups=groups,
                                  offsets=w.size(0), precision=_precision)) as info:
             check(lib.scn_submanifold_convolution_forward(
@@ -470,9 +472,11 @@ def Convolution_updateOutput(inputSize, outputSize, filterSize, filterStride, m,
             raise RuntimeError("features have %d rows, metadata has %d active sites"
                                % (f.size(0), m.getNActive(inputSize)))
         with _timed("rules_strided", dict(sites=f.size(0), offsets=w.size(0), dim=m.dimension)) as info:
+            builds = lib.scn_rulebook_build_count()
             check(lib.scn_md_strided_rulebook(m._h, sizes(inputSize), sizes(outputSize), sizes(filterSize),
                                               sizes(filterStride), _stream(), C.byref(n_out), None))
             info["sites_out"] = n_out.value
+            info["built"] = lib.scn_rulebook_build_count() > builds
         output_features.resize_(n_out.value, groups * cout)
         with _timed("conv", dict(op="strided", n_in=f.size(0), n_out=n_out.value, cin=cin, cout=cout,
                                  groups=groups, offsets=w.size(0), precision=_precision)) as info:

@@ -18,7 +18,10 @@ SIGNATURES = {
     "scn_status_string": (C.c_char_p, [C.c_int]),
     "scn_last_error": (C.c_char_p, []),
     "scn_launch_count": (C.c_longlong, []),
+    "scn_rulebook_build_count": (C.c_longlong, []),
     "scn_last_conv_kernel": (C.c_int, []),
+    "scn_tc_probe_mma": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp,
+                                   C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "scn_set_deferred_counts": (C.c_int, [C.c_int]),
     "scn_set_backward_precision": (C.c_int, [C.c_int]),
     "scn_md_take_count_ticket": (C.c_int, [_vp, C.POINTER(_vp)]),

@@ -13,11 +13,14 @@
 #include <algorithm>
 #include <climits>
 
+#include <atomic>
 #include <mutex>
 
 #include "metadata.cuh"
 
 namespace scn {
+
+static std::atomic<long long> g_rulebook_builds{0};  // rulebooks constructed (not served from a cache)
 
 // ------------------------------------------------------------------------------------------
 // key layout
@@ -590,6 +593,7 @@ int get_submanifold_rulebook(scn_metadata *md, const int64_t *spatial_size,
     SCN_CUDA_CHECK(cudaGetLastError());
   }
   rb.built = true;
+  g_rulebook_builds.fetch_add(1);
   return SCN_OK;
 }
 
@@ -782,6 +786,7 @@ int get_strided_rulebook(scn_metadata *md, const int64_t *input_size, const int6
   device_free(rank, stream);
   md->grids[okey] = gout;
   rb.built = true;
+  g_rulebook_builds.fetch_add(1);
   return SCN_OK;
 }
 
@@ -989,6 +994,8 @@ static int rulebook_export(Rulebook &rb, int64_t *n_offsets, int64_t *counts_hos
 using namespace scn;
 
 extern "C" {
+
+long long scn_rulebook_build_count(void) { return g_rulebook_builds.load(); }
 
 int scn_md_create(int dimension, scn_metadata **md) {
   SCN_REQUIRE(md, SCN_ERR_BAD_ARG, "null output pointer");

@@ -95,3 +95,110 @@ def gather_rows(rows, group=None, count_group=None, async_op=False):
     work = dist.all_gather_into_tensor(out, padded, group=group, async_op=async_op)
     pending = PendingGather(out, padded, counts, biggest, work if async_op else None)
     return pending if async_op else pending.result()
+
+
+class RowGather(object):
+    """Gather of per-row results without staging copies: a preallocated buffer of
+    ``world x capacity`` rows per step in flight; the last operator of the step (the linear head)
+    writes this rank's rows straight into its own block (``block(n)``), and ``start(n)`` enqueues
+    one collective on that buffer in place -- no padding copy, no zero fill.  Row counts travel on
+    the host through `count_group` (see host_group) before anything is enqueued, so every rank sees
+    the same counts and decides the same way: a count above the capacity raises ``ValueError`` on
+    every rank instead of corrupting a neighbour's block, and a rank that never arrives ends the
+    others' count exchange with the group's timeout, not with a hang on the GPU.
+
+    `dst` = None: every rank receives all blocks (all_gather); `dst` = r: only rank r does (gather),
+    the other ranks send their block and receive nothing.  `depth` buffers rotate, so a gather may
+    still be running while the next step fills the next buffer."""
+
+    def __init__(self, width, capacity, device, dtype=torch.float32, group=None, count_group=None, dst=None,
+                 depth=2):
+        self.group, self.count_group, self.dst = group, count_group, dst
+        self.distributed = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+        self.world = dist.get_world_size(group) if self.distributed else 1
+        self.rank = dist.get_rank(group) if self.distributed else 0
+        self.capacity, self.width = int(capacity), int(width)
+        receives = dst is None or dst == self.rank
+        rows = self.world * self.capacity if receives else self.capacity
+        self.buffers = [torch.empty(rows, self.width, dtype=dtype, device=device) for _ in range(depth)]
+        self.receives = receives
+        self.turn = 0
+
+    def block(self, n):
+        """View of this rank's block in the current buffer: write the step's `n` result rows here."""
+        if n > self.capacity:
+            raise ValueError("%d rows exceed the gather capacity of %d rows per rank" % (n, self.capacity))
+        base = self.rank * self.capacity if self.receives else 0
+        return self.buffers[self.turn][base:base + n]
+
+    def start(self, n):
+        """Enqueues the gather of the current buffer (this rank wrote `n` rows) and moves on to the next
+        buffer.  Returns a PendingGather whose result() is (rows in rank order or None, counts)."""
+        buf = self.buffers[self.turn]
+        self.turn = (self.turn + 1) % len(self.buffers)
+        if not self.distributed:
+            return _Done(buf[:n], [n])
+        if self.count_group is not None:
+            parts = [torch.empty(1, dtype=torch.int64) for _ in range(self.world)]
+            dist.all_gather(parts, torch.tensor([n], dtype=torch.int64), group=self.count_group)
+            counts = torch.cat(parts).tolist()
+        else:
+            c = torch.empty(self.world, dtype=torch.int64, device=buf.device)
+            dist.all_gather_into_tensor(c, torch.tensor([n], dtype=torch.int64, device=buf.device), group=self.group)
+            counts = c.tolist()
+        if max(counts) > self.capacity:  # every rank sees the same counts and raises together
+            raise ValueError("a rank reported %d rows, the gather capacity is %d rows per rank"
+                             % (max(counts), self.capacity))
+        cap = self.capacity
+        if self.dst is None:
+            mine = buf[self.rank * cap:(self.rank + 1) * cap]
+            work = dist.all_gather_into_tensor(buf, mine, group=self.group, async_op=True)
+        elif self.receives:
+            work = dist.gather(buf[self.rank * cap:(self.rank + 1) * cap],
+                               [buf[r * cap:(r + 1) * cap] for r in range(self.world)],
+                               dst=dist.get_global_rank(self.group, self.dst) if self.group is not None else self.dst,
+                               group=self.group, async_op=True)
+        else:
+            work = dist.gather(buf, None,
+                               dst=dist.get_global_rank(self.group, self.dst) if self.group is not None else self.dst,
+                               group=self.group, async_op=True)
+        return _PendingBlocks(buf if self.receives else None, counts, cap, work)
+
+
+class _Done(object):
+    def __init__(self, rows, counts):
+        self.rows, self.counts = rows, counts
+
+    def result(self):
+        return self.rows, self.counts
+
+    def blocks(self):
+        return [self.rows], self.counts
+
+
+class _PendingBlocks(object):
+    def __init__(self, buf, counts, cap, work):
+        self.buf, self.counts, self.cap, self.work = buf, counts, cap, work
+
+    def wait(self):
+        if self.work is not None:
+            self.work.wait()
+            self.work = None
+
+    def blocks(self):
+        """(list of per-rank views [n_r, width] or None on a rank that receives nothing, counts):
+        no copy at all."""
+        self.wait()
+        if self.buf is None:
+            return None, self.counts
+        return [self.buf[r * self.cap:r * self.cap + c] for r, c in enumerate(self.counts)], self.counts
+
+    def result(self):
+        """(all ranks' rows concatenated in rank order, counts); one concatenation copy unless every
+        block is full."""
+        views, counts = self.blocks()
+        if views is None:
+            return None, counts
+        if all(c == self.cap for c in counts):
+            return self.buf, counts
+        return torch.cat(views), counts

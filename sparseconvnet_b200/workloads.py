@@ -14,7 +14,10 @@ so the CPU oracle and the GPU path see identical arrays.
 import numpy as np
 import torch
 
-import sparseconvnet_b200 as scn
+# The generators need numpy only.  The network builders take the package that provides the modules
+# (`scn`): this package by default, or the reference's own `sparseconvnet` -- the two build the same
+# module tree with the same parameter names, so a state_dict moves between them.  This file can be
+# loaded by path without importing the package (and with it the CUDA library).
 
 
 def _rng(config, sample):
@@ -233,13 +236,18 @@ def batch_config5(samples):
 
 # ---- networks --------------------------------------------------------------------------------------
 
+def _default_package():
+    import sparseconvnet_b200
+    return sparseconvnet_b200
+
+
 def randomize(model, seed):
     """Seeded non-trivial state: BatchNorm statistics and affine terms away from (0, 1) so a
     wrong mean/variance/eps convention cannot hide.  Convolution weights keep the module's own
     initialisation (drawn under the same seed)."""
     g = torch.Generator().manual_seed(seed)
     for m in model.modules():
-        if isinstance(m, scn.BatchNormalization):
+        if hasattr(m, "running_mean") and hasattr(m, "nPlanes") and getattr(m, "weight", None) is not None:
             m.running_mean.copy_(torch.randn(m.nPlanes, generator=g) * 0.2)
             m.running_var.copy_(torch.rand(m.nPlanes, generator=g) + 0.5)
             m.weight.data.copy_(torch.rand(m.nPlanes, generator=g) + 0.5)
@@ -247,9 +255,11 @@ def randomize(model, seed):
     return model
 
 
-def build_config(config, seed=0):
-    """Returns (input_layer, sparse_model, head) for BASELINE configuration 1..5; `head` is a
-    torch.nn.Linear applied to `.features` or None.  Eval mode, seeded weights."""
+def build_config(config, seed=0, scn=None):
+    """Returns (input_layer, sparse_model, head) for benchmark configuration 1..5; `head` is a
+    torch.nn.Linear applied to `.features` or None.  Eval mode, seeded weights.  `scn` is the
+    package the modules come from (default: sparseconvnet_b200)."""
+    scn = scn or _default_package()
     torch.manual_seed(1234 + 17 * config + seed)
     head = None
     if config == 1:
