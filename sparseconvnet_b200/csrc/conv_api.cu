@@ -5,6 +5,7 @@
 #include <atomic>
 
 #include "metadata.cuh"
+#include "tc_ptx.cuh"
 
 namespace scn {
 int conv_forward_simt(const float *in, long long n_in, float *out, long long n_out, const float *weight,
@@ -38,6 +39,11 @@ int conv_forward_rows_thin(const float *in, long long n_in, float *out, long lon
 int conv_forward_rows_scatter(const float *in, long long n_in, float *out, long long n_out, const float *weight,
                               const float *bias, const int *child_of, int K, int cin, int cout, int *flags,
                               cudaStream_t stream);
+
+int split_mode_of_env() {
+  const char *e = getenv("SCN_X3_FORM");
+  return (e && e[0] == 't') ? TC_TF32X3 : TC_BF16X3;
+}
 
 static thread_local int g_last_kernel = -1;
 static std::atomic<int> g_deferred_counts{0};

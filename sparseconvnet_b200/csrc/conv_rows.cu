@@ -104,6 +104,43 @@ __global__ void k_rows_prepare(const float *__restrict__ w, uint4 *__restrict__ 
   img[2 * i + 1] = pk;
 }
 
+// The image of the bf16 three-term form: [K][cin / 32][2][cout / 8][32] of uint4 =
+//   bf16 pairs (h(W[P+t]), h(W[P+t+4])), (h(W[P+8+t]), h(W[P+12+t])), then the same of m = bf16(W - h)
+__global__ void k_rows_prepare_b3(const float *__restrict__ w, uint4 *__restrict__ img, int K, int cin, int cout) {
+  const int nt_n = cout / 8, nch = cin / kRChunk;
+  const long long total = (long long)K * nch * 2 * nt_n * 32;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int lane = (int)(i & 31);
+  long long r = i >> 5;
+  const int nt = (int)(r % nt_n);
+  r /= nt_n;
+  const int kp = (int)(r & 1);
+  r >>= 1;
+  const int c = (int)(r % nch);
+  const int k = (int)(r / nch);
+  const int g = lane >> 2, t = lane & 3;
+  const int p0 = c * kRChunk + kp * 16 + t, n = nt * 8 + g;
+  const float *wk = w + ((long long)k * cin + p0) * cout + n;
+  float x[4] = {wk[0], wk[4 * (long long)cout], wk[8 * (long long)cout], wk[12 * (long long)cout]};
+  float m[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) m[e] = x[e] - __bfloat162float(__float2bfloat16_rn(x[e]));
+  uint4 q;
+  q.x = rows_pack_bf16(x[0], x[1]);
+  q.y = rows_pack_bf16(x[2], x[3]);
+  q.z = rows_pack_bf16(m[0], m[1]);
+  q.w = rows_pack_bf16(m[2], m[3]);
+  img[i] = q;
+}
+
+// a pair of floats as a bf16 pair (round to nearest) and the pair of what the rounding left over
+__device__ __forceinline__ void rows_split_bf16(float a, float b, unsigned &h, unsigned &m) {
+  h = rows_pack_bf16(a, b);
+  const float ra = a - __uint_as_float(h << 16), rb = b - __uint_as_float(h & 0xFFFF0000u);
+  m = rows_pack_bf16(ra, rb);
+}
+
 // One (offset, 32-plane chunk) step of a warp: its two 16-row tiles times the slab.
 // D fragment: d[mt][nt] = rows (g, g + 8) of tile mt x planes 8 nt + 2 t, + 1.
 // The A values are read with scalar loads in fragment order.  (Reading a lane's eight planes of a
@@ -120,7 +157,9 @@ __global__ void k_rows_prepare(const float *__restrict__ w, uint4 *__restrict__ 
 // from the feature matrix one half-step ahead (27 % slower: registers, and the loads' latency).
 // MODE (a TcMode): TC_TF32X3 as described above; TC_TF32 only the two tf32 instructions, on the values as
 // they are (the tensor core drops the low mantissa bits); TC_BF16 only the bf16 instruction x x W.  The
-// single-pass modes read only their half of the weight image.
+// single-pass modes read only their half of the weight image.  TC_BF16X3: the three bf16 products of the
+// h / m split (bp = {h pair, h pair, m pair, m pair} of the image of k_rows_prepare_b3): three tensor
+// instructions per 16 planes instead of four, and half the weight image.
 template <int NT, int MODE = TC_TF32X3>
 __device__ __forceinline__ void rows_tile16v(float (&d)[NT][4], const float (&x)[8], const unsigned (&bh)[NT][4],
                                              const unsigned (&bp)[NT][4]);
@@ -148,6 +187,30 @@ __device__ __forceinline__ void rows_tile16v(float (&d)[NT][4], const float (&x)
     for (int nt = 0; nt < NT; ++nt) {
       const unsigned b[2] = {bp[nt][0], bp[nt][1]};
       rows_mma_bf16(d[nt], ax, b);
+    }
+    return;
+  }
+  if (MODE == TC_BF16X3) {
+    unsigned ah[4], am[4];
+    rows_split_bf16(x00, x01, ah[0], am[0]);
+    rows_split_bf16(x10, x11, ah[1], am[1]);
+    rows_split_bf16(x02, x03, ah[2], am[2]);
+    rows_split_bf16(x12, x13, ah[3], am[3]);
+    // the small terms first; consecutive instructions write different accumulators
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const unsigned b[2] = {bp[nt][0], bp[nt][1]};
+      rows_mma_bf16(d[nt], am, b);
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const unsigned b[2] = {bp[nt][2], bp[nt][3]};
+      rows_mma_bf16(d[nt], ah, b);
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const unsigned b[2] = {bp[nt][0], bp[nt][1]};
+      rows_mma_bf16(d[nt], ah, b);
     }
     return;
   }
@@ -217,6 +280,11 @@ __device__ __forceinline__ void rows_chunk(float (&d)[2][NT][4], const float *a_
     unsigned bh[NT][4], bp[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
+      if (MODE == TC_BF16X3) {
+        const uint4 q = __ldg(w_slab + (kp * NT + nt) * 32 + lane);
+        bp[nt][0] = q.x, bp[nt][1] = q.y, bp[nt][2] = q.z, bp[nt][3] = q.w;
+        continue;
+      }
       if (MODE != TC_BF16) {
         const uint4 q0 = __ldg(w_slab + ((kp * NT + nt) * 32 + lane) * 2);
         bh[nt][0] = q0.x, bh[nt][1] = q0.y, bh[nt][2] = q0.z, bh[nt][3] = q0.w;
@@ -240,7 +308,7 @@ k_conv_rows(const float *__restrict__ in, int ld_in, long long n_in, float *__re
             long long n_out, const uint4 *__restrict__ img, const float *__restrict__ bias,
             const int *__restrict__ nbr, int K, int nch, int *flags) {
   constexpr unsigned kFull = 0xffffffffu;
-  constexpr int kSlab = 4 * NT * 32;  // uint4 per (offset, chunk) slab
+  constexpr int kSlab = (MODE == TC_BF16X3 ? 2 : 4) * NT * 32;  // uint4 per (offset, chunk) slab
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int lane = threadIdx.x;
   float *a_ring = reinterpret_cast<float *>(smem_raw);
@@ -366,7 +434,7 @@ static int launch_rows(const float *in, int ld_in, long long n_in, float *out, i
     // with 64 output planes the registers of the three-term mode hold the SM to 12 warps (110 KB of rings): half
     // the SM's memory is enough and the other half serves the weight fragments as L1 (3 % faster)
     SCN_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                        NT > 4 && MODE == TC_TF32X3 ? 50 : 80));
+                                        NT > 4 ? (MODE == TC_TF32X3 ? 50 : MODE == TC_BF16X3 ? 70 : 80) : 80));
     if (dev < 64) configured[dev] = true;
   }
   SCN_LAUNCH(kernel, (unsigned)ceil_div(n_out, 32LL), 32, smem, stream, in, ld_in, n_in, out, ld_out, n_out, img, bias,
@@ -521,13 +589,13 @@ int conv_forward_rows_thin(const float *in, long long n_in, float *out, long lon
 // once (filter = stride makes the children of different sites and offsets disjoint and covers every fine
 // site), so nothing is accumulated in memory.  Measured 10 % faster than the gather form (64 -> 32 planes,
 // 1.59 M fine rows: 0.33 against 0.37 ms; rows sorted by coordinate keep the gather form's tiles to two offsets).
-template <int NT>
+template <int NT, int MODE>
 __global__ void __launch_bounds__(32)
 k_conv_rows_scatter(const float *__restrict__ in, int ld_in, long long n_in, float *__restrict__ out, int ld_out,
                     long long n_out, const uint4 *__restrict__ img, const float *__restrict__ bias,
                     const int *__restrict__ child_of /* [K][n_in] -> output row */, int K, int nch, int *flags) {
   constexpr unsigned kFull = 0xffffffffu;
-  constexpr int kSlab = 4 * NT * 32;
+  constexpr int kSlab = (MODE == TC_BF16X3 ? 2 : 4) * NT * 32;
   const int lane = threadIdx.x, g = lane >> 2, t = lane & 3;
   const long long row0 = (long long)blockIdx.x * 32;
   if (row0 >= n_in) return;
@@ -560,10 +628,15 @@ k_conv_rows_scatter(const float *__restrict__ in, int ld_in, long long n_in, flo
         unsigned bh[NT][4], bp[NT][4];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-          const uint4 q0 = __ldg(w_slab + ((kp * NT + nt) * 32 + lane) * 2);
-          const uint4 q1 = __ldg(w_slab + ((kp * NT + nt) * 32 + lane) * 2 + 1);
-          bh[nt][0] = q0.x, bh[nt][1] = q0.y, bh[nt][2] = q0.z, bh[nt][3] = q0.w;
-          bp[nt][0] = q1.x, bp[nt][1] = q1.y, bp[nt][2] = q1.z, bp[nt][3] = q1.w;
+          if (MODE == TC_BF16X3) {
+            const uint4 q = __ldg(w_slab + (kp * NT + nt) * 32 + lane);
+            bp[nt][0] = q.x, bp[nt][1] = q.y, bp[nt][2] = q.z, bp[nt][3] = q.w;
+          } else {
+            const uint4 q0 = __ldg(w_slab + ((kp * NT + nt) * 32 + lane) * 2);
+            const uint4 q1 = __ldg(w_slab + ((kp * NT + nt) * 32 + lane) * 2 + 1);
+            bh[nt][0] = q0.x, bh[nt][1] = q0.y, bh[nt][2] = q0.z, bh[nt][3] = q0.w;
+            bp[nt][0] = q1.x, bp[nt][1] = q1.y, bp[nt][2] = q1.z, bp[nt][3] = q1.w;
+          }
         }
         const int off = c * kRChunk + kp * 16;
 #pragma unroll
@@ -574,7 +647,7 @@ k_conv_rows_scatter(const float *__restrict__ in, int ld_in, long long n_in, flo
           for (int h = 0; h < 2; ++h)
 #pragma unroll
             for (int e = 0; e < 4; ++e) x[h * 4 + e] = ap[mt][h] ? __ldg(ap[mt][h] + off + 4 * e) : 0.f;
-          rows_tile16v<NT>(d[mt], x, bh, bp);
+          rows_tile16v<NT, MODE>(d[mt], x, bh, bp);
         }
       }
     }
@@ -610,13 +683,21 @@ int conv_forward_rows_scatter(const float *in, long long n_in, float *out, long 
   const int nch = cin / kRChunk;
   uint4 *img = nullptr;
   const long long total = (long long)K * nch * 2 * (cout / 8) * 32;
-  SCN_TRY(device_alloc((void **)&img, (size_t)total * 2 * sizeof(uint4), stream));
-  SCN_LAUNCH(k_rows_prepare, (unsigned)ceil_div(total, 256LL), 256, 0, stream, weight, img, K, cin, cout);
-  const unsigned grid = (unsigned)ceil_div(n_in, 32LL);
-  if (cout == 32)
-    SCN_LAUNCH(k_conv_rows_scatter<4>, grid, 32, 0, stream, in, cin, n_in, out, cout, n_out, img, bias, child_of, K, nch, flags);
+  const bool b3 = split_mode_of_env() == TC_BF16X3;
+  SCN_TRY(device_alloc((void **)&img, (size_t)total * (b3 ? 1 : 2) * sizeof(uint4), stream));
+  if (b3)
+    SCN_LAUNCH(k_rows_prepare_b3, (unsigned)ceil_div(total, 256LL), 256, 0, stream, weight, img, K, cin, cout);
   else
-    SCN_LAUNCH(k_conv_rows_scatter<8>, grid, 32, 0, stream, in, cin, n_in, out, cout, n_out, img, bias, child_of, K, nch, flags);
+    SCN_LAUNCH(k_rows_prepare, (unsigned)ceil_div(total, 256LL), 256, 0, stream, weight, img, K, cin, cout);
+  const unsigned grid = (unsigned)ceil_div(n_in, 32LL);
+#define SCN_SCATTER_CALL(NT, MODE) \
+  SCN_LAUNCH((k_conv_rows_scatter<NT, MODE>), grid, 32, 0, stream, in, cin, n_in, out, cout, n_out, img, bias, child_of, K, nch, flags)
+  if (cout == 32) {
+    if (b3) SCN_SCATTER_CALL(4, TC_BF16X3); else SCN_SCATTER_CALL(4, TC_TF32X3);
+  } else {
+    if (b3) SCN_SCATTER_CALL(8, TC_BF16X3); else SCN_SCATTER_CALL(8, TC_TF32X3);
+  }
+#undef SCN_SCATTER_CALL
   const cudaError_t e = cudaGetLastError();
   const int rf = device_free(img, stream);
   SCN_CUDA_CHECK(e);
@@ -638,14 +719,20 @@ int conv_forward_rows(const float *in, long long n_in, float *out, long long n_o
   const int nch = cin / kRChunk;
   uint4 *img = nullptr;
   const long long total = (long long)K * nch * 4 * (cout / 8) * 32;
+  const bool b3 = precision == SCN_PRECISION_TF32X3 && split_mode_of_env() == TC_BF16X3;
   SCN_TRY(device_alloc((void **)&img, (size_t)total * sizeof(uint4), stream));
-  SCN_LAUNCH(k_rows_prepare, (unsigned)ceil_div(total, 256LL), 256, 0, stream, weight, img, K, cin, cout);
+  if (b3)
+    SCN_LAUNCH(k_rows_prepare_b3, (unsigned)ceil_div(total / 2, 256LL), 256, 0, stream, weight, img, K, cin, cout);
+  else
+    SCN_LAUNCH(k_rows_prepare, (unsigned)ceil_div(total / 2, 256LL), 256, 0, stream, weight, img, K, cin, cout);
   int rc;
 #define SCN_ROWS_CALL(NT, MODE) launch_rows<NT, MODE>(in, cin, n_in, out, cout, n_out, img, bias, table, K, nch, flags, stream)
   if (precision == SCN_PRECISION_BF16)
     rc = cout == 32 ? SCN_ROWS_CALL(4, TC_BF16) : SCN_ROWS_CALL(8, TC_BF16);
   else if (precision == SCN_PRECISION_TF32)
     rc = cout == 32 ? SCN_ROWS_CALL(4, TC_TF32) : SCN_ROWS_CALL(8, TC_TF32);
+  else if (b3)
+    rc = cout == 32 ? SCN_ROWS_CALL(4, TC_BF16X3) : SCN_ROWS_CALL(8, TC_BF16X3);
   else
     rc = cout == 32 ? SCN_ROWS_CALL(4, TC_TF32X3) : SCN_ROWS_CALL(8, TC_TF32X3);
 #undef SCN_ROWS_CALL

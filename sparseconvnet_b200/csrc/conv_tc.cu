@@ -75,11 +75,15 @@ __global__ void k_prepare_weights(const float *__restrict__ w, unsigned char *__
   float v = w[idx];
   int slice = c / kc, kk = c % kc;
   int n_slices = cin / kc;
-  int parts = mode == TC_TF32X3 ? 2 : 1;
-  if (mode == TC_BF16) {
+  int parts = (mode == TC_TF32X3 || mode == TC_BF16X3) ? 2 : 1;
+  if (mode == TC_BF16 || mode == TC_BF16X3) {
     size_t tile = (size_t)cout * kc * 2;
     size_t off = (size_t)(n / 8) * (kc / 8) * 128 + (size_t)(kk / 8) * 128 + (n % 8) * 16 + (kk % 8) * 2;
-    *reinterpret_cast<__nv_bfloat16 *>(out + ((size_t)k * n_slices + slice) * tile + off) = __float2bfloat16_rn(v);
+    unsigned char *base = out + (((size_t)k * n_slices + slice) * parts) * tile;
+    const __nv_bfloat16 h = __float2bfloat16_rn(v);
+    *reinterpret_cast<__nv_bfloat16 *>(base + off) = h;
+    if (mode == TC_BF16X3)  // what the rounding left over, again as bf16
+      *reinterpret_cast<__nv_bfloat16 *>(base + tile + off) = __float2bfloat16_rn(v - __bfloat162float(h));
   } else {
     size_t tile = (size_t)cout * kc * 4;
     size_t off = (size_t)(n / 8) * (kc / 4) * 128 + (size_t)(kk / 4) * 128 + (n % 8) * 16 + (kk % 4) * 4;
@@ -140,8 +144,8 @@ __device__ __forceinline__ void cp_async_wait_dyn(int n) {
 //   acc_full   tcgen05.commit after the last MMA of the tile
 template <int MODE>
 __global__ void __launch_bounds__(kTcThreads) k_conv_tc(TcParams P) {
-  constexpr bool kBf16 = (MODE == TC_BF16);
-  constexpr bool kSplit = (MODE == TC_TF32X3);
+  constexpr bool kBf16 = (MODE == TC_BF16 || MODE == TC_BF16X3);     // operands are bf16, converted while staging
+  constexpr bool kSplit = (MODE == TC_TF32X3 || MODE == TC_BF16X3);  // two parts per operand, three products
   constexpr int kEsize = kBf16 ? 2 : 4;
   constexpr int kPerPiece = 16 / kEsize;  // elements per 16-byte piece
   constexpr int kMmaK = 32 / kEsize;      // K per instruction (32 bytes)
@@ -275,19 +279,19 @@ __global__ void __launch_bounds__(kTcThreads) k_conv_tc(TcParams P) {
               else
                 *reinterpret_cast<uint4 *>(sa + off) = make_uint4(0, 0, 0, 0);
             } else {
-              // bf16: 8 input floats -> one 16-byte piece of 8 bf16, converted in registers
-              uint4 packed = make_uint4(0, 0, 0, 0);
+              // bf16: 8 input floats -> one 16-byte piece of 8 bf16, converted in registers; the
+              // three-term form also stores what the rounding left over, as a second bf16 tile
+              uint4 packed = make_uint4(0, 0, 0, 0), rest = make_uint4(0, 0, 0, 0);
               if (src_row >= 0) {
                 const float4 *src = reinterpret_cast<const float4 *>(col + (long long)src_row * P.ld_in);
                 float4 x = __ldg(src), y = __ldg(src + 1);
-                __nv_bfloat162 b0 = __floats2bfloat162_rn(x.x, x.y), b1 = __floats2bfloat162_rn(x.z, x.w);
-                __nv_bfloat162 b2 = __floats2bfloat162_rn(y.x, y.y), b3 = __floats2bfloat162_rn(y.z, y.w);
-                packed.x = *reinterpret_cast<unsigned *>(&b0);
-                packed.y = *reinterpret_cast<unsigned *>(&b1);
-                packed.z = *reinterpret_cast<unsigned *>(&b2);
-                packed.w = *reinterpret_cast<unsigned *>(&b3);
+                split_bf16_pair(x.x, x.y, packed.x, rest.x);
+                split_bf16_pair(x.z, x.w, packed.y, rest.y);
+                split_bf16_pair(y.x, y.y, packed.z, rest.z);
+                split_bf16_pair(y.z, y.w, packed.w, rest.w);
               }
               *reinterpret_cast<uint4 *>(sa + off) = packed;
+              if (kSplit) *reinterpret_cast<uint4 *>(sa + g_bytes + off) = rest;
             }
           }
         }
@@ -308,7 +312,7 @@ __global__ void __launch_bounds__(kTcThreads) k_conv_tc(TcParams P) {
         // step c = s - L: its rows have landed once only L groups are still pending
         cp_async_wait_dyn(L);
         unsigned char *sa = stage_base + (size_t)st_c * stage_bytes;
-        if (kSplit) {
+        if (kSplit && !kBf16) {
           // low parts of the pieces this thread copied: g_lo = g - trunc_tf32(g)
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
@@ -469,7 +473,7 @@ static int tc_mode_of(int precision) {
   switch (precision) {
     case SCN_PRECISION_TF32: return TC_TF32;
     case SCN_PRECISION_BF16: return TC_BF16;
-    case SCN_PRECISION_TF32X3: return TC_TF32X3;
+    case SCN_PRECISION_TF32X3: return split_mode_of_env();
     default: return -1;
   }
 }
@@ -518,7 +522,8 @@ static int split_factor(long long n_out, int K, int cout) {
 // (Cout <= 128: 256 columns each) and the ring keeps at least three stages; otherwise one CTA
 // with a deeper ring.  SCN_TC_STAGES / SCN_TC_KC / SCN_TC_LOOKAHEAD override the choice.
 static bool plan(int mode, int K, int cin, int cout, TcPlan &pl) {
-  const int esize = mode == TC_BF16 ? 2 : 4;
+  const int esize = (mode == TC_BF16 || mode == TC_BF16X3) ? 2 : 4;
+  const int parts = (mode == TC_TF32X3 || mode == TC_BF16X3) ? 2 : 1;
   const size_t control = (size_t)K * kTcRows * 4 + 16 * 8 + 2 * kTcMaxOffsets * 4 + 64;
   const size_t one_cta = 200 * 1024, two_ctas = 110 * 1024;
   const int force_kc = env_int("SCN_TC_KC", 0), force_ns = env_int("SCN_TC_STAGES", 0);
@@ -530,7 +535,7 @@ static bool plan(int mode, int K, int cin, int cout, TcPlan &pl) {
     for (int kc : {32, 16}) {
       if (cin % kc) continue;
       if (force_kc && kc != force_kc) continue;
-      size_t stage = ((size_t)kTcRows * kc * esize + (size_t)cout * kc * esize) * (mode == TC_TF32X3 ? 2 : 1);
+      size_t stage = ((size_t)kTcRows * kc * esize + (size_t)cout * kc * esize) * parts;
       if (control + 2 * stage > budget) continue;
       int stages = force_ns ? force_ns : (int)std::min<size_t>(4, (budget - control) / stage);
       if (control + (size_t)stages * stage > 220 * 1024) continue;
@@ -547,7 +552,7 @@ static bool plan(int mode, int K, int cin, int cout, TcPlan &pl) {
   // finished, so the ring needs lookahead + 2 stages to keep the producers from waiting on the
   // tensor core's round trip every step.  bf16 converts in registers with blocking loads, so
   // running ahead buys nothing there.
-  best.lookahead = mode == TC_BF16
+  best.lookahead = (mode == TC_BF16 || mode == TC_BF16X3)
                        ? 0
                        : std::max(1, std::min(env_int("SCN_TC_LOOKAHEAD", best.stages - 2), best.stages - 1));
   pl = best;
@@ -563,6 +568,7 @@ static int configure_tc_kernels() {
   SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_tc<TC_TF32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
   SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_tc<TC_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
   SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_tc<TC_TF32X3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+  SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_tc<TC_BF16X3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
   if (dev >= 0 && dev < 64) configured[dev] = true;
   return SCN_OK;
 }
@@ -576,8 +582,8 @@ int conv_forward_tc(const float *in, long long n_in, float *out, long long n_out
   SCN_REQUIRE((uintptr_t)in % 16 == 0, SCN_ERR_BAD_ARG, "tensor-core path needs a 16-byte aligned input matrix");
   TcPlan pl;
   SCN_REQUIRE(plan(mode, K, cin, cout, pl), SCN_ERR_UNSUPPORTED, "tensor-core path: tile does not fit shared memory");
-  const int esize = mode == TC_BF16 ? 2 : 4;
-  const int parts = mode == TC_TF32X3 ? 2 : 1;
+  const int esize = (mode == TC_BF16 || mode == TC_BF16X3) ? 2 : 4;
+  const int parts = (mode == TC_TF32X3 || mode == TC_BF16X3) ? 2 : 1;
   size_t wbytes = (size_t)K * cin * cout * esize * parts;
   unsigned char *wprep = nullptr;
   SCN_TRY(device_alloc((void **)&wprep, wbytes, stream));
@@ -612,6 +618,8 @@ int conv_forward_tc(const float *in, long long n_in, float *out, long long n_out
     SCN_LAUNCH(k_conv_tc<TC_TF32>, grid, kTcThreads, pl.smem, stream, P);
   else if (mode == TC_BF16)
     SCN_LAUNCH(k_conv_tc<TC_BF16>, grid, kTcThreads, pl.smem, stream, P);
+  else if (mode == TC_BF16X3)
+    SCN_LAUNCH(k_conv_tc<TC_BF16X3>, grid, kTcThreads, pl.smem, stream, P);
   else
     SCN_LAUNCH(k_conv_tc<TC_TF32X3>, grid, kTcThreads, pl.smem, stream, P);
   SCN_CUDA_CHECK(cudaGetLastError());
@@ -684,11 +692,12 @@ extern "C" int scn_submanifold_convolution_forward_static(scn_metadata *md, cons
               "filter volume above %d or input matrix not 16-byte aligned", kTcMaxOffsets);
   TcPlan pl;
   SCN_REQUIRE(plan(mode, K, cin, cout, pl), SCN_ERR_UNSUPPORTED, "tile does not fit shared memory");
-  const int esize = mode == TC_BF16 ? 2 : 4;
-  const size_t wbytes = (size_t)K * cin * cout * esize * (mode == TC_TF32X3 ? 2 : 1);
+  const int esize = (mode == TC_BF16 || mode == TC_BF16X3) ? 2 : 4;
+  const int parts = (mode == TC_TF32X3 || mode == TC_BF16X3) ? 2 : 1;
+  const size_t wbytes = (size_t)K * cin * cout * esize * parts;
   SCN_REQUIRE(wbytes <= kStaticWeightBytes, SCN_ERR_UNSUPPORTED,
               "prepared weights need %zu bytes, the built-in buffer holds %zu (filter volume x n_in x n_out x %d)",
-              wbytes, kStaticWeightBytes, esize * (mode == TC_TF32X3 ? 2 : 1));
+              wbytes, kStaticWeightBytes, esize * parts);
   void *image = nullptr;
   SCN_TRY(static_weight_image(&image));
   // the image is rewritten in full for this call's shape; nothing in it has to start at zero
@@ -721,6 +730,8 @@ extern "C" int scn_submanifold_convolution_forward_static(scn_metadata *md, cons
     SCN_LAUNCH(k_conv_tc<TC_TF32>, grid, kTcThreads, pl.smem, stream, P);
   else if (mode == TC_BF16)
     SCN_LAUNCH(k_conv_tc<TC_BF16>, grid, kTcThreads, pl.smem, stream, P);
+  else if (mode == TC_BF16X3)
+    SCN_LAUNCH(k_conv_tc<TC_BF16X3>, grid, kTcThreads, pl.smem, stream, P);
   else
     SCN_LAUNCH(k_conv_tc<TC_TF32X3>, grid, kTcThreads, pl.smem, stream, P);
   SCN_CUDA_CHECK(cudaGetLastError());

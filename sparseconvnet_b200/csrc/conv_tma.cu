@@ -88,11 +88,17 @@ __host__ __device__ inline unsigned instr_desc_tma(bool bf16) {
 template <int MODE, bool TMA_GATHER>
 __global__ void __launch_bounds__(N_WARPS * 32, 1)
 k_conv_tma(const __grid_constant__ CUtensorMap in_map, TmaParams P) {
-  constexpr bool kBf16 = (MODE == TC_BF16);
-  constexpr bool kSplit = (MODE == TC_TF32X3);
+  constexpr bool kBf16 = (MODE == TC_BF16 || MODE == TC_BF16X3);     // bf16 operands, made by the transform warps
+  constexpr bool kSplit = (MODE == TC_TF32X3 || MODE == TC_BF16X3);  // two parts per operand, three products
+  constexpr bool kB3 = (MODE == TC_BF16X3);
   constexpr bool kTransform = kBf16 || kSplit;
   constexpr int kEsize = kBf16 ? 2 : 4;
   constexpr unsigned kAuxBytes = kSplit ? kGBytes : (kBf16 ? kGBytes / 2 : 0);
+  // TC_BF16X3 with the cp.async gather: the tensor core never reads the raw fp32 tile, only the two bf16 tiles
+  // the transform warps make of it, so the producers copy the rows that have a rule and nothing else -- no zero
+  // stores -- and leave a 256-bit mask of those rows with the stage; the transform warps write zeros for the
+  // others without reading them.
+  constexpr bool kMasked = kB3 && !TMA_GATHER;
 
   extern __shared__ __align__(1024) unsigned char smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -156,6 +162,7 @@ k_conv_tma(const __grid_constant__ CUtensorMap in_map, TmaParams P) {
     int *list_idx = list_row + kRows;                     // [256] their input rows
     int *list_miss = list_idx + kRows;                    // [256] tile rows without a rule
     int *warp_cnt = list_miss + kRows;                    // [8]
+    unsigned *hit_mask = reinterpret_cast<unsigned *>(warp_cnt + N_PRODUCER_WARPS);  // [NS][8]
     int st = 0, round = 0;
     bool ok = true;
     auto producer_sync = [] { asm volatile("bar.sync 1, %0;" ::"n"(N_PRODUCER_WARPS * 32) : "memory"); };
@@ -261,9 +268,16 @@ k_conv_tma(const __grid_constant__ CUtensorMap in_map, TmaParams P) {
             cp_async16(smem_u32(g) + (unsigned)r * 128 + ((unsigned)(c ^ (r & 7)) << 4),
                        col + (long long)list_idx[e] * P.ld_in, 16u);
           }
-          for (int e = tid >> 3; e < n_miss; e += N_PRODUCER_WARPS * 4) {
-            const int r = list_miss[e];
-            *reinterpret_cast<uint4 *>(g + (unsigned)r * 128 + ((unsigned)(c ^ (r & 7)) << 4)) = make_uint4(0, 0, 0, 0);
+          if (kMasked) {
+            if (lane == 0) {
+              hit_mask[st * N_PRODUCER_WARPS + warp] = hits;
+              __threadfence_block();  // ordered before this thread's arrival on the stage barrier
+            }
+          } else {
+            for (int e = tid >> 3; e < n_miss; e += N_PRODUCER_WARPS * 4) {
+              const int r = list_miss[e];
+              *reinterpret_cast<uint4 *>(g + (unsigned)r * 128 + ((unsigned)(c ^ (r & 7)) << 4)) = make_uint4(0, 0, 0, 0);
+            }
           }
           close_stage();
         }
@@ -410,9 +424,11 @@ k_conv_tma(const __grid_constant__ CUtensorMap in_map, TmaParams P) {
 #pragma unroll
           for (int jj = 0; jj < n_mma; ++jj) {
             // B operand: gathered rows.  tf32: the swizzled raw tile (32 bytes of K per MMA);
-            // bf16: the converted tile in plain core-matrix layout (4 pieces of 16 bytes per row)
+            // bf16: the converted tile in plain core-matrix layout (4 pieces of 16 bytes per row), in
+            // the three-term form followed by the tile of what the rounding left over
             const unsigned long long dg = kBf16 ? smem_desc(aux_addr + jj * 256, 128, 512) : smem_desc_sw128(g_addr + jj * 32);
-            const unsigned long long dg_lo = smem_desc_sw128(aux_addr + jj * 32);
+            const unsigned long long dg_lo =
+                kB3 ? smem_desc(aux_addr + kGBytes / 2 + jj * 256, 128, 512) : smem_desc_sw128(aux_addr + jj * 32);
             const unsigned acc = (first && jj == 0) ? 0u : 1u;
             for (int mt = 0; mt < n_mt; ++mt) {
               const unsigned d = tmem_base + (unsigned)((ab * n_mt + mt) * kRows);
@@ -460,7 +476,7 @@ k_conv_tma(const __grid_constant__ CUtensorMap in_map, TmaParams P) {
         const bool marker = !TMA_GATHER && (flags & META_LAST_OF_TILE);
         if (marker) {
           // end-of-tile marker slot: nothing to transform
-        } else if (kSplit) {
+        } else if (kSplit && !kB3) {
           // low part in the same (swizzled) position: g_lo = g - trunc_tf32(g)
 #pragma unroll 4
           for (int i = 0; i < kGBytes / 16 / 128; ++i) {
@@ -472,6 +488,30 @@ k_conv_tma(const __grid_constant__ CUtensorMap in_map, TmaParams P) {
             lo.z = a.z - __uint_as_float(__float_as_uint(a.z) & 0xFFFFE000u);
             lo.w = a.w - __uint_as_float(__float_as_uint(a.w) & 0xFFFFE000u);
             *reinterpret_cast<float4 *>(aux + c * 16) = lo;
+          }
+        } else if (kB3) {
+          // fp32 (swizzled rows of 128 bytes) -> two bf16 tiles in plain K-major core-matrix layout
+          // (piece j = 8 planes of row r at (r/8)*512 + j*128 + (r%8)*16): the values rounded to bf16
+          // and, 16 KB further on, what the rounding left over.  Rows without a rule become zeros.
+          const unsigned *mask = reinterpret_cast<const unsigned *>(ctl + 512 + 3 * kRows * 4 + N_PRODUCER_WARPS * 4) +
+                                 st * N_PRODUCER_WARPS;
+#pragma unroll 4
+          for (int i = 0; i < kRows * 4 / 128; ++i) {
+            const int p = t128 + 128 * i;
+            const int r = p >> 2, j = p & 3;
+            uint4 hq = make_uint4(0, 0, 0, 0), mq = make_uint4(0, 0, 0, 0);
+            if (!kMasked || ((mask[r >> 5] >> (r & 31)) & 1u)) {
+              const unsigned char *row = g + r * 128;
+              const float4 x = *reinterpret_cast<const float4 *>(row + (((2 * j) ^ (r & 7)) << 4));
+              const float4 y = *reinterpret_cast<const float4 *>(row + (((2 * j + 1) ^ (r & 7)) << 4));
+              split_bf16_pair(x.x, x.y, hq.x, mq.x);
+              split_bf16_pair(x.z, x.w, hq.y, mq.y);
+              split_bf16_pair(y.x, y.y, hq.z, mq.z);
+              split_bf16_pair(y.z, y.w, hq.w, mq.w);
+            }
+            const unsigned off = (r >> 3) * 512 + j * 128 + (r & 7) * 16;
+            *reinterpret_cast<uint4 *>(aux + off) = hq;
+            *reinterpret_cast<uint4 *>(aux + kGBytes / 2 + off) = mq;
           }
         } else {
           // fp32 (swizzled rows of 128 bytes) -> bf16 tile in plain K-major core-matrix layout:
@@ -557,14 +597,16 @@ static int tma_mode_of(int precision) {
   switch (precision) {
     case SCN_PRECISION_TF32: return TC_TF32;
     case SCN_PRECISION_BF16: return TC_BF16;
-    case SCN_PRECISION_TF32X3: return TC_TF32X3;
+    case SCN_PRECISION_TF32X3: return split_mode_of_env();
     default: return -1;
   }
 }
 
 static size_t tma_stage_bytes(int mode, int cout) {
-  size_t aux = mode == TC_TF32X3 ? kGBytes : (mode == TC_BF16 ? kGBytes / 2 : 0);
-  size_t w = (size_t)cout * kSlice * (mode == TC_BF16 ? 2 : 4) * (mode == TC_TF32X3 ? 2 : 1);
+  const bool two_parts = mode == TC_TF32X3 || mode == TC_BF16X3;
+  const bool bf16 = mode == TC_BF16 || mode == TC_BF16X3;
+  size_t aux = two_parts ? kGBytes : (bf16 ? kGBytes / 2 : 0);
+  size_t w = (size_t)cout * kSlice * (bf16 ? 2 : 4) * (two_parts ? 2 : 1);
   return ((w + 1023) & ~(size_t)1023) + kGBytes + aux;
 }
 constexpr size_t kTmaControlBytes = 4096;  // barriers, step flags, and the producers' row lists
@@ -581,7 +623,7 @@ bool conv_tma_supported(int K, int cin, int cout, int groups, int precision, lon
   // the simpler per-tile kernel.  SCN_TC_PERSISTENT=1 / 0 forces it on / off for every mode.
   const char *e = getenv("SCN_TC_PERSISTENT");
   if (e && atoi(e) == 0) return false;
-  if (!(e && atoi(e) != 0) && mode != TC_TF32X3) return false;
+  if (!(e && atoi(e) != 0) && mode != TC_TF32X3 && mode != TC_BF16X3) return false;
   return (kTmaSmemBudget - kTmaControlBytes) / tma_stage_bytes(mode, cout) >= 2;
 }
 
@@ -622,8 +664,8 @@ int conv_forward_tma(const float *in, long long n_in, float *out, long long n_ou
                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   SCN_REQUIRE(cr == CUDA_SUCCESS, SCN_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)cr);
 
-  const int esize = mode == TC_BF16 ? 2 : 4;
-  const int parts = mode == TC_TF32X3 ? 2 : 1;
+  const int esize = (mode == TC_BF16 || mode == TC_BF16X3) ? 2 : 4;
+  const int parts = (mode == TC_TF32X3 || mode == TC_BF16X3) ? 2 : 1;
   unsigned char *wprep = nullptr;
   SCN_TRY(device_alloc((void **)&wprep, (size_t)K * cin * cout * esize * parts, stream));
   SCN_TRY(prepare_weights(weight, wprep, K, cin, cout, kSlice, mode, stream));
@@ -657,6 +699,8 @@ int conv_forward_tma(const float *in, long long n_in, float *out, long long n_ou
     SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_tma<TC_TF32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, b));
     SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_tma<TC_BF16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, b));
     SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_tma<TC_TF32X3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, b));
+    SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_tma<TC_BF16X3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, b));
+    SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_tma<TC_BF16X3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, b));
   }
   const unsigned grid = (unsigned)std::min<long long>(P.n_tiles, n_sm[dev]);
   // Ask for the whole budget: one CTA per SM by construction (it also owns all 512 TMEM columns)
@@ -668,6 +712,8 @@ int conv_forward_tma(const float *in, long long n_in, float *out, long long n_ou
       SCN_LAUNCH((k_conv_tma<TC_TF32, true>), grid, N_WARPS * 32, smem, stream, map, P);
     else if (mode == TC_BF16)
       SCN_LAUNCH((k_conv_tma<TC_BF16, true>), grid, N_WARPS * 32, smem, stream, map, P);
+    else if (mode == TC_BF16X3)
+      SCN_LAUNCH((k_conv_tma<TC_BF16X3, true>), grid, N_WARPS * 32, smem, stream, map, P);
     else
       SCN_LAUNCH((k_conv_tma<TC_TF32X3, true>), grid, N_WARPS * 32, smem, stream, map, P);
   } else {
@@ -675,6 +721,8 @@ int conv_forward_tma(const float *in, long long n_in, float *out, long long n_ou
       SCN_LAUNCH((k_conv_tma<TC_TF32, false>), grid, N_WARPS * 32, smem, stream, map, P);
     else if (mode == TC_BF16)
       SCN_LAUNCH((k_conv_tma<TC_BF16, false>), grid, N_WARPS * 32, smem, stream, map, P);
+    else if (mode == TC_BF16X3)
+      SCN_LAUNCH((k_conv_tma<TC_BF16X3, false>), grid, N_WARPS * 32, smem, stream, map, P);
     else
       SCN_LAUNCH((k_conv_tma<TC_TF32X3, false>), grid, N_WARPS * 32, smem, stream, map, P);
   }

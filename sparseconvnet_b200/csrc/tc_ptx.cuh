@@ -11,7 +11,13 @@ namespace scn {
 
 constexpr unsigned kWaitLimit = 1u << 20;  // polls before a bounded wait gives up
 
-enum TcMode : int { TC_TF32 = 0, TC_BF16 = 1, TC_TF32X3 = 2 };
+// TC_TF32X3 and TC_BF16X3 are the two forms of the fp32-class mode: x = hi + lo with hi the tf32
+// truncation (three tf32 products, or one tf32 and two bf16 ones), or x = h + m with h = bf16(x),
+// m = bf16(x - h) and the three bf16 products h h, m h, h m (what is left out is 2^-17 of a product).
+enum TcMode : int { TC_TF32 = 0, TC_BF16 = 1, TC_TF32X3 = 2, TC_BF16X3 = 3 };
+
+// which form SCN_PRECISION_TF32X3 runs: the bf16 one unless SCN_X3_FORM=tf32
+int split_mode_of_env();
 
 // W [K][Cin][Cout] fp32 -> per (offset, slice of kc input planes) the shared-memory image of the
 // weight operand (conv_tc.cu)
@@ -121,6 +127,15 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, float *v) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Two floats as a bf16 pair rounded to nearest (`a` in the low half) and the pair of what the
+// rounding left over, again as bf16: the two parts of the three-term bf16 split.
+__device__ __forceinline__ void split_bf16_pair(float a, float b, unsigned &h, unsigned &m) {
+  __nv_bfloat162 hv = __floats2bfloat162_rn(a, b);
+  h = *reinterpret_cast<unsigned *>(&hv);
+  __nv_bfloat162 mv = __floats2bfloat162_rn(a - __uint_as_float(h << 16), b - __uint_as_float(h & 0xFFFF0000u));
+  m = *reinterpret_cast<unsigned *>(&mv);
 }
 
 // Shared-memory matrix descriptor, K-major, no swizzle: 8-row x 16-byte core matrices stored as
