@@ -21,8 +21,11 @@
  *    rulebooks and their cache, exactly the role of the reference's `Metadata<D>`
  *    (sparseconvnet/SCN/Metadata/Metadata.h:44-167).  It is not thread safe, like the
  *    reference object.
- *  - device memory for tables and rulebooks comes from the CUDA stream-ordered allocator
- *    of the current device.
+ *  - device memory for tables, rulebooks and per-call scratch comes from a stream-ordered memory
+ *    pool that the library creates per device (not the device's default pool); freed blocks stay
+ *    in that pool for reuse until scn_trim_memory gives them back to the driver.
+ *  - a scn_metadata belongs to the device that was current at its first use; using it with
+ *    another device current is SCN_ERR_BAD_ARG.  It may be used on one stream at a time.
  */
 #ifndef SCN_B200_H
 #define SCN_B200_H
@@ -70,7 +73,8 @@ enum scn_conv_kernel {
   SCN_KERNEL_CONV_TC = 1,            /* k_conv_tc: tcgen05, one tile per CTA                  */
   SCN_KERNEL_CONV_TC_PERSISTENT = 2, /* k_conv_tma: tcgen05, persistent, double-buffered TMEM */
   SCN_KERNEL_CONV_PIPE_MMA = 3,      /* k_conv_pipe with three tf32 mma.sync passes           */
-  SCN_KERNEL_CONV_ROWS = 4           /* k_conv_rows: row-stationary, three tf32 mma.sync passes */
+  SCN_KERNEL_CONV_ROWS = 4,          /* k_conv_rows: row-stationary, warp-level mma.sync      */
+  SCN_KERNEL_CONV_WIDE = 5           /* k_conv_wide: tcgen05, persistent, bf16 operands split in registers */
 };
 /* The tensor-core modes need groups == 1, n_in_planes % 32 == 0, n_out_planes % 16 == 0 and
  * n_out_planes <= 256; other shapes run the fp32 kernel whatever the precision says. */
@@ -91,12 +95,25 @@ SCN_API long long scn_launch_count(void);
  * object's cache does not count).  No counterpart in the reference; lets a profiler credit the
  * bytes of a rulebook build only to the call that built it. */
 SCN_API long long scn_rulebook_build_count(void);
+/* gives idle blocks of the current device's scratch pool back to the driver, keeping at most
+ * `keep_bytes` reserved (0 = everything idle).  No counterpart in the reference. */
+SCN_API int scn_trim_memory(uint64_t keep_bytes);
+/* bytes the current device's scratch pool holds from the driver, and bytes of them handed out to
+ * live allocations (tables, rulebooks, scratch of calls still in flight).  No counterpart in the
+ * reference. */
+SCN_API int scn_memory_usage(uint64_t *reserved_bytes, uint64_t *used_bytes);
 
 /* ---- Metadata object ------------------------------------------------------------------ */
 
 /* replaces `Metadata_<D>()` (pybind.cpp:12-14, 204-209).  dimension in 1..SCN_MAX_DIMENSION. */
 SCN_API int scn_md_create(int dimension, scn_metadata **md);
+/* Frees the object's device memory stream-ordered BEHIND THE LAST WORK enqueued with the object
+ * (the stream of the most recent call that took it), on the device that owns it whatever device
+ * is current: kernels still reading the tables finish first.  If other streams still read the
+ * tables (the caller made them wait on that work), use scn_md_destroy_on_stream with a stream
+ * that is ordered after all of them. */
 SCN_API int scn_md_destroy(scn_metadata *md);
+SCN_API int scn_md_destroy_on_stream(scn_metadata *md, void *stream);
 /* replaces Metadata<D>::clear (Metadata.cpp:52-66) */
 SCN_API int scn_md_clear(scn_metadata *md, void *stream);
 
@@ -199,6 +216,19 @@ SCN_API int scn_tc_probe_mma(int m, int n, int kind_bf16, int a_in_tmem, int n_m
                              void *stream, double *cycles_issue, double *cycles_total,
                              double *event_ms);
 
+/* Prepared weight images.  The tensor-path kernels read the weights in operand layouts of their own,
+ * made by a small kernel before the convolution (per call: scratch).  A caller whose weights do not
+ * change between calls sets a non-zero token for the calling thread before a convolution call: the
+ * images made during calls under that token are kept (per device, layout and shape) and found again
+ * by later calls under the same token, which then skip the preparation.  The caller chooses tokens so
+ * that one token never stands for two different weight contents (e.g. a counter bumped whenever a
+ * weight tensor is written), sets 0 again for calls that must not use the cache, and releases a token
+ * when its weights change or die (stream-ordered free on `stream`).  An image is built on the stream
+ * of the call that first needed it; calls on other streams must be ordered after that one.
+ * No counterpart in the reference. */
+SCN_API int scn_set_weight_token(uint64_t token);
+SCN_API int scn_release_weight_token(uint64_t token, void *stream);
+
 /* The convolution operators return the reference's multiply-add count (rules x planes in x planes
  * out, CPU/Convolution.cpp:141) through `macs`.  The reference knows the rule totals on the host;
  * here they are counted on the device, and fetching them where the operator is called makes the
@@ -233,6 +263,18 @@ SCN_API int scn_submanifold_convolution_forward(scn_metadata *md, const int64_t 
                                         const float *bias, int n_in_planes, int n_out_planes,
                                         int groups, int precision, void *stream, double *macs);
 
+/* Test hook for the failure path of the tensor-core kernels.  Every wait inside them (on an
+ * mbarrier another role arrives on) is bounded: when it runs out the kernel raises a status bit,
+ * all its roles leave their loops, tensor memory is freed and the kernel returns; the host reads the
+ * status through scn_md_poll_errors as SCN_ERR_CUDA with a message naming the wait.  After this call
+ * the NEXT per-tile tensor-core convolution of the calling thread (k_conv_tc: a level with at most
+ * 148 tiles of 256 rows, precision tf32 / bf16 / tf32x3) leaves out one barrier arrival in one of
+ * its CTAs -- a flag that nothing sets -- so that exactly this path runs: the call itself returns
+ * SCN_OK (the kernel is asynchronous), its output is incomplete, scn_md_poll_errors reports the
+ * expired wait, and the next convolution works again.  Nothing traps, faults or waits without a
+ * bound.  No counterpart in the reference. */
+SCN_API int scn_test_drop_barrier_arrival(void);
+
 /* Allocation-free SubmanifoldConvolution.  No counterpart in the reference.
  *
  * scn_submanifold_convolution_forward takes a temporary buffer for the prepared weight image
@@ -241,12 +283,15 @@ SCN_API int scn_submanifold_convolution_forward(scn_metadata *md, const int64_t 
  * the driver's allocator, a process with a pre-assigned memory budget -- uses this entry point
  * instead: the same tensor-core kernels with the image kept in an 8 MiB array that is part of
  * the library (every GPU that loads the library holds those 8 MiB until the process exits).
- * It calls no cudaMalloc / cudaFree and no allocating library routine.
+ * It makes no device allocation: no cudaMalloc / cudaFree, no memory-pool call, no allocating
+ * library routine on the device side (the host side uses a few hundred bytes of ordinary heap
+ * for the rulebook lookup key).
  *
  *  - precision must be SCN_PRECISION_TF32, _BF16 or _TF32X3, groups == 1, and the shape one the
  *    tensor-core path takes (see scn_precision); anything else is SCN_ERR_UNSUPPORTED.
- *  - limit: filter_volume * n_in_planes * n_out_planes * (4 for tf32, 2 for bf16, 8 for tf32x3)
- *    bytes <= 8 MiB, otherwise SCN_ERR_UNSUPPORTED with the sizes in scn_last_error().
+ *  - limit: filter_volume * n_in_planes * n_out_planes * (4 for tf32, 2 for bf16, 4 for tf32x3 in
+ *    its default form of two bf16 parts, 8 in the form of two tf32 parts that SCN_X3_FORM=tf32
+ *    selects) bytes <= 8 MiB, otherwise SCN_ERR_UNSUPPORTED with the sizes in scn_last_error().
  *  - the rulebook of (spatial_size, filter_size) must already exist
  *    (scn_md_submanifold_rulebook, which does allocate); otherwise SCN_ERR_NO_GRID.
  *  - the first call on each device looks up the array's device address; make that call with
@@ -261,6 +306,36 @@ SCN_API int scn_submanifold_convolution_forward_static(scn_metadata *md, const i
                                                        const float *weight, const float *bias,
                                                        int n_in_planes, int n_out_planes,
                                                        int precision, void *stream);
+
+/* The three convolutions with the eval-mode BatchNormalization (+ leaky ReLU) that FOLLOWS them
+ * applied in the kernel's store: out = act((conv + bias) * bn_scale + bn_shift), act(y) = y > 0 ? y :
+ * y * leakiness -- BatchNormalization_updateOutput's eval branch (sparseconvnet.h:22-26;
+ * CPU/BatchNormalization.cpp:41-61) without a second pass over the activation.  bn_scale / bn_shift
+ * [n_out_planes] come from scn_batchnorm_fold (scale = gamma / sqrt(running_var + eps), shift = beta -
+ * running_mean * scale, rounded like the stand-alone operator, so the fused result has the same bits
+ * as the two calls).  Kernels without a fused store apply the same arithmetic in place afterwards.
+ * The reference has no fused form; its Python runs the two operators one after the other. */
+SCN_API int scn_batchnorm_fold(const float *running_mean, const float *running_var, const float *weight,
+                               const float *bias, double eps, int n_planes, float *scale, float *shift,
+                               void *stream);
+SCN_API int scn_submanifold_convolution_bn_forward(scn_metadata *md, const int64_t *spatial_size,
+                                                   const int64_t *filter_size, const float *in_features,
+                                                   float *out_features, const float *weight, const float *bias,
+                                                   const float *bn_scale, const float *bn_shift, double leakiness,
+                                                   int n_in_planes, int n_out_planes, int groups, int precision,
+                                                   void *stream, double *macs);
+SCN_API int scn_convolution_bn_forward(scn_metadata *md, const int64_t *input_size, const int64_t *output_size,
+                                       const int64_t *filter_size, const int64_t *filter_stride,
+                                       const float *in_features, float *out_features, const float *weight,
+                                       const float *bias, const float *bn_scale, const float *bn_shift,
+                                       double leakiness, int n_in_planes, int n_out_planes, int groups,
+                                       int precision, void *stream, double *macs);
+SCN_API int scn_deconvolution_bn_forward(scn_metadata *md, const int64_t *input_size, const int64_t *output_size,
+                                         const int64_t *filter_size, const int64_t *filter_stride,
+                                         const float *in_features, float *out_features, const float *weight,
+                                         const float *bias, const float *bn_scale, const float *bn_shift,
+                                         double leakiness, int n_in_planes, int n_out_planes, int groups,
+                                         int precision, void *stream, double *macs);
 
 /* replaces Convolution_updateOutput (sparseconvnet.h:87-92; CPU/Convolution.cpp:45-79).
  * out must have the n_active_out rows reported by scn_md_strided_rulebook. */

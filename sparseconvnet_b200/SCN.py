@@ -130,7 +130,7 @@ def _macs_result(m, macs):
 
 
 # scn_last_conv_kernel() -> name (enum scn_conv_kernel of include/scn_b200.h)
-_KERNEL_NAMES = ("k_conv_simt", "k_conv_tc", "k_conv_tma", "k_conv_pipe_mma", "k_conv_rows")
+_KERNEL_NAMES = ("k_conv_simt", "k_conv_tc", "k_conv_tma", "k_conv_pipe_mma", "k_conv_rows", "k_conv_wide")
 
 PRECISION_FP32, PRECISION_TF32, PRECISION_BF16, PRECISION_TF32X3 = 0, 1, 2, 3
 _precision = PRECISION_FP32
@@ -211,6 +211,39 @@ class _timed(object):
         if p is not None and exc[0] is None:
             self.b.record()
             p.records.append((self.kind, self.info, self.a, self.b))
+
+
+_token_counter = [0]
+
+
+def new_weight_token():
+    """A fresh non-zero token for scn_set_weight_token (see include/scn_b200.h)."""
+    _token_counter[0] += 1
+    return _token_counter[0]
+
+
+class weight_token(object):
+    """``with SCN.weight_token(t):`` -- convolution calls inside keep / reuse their prepared weight
+    images under token `t` (0: no caching)."""
+
+    def __init__(self, token):
+        self.token = int(token)
+
+    def __enter__(self):
+        if self.token:
+            lib.scn_set_weight_token(self.token)
+
+    def __exit__(self, *exc):
+        if self.token:
+            lib.scn_set_weight_token(0)
+
+
+def release_weight_token(token):
+    if token and torch is not None and lib is not None:
+        try:
+            lib.scn_release_weight_token(int(token), _stream() if torch.cuda.is_available() else None)
+        except Exception:  # interpreter shutdown: the process's memory goes with it
+            pass
 
 
 def launch_count():
@@ -435,9 +468,33 @@ def _conv_args(input_features, weight, bias):
     return f, w, b, groups, cin, cout
 
 
+def _epilogue_args(epilogue, f, planes):
+    """(scale ptr, shift ptr, leakiness) of an optional fused BatchNorm: `epilogue` = (scale [planes],
+    shift [planes], leakiness) as made by batchnorm_fold."""
+    scale, shift, leak = epilogue
+    for t in (scale, shift):
+        if not t.is_cuda or t.dtype != torch.float32 or t.numel() != planes or t.device != f.device:
+            raise RuntimeError("fused BatchNorm: scale / shift must be CUDA float32 [%d] on %s" % (planes, f.device))
+    return _ptr(scale), _ptr(shift), float(leak)
+
+
+def batchnorm_fold(running_mean, running_var, weight, bias, eps):
+    """scale = weight / sqrt(running_var + eps), shift = bias - running_mean * scale of an eval-mode
+    BatchNormalization (CPU/BatchNormalization.cpp:41-46), computed on the device with the roundings
+    of the stand-alone operator.  Returns (scale, shift)."""
+    c = running_mean.numel()
+    scale, shift = running_mean.new_empty(c), running_mean.new_empty(c)
+    w = _optional(weight, running_mean, "weight")
+    b = _optional(bias, running_mean, "bias")
+    with torch.cuda.device(running_mean.device):
+        check(lib.scn_batchnorm_fold(_ptr(running_mean), _ptr(running_var), _ptr(w), _ptr(b), float(eps), c,
+                                     _ptr(scale), _ptr(shift), _stream()))
+    return scale, shift
+
+
 def SubmanifoldConvolution_updateOutput(inputSize, filterSize, m, input_features, output_features,
-                                        weight, bias):
-    """sparseconvnet.h:101-104."""
+                                        weight, bias, epilogue=None):
+    """sparseconvnet.h:101-104.  `epilogue` (not in the reference): see batchnorm_fold."""
     f, w, b, groups, cin, cout = _conv_args(input_features, weight, bias)
     macs = C.c_double()
     with torch.cuda.device(f.device):
@@ -451,9 +508,16 @@ def SubmanifoldConvolution_updateOutput(inputSize, filterSize, m, input_features
             info["built"] = lib.scn_rulebook_build_count() > builds  # False: served from the cache
         with _timed("conv", dict(op="submanifold", n_in=n, n_out=n, cin=cin, cout=cout, groups=groups,
                                  offsets=w.size(0), precision=_precision)) as info:
-            check(lib.scn_submanifold_convolution_forward(
-                m._h, sizes(inputSize), sizes(filterSize), _ptr(f), _ptr(output_features), _ptr(w), _ptr(b),
-                groups * cin, groups * cout, groups, _precision, _stream(), C.byref(macs)))
+            if epilogue is None:
+                check(lib.scn_submanifold_convolution_forward(
+                    m._h, sizes(inputSize), sizes(filterSize), _ptr(f), _ptr(output_features), _ptr(w), _ptr(b),
+                    groups * cin, groups * cout, groups, _precision, _stream(), C.byref(macs)))
+            else:
+                sc, sh, leak = _epilogue_args(epilogue, f, groups * cout)
+                info["fused_bn"] = True
+                check(lib.scn_submanifold_convolution_bn_forward(
+                    m._h, sizes(inputSize), sizes(filterSize), _ptr(f), _ptr(output_features), _ptr(w), _ptr(b),
+                    sc, sh, leak, groups * cin, groups * cout, groups, _precision, _stream(), C.byref(macs)))
             result = _macs_result(m, macs)
             if Profile.active is not None:
                 info["macs"] = float(result)
@@ -462,8 +526,8 @@ def SubmanifoldConvolution_updateOutput(inputSize, filterSize, m, input_features
 
 
 def Convolution_updateOutput(inputSize, outputSize, filterSize, filterStride, m, input_features,
-                             output_features, weight, bias):
-    """sparseconvnet.h:87-92."""
+                             output_features, weight, bias, epilogue=None):
+    """sparseconvnet.h:87-92.  `epilogue` (not in the reference): see batchnorm_fold."""
     f, w, b, groups, cin, cout = _conv_args(input_features, weight, bias)
     macs = C.c_double()
     n_out = C.c_int64()
@@ -480,10 +544,18 @@ def Convolution_updateOutput(inputSize, outputSize, filterSize, filterStride, m,
         output_features.resize_(n_out.value, groups * cout)
         with _timed("conv", dict(op="strided", n_in=f.size(0), n_out=n_out.value, cin=cin, cout=cout,
                                  groups=groups, offsets=w.size(0), precision=_precision)) as info:
-            check(lib.scn_convolution_forward(
-                m._h, sizes(inputSize), sizes(outputSize), sizes(filterSize), sizes(filterStride), _ptr(f),
-                _ptr(output_features), _ptr(w), _ptr(b), groups * cin, groups * cout, groups, _precision,
-                _stream(), C.byref(macs)))
+            if epilogue is None:
+                check(lib.scn_convolution_forward(
+                    m._h, sizes(inputSize), sizes(outputSize), sizes(filterSize), sizes(filterStride), _ptr(f),
+                    _ptr(output_features), _ptr(w), _ptr(b), groups * cin, groups * cout, groups, _precision,
+                    _stream(), C.byref(macs)))
+            else:
+                sc, sh, leak = _epilogue_args(epilogue, f, groups * cout)
+                info["fused_bn"] = True
+                check(lib.scn_convolution_bn_forward(
+                    m._h, sizes(inputSize), sizes(outputSize), sizes(filterSize), sizes(filterStride), _ptr(f),
+                    _ptr(output_features), _ptr(w), _ptr(b), sc, sh, leak, groups * cin, groups * cout, groups,
+                    _precision, _stream(), C.byref(macs)))
             result = _macs_result(m, macs)
             if Profile.active is not None:
                 info["macs"] = float(result)
@@ -492,8 +564,8 @@ def Convolution_updateOutput(inputSize, outputSize, filterSize, filterStride, m,
 
 
 def Deconvolution_updateOutput(inputSize, outputSize, filterSize, filterStride, m, input_features,
-                               output_features, weight, bias):
-    """sparseconvnet.h:149-154."""
+                               output_features, weight, bias, epilogue=None):
+    """sparseconvnet.h:149-154.  `epilogue` (not in the reference): see batchnorm_fold."""
     f, w, b, groups, cin, cout = _conv_args(input_features, weight, bias)
     macs = C.c_double()
     with torch.cuda.device(f.device):
@@ -507,10 +579,18 @@ def Deconvolution_updateOutput(inputSize, outputSize, filterSize, filterStride, 
         output_features.resize_(n_fine, groups * cout)
         with _timed("conv", dict(op="deconvolution", n_in=f.size(0), n_out=n_fine, cin=cin, cout=cout,
                                  groups=groups, offsets=w.size(0), precision=_precision)) as info:
-            check(lib.scn_deconvolution_forward(
-                m._h, sizes(inputSize), sizes(outputSize), sizes(filterSize), sizes(filterStride), _ptr(f),
-                _ptr(output_features), _ptr(w), _ptr(b), groups * cin, groups * cout, groups, _precision,
-                _stream(), C.byref(macs)))
+            if epilogue is None:
+                check(lib.scn_deconvolution_forward(
+                    m._h, sizes(inputSize), sizes(outputSize), sizes(filterSize), sizes(filterStride), _ptr(f),
+                    _ptr(output_features), _ptr(w), _ptr(b), groups * cin, groups * cout, groups, _precision,
+                    _stream(), C.byref(macs)))
+            else:
+                sc, sh, leak = _epilogue_args(epilogue, f, groups * cout)
+                info["fused_bn"] = True
+                check(lib.scn_deconvolution_bn_forward(
+                    m._h, sizes(inputSize), sizes(outputSize), sizes(filterSize), sizes(filterStride), _ptr(f),
+                    _ptr(output_features), _ptr(w), _ptr(b), sc, sh, leak, groups * cin, groups * cout, groups,
+                    _precision, _stream(), C.byref(macs)))
             result = _macs_result(m, macs)
             if Profile.active is not None:
                 info["macs"] = float(result)

@@ -22,6 +22,9 @@ SIGNATURES = {
     "scn_last_conv_kernel": (C.c_int, []),
     "scn_tc_probe_mma": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp,
                                    C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double)]),
+    "scn_test_drop_barrier_arrival": (C.c_int, []),
+    "scn_set_weight_token": (C.c_int, [C.c_uint64]),
+    "scn_release_weight_token": (C.c_int, [C.c_uint64, _vp]),
     "scn_set_deferred_counts": (C.c_int, [C.c_int]),
     "scn_set_backward_precision": (C.c_int, [C.c_int]),
     "scn_md_take_count_ticket": (C.c_int, [_vp, C.POINTER(_vp)]),
@@ -29,6 +32,9 @@ SIGNATURES = {
     "scn_count_ticket_release": (C.c_int, [_vp]),
     "scn_md_create": (C.c_int, [C.c_int, C.POINTER(_vp)]),
     "scn_md_destroy": (C.c_int, [_vp]),
+    "scn_md_destroy_on_stream": (C.c_int, [_vp, _vp]),
+    "scn_trim_memory": (C.c_int, [C.c_uint64]),
+    "scn_memory_usage": (C.c_int, [C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "scn_md_clear": (C.c_int, [_vp, _vp]),
     "scn_md_input_layer": (C.c_int, [_vp, _i64p, _vp, C.c_int, C.c_int64, C.c_int, C.c_int64,
                                      C.c_int, _vp, _i64p]),
@@ -53,6 +59,16 @@ SIGNATURES = {
     "scn_deconvolution_forward": (C.c_int, [_vp, _i64p, _i64p, _i64p, _i64p, _vp, _vp, _vp, _vp,
                                             C.c_int, C.c_int, C.c_int, C.c_int, _vp,
                                             C.POINTER(C.c_double)]),
+    "scn_batchnorm_fold": (C.c_int, [_vp, _vp, _vp, _vp, C.c_double, C.c_int, _vp, _vp, _vp]),
+    "scn_submanifold_convolution_bn_forward": (C.c_int, [_vp, _i64p, _i64p, _vp, _vp, _vp, _vp, _vp, _vp, C.c_double,
+                                                         C.c_int, C.c_int, C.c_int, C.c_int, _vp,
+                                                         C.POINTER(C.c_double)]),
+    "scn_convolution_bn_forward": (C.c_int, [_vp, _i64p, _i64p, _i64p, _i64p, _vp, _vp, _vp, _vp, _vp, _vp,
+                                             C.c_double, C.c_int, C.c_int, C.c_int, C.c_int, _vp,
+                                             C.POINTER(C.c_double)]),
+    "scn_deconvolution_bn_forward": (C.c_int, [_vp, _i64p, _i64p, _i64p, _i64p, _vp, _vp, _vp, _vp, _vp, _vp,
+                                               C.c_double, C.c_int, C.c_int, C.c_int, C.c_int, _vp,
+                                               C.POINTER(C.c_double)]),
     "scn_submanifold_convolution_backward": (C.c_int, [_vp, _i64p, _i64p, _vp, _vp, _vp, _vp, _vp, _vp,
                                                        C.c_int, C.c_int, C.c_int, _vp]),
     "scn_convolution_backward": (C.c_int, [_vp, _i64p, _i64p, _i64p, _i64p, _vp, _vp, _vp, _vp, _vp, _vp,

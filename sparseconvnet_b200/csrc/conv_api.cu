@@ -2,7 +2,11 @@
 // and cached, like the reference's Metadata), shape checks, kernel choice.
 #include <stdlib.h>
 
+#include <algorithm>
 #include <atomic>
+#include <map>
+#include <mutex>
+#include <tuple>
 
 #include "metadata.cuh"
 #include "tc_ptx.cuh"
@@ -12,13 +16,17 @@ int conv_forward_simt(const float *in, long long n_in, float *out, long long n_o
                       const float *bias, const int *table, int K, int cin, int cout, int groups,
                       int *flags, cudaStream_t stream);
 int conv_forward_tc(const float *in, long long n_in, float *out, long long n_out, const float *weight,
-                    const float *bias, const int *table, int K, int cin, int cout, int precision,
-                    int *flags, cudaStream_t stream);
+                    const float *bias, const float *bn_scale, const float *bn_shift, float leak, const int *table,
+                    int K, int cin, int cout, int precision, int *flags, cudaStream_t stream);
 bool conv_tc_supported(int cin, int cout, int groups, int precision);
 int conv_forward_tma(const float *in, long long n_in, float *out, long long n_out, const float *weight,
                      const float *bias, const int *table, int K, int cin, int cout, int precision, int *flags,
                      cudaStream_t stream);
 bool conv_tma_supported(int K, int cin, int cout, int groups, int precision, long long n_in);
+bool conv_wide_supported(int K, int cin, int cout, int groups, int precision, long long n_in);
+int conv_forward_wide(const float *in, long long n_in, float *out, long long n_out, const float *weight,
+                      const float *bias, const float *bn_scale, const float *bn_shift, float leak, const int *table,
+                      int K, int cin, int cout, int precision, int *flags, cudaStream_t stream);
 bool conv_pipe_supported(const float *in, const float *out, const float *weight, const float *bias, int K, int cin,
                          int cout);
 int conv_forward_pipe(const float *in, long long n_in, float *out, long long n_out, const float *weight,
@@ -28,21 +36,69 @@ int conv_forward_pipe(const float *in, long long n_in, float *out, long long n_o
 bool conv_rows_supported(const float *in, const float *out, const float *weight, const float *bias, int K, int cin,
                          int cout, int groups);
 int conv_forward_rows(const float *in, long long n_in, float *out, long long n_out, const float *weight,
-                      const float *bias, const int *table, int K, int cin, int cout, int precision, int *flags,
-                      cudaStream_t stream);
+                      const float *bias, const float *bn_scale, const float *bn_shift, float leak, const int *table,
+                      int K, int cin, int cout, int precision, int *flags, cudaStream_t stream);
 
 bool conv_rows_thin_supported(const float *out, const float *bias, int cin, int cout, int groups);
 int conv_forward_rows_thin(const float *in, long long n_in, float *out, long long n_out, const float *weight,
-                           const float *bias, const int *table, int K, int cin, int cout, int *flags,
-                           cudaStream_t stream);
+                           const float *bias, const float *bn_scale, const float *bn_shift, float leak,
+                           const int *table, int K, int cin, int cout, int *flags, cudaStream_t stream);
 
 int conv_forward_rows_scatter(const float *in, long long n_in, float *out, long long n_out, const float *weight,
-                              const float *bias, const int *child_of, int K, int cin, int cout, int *flags,
-                              cudaStream_t stream);
+                              const float *bias, const float *bn_scale, const float *bn_shift, float leak,
+                              const int *child_of, int K, int cin, int cout, int *flags, cudaStream_t stream);
 
-int split_mode_of_env() {
+int split_mode_of_env(int dflt) {
   const char *e = getenv("SCN_X3_FORM");
-  return (e && e[0] == 't') ? TC_TF32X3 : TC_BF16X3;
+  if (e && e[0] == 't') return TC_TF32X3;
+  if (e && e[0] == 'b') return TC_BF16X3;
+  return dflt;
+}
+
+// ---- prepared weight images kept under a caller-chosen token ------------------------------------------
+namespace {
+struct WeightKey {
+  int device;
+  unsigned long long token;
+  int kind, K, cin, cout, extra;
+  bool operator<(const WeightKey &o) const {
+    return std::tie(device, token, kind, K, cin, cout, extra) <
+           std::tie(o.device, o.token, o.kind, o.K, o.cin, o.cout, o.extra);
+  }
+};
+std::mutex g_weight_mu;
+std::map<WeightKey, void *> g_weight_images;
+thread_local unsigned long long g_weight_token = 0;
+}  // namespace
+
+int weight_image_get(int kind, int K, int cin, int cout, int extra, size_t bytes, cudaStream_t stream,
+                     WeightImage *img, bool *needs_build) {
+  *needs_build = true;
+  img->cached = false;
+  if (g_weight_token != 0) {
+    int dev = 0;
+    SCN_CUDA_CHECK(cudaGetDevice(&dev));
+    const WeightKey key{dev, g_weight_token, kind, K, cin, cout, extra};
+    std::lock_guard<std::mutex> lock(g_weight_mu);
+    auto it = g_weight_images.find(key);
+    if (it != g_weight_images.end()) {
+      img->ptr = it->second;
+      *needs_build = false;
+    } else {
+      SCN_TRY(device_alloc(&img->ptr, bytes, stream));
+      g_weight_images[key] = img->ptr;
+    }
+    img->cached = true;
+    return SCN_OK;
+  }
+  return device_alloc(&img->ptr, bytes, stream);
+}
+
+int weight_image_put(WeightImage &img, cudaStream_t stream) {
+  if (img.cached || !img.ptr) return SCN_OK;
+  void *p = img.ptr;
+  img.ptr = nullptr;
+  return device_free(p, stream);
 }
 
 static thread_local int g_last_kernel = -1;
@@ -51,9 +107,35 @@ std::atomic<int> g_backward_precision{SCN_PRECISION_FP32};  // arithmetic of the
 
 // Kernel choice for out [rows_out, groups * cout] = bias + sum_k in[table[k][.]] @ W[k]; shared by the
 // forward operators and by the input-gradient pass of the backward ones (same kernels, opposite table).
+// y = y * scale[plane] + shift[plane], then leaky ReLU, in place: the eval-mode BatchNorm behind a
+// convolution whose kernel has no fused epilogue
+__global__ void k_scale_shift_act(float *__restrict__ y, long long n_rows, int planes, const float *__restrict__ scale,
+                                  const float *__restrict__ shift, float leak) {
+  const long long total = n_rows * planes;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % planes);
+    float v = __fadd_rn(__fmul_rn(y[i], scale[c]), shift[c]);
+    v *= (v > 0.f) ? 1.f : leak;
+    y[i] = v;
+  }
+}
+
+// W, x -> scale = gamma / sqrt(var + eps), shift = beta - mean * scale, with the roundings of the
+// stand-alone BatchNorm kernel (CPU/BatchNormalization.cpp:41-46 of the reference)
+__global__ void k_bn_fold(const float *__restrict__ mean, const float *__restrict__ var, const float *__restrict__ gamma,
+                          const float *__restrict__ beta, float eps, int planes, float *__restrict__ scale,
+                          float *__restrict__ shift) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= planes) return;
+  const float w = powf(var[c] + eps, -0.5f) * (gamma ? gamma[c] : 1.f);
+  scale[c] = w;
+  shift[c] = __fadd_rn(__fmul_rn(-mean[c], w), beta ? beta[c] : 0.f);
+}
+
 int conv_forward_dispatch(const float *in, long long rows_in, float *out, long long rows_out, const float *weight,
                           const float *bias, const int *table, int K, int cin, int cout, int groups, int precision,
-                          int *flags, cudaStream_t stream) {
+                          int *flags, cudaStream_t stream, const float *bn_scale, const float *bn_shift, float leak) {
+  bool fused = true;  // did the kernel apply the optional BatchNorm epilogue itself?
   // TF32X3 is the fp32-accuracy mode: each shape runs whichever fp32-class kernel is fastest.
   // With 32 or 64 output planes (and first layers) that is the row-stationary kernel of
   // conv_rows.cu on the warp-level tensor path; other narrow shapes take the pipelined kernel of
@@ -75,37 +157,55 @@ int conv_forward_dispatch(const float *in, long long rows_in, float *out, long l
   // a narrow shape none of the three takes (more than 32 filter offsets, groups ...) goes on to tcgen05
   const bool tensor = precision != SCN_PRECISION_FP32 && !(rows_thin || rows || pipe_mma);
   if (rows_thin) {
-    SCN_TRY(conv_forward_rows_thin(in, rows_in, out, rows_out, weight, bias, table, K, cin, cout,
-                                   flags, stream));
+    SCN_TRY(conv_forward_rows_thin(in, rows_in, out, rows_out, weight, bias, bn_scale, bn_shift, leak, table, K, cin,
+                                   cout, flags, stream));
     g_last_kernel = SCN_KERNEL_CONV_ROWS;
   } else if (rows) {
-    SCN_TRY(conv_forward_rows(in, rows_in, out, rows_out, weight, bias, table, K, cin, cout, precision,
-                              flags, stream));
+    SCN_TRY(conv_forward_rows(in, rows_in, out, rows_out, weight, bias, bn_scale, bn_shift, leak, table, K, cin, cout,
+                              precision, flags, stream));
     g_last_kernel = SCN_KERNEL_CONV_ROWS;
   } else if (pipe_mma) {
     SCN_TRY(conv_forward_pipe(in, rows_in, out, rows_out, weight, bias, table, K, cin, cout, groups, 1,
                               flags, stream));
     g_last_kernel = SCN_KERNEL_CONV_PIPE_MMA;
+    fused = false;
+  } else if (tensor && !few_tiles && conv_wide_supported(K, cin, cout, groups, precision, rows_in)) {
+    SCN_TRY(conv_forward_wide(in, rows_in, out, rows_out, weight, bias, bn_scale, bn_shift, bn_scale ? leak : 1.f, table,
+                              K, cin, cout, precision, flags, stream));
+    g_last_kernel = SCN_KERNEL_CONV_WIDE;
   } else if (tensor && !few_tiles && conv_tma_supported(K, cin, cout, groups, precision, rows_in)) {
     SCN_TRY(conv_forward_tma(in, rows_in, out, rows_out, weight, bias, table, K, cin, cout,
                              precision, flags, stream));
     g_last_kernel = SCN_KERNEL_CONV_TC_PERSISTENT;
+    fused = false;
   } else if (tensor && conv_tc_supported(cin, cout, groups, precision)) {
-    SCN_TRY(conv_forward_tc(in, rows_in, out, rows_out, weight, bias, table, K, cin, cout,
+    SCN_TRY(conv_forward_tc(in, rows_in, out, rows_out, weight, bias, bn_scale, bn_shift, leak, table, K, cin, cout,
                             precision, flags, stream));
     g_last_kernel = SCN_KERNEL_CONV_TC;
   } else {
     SCN_TRY(conv_forward_simt(in, rows_in, out, rows_out, weight, bias, table, K, cin, cout,
                               groups, flags, stream));
     g_last_kernel = SCN_KERNEL_CONV_SIMT;
+    fused = false;
+  }
+  if (bn_scale && !fused && rows_out > 0) {
+    const long long total = rows_out * (long long)cout * groups;
+    SCN_LAUNCH(k_scale_shift_act, (unsigned)std::min<long long>(ceil_div(total, 256), 148 * 16), 256, 0, stream, out,
+               rows_out, cout * groups, bn_scale, bn_shift, leak);
+    SCN_CUDA_CHECK(cudaGetLastError());
   }
   return SCN_OK;
 }
 
 // `disjoint` (only with `transposed`): every output row has exactly one rule (filter = stride).
+// `disjoint` additionally promises that every output row HAS a rule: the caller clears it when the
+// fine grid may hold rows that are in no map (earlier duplicates under input mode 0), whose output
+// the scatter form would leave unwritten while the gather form and the reference give them the bias.
 static int run_conv(scn_metadata *md, Rulebook &rb, bool transposed, const float *in, float *out,
                     const float *weight, const float *bias, int n_in_planes, int n_out_planes, int groups,
-                    int precision, cudaStream_t stream, double *macs, bool disjoint = false) {
+                    int precision, cudaStream_t stream, double *macs, bool disjoint = false,
+                    const float *bn_scale = nullptr, const float *bn_shift = nullptr, float leak = 1.f) {
+  SCN_REQUIRE(!bn_scale == !bn_shift, SCN_ERR_BAD_ARG, "scale and shift of the fused BatchNorm come together");
   SCN_REQUIRE(groups >= 1 && n_in_planes >= 1 && n_out_planes >= 1 && n_in_planes % groups == 0 &&
                   n_out_planes % groups == 0,
               SCN_ERR_BAD_ARG, "planes %d -> %d not divisible into %d groups", n_in_planes, n_out_planes, groups);
@@ -133,12 +233,12 @@ static int run_conv(scn_metadata *md, Rulebook &rb, bool transposed, const float
     }
   }
   if (rows_out > 0 && scatter) {
-    SCN_TRY(conv_forward_rows_scatter(in, rows_in, out, rows_out, weight, bias, rb.nbr, rb.n_offsets, cin, cout,
-                                      md->flags_dev, stream));
+    SCN_TRY(conv_forward_rows_scatter(in, rows_in, out, rows_out, weight, bias, bn_scale, bn_shift, leak, rb.nbr,
+                                      rb.n_offsets, cin, cout, md->flags_dev, stream));
     g_last_kernel = SCN_KERNEL_CONV_ROWS;
   } else if (rows_out > 0) {
     SCN_TRY(conv_forward_dispatch(in, rows_in, out, rows_out, weight, bias, table, rb.n_offsets, cin, cout, groups,
-                                  precision, md->flags_dev, stream));
+                                  precision, md->flags_dev, stream, bn_scale, bn_shift, leak));
   }
   if (macs) {  // the reference's return value: rules x ip x op x groups (CPU/Convolution.cpp:141)
     if (g_deferred_counts.load()) {
@@ -165,6 +265,29 @@ using namespace scn;
 extern "C" {
 
 int scn_last_conv_kernel(void) { return g_last_kernel; }
+
+int scn_set_weight_token(uint64_t token) {
+  g_weight_token = token;
+  return SCN_OK;
+}
+
+int scn_release_weight_token(uint64_t token, void *stream) {
+  if (token == 0) return SCN_OK;
+  int current = -1;
+  cudaGetDevice(&current);
+  std::lock_guard<std::mutex> lock(g_weight_mu);
+  for (auto it = g_weight_images.begin(); it != g_weight_images.end();) {
+    if (it->first.token == token) {
+      if (it->first.device != current) cudaSetDevice(it->first.device);
+      device_free(it->second, it->first.device == current ? (cudaStream_t)stream : nullptr);
+      if (it->first.device != current) cudaSetDevice(current);
+      it = g_weight_images.erase(it);
+    } else {
+      ++it;
+    }
+  }
+  return SCN_OK;
+}
 
 int scn_set_backward_precision(int precision) {
   SCN_REQUIRE(precision >= SCN_PRECISION_FP32 && precision <= SCN_PRECISION_TF32X3, SCN_ERR_BAD_ARG,
@@ -236,7 +359,66 @@ int scn_deconvolution_forward(scn_metadata *md, const int64_t *input_size, const
   SCN_TRY(get_strided_rulebook(md, output_size, input_size, filter_size, filter_stride, stream, &rb));
   bool disjoint = true;  // filter = stride: the children of different coarse sites and offsets never coincide
   for (int d = 0; d < md->dim; ++d) disjoint &= filter_size[d] == filter_stride[d];
+  const Grid *fine = find_grid(md, output_size);
+  disjoint &= fine && !fine->may_have_blank_rows;
   return run_conv(md, *rb, true, in_features, out_features, weight, bias, n_in_planes, n_out_planes,
                   groups, precision, stream, macs, disjoint);
+}
+
+/* ---- convolutions with the eval-mode BatchNorm (+ leaky ReLU) that follows them applied in the store ---- */
+
+int scn_batchnorm_fold(const float *running_mean, const float *running_var, const float *weight, const float *bias,
+                       double eps, int n_planes, float *scale, float *shift, void *stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SCN_REQUIRE(running_mean && running_var && scale && shift && n_planes >= 1, SCN_ERR_BAD_ARG, "null argument");
+  SCN_LAUNCH(k_bn_fold, (unsigned)ceil_div(n_planes, 128), 128, 0, stream, running_mean, running_var, weight, bias,
+             (float)eps, n_planes, scale, shift);
+  SCN_CUDA_CHECK(cudaGetLastError());
+  return SCN_OK;
+}
+
+int scn_submanifold_convolution_bn_forward(scn_metadata *md, const int64_t *spatial_size, const int64_t *filter_size,
+                                           const float *in_features, float *out_features, const float *weight,
+                                           const float *bias, const float *bn_scale, const float *bn_shift,
+                                           double leakiness, int n_in_planes, int n_out_planes, int groups,
+                                           int precision, void *stream_, double *macs) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SCN_REQUIRE(md && spatial_size && filter_size && bn_scale && bn_shift, SCN_ERR_BAD_ARG, "null argument");
+  Rulebook *rb = nullptr;
+  SCN_TRY(get_submanifold_rulebook(md, spatial_size, filter_size, stream, &rb));
+  return run_conv(md, *rb, false, in_features, out_features, weight, bias, n_in_planes, n_out_planes, groups,
+                  precision, stream, macs, false, bn_scale, bn_shift, (float)leakiness);
+}
+
+int scn_convolution_bn_forward(scn_metadata *md, const int64_t *input_size, const int64_t *output_size,
+                               const int64_t *filter_size, const int64_t *filter_stride, const float *in_features,
+                               float *out_features, const float *weight, const float *bias, const float *bn_scale,
+                               const float *bn_shift, double leakiness, int n_in_planes, int n_out_planes, int groups,
+                               int precision, void *stream_, double *macs) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SCN_REQUIRE(md && input_size && output_size && filter_size && filter_stride && bn_scale && bn_shift, SCN_ERR_BAD_ARG,
+              "null argument");
+  Rulebook *rb = nullptr;
+  SCN_TRY(get_strided_rulebook(md, input_size, output_size, filter_size, filter_stride, stream, &rb));
+  return run_conv(md, *rb, false, in_features, out_features, weight, bias, n_in_planes, n_out_planes, groups,
+                  precision, stream, macs, false, bn_scale, bn_shift, (float)leakiness);
+}
+
+int scn_deconvolution_bn_forward(scn_metadata *md, const int64_t *input_size, const int64_t *output_size,
+                                 const int64_t *filter_size, const int64_t *filter_stride, const float *in_features,
+                                 float *out_features, const float *weight, const float *bias, const float *bn_scale,
+                                 const float *bn_shift, double leakiness, int n_in_planes, int n_out_planes,
+                                 int groups, int precision, void *stream_, double *macs) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SCN_REQUIRE(md && input_size && output_size && filter_size && filter_stride && bn_scale && bn_shift, SCN_ERR_BAD_ARG,
+              "null argument");
+  Rulebook *rb = nullptr;
+  SCN_TRY(get_strided_rulebook(md, output_size, input_size, filter_size, filter_stride, stream, &rb));
+  bool disjoint = true;
+  for (int d = 0; d < md->dim; ++d) disjoint &= filter_size[d] == filter_stride[d];
+  const Grid *fine = find_grid(md, output_size);
+  disjoint &= fine && !fine->may_have_blank_rows;
+  return run_conv(md, *rb, true, in_features, out_features, weight, bias, n_in_planes, n_out_planes, groups,
+                  precision, stream, macs, disjoint, bn_scale, bn_shift, (float)leakiness);
 }
 }

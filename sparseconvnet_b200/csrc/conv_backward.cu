@@ -23,7 +23,8 @@ namespace scn {
 extern std::atomic<int> g_backward_precision;
 int conv_forward_dispatch(const float *in, long long rows_in, float *out, long long rows_out, const float *weight,
                           const float *bias, const int *table, int K, int cin, int cout, int groups, int precision,
-                          int *flags, cudaStream_t stream);
+                          int *flags, cudaStream_t stream, const float *bn_scale = nullptr,
+                          const float *bn_shift = nullptr, float leak = 1.f);
 int conv_forward_simt(const float *in, long long n_in, float *out, long long n_out, const float *weight,
                       const float *bias, const int *table, int K, int cin, int cout, int groups, int *flags,
                       cudaStream_t stream);

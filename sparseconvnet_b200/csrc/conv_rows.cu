@@ -34,6 +34,14 @@
 
 namespace scn {
 
+// optional per-plane scale / shift / leaky ReLU applied to a finished output value: the eval-mode
+// BatchNorm (+ activation) that follows the convolution, with the same rounding as the stand-alone
+// kernel (separate multiply and add)
+__device__ __forceinline__ float rows_epilogue(float v, float sc, float sh, float leak) {
+  const float y = __fadd_rn(__fmul_rn(v, sc), sh);
+  return y * (y > 0.f ? 1.f : leak);
+}
+
 constexpr int kRChunk = 32;                    // input planes per step
 constexpr int kRAStride = kRChunk + 4;         // floats; rows g and g + 1 land on different bank quads
 constexpr int kRAStages = 2;                   // per-warp ring of gathered rows (three: slower, fewer warps fit)
@@ -306,6 +314,7 @@ template <int NT, int MODE>
 __global__ void __launch_bounds__(32)
 k_conv_rows(const float *__restrict__ in, int ld_in, long long n_in, float *__restrict__ out, int ld_out,
             long long n_out, const uint4 *__restrict__ img, const float *__restrict__ bias,
+            const float *__restrict__ bn_scale, const float *__restrict__ bn_shift, float leak,
             const int *__restrict__ nbr, int K, int nch, int *flags) {
   constexpr unsigned kFull = 0xffffffffu;
   constexpr int kSlab = (MODE == TC_BF16X3 ? 2 : 4) * NT * 32;  // uint4 per (offset, chunk) slab
@@ -413,6 +422,12 @@ k_conv_rows(const float *__restrict__ in, int ld_in, long long n_in, float *__re
           v.x += b.x;
           v.y += b.y;
         }
+        if (bn_scale) {
+          const float2 sc = __ldg(reinterpret_cast<const float2 *>(bn_scale + nt * 8 + t2));
+          const float2 sh = __ldg(reinterpret_cast<const float2 *>(bn_shift + nt * 8 + t2));
+          v.x = rows_epilogue(v.x, sc.x, sh.x, leak);
+          v.y = rows_epilogue(v.y, sc.y, sh.y, leak);
+        }
         __stcs(reinterpret_cast<float2 *>(dst + nt * 8), v);
       }
     }
@@ -420,8 +435,8 @@ k_conv_rows(const float *__restrict__ in, int ld_in, long long n_in, float *__re
 
 template <int NT, int MODE>
 static int launch_rows(const float *in, int ld_in, long long n_in, float *out, int ld_out, long long n_out,
-                       const uint4 *img, const float *bias, const int *table, int K, int nch, int *flags,
-                       cudaStream_t stream) {
+                       const uint4 *img, const float *bias, const float *bn_scale, const float *bn_shift, float leak,
+                       const int *table, int K, int nch, int *flags, cudaStream_t stream) {
   static bool configured[64] = {false};
   int dev = 0;
   SCN_CUDA_CHECK(cudaGetDevice(&dev));
@@ -438,7 +453,7 @@ static int launch_rows(const float *in, int ld_in, long long n_in, float *out, i
     if (dev < 64) configured[dev] = true;
   }
   SCN_LAUNCH(kernel, (unsigned)ceil_div(n_out, 32LL), 32, smem, stream, in, ld_in, n_in, out, ld_out, n_out, img, bias,
-             table, K, nch, flags);
+             bn_scale, bn_shift, leak, table, K, nch, flags);
   SCN_CUDA_CHECK(cudaGetLastError());
   return SCN_OK;
 }
@@ -471,8 +486,9 @@ __global__ void k_rows_thin_prepare(const float *__restrict__ w, uint2 *__restri
 template <int NT>
 __global__ void __launch_bounds__(128)
 k_conv_rows_thin(const float *__restrict__ in, long long n_in, float *__restrict__ out, long long n_out,
-                 const uint2 *__restrict__ img, const float *__restrict__ bias, const int *__restrict__ nbr,
-                 int K, int cin, int *flags) {
+                 const uint2 *__restrict__ img, const float *__restrict__ bias, const float *__restrict__ bn_scale,
+                 const float *__restrict__ bn_shift, float leak, const int *__restrict__ nbr, int K, int cin,
+                 int *flags) {
   constexpr unsigned kFull = 0xffffffffu;
   constexpr int kGroup = 4;  // offsets in flight
   const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -550,6 +566,12 @@ k_conv_rows_thin(const float *__restrict__ in, long long n_in, float *__restrict
           y.x += b.x;
           y.y += b.y;
         }
+        if (bn_scale) {
+          const float2 sc = __ldg(reinterpret_cast<const float2 *>(bn_scale + nt * 8 + t2));
+          const float2 sh = __ldg(reinterpret_cast<const float2 *>(bn_shift + nt * 8 + t2));
+          y.x = rows_epilogue(y.x, sc.x, sh.x, leak);
+          y.y = rows_epilogue(y.y, sc.y, sh.y, leak);
+        }
         __stcs(reinterpret_cast<float2 *>(dst + nt * 8), y);
       }
     }
@@ -561,22 +583,25 @@ bool conv_rows_thin_supported(const float *out, const float *bias, int cin, int 
 }
 
 int conv_forward_rows_thin(const float *in, long long n_in, float *out, long long n_out, const float *weight,
-                           const float *bias, const int *table, int K, int cin, int cout, int *flags,
-                           cudaStream_t stream) {
+                           const float *bias, const float *bn_scale, const float *bn_shift, float leak,
+                           const int *table, int K, int cin, int cout, int *flags, cudaStream_t stream) {
   if (n_out == 0) return SCN_OK;
-  uint2 *img = nullptr;
   const long long total = (long long)K * (cout / 8) * 32;
-  SCN_TRY(device_alloc((void **)&img, (size_t)total * sizeof(uint2), stream));
-  SCN_LAUNCH(k_rows_thin_prepare, (unsigned)ceil_div(total, 256LL), 256, 0, stream, weight, img, K, cin, cout);
+  WeightImage wi;
+  bool build = true;
+  SCN_TRY(weight_image_get(WIMG_ROWS_THIN, K, cin, cout, 0, (size_t)total * sizeof(uint2), stream, &wi, &build));
+  uint2 *img = (uint2 *)wi.ptr;
+  if (build)
+    SCN_LAUNCH(k_rows_thin_prepare, (unsigned)ceil_div(total, 256LL), 256, 0, stream, weight, img, K, cin, cout);
   const unsigned grid = (unsigned)ceil_div(n_out, 128LL);
   if (cout == 16)
-    SCN_LAUNCH(k_conv_rows_thin<2>, grid, 128, 0, stream, in, n_in, out, n_out, img, bias, table, K, cin, flags);
+    SCN_LAUNCH(k_conv_rows_thin<2>, grid, 128, 0, stream, in, n_in, out, n_out, img, bias, bn_scale, bn_shift, leak, table, K, cin, flags);
   else if (cout == 32)
-    SCN_LAUNCH(k_conv_rows_thin<4>, grid, 128, 0, stream, in, n_in, out, n_out, img, bias, table, K, cin, flags);
+    SCN_LAUNCH(k_conv_rows_thin<4>, grid, 128, 0, stream, in, n_in, out, n_out, img, bias, bn_scale, bn_shift, leak, table, K, cin, flags);
   else
-    SCN_LAUNCH(k_conv_rows_thin<8>, grid, 128, 0, stream, in, n_in, out, n_out, img, bias, table, K, cin, flags);
+    SCN_LAUNCH(k_conv_rows_thin<8>, grid, 128, 0, stream, in, n_in, out, n_out, img, bias, bn_scale, bn_shift, leak, table, K, cin, flags);
   const cudaError_t e = cudaGetLastError();
-  const int rf = device_free(img, stream);
+  const int rf = weight_image_put(wi, stream);
   SCN_CUDA_CHECK(e);
   return rf;
 }
@@ -593,6 +618,7 @@ template <int NT, int MODE>
 __global__ void __launch_bounds__(32)
 k_conv_rows_scatter(const float *__restrict__ in, int ld_in, long long n_in, float *__restrict__ out, int ld_out,
                     long long n_out, const uint4 *__restrict__ img, const float *__restrict__ bias,
+                    const float *__restrict__ bn_scale, const float *__restrict__ bn_shift, float leak,
                     const int *__restrict__ child_of /* [K][n_in] -> output row */, int K, int nch, int *flags) {
   constexpr unsigned kFull = 0xffffffffu;
   constexpr int kSlab = (MODE == TC_BF16X3 ? 2 : 4) * NT * 32;
@@ -668,6 +694,12 @@ k_conv_rows_scatter(const float *__restrict__ in, int ld_in, long long n_in, flo
             v.x += bb.x;
             v.y += bb.y;
           }
+          if (bn_scale) {
+            const float2 sc = __ldg(reinterpret_cast<const float2 *>(bn_scale + nt * 8 + t2));
+            const float2 sh = __ldg(reinterpret_cast<const float2 *>(bn_shift + nt * 8 + t2));
+            v.x = rows_epilogue(v.x, sc.x, sh.x, leak);
+            v.y = rows_epilogue(v.y, sc.y, sh.y, leak);
+          }
           __stcs(reinterpret_cast<float2 *>(dst + nt * 8), v);
         }
       }
@@ -677,21 +709,24 @@ k_conv_rows_scatter(const float *__restrict__ in, int ld_in, long long n_in, flo
 // out [n_out, cout]: row child_of[k][i] = bias + in[i] @ W[k] for every rule; every output row must have exactly
 // one rule (the caller's promise).  Same shapes as conv_forward_rows.
 int conv_forward_rows_scatter(const float *in, long long n_in, float *out, long long n_out, const float *weight,
-                              const float *bias, const int *child_of, int K, int cin, int cout, int *flags,
-                              cudaStream_t stream) {
+                              const float *bias, const float *bn_scale, const float *bn_shift, float leak,
+                              const int *child_of, int K, int cin, int cout, int *flags, cudaStream_t stream) {
   if (n_out == 0 || n_in == 0) return SCN_OK;
   const int nch = cin / kRChunk;
-  uint4 *img = nullptr;
   const long long total = (long long)K * nch * 2 * (cout / 8) * 32;
   const bool b3 = split_mode_of_env() == TC_BF16X3;
-  SCN_TRY(device_alloc((void **)&img, (size_t)total * (b3 ? 1 : 2) * sizeof(uint4), stream));
-  if (b3)
+  WeightImage wi;
+  bool build = true;
+  SCN_TRY(weight_image_get(b3 ? WIMG_ROWS_B3 : WIMG_ROWS, K, cin, cout, 0, (size_t)total * (b3 ? 1 : 2) * sizeof(uint4),
+                           stream, &wi, &build));
+  uint4 *img = (uint4 *)wi.ptr;
+  if (build && b3)
     SCN_LAUNCH(k_rows_prepare_b3, (unsigned)ceil_div(total, 256LL), 256, 0, stream, weight, img, K, cin, cout);
-  else
+  else if (build)
     SCN_LAUNCH(k_rows_prepare, (unsigned)ceil_div(total, 256LL), 256, 0, stream, weight, img, K, cin, cout);
   const unsigned grid = (unsigned)ceil_div(n_in, 32LL);
 #define SCN_SCATTER_CALL(NT, MODE) \
-  SCN_LAUNCH((k_conv_rows_scatter<NT, MODE>), grid, 32, 0, stream, in, cin, n_in, out, cout, n_out, img, bias, child_of, K, nch, flags)
+  SCN_LAUNCH((k_conv_rows_scatter<NT, MODE>), grid, 32, 0, stream, in, cin, n_in, out, cout, n_out, img, bias, bn_scale, bn_shift, leak, child_of, K, nch, flags)
   if (cout == 32) {
     if (b3) SCN_SCATTER_CALL(4, TC_BF16X3); else SCN_SCATTER_CALL(4, TC_TF32X3);
   } else {
@@ -699,7 +734,7 @@ int conv_forward_rows_scatter(const float *in, long long n_in, float *out, long 
   }
 #undef SCN_SCATTER_CALL
   const cudaError_t e = cudaGetLastError();
-  const int rf = device_free(img, stream);
+  const int rf = weight_image_put(wi, stream);
   SCN_CUDA_CHECK(e);
   return rf;
 }
@@ -708,25 +743,30 @@ bool conv_rows_supported(const float *in, const float *out, const float *weight,
                          int cout, int groups) {
   return groups == 1 && K <= kRMaxK && cin % kRChunk == 0 && (cout == 32 || cout == 64) &&
          (uintptr_t)in % 16 == 0 && (uintptr_t)out % 8 == 0 && (uintptr_t)bias % 8 == 0 && (uintptr_t)weight % 4 == 0;
+  // (the optional scale / shift vectors of the fused BatchNorm are this library's own allocations: aligned)
 }
 
 // out [n_out, cout] = bias + sum_k in[table[k][.]] @ W[k]; precision: SCN_PRECISION_TF32X3 (fp32-class accuracy),
 // SCN_PRECISION_TF32 or SCN_PRECISION_BF16 (single pass)
 int conv_forward_rows(const float *in, long long n_in, float *out, long long n_out, const float *weight,
-                      const float *bias, const int *table, int K, int cin, int cout, int precision, int *flags,
-                      cudaStream_t stream) {
+                      const float *bias, const float *bn_scale, const float *bn_shift, float leak, const int *table,
+                      int K, int cin, int cout, int precision, int *flags, cudaStream_t stream) {
   if (n_out == 0) return SCN_OK;
   const int nch = cin / kRChunk;
-  uint4 *img = nullptr;
   const long long total = (long long)K * nch * 4 * (cout / 8) * 32;
   const bool b3 = precision == SCN_PRECISION_TF32X3 && split_mode_of_env() == TC_BF16X3;
-  SCN_TRY(device_alloc((void **)&img, (size_t)total * sizeof(uint4), stream));
-  if (b3)
+  WeightImage wi;
+  bool build = true;
+  SCN_TRY(weight_image_get(b3 ? WIMG_ROWS_B3 : WIMG_ROWS, K, cin, cout, 0, (size_t)total / (b3 ? 2 : 1) * sizeof(uint4),
+                           stream, &wi, &build));
+  uint4 *img = (uint4 *)wi.ptr;
+  if (build && b3)
     SCN_LAUNCH(k_rows_prepare_b3, (unsigned)ceil_div(total / 2, 256LL), 256, 0, stream, weight, img, K, cin, cout);
-  else
+  else if (build)
     SCN_LAUNCH(k_rows_prepare, (unsigned)ceil_div(total / 2, 256LL), 256, 0, stream, weight, img, K, cin, cout);
   int rc;
-#define SCN_ROWS_CALL(NT, MODE) launch_rows<NT, MODE>(in, cin, n_in, out, cout, n_out, img, bias, table, K, nch, flags, stream)
+#define SCN_ROWS_CALL(NT, MODE) \
+  launch_rows<NT, MODE>(in, cin, n_in, out, cout, n_out, img, bias, bn_scale, bn_shift, leak, table, K, nch, flags, stream)
   if (precision == SCN_PRECISION_BF16)
     rc = cout == 32 ? SCN_ROWS_CALL(4, TC_BF16) : SCN_ROWS_CALL(8, TC_BF16);
   else if (precision == SCN_PRECISION_TF32)
@@ -736,7 +776,7 @@ int conv_forward_rows(const float *in, long long n_in, float *out, long long n_o
   else
     rc = cout == 32 ? SCN_ROWS_CALL(4, TC_TF32X3) : SCN_ROWS_CALL(8, TC_TF32X3);
 #undef SCN_ROWS_CALL
-  const int rf = device_free(img, stream);
+  const int rf = weight_image_put(wi, stream);
   return rc != SCN_OK ? rc : rf;
 }
 

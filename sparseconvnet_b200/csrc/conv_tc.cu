@@ -114,6 +114,8 @@ struct TcParams {
   int ld_out;
   const unsigned char *wprep;
   const float *bias;
+  const float *bn_scale, *bn_shift;  // optional fused eval-mode BatchNorm: out = act((acc + bias) * scale + shift)
+  float leak;                        // act(y) = y > 0 ? y : y * leak (1 = identity)
   const int *nbr;  // [K][n_out]
   int K, cin, cout;
   int kc;          // input planes per step (32 or 16)
@@ -123,6 +125,7 @@ struct TcParams {
   int n_split;     // CTAs per tile (grid.y): each takes a contiguous range of the filter offsets
   float *partial;  // [n_split][n_out][cout] partial sums when n_split > 1 (k_sum_partials adds them up)
   int *flags;
+  int drop_arrival;  // test hook (scn_test_drop_barrier_arrival): CTA 0 leaves out one arrival on full_g[0]
 };
 
 __device__ __forceinline__ void cp_async_wait_dyn(int n) {
@@ -331,7 +334,9 @@ __global__ void __launch_bounds__(kTcThreads) k_conv_tc(TcParams P) {
         // No proxy fence here: with copies of later steps still in flight it would wait for all
         // of them and serialise the gather.  The consumer fences after it has acquired the barrier.
         __syncwarp();
-        if (lane == 0) mbar_arrive(&full_g[st_c]);  // one arrival per warp (release)
+        // (test hook: one warp of CTA 0 never reports its first step, so the MMA thread's bounded wait runs out)
+        const bool dropped = P.drop_arrival && blockIdx.x == 0 && blockIdx.y == 0 && warp == 0 && s == L;
+        if (lane == 0 && !dropped) mbar_arrive(&full_g[st_c]);  // one arrival per warp (release)
         if (++st_c == NS) st_c = 0;
       }
     }
@@ -356,6 +361,10 @@ __global__ void __launch_bounds__(kTcThreads) k_conv_tc(TcParams P) {
         const int plane = plane0 + lane;
         const bool plane_ok = plane < P.cout;
         const float b = (bias_base && plane_ok) ? bias_base[plane] : 0.f;
+        // the fused BatchNorm belongs to the finished sum: with split offsets k_sum_partials applies it
+        const bool epi = P.bn_scale && !P.partial && plane_ok;
+        const float sc = epi ? P.bn_scale[plane] : 1.f, sh = epi ? P.bn_shift[plane] : 0.f;
+        const float leak = epi ? P.leak : 1.f;
         for (int n0 = (warp >> 2) * 16; n0 < kTcRows; n0 += 32) {
           if (row0 + n0 >= P.n_out) break;
           float v[16];
@@ -369,7 +378,14 @@ __global__ void __launch_bounds__(kTcThreads) k_conv_tc(TcParams P) {
             float *dst = out_base + (row0 + n0) * P.ld_out + plane;
 #pragma unroll
             for (int i = 0; i < 16; ++i)
-              if (row0 + n0 + i < P.n_out) dst[(long long)i * P.ld_out] = v[i] + b;
+              if (row0 + n0 + i < P.n_out) {
+                float y = v[i] + b;
+                if (epi) {
+                  y = __fadd_rn(__fmul_rn(y, sc), sh);
+                  y *= (y > 0.f) ? 1.f : leak;
+                }
+                dst[(long long)i * P.ld_out] = y;
+              }
           }
         }
       }
@@ -451,11 +467,12 @@ __global__ void __launch_bounds__(kTcThreads) k_conv_tc(TcParams P) {
 // out[i] = bias[i % cout] + sum over s of partial[s][i], in the fixed order s = 0, 1, ...: the result
 // does not depend on which CTA finished first.
 __global__ void k_sum_partials(const float4 *__restrict__ partial, int n_split, long long n4, const float *__restrict__ bias,
+                               const float *__restrict__ bn_scale, const float *__restrict__ bn_shift, float leak,
                                int cout, float4 *__restrict__ out) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n4) return;
+  const int plane = (int)((i * 4) % cout);
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (bias) acc = __ldg(reinterpret_cast<const float4 *>(bias + (int)((i * 4) % cout)));
   for (int s = 0; s < n_split; ++s) {
     const float4 v = partial[(long long)s * n4 + i];
     acc.x += v.x;
@@ -463,12 +480,34 @@ __global__ void k_sum_partials(const float4 *__restrict__ partial, int n_split, 
     acc.z += v.z;
     acc.w += v.w;
   }
+  if (bias) {  // added last, as the unsplit kernel adds it to the finished sum
+    const float4 b = __ldg(reinterpret_cast<const float4 *>(bias + plane));
+    acc.x += b.x;
+    acc.y += b.y;
+    acc.z += b.z;
+    acc.w += b.w;
+  }
+  if (bn_scale) {
+    const float4 sc = __ldg(reinterpret_cast<const float4 *>(bn_scale + plane));
+    const float4 sh = __ldg(reinterpret_cast<const float4 *>(bn_shift + plane));
+    acc.x = __fadd_rn(__fmul_rn(acc.x, sc.x), sh.x);
+    acc.y = __fadd_rn(__fmul_rn(acc.y, sc.y), sh.y);
+    acc.z = __fadd_rn(__fmul_rn(acc.z, sc.z), sh.z);
+    acc.w = __fadd_rn(__fmul_rn(acc.w, sc.w), sh.w);
+    acc.x *= (acc.x > 0.f) ? 1.f : leak;
+    acc.y *= (acc.y > 0.f) ? 1.f : leak;
+    acc.z *= (acc.z > 0.f) ? 1.f : leak;
+    acc.w *= (acc.w > 0.f) ? 1.f : leak;
+  }
   out[i] = acc;
 }
 
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
+// set by scn_test_drop_barrier_arrival, consumed by the next conv_forward_tc of the calling thread
+static thread_local int g_drop_arrival = 0;
+
 static int tc_mode_of(int precision) {
   switch (precision) {
     case SCN_PRECISION_TF32: return TC_TF32;
@@ -574,8 +613,8 @@ static int configure_tc_kernels() {
 }
 
 int conv_forward_tc(const float *in, long long n_in, float *out, long long n_out, const float *weight,
-                    const float *bias, const int *table, int K, int cin, int cout, int precision, int *flags,
-                    cudaStream_t stream) {
+                    const float *bias, const float *bn_scale, const float *bn_shift, float leak, const int *table,
+                    int K, int cin, int cout, int precision, int *flags, cudaStream_t stream) {
   if (n_out == 0) return SCN_OK;
   int mode = tc_mode_of(precision);
   SCN_REQUIRE(mode >= 0 && K <= kTcMaxOffsets, SCN_ERR_UNSUPPORTED, "tensor-core path: unsupported precision/filter");
@@ -585,10 +624,13 @@ int conv_forward_tc(const float *in, long long n_in, float *out, long long n_out
   const int esize = (mode == TC_BF16 || mode == TC_BF16X3) ? 2 : 4;
   const int parts = (mode == TC_TF32X3 || mode == TC_BF16X3) ? 2 : 1;
   size_t wbytes = (size_t)K * cin * cout * esize * parts;
-  unsigned char *wprep = nullptr;
-  SCN_TRY(device_alloc((void **)&wprep, wbytes, stream));
+  WeightImage wi;
+  bool build = true;
+  SCN_TRY(weight_image_get(WIMG_TC, K, cin, cout, pl.kc * 16 + mode, wbytes, stream, &wi, &build));
+  unsigned char *wprep = (unsigned char *)wi.ptr;
   long long total = (long long)K * cin * cout;
-  SCN_LAUNCH(k_prepare_weights, (unsigned)ceil_div(total, 256), 256, 0, stream, weight, wprep, K, cin, cout, pl.kc, mode);
+  if (build)
+    SCN_LAUNCH(k_prepare_weights, (unsigned)ceil_div(total, 256), 256, 0, stream, weight, wprep, K, cin, cout, pl.kc, mode);
 
   TcParams P;
   P.in = in;
@@ -599,6 +641,9 @@ int conv_forward_tc(const float *in, long long n_in, float *out, long long n_out
   P.ld_out = cout;
   P.wprep = wprep;
   P.bias = bias;
+  P.bn_scale = bn_scale;
+  P.bn_shift = bn_shift;
+  P.leak = leak;
   P.nbr = table;
   P.K = K;
   P.cin = cin;
@@ -608,6 +653,8 @@ int conv_forward_tc(const float *in, long long n_in, float *out, long long n_out
   P.lookahead = pl.lookahead;
   P.tmem_cols = kTcRows * (int)ceil_div(cout, kTcPlanes);
   P.flags = flags;
+  P.drop_arrival = g_drop_arrival;
+  g_drop_arrival = 0;
   const bool vec_ok = (uintptr_t)out % 16 == 0 && (uintptr_t)bias % 16 == 0;  // k_sum_partials moves float4
   P.n_split = vec_ok ? split_factor(n_out, K, cout) : 1;
   P.partial = nullptr;
@@ -625,11 +672,11 @@ int conv_forward_tc(const float *in, long long n_in, float *out, long long n_out
   SCN_CUDA_CHECK(cudaGetLastError());
   if (P.n_split > 1) {
     const long long n4 = n_out * cout / 4;  // cout is a multiple of 8
-    SCN_LAUNCH(k_sum_partials, (unsigned)ceil_div(n4, 256), 256, 0, stream, reinterpret_cast<const float4 *>(P.partial), P.n_split, n4, bias, cout, reinterpret_cast<float4 *>(out));
+    SCN_LAUNCH(k_sum_partials, (unsigned)ceil_div(n4, 256), 256, 0, stream, reinterpret_cast<const float4 *>(P.partial), P.n_split, n4, bias, bn_scale, bn_shift, leak, cout, reinterpret_cast<float4 *>(out));
     SCN_CUDA_CHECK(cudaGetLastError());
     SCN_TRY(device_free(P.partial, stream));
   }
-  SCN_TRY(device_free(wprep, stream));
+  SCN_TRY(weight_image_put(wi, stream));
   return SCN_OK;
 }
 
@@ -665,6 +712,11 @@ static int static_weight_image(void **ptr) {
 }
 
 }  // namespace scn
+
+extern "C" int scn_test_drop_barrier_arrival(void) {
+  scn::g_drop_arrival = 1;
+  return SCN_OK;
+}
 
 extern "C" int scn_submanifold_convolution_forward_static(scn_metadata *md, const int64_t *spatial_size,
                                                           const int64_t *filter_size, const float *in_features,
@@ -713,6 +765,8 @@ extern "C" int scn_submanifold_convolution_forward_static(scn_metadata *md, cons
   P.ld_out = cout;
   P.wprep = (const unsigned char *)image;
   P.bias = bias;
+  P.bn_scale = P.bn_shift = nullptr;
+  P.leak = 1.f;
   P.nbr = rb.nbr;
   P.K = K;
   P.cin = cin;
@@ -724,6 +778,7 @@ extern "C" int scn_submanifold_convolution_forward_static(scn_metadata *md, cons
   P.n_split = 1;  // splitting needs scratch for the partial sums
   P.partial = nullptr;
   P.flags = md->flags_dev;
+  P.drop_arrival = 0;
   const unsigned grid = (unsigned)ceil_div(rb.n_out, kTcRows);
   SCN_TRY(configure_tc_kernels());  // attribute calls: no allocation
   if (mode == TC_TF32)

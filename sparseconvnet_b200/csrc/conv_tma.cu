@@ -666,9 +666,12 @@ int conv_forward_tma(const float *in, long long n_in, float *out, long long n_ou
 
   const int esize = (mode == TC_BF16 || mode == TC_BF16X3) ? 2 : 4;
   const int parts = (mode == TC_TF32X3 || mode == TC_BF16X3) ? 2 : 1;
-  unsigned char *wprep = nullptr;
-  SCN_TRY(device_alloc((void **)&wprep, (size_t)K * cin * cout * esize * parts, stream));
-  SCN_TRY(prepare_weights(weight, wprep, K, cin, cout, kSlice, mode, stream));
+  WeightImage wi;
+  bool build = true;
+  SCN_TRY(weight_image_get(WIMG_TC, K, cin, cout, kSlice * 16 + mode, (size_t)K * cin * cout * esize * parts, stream, &wi,
+                           &build));
+  unsigned char *wprep = (unsigned char *)wi.ptr;
+  if (build) SCN_TRY(prepare_weights(weight, wprep, K, cin, cout, kSlice, mode, stream));
 
   TmaParams P;
   P.in = in;
@@ -691,7 +694,8 @@ int conv_forward_tma(const float *in, long long n_in, float *out, long long n_ou
   SCN_CUDA_CHECK(cudaGetDevice(&dev));
   SCN_REQUIRE(dev >= 0 && dev < 64, SCN_ERR_UNSUPPORTED, "device index %d unsupported", dev);
   if (!n_sm[dev]) {
-    SCN_CUDA_CHECK(cudaDeviceGetAttribute(&n_sm[dev], cudaDevAttrMultiProcessorCount, dev));
+    int sms = 0;
+    SCN_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     const int b = (int)kTmaSmemBudget;
     SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_tma<TC_TF32, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, b));
     SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_tma<TC_BF16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, b));
@@ -701,6 +705,7 @@ int conv_forward_tma(const float *in, long long n_in, float *out, long long n_ou
     SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_tma<TC_TF32X3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, b));
     SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_tma<TC_BF16X3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, b));
     SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_tma<TC_BF16X3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, b));
+    n_sm[dev] = sms;  // only now: a failed attribute call is retried by the next call
   }
   const unsigned grid = (unsigned)std::min<long long>(P.n_tiles, n_sm[dev]);
   // Ask for the whole budget: one CTA per SM by construction (it also owns all 512 TMEM columns)
@@ -727,7 +732,7 @@ int conv_forward_tma(const float *in, long long n_in, float *out, long long n_ou
       SCN_LAUNCH((k_conv_tma<TC_TF32X3, false>), grid, N_WARPS * 32, smem, stream, map, P);
   }
   SCN_CUDA_CHECK(cudaGetLastError());
-  SCN_TRY(device_free(wprep, stream));
+  SCN_TRY(weight_image_put(wi, stream));
   return SCN_OK;
 }
 

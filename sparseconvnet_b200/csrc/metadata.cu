@@ -52,6 +52,16 @@ std::vector<int64_t> make_key(int dim, const int64_t *a, const int64_t *b, const
   return k;
 }
 
+int md_touch(scn_metadata *md, cudaStream_t stream) {
+  int dev = 0;
+  SCN_CUDA_CHECK(cudaGetDevice(&dev));
+  if (md->device < 0) md->device = dev;
+  SCN_REQUIRE(md->device == dev, SCN_ERR_BAD_ARG, "metadata object lives on device %d, current device is %d",
+              md->device, dev);
+  md->last_stream = stream;
+  return SCN_OK;
+}
+
 Grid *find_grid(scn_metadata *md, const int64_t *spatial_size) {
   auto it = md->grids.find(make_key(md->dim, spatial_size));
   return it == md->grids.end() ? nullptr : &it->second;
@@ -361,15 +371,14 @@ static int md_input_layer(scn_metadata *md, const int64_t *spatial_size, const i
               "coords must have %d or %d columns, got %d", md->dim, md->dim + 1, ncols);
   SCN_REQUIRE(n >= 0 && n < (1ll << 30), SCN_ERR_UNSUPPORTED, "row count %lld unsupported", (long long)n);
   SCN_REQUIRE(n == 0 || coords, SCN_ERR_BAD_ARG, "null coords");
+  SCN_TRY(md_touch(md, stream));
   SCN_TRY(ensure_scratch(md, stream));
 
+  // A new input replaces everything the object knew: grids of other scales and rulebooks built from
+  // the old input would otherwise stay cached with the old row counts.  (The reference asserts that
+  // the object is empty, IOLayersRules.h:22-24.)
+  SCN_TRY(md_clear(md, stream));
   auto key = make_key(md->dim, spatial_size);
-  auto old = md->grids.find(key);
-  if (old != md->grids.end()) {
-    free_grid(old->second, stream);
-    md->grids.erase(old);
-  }
-  clear_input_rules(md, stream);
 
   Grid g;
   SCN_TRY(make_layout(md->dim, spatial_size, g.layout));
@@ -435,6 +444,7 @@ static int md_input_layer(scn_metadata *md, const int64_t *spatial_size, const i
     return st;
   }
   g.n_active = active;
+  g.may_have_blank_rows = (mode == 0);
   // batch size: IOLayersRules.h:25,35,52-53 -- one sample when there is no batch column,
   // otherwise max(requested, largest index + 1)
   if (bl_length > 0)
@@ -550,6 +560,7 @@ k_submanifold_rules(KeyLayout L, HashTable T, const unsigned long long *__restri
 
 int get_submanifold_rulebook(scn_metadata *md, const int64_t *spatial_size,
                              const int64_t *filter_size, cudaStream_t stream, Rulebook **out) {
+  SCN_TRY(md_touch(md, stream));
   auto key = make_key(md->dim, spatial_size, filter_size);
   Rulebook &rb = md->sub_rules[key];
   *out = &rb;
@@ -684,6 +695,7 @@ __global__ void k_strided_fill(KeyLayout Lin, FilterDesc F, const Slot *__restri
 int get_strided_rulebook(scn_metadata *md, const int64_t *input_size, const int64_t *output_size,
                          const int64_t *filter_size, const int64_t *filter_stride,
                          cudaStream_t stream, Rulebook **out) {
+  SCN_TRY(md_touch(md, stream));
   auto key = make_key(md->dim, input_size, filter_size, filter_stride);
   Rulebook &rb = md->strided_rules[key];
   *out = &rb;
@@ -853,14 +865,24 @@ static int count_ticket_start(Rulebook &rb, cudaStream_t stream) {
     count_ticket_release(t);
     SCN_REQUIRE(false, SCN_ERR_CUDA, "event creation failed");
   }
-  rb.ticket = t;
   // posted by a kernel into mapped host memory, not copied: a copy on this stream would hold the stream's next
   // kernels until the copy engine has finished whatever the application is copying (see the mailboxes above)
   unsigned long long *host_dev = nullptr;
-  SCN_CUDA_CHECK(cudaHostGetDevicePointer((void **)&host_dev, t->host, 0));
-  SCN_LAUNCH(k_post_counts, 1, 256, 0, stream, rb.counts_dev, host_dev, rb.n_offsets);
-  SCN_CUDA_CHECK(cudaGetLastError());
-  SCN_CUDA_CHECK(cudaEventRecord(t->event, stream));
+  cudaError_t e = cudaHostGetDevicePointer((void **)&host_dev, t->host, 0);
+  if (e == cudaSuccess) {
+    SCN_LAUNCH(k_post_counts, 1, 256, 0, stream, rb.counts_dev, host_dev, rb.n_offsets);
+    e = cudaGetLastError();
+  }
+  if (e == cudaSuccess) e = cudaEventRecord(t->event, stream);
+  if (e != cudaSuccess) {
+    // the rulebook gets the ticket only once its event has been recorded: a later wait on a
+    // never-recorded event would return at once and sum whatever the chunk held
+    cudaEventDestroy(t->event);  // possibly half-recorded: not returned to the pool
+    t->event = nullptr;
+    count_ticket_release(t);
+    SCN_CUDA_CHECK(e);
+  }
+  rb.ticket = t;
   return SCN_OK;
 }
 
@@ -1011,18 +1033,31 @@ int scn_md_clear(scn_metadata *md, void *stream) {
   return md_clear(md, (cudaStream_t)stream);
 }
 
-int scn_md_destroy(scn_metadata *md) {
+static int md_destroy_on(scn_metadata *md, cudaStream_t stream) {
   if (!md) return SCN_OK;
+  // free on the device that owns the tables, whatever device is current
+  int current = -1;
+  const bool switch_device = md->device >= 0 && cudaGetDevice(&current) == cudaSuccess && current != md->device;
+  if (switch_device) cudaSetDevice(md->device);
   mailbox_release(md->mailbox);
   md->mailbox = nullptr;
   count_ticket_release(md->last_ticket);
   md->last_ticket = nullptr;
-  md_clear(md, 0);
-  device_free(md->flags_dev, 0);
-  device_free(md->scalars_dev, 0);
+  md_clear(md, stream);
+  device_free(md->flags_dev, stream);
+  device_free(md->scalars_dev, stream);
   delete md;
+  if (switch_device) cudaSetDevice(current);
   return SCN_OK;
 }
+
+int scn_md_destroy(scn_metadata *md) {
+  // stream-ordered frees behind the last work enqueued on the object: kernels of that stream that
+  // still read the tables finish before the memory can be handed out again
+  return md_destroy_on(md, md ? md->last_stream : nullptr);
+}
+
+int scn_md_destroy_on_stream(scn_metadata *md, void *stream) { return md_destroy_on(md, (cudaStream_t)stream); }
 
 int scn_md_input_layer(scn_metadata *md, const int64_t *spatial_size, const int64_t *coords,
                        int coords_on_device, int64_t n_rows, int n_cols, int64_t batch_size,
@@ -1049,6 +1084,7 @@ int scn_md_bl_input_layer(scn_metadata *md, const int64_t *spatial_size, const i
 int scn_md_poll_errors(scn_metadata *md, void *stream) {
   SCN_REQUIRE(md, SCN_ERR_BAD_ARG, "null metadata");
   if (!md->flags_dev) return SCN_OK;
+  SCN_TRY(md_touch(md, (cudaStream_t)stream));
   int flags = 0;
   SCN_TRY(fetch_flags(md, (cudaStream_t)stream, &flags, nullptr));
   return flags_to_status(flags);
@@ -1076,6 +1112,7 @@ int scn_md_spatial_locations(scn_metadata *md, const int64_t *spatial_size, int6
   SCN_REQUIRE(g, SCN_ERR_NO_GRID, "no grid for that spatial size");
   if (g->n_active == 0) return SCN_OK;
   SCN_REQUIRE(out_dev, SCN_ERR_BAD_ARG, "null output");
+  SCN_TRY(md_touch(md, (cudaStream_t)stream));
   SCN_LAUNCH(k_spatial_locations, (unsigned)ceil_div(g->n_active, 256), 256, 0, (cudaStream_t)stream, g->layout, g->row_keys, g->n_active, (long long *)out_dev);
   SCN_CUDA_CHECK(cudaGetLastError());
   return SCN_OK;

@@ -15,6 +15,7 @@ struct Grid {
   KeyLayout layout{};
   long long n_active = 0;
   long long batch_size = 0;
+  bool may_have_blank_rows = false;  // input mode 0: rows whose site a later row took over are in no map
   unsigned long long *row_keys = nullptr;  // [n_active] packed key of every feature row
   HashTable table{};                       // key -> row
 };
@@ -64,6 +65,11 @@ int rulebook_transposed(Rulebook &rb, cudaStream_t stream);     // builds tnbr i
 
 struct scn_metadata {
   int dim = 0;
+  // Where the tables live and what last touched them: every entry point that takes the object and
+  // a stream notes both (scn::md_touch), so that destroying the object can free on the device that
+  // owns the memory and, stream-ordered, behind the last work that reads it.
+  int device = -1;
+  cudaStream_t last_stream = nullptr;
   std::map<std::vector<int64_t>, scn::Grid> grids;             // key: spatial size
   std::map<std::vector<int64_t>, scn::Rulebook> sub_rules;      // key: size | filter
   std::map<std::vector<int64_t>, scn::Rulebook> strided_rules;  // key: in size | filter | stride
@@ -83,6 +89,9 @@ struct scn_metadata {
 };
 
 namespace scn {
+// notes the device (first call) and the stream of an operation on `md`; SCN_ERR_BAD_ARG when the
+// object is used from another device than the one that holds its tables
+int md_touch(scn_metadata *md, cudaStream_t stream);
 std::vector<int64_t> make_key(int dim, const int64_t *a, const int64_t *b = nullptr,
                               const int64_t *c = nullptr);
 Grid *find_grid(scn_metadata *md, const int64_t *spatial_size);

@@ -410,6 +410,7 @@ int scn_input_layer_forward(scn_metadata *md, const float *in_features, int64_t 
   SCN_REQUIRE(n_planes >= 1, SCN_ERR_BAD_ARG, "n_planes must be positive");
   if (n_out == 0) return SCN_OK;
   SCN_REQUIRE(in_features && out_features, SCN_ERR_BAD_ARG, "null features");
+  SCN_TRY(md_touch(md, stream));
   if (md->input_mode == 0) {  // row i <-> input i (CPU/IOLayers.cpp:61-63)
     if (in_features != out_features)
       SCN_CUDA_CHECK(cudaMemcpyAsync(out_features, in_features, sizeof(float) * (size_t)n_in * n_planes,
@@ -434,6 +435,7 @@ int scn_output_layer_forward(scn_metadata *md, const float *in_features, int64_t
               (long long)n_out, (long long)md->input_n_rows);
   if (n_out == 0) return SCN_OK;
   SCN_REQUIRE(out_features && (in_features || n_in == 0), SCN_ERR_BAD_ARG, "null features");
+  SCN_TRY(md_touch(md, stream));
   const size_t bytes = sizeof(float) * (size_t)n_out * n_planes;
   if (md->input_mode == 0) {  // rows are the input points themselves
     SCN_CUDA_CHECK(cudaMemcpyAsync(out_features, in_features, bytes, cudaMemcpyDeviceToDevice, stream));
@@ -581,6 +583,7 @@ int scn_sparse_to_dense_forward(scn_metadata *md, const int64_t *spatial_size, c
   size_t bytes = sizeof(float) * (size_t)g->batch_size * n_planes * volume;
   if (bytes == 0) return SCN_OK;
   SCN_REQUIRE(out_dense, SCN_ERR_BAD_ARG, "null output");
+  SCN_TRY(md_touch(md, stream));
   SCN_CUDA_CHECK(cudaMemsetAsync(out_dense, 0, bytes, stream));
   if (g->n_active == 0) return SCN_OK;
   SCN_REQUIRE(in_features, SCN_ERR_BAD_ARG, "null features");

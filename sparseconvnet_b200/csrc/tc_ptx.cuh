@@ -16,13 +16,28 @@ constexpr unsigned kWaitLimit = 1u << 20;  // polls before a bounded wait gives 
 // m = bf16(x - h) and the three bf16 products h h, m h, h m (what is left out is 2^-17 of a product).
 enum TcMode : int { TC_TF32 = 0, TC_BF16 = 1, TC_TF32X3 = 2, TC_BF16X3 = 3 };
 
-// which form SCN_PRECISION_TF32X3 runs: the bf16 one unless SCN_X3_FORM=tf32
-int split_mode_of_env();
+// Which form SCN_PRECISION_TF32X3 runs in a kernel whose default is `dflt`: SCN_X3_FORM=tf32 / bf16
+// forces one form everywhere (for measurements and the parity tests of both).
+int split_mode_of_env(int dflt = TC_BF16X3);
 
 // W [K][Cin][Cout] fp32 -> per (offset, slice of kc input planes) the shared-memory image of the
 // weight operand (conv_tc.cu)
 int prepare_weights(const float *w, unsigned char *out, int K, int cin, int cout, int kc, int mode,
                     cudaStream_t stream);
+
+// Prepared weight images (the operand layouts the kernels read) are small and depend only on the
+// weights, so a caller whose weights do not change between calls can have them kept: while the calling
+// thread has a non-zero weight token set (scn_set_weight_token), an image is looked up under
+// (device, token, layout, shape) and built only when it is not there; with token 0 it is scratch of the
+// call.  `needs_build` says whether the caller has to launch its preparation kernel.
+enum WeightImageKind : int { WIMG_ROWS = 1, WIMG_ROWS_B3, WIMG_ROWS_THIN, WIMG_TC };
+struct WeightImage {
+  void *ptr = nullptr;
+  bool cached = false;
+};
+int weight_image_get(int kind, int K, int cin, int cout, int extra, size_t bytes, cudaStream_t stream,
+                     WeightImage *img, bool *needs_build);
+int weight_image_put(WeightImage &img, cudaStream_t stream);  // frees a scratch image, keeps a cached one
 
 // ---------------------------------------------------------------------------------------------
 // PTX wrappers

@@ -21,22 +21,41 @@ void set_error(const char *fmt, ...) {
   va_end(ap);
 }
 
-int device_alloc(void **p, size_t bytes, cudaStream_t stream) {
-  static std::once_flag once[64];
+// The library's scratch memory (site tables, rulebooks, prepared weight images, partial sums) comes
+// from a memory pool of its own per device, not from the device's default pool: its release
+// threshold is raised so that freed blocks are reused instead of going back to the driver at every
+// synchronisation, and that setting must not leak to other users of cudaMallocAsync in the process.
+// scn_trim_memory gives idle blocks back.
+static cudaMemPool_t g_pool[64] = {nullptr};
+static std::mutex g_pool_mu;
+
+static int device_pool(cudaMemPool_t *pool) {
   int dev = 0;
   SCN_CUDA_CHECK(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64) {
-    std::call_once(once[dev], [dev]() {
-      cudaMemPool_t pool;
-      if (cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) {
-        unsigned long long keep = ~0ull;
-        cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
-      }
-    });
+  SCN_REQUIRE(dev >= 0 && dev < 64, SCN_ERR_UNSUPPORTED, "device index %d unsupported", dev);
+  std::lock_guard<std::mutex> lock(g_pool_mu);
+  if (!g_pool[dev]) {
+    cudaMemPoolProps props = {};
+    props.allocType = cudaMemAllocationTypePinned;
+    props.handleTypes = cudaMemHandleTypeNone;
+    props.location.type = cudaMemLocationTypeDevice;
+    props.location.id = dev;
+    cudaMemPool_t p = nullptr;
+    SCN_CUDA_CHECK(cudaMemPoolCreate(&p, &props));
+    unsigned long long keep = ~0ull;
+    SCN_CUDA_CHECK(cudaMemPoolSetAttribute(p, cudaMemPoolAttrReleaseThreshold, &keep));
+    g_pool[dev] = p;
   }
+  *pool = g_pool[dev];
+  return SCN_OK;
+}
+
+int device_alloc(void **p, size_t bytes, cudaStream_t stream) {
+  cudaMemPool_t pool = nullptr;
+  SCN_TRY(device_pool(&pool));
   *p = nullptr;
   if (bytes == 0) bytes = 16;
-  SCN_CUDA_CHECK(cudaMallocAsync(p, bytes, stream));
+  SCN_CUDA_CHECK(cudaMallocFromPoolAsync(p, bytes, pool, stream));
   return SCN_OK;
 }
 
@@ -146,6 +165,32 @@ extern "C" {
 int scn_abi_version(void) { return SCN_ABI_VERSION; }
 
 long long scn_launch_count(void) { return scn::g_launches.load(std::memory_order_relaxed); }
+
+int scn_memory_usage(uint64_t *reserved_bytes, uint64_t *used_bytes) {
+  using namespace scn;
+  SCN_REQUIRE(reserved_bytes && used_bytes, SCN_ERR_BAD_ARG, "null argument");
+  *reserved_bytes = *used_bytes = 0;
+  int dev = 0;
+  SCN_CUDA_CHECK(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(g_pool_mu);
+  if (dev >= 0 && dev < 64 && g_pool[dev]) {
+    unsigned long long r = 0, u = 0;
+    SCN_CUDA_CHECK(cudaMemPoolGetAttribute(g_pool[dev], cudaMemPoolAttrReservedMemCurrent, &r));
+    SCN_CUDA_CHECK(cudaMemPoolGetAttribute(g_pool[dev], cudaMemPoolAttrUsedMemCurrent, &u));
+    *reserved_bytes = r;
+    *used_bytes = u;
+  }
+  return SCN_OK;
+}
+
+int scn_trim_memory(uint64_t keep_bytes) {
+  using namespace scn;
+  int dev = 0;
+  SCN_CUDA_CHECK(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(g_pool_mu);
+  if (dev >= 0 && dev < 64 && g_pool[dev]) SCN_CUDA_CHECK(cudaMemPoolTrimTo(g_pool[dev], (size_t)keep_bytes));
+  return SCN_OK;
+}
 
 const char *scn_last_error(void) { return scn::g_last_error; }
 

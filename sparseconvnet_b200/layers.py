@@ -8,6 +8,8 @@ Reference counterparts: sparseconvnet/ioLayers.py:15-65, submanifoldConvolution.
 convolution.py:13-66, deconvolution.py:13-64, batchNormalization.py:13-91,
 maxPooling.py:71-104, sparseToDense.py:59-75, networkInNetwork.py, identity.py.
 """
+import weakref
+
 import torch
 from torch.nn import Module, Parameter
 
@@ -173,6 +175,25 @@ class _ConvBase(Module):
         if bias:
             self.bias = Parameter(torch.zeros(nOut))
 
+    cache_weight_images = True   # class-wide switch (tests turn it off to compare)
+
+    def _weight_token(self):
+        """Token under which this layer's prepared weight images are kept by the library: renewed
+        whenever the weight tensor is written (version counter) or moved (data pointer)."""
+        if not _ConvBase.cache_weight_images:
+            return 0
+        w = self.weight
+        key = (w.data_ptr(), w._version)
+        if getattr(self, "_wkey", None) != key:
+            old = getattr(self, "_wtoken", 0)
+            if old:
+                SCN.release_weight_token(old)
+                self._wfinal.detach()
+            self._wtoken = SCN.new_weight_token()
+            self._wkey = key
+            self._wfinal = weakref.finalize(self, SCN.release_weight_token, self._wtoken)
+        return self._wtoken
+
     def _count(self, macs, output_features):
         SCN.flop_counter.add(macs)
         _pkg.forward_pass_hidden_states += output_features.nelement()
@@ -183,19 +204,23 @@ class SubmanifoldConvolution(_ConvBase):
         Module.__init__(self)
         self._init_weight(dimension, nIn, nOut, filter_size, bias, groups)
 
-    def forward(self, input):
+    def forward(self, input, bn=None):
+        """`bn` (used by Sequential): an eval-mode BatchNormalization that follows this layer and is
+        applied in the convolution's store instead of as a pass of its own."""
         assert input.features.nelement() == 0 or input.features.size(1) == self.nIn, (self.nIn, self.nOut, input)
         output = SparseConvNetTensor(metadata=input.metadata, spatial_size=input.spatial_size)
         bias = optional_tensor(self, "bias")
         if autograd.needs_grad(input.features, self.weight, bias):
+            assert bn is None
             output.features, macs = autograd.convolution(
                 autograd.SUBMANIFOLD, input.features, self.weight, bias.to(self.weight.device), input.metadata,
                 input.spatial_size, None, self.filter_size, None)
         else:
             output.features = input.features.new_empty(0)
-            macs = SCN.SubmanifoldConvolution_updateOutput(
-                input.spatial_size, self.filter_size, input.metadata, input.features.detach().contiguous(),
-                output.features, self.weight, bias)
+            with SCN.weight_token(self._weight_token()):
+                macs = SCN.SubmanifoldConvolution_updateOutput(
+                    input.spatial_size, self.filter_size, input.metadata, input.features.detach().contiguous(),
+                    output.features, self.weight, bias, epilogue=bn.folded() if bn is not None else None)
         self._count(macs, output.features)
         return output
 
@@ -216,7 +241,7 @@ class Convolution(_ConvBase):
         self._init_weight(dimension, nIn, nOut, filter_size, bias, groups)
         self.filter_stride = to_long_tensor(dimension, filter_stride)
 
-    def forward(self, input):
+    def forward(self, input, bn=None):
         assert input.features.nelement() == 0 or input.features.size(1) == self.nIn
         out_size = torch.div(input.spatial_size - self.filter_size, self.filter_stride, rounding_mode="trunc") + 1
         assert ((out_size - 1) * self.filter_stride + self.filter_size == input.spatial_size).all(), \
@@ -229,9 +254,11 @@ class Convolution(_ConvBase):
                 input.spatial_size, out_size, self.filter_size, self.filter_stride)
         else:
             output.features = input.features.new_empty(0)
-            macs = SCN.Convolution_updateOutput(
-                input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata,
-                input.features.detach().contiguous(), output.features, self.weight, bias)
+            with SCN.weight_token(self._weight_token()):
+                macs = SCN.Convolution_updateOutput(
+                    input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata,
+                    input.features.detach().contiguous(), output.features, self.weight, bias,
+                    epilogue=bn.folded() if bn is not None else None)
         self._count(macs, output.features)
         return output
 
@@ -249,7 +276,7 @@ class Deconvolution(_ConvBase):
         self._init_weight(dimension, nIn, nOut, filter_size, bias, groups)
         self.filter_stride = to_long_tensor(dimension, filter_stride)
 
-    def forward(self, input):
+    def forward(self, input, bn=None):
         assert input.features.nelement() == 0 or input.features.size(1) == self.nIn
         out_size = (input.spatial_size - 1) * self.filter_stride + self.filter_size
         output = SparseConvNetTensor(metadata=input.metadata, spatial_size=out_size)
@@ -260,9 +287,11 @@ class Deconvolution(_ConvBase):
                 input.spatial_size, out_size, self.filter_size, self.filter_stride)
         else:
             output.features = input.features.new_empty(0)
-            macs = SCN.Deconvolution_updateOutput(
-                input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata,
-                input.features.detach().contiguous(), output.features, self.weight, bias)
+            with SCN.weight_token(self._weight_token()):
+                macs = SCN.Deconvolution_updateOutput(
+                    input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata,
+                    input.features.detach().contiguous(), output.features, self.weight, bias,
+                    epilogue=bn.folded() if bn is not None else None)
         self._count(macs, output.features)
         return output
 
@@ -291,6 +320,27 @@ class BatchNormalization(Module):
         if affine:
             self.weight = Parameter(torch.ones(nPlanes))
             self.bias = Parameter(torch.zeros(nPlanes))
+
+    def folded(self):
+        """(scale, shift, leakiness) of this layer in eval mode, for a convolution that applies it in its
+        store.  Kept until a parameter or running statistic changes (tensor version counters)."""
+        tensors = (self.running_mean, self.running_var, getattr(self, "weight", None), getattr(self, "bias", None))
+        key = tuple((t.data_ptr(), t._version) if t is not None else None for t in tensors) + (self.eps,)
+        cached = getattr(self, "_folded", None)
+        if cached is None or cached[0] != key:
+            scale, shift = SCN.batchnorm_fold(self.running_mean, self.running_var, optional_tensor(self, "weight"),
+                                              optional_tensor(self, "bias"), self.eps)
+            cached = (key, scale, shift)
+            self._folded = cached
+        return cached[1], cached[2], self.leakiness
+
+    def fusable(self, features):
+        """True when a preceding convolution may apply this layer in its store: eval mode, no gradients
+        wanted, statistics on the features' device."""
+        return (not self.training and not autograd.needs_grad(features, optional_tensor(self, "weight"),
+                                                              optional_tensor(self, "bias"))
+                and self.running_mean.is_cuda and self.running_mean.device == features.device
+                and not self._forward_hooks and not self._forward_pre_hooks)
 
     def forward(self, input):
         if input.features.nelement() == 0:

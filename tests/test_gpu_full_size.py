@@ -82,7 +82,7 @@ def test_config3_full_batch_vs_reference(precision, tol, cuda):
     print("config3 x8 %s rel err %.3g kernels %s" % (precision, e, sorted(set(kernels))))
     assert len(kernels) == 39
     if precision == "tf32x3":
-        assert {"k_conv_rows", "k_conv_tma", "k_conv_tc"} <= set(kernels), sorted(set(kernels))
+        assert {"k_conv_rows", "k_conv_wide", "k_conv_tc"} <= set(kernels), sorted(set(kernels))
     else:
         assert set(kernels) == {"k_conv_simt"}, sorted(set(kernels))
 
@@ -171,29 +171,40 @@ def _layer_vs_reference(cin, cout, precision, tol, expect_kernel, n=60000, size=
     return e, yg.features.shape[0]
 
 
-@pytest.mark.parametrize("precision,tol", [("tf32x3", helpers.FP32_TOL), ("tf32", helpers.TC_TOL),
-                                           ("bf16", helpers.TC_TOL)])
-@pytest.mark.parametrize("cin,cout", [(96, 96), (128, 128), (192, 96)])
-def test_persistent_tcgen05_vs_reference(cin, cout, precision, tol, cuda, monkeypatch):
-    """k_conv_tma forced on (SCN_TC_PERSISTENT=1) for 96 and 128 output planes in all three modes."""
-    e, rows = _layer_vs_reference(cin, cout, precision, tol, 2, env={"SCN_TC_PERSISTENT": "1"}, monkeypatch=monkeypatch)
-    print("k_conv_tma %d->%d %s: %d rows, rel err %.3g" % (cin, cout, precision, rows, e))
+@pytest.mark.parametrize("precision,form,tol,kernel", [
+    ("tf32x3", "bf16", helpers.FP32_TOL, 5),   # k_conv_wide, three bf16 products
+    ("bf16", "bf16", helpers.TC_TOL, 5),       # k_conv_wide, one product
+    ("tf32x3", "tf32", helpers.FP32_TOL, 2),   # k_conv_tma, three-pass tf32 split
+    ("tf32", "bf16", helpers.TC_TOL, 2)])      # k_conv_tma, single tf32 pass
+@pytest.mark.parametrize("cin,cout", [(96, 96), (128, 128), (192, 96), (64, 64), (96, 160), (256, 224)])
+def test_persistent_tcgen05_vs_reference(cin, cout, precision, form, tol, kernel, cuda, monkeypatch):
+    """The two persistent tcgen05 kernels forced on (SCN_TC_PERSISTENT=1; 64 output planes sent to them by
+    SCN_X3_MIN_COUT) in every arithmetic mode, for one and two 128-plane accumulator tiles."""
+    if precision == "tf32x3" and form == "tf32" and cout > 160:
+        pytest.skip("two fp32 weight slabs of this width leave k_conv_tma a single stage: k_conv_tc takes the shape")
+    e, rows = _layer_vs_reference(cin, cout, precision, tol, kernel, monkeypatch=monkeypatch,
+                                  env={"SCN_TC_PERSISTENT": "1", "SCN_X3_FORM": form, "SCN_X3_MIN_COUT": "64",
+                                       "SCN_X3_ROWS": "0" if cout == 64 and precision != "tf32x3" else "1"})
+    print("persistent tcgen05 %d->%d %s/%s: %d rows, rel err %.3g" % (cin, cout, precision, form, rows, e))
 
 
 @pytest.mark.parametrize("split", ["1", "4"])
-@pytest.mark.parametrize("precision,tol", [("tf32x3", helpers.FP32_TOL), ("bf16", helpers.TC_TOL)])
+@pytest.mark.parametrize("precision,form,tol", [("tf32x3", "bf16", helpers.FP32_TOL), ("tf32x3", "tf32", helpers.FP32_TOL),
+                                                ("bf16", "bf16", helpers.TC_TOL)])
 @pytest.mark.parametrize("cin,cout", [(96, 96), (160, 160), (224, 224)])
-def test_per_tile_tcgen05_vs_reference(cin, cout, precision, tol, split, cuda, monkeypatch):
-    """k_conv_tc (SCN_TC_PERSISTENT=0) without and with the split of the filter offsets over CTAs."""
+def test_per_tile_tcgen05_vs_reference(cin, cout, precision, form, tol, split, cuda, monkeypatch):
+    """k_conv_tc (the default below 148 tiles) without and with the split of the filter offsets over CTAs,
+    in both forms of the fp32-class mode."""
     e, rows = _layer_vs_reference(cin, cout, precision, tol, 1, n=20000, size=96,
-                                  env={"SCN_TC_PERSISTENT": "0", "SCN_TC_SPLIT": split}, monkeypatch=monkeypatch)
-    print("k_conv_tc %d->%d %s split %s: %d rows, rel err %.3g" % (cin, cout, precision, split, rows, e))
+                                  env={"SCN_TC_SPLIT": split, "SCN_X3_FORM": form}, monkeypatch=monkeypatch)
+    print("k_conv_tc %d->%d %s/%s split %s: %d rows, rel err %.3g" % (cin, cout, precision, form, split, rows, e))
 
 
-@pytest.mark.parametrize("precision,tol", [("tf32x3", helpers.FP32_TOL), ("tf32", helpers.TC_TOL),
-                                           ("bf16", helpers.TC_TOL)])
+@pytest.mark.parametrize("precision,form,tol", [("tf32x3", "bf16", helpers.FP32_TOL), ("tf32x3", "tf32", helpers.FP32_TOL),
+                                                ("tf32", "bf16", helpers.TC_TOL), ("bf16", "bf16", helpers.TC_TOL)])
 @pytest.mark.parametrize("cin,cout", [(32, 32), (64, 32), (64, 64), (128, 64)])
-def test_rows_kernel_vs_reference(cin, cout, precision, tol, cuda, monkeypatch):
-    """k_conv_rows (32 / 64 output planes) in its three arithmetic modes."""
-    e, rows = _layer_vs_reference(cin, cout, precision, tol, 4, monkeypatch=monkeypatch, bias=(cin == 64))
-    print("k_conv_rows %d->%d %s: %d rows, rel err %.3g" % (cin, cout, precision, rows, e))
+def test_rows_kernel_vs_reference(cin, cout, precision, form, tol, cuda, monkeypatch):
+    """k_conv_rows (32 / 64 output planes) in its arithmetic modes, both forms of the fp32-class one."""
+    e, rows = _layer_vs_reference(cin, cout, precision, tol, 4, monkeypatch=monkeypatch, bias=(cin == 64),
+                                  env={"SCN_X3_FORM": form})
+    print("k_conv_rows %d->%d %s/%s: %d rows, rel err %.3g" % (cin, cout, precision, form, rows, e))

@@ -291,3 +291,34 @@ def test_large_filter_volume_counts(cuda):
     assert len(book) == 625
     assert float(macs) == float(sum(b.shape[0] for b in book)) * 2 * 3
     x.metadata.poll_errors()
+
+
+@pytest.mark.parametrize("precision", ["fp32", "tf32x3", "bf16"])
+def test_fused_batchnorm_equals_two_passes(precision, cuda):
+    """A convolution that applies the following eval-mode BatchNorm in its store gives the same bits
+    as the convolution followed by the BatchNorm operator, in every kernel class (warp-level rows
+    kernel, first-layer kernel, both tcgen05 kernels with and without offset split, the fp32 kernels
+    through the in-place fallback), and the U-Net runs with a fraction of the BatchNorm launches."""
+    import sparseconvnet_b200 as scn
+    from sparseconvnet_b200 import SCN, workloads
+    coords, feats = workloads.batch_config3([0], target_voxels=60000)
+    inp, net, _ = workloads.build_config(3)
+    net.to(cuda)
+    scn.set_precision(precision)
+    try:
+        outs, bn_calls, fused = [], [], []
+        for fuse in (False, True):
+            scn.Sequential.fuse = fuse
+            with torch.no_grad(), SCN.Profile() as prof:
+                y = net(inp([torch.from_numpy(coords), torch.from_numpy(feats).to(cuda)]))
+            rows = prof.rows()
+            bn_calls.append(sum(r["kind"] == "batchnorm" for r in rows))
+            fused.append(sum(bool(r.get("fused_bn")) for r in rows if r["kind"] == "conv"))
+            y.metadata.poll_errors()
+            outs.append(y.features.clone())
+    finally:
+        scn.Sequential.fuse = True
+        scn.set_precision("fp32")
+    assert bn_calls[0] == 39 and fused[0] == 0
+    assert fused[1] == 27 and bn_calls[1] == 12, (bn_calls, fused)
+    assert torch.equal(outs[0], outs[1]), float((outs[0] - outs[1]).abs().max())

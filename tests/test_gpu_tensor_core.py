@@ -183,3 +183,35 @@ def test_unet_tensor_core_against_golden(mode, tol, cuda, restore_precision):
     scn.set_precision(mode)
     y = gpu.run(net, gpu.run(inp, [g["coords"], g["feats"]]))
     helpers.assert_features_match(gpu.locations(y), y.features, g["loc/y"], g["feat/y"], tol, what=mode)
+
+
+def test_bounded_wait_runs_out_and_the_library_recovers(cuda, restore_precision):
+    """Failure path of the tensor-core kernels, made on the host: one barrier arrival of one CTA is left
+    out (a flag that nothing sets), so the MMA thread's bounded wait runs out.  The kernel must return on
+    its own, the status must reach the host through poll_errors, and the next call must work."""
+    import sparseconvnet_b200 as scn
+    from sparseconvnet_b200._lib import ScnError, lib
+    coords = _surface(20000, 96, 2, 5)
+    rng = np.random.default_rng(6)
+    torch.manual_seed(7)
+    inp = scn.InputLayer(3, 96, mode=3)
+    sc = scn.SubmanifoldConvolution(3, 96, 96, 3, False).to(cuda)
+    feats = torch.from_numpy(rng.standard_normal((coords.shape[0], 96)).astype(np.float32)).to(cuda)
+    with torch.no_grad():
+        x = inp([torch.from_numpy(coords), feats])
+        scn.set_precision("fp32")
+        want = sc(x).features
+        scn.set_precision("bf16")
+        good = sc(x).features.clone()
+        assert lib.scn_last_conv_kernel() == 1      # the per-tile kernel: the one the hook reaches
+        x.metadata.poll_errors()
+        assert lib.scn_test_drop_barrier_arrival() == 0
+        sc(x)                                        # returns: the launch is asynchronous
+        torch.cuda.synchronize()                     # ... and the kernel ends by itself
+        with pytest.raises(ScnError) as failure:
+            x.metadata.poll_errors()
+        assert "bounded wait" in str(failure.value)
+        again = sc(x).features                       # the flag was cleared by the poll; the library works on
+        x.metadata.poll_errors()
+    assert torch.equal(again, good)
+    assert helpers.rel_err(again.cpu().numpy(), want.cpu().numpy()) <= helpers.TC_TOL
