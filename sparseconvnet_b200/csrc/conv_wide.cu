@@ -29,6 +29,14 @@
 // operator, 3e-5 through the four 81-offset layers of the 4-D stack -- better than the three-pass
 // tf32 split on the same instruction, whose high part is a truncation.
 //
+// Where the time goes (96 -> 96 planes, 154 k rows, 0.44 ms; the kernel it replaces took 0.75 ms): the
+// MMA thread waits for full steps two thirds of the time; phase timers in the producers showed the work
+// of a (tile, offset) group spread over its barriers, the list reads, the loads, the conversion and the
+// zero stores with no single dominant term, and ncu shows no saturated pipe (tensor 38 %, LSU 34 %,
+// issue slots 39 %): 2 900 warp instructions per step at 1.5 issued per clock.  What moved it: reading a
+// row's 128 bytes with four neighbouring lanes (one line per row and load instruction instead of one
+// sector per lane: 0.56 -> 0.44 ms) and two block barriers per group instead of three.
+//
 // Every wait is bounded: on expiry the role raises the abort flag, everybody leaves their loops,
 // tensor memory is freed and the host sees FLAG_TC_TIMEOUT through scn_md_poll_errors.
 #include <stdlib.h>
@@ -46,8 +54,9 @@ constexpr int kWMaxRows = 256; // output rows per tile = MMA N: 256 or 128 (temp
 constexpr int kWPlanes = 128;  // output planes per MMA = M
 constexpr int kWSlice = 32;    // input planes per step
 constexpr int kWMaxStages = 8;
-// warps 0 .. PW-1 produce (PW = 12 or 24, a multiple of four), the next four drain accumulators (their
-// warp id mod 4 selects the TMEM lane quadrant), the last issues the MMAs
+// warps 0 .. PW-1 produce (PW a multiple of four), the next four drain accumulators (their warp id mod 4
+// selects the TMEM lane quadrant), the last issues the MMAs.  One CTA per SM with the whole shared memory
+// and all 512 TMEM columns.
 enum : int { W_LAST_OF_TILE = 1, W_LAST_OF_CTA = 2 };
 
 struct WideParams {
@@ -77,7 +86,8 @@ template <int TERMS, int ROWS, int PW>
 __global__ void __launch_bounds__((PW + 5) * 32, 1) k_conv_wide(WideParams P) {
   constexpr int kWProducerWarps = PW, kWProducers = PW * 32;
   constexpr int kWEpilogue0 = PW, kWMmaWarp = PW + 4;
-  constexpr int kWBatch = PW > 12 ? 1 : 2;  // steps whose loads are in flight together
+  constexpr int kWBatch = 2;  // steps whose loads are in flight together
+  constexpr unsigned kTmemCols = 512u;
   constexpr int kParts = TERMS == 3 ? 2 : 1;
   constexpr int kWRows = ROWS;
   // A bf16 tile of gathered rows [ROWS x 32 planes] is stored as four planes of 16-byte pieces (piece j =
@@ -102,7 +112,7 @@ __global__ void __launch_bounds__((PW + 5) * 32, 1) k_conv_wide(WideParams P) {
   const unsigned w_region = (total_w + 1023u) & ~1023u;
   const unsigned stage_bytes = w_region + kWTile * kParts;  // a multiple of 128
   const int n_mt = (P.cout + kWPlanes - 1) / kWPlanes;
-  const int n_acc = (n_mt * kWRows <= 256) ? 2 : 1;  // accumulator buffers in TMEM (512 columns in all)
+  const int n_acc = (2 * n_mt * kWRows <= (int)kTmemCols) ? 2 : 1;  // accumulator buffers in TMEM
 
   unsigned char *ctl = smem + (size_t)NS * stage_bytes;
   unsigned long long *full = reinterpret_cast<unsigned long long *>(ctl);  // [NS] rows stored, slab landed
@@ -129,7 +139,7 @@ __global__ void __launch_bounds__((PW + 5) * 32, 1) k_conv_wide(WideParams P) {
     *sh_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == kWMmaWarp) tmem_alloc(sh_tmem, 512u);
+  if (warp == kWMmaWarp) tmem_alloc(sh_tmem, kTmemCols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -430,7 +440,7 @@ __global__ void __launch_bounds__((PW + 5) * 32, 1) k_conv_wide(WideParams P) {
   tc_fence_before();
   __syncthreads();
   if (*sh_abort && tid == 0) atomicOr(P.flags, FLAG_TC_TIMEOUT);
-  if (warp == kWMmaWarp) tmem_dealloc(tmem_base, 512u);
+  if (warp == kWMmaWarp) tmem_dealloc(tmem_base, kTmemCols);
 }
 
 size_t wide_stage_bytes(int terms, int cout, int rows) {
@@ -438,11 +448,10 @@ size_t wide_stage_bytes(int terms, int cout, int rows) {
   const size_t w = (size_t)cout * kWSlice * 2 * parts;
   return ((w + 1023) & ~(size_t)1023) + (size_t)4 * (rows * 16 + 32) * parts;
 }
-// rows per tile: 256 unless SCN_WIDE_ROWS=128
-int wide_rows() {
-  const char *e = getenv("SCN_WIDE_ROWS");
-  return (e && atoi(e) == 128) ? 128 : 256;
-}
+// Rows per tile.  Measured alternatives that lost: 128-row tiles (N = 128 instructions are as efficient, but the
+// per-group work of the producers doubles: 0.65 against 0.56 ms on 96 -> 96 planes at 154 k rows), 24 producer
+// warps (0.45 against 0.44 ms) and two CTAs per SM with half the ring and one accumulator each (0.45 ms).
+int wide_rows() { return 256; }
 constexpr size_t kWideControlBytes = 4096;  // barriers, step flags, and the producers' row lists
 constexpr size_t kWideSmemBudget = 226 * 1024;
 
@@ -469,7 +478,8 @@ int conv_forward_wide(const float *in, long long n_in, float *out, long long n_o
   SCN_REQUIRE(n_in < (1ll << 31) && n_out < (1ll << 31), SCN_ERR_UNSUPPORTED, "row count above 2^31");
   const int rows = wide_rows();
   const size_t stage = wide_stage_bytes(terms, cout, rows);
-  const int stages = (int)std::min<size_t>(kWMaxStages, (kWideSmemBudget - kWideControlBytes) / stage);
+  const size_t budget = kWideSmemBudget;
+  const int stages = (int)std::min<size_t>(kWMaxStages, (budget - kWideControlBytes) / stage);
   SCN_REQUIRE(stages >= 2, SCN_ERR_UNSUPPORTED, "tensor-core path: stage does not fit shared memory");
   const int parts = terms == 3 ? 2 : 1;
   const int mode = terms == 3 ? TC_BF16X3 : TC_BF16;
@@ -509,27 +519,14 @@ int conv_forward_wide(const float *in, long long n_in, float *out, long long n_o
     const int b = (int)kWideSmemBudget;
     SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_wide<1, 256, 12>, cudaFuncAttributeMaxDynamicSharedMemorySize, b));
     SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_wide<3, 256, 12>, cudaFuncAttributeMaxDynamicSharedMemorySize, b));
-    SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_wide<1, 128, 12>, cudaFuncAttributeMaxDynamicSharedMemorySize, b));
-    SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_wide<3, 128, 12>, cudaFuncAttributeMaxDynamicSharedMemorySize, b));
-    SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_wide<1, 256, 24>, cudaFuncAttributeMaxDynamicSharedMemorySize, b));
-    SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_wide<3, 256, 24>, cudaFuncAttributeMaxDynamicSharedMemorySize, b));
     n_sm[dev] = sms;
   }
   const unsigned grid = (unsigned)std::min<long long>(P.n_tiles, n_sm[dev]);
-  // the whole budget: one CTA per SM by construction (it also owns all 512 TMEM columns)
-  const bool pw24 = rows == 256 && getenv("SCN_WIDE_PW") && atoi(getenv("SCN_WIDE_PW")) == 24;
-  if (pw24 && terms == 3)
-    SCN_LAUNCH((k_conv_wide<3, 256, 24>), grid, 29 * 32, kWideSmemBudget, stream, P);
-  else if (pw24)
-    SCN_LAUNCH((k_conv_wide<1, 256, 24>), grid, 29 * 32, kWideSmemBudget, stream, P);
-  else if (terms == 3 && rows == 256)
-    SCN_LAUNCH((k_conv_wide<3, 256, 12>), grid, 17 * 32, kWideSmemBudget, stream, P);
-  else if (terms == 3)
-    SCN_LAUNCH((k_conv_wide<3, 128, 12>), grid, 17 * 32, kWideSmemBudget, stream, P);
-  else if (rows == 256)
-    SCN_LAUNCH((k_conv_wide<1, 256, 12>), grid, 17 * 32, kWideSmemBudget, stream, P);
+  // one CTA per SM by construction: it asks for the whole shared memory and owns all 512 TMEM columns
+  if (terms == 3)
+    SCN_LAUNCH((k_conv_wide<3, 256, 12>), grid, 17 * 32, budget, stream, P);
   else
-    SCN_LAUNCH((k_conv_wide<1, 128, 12>), grid, 17 * 32, kWideSmemBudget, stream, P);
+    SCN_LAUNCH((k_conv_wide<1, 256, 12>), grid, 17 * 32, budget, stream, P);
   SCN_CUDA_CHECK(cudaGetLastError());
   SCN_TRY(weight_image_put(wi, stream));
   return SCN_OK;

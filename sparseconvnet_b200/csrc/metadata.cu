@@ -412,7 +412,17 @@ static int md_input_layer(scn_metadata *md, const int64_t *spatial_size, const i
     SCN_TRY(exclusive_scan_i32(flag, rank, n, &md->scalars_dev[0], stream));
     SCN_LAUNCH(k_number_input_sites, blocks, threads, 0, stream, g.table.slots, slot_of, flag, rank, n, g.row_keys);
     SCN_CUDA_CHECK(cudaGetLastError());
-    // CSR of input rows per site
+  }
+
+  int flags = 0, sc[4];
+  SCN_TRY(fetch_flags(md, stream, &flags, sc));
+  long long active = (mode == 0) ? n : (n > 0 ? sc[0] : 0);
+  // Every point has a site of its own (no repeated coordinates, no empty slots): rows are numbered in
+  // order of first occurrence, so row i is point i and the rule table is the identity -- the feature
+  // pass is then the plain copy of mode 0 and no table is built.  Otherwise: CSR of the input rows of
+  // every site, each site's rows ascending (the order the reference sums them in).
+  const bool identity = mode != 0 && flags == 0 && active == n;
+  if (mode != 0 && n > 0 && flags == 0 && active > 0 && !identity) {
     SCN_TRY(device_alloc((void **)&md->input_csr_start, sizeof(int) * (size_t)(n + 1), stream));
     SCN_TRY(device_alloc((void **)&md->input_csr_rows, sizeof(int) * (size_t)n, stream));
     SCN_TRY(device_alloc((void **)&cursor, sizeof(int) * (size_t)(n + 1), stream));
@@ -421,13 +431,6 @@ static int md_input_layer(scn_metadata *md, const int64_t *spatial_size, const i
     SCN_TRY(exclusive_scan_i32(cursor, md->input_csr_start, n + 1, nullptr, stream));
     SCN_CUDA_CHECK(cudaMemsetAsync(cursor, 0, sizeof(int) * (size_t)(n + 1), stream));
     SCN_LAUNCH(k_fill_per_site, blocks, threads, 0, stream, g.table.slots, slot_of, n, md->input_csr_start, cursor, md->input_csr_rows);
-    SCN_CUDA_CHECK(cudaGetLastError());
-  }
-
-  int flags = 0, sc[4];
-  SCN_TRY(fetch_flags(md, stream, &flags, sc));
-  long long active = (mode == 0) ? n : (n > 0 ? sc[0] : 0);
-  if (mode != 0 && n > 0 && flags == 0 && active > 0) {
     unsigned sblocks = (unsigned)ceil_div(active, threads);
     SCN_LAUNCH(k_sort_segments, sblocks, threads, 0, stream, md->input_csr_start, active, md->input_csr_rows);
     SCN_CUDA_CHECK(cudaGetLastError());
@@ -453,7 +456,7 @@ static int md_input_layer(scn_metadata *md, const int64_t *spatial_size, const i
     g.batch_size = 1;
   else
     g.batch_size = std::max<long long>(batch_size, (long long)sc[1] + 1);
-  md->input_mode = mode;
+  md->input_mode = identity ? 0 : mode;  // what the feature passes do (a copy when the table is the identity)
   md->input_n_rows = n;
   md->input_n_active = active;
   md->grids[key] = g;
@@ -846,9 +849,9 @@ static int count_ticket_start(Rulebook &rb, cudaStream_t stream) {
       P.events[dev].pop_back();
     }
   }
-  if (!t->host) {  // a slab of 64 chunks at a time
+  if (!t->host) {  // a slab of 256 chunks (512 KB of pinned memory) at a time
     unsigned long long *slab = nullptr;
-    if (cudaHostAlloc((void **)&slab, sizeof(unsigned long long) * kTicketValues * 64,
+    if (cudaHostAlloc((void **)&slab, sizeof(unsigned long long) * kTicketValues * 256,
                       cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) {
       cudaGetLastError();
       delete t;
@@ -857,7 +860,7 @@ static int count_ticket_start(Rulebook &rb, cudaStream_t stream) {
     t->host = slab;
     TicketPool &P = ticket_pool();
     std::lock_guard<std::mutex> lock(P.mu);
-    for (int i = 1; i < 64; ++i) P.chunks[dev].push_back(slab + (size_t)i * kTicketValues);
+    for (int i = 1; i < 256; ++i) P.chunks[dev].push_back(slab + (size_t)i * kTicketValues);
   }
   if (!t->event && cudaEventCreateWithFlags(&t->event, cudaEventDisableTiming) != cudaSuccess) {
     cudaGetLastError();
