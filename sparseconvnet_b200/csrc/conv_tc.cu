@@ -251,6 +251,85 @@ __global__ void __launch_bounds__(kTcThreads) k_conv_tc(TcParams P) {
     // and of the step being completed (c = s - L), offset index and slice of step s
     int st = 0, round = 0, ki = 0, slice = 0;
     int st_c = 0;
+    if constexpr (kBf16) {
+      // bf16 operands are made in registers, so the gather cannot run ahead through the ring like the
+      // cp.async one.  It runs ahead through registers instead: the loads of step s + 1 are issued
+      // before step s is converted and stored (two register buffers, the loop handles two steps per
+      // turn), which hides the L2 latency of every step but the first behind the previous one's work.
+      constexpr int kMine = 4;  // pieces per thread and step: 32 input planes / 8 per 16-byte bf16 piece
+      float4 xa[kMine][2], xb[kMine][2];
+      unsigned va = 0, vb = 0;  // which pieces of the buffer hold a real row
+      auto load_step = [&](float4 (&x)[kMine][2], unsigned &valid) {
+        const int k = sh_steps[ki];
+        const int *idx = sh_idx + k * kTcRows + r_base;
+        const float *col = P.in + slice * kc + j * kPerPiece;
+        valid = 0;
+#pragma unroll
+        for (int i = 0; i < kMine; ++i)
+          if (i < n_mine) {
+            const int src_row = idx[i * r_step];
+            if (src_row >= 0) {
+              const float4 *src = reinterpret_cast<const float4 *>(col + (long long)src_row * P.ld_in);
+              x[i][0] = __ldg(src);
+              x[i][1] = __ldg(src + 1);
+              valid |= 1u << i;
+            }
+          }
+        if (++slice == n_slices) {
+          slice = 0;
+          ++ki;
+        }
+      };
+      auto store_step = [&](const float4 (&x)[kMine][2], unsigned valid, int step) -> bool {
+        if (round > 0) {  // one lane polls, the warp follows
+          int freed = 1;
+          if (lane == 0) freed = mbar_wait(&empty[st], (unsigned)((round - 1) & 1)) ? 1 : 0;
+          if (!__shfl_sync(0xffffffffu, freed, 0)) return false;
+        }
+        unsigned char *sa = stage_base + (size_t)st * stage_bytes;
+#pragma unroll
+        for (int i = 0; i < kMine; ++i)
+          if (i < n_mine) {
+            // 8 input floats -> one 16-byte piece of 8 bf16; the three-term form also stores what the
+            // rounding left over, as a second bf16 tile
+            uint4 packed = make_uint4(0, 0, 0, 0), rest = make_uint4(0, 0, 0, 0);
+            if (valid & (1u << i)) {
+              split_bf16_pair(x[i][0].x, x[i][0].y, packed.x, rest.x);
+              split_bf16_pair(x[i][0].z, x[i][0].w, packed.y, rest.y);
+              split_bf16_pair(x[i][1].x, x[i][1].y, packed.z, rest.z);
+              split_bf16_pair(x[i][1].z, x[i][1].w, packed.w, rest.w);
+            }
+            const unsigned off = off_base + i * off_step;
+            *reinterpret_cast<uint4 *>(sa + off) = packed;
+            if (kSplit) *reinterpret_cast<uint4 *>(sa + g_bytes + off) = rest;
+          }
+        __syncwarp();
+        // (test hook: one warp of CTA 0 never reports its first step, so the MMA thread's bounded wait runs out)
+        const bool dropped = P.drop_arrival && blockIdx.x == 0 && blockIdx.y == 0 && warp == 0 && step == 0;
+        if (lane == 0 && !dropped) mbar_arrive(&full_g[st]);  // one arrival per warp (release)
+        if (++st == NS) {
+          st = 0;
+          ++round;
+        }
+        return true;
+      };
+      if (S > 0) load_step(xa, va);
+      for (int s = 0; s < S; s += 2) {
+        if (*sh_abort) break;
+        if (s + 1 < S) load_step(xb, vb);
+        if (!store_step(xa, va, s)) {
+          *sh_abort = 1;
+          break;
+        }
+        if (s + 1 < S) {
+          if (s + 2 < S) load_step(xa, va);
+          if (!store_step(xb, vb, s + 1)) {
+            *sh_abort = 1;
+            break;
+          }
+        }
+      }
+    } else {
     for (int s = 0; s < S + L; ++s) {
       if (*sh_abort) break;
       if (s < S) {
@@ -339,6 +418,7 @@ __global__ void __launch_bounds__(kTcThreads) k_conv_tc(TcParams P) {
         if (lane == 0 && !dropped) mbar_arrive(&full_g[st_c]);  // one arrival per warp (release)
         if (++st_c == NS) st_c = 0;
       }
+    }
     }
     cp_async_wait<0>();
 
