@@ -318,6 +318,15 @@ SCN_API int scn_submanifold_convolution_forward_static(scn_metadata *md, const i
 SCN_API int scn_batchnorm_fold(const float *running_mean, const float *running_var, const float *weight,
                                const float *bias, double eps, int n_planes, float *scale, float *shift,
                                void *stream);
+/* Eval-mode BatchNormalization (+ leaky ReLU) of the column-wise concatenation [in_a | in_b] of two dense
+ * matrices with n_rows rows -- a JoinTable (sparseconvnet/tables.py:37-49) followed by
+ * BatchNormalization_updateOutput's eval branch -- in one pass, without the joined matrix being written
+ * first.  Statistics and affine terms have planes_a + planes_b entries.  Plane counts must be multiples
+ * of four. */
+SCN_API int scn_batchnorm_join_forward(const float *in_a, int planes_a, const float *in_b, int planes_b,
+                                       float *out_features, int64_t n_rows, const float *running_mean,
+                                       const float *running_var, const float *weight, const float *bias,
+                                       double eps, double leakiness, void *stream);
 SCN_API int scn_submanifold_convolution_bn_forward(scn_metadata *md, const int64_t *spatial_size,
                                                    const int64_t *filter_size, const float *in_features,
                                                    float *out_features, const float *weight, const float *bias,

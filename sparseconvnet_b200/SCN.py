@@ -622,6 +622,30 @@ def BatchNormalization_updateOutput(input_features, output_features, saveMean, s
                 int(bool(train)), float(leakiness), _stream()))
 
 
+def batchnorm_concat(inputs, running_mean, running_var, weight, bias, eps, leakiness):
+    """Eval-mode BatchNormalization of the column-wise concatenation of two matrices (a JoinTable followed
+    by a BatchNorm) without materialising the concatenation: same arithmetic as
+    BatchNormalization_updateOutput on torch.cat(inputs, 1) (CPU/BatchNormalization.cpp:41-61), one read
+    and one write of the activation instead of two each.  Not in the reference.  Returns None when the
+    shapes are not ones the fused kernel takes (the caller then joins and normalises in two steps)."""
+    if len(inputs) != 2:
+        return None
+    fa, fb = (_features(f, "input_features") for f in inputs)
+    if fa.size(0) != fb.size(0) or fa.size(1) % 4 or fb.size(1) % 4 or fa.device != fb.device:
+        return None
+    n, ca, cb = fa.size(0), fa.size(1), fb.size(1)
+    out = fa.new_empty(n, ca + cb)
+    w = _optional(weight, fa, "weight")
+    b = _optional(bias, fa, "bias")
+    with torch.cuda.device(fa.device):
+        with _timed("batchnorm", dict(rows=n, planes=ca + cb, joined=True)):
+            check(lib.scn_batchnorm_join_forward(_ptr(fa), ca, _ptr(fb), cb, _ptr(out), n,
+                                                 _ptr(_features(running_mean, "runningMean")),
+                                                 _ptr(_features(running_var, "runningVar")), _ptr(w), _ptr(b),
+                                                 float(eps), float(leakiness), _stream()))
+    return out
+
+
 def _conv_backward_args(input_features, d_input_features, d_output_features, weight, d_weight, d_bias):
     f, w, _, groups, cin, cout = _conv_args(input_features, weight, torch.empty(0))
     go = _features(d_output_features, "d_output_features")

@@ -59,6 +59,8 @@ SIGNATURES = {
     "scn_deconvolution_forward": (C.c_int, [_vp, _i64p, _i64p, _i64p, _i64p, _vp, _vp, _vp, _vp,
                                             C.c_int, C.c_int, C.c_int, C.c_int, _vp,
                                             C.POINTER(C.c_double)]),
+    "scn_batchnorm_join_forward": (C.c_int, [_vp, C.c_int, _vp, C.c_int, _vp, C.c_int64, _vp, _vp, _vp, _vp, C.c_double,
+                                             C.c_double, _vp]),
     "scn_batchnorm_fold": (C.c_int, [_vp, _vp, _vp, _vp, C.c_double, C.c_int, _vp, _vp, _vp]),
     "scn_submanifold_convolution_bn_forward": (C.c_int, [_vp, _i64p, _i64p, _vp, _vp, _vp, _vp, _vp, _vp, C.c_double,
                                                          C.c_int, C.c_int, C.c_int, C.c_int, _vp,

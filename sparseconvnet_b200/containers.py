@@ -36,6 +36,18 @@ class Sequential(torch.nn.Sequential):
                 input = m.forward(input, bn=nxt)  # (no output rows: nothing to apply, as the BatchNorm itself)
                 i += 2
                 continue
+            # a JoinTable whose result goes straight into an eval-mode BatchNormalization: every joined tensor is
+            # normalised into its columns of the result, the concatenation itself is never written
+            if (Sequential.fuse and type(m) is JoinTable and isinstance(nxt, layers.BatchNormalization)
+                    and not m._forward_hooks and not m._forward_pre_hooks and isinstance(input, (list, tuple))
+                    and len(input) > 0 and all(t.features.nelement() > 0 and t.features.dim() == 2 for t in input)
+                    and nxt.fusable(input[0].features)
+                    and not any(layers.autograd.needs_grad(t.features) for t in input)):
+                joined = nxt.forward_joined(input)
+                if joined is not None:
+                    input = joined
+                    i += 2
+                    continue
             input = m(input)
             i += 1
         return input

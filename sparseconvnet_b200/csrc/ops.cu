@@ -484,6 +484,62 @@ int scn_batchnorm_forward(const float *in_features, float *out_features, int64_t
   return SCN_OK;
 }
 
+// Eval-mode BatchNorm (+ leaky ReLU) of the column-wise concatenation [a | b] without the concatenation being
+// written first: a JoinTable followed by a BatchNormalization as one pass (read a and b once, write the
+// result once; torch.cat + the stand-alone operator read and write the joined matrix twice).
+__global__ void __launch_bounds__(256)
+k_bn_apply_join(const float *__restrict__ a, int ca, const float *__restrict__ b, int cb, float *__restrict__ out,
+                long long n_rows, const float *__restrict__ running_mean, const float *__restrict__ running_var,
+                float eps, const float *__restrict__ weight, const float *__restrict__ bias, float leak) {
+  extern __shared__ float sh_wb[];  // [2][ca + cb]
+  const int C = ca + cb;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const float w = powf(running_var[c] + eps, -0.5f) * (weight ? weight[c] : 1.f);
+    sh_wb[c] = w;
+    sh_wb[C + c] = __fadd_rn(__fmul_rn(-running_mean[c], w), bias ? bias[c] : 0.f);
+  }
+  __syncthreads();
+  const int cv = C / 4, cav = ca / 4;
+  const long long total = n_rows * cv;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const long long r = idx / cv;
+    const int q = (int)(idx % cv), c = q * 4;
+    const float4 x = q < cav ? *reinterpret_cast<const float4 *>(a + r * ca + c)
+                             : *reinterpret_cast<const float4 *>(b + r * cb + (c - ca));
+    float4 y;
+    y.x = __fadd_rn(__fmul_rn(x.x, sh_wb[c + 0]), sh_wb[C + c + 0]);
+    y.y = __fadd_rn(__fmul_rn(x.y, sh_wb[c + 1]), sh_wb[C + c + 1]);
+    y.z = __fadd_rn(__fmul_rn(x.z, sh_wb[c + 2]), sh_wb[C + c + 2]);
+    y.w = __fadd_rn(__fmul_rn(x.w, sh_wb[c + 3]), sh_wb[C + c + 3]);
+    y.x *= (y.x > 0.f) ? 1.f : leak;
+    y.y *= (y.y > 0.f) ? 1.f : leak;
+    y.z *= (y.z > 0.f) ? 1.f : leak;
+    y.w *= (y.w > 0.f) ? 1.f : leak;
+    *reinterpret_cast<float4 *>(out + r * C + c) = y;
+  }
+}
+
+int scn_batchnorm_join_forward(const float *in_a, int planes_a, const float *in_b, int planes_b, float *out_features,
+                               int64_t n_rows, const float *running_mean, const float *running_var,
+                               const float *weight, const float *bias, double eps, double leakiness, void *stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SCN_REQUIRE(planes_a >= 4 && planes_b >= 4 && planes_a % 4 == 0 && planes_b % 4 == 0 && planes_a + planes_b <= 4096,
+              SCN_ERR_UNSUPPORTED, "plane counts %d + %d unsupported (multiples of four)", planes_a, planes_b);
+  SCN_REQUIRE(running_mean && running_var, SCN_ERR_BAD_ARG, "null statistics");
+  if (n_rows == 0) return SCN_OK;
+  SCN_REQUIRE(in_a && in_b && out_features, SCN_ERR_BAD_ARG, "null features");
+  SCN_REQUIRE((uintptr_t)in_a % 16 == 0 && (uintptr_t)in_b % 16 == 0 && (uintptr_t)out_features % 16 == 0,
+              SCN_ERR_BAD_ARG, "feature matrices must be 16-byte aligned");
+  const int C = planes_a + planes_b;
+  const long long work = n_rows * (C / 4);
+  const unsigned blocks = (unsigned)std::min<long long>(ceil_div(work, 256), 148 * 16);
+  SCN_LAUNCH(k_bn_apply_join, blocks, 256, sizeof(float) * 2 * C, stream, in_a, planes_a, in_b, planes_b, out_features,
+             n_rows, running_mean, running_var, (float)eps, weight, bias, (float)leakiness);
+  SCN_CUDA_CHECK(cudaGetLastError());
+  return SCN_OK;
+}
+
 int scn_batchnorm_backward(const float *in_features, float *d_in_features, const float *out_features,
                            const float *d_out_features, int64_t n_rows, int n_planes, int64_t in_stride,
                            int64_t out_stride, const float *save_mean, const float *save_invstd,

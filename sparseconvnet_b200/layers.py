@@ -342,6 +342,19 @@ class BatchNormalization(Module):
                 and self.running_mean.is_cuda and self.running_mean.device == features.device
                 and not self._forward_hooks and not self._forward_pre_hooks)
 
+    def forward_joined(self, inputs):
+        """This layer (eval mode) applied to the concatenation of `inputs` (what a JoinTable in front of
+        it would produce) without building the concatenation first."""
+        assert sum(i.features.size(1) for i in inputs) == self.nPlanes
+        features = SCN.batchnorm_concat([i.features.detach().contiguous() for i in inputs], self.running_mean,
+                                        self.running_var, optional_tensor(self, "weight"),
+                                        optional_tensor(self, "bias"), self.eps, self.leakiness)
+        if features is None:  # shapes the fused kernel does not take
+            return None
+        output = SparseConvNetTensor(metadata=inputs[0].metadata, spatial_size=inputs[0].spatial_size)
+        output.features = features
+        return output
+
     def forward(self, input):
         if input.features.nelement() == 0:
             return input
