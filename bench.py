@@ -41,19 +41,26 @@ UNIT = "voxels/s"
 # launches against their algorithmic bytes).  The traffic grows with the rows, like the
 # algorithmic bytes: DRAM sees input, rulebook and output about once, the gather's re-reads
 # (which the algorithmic figure counts per rule) hit L2.
-TRAFFIC_RATIO = {"k_conv_tma": 0.22, "k_conv_pipe_mma": 0.22, "k_conv_rows": 0.24, "k_conv_simt": 0.25}
+TRAFFIC_RATIO = {"k_conv_tma": 0.22, "k_conv_pipe_mma": 0.22, "k_conv_rows": 0.24, "k_conv_simt": 0.25,
+                 "k_conv_wide": 0.17}
 # (bound reported for the kernel, what the ncu captures show as its limiter)
 LIMITS = {
     "k_conv_tma": ("hbm", "shared-memory data pipe 77 % busy, tensor pipe 40-46 % (ncu, 4-room case)"),
     "k_conv_pipe_mma": ("hbm", "instruction issue and the shared-memory data pipe of small (offset, 128-row) steps"),
-    "k_conv_rows": ("hbm", "LSU data pipe 75 % busy (fragment loads, weight fragments from L2), warp-level tensor "
-                           "pipe 43-50 %; DRAM sees 0.24 of the algorithmic bytes, the gather's re-reads hit L2"),
+    "k_conv_rows": ("hbm", "no saturated pipe (ncu, 4-room case): warp-level tensor pipe 41-53 % active, LSU wavefronts "
+                           "39-47 % of peak, issue slots 42-57 %; the warp's dependent chain rulebook entry -> gather -> "
+                           "fragment loads -> bf16 split -> tensor instruction with 13-19 warps per SM; DRAM sees 0.19-0.24 "
+                           "of the algorithmic bytes, the gather's re-reads hit L2"),
+    "k_conv_wide": ("hbm", "the producer warps (no saturated pipe: tensor 38 %, LSU 34 %, issue slots 39 %); the MMA thread "
+                           "waits for full steps two thirds of the time"),
+    "k_conv_tc": ("hbm", "latency: few 256-row tiles per level (tensor pipe 13-16 %)"),
 }
 # what `dtype` says for each arithmetic mode: the type the path computes in, kernel by kernel
 DTYPE_LABEL = {
     "fp32": "f32 (fp32 FMA in every convolution)",
-    "tf32x3": "f32-class split arithmetic, fp32 accumulate: warp-level mma.sync (tf32 hi x hi + two bf16 cross "
-              "terms) for 32/64 output planes, tcgen05 three-term tf32 split in TMEM for wider layers",
+    "tf32x3": "f32-class split arithmetic, fp32 accumulate: every operand as two bf16 parts, three bf16 products "
+              "per term -- warp-level mma.sync.m16n8k16 for 32/64 output planes, tcgen05 kind::f16 with TMEM "
+              "accumulators for wider layers",
     "tf32": "tf32 (single pass, fp32 accumulate)",
     "bf16": "bf16 (single pass, fp32 accumulate)",
 }

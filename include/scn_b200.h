@@ -62,10 +62,16 @@ enum scn_status {
 /* arithmetic used inside the convolution kernels */
 enum scn_precision {
   SCN_PRECISION_FP32 = 0, /* fp32 FMA, fp32 accumulate (matches the reference's float path)  */
-  SCN_PRECISION_TF32 = 1, /* tcgen05 kind::tf32 tensor-core tiles, fp32 accumulate in TMEM   */
-  SCN_PRECISION_BF16 = 2, /* tcgen05 kind::f16 (bf16 operands), fp32 accumulate in TMEM      */
-  SCN_PRECISION_TF32X3 = 3 /* tcgen05 kind::tf32, three passes over the hi/lo split of both
-                             operands, fp32 accumulate in TMEM: fp32-class accuracy          */
+  SCN_PRECISION_TF32 = 1, /* one tf32 product, fp32 accumulate: warp-level mma.sync for 32 / 64 output
+                             planes, tcgen05 kind::tf32 with the accumulator in TMEM above          */
+  SCN_PRECISION_BF16 = 2, /* one bf16 product, fp32 accumulate: mma.sync for 32 / 64 output planes,
+                             tcgen05 kind::f16 with the accumulator in TMEM above                   */
+  SCN_PRECISION_TF32X3 = 3 /* fp32-class accuracy on the tensor paths (1e-4 of the reference's fp32
+                             results): every operand is split in two bf16 parts, x = h + m, and the
+                             three products h h, m h, h m are accumulated in fp32 -- warp-level
+                             mma.sync.m16n8k16 for 32 / 64 output planes, tcgen05 kind::f16 in TMEM
+                             for wider layers.  (The name is kept from the first form, three tf32
+                             products of a tf32 hi / lo split, which SCN_X3_FORM=tf32 still selects.) */
 };
 /* which convolution kernel the last convolution call of this thread ran (for profiling) */
 enum scn_conv_kernel {
@@ -239,7 +245,9 @@ SCN_API int scn_release_weight_token(uint64_t token, void *stream);
  * such answer on that metadata object.  scn_count_ticket_total waits for that one copy only (not
  * for the stream) and returns the number of rules; the ticket stays valid after the metadata
  * object is gone and is given back with scn_count_ticket_release.  Off by default: *macs is then
- * always the count.  No counterpart in the reference. */
+ * always the count.  The switch is process-wide: every client of the library in the process sees the
+ * deferred answers once one of them turns it on (the Python mirror does at import).  No counterpart
+ * in the reference. */
 SCN_API int scn_set_deferred_counts(int on);
 
 /* Arithmetic (an scn_precision value) of the input-gradient pass of the three convolution backward

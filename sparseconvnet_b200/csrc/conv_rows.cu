@@ -5,23 +5,29 @@
 // per-offset gather / GEMM / scatter-add is CPU/Convolution.cpp:137-148 and
 // CUDA/Convolution.cu:57-233,618-642).  The work is laid out by OUTPUT ROW, not by rule:
 //
-//   warp      32 consecutive output rows as two 16-row tiles of mma.sync.m16n8k8, their 32 x Cout
+//   warp      32 consecutive output rows as two 16-row tiles of mma.sync, their 32 x Cout
 //             accumulators in registers for the whole filter.  For every filter offset the warp
 //             gathers the input rows of its rows (16-byte cp.async into a private ring of stages,
 //             zero fill where the rulebook has no rule) and multiplies them with the offset's
 //             weights.  A 16-row tile without a rule for the offset is skipped: rows come sorted by
 //             coordinate, so the rules of an offset cluster (54 % of the (offset, 16-row tile) slots
 //             of an indoor scan hold a rule, at 62 % fill)
-//   weights   prepared once per call as the per-lane fragment image of (offset, 32-plane chunk)
-//             slabs, tf32 and bf16 parts ready (8 or 16 KB); every warp reads its B fragments
+//   weights   prepared (per call, or once per layer under a weight token) as the per-lane fragment
+//             image of (offset, 32-plane chunk) slabs: bf16 h / m pairs, 4 or 8 KB per slab (the
+//             tf32 form: tf32 and bf16 parts, twice that); every warp reads its B fragments
 //             straight from that image with 128-bit loads; they come from L2 (the slabs of the 20
 //             warps of an SM do not fit L1 beside the shared memory, hit rate 9 %; an L1 prefetch a
 //             step ahead made it slower), and the other warps cover the latency
 //   nothing   is shared between warps: no barrier, no shared-memory accumulator, no pair lists.
 //             A CTA is one warp; 12 to 21 of them are resident per SM
-//   arithmetic x = hi + lo with hi = x truncated to tf32; D += A_lo B + A B_lo + A_hi B_hi in fp32
-//             accumulators, the large term as tf32 m16n8k8, the two small ones as bf16 m16n8k16
-//             (see k_rows_prepare); 5e-6 of max against fp32
+//   arithmetic the fp32-class mode in its default form: x = h + m with h = bf16(x), m = bf16(x - h);
+//             D += A_m B_h + A_h B_m + A_h B_h as three bf16 m16n8k16 per 16 planes, fp32
+//             accumulators (TC_BF16X3; 2e-6 to 6e-6 of max against the reference's CPU operator).
+//             The other form (SCN_X3_FORM=tf32): x = hi + lo with hi = x truncated to tf32, the
+//             large term as two tf32 m16n8k8, the two small ones as one bf16 m16n8k16 each: four
+//             instructions per 16 planes and twice the weight image; 25 to 30 % slower
+//   store     bias, then optionally the scale / shift / leaky ReLU of the eval-mode BatchNorm that
+//             follows the layer, then each row once
 //   also here k_conv_rows_thin (first layers, at most four input planes) and k_conv_rows_scatter
 //             (Deconvolution with filter = stride, run from its input side)
 //
@@ -448,6 +454,7 @@ static int launch_rows(const float *in, int ld_in, long long n_in, float *out, i
     // more with 32 output planes), the rest of the 256 KB stays L1 for the weight image
     // with 64 output planes the registers of the three-term mode hold the SM to 12 warps (110 KB of rings): half
     // the SM's memory is enough and the other half serves the weight fragments as L1 (3 % faster)
+    // (measured with the bf16 form: carve-outs of 70, 80, 90 and 100 % give the same times within 2 %)
     SCN_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                                         NT > 4 ? (MODE == TC_TF32X3 ? 50 : MODE == TC_BF16X3 ? 70 : 80) : 80));
     if (dev < 64) configured[dev] = true;

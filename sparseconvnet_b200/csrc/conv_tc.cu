@@ -4,10 +4,10 @@
 // filter, so their accumulators live in tensor memory from the first filter offset to the last
 // and every output row is written to HBM exactly once.
 //
-// Orientation.  A tcgen05.mma instruction costs about the same ~150 cycles whatever its N
-// (measured: 152 cycles per instruction for N = 32 ... 256, tf32 and bf16 alike), so the wide
-// dimension has to be N.  Channel counts are small (32 ... 224) while rows are plentiful, hence
-// the product is computed transposed:
+// Orientation.  A tcgen05.mma instruction costs max(56, N / 2) cycles whatever its M and kind (measured
+// by scn_tc_probe_mma: 128 cycles at N = 256, a floor of 56 below N = 112), so the wide dimension has
+// to be N.  Channel counts are small (32 ... 224) while rows are plentiful, hence the product is
+// computed transposed:
 //     D^T[Cout x 256 rows] += W[k]^T[Cout x Cin-slice] * G^T[Cin-slice x 256 rows]
 // i.e. the MMA's A operand (M = 128 TMEM lanes) is the weight slab, its B operand (N = 256) the
 // gathered input rows.  TMEM lane = output plane, TMEM column = row of the tile.
@@ -28,9 +28,11 @@
 // Arithmetic modes:
 //   TF32    one pass, operands truncated to tf32 by the tensor core            (1e-2 class)
 //   BF16    operands rounded to bf16 while staging, fp32 accumulate            (1e-2 class)
-//   TF32X3  split a = a_hi + a_lo (both tf32-representable): D += W_hi*G_hi + W_hi*G_lo +
-//           W_lo*G_hi, fp32 accumulate -- recovers fp32-class accuracy (error ~2^-21 per
-//           product) on the tensor pipe, for the reference's fp32 parity bar.
+//   BF16X3  the fp32-class mode in its default form: a = h + m with h = bf16(a), m = bf16(a - h), both
+//           made in registers while staging; D += W_h*G_h + W_h*G_m + W_m*G_h, fp32 accumulate
+//           (what is dropped is 2^-17 of a product; half the instructions of TF32X3)
+//   TF32X3  the other form (SCN_X3_FORM=tf32): a = a_hi + a_lo with a_hi the tf32 truncation,
+//           D += W_hi*G_hi + W_hi*G_lo + W_lo*G_hi
 //
 // Every wait on an mbarrier is bounded; on expiry the kernel raises FLAG_TC_TIMEOUT, stops
 // issuing work, drains its own copies, frees its tensor memory and returns.
@@ -612,7 +614,7 @@ static int env_int(const char *name, int dflt) {
   return v ? atoi(v) : dflt;
 }
 
-// A tile costs K * Cin/8 (x3) tensor-core instructions of ~150 cycles however few rows it holds,
+// A tile costs K * Cin/16 x 3 tensor-core instructions of 128 cycles however few rows it holds,
 // so a level with fewer tiles than the GPU has SMs leaves most tensor cores idle for the whole
 // call.  Such calls split every tile's filter offsets over n CTAs; the CTAs write partial sums
 // and k_sum_partials adds them in a fixed order.  n minimises (waves of CTAs) x (offsets per
