@@ -164,6 +164,8 @@ def op_bytes(r):
         return r["sites"] * (8 + 16 + 16) + r.get("sites_out", 0) * (16 + 8 + 4 * r["offsets"])
     if k == "input_hash":
         return r["rows"] * r["cols"] * 8 + r["rows"] * 16 + r.get("sites", 0) * 8
+    if k == "rows_affine":
+        return r["rows"] * (r["nin"] + r["nout"]) * 4
     if k == "input_features":
         return (r["rows"] + r["sites"]) * r["planes"] * 4
     return 0.0
@@ -365,6 +367,12 @@ def main():
     net.to(dev)
     head.to(dev)
     head_wt = head.weight.detach().t().contiguous()
+    head_b = head.bias.detach()
+
+    def scores(x, out=None):
+        """The 20-class head on the library's rows-times-small-matrix kernel (one read of the rows, one
+        write of the scores; torch.nn.Linear's weight transposed)."""
+        return SCN.rows_affine(x, head_wt, head_b, out=out)
 
     class Job(object):
         """One rank's share of a batch: resident and pinned copies of its inputs, the gather buffers."""
@@ -398,9 +406,8 @@ def main():
             with torch.no_grad():
                 x = net(inp([c, f])).features
                 if self.gather is None:
-                    return head(x)
-                y = self.gather.block(x.shape[0])
-                torch.addmm(head.bias, x, head_wt, out=y)
+                    return scores(x)
+                y = scores(x, out=self.gather.block(x.shape[0]))
                 self.pending.append(self.gather.start(x.shape[0]))
                 if len(self.pending) > 1:
                     self.pending.pop(0).wait()
@@ -431,6 +438,7 @@ def main():
         barrier()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         l0 = SCN.launch_count()
+        w0 = SCN.host_wait_count()
         marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps - 1)]
         a.record()
         if begin:
@@ -449,6 +457,7 @@ def main():
         edges = [a] + marks + [b]
         timed.per_step = [round(edges[i].elapsed_time(edges[i + 1]), 3) for i in range(steps)]
         launches = SCN.launch_count() - l0
+        timed.host_waits = SCN.host_wait_count() - w0
         if world > 1:
             t = torch.tensor([ms], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -516,6 +525,7 @@ def main():
         sampler.start()
         ms, launches = timed(lambda: job.forward(job.coords_dev, job.feats_dev), steps, drain=job.drain)
         per_step = timed.per_step
+        measure.host_waits_per_step = timed.host_waits / float(steps)
         clocks = sampler.stop()
         loop = E2E(job)
         for _ in range(2):
@@ -538,10 +548,9 @@ def main():
     strong = None
     if world > 1:
         with torch.no_grad():
-            y_ref = head(net(inp([job.coords_dev, job.feats_dev])).features)       # the plain path, own rows
+            y_ref = scores(net(inp([job.coords_dev, job.feats_dev])).features)     # the plain path, own rows
             check = shard.RowGather(20, job.gather.capacity, dev, count_group=count_group, dst=None, depth=1)
-            torch.addmm(head.bias, net(inp([job.coords_dev, job.feats_dev])).features, head_wt,
-                        out=check.block(y_ref.shape[0]))
+            scores(net(inp([job.coords_dev, job.feats_dev])).features, out=check.block(y_ref.shape[0]))
             views, counts = check.start(y_ref.shape[0]).blocks()
             torch.cuda.synchronize()
         # every rank: its own block of the gathered buffer holds exactly the bits of its plain result;
@@ -735,7 +744,8 @@ def main():
             "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": int(job.coords_host.numel() * 8 + job.feats_host.numel() * 4),
                     "d2h_bytes_per_step": int(n_vox * 20 * 4)},
-            "gpu_launches": int(launches), "ms_each_step": per_step,
+            "gpu_launches": int(launches), "host_waits_per_step": measure.host_waits_per_step,
+            "ms_each_step": per_step,
             "roofline": roofline, "breakdown_ms_per_step": breakdown, "submanifold_conv": sub, "configs": configs,
             "variants_voxels_per_sec": variants, "training_step": training,
             "cpu_baseline": cpu, "clocks": clocks,

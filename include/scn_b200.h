@@ -97,6 +97,10 @@ SCN_API const char *scn_last_error(void);
 /* number of CUDA kernels this library has launched in this process so far (no counterpart in
  * the reference; used to report how many kernels a timed region ran) */
 SCN_API long long scn_launch_count(void);
+/* number of times this library has made the calling thread wait for the GPU so far (stream or event
+ * synchronisations: site counts of the input layer and of strided rulebooks, rule counts asked for
+ * before they landed, scn_md_poll_errors).  No counterpart in the reference. */
+SCN_API long long scn_host_wait_count(void);
 /* number of rulebooks this process has CONSTRUCTED so far (a lookup served from a metadata
  * object's cache does not count).  No counterpart in the reference; lets a profiler credit the
  * bytes of a rulebook build only to the call that built it. */
@@ -192,6 +196,19 @@ SCN_API int scn_md_strided_rulebook(scn_metadata *md, const int64_t *input_size,
                             const int64_t *output_size, const int64_t *filter_size,
                             const int64_t *filter_stride, void *stream, int64_t *n_active_out,
                             int64_t *n_rules);
+
+/* Builds, in one enqueued chain, the grids and rulebooks of up to `levels` consecutive levels of the same
+ * downsampling (filter_size == filter_stride in every dimension, each level's output size (in - f) / s +
+ * 1 being the next level's input size) below the grid of `input_size`: what an encoder's Convolutions
+ * would otherwise request one at a time through scn_md_strided_rulebook (Metadata<D>::getRuleBook,
+ * Metadata.cpp:492-518), each request ending in a wait for that level's site count.  The chain waits for
+ * `stream` once, for all counts together; the per-level calls that follow find their rulebooks built.
+ * Grids, row numbering and rulebooks are the ones the per-level calls would have made.  Where the chain
+ * does not apply (filter != stride, fewer than two levels left to build, no grid of `input_size`) nothing
+ * is built and the result is SCN_OK.  n_built (may be NULL) receives the number of levels built.  The
+ * reference has no such call; it is a hint for callers that know the shape of their network. */
+SCN_API int scn_md_strided_chain(scn_metadata *md, const int64_t *input_size, const int64_t *filter_size,
+                                 const int64_t *filter_stride, int levels, void *stream, int *n_built);
 
 /* Rulebook read-back in the reference's format (RuleBook = one flat list of
  * (input_row, output_row) int32 pairs per filter offset, Metadata.h:35).  The reference does
@@ -335,6 +352,15 @@ SCN_API int scn_batchnorm_join_forward(const float *in_a, int planes_a, const fl
                                        float *out_features, int64_t n_rows, const float *running_mean,
                                        const float *running_var, const float *weight, const float *bias,
                                        double eps, double leakiness, void *stream);
+/* out_features[r, :] = bias + in_features[r, :] * weight for a small weight matrix [n_in_planes]
+ * [n_out_planes] (row-major, n_out_planes <= 32, n_in_planes a multiple of four up to 256): the shape of
+ * NetworkInNetwork_updateOutput (sparseconvnet/SCN/sparseconvnet.h:51-53, CPU/NetworkInNetwork.cpp:7-23)
+ * with few output planes and of the per-voxel class head that follows a segmentation network.  bias may
+ * be null.  One read of the rows, one write of the result; wider products return SCN_ERR_UNSUPPORTED and
+ * belong to the dense matrix library, as in the reference. */
+SCN_API int scn_rows_affine_forward(const float *in_features, float *out_features, int64_t n_rows,
+                                    int n_in_planes, int n_out_planes, const float *weight, const float *bias,
+                                    void *stream);
 SCN_API int scn_submanifold_convolution_bn_forward(scn_metadata *md, const int64_t *spatial_size,
                                                    const int64_t *filter_size, const float *in_features,
                                                    float *out_features, const float *weight, const float *bias,

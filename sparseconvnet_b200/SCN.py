@@ -251,6 +251,11 @@ def launch_count():
     return lib.scn_launch_count()
 
 
+def host_wait_count():
+    """Times the library has made the calling thread wait for the GPU in this process so far."""
+    return lib.scn_host_wait_count()
+
+
 def _features(t, name):
     if not t.is_cuda:
         raise RuntimeError("%s must be a CUDA tensor: sparseconvnet_b200 has no CPU path" % name)
@@ -525,6 +530,31 @@ def SubmanifoldConvolution_updateOutput(inputSize, filterSize, m, input_features
     return result
 
 
+def strided_chain(m, inputSize, filterSize, filterStride, levels, device):
+    """Not in the reference: a hint from a caller that knows its network goes `levels` levels down with
+    the same filter = stride downsampling (a U-Net's encoder).  The grids and rulebooks of those levels
+    (Metadata<D>::getRuleBook, Metadata.cpp:492-518, once per level) are built in one enqueued chain with
+    a single wait for all the level counts; the Convolutions then find theirs in the cache.  Returns the
+    number of levels built (0 when there was nothing to chain)."""
+    if levels < 2:
+        return 0
+    built = C.c_int(0)
+    with torch.cuda.device(device), _timed("rules_strided", dict(
+            sites=0, sites_out=0, offsets=int(torch.as_tensor(filterSize).prod()), dim=m.dimension)) as info:
+        check(lib.scn_md_strided_chain(m._h, sizes(inputSize), sizes(filterSize), sizes(filterStride), int(levels),
+                                       _stream(), C.byref(built)))
+        info["built"] = built.value > 0
+        info["levels"] = built.value
+        if built.value and Profile.active is not None:  # all the levels' sites are this call's work
+            cur = [int(v) for v in inputSize]
+            for _ in range(built.value):
+                nxt = [(c - int(fs)) // int(st) + 1 for c, fs, st in zip(cur, filterSize, filterStride)]
+                info["sites"] += m.getNActive(torch.LongTensor(cur))
+                info["sites_out"] += m.getNActive(torch.LongTensor(nxt))
+                cur = nxt
+    return built.value
+
+
 def Convolution_updateOutput(inputSize, outputSize, filterSize, filterStride, m, input_features,
                              output_features, weight, bias, epilogue=None):
     """sparseconvnet.h:87-92.  `epilogue` (not in the reference): see batchnorm_fold."""
@@ -747,12 +777,47 @@ def SparseToDense_updateOutput(inputSize, m, input_features, output_features, nP
             output_features.zero_()
 
 
+def rows_affine_supported(features, weight):
+    """True when scn_rows_affine_forward takes the product features @ weight (fp32 on a GPU, at most 32
+    output planes, input planes a multiple of four up to 256)."""
+    return (features.is_cuda and features.dtype == torch.float32 and weight.dtype == torch.float32
+            and weight.dim() == 2 and features.dim() == 2 and features.size(1) == weight.size(0)
+            and 1 <= weight.size(1) <= 32 and weight.size(0) % 4 == 0 and 4 <= weight.size(0) <= 256)
+
+
+def rows_affine(features, weight, bias=None, out=None):
+    """out = bias + features @ weight for a weight matrix [nIn, nOut] with nOut <= 32, in one pass over
+    the rows (a NetworkInNetwork with few output planes, CPU/NetworkInNetwork.cpp:7-23; the per-voxel
+    class head of a segmentation network, with torch.nn.Linear's weight transposed).  Forward only.
+    ``out`` may be any [n, nOut] fp32 matrix with contiguous rows, for instance a block of a larger buffer."""
+    f = _features(features, "features")
+    w = _features(weight, "weight")
+    if not rows_affine_supported(f, w):
+        raise RuntimeError("rows_affine: unsupported shapes %s x %s" % (tuple(f.shape), tuple(w.shape)))
+    n, cout = f.size(0), w.size(1)
+    if out is None:
+        out = f.new_empty(n, cout)
+    elif out.shape != (n, cout) or not out.is_contiguous() or out.dtype != torch.float32 or out.device != f.device:
+        raise RuntimeError("rows_affine: out must be a contiguous fp32 [%d, %d] matrix on %s" % (n, cout, f.device))
+    b = _features(bias, "bias") if bias is not None else None
+    if b is not None and b.numel() != cout:
+        raise RuntimeError("rows_affine: bias must have %d entries" % cout)
+    with torch.cuda.device(f.device):
+        with _timed("rows_affine", dict(rows=n, nin=f.size(1), nout=cout)):
+            check(lib.scn_rows_affine_forward(_ptr(f), _ptr(out), n, f.size(1), cout, _ptr(w), _ptr(b), _stream()))
+    return out
+
+
 def NetworkInNetwork_updateOutput(input_features, output_features, weight, bias):
     """sparseconvnet.h:51-53.  The reference itself hands this 1x1 convolution to the dense
     matrix library (CPU/NetworkInNetwork.cpp:7-23: ``addmm_``); so does this."""
     f = _features(input_features, "input_features")
     n, cout = f.size(0), weight.size(1)
     output_features.resize_(n, cout)
+    if rows_affine_supported(f, weight):
+        rows_affine(f, weight.detach(), bias.detach() if bias is not None and bias.numel() else None,
+                    out=output_features)
+        return float(n * f.size(1) * cout)
     if bias is not None and bias.numel():
         output_features.copy_(bias.detach().expand(n, cout))
     else:

@@ -19,6 +19,7 @@ SIGNATURES = {
     "scn_last_error": (C.c_char_p, []),
     "scn_launch_count": (C.c_longlong, []),
     "scn_rulebook_build_count": (C.c_longlong, []),
+    "scn_host_wait_count": (C.c_longlong, []),
     "scn_last_conv_kernel": (C.c_int, []),
     "scn_tc_probe_mma": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp,
                                    C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double)]),
@@ -47,6 +48,7 @@ SIGNATURES = {
     "scn_md_spatial_locations": (C.c_int, [_vp, _i64p, _vp, _vp]),
     "scn_md_submanifold_rulebook": (C.c_int, [_vp, _i64p, _i64p, _vp, _i64p]),
     "scn_md_strided_rulebook": (C.c_int, [_vp, _i64p, _i64p, _i64p, _i64p, _vp, _i64p, _i64p]),
+    "scn_md_strided_chain": (C.c_int, [_vp, _i64p, _i64p, _i64p, C.c_int, _vp, C.POINTER(C.c_int)]),
     "scn_md_rulebook_export": (C.c_int, [_vp, C.c_int, _i64p, _i64p, _i64p, _i64p, _i64p, _vp, _vp]),
     "scn_submanifold_convolution_forward": (C.c_int, [_vp, _i64p, _i64p, _vp, _vp, _vp, _vp, C.c_int,
                                                       C.c_int, C.c_int, C.c_int, _vp,
@@ -61,6 +63,7 @@ SIGNATURES = {
                                             C.POINTER(C.c_double)]),
     "scn_batchnorm_join_forward": (C.c_int, [_vp, C.c_int, _vp, C.c_int, _vp, C.c_int64, _vp, _vp, _vp, _vp, C.c_double,
                                              C.c_double, _vp]),
+    "scn_rows_affine_forward": (C.c_int, [_vp, _vp, C.c_int64, C.c_int, C.c_int, _vp, _vp, _vp]),
     "scn_batchnorm_fold": (C.c_int, [_vp, _vp, _vp, _vp, C.c_double, C.c_int, _vp, _vp, _vp]),
     "scn_submanifold_convolution_bn_forward": (C.c_int, [_vp, _i64p, _i64p, _vp, _vp, _vp, _vp, _vp, _vp, C.c_double,
                                                          C.c_int, C.c_int, C.c_int, C.c_int, _vp,

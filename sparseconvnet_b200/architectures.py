@@ -111,6 +111,11 @@ def UNet(dimension, reps, nPlanes, residual_blocks=False, downsample=[2, 2], lea
                   .add(scn.BatchNormLeakyReLU(a, leakiness=leakiness))
                   .add(scn.SubmanifoldConvolution(dimension, a, b, 3, False)))
 
+    def down(planes):
+        conv = scn.Convolution(dimension, planes[0], planes[1], downsample[0], downsample[1], False)
+        conv.levels_below = len(planes) - 1  # the encoder goes this many levels further down
+        return conv
+
     def level(planes, n_in=-1):
         m = scn.Sequential()
         for _ in range(reps):
@@ -119,7 +124,7 @@ def UNet(dimension, reps, nPlanes, residual_blocks=False, downsample=[2, 2], lea
         if len(planes) > 1:
             down_up = (scn.Sequential()
                        .add(scn.BatchNormLeakyReLU(planes[0], leakiness=leakiness))
-                       .add(scn.Convolution(dimension, planes[0], planes[1], downsample[0], downsample[1], False))
+                       .add(down(planes))
                        .add(level(planes[1:]))
                        .add(scn.BatchNormLeakyReLU(planes[1], leakiness=leakiness))
                        .add(scn.Deconvolution(dimension, planes[1], planes[0], downsample[0], downsample[1], False)))
@@ -149,6 +154,11 @@ def FullyConvolutionalNet(dimension, reps, nPlanes, residual_blocks=False, downs
             m.add(scn.Sequential().add(scn.BatchNormReLU(a))
                   .add(scn.SubmanifoldConvolution(dimension, a, b, 3, False)))
 
+    def down(planes):
+        conv = scn.Convolution(dimension, planes[0], planes[1], downsample[0], downsample[1], False)
+        conv.levels_below = len(planes) - 1
+        return conv
+
     def level(planes):
         m = scn.Sequential()
         for _ in range(reps):
@@ -156,7 +166,7 @@ def FullyConvolutionalNet(dimension, reps, nPlanes, residual_blocks=False, downs
         if len(planes) > 1:
             deeper = (scn.Sequential()
                       .add(scn.BatchNormReLU(planes[0]))
-                      .add(scn.Convolution(dimension, planes[0], planes[1], downsample[0], downsample[1], False))
+                      .add(down(planes))
                       .add(level(planes[1:]))
                       .add(scn.UnPooling(dimension, downsample[0], downsample[1])))
             m.add(scn.ConcatTable().add(scn.Identity()).add(deeper))

@@ -43,6 +43,9 @@ void set_error(const char *fmt, ...);
 // Every kernel launch of the library goes through this macro so that the number of launches
 // can be read back (scn_launch_count), e.g. to state how many kernels a timed region ran.
 void note_launch();
+// Every place where the library makes the calling thread wait for the GPU (a stream or event
+// synchronisation) notes it; scn_host_wait_count reads the total.
+void note_host_wait();
 #define SCN_LAUNCH(kernel, grid, block, smem, stream, ...)                                      \
   do {                                                                                         \
     scn::note_launch();                                                                        \

@@ -104,7 +104,8 @@ static int ensure_scratch(scn_metadata *md, cudaStream_t stream) {
 // kernel into pinned host memory that is mapped into the device's address space, not copied by
 // cudaMemcpy: a device-to-host copy queues on the copy engine behind whatever the application is
 // copying at the time (a previous batch's 127 MB of results held every such read-back up for 2 ms,
-// seven times per U-Net forward).  Slots of 32 bytes from slabs that are never given back.
+// seven times per U-Net forward).  Slots of 256 bytes from slabs that are never given back.
+constexpr int kMailboxBytes = 256;  // 64 integers: flag word + the counts of a whole chain of levels
 namespace {
 struct MailboxPool {
   std::mutex mu;
@@ -122,7 +123,7 @@ static int mailbox_acquire(int **slot) {
   if (P.free_slots.empty()) {
     int *slab = nullptr;
     SCN_CUDA_CHECK(cudaHostAlloc((void **)&slab, 4096, cudaHostAllocMapped | cudaHostAllocPortable));
-    for (int i = 0; i < 4096 / 32; ++i) P.free_slots.push_back(slab + i * 8);
+    for (int i = 0; i < 4096 / kMailboxBytes; ++i) P.free_slots.push_back(slab + i * (kMailboxBytes / 4));
   }
   *slot = P.free_slots.back();
   P.free_slots.pop_back();
@@ -151,6 +152,7 @@ static int fetch_flags(scn_metadata *md, cudaStream_t stream, int *flags, int *s
   SCN_CUDA_CHECK(cudaHostGetDevicePointer((void **)&mailbox_dev, md->mailbox, 0));
   SCN_LAUNCH(k_post_scalars, 1, 1, 0, stream, md->flags_dev, scalars4 ? md->scalars_dev : nullptr, mailbox_dev);
   SCN_CUDA_CHECK(cudaGetLastError());
+  note_host_wait();
   SCN_CUDA_CHECK(cudaStreamSynchronize(stream));
   const volatile int *host = md->mailbox;
   *flags = host[0];
@@ -258,18 +260,30 @@ __global__ void k_flag_first(const Slot *__restrict__ slots, const int *__restri
   flag[i] = (s >= 0 && slots[s].aux == (unsigned)i) ? 1 : 0;
 }
 
-// Rows that were the first to touch their site give the site its output row number (rank in
-// input order), which is the numbering of the reference (one counter over the whole input,
-// IOLayersRules.h:69-72,84-87).
-__global__ void k_number_input_sites(Slot *slots, const int *__restrict__ slot_of,
-                                     const int *__restrict__ flag, const int *__restrict__ rank,
-                                     long long n, unsigned long long *__restrict__ row_keys) {
-  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n || !flag[i]) return;
-  int s = slot_of[i];
-  int r = rank[i];
-  slots[s].row = r;
-  row_keys[r] = slots[s].key;
+// The row that touched a site first gives the site its row number: its rank among such rows in input
+// order, which is the numbering of the reference (one counter over the whole input,
+// IOLayersRules.h:69-72,84-87; one per output grid, ConvolutionRules.h:24-30).  One thread per table
+// SLOT, not per candidate: the table is read and written front to back, and what is reached at random
+// (the rank of the slot's first toucher, the row -> key array) is a few MB that stay in L2.  The
+// candidate-order form of this pass (a random read-modify-write of a slot per numbered site) was bound by
+// the DRAM's random-access rate: 198 us against 142 us for the inserts themselves at 1.6 M sites.
+// `capacity`: rows the output arrays were sized for; a site numbered beyond it (a chain level that
+// shrank less than guessed) is not written and raises FLAG_TABLE_FULL in `level_flags`.
+__global__ void k_number_slots(Slot *slots, long long n_slots, const int *__restrict__ rank,
+                               long long capacity, int *level_flags,
+                               unsigned long long *__restrict__ row_keys) {
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n_slots) return;
+  const uint4 v = *reinterpret_cast<const uint4 *>(slots + idx);
+  const unsigned long long key = ((unsigned long long)v.y << 32) | v.x;
+  if (key == kEmptyKey || v.w == 0xFFFFFFFFu) return;
+  const int r = rank[v.w];
+  if (r >= capacity) {
+    atomicOr(level_flags, FLAG_TABLE_FULL);
+    return;
+  }
+  slots[idx].row = r;
+  row_keys[r] = key;
 }
 
 __global__ void k_count_per_site(const Slot *__restrict__ slots, const int *__restrict__ slot_of,
@@ -410,10 +424,17 @@ static int md_input_layer(scn_metadata *md, const int64_t *spatial_size, const i
     SCN_TRY(device_alloc((void **)&rank, sizeof(int) * (size_t)n, stream));
     SCN_LAUNCH(k_flag_first, blocks, threads, 0, stream, g.table.slots, slot_of, n, flag);
     SCN_TRY(exclusive_scan_i32(flag, rank, n, &md->scalars_dev[0], stream));
-    SCN_LAUNCH(k_number_input_sites, blocks, threads, 0, stream, g.table.slots, slot_of, flag, rank, n, g.row_keys);
+    const long long n_slots = 2 * (long long)g.table.n_buckets;
+    SCN_LAUNCH(k_number_slots, (unsigned)ceil_div(n_slots, threads), threads, 0, stream, g.table.slots, n_slots, rank, (long long)n, md->flags_dev, g.row_keys);
     SCN_CUDA_CHECK(cudaGetLastError());
   }
 
+  // stream-ordered: what only the kernels above read goes back before the host waits
+  device_free(staged, stream);
+  device_free(flag, stream);
+  device_free(rank, stream);
+  staged = nullptr;
+  flag = rank = nullptr;
   int flags = 0, sc[4];
   SCN_TRY(fetch_flags(md, stream, &flags, sc));
   long long active = (mode == 0) ? n : (n > 0 ? sc[0] : 0);
@@ -435,10 +456,7 @@ static int md_input_layer(scn_metadata *md, const int64_t *spatial_size, const i
     SCN_LAUNCH(k_sort_segments, sblocks, threads, 0, stream, md->input_csr_start, active, md->input_csr_rows);
     SCN_CUDA_CHECK(cudaGetLastError());
   }
-  device_free(staged, stream);
   device_free(slot_of, stream);
-  device_free(flag, stream);
-  device_free(rank, stream);
   device_free(cursor, stream);
   int st = flags_to_status(flags);
   if (st != SCN_OK) {
@@ -639,56 +657,76 @@ __device__ inline bool strided_target(const KeyLayout &L, const FilterDesc &F, c
   return true;
 }
 
+// The builders of a strided rulebook take the number of input sites either from the host (`n_in`,
+// n_in_dev null) or, inside a chain of levels whose counts the host has not seen yet, from the device
+// (*n_in_dev, with `n_in` the host's upper bound that sized the launch and the arrays): candidates
+// between the real count and the bound are marked "no site" so that the scan over the bound counts
+// only real ones.
+__device__ __forceinline__ long long sites_here(const int *n_dev, long long bound) {
+  if (!n_dev) return bound;
+  long long n = *n_dev;
+  return n < bound ? n : bound;
+}
+
 __global__ void k_strided_insert(KeyLayout Lin, KeyLayout Lout, FilterDesc F, HashTable Tout,
                                  const unsigned long long *__restrict__ in_keys, long long n_in,
-                                 int *__restrict__ slot_of, int *flags) {
+                                 const int *__restrict__ n_in_dev, int *__restrict__ slot_of, int *flags) {
   long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (id >= n_in * F.tmax) return;
+  if (id >= sites_here(n_in_dev, n_in) * F.tmax) {
+    slot_of[id] = -1;
+    return;
+  }
   long long i = id / F.tmax;
   int t = (int)(id % F.tmax);
   unsigned long long key = in_keys[i];
-  int s_out = -1;
+  unsigned long long okey = kEmptyKey;
   if (key != kEmptyKey) {
     int x[kMaxDim], o[kMaxDim], b, k;
     unpack_key(Lin, key, x, b);
-    if (strided_target(Lin, F, x, t, o, k)) {
-      long long s = hash_insert(Tout, pack_key(Lout, o, b));
-      if (s < 0)
-        atomicOr(flags, FLAG_TABLE_FULL);
-      else {
-        s_out = (int)s;
-        atomicMin(&Tout.slots[s].aux, (unsigned)id);
-      }
+    if (strided_target(Lin, F, x, t, o, k)) okey = pack_key(Lout, o, b);
+  }
+  // Candidates of one warp that name the same output site (neighbouring input rows usually do) insert
+  // it once: the lowest lane of the group, which also holds the group's smallest id, does the insert
+  // and hands the slot to the others.
+  const unsigned peers = __match_any_sync(__activemask(), okey);
+  const int leader = __ffs(peers) - 1;
+  int s_out = -1;
+  if (okey != kEmptyKey && (int)(threadIdx.x & 31) == leader) {
+    long long s = hash_insert(Tout, okey);
+    if (s < 0)
+      atomicOr(flags, FLAG_TABLE_FULL);
+    else {
+      s_out = (int)s;
+      atomicMin(&Tout.slots[s].aux, (unsigned)id);
     }
   }
-  slot_of[id] = s_out;
-}
-
-__global__ void k_strided_number(Slot *slots, const int *__restrict__ slot_of,
-                                 const int *__restrict__ flag, const int *__restrict__ rank,
-                                 long long n_ids, unsigned long long *__restrict__ out_keys) {
-  long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (id >= n_ids || !flag[id]) return;
-  int s = slot_of[id];
-  int r = rank[id];
-  slots[s].row = r;
-  out_keys[r] = slots[s].key;
+  slot_of[id] = __shfl_sync(peers, s_out, leader);
 }
 
 __global__ void k_strided_fill(KeyLayout Lin, FilterDesc F, const Slot *__restrict__ slots,
                                const unsigned long long *__restrict__ in_keys,
                                const int *__restrict__ slot_of, long long n_in, long long n_out,
+                               const int *__restrict__ n_out_dev, long long capacity,
                                int *__restrict__ nbr, unsigned long long *counts) {
   long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (id >= n_in * F.tmax) return;
   int s = slot_of[id];
   if (s < 0) return;
+  if (n_out_dev) {  // inside a chain: the level's row count is on the device only
+    n_out = *n_out_dev;
+    if (n_out > capacity) return;  // the level overflowed its arrays and will be rebuilt
+  }
   long long i = id / F.tmax;
   int t = (int)(id % F.tmax);
   int x[kMaxDim], o[kMaxDim], b, k;
   unpack_key(Lin, in_keys[i], x, b);
   strided_target(Lin, F, x, t, o, k);
-  int orow = slots[s].row;
+  // one read of the slot per group of lanes that share it
+  const unsigned same = __match_any_sync(__activemask(), s);
+  const int first = __ffs(same) - 1;
+  int orow = ((int)(threadIdx.x & 31) == first) ? slots[s].row : 0;
+  orow = __shfl_sync(same, orow, first);
   nbr[(long long)k * n_out + orow] = (int)i;
   // one counter update per distinct offset in the warp
   unsigned peers = __match_any_sync(__activemask(), k);
@@ -753,7 +791,7 @@ int get_strided_rulebook(scn_metadata *md, const int64_t *input_size, const int6
     long long expect = n_in;
     for (int attempt = 0;; ++attempt) {
       SCN_TRY(alloc_table(gout.table, expect, stream));
-      SCN_LAUNCH(k_strided_insert, blocks, threads, 0, stream, gin->layout, gout.layout, F, gout.table, gin->row_keys, n_in, slot_of, md->flags_dev);
+      SCN_LAUNCH(k_strided_insert, blocks, threads, 0, stream, gin->layout, gout.layout, F, gout.table, gin->row_keys, n_in, nullptr, slot_of, md->flags_dev);
       SCN_LAUNCH(k_flag_first, blocks, threads, 0, stream, gout.table.slots, slot_of, n_ids, flag);
       SCN_TRY(exclusive_scan_i32(flag, rank, n_ids, &md->scalars_dev[0], stream));
       SCN_CUDA_CHECK(cudaGetLastError());
@@ -792,8 +830,9 @@ int get_strided_rulebook(scn_metadata *md, const int64_t *input_size, const int6
   SCN_CUDA_CHECK(cudaMemsetAsync(rb.counts_dev, 0, sizeof(unsigned long long) * (size_t)K, stream));
   if (n_ids > 0) {
     unsigned blocks = (unsigned)ceil_div(n_ids, threads);
-    SCN_LAUNCH(k_strided_number, blocks, threads, 0, stream, gout.table.slots, slot_of, flag, rank, n_ids, gout.row_keys);
-    SCN_LAUNCH(k_strided_fill, blocks, threads, 0, stream, gin->layout, F, gout.table.slots, gin->row_keys, slot_of, n_in, n_out, rb.nbr, rb.counts_dev);
+    const long long n_slots = 2 * (long long)gout.table.n_buckets;
+    SCN_LAUNCH(k_number_slots, (unsigned)ceil_div(n_slots, threads), threads, 0, stream, gout.table.slots, n_slots, rank, n_out, md->flags_dev, gout.row_keys);
+    SCN_LAUNCH(k_strided_fill, blocks, threads, 0, stream, gin->layout, F, gout.table.slots, gin->row_keys, slot_of, n_in, n_out, nullptr, n_out, rb.nbr, rb.counts_dev);
     SCN_CUDA_CHECK(cudaGetLastError());
   }
   device_free(slot_of, stream);
@@ -802,6 +841,197 @@ int get_strided_rulebook(scn_metadata *md, const int64_t *input_size, const int6
   md->grids[okey] = gout;
   rb.built = true;
   g_rulebook_builds.fetch_add(1);
+  return SCN_OK;
+}
+
+// ---- a chain of strided levels ---------------------------------------------------------------
+// A U-Net asks for the same filter = stride rulebook at every level, each level's input being the last
+// level's output.  Built one call at a time, every level ends with the host waiting for its row count
+// (the next level's arrays and launches are sized by it), the GPU idling through each round trip.
+// Here the whole chain is enqueued at once: level l reads its number of input sites from the device
+// (`lev[l]`), its launches and arrays are sized by a bound the host knows, and one mailbox read at the
+// end fetches every level's count.  With disjoint windows (filter == stride) a level has at most as
+// many sites as its input; the arrays are sized for half of the input bound (surfaces and volumes
+// shrink by 2.5x to 8x per level in 3-D), and a level that shrank less raises its own flag, after
+// which that level and the deeper ones are enqueued again with the safe bound.  Same kernels, same
+// numbering (first touch in input-row order) as one call per level.
+constexpr int kMaxChain = 16;
+
+struct ChainLevel {
+  std::vector<int64_t> in_size, out_size;
+  FilterDesc F{};
+  long long K = 1;
+  Grid gout;
+  Rulebook rb;
+  long long bound_in = 0, cap_out = 0;
+  int *slot_of = nullptr, *flag = nullptr, *rank = nullptr;
+};
+
+__global__ void k_chain_init(int *lev, int n_ints, int n0) {
+  for (int i = threadIdx.x; i < n_ints; i += blockDim.x) lev[i] = i == 0 ? n0 : 0;
+}
+
+__global__ void k_chain_post(const int *lev, int n_ints, volatile int *mailbox) {
+  for (int i = threadIdx.x; i < n_ints; i += blockDim.x) mailbox[i] = lev[i];
+  __threadfence_system();
+}
+
+static void chain_free_level(ChainLevel &lv, bool keep_result, cudaStream_t stream) {
+  device_free(lv.slot_of, stream);
+  device_free(lv.flag, stream);
+  device_free(lv.rank, stream);
+  lv.slot_of = lv.flag = lv.rank = nullptr;
+  if (!keep_result) {
+    free_grid(lv.gout, stream);
+    free_rulebook(lv.rb, stream);
+  }
+}
+
+static int chain_enqueue(scn_metadata *md, const Grid *gin, std::vector<ChainLevel> &plan, int *lev,
+                         cudaStream_t stream) {
+  const int L = (int)plan.size(), threads = 256;
+  SCN_LAUNCH(k_chain_init, 1, 64, 0, stream, lev, 2 * L + 1, (int)gin->n_active);
+  const unsigned long long *in_keys = gin->row_keys;
+  KeyLayout Lin = gin->layout;
+  for (int l = 0; l < L; ++l) {
+    ChainLevel &lv = plan[l];
+    const size_t n_ids = (size_t)std::max<long long>(lv.bound_in, 1), cap = (size_t)std::max<long long>(lv.cap_out, 1);
+    SCN_TRY(device_alloc((void **)&lv.slot_of, sizeof(int) * n_ids, stream));
+    SCN_TRY(device_alloc((void **)&lv.flag, sizeof(int) * n_ids, stream));
+    SCN_TRY(device_alloc((void **)&lv.rank, sizeof(int) * n_ids, stream));
+    SCN_TRY(alloc_table(lv.gout.table, lv.cap_out, stream));
+    SCN_TRY(device_alloc((void **)&lv.gout.row_keys, sizeof(unsigned long long) * cap, stream));
+    const size_t nbr_bytes = sizeof(int) * (size_t)lv.K * cap;
+    SCN_TRY(device_alloc((void **)&lv.rb.nbr, nbr_bytes, stream));
+    SCN_CUDA_CHECK(cudaMemsetAsync(lv.rb.nbr, 0xFF, nbr_bytes, stream));
+    SCN_TRY(device_alloc((void **)&lv.rb.counts_dev, sizeof(unsigned long long) * (size_t)lv.K, stream));
+    SCN_CUDA_CHECK(cudaMemsetAsync(lv.rb.counts_dev, 0, sizeof(unsigned long long) * (size_t)lv.K, stream));
+    if (lv.bound_in > 0) {
+      const unsigned blocks = (unsigned)ceil_div(lv.bound_in, threads);
+      int *n_in_dev = lev + l, *n_out_dev = lev + l + 1, *level_flags = lev + L + 1 + l;
+      SCN_LAUNCH(k_strided_insert, blocks, threads, 0, stream, Lin, lv.gout.layout, lv.F, lv.gout.table, in_keys, lv.bound_in, n_in_dev, lv.slot_of, level_flags);
+      SCN_LAUNCH(k_flag_first, blocks, threads, 0, stream, lv.gout.table.slots, lv.slot_of, lv.bound_in, lv.flag);
+      SCN_TRY(exclusive_scan_i32(lv.flag, lv.rank, lv.bound_in, n_out_dev, stream));
+      const long long n_slots = 2 * (long long)lv.gout.table.n_buckets;
+      SCN_LAUNCH(k_number_slots, (unsigned)ceil_div(n_slots, threads), threads, 0, stream, lv.gout.table.slots, n_slots, lv.rank, lv.cap_out, level_flags, lv.gout.row_keys);
+      SCN_LAUNCH(k_strided_fill, blocks, threads, 0, stream, Lin, lv.F, lv.gout.table.slots, in_keys, lv.slot_of, lv.bound_in, 0ll, n_out_dev, lv.cap_out, lv.rb.nbr, lv.rb.counts_dev);
+      SCN_CUDA_CHECK(cudaGetLastError());
+    }
+    // stream-ordered: the scratch goes back behind the level's kernels, before the host waits
+    device_free(lv.slot_of, stream);
+    device_free(lv.flag, stream);
+    device_free(lv.rank, stream);
+    lv.slot_of = lv.flag = lv.rank = nullptr;
+    in_keys = lv.gout.row_keys;
+    Lin = lv.gout.layout;
+  }
+  return SCN_OK;
+}
+
+// Builds up to `levels` consecutive rulebooks of (filter_size, filter_stride) starting at the grid of
+// `input_size`, each level's output size (in - f) / s + 1.  Does nothing (SCN_OK) where the chain does
+// not apply -- filter != stride, fewer than two levels to build, no grid, rulebooks already there --
+// because the per-level call that follows builds or reports whatever is left.
+int build_strided_chain(scn_metadata *md, const int64_t *input_size, const int64_t *filter_size,
+                        const int64_t *filter_stride, int levels, cudaStream_t stream, int *n_built) {
+  if (n_built) *n_built = 0;
+  SCN_TRY(md_touch(md, stream));
+  const int dim = md->dim;
+  for (int d = 0; d < dim; ++d)
+    if (filter_size[d] != filter_stride[d] || filter_size[d] < 1 || filter_size[d] > 127) return SCN_OK;
+  levels = std::min(levels, kMaxChain);
+  std::vector<int64_t> start(input_size, input_size + dim);
+  bool safe = false;
+  while (levels >= 2) {
+    Grid *gin = find_grid(md, start.data());
+    if (!gin || gin->n_active >= (1ll << 31)) return SCN_OK;
+    // ---- plan: sizes, layouts and bounds of the levels that can be chained
+    std::vector<ChainLevel> plan;
+    std::vector<int64_t> cur = start;
+    long long bound = gin->n_active;
+    for (int l = 0; l < levels; ++l) {
+      ChainLevel lv;
+      lv.in_size = cur;
+      lv.out_size.resize(dim);
+      bool ok = true;
+      lv.F.tmax = 1;
+      for (int d = 0; d < dim; ++d) {
+        const int64_t f = filter_size[d];
+        if (cur[d] < f || (cur[d] - f) % f != 0) ok = false;
+        lv.out_size[d] = ok ? (cur[d] - f) / f + 1 : 1;
+        if (lv.out_size[d] > INT_MAX) ok = false;
+        lv.F.f[d] = lv.F.s[d] = (int)f;
+        lv.F.out_size[d] = (int)lv.out_size[d];
+        lv.F.tdim[d] = 1;
+        lv.K *= f;
+      }
+      if (!ok || lv.K > 4096) break;
+      auto found = md->strided_rules.find(make_key(dim, cur.data(), filter_size, filter_stride));
+      if (found != md->strided_rules.end() && found->second.built) break;
+      if (md->grids.count(make_key(dim, lv.out_size.data()))) break;
+      if (make_layout(dim, lv.out_size.data(), lv.gout.layout) != SCN_OK) break;
+      if (!(lv.gout.layout.batch_bits >= gin->layout.batch_bits ||
+            gin->batch_size <= (1ll << lv.gout.layout.batch_bits)))
+        break;
+      lv.bound_in = bound;
+      lv.cap_out = safe ? bound : std::max((bound + 1) / 2, std::min<long long>(bound, 4096));
+      bound = lv.cap_out;
+      cur = lv.out_size;
+      plan.push_back(std::move(lv));
+    }
+    const int L = (int)plan.size();
+    if (L < 2) return SCN_OK;
+    SCN_TRY(ensure_scratch(md, stream));
+    if (!md->mailbox) SCN_TRY(mailbox_acquire(&md->mailbox));
+    int *mailbox_dev = nullptr;
+    SCN_CUDA_CHECK(cudaHostGetDevicePointer((void **)&mailbox_dev, md->mailbox, 0));
+    int *lev = nullptr;
+    SCN_TRY(device_alloc((void **)&lev, sizeof(int) * (2 * L + 1), stream));
+    int st = chain_enqueue(md, gin, plan, lev, stream);
+    if (st == SCN_OK) {
+      SCN_LAUNCH(k_chain_post, 1, 64, 0, stream, lev, 2 * L + 1, mailbox_dev);
+      note_host_wait();
+      if (cudaGetLastError() != cudaSuccess || cudaStreamSynchronize(stream) != cudaSuccess) {
+        set_error("strided chain: CUDA error while waiting for the level counts");
+        st = SCN_ERR_CUDA;
+      }
+    }
+    device_free(lev, stream);
+    if (st != SCN_OK) {
+      for (auto &lv : plan) chain_free_level(lv, false, stream);
+      return st;
+    }
+    const volatile int *host = md->mailbox;
+    int good = 0;
+    while (good < L && host[L + 1 + good] == 0 && host[good + 1] <= plan[good].cap_out) ++good;
+    long long n_in = gin->n_active;
+    const long long batch_size = gin->batch_size;
+    for (int l = 0; l < L; ++l) {
+      ChainLevel &lv = plan[l];
+      if (l < good) {
+        const long long n_out = host[l + 1];
+        lv.gout.n_active = n_out;
+        lv.gout.batch_size = batch_size;
+        lv.rb.n_offsets = (int)lv.K;
+        lv.rb.n_in = n_in;
+        lv.rb.n_out = n_out;
+        lv.rb.built = true;
+        chain_free_level(lv, true, stream);
+        md->grids[make_key(dim, lv.out_size.data())] = lv.gout;
+        md->strided_rules[make_key(dim, lv.in_size.data(), filter_size, filter_stride)] = lv.rb;
+        g_rulebook_builds.fetch_add(1);
+        if (n_built) ++*n_built;
+        n_in = n_out;
+      } else {
+        chain_free_level(lv, false, stream);
+      }
+    }
+    if (good == L) return SCN_OK;
+    // a level shrank less than guessed: that level and the deeper ones again, arrays sized by the input
+    start = plan[good].in_size;
+    levels = L - good;
+    safe = true;
+  }
   return SCN_OK;
 }
 
@@ -902,6 +1132,7 @@ void count_ticket_release(CountTicket *t) {
 }
 
 int count_ticket_total(CountTicket *t, long long *total) {
+  if (cudaEventQuery(t->event) != cudaSuccess) note_host_wait();  // an answer that already landed is no wait
   SCN_CUDA_CHECK(cudaEventSynchronize(t->event));
   long long s = 0;
   for (int k = 0; k < t->n; ++k) s += (long long)t->host[k];
@@ -921,6 +1152,7 @@ static int rulebook_counts_blocking(Rulebook &rb, cudaStream_t stream) {
   std::vector<unsigned long long> h(rb.n_offsets);
   SCN_CUDA_CHECK(cudaMemcpyAsync(h.data(), rb.counts_dev, sizeof(unsigned long long) * rb.n_offsets,
                                  cudaMemcpyDeviceToHost, stream));
+  note_host_wait();
   SCN_CUDA_CHECK(cudaStreamSynchronize(stream));
   rb.counts_host.assign(h.begin(), h.end());
   long long t = 0;
@@ -946,6 +1178,7 @@ int rulebook_counts(Rulebook &rb, cudaStream_t stream) {
   if (rb.total_rules >= 0) return SCN_OK;
   if (rb.n_offsets > kTicketValues) return rulebook_counts_blocking(rb, stream);
   SCN_TRY(count_ticket_start(rb, stream));
+  note_host_wait();
   SCN_CUDA_CHECK(cudaEventSynchronize(rb.ticket->event));
   counts_from_ticket(rb);
   return SCN_OK;
@@ -1131,6 +1364,12 @@ int scn_md_submanifold_rulebook(scn_metadata *md, const int64_t *spatial_size,
     *n_rules = rb->total_rules;
   }
   return SCN_OK;
+}
+
+int scn_md_strided_chain(scn_metadata *md, const int64_t *input_size, const int64_t *filter_size,
+                         const int64_t *filter_stride, int levels, void *stream, int *n_built) {
+  SCN_REQUIRE(md && input_size && filter_size && filter_stride, SCN_ERR_BAD_ARG, "null argument");
+  return build_strided_chain(md, input_size, filter_size, filter_stride, levels, (cudaStream_t)stream, n_built);
 }
 
 int scn_md_strided_rulebook(scn_metadata *md, const int64_t *input_size, const int64_t *output_size,

@@ -394,6 +394,61 @@ k_dense_to_sparse_grad(KeyLayout L, const unsigned long long *__restrict__ row_k
   d_in[idx] = d_dense[((long long)b * C + c) * volume + lin];
 }
 
+// ------------------------------------------------------------------------------------------------
+// Rows times a small matrix: out[r, :] = bias + in[r, :] * W, W [n_in][n_out] with n_out <= 32.
+// NetworkInNetwork_updateOutput (CPU/NetworkInNetwork.cpp:7-23) and the per-voxel class head of the
+// segmentation networks are this shape: millions of rows, a few dozen columns.  The operation is bound
+// by reading the rows once and writing the scores once; a dense-library GEMM picks a tile shape made for
+// wide outputs and takes several times that.  One thread per row: the row is read in 16-byte pieces, the
+// weights (zero-padded to a multiple of four columns) sit in shared memory and are read as broadcasts,
+// the n_out sums stay in registers (fp32 FMA, plane order -- the order a scalar loop over n_in has).
+template <int COUT4>
+__global__ void __launch_bounds__(256)
+k_rows_affine(const float *__restrict__ in, float *__restrict__ out, long long n_rows, int cin, int cout,
+              const float *__restrict__ weight, const float *__restrict__ bias) {
+  extern __shared__ float4 sh_w4[];  // [cin][COUT4]
+  float *sh_w = reinterpret_cast<float *>(sh_w4);
+  constexpr int CP = COUT4 * 4;
+  for (int i = threadIdx.x; i < cin * CP; i += blockDim.x) {
+    const int k = i / CP, c = i % CP;
+    sh_w[i] = c < cout ? weight[(size_t)k * cout + c] : 0.f;
+  }
+  __syncthreads();
+  const long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= n_rows) return;
+  float acc[CP];
+#pragma unroll
+  for (int c = 0; c < CP; ++c) acc[c] = (bias && c < cout) ? bias[c] : 0.f;
+  const float4 *row = reinterpret_cast<const float4 *>(in + r * cin);
+  for (int q = 0; q < cin / 4; ++q) {
+    const float4 x = __ldg(row + q);
+    const float xs[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+      for (int c4 = 0; c4 < COUT4; ++c4) {
+        const float4 w = sh_w4[(q * 4 + j) * COUT4 + c4];
+        acc[c4 * 4 + 0] = fmaf(xs[j], w.x, acc[c4 * 4 + 0]);
+        acc[c4 * 4 + 1] = fmaf(xs[j], w.y, acc[c4 * 4 + 1]);
+        acc[c4 * 4 + 2] = fmaf(xs[j], w.z, acc[c4 * 4 + 2]);
+        acc[c4 * 4 + 3] = fmaf(xs[j], w.w, acc[c4 * 4 + 3]);
+      }
+    }
+  }
+  float *o = out + r * cout;
+  if (cout % 4 == 0) {
+#pragma unroll
+    for (int c4 = 0; c4 < COUT4; ++c4)
+      if (c4 * 4 < cout)
+        *reinterpret_cast<float4 *>(o + c4 * 4) =
+            make_float4(acc[c4 * 4], acc[c4 * 4 + 1], acc[c4 * 4 + 2], acc[c4 * 4 + 3]);
+  } else {
+#pragma unroll
+    for (int c = 0; c < CP; ++c)
+      if (c < cout) o[c] = acc[c];
+  }
+}
+
 }  // namespace scn
 
 using namespace scn;
@@ -536,6 +591,35 @@ int scn_batchnorm_join_forward(const float *in_a, int planes_a, const float *in_
   const unsigned blocks = (unsigned)std::min<long long>(ceil_div(work, 256), 148 * 16);
   SCN_LAUNCH(k_bn_apply_join, blocks, 256, sizeof(float) * 2 * C, stream, in_a, planes_a, in_b, planes_b, out_features,
              n_rows, running_mean, running_var, (float)eps, weight, bias, (float)leakiness);
+  SCN_CUDA_CHECK(cudaGetLastError());
+  return SCN_OK;
+}
+
+int scn_rows_affine_forward(const float *in_features, float *out_features, int64_t n_rows, int n_in_planes,
+                            int n_out_planes, const float *weight, const float *bias, void *stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SCN_REQUIRE(n_in_planes >= 4 && n_in_planes % 4 == 0 && n_in_planes <= 256, SCN_ERR_UNSUPPORTED,
+              "n_in_planes %d unsupported (a multiple of four, at most 256)", n_in_planes);
+  SCN_REQUIRE(n_out_planes >= 1 && n_out_planes <= 32, SCN_ERR_UNSUPPORTED,
+              "n_out_planes %d unsupported (1..32; wider products belong to the dense matrix library)",
+              n_out_planes);
+  SCN_REQUIRE(n_rows >= 0 && n_rows < (1ll << 31) * 256, SCN_ERR_BAD_ARG, "bad row count");
+  if (n_rows == 0) return SCN_OK;
+  SCN_REQUIRE(in_features && out_features && weight, SCN_ERR_BAD_ARG, "null argument");
+  SCN_REQUIRE((uintptr_t)in_features % 16 == 0 && (uintptr_t)out_features % 16 == 0, SCN_ERR_BAD_ARG,
+              "feature matrices must be 16-byte aligned");
+  const int c4 = (n_out_planes + 3) / 4;
+  const unsigned blocks = (unsigned)ceil_div(n_rows, 256);
+  const size_t smem = sizeof(float) * 4 * (size_t)c4 * n_in_planes;
+#define SCN_AFFINE(N)                                                                                       \
+  case N:                                                                                                   \
+    SCN_LAUNCH(k_rows_affine<N>, blocks, 256, smem, stream, in_features, out_features, (long long)n_rows,   \
+               n_in_planes, n_out_planes, weight, bias);                                                    \
+    break;
+  switch (c4) {
+    SCN_AFFINE(1) SCN_AFFINE(2) SCN_AFFINE(3) SCN_AFFINE(4) SCN_AFFINE(5) SCN_AFFINE(6) SCN_AFFINE(7) SCN_AFFINE(8)
+  }
+#undef SCN_AFFINE
   SCN_CUDA_CHECK(cudaGetLastError());
   return SCN_OK;
 }

@@ -13,6 +13,8 @@ static thread_local char g_last_error[512] = "";
 static std::atomic<long long> g_launches{0};
 
 void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+static std::atomic<long long> g_host_waits{0};
+void note_host_wait() { g_host_waits.fetch_add(1, std::memory_order_relaxed); }
 
 void set_error(const char *fmt, ...) {
   va_list ap;
@@ -165,6 +167,7 @@ extern "C" {
 int scn_abi_version(void) { return SCN_ABI_VERSION; }
 
 long long scn_launch_count(void) { return scn::g_launches.load(std::memory_order_relaxed); }
+long long scn_host_wait_count(void) { return scn::g_host_waits.load(std::memory_order_relaxed); }
 
 int scn_memory_usage(uint64_t *reserved_bytes, uint64_t *used_bytes) {
   using namespace scn;

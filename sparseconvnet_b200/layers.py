@@ -236,6 +236,12 @@ class ValidConvolution(SubmanifoldConvolution):
 
 
 class Convolution(_ConvBase):
+    # Not in the reference: how many consecutive levels of this same downsampling the network goes down
+    # from here (this layer included), set by the network builders that know (UNet, FullyConvolutionalNet).
+    # More than one: the grids and rulebooks of all those levels are built together on first use
+    # (SCN.strided_chain), with one wait for their site counts instead of one per level.
+    levels_below = 1
+
     def __init__(self, dimension, nIn, nOut, filter_size, filter_stride, bias, groups=1):
         Module.__init__(self)
         self._init_weight(dimension, nIn, nOut, filter_size, bias, groups)
@@ -248,6 +254,9 @@ class Convolution(_ConvBase):
             (input.spatial_size, out_size, self.filter_size, self.filter_stride)
         output = SparseConvNetTensor(metadata=input.metadata, spatial_size=out_size)
         bias = optional_tensor(self, "bias")
+        if self.levels_below > 1 and input.features.is_cuda:
+            SCN.strided_chain(input.metadata, input.spatial_size, self.filter_size, self.filter_stride,
+                              self.levels_below, input.features.device)
         if autograd.needs_grad(input.features, self.weight, bias):
             output.features, macs = autograd.convolution(
                 autograd.STRIDED, input.features, self.weight, bias.to(self.weight.device), input.metadata,

@@ -325,3 +325,112 @@ def test_fused_batchnorm_equals_two_passes(precision, cuda):
     assert fused[1] == 27 and bn_calls[1] == 12, (bn_calls, fused)
     assert sum(bool(r.get("joined")) for r in rows if r["kind"] == "batchnorm") == 6
     assert torch.equal(outs[0], outs[1]), float((outs[0] - outs[1]).abs().max())
+
+
+@pytest.mark.parametrize("cin,cout", [(4, 1), (32, 20), (32, 3), (64, 32), (256, 17), (96, 8)])
+def test_rows_times_small_matrix(cin, cout, cuda):
+    """scn_rows_affine_forward (NetworkInNetwork with few output planes, the per-voxel class head) against
+    a float64 product; tolerance 1e-5 of the largest score (fp32 FMA sums over at most 256 planes)."""
+    from sparseconvnet_b200 import SCN
+    g = torch.Generator().manual_seed(cin * 100 + cout)
+    w = torch.randn(cin, cout, generator=g).cuda()
+    b = torch.randn(cout, generator=g).cuda()
+    for n in (0, 1, 255, 100003):
+        x = torch.randn(n, cin, generator=g).cuda()
+        for bias in (b, None):
+            y = SCN.rows_affine(x, w, bias)
+            ref = x.double() @ w.double() + (bias.double() if bias is not None else 0.0)
+            assert y.shape == (n, cout)
+            if n:
+                assert (y.double() - ref).abs().max().item() <= 1e-5 * max(1.0, ref.abs().max().item())
+    # into a block of a larger buffer, neighbours untouched
+    buf = torch.full((300, cout), 7.0, device="cuda")
+    x = torch.randn(100, cin, generator=g).cuda()
+    SCN.rows_affine(x, w, b, out=buf[100:200])
+    assert torch.equal(buf[:100], torch.full((100, cout), 7.0, device="cuda"))
+    assert torch.equal(buf[200:], torch.full((100, cout), 7.0, device="cuda"))
+    assert torch.equal(buf[100:200], SCN.rows_affine(x, w, b))
+    # the module form takes the same kernel and keeps the reference's multiply-add count
+    out = torch.empty(0, device="cuda")
+    macs = SCN.NetworkInNetwork_updateOutput(x, out, w, b)
+    assert macs == 100.0 * cin * cout and torch.equal(out, buf[100:200])
+
+
+def test_rows_times_small_matrix_refuses_other_shapes(cuda):
+    from sparseconvnet_b200 import SCN
+    x = torch.randn(10, 30).cuda()
+    with pytest.raises(RuntimeError):
+        SCN.rows_affine(x, torch.randn(30, 8).cuda())          # input planes not a multiple of four
+    x = torch.randn(10, 32).cuda()
+    with pytest.raises(RuntimeError):
+        SCN.rows_affine(x, torch.randn(32, 33).cuda())         # wider than the kernel takes
+    out = torch.empty(0, device="cuda")                          # the module form falls back to the dense library
+    SCN.NetworkInNetwork_updateOutput(x, out, torch.randn(32, 33).cuda(), None)
+    assert out.shape == (10, 33)
+
+
+def _pyramid(cuda, coords, size, levels, chained):
+    """Grids and rulebooks of `levels` f2/s2 levels below an input layer: ([locations], [rulebooks],
+    host waits, rulebooks built), built level by level or, `chained`, in one enqueued chain first."""
+    import ctypes as C
+    import sparseconvnet_b200 as scn
+    from sparseconvnet_b200 import SCN
+    dim = coords.shape[1] - 1
+    x = scn.InputLayer(dim, size, mode=3)([torch.from_numpy(coords), torch.ones(len(coords), 1, device=cuda)])
+    m = x.metadata
+    waits, builds = SCN.host_wait_count(), SCN.lib.scn_rulebook_build_count()
+    f = torch.LongTensor([2] * dim)
+    n_chained = SCN.strided_chain(m, x.spatial_size, f, f, levels, cuda) if chained else 0
+    locs, rules, cur = [], [], x.spatial_size.clone()
+    for _ in range(levels):
+        nxt = (cur - 2) // 2 + 1
+        n_out = C.c_int64()
+        with torch.cuda.device(cuda):
+            SCN.check(SCN.lib.scn_md_strided_rulebook(m._h, SCN.sizes(cur), SCN.sizes(nxt), SCN.sizes(f),
+                                                      SCN.sizes(f), SCN._stream(), C.byref(n_out), None))
+        assert n_out.value == m.getNActive(nxt)
+        cur = nxt
+    waits, builds = SCN.host_wait_count() - waits, SCN.lib.scn_rulebook_build_count() - builds
+    cur = x.spatial_size.clone()
+    for _ in range(levels):
+        nxt = (cur - 2) // 2 + 1
+        locs.append(m.getSpatialLocations(nxt).numpy())
+        rules.append([t.cpu().numpy() for t in m.rulebook(1, cur, f, f)])
+        cur = nxt
+    return locs, rules, waits, builds, n_chained
+
+
+@pytest.mark.parametrize("kind", ["surface", "scattered", "empty", "tiny"])
+def test_chained_strided_levels_equal_level_by_level(kind, cuda):
+    """scn_md_strided_chain: the same grids (row for row) and rulebooks (rule for rule) as one
+    scn_md_strided_rulebook call per level, with one wait for all levels.  'scattered': isolated sites
+    two apart do not thin out from one level to the next, so the first guess of the level sizes is too
+    small and the chain falls back to the safe sizes for those levels."""
+    rng = np.random.default_rng(5)
+    if kind == "surface":      # a closed sheet, rows shuffled: shrinks by about four per level
+        u = np.stack(np.meshgrid(np.arange(300), np.arange(200), indexing="ij"), -1).reshape(-1, 2)
+        z = (100 + 20 * np.sin(u[:, 0] / 40.0)).astype(np.int64)
+        coords = np.concatenate([u, z[:, None], (u[:, :1] // 100)], 1).astype(np.int64)
+        coords = coords[rng.permutation(len(coords))]
+    elif kind == "scattered":  # every site alone in its 2^3 cell at level 0 and again one level down
+        g = np.stack(np.meshgrid(np.arange(24), np.arange(24), np.arange(24), indexing="ij"), -1).reshape(-1, 3) * 4
+        coords = np.concatenate([g, np.zeros((len(g), 1), np.int64)], 1).astype(np.int64)
+    elif kind == "empty":
+        coords = np.zeros((0, 4), np.int64)
+    else:
+        coords = np.array([[5, 6, 7, 0], [1020, 3, 9, 1]], np.int64)
+    levels = 5
+    a = _pyramid(cuda, coords, 1024, levels, chained=False)
+    b = _pyramid(cuda, coords, 1024, levels, chained=True)
+    assert a[3] == levels and b[3] == levels          # every rulebook built exactly once either way
+    assert b[4] == levels                             # ... all of them by the chain
+    for l in range(levels):
+        assert np.array_equal(a[0][l], b[0][l]), "grid of level %d" % l
+        _exact_rules(a[1][l], b[1][l], "rulebook of level %d" % l)
+    if kind == "empty":                                # nothing to count, nothing to wait for level by level
+        return
+    assert a[2] == levels                              # one wait per level (after the input layer's own)
+    if kind == "scattered":
+        assert 2 <= b[2] <= 3                          # the first pass and one or two repeats
+    else:
+        assert b[2] == 1                               # one wait for the whole chain
