@@ -1,6 +1,6 @@
-// Persistent tcgen05 sparse convolution with bf16 operands made in registers: the kernel for wide
-// layers (64 output planes and more) on levels with many rows, in the fp32-class three-term form
-// and in the single-pass bf16 mode.
+// Persistent tcgen05 sparse convolution with bf16 operands: the kernel for wide layers (more than 64
+// output planes) on levels with many rows, in the fp32-class three-term form and in the single-pass
+// bf16 mode.
 //
 // Same mathematics and orientation as conv_tc.cu / conv_tma.cu (output stationary,
 // D^T[planes x 256 rows] += W_k^T G_k^T with the accumulators in TMEM; the reference's per-offset
@@ -10,16 +10,20 @@
 // 32-plane step of the three-term form is 6 instructions = 768 cycles, and everything else has to
 // fit under that:
 //
-//   * the fp32 rows never touch shared memory.  The twelve producer warps read the input rows that
-//     have a rule with 128-bit loads into registers -- all loads of a (tile, offset) group's next
-//     two steps are issued before the first is used, so a thread has up to 12 loads in flight --
-//     split every value into h = bf16(x) and m = bf16(x - h), and store the two bf16 tiles straight
-//     in the K-major core-matrix layout the instruction reads; rows without a rule get zero
-//     stores.  Shared-memory traffic per step: 32 KB of stores + 72 KB of operand reads, against
-//     32 + 64 + 144 KB when a raw fp32 tile is staged and converted by a second set of warps;
+//   * a pass before the launch (k_wide_split_rows) writes every input row once as its two bf16 parts,
+//     h = bf16(x) and m = bf16(x - h), per 32-plane slice [32 h | 32 m]: the same 128 bytes as the fp32
+//     slice.  A row is gathered by up to K output rows; it is converted once instead of K times;
+//   * the twelve producer warps only copy: for every (tile row, 16-byte piece) one cp.async per part
+//     straight into the K-major core-matrix layout the instruction reads, with zero fill where the tile
+//     row has no rule for the offset.  Nothing passes through registers, nothing is converted, there is
+//     no list of hits; a thread's arrival at the step's barrier is tied to the completion of its own
+//     copies (cp.async.mbarrier.arrive), so the only thing a producer ever waits for is a free ring
+//     slot.  (The form this replaced read fp32 rows into registers, split them there and stored both
+//     tiles: 0.44 against 0.37 ms on 96 -> 96 planes at 154 k rows, the pass before the launch included);
 //   * a step is 44-48 KB (two bf16 tiles + the two weight slabs), so the ring holds four steps;
-//   * per filter offset the 256 row-owning threads compact the rows that do have a rule (ballots +
-//     one prefix over eight warp counts); offsets for which the tile has no rule cost nothing;
+//   * per filter offset the 256 row-owning threads publish their rulebook entry and one barrier (which
+//     also carries the decision to stop) makes them visible; offsets for which the tile has no rule
+//     cost that barrier and nothing else;
 //   * one thread issues the MMAs (h h, h m, m h per 16 planes) into one of two TMEM accumulators
 //     while four epilogue warps drain the other (tcgen05.ld -> bias -> optional per-plane
 //     scale / shift / leaky ReLU of a following BatchNorm -> coalesced stores, each row once).
@@ -29,13 +33,11 @@
 // operator, 3e-5 through the four 81-offset layers of the 4-D stack -- better than the three-pass
 // tf32 split on the same instruction, whose high part is a truncation.
 //
-// Where the time goes (96 -> 96 planes, 154 k rows, 0.44 ms; the kernel it replaces took 0.75 ms): the
-// MMA thread waits for full steps two thirds of the time; phase timers in the producers showed the work
-// of a (tile, offset) group spread over its barriers, the list reads, the loads, the conversion and the
-// zero stores with no single dominant term, and ncu shows no saturated pipe (tensor 38 %, LSU 34 %,
-// issue slots 39 %): 2 900 warp instructions per step at 1.5 issued per clock.  What moved it: reading a
-// row's 128 bytes with four neighbouring lanes (one line per row and load instruction instead of one
-// sector per lane: 0.56 -> 0.44 ms) and two block barriers per group instead of three.
+// What bounds it now: shared-memory bandwidth.  A step moves 32 KB of gathered tiles and 12-24 KB of
+// weights in and lets the tensor core read 72 KB of operands out (each of the six instructions reads its
+// 4 KB weight block and its 8 KB row block): about 120 KB per 768 cycles against the 128 bytes per cycle
+// an SM's shared memory delivers.  96 -> 96 planes at 154 k rows runs at 1 700 cycles per step, the
+// zero rows of a tile (60 % at that level) included.
 //
 // Every wait is bounded: on expiry the role raises the abort flag, everybody leaves their loops,
 // tensor memory is freed and the host sees FLAG_TC_TIMEOUT through scn_md_poll_errors.
@@ -61,6 +63,7 @@ enum : int { W_LAST_OF_TILE = 1, W_LAST_OF_CTA = 2 };
 
 struct WideParams {
   const float *in;
+  const unsigned char *in_split;  // the input rows as bf16 parts: per row and 32-plane slice [32 h | 32 m]
   int ld_in;
   long long n_in;
   float *out;
@@ -86,7 +89,6 @@ template <int TERMS, int ROWS, int PW>
 __global__ void __launch_bounds__((PW + 5) * 32, 1) k_conv_wide(WideParams P) {
   constexpr int kWProducerWarps = PW, kWProducers = PW * 32;
   constexpr int kWEpilogue0 = PW, kWMmaWarp = PW + 4;
-  constexpr int kWBatch = 2;  // steps whose loads are in flight together
   constexpr unsigned kTmemCols = 512u;
   constexpr int kParts = TERMS == 3 ? 2 : 1;
   constexpr int kWRows = ROWS;
@@ -94,7 +96,7 @@ __global__ void __launch_bounds__((PW + 5) * 32, 1) k_conv_wide(WideParams P) {
   // 8 input planes of every row): piece j of row r at j * kWLbo + r * 16.  That is the K-major
   // core-matrix layout with 128 bytes between 8-row groups and kWLbo between the K pieces; the 32
   // bytes of padding in kWLbo put the four pieces of a row on different banks, so the four lanes that
-  // convert one row (they read its 128 contiguous bytes: one line per row and load instruction) store
+  // copy one row's part (its 64 contiguous bytes: one line per row and copy instruction) write
   // without conflicting with one another.
   constexpr unsigned kWLbo = kWRows * 16 + 32;
   constexpr unsigned kWTile = 4 * kWLbo;  // bytes of one tile (a multiple of 128)
@@ -122,14 +124,12 @@ __global__ void __launch_bounds__((PW + 5) * 32, 1) k_conv_wide(WideParams P) {
   int *meta = reinterpret_cast<int *>(acc_empty + 2);                      // [NS] step flags
   unsigned *sh_tmem = reinterpret_cast<unsigned *>(meta + kWMaxStages);
   volatile int *sh_abort = reinterpret_cast<volatile int *>(sh_tmem + 1);
-  int *list_row = reinterpret_cast<int *>(ctl + 512);  // [256] tile rows with a rule, then
-  int *list_idx = list_row + kWMaxRows;                // [256] their input rows
-  int *list_miss = list_idx + kWMaxRows;               // [256] tile rows without a rule
-  int *warp_cnt = list_miss + kWMaxRows;               // [8]
+  int *ent = reinterpret_cast<int *>(ctl + 512);  // [2][256] input row of every tile row for the group's offset, or -1
+  int *warp_cnt = ent + 2 * kWMaxRows;            // [2][8] rows with a rule per owner warp
 
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
-      mbar_init(&full[s], kWProducerWarps + 1);
+      mbar_init(&full[s], kWProducers + 1);  // every producer thread (its copies landed) + the slab
       mbar_init(&empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -148,10 +148,9 @@ __global__ void __launch_bounds__((PW + 5) * 32, 1) k_conv_wide(WideParams P) {
       ((long long)blockIdx.x < P.n_tiles) ? (P.n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
 
   if (warp < kWProducerWarps) {
-    // =============================== producers: gather, split, store ===========================
+    // =============================== producers: copy the gathered rows ==========================
     int st = 0, round = 0;
     bool ok = true;
-    auto producer_sync = [] { asm volatile("bar.sync 1, %0;" ::"n"(kWProducers) : "memory"); };
     // barrier + OR over the producers: every producer thread gets the same answer, so they leave
     // the loop together (a warp that left alone would strand the others at the next barrier)
     auto producer_vote = [](bool x) -> bool {
@@ -191,134 +190,93 @@ __global__ void __launch_bounds__((PW + 5) * 32, 1) k_conv_wide(WideParams P) {
     advance(tile_c, k_c);
     int v0 = entry(tile_a, k_a), v1 = entry(tile_b, k_b), v2;
     int issued_in_tile = 0;
-    for (long long t = 0; t < my_tiles;) {
-      v2 = entry(tile_c, k_c);
-      const bool hit = (unsigned)v0 < (unsigned)P.n_in;
-      if (v0 >= 0 && !hit) atomicOr(P.flags, FLAG_BAD_ROW);
-      const unsigned hits = __ballot_sync(0xffffffffu, hit);
-      // Two barriers per group.  The first also carries the decision to stop (a bounded wait ran out
-      // somewhere): it is a reduction, so every producer gets the same answer.  Behind it the lists of
-      // the previous group are free to be rewritten: nobody passes it before all have finished that group.
-      if (lane == 0 && warp < kWOwners) warp_cnt[warp] = __popc(hits);
-      if (producer_vote(!ok || *sh_abort)) break;
-      int base = 0, total = 0;
-#pragma unroll
-      for (int w = 0; w < kWOwners; ++w) {
-        const int cw = warp_cnt[w];
-        if (w < warp) base += cw;
-        total += cw;
-      }
-      const bool tile_end = (k_a == P.K - 1);
-      const bool zero_step = tile_end && total == 0 && issued_in_tile == 0;  // a tile must get one step
-      if (total > 0 || zero_step) {
+    {
+      // entries and warp counts of a group are published before the group's barrier and read after it;
+      // the next group's are written while slow threads may still read this one's: two copies, by parity
+      int par = 0;
+      for (long long t = 0; t < my_tiles; par ^= 1) {
+        v2 = entry(tile_c, k_c);
+        const bool hit = (unsigned)v0 < (unsigned)P.n_in;
+        if (v0 >= 0 && !hit) atomicOr(P.flags, FLAG_BAD_ROW);
+        const unsigned hits = __ballot_sync(0xffffffffu, hit);
         if (warp < kWOwners) {
-          const unsigned lt = (1u << lane) - 1;
-          if (hit) {
-            const int pos = base + __popc(hits & lt);
-            list_row[pos] = tid;
-            list_idx[pos] = v0;
-          } else {
-            list_miss[32 * warp - base + __popc(~hits & lt)] = tid;
-          }
+          ent[par * kWRows + tid] = hit ? v0 : -1;
+          if (lane == 0) warp_cnt[par * 8 + warp] = __popc(hits);
         }
-        producer_sync();
-        const int n_miss = kWRows - total;
-        const int n_hit_items = total * 4, n_miss_items = n_miss * 4;
-        // This thread's items of every step of the group: (row, 16-byte piece) -> offset inside a bf16
-        // tile, source.  Four consecutive lanes take the four pieces of one row.
-        unsigned off[kWItems];
-        const float *src[kWItems];
+        if (producer_vote(!ok || *sh_abort)) break;
+        int total = 0;
 #pragma unroll
-        for (int i = 0; i < kWItems; ++i) {
-          const int it = tid + i * kWProducers;
-          src[i] = nullptr;
-          off[i] = 0;
-          if (it < n_hit_items) {
-            const int e = it >> 2, j = it & 3, r = list_row[e];
-            off[i] = (unsigned)j * kWLbo + (unsigned)r * 16u;
-            src[i] = P.in + (long long)list_idx[e] * P.ld_in + j * 8;
+        for (int w = 0; w < kWOwners; ++w) total += warp_cnt[par * 8 + w];
+        const bool tile_end = (k_a == P.K - 1);
+        const bool zero_step = tile_end && total == 0 && issued_in_tile == 0;  // a tile must get one step
+        if (total > 0 || zero_step) {
+          // this thread's (row, 16-byte piece) items: four consecutive lanes take the four pieces of a row
+          unsigned off[kWItems], size[kWItems];
+          const unsigned char *src[kWItems];
+#pragma unroll
+          for (int i = 0; i < kWItems; ++i) {
+            const int it = tid + i * kWProducers;
+            const int r = (it >> 2) & (kWRows - 1), j = it & 3;
+            const int v = it < kWRows * 4 ? ent[par * kWRows + r] : -1;
+            off[i] = it < kWRows * 4 ? (unsigned)j * kWLbo + (unsigned)r * 16u : 0xFFFFFFFFu;
+            size[i] = v >= 0 ? 16u : 0u;
+            src[i] = P.in_split + (v >= 0 ? (size_t)v * P.ld_in * 4 : 0) + j * 16;
           }
-        }
-        for (int s0 = 0; s0 < n_slices && ok; s0 += kWBatch) {
-          const int nb = min(kWBatch, n_slices - s0);
-          // all loads of the batch first: up to kWItems x kWBatch x 2 128-bit loads in flight per thread
-          float4 x[kWBatch][kWItems][2];
-#pragma unroll
-          for (int b = 0; b < kWBatch; ++b)
-#pragma unroll
-            for (int i = 0; i < kWItems; ++i)
-              if (b < nb && src[i]) {
-                const float4 *p = reinterpret_cast<const float4 *>(src[i] + (s0 + b) * kWSlice);
-                x[b][i][0] = __ldg(p);
-                x[b][i][1] = __ldg(p + 1);
-              }
-#pragma unroll
-          for (int b = 0; b < kWBatch; ++b) {
-            if (b >= nb || !ok) continue;
+          for (int s0 = 0; s0 < n_slices && ok; ++s0) {
             if (!slot_free(st, round)) {
               ok = false;
-              continue;
+              break;
             }
-            unsigned char *stage = smem + (size_t)st * stage_bytes;
+            const unsigned stage = smem_u32(smem) + (unsigned)st * stage_bytes;
             if (tid == 0) {
               meta[st] = 0;
               mbar_expect_tx(&full[st], total_w);
-              bulk_copy_g2s(smem_u32(stage), P.wprep + ((size_t)k_a * n_slices + (s0 + b)) * total_w, total_w, &full[st]);
+              bulk_copy_g2s(stage, P.wprep + ((size_t)k_a * n_slices + s0) * total_w, total_w, &full[st]);
             }
-            unsigned char *g = stage + w_region;
+            const unsigned g = stage + w_region;
 #pragma unroll
             for (int i = 0; i < kWItems; ++i)
-              if (src[i]) {
-                uint4 h, m;
-                split_bf16_pair(x[b][i][0].x, x[b][i][0].y, h.x, m.x);
-                split_bf16_pair(x[b][i][0].z, x[b][i][0].w, h.y, m.y);
-                split_bf16_pair(x[b][i][1].x, x[b][i][1].y, h.z, m.z);
-                split_bf16_pair(x[b][i][1].z, x[b][i][1].w, h.w, m.w);
-                *reinterpret_cast<uint4 *>(g + off[i]) = h;
-                if (TERMS == 3) *reinterpret_cast<uint4 *>(g + kWTile + off[i]) = m;
+              if (off[i] != 0xFFFFFFFFu) {
+                const unsigned char *q = src[i] + (size[i] ? (size_t)s0 * (kWSlice * 4) : 0);
+                cp_async16(g + off[i], q, size[i]);
+                if (TERMS == 3) cp_async16(g + kWTile + off[i], q + (size[i] ? 64 : 0), size[i]);
               }
-            for (int it = tid; it < n_miss_items; it += kWProducers) {
-              const unsigned o = (unsigned)(it & 3) * kWLbo + (unsigned)list_miss[it >> 2] * 16u;
-              *reinterpret_cast<uint4 *>(g + o) = make_uint4(0, 0, 0, 0);
-              if (TERMS == 3) *reinterpret_cast<uint4 *>(g + kWTile + o) = make_uint4(0, 0, 0, 0);
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&full[st]);  // one arrival per warp (release)
+            // this thread's arrival happens when its copies above have landed
+            asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&full[st])) : "memory");
             if (++st == NS) {
               st = 0;
               ++round;
             }
           }
+          ++issued_in_tile;
         }
-        ++issued_in_tile;
-      }
-      if (tile_end && ok) {
-        // end-of-tile marker: a slot without data that tells the MMA thread to hand the accumulator
-        // to the epilogue
-        if (slot_free(st, round)) {
-          if (tid == 0) {
-            meta[st] = W_LAST_OF_TILE | (t == my_tiles - 1 ? W_LAST_OF_CTA : 0);
-            mbar_arrive(&full[st]);  // stands in for the slab's transaction arrival
+        if (tile_end && ok) {
+          if (slot_free(st, round)) {
+            if (tid == 0) {
+              meta[st] = W_LAST_OF_TILE | (t == my_tiles - 1 ? W_LAST_OF_CTA : 0);
+              mbar_arrive(&full[st]);  // stands in for the slab's transaction arrival
+            }
+            mbar_arrive(&full[st]);
+            if (++st == NS) {
+              st = 0;
+              ++round;
+            }
+          } else {
+            ok = false;
           }
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&full[st]);
-          if (++st == NS) {
-            st = 0;
-            ++round;
-          }
-        } else {
-          ok = false;
+          issued_in_tile = 0;
+          ++t;
         }
-        issued_in_tile = 0;
-        ++t;
+        v0 = v1;
+        v1 = v2;
+        tile_a = tile_b;
+        k_a = k_b;
+        tile_b = tile_c;
+        k_b = k_c;
+        advance(tile_c, k_c);
       }
-      v0 = v1;
-      v1 = v2;
-      tile_a = tile_b;
-      k_a = k_b;
-      tile_b = tile_c;
-      k_b = k_c;
-      advance(tile_c, k_c);
+      // copies still in flight must land before the CTA's shared memory goes away
+      asm volatile("cp.async.wait_all;" ::: "memory");
     }
     if (!ok) *sh_abort = 1;
   } else if (warp == kWMmaWarp) {
@@ -443,6 +401,27 @@ __global__ void __launch_bounds__((PW + 5) * 32, 1) k_conv_wide(WideParams P) {
   if (warp == kWMmaWarp) tmem_dealloc(tmem_base, kTmemCols);
 }
 
+// in [n][cin] fp32 -> out, per row and 32-plane slice: the 32 h = bf16(x) then the 32 m = bf16(x - h)
+// (128 bytes, the size of the fp32 slice).  One thread per 8 planes: 32 bytes in, 16 + 16 out.
+__global__ void __launch_bounds__(256)
+k_wide_split_rows(const float *__restrict__ in, unsigned char *__restrict__ out, long long n_pieces, int cin) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n_pieces) return;
+  const int ppr = cin / 8;  // pieces per row
+  const long long row = idx / ppr;
+  const int piece = (int)(idx % ppr), slice = piece >> 2, j = piece & 3;
+  const float4 *p = reinterpret_cast<const float4 *>(in + row * cin + piece * 8);
+  const float4 a = __ldg(p), b = __ldg(p + 1);
+  uint4 h, m;
+  split_bf16_pair(a.x, a.y, h.x, m.x);
+  split_bf16_pair(a.z, a.w, h.y, m.y);
+  split_bf16_pair(b.x, b.y, h.z, m.z);
+  split_bf16_pair(b.z, b.w, h.w, m.w);
+  unsigned char *q = out + (size_t)row * cin * 4 + (size_t)slice * (kWSlice * 4) + j * 16;
+  *reinterpret_cast<uint4 *>(q) = h;
+  *reinterpret_cast<uint4 *>(q + 64) = m;
+}
+
 size_t wide_stage_bytes(int terms, int cout, int rows) {
   const int parts = terms == 3 ? 2 : 1;
   const size_t w = (size_t)cout * kWSlice * 2 * parts;
@@ -452,7 +431,7 @@ size_t wide_stage_bytes(int terms, int cout, int rows) {
 // per-group work of the producers doubles: 0.65 against 0.56 ms on 96 -> 96 planes at 154 k rows), 24 producer
 // warps (0.45 against 0.44 ms) and two CTAs per SM with half the ring and one accumulator each (0.45 ms).
 int wide_rows() { return 256; }
-constexpr size_t kWideControlBytes = 4096;  // barriers, step flags, and the producers' row lists
+constexpr size_t kWideControlBytes = 4096;  // barriers, step flags, and the rulebook entries of two groups
 constexpr size_t kWideSmemBudget = 226 * 1024;
 
 }  // namespace
@@ -490,8 +469,14 @@ int conv_forward_wide(const float *in, long long n_in, float *out, long long n_o
   unsigned char *wprep = (unsigned char *)wi.ptr;
   if (build) SCN_TRY(prepare_weights(weight, wprep, K, cin, cout, kWSlice, mode, stream));
 
+  // the input rows as bf16 parts, made once per call (every row is gathered by up to K output rows)
+  unsigned char *split = nullptr;
+  SCN_TRY(device_alloc((void **)&split, (size_t)n_in * cin * 4, stream));
+  const long long n_pieces = n_in * (cin / 8);
+  SCN_LAUNCH(k_wide_split_rows, (unsigned)ceil_div(n_pieces, 256LL), 256, 0, stream, in, split, n_pieces, cin);
   WideParams P;
   P.in = in;
+  P.in_split = split;
   P.ld_in = cin;
   P.n_in = n_in;
   P.out = out;
@@ -527,7 +512,9 @@ int conv_forward_wide(const float *in, long long n_in, float *out, long long n_o
     SCN_LAUNCH((k_conv_wide<3, 256, 12>), grid, 17 * 32, budget, stream, P);
   else
     SCN_LAUNCH((k_conv_wide<1, 256, 12>), grid, 17 * 32, budget, stream, P);
-  SCN_CUDA_CHECK(cudaGetLastError());
+  const cudaError_t launch_err = cudaGetLastError();
+  device_free(split, stream);
+  SCN_CUDA_CHECK(launch_err);
   SCN_TRY(weight_image_put(wi, stream));
   return SCN_OK;
 }
