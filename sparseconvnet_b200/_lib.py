@@ -131,7 +131,17 @@ def check(status):
         raise ScnError(status, lib.scn_last_error().decode() or lib.scn_status_string(status).decode())
 
 
+_sizes_cache = {}
+
+
 def sizes(seq):
-    """Host int64 array for a spatial size / filter size / stride."""
-    vals = [int(v) for v in seq]
-    return (C.c_int64 * len(vals))(*vals)
+    """Host int64 array for a spatial size / filter size / stride.  The arrays are only read by the
+    library, so one array per distinct value is kept and shared (a network asks for the same handful of
+    sizes hundreds of times per pass; iterating a tensor element by element costs microseconds each)."""
+    vals = tuple(seq.tolist()) if hasattr(seq, "tolist") else tuple(int(v) for v in seq)
+    arr = _sizes_cache.get(vals)
+    if arr is None:
+        if len(_sizes_cache) > 4096:
+            _sizes_cache.clear()
+        arr = _sizes_cache[vals] = (C.c_int64 * len(vals))(*[int(v) for v in vals])
+    return arr
