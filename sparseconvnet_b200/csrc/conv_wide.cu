@@ -383,8 +383,11 @@ __global__ void __launch_bounds__((PW + 5) * 32, 1) k_conv_wide(WideParams P) {
 #pragma unroll
             for (int i = 0; i < 32; ++i)
               if (row0 + n0 + i < P.n_out) {
-                float y = (v[i] + b) * sc + sh;
-                y = y > 0.f ? y : y * leak;
+                float y = v[i] + b;
+                if (P.bn_scale) {  // separate multiply and add, as the stand-alone BatchNorm kernel rounds them
+                  y = __fadd_rn(__fmul_rn(y, sc), sh);
+                  y *= (y > 0.f) ? 1.f : leak;
+                }
                 dst[(long long)i * P.ld_out] = y;
               }
           }

@@ -327,6 +327,42 @@ def test_fused_batchnorm_equals_two_passes(precision, cuda):
     assert torch.equal(outs[0], outs[1]), float((outs[0] - outs[1]).abs().max())
 
 
+@pytest.mark.parametrize("cout", [96, 160])
+def test_fused_batchnorm_in_the_persistent_tcgen05_kernel(cout, cuda, monkeypatch):
+    """k_conv_wide (forced onto a small level: the U-Net of the test above is too small to reach it): the fused
+    BatchNorm gives the bits of the two separate operators, with one and with two 128-plane accumulator tiles."""
+    import sparseconvnet_b200 as scn
+    from sparseconvnet_b200 import SCN
+    monkeypatch.setenv("SCN_TC_PERSISTENT", "1")
+    rng = np.random.default_rng(11)
+    pts = rng.integers(0, 96, (20000, 2))
+    z = (48 + 19 * np.sin(pts[:, 0] / 6.0)).astype(np.int64)
+    coords = np.concatenate([pts, z[:, None], rng.integers(0, 2, (20000, 1))], 1).astype(np.int64)
+    torch.manual_seed(3)
+    net = scn.Sequential().add(scn.SubmanifoldConvolution(3, 96, cout, 3, True)).add(
+        scn.BatchNormLeakyReLU(cout, leakiness=0.1)).to(cuda).eval()
+    net[1].running_mean.normal_()
+    net[1].running_var.uniform_(0.5, 2.0)
+    net[1].weight.data.normal_()
+    net[1].bias.data.normal_()
+    net[0].bias.data.normal_()
+    feats = torch.randn(20000, 96, device=cuda)
+    scn.set_precision("tf32x3")
+    try:
+        outs = []
+        for fuse in (False, True):
+            scn.Sequential.fuse = fuse
+            with torch.no_grad():
+                y = net(scn.InputLayer(3, 96, mode=3)([torch.from_numpy(coords), feats]))
+            assert SCN._KERNEL_NAMES[SCN.lib.scn_last_conv_kernel()] == "k_conv_wide"
+            y.metadata.poll_errors()
+            outs.append(y.features.clone())
+    finally:
+        scn.Sequential.fuse = True
+        scn.set_precision("fp32")
+    assert torch.equal(outs[0], outs[1]), float((outs[0] - outs[1]).abs().max())
+
+
 @pytest.mark.parametrize("cin,cout", [(4, 1), (32, 20), (32, 3), (64, 32), (256, 17), (96, 8)])
 def test_rows_times_small_matrix(cin, cout, cuda):
     """scn_rows_affine_forward (NetworkInNetwork with few output planes, the per-voxel class head) against
