@@ -536,6 +536,18 @@ def SubmanifoldConvolution_updateOutput(inputSize, filterSize, m, input_features
         if f.size(0) != n:
             raise RuntimeError("features have %d rows, metadata has %d active sites" % (f.size(0), n))
         output_features.resize_(n, groups * cout)
+        if Profile.active is None:  # the convolution entry finds or builds the rulebook itself
+            if epilogue is None:
+                check(lib.scn_submanifold_convolution_forward(
+                    m._h, sizes(inputSize), sizes(filterSize), _ptr(f), _ptr(output_features), _ptr(w), _ptr(b),
+                    groups * cin, groups * cout, groups, _precision, _stream(), C.byref(macs)))
+            else:
+                sc, sh, leak = _epilogue_args(epilogue, f, groups * cout)
+                check(lib.scn_submanifold_convolution_bn_forward(
+                    m._h, sizes(inputSize), sizes(filterSize), _ptr(f), _ptr(output_features), _ptr(w), _ptr(b),
+                    sc, sh, leak, groups * cin, groups * cout, groups, _precision, _stream(), C.byref(macs)))
+            return _macs_result(m, macs)
+        # profiled: the rulebook call on its own, so that its time and bytes are not the convolution's
         with _timed("rules_submanifold", dict(sites=n, offsets=w.size(0), dim=m.dimension)) as info:
             builds = lib.scn_rulebook_build_count()
             check(lib.scn_md_submanifold_rulebook(m._h, sizes(inputSize), sizes(filterSize), _stream(), None))
