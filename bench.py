@@ -51,8 +51,8 @@ LIMITS = {
                            "39-47 % of peak, issue slots 42-57 %; the warp's dependent chain rulebook entry -> gather -> "
                            "fragment loads -> bf16 split -> tensor instruction with 13-19 warps per SM; DRAM sees 0.19-0.24 "
                            "of the algorithmic bytes, the gather's re-reads hit L2"),
-    "k_conv_wide": ("hbm", "the producer warps (no saturated pipe: tensor 38 %, LSU 34 %, issue slots 39 %); the MMA thread "
-                           "waits for full steps two thirds of the time"),
+    "k_conv_wide": ("hbm", "shared-memory bandwidth: a 32-plane step writes 45 KB of tiles and slabs and the tensor core reads "
+                           "72 KB of operands, against 128 B per cycle; tensor pipe 47.5 % active (ncu, 4-room case)"),
     "k_conv_tc": ("hbm", "latency: few 256-row tiles per level (tensor pipe 13-16 %)"),
 }
 # what `dtype` says for each arithmetic mode: the type the path computes in, kernel by kernel

@@ -80,7 +80,7 @@ enum scn_conv_kernel {
   SCN_KERNEL_CONV_TC_PERSISTENT = 2, /* k_conv_tma: tcgen05, persistent, double-buffered TMEM */
   SCN_KERNEL_CONV_PIPE_MMA = 3,      /* k_conv_pipe with three tf32 mma.sync passes           */
   SCN_KERNEL_CONV_ROWS = 4,          /* k_conv_rows: row-stationary, warp-level mma.sync      */
-  SCN_KERNEL_CONV_WIDE = 5           /* k_conv_wide: tcgen05, persistent, bf16 operands split in registers */
+  SCN_KERNEL_CONV_WIDE = 5           /* k_conv_wide: tcgen05, persistent, rows split to bf16 parts once per call and copied in by cp.async */
 };
 /* The tensor-core modes need groups == 1, n_in_planes % 32 == 0, n_out_planes % 16 == 0 and
  * n_out_planes <= 256; other shapes run the fp32 kernel whatever the precision says. */

@@ -104,7 +104,7 @@ static int ensure_scratch(scn_metadata *md, cudaStream_t stream) {
 // kernel into pinned host memory that is mapped into the device's address space, not copied by
 // cudaMemcpy: a device-to-host copy queues on the copy engine behind whatever the application is
 // copying at the time (a previous batch's 127 MB of results held every such read-back up for 2 ms,
-// seven times per U-Net forward).  Slots of 256 bytes from slabs that are never given back.
+// once per strided level of a U-Net forward).  Slots of 256 bytes from slabs that are never given back.
 constexpr int kMailboxBytes = 256;  // 64 integers: flag word + the counts of a whole chain of levels
 namespace {
 struct MailboxPool {
