@@ -194,7 +194,10 @@ def summarize_profile(rows):
         a = agg.setdefault(name, {"ms": 0.0, "calls": 0, "bytes": 0.0, "flops": 0.0})
         if r["kind"].startswith("rules_"):
             a["built"] = a.get("built", 0) + (1 if r.get("built", True) else 0)
-            if not r.get("built", True):
+            if r.get("overlapped") and r.get("built", True):
+                # built on the side stream beside other operators: the call only took the result over
+                a["overlapped_builds"] = a.get("overlapped_builds", 0) + 1
+            if not r.get("built", True) or r.get("overlapped"):
                 a["calls"] += 1
                 a["cached_ms"] = a.get("cached_ms", 0.0) + r["ms"]
                 continue
@@ -626,6 +629,8 @@ def main():
             breakdown[k]["frac_of_tf32_peak"] = round(tf / tpeak, 3)
         if "built" in v:
             breakdown[k]["built"] = v["built"]
+        if "overlapped_builds" in v:
+            breakdown[k]["built_on_side_stream"] = v["overlapped_builds"]
 
     # ---- the other configurations (rank 0, one GPU): voxels/s and the reference CPU beside each -----------
     configs = None

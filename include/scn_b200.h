@@ -210,6 +210,17 @@ SCN_API int scn_md_strided_rulebook(scn_metadata *md, const int64_t *input_size,
 SCN_API int scn_md_strided_chain(scn_metadata *md, const int64_t *input_size, const int64_t *filter_size,
                                  const int64_t *filter_stride, int levels, void *stream, int *n_built);
 
+/* scn_md_strided_chain without the wait: the chain's kernels go to a side stream of the device, ordered behind
+ * what `stream` holds at the time of the call (the grid of `input_size` must exist), and run beside whatever the
+ * caller enqueues on `stream` afterwards -- for a U-Net, the convolutions of its finest level.  The call returns
+ * at once.  The first call that needs one of those levels (scn_md_strided_rulebook, scn_md_strided_chain, a
+ * convolution or a query on a level's grid) waits for the chain's event, which has usually long passed, and takes
+ * the levels over; until then they do not exist for scn_md_n_active and friends in any other sense.  Nothing is
+ * started when a chain is under way already or does not apply.  scn_md_clear / scn_md_input_layer /
+ * scn_md_destroy drop a started chain.  The reference has no such call. */
+SCN_API int scn_md_strided_chain_start(scn_metadata *md, const int64_t *input_size, const int64_t *filter_size,
+                                       const int64_t *filter_stride, int levels, void *stream);
+
 /* Rulebook read-back in the reference's format (RuleBook = one flat list of
  * (input_row, output_row) int32 pairs per filter offset, Metadata.h:35).  The reference does
  * not bind this; it exists so parity tests can compare rulebooks bit for bit.

@@ -318,6 +318,8 @@ class _Metadata(object):
         self._h = C.c_void_p()
         check(lib.scn_md_create(self.dimension, C.byref(self._h)))
         self.device = None
+        self.chain_looked_for = False  # containers.Sequential: has a container looked for an encoder to prefetch?
+        self.chain_started = False     # ... and started one (SCN.strided_chain_start)
 
     def __del__(self):
         h, self._h = getattr(self, "_h", None), None
@@ -422,6 +424,8 @@ def InputLayer_updateOutput(m, spatial_size, input_coords, input_features, outpu
     if coords.is_cuda and coords.device != f.device:
         coords = coords.to(f.device)
     m.device = f.device
+    m.chain_looked_for = False  # a new input: the containers may look for an encoder to prefetch again
+    m.chain_started = False
     m.n_input_rows, m.bl_shape = coords.size(0), None
     n_active = C.c_int64()
     with _on_device(f.device):
@@ -449,6 +453,7 @@ def BLInputLayer_updateOutput(m, spatial_size, input_coords, input_features, out
     if coords.is_cuda and coords.device != f.device:
         coords = coords.to(f.device)
     m.device = f.device
+    m.chain_looked_for = False  # a new input: the containers may look for an encoder to prefetch again
     m.bl_shape, m.n_input_rows = (f.size(0), f.size(1)), f.size(0) * f.size(1)
     n_active = C.c_int64()
     with _on_device(f.device):
@@ -586,6 +591,8 @@ def strided_chain(m, inputSize, filterSize, filterStride, levels, device):
                                        _stream(), C.byref(built)))
         info["built"] = built.value > 0
         info["levels"] = built.value
+        # started earlier on the side stream: its kernels ran beside other operators' and are in their times
+        info["overlapped"] = bool(getattr(m, "chain_started", False))
         if built.value and Profile.active is not None:  # all the levels' sites are this call's work
             cur = [int(v) for v in inputSize]
             for _ in range(built.value):
@@ -594,6 +601,18 @@ def strided_chain(m, inputSize, filterSize, filterStride, levels, device):
                 info["sites_out"] += m.getNActive(torch.LongTensor(nxt))
                 cur = nxt
     return built.value
+
+
+def strided_chain_start(m, inputSize, filterSize, filterStride, levels, device):
+    """strided_chain without the wait (scn_md_strided_chain_start): the chain's kernels go to the library's side
+    stream behind what the current stream holds now and run beside what is enqueued next; the call that first
+    needs one of the levels takes them over.  Not in the reference."""
+    if levels < 2:
+        return
+    with _on_device(device):
+        check(lib.scn_md_strided_chain_start(m._h, sizes(inputSize), sizes(filterSize), sizes(filterStride),
+                                             int(levels), _stream()))
+    m.chain_started = True
 
 
 def Convolution_updateOutput(inputSize, outputSize, filterSize, filterStride, m, input_features,

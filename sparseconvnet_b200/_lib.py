@@ -49,6 +49,7 @@ SIGNATURES = {
     "scn_md_submanifold_rulebook": (C.c_int, [_vp, _i64p, _i64p, _vp, _i64p]),
     "scn_md_strided_rulebook": (C.c_int, [_vp, _i64p, _i64p, _i64p, _i64p, _vp, _i64p, _i64p]),
     "scn_md_strided_chain": (C.c_int, [_vp, _i64p, _i64p, _i64p, C.c_int, _vp, C.POINTER(C.c_int)]),
+    "scn_md_strided_chain_start": (C.c_int, [_vp, _i64p, _i64p, _i64p, C.c_int, _vp]),
     "scn_md_rulebook_export": (C.c_int, [_vp, C.c_int, _i64p, _i64p, _i64p, _i64p, _i64p, _vp, _vp]),
     "scn_submanifold_convolution_forward": (C.c_int, [_vp, _i64p, _i64p, _vp, _vp, _vp, _vp, C.c_int,
                                                       C.c_int, C.c_int, C.c_int, _vp,

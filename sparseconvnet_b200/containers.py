@@ -14,17 +14,53 @@ def _flatten(seq, out):
     return out
 
 
+def _chain_ahead(steps):
+    """The first downsampling Convolution that announces further levels (``levels_below > 1``) and is reached
+    from the start of `steps` through modules that keep the sites and the spatial size -- so that its input grid
+    is the grid of the tensor that enters `steps` -- looking into the branches of a ConcatTable.  None if there
+    is none."""
+    from . import layers
+    keeps = (layers.SubmanifoldConvolution, layers.BatchNormalization, layers.Identity, layers.NetworkInNetwork)
+    for m in steps:
+        if isinstance(m, layers.Convolution):
+            return m if m.levels_below > 1 else None
+        if type(m) is ConcatTable:
+            for branch in m._modules.values():
+                found = _chain_ahead(_flatten(branch, []) if type(branch) is Sequential else [branch])
+                if found is not None:
+                    return found
+            return None  # what follows a ConcatTable works on a list of tensors
+        if not isinstance(m, keeps):
+            return None
+    return None
+
+
 class Sequential(torch.nn.Sequential):
     """Runs its children in order, like the reference's container.  One peephole: a convolution whose
     output goes straight into an eval-mode BatchNormalization (possibly across the boundary of a
     nested Sequential, as in the U-Net's blocks) applies that layer's scale, shift and leaky ReLU in
     its own store -- same arithmetic, one pass over the activation less.  `Sequential.fuse = False`
-    turns it off."""
+    turns it off.
+
+    And one look ahead (`Sequential.prefetch_rulebooks = False` turns it off): the first Sequential that sees a
+    tensor of a new Metadata looks for the encoder's first downsampling Convolution behind the layers that keep
+    the sites (the builders mark it with the number of levels below it) and has the grids and rulebooks of all
+    those levels started on the library's side stream (SCN.strided_chain_start).  They are built while the
+    layers of the finest level run, and the Convolution, when its turn comes, finds them finished instead of
+    building them and waiting with an empty stream."""
     fuse = True
+    prefetch_rulebooks = True
 
     def forward(self, input):
         from . import layers
         steps = _flatten(self, [])
+        if (Sequential.prefetch_rulebooks and isinstance(input, SparseConvNetTensor) and input.features.is_cuda
+                and not getattr(input.metadata, "chain_looked_for", True)):
+            input.metadata.chain_looked_for = True  # one look per Metadata, by the outermost container
+            conv = _chain_ahead(steps)
+            if conv is not None:
+                layers.SCN.strided_chain_start(input.metadata, input.spatial_size, conv.filter_size, conv.filter_stride,
+                                               conv.levels_below, input.features.device)
         i, n = 0, len(steps)
         while i < n:
             m = steps[i]

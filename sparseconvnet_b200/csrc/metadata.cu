@@ -62,8 +62,16 @@ int md_touch(scn_metadata *md, cudaStream_t stream) {
   return SCN_OK;
 }
 
+static int chain_finalize(scn_metadata *md, cudaStream_t stream, int *n_built);
+static void chain_abandon(scn_metadata *md, cudaStream_t stream);
+
 Grid *find_grid(scn_metadata *md, const int64_t *spatial_size) {
   auto it = md->grids.find(make_key(md->dim, spatial_size));
+  if (it == md->grids.end() && md->pending) {
+    // the grid may be one of a chain that was started on the side stream: take the chain over, then look again
+    if (chain_finalize(md, md->last_stream, nullptr) != SCN_OK) return nullptr;
+    it = md->grids.find(make_key(md->dim, spatial_size));
+  }
   return it == md->grids.end() ? nullptr : &it->second;
 }
 
@@ -366,6 +374,7 @@ static void clear_input_rules(scn_metadata *md, cudaStream_t stream) {
 }
 
 static int md_clear(scn_metadata *md, cudaStream_t stream) {
+  chain_abandon(md, stream);
   for (auto &g : md->grids) free_grid(g.second, stream);
   for (auto &r : md->sub_rules) free_rulebook(r.second, stream);
   for (auto &r : md->strided_rules) free_rulebook(r.second, stream);
@@ -741,6 +750,10 @@ int get_strided_rulebook(scn_metadata *md, const int64_t *input_size, const int6
   Rulebook &rb = md->strided_rules[key];
   *out = &rb;
   if (rb.built) return SCN_OK;
+  if (md->pending) {  // it may be one of a chain that was started on the side stream
+    SCN_TRY(chain_finalize(md, stream, nullptr));
+    if (rb.built) return SCN_OK;
+  }
   Grid *gin = find_grid(md, input_size);
   if (!gin) {
     md->strided_rules.erase(key);
@@ -928,110 +941,262 @@ static int chain_enqueue(scn_metadata *md, const Grid *gin, std::vector<ChainLev
   return SCN_OK;
 }
 
-// Builds up to `levels` consecutive rulebooks of (filter_size, filter_stride) starting at the grid of
-// `input_size`, each level's output size (in - f) / s + 1.  Does nothing (SCN_OK) where the chain does
-// not apply -- filter != stride, fewer than two levels to build, no grid, rulebooks already there --
-// because the per-level call that follows builds or reports whatever is left.
-int build_strided_chain(scn_metadata *md, const int64_t *input_size, const int64_t *filter_size,
-                        const int64_t *filter_stride, int levels, cudaStream_t stream, int *n_built) {
-  if (n_built) *n_built = 0;
-  SCN_TRY(md_touch(md, stream));
+// ---- plan / launch / collect: the three parts of a chain ------------------------------------------------------
+// plan: sizes, layouts and bounds of the levels below `start` that can be chained (stops at the first level that
+// is already there, does not divide, or does not fit the key)
+static void chain_plan(scn_metadata *md, const Grid *gin, const std::vector<int64_t> &start, const int64_t *filter,
+                       int levels, bool safe, std::vector<ChainLevel> &plan) {
   const int dim = md->dim;
-  for (int d = 0; d < dim; ++d)
-    if (filter_size[d] != filter_stride[d] || filter_size[d] < 1 || filter_size[d] > 127) return SCN_OK;
-  levels = std::min(levels, kMaxChain);
-  std::vector<int64_t> start(input_size, input_size + dim);
-  bool safe = false;
-  while (levels >= 2) {
-    Grid *gin = find_grid(md, start.data());
-    if (!gin || gin->n_active >= (1ll << 31)) return SCN_OK;
-    // ---- plan: sizes, layouts and bounds of the levels that can be chained
-    std::vector<ChainLevel> plan;
-    std::vector<int64_t> cur = start;
-    long long bound = gin->n_active;
-    for (int l = 0; l < levels; ++l) {
-      ChainLevel lv;
-      lv.in_size = cur;
-      lv.out_size.resize(dim);
-      bool ok = true;
-      lv.F.tmax = 1;
-      for (int d = 0; d < dim; ++d) {
-        const int64_t f = filter_size[d];
-        if (cur[d] < f || (cur[d] - f) % f != 0) ok = false;
-        lv.out_size[d] = ok ? (cur[d] - f) / f + 1 : 1;
-        if (lv.out_size[d] > INT_MAX) ok = false;
-        lv.F.f[d] = lv.F.s[d] = (int)f;
-        lv.F.out_size[d] = (int)lv.out_size[d];
-        lv.F.tdim[d] = 1;
-        lv.K *= f;
-      }
-      if (!ok || lv.K > 4096) break;
-      auto found = md->strided_rules.find(make_key(dim, cur.data(), filter_size, filter_stride));
-      if (found != md->strided_rules.end() && found->second.built) break;
-      if (md->grids.count(make_key(dim, lv.out_size.data()))) break;
-      if (make_layout(dim, lv.out_size.data(), lv.gout.layout) != SCN_OK) break;
-      if (!(lv.gout.layout.batch_bits >= gin->layout.batch_bits ||
-            gin->batch_size <= (1ll << lv.gout.layout.batch_bits)))
-        break;
-      lv.bound_in = bound;
-      lv.cap_out = safe ? bound : std::max((bound + 1) / 2, std::min<long long>(bound, 4096));
-      bound = lv.cap_out;
-      cur = lv.out_size;
-      plan.push_back(std::move(lv));
+  std::vector<int64_t> cur = start;
+  long long bound = gin->n_active;
+  for (int l = 0; l < levels; ++l) {
+    ChainLevel lv;
+    lv.in_size = cur;
+    lv.out_size.resize(dim);
+    bool ok = true;
+    lv.F.tmax = 1;
+    for (int d = 0; d < dim; ++d) {
+      const int64_t f = filter[d];
+      if (cur[d] < f || (cur[d] - f) % f != 0) ok = false;
+      lv.out_size[d] = ok ? (cur[d] - f) / f + 1 : 1;
+      if (lv.out_size[d] > INT_MAX) ok = false;
+      lv.F.f[d] = lv.F.s[d] = (int)f;
+      lv.F.out_size[d] = (int)lv.out_size[d];
+      lv.F.tdim[d] = 1;
+      lv.K *= f;
     }
+    if (!ok || lv.K > 4096) break;
+    auto found = md->strided_rules.find(make_key(dim, cur.data(), filter, filter));
+    if (found != md->strided_rules.end() && found->second.built) break;
+    if (md->grids.count(make_key(dim, lv.out_size.data()))) break;
+    if (make_layout(dim, lv.out_size.data(), lv.gout.layout) != SCN_OK) break;
+    if (!(lv.gout.layout.batch_bits >= gin->layout.batch_bits || gin->batch_size <= (1ll << lv.gout.layout.batch_bits)))
+      break;
+    lv.bound_in = bound;
+    lv.cap_out = safe ? bound : std::max((bound + 1) / 2, std::min<long long>(bound, 4096));
+    bound = lv.cap_out;
+    cur = lv.out_size;
+    plan.push_back(std::move(lv));
+  }
+}
+
+// launch: every level's kernels and the post of all counts and flags into `mailbox` (pinned, mapped), on `stream`
+static int chain_launch(scn_metadata *md, const Grid *gin, std::vector<ChainLevel> &plan, int *mailbox,
+                        cudaStream_t stream) {
+  const int L = (int)plan.size();
+  int *mailbox_dev = nullptr;
+  SCN_CUDA_CHECK(cudaHostGetDevicePointer((void **)&mailbox_dev, mailbox, 0));
+  int *lev = nullptr;
+  SCN_TRY(device_alloc((void **)&lev, sizeof(int) * (2 * L + 1), stream));
+  int st = chain_enqueue(md, gin, plan, lev, stream);
+  if (st == SCN_OK) {
+    SCN_LAUNCH(k_chain_post, 1, 64, 0, stream, lev, 2 * L + 1, mailbox_dev);
+    if (cudaGetLastError() != cudaSuccess) {
+      set_error("strided chain: launch failed");
+      st = SCN_ERR_CUDA;
+    }
+  }
+  device_free(lev, stream);
+  if (st != SCN_OK)
+    for (auto &lv : plan) chain_free_level(lv, false, stream);
+  return st;
+}
+
+// collect (after the host has seen the mailbox): the levels up to the first that overflowed its arrays become
+// grids and rulebooks of the object, the others are freed.  Returns the number of good levels.
+static int chain_collect(scn_metadata *md, long long n_in, long long batch_size, std::vector<ChainLevel> &plan,
+                         const int64_t *filter, const volatile int *host, cudaStream_t stream, int *n_built) {
+  const int dim = md->dim, L = (int)plan.size();
+  int good = 0;
+  while (good < L && host[L + 1 + good] == 0 && host[good + 1] <= plan[good].cap_out) ++good;
+  for (int l = 0; l < L; ++l) {
+    ChainLevel &lv = plan[l];
+    if (l < good) {
+      const long long n_out = host[l + 1];
+      lv.gout.n_active = n_out;
+      lv.gout.batch_size = batch_size;
+      lv.rb.n_offsets = (int)lv.K;
+      lv.rb.n_in = n_in;
+      lv.rb.n_out = n_out;
+      lv.rb.built = true;
+      chain_free_level(lv, true, stream);
+      md->grids[make_key(dim, lv.out_size.data())] = lv.gout;
+      md->strided_rules[make_key(dim, lv.in_size.data(), filter, filter)] = lv.rb;
+      g_rulebook_builds.fetch_add(1);
+      if (n_built) ++*n_built;
+      n_in = n_out;
+    } else {
+      chain_free_level(lv, false, stream);
+    }
+  }
+  return good;
+}
+
+static bool chain_applies(int dim, const int64_t *filter_size, const int64_t *filter_stride) {
+  for (int d = 0; d < dim; ++d)
+    if (filter_size[d] != filter_stride[d] || filter_size[d] < 1 || filter_size[d] > 127) return false;
+  return true;
+}
+
+static Grid *find_grid_now(scn_metadata *md, const int64_t *spatial_size) {  // no pending chain is waited for
+  auto it = md->grids.find(make_key(md->dim, spatial_size));
+  return it == md->grids.end() ? nullptr : &it->second;
+}
+
+// A chain that was started on the side stream and whose counts the host has not looked at yet.
+struct PendingChain {
+  std::vector<ChainLevel> plan;
+  std::vector<int64_t> filter;
+  long long n_in = 0, batch_size = 0;
+  cudaEvent_t done = nullptr;
+  int *mailbox = nullptr;
+};
+
+static cudaStream_t g_side_stream[64] = {nullptr};
+static std::mutex g_side_mu;
+
+static int side_stream(cudaStream_t *out) {
+  int dev = 0;
+  SCN_CUDA_CHECK(cudaGetDevice(&dev));
+  SCN_REQUIRE(dev >= 0 && dev < 64, SCN_ERR_UNSUPPORTED, "device index %d unsupported", dev);
+  std::lock_guard<std::mutex> lock(g_side_mu);
+  if (!g_side_stream[dev]) SCN_CUDA_CHECK(cudaStreamCreateWithFlags(&g_side_stream[dev], cudaStreamNonBlocking));
+  *out = g_side_stream[dev];
+  return SCN_OK;
+}
+
+static int build_strided_chain_from(scn_metadata *md, std::vector<int64_t> start, const int64_t *filter, int levels,
+                                    bool safe, cudaStream_t stream, int *n_built);
+
+// The host looks at a started chain: waits for its event (usually long past), makes its levels the object's, and
+// builds again, on `stream` and with the safe bounds, whatever overflowed.
+static int chain_finalize(scn_metadata *md, cudaStream_t stream, int *n_built) {
+  PendingChain *p = md->pending;
+  if (!p) return SCN_OK;
+  md->pending = nullptr;
+  if (cudaEventQuery(p->done) != cudaSuccess) note_host_wait();
+  int st = SCN_OK;
+  if (cudaEventSynchronize(p->done) != cudaSuccess) {
+    set_error("strided chain: CUDA error while waiting for the level counts");
+    st = SCN_ERR_CUDA;
+  }
+  cudaEventDestroy(p->done);
+  const int L = (int)p->plan.size();
+  int good = L;
+  std::vector<int64_t> rest;
+  if (st == SCN_OK) {
+    good = chain_collect(md, p->n_in, p->batch_size, p->plan, p->filter.data(), p->mailbox, stream, n_built);
+    if (good < L) rest = p->plan[good].in_size;
+  } else {
+    for (auto &lv : p->plan) chain_free_level(lv, false, stream);
+  }
+  mailbox_release(p->mailbox);
+  std::vector<int64_t> filter = p->filter;
+  delete p;
+  if (st == SCN_OK && good < L) st = build_strided_chain_from(md, rest, filter.data(), L - good, true, stream, n_built);
+  return st;
+}
+
+// Drops a started chain (the object is cleared or destroyed): its arrays go back once its kernels have run.
+static void chain_abandon(scn_metadata *md, cudaStream_t stream) {
+  PendingChain *p = md->pending;
+  if (!p) return;
+  md->pending = nullptr;
+  cudaEventSynchronize(p->done);
+  cudaEventDestroy(p->done);
+  for (auto &lv : p->plan) chain_free_level(lv, false, stream);
+  mailbox_release(p->mailbox);
+  delete p;
+}
+
+static int build_strided_chain_from(scn_metadata *md, std::vector<int64_t> start, const int64_t *filter, int levels,
+                                    bool safe, cudaStream_t stream, int *n_built) {
+  while (levels >= 2) {
+    Grid *gin = find_grid_now(md, start.data());
+    if (!gin || gin->n_active >= (1ll << 31)) return SCN_OK;
+    std::vector<ChainLevel> plan;
+    chain_plan(md, gin, start, filter, levels, safe, plan);
     const int L = (int)plan.size();
     if (L < 2) return SCN_OK;
-    SCN_TRY(ensure_scratch(md, stream));
     if (!md->mailbox) SCN_TRY(mailbox_acquire(&md->mailbox));
-    int *mailbox_dev = nullptr;
-    SCN_CUDA_CHECK(cudaHostGetDevicePointer((void **)&mailbox_dev, md->mailbox, 0));
-    int *lev = nullptr;
-    SCN_TRY(device_alloc((void **)&lev, sizeof(int) * (2 * L + 1), stream));
-    int st = chain_enqueue(md, gin, plan, lev, stream);
-    if (st == SCN_OK) {
-      SCN_LAUNCH(k_chain_post, 1, 64, 0, stream, lev, 2 * L + 1, mailbox_dev);
-      note_host_wait();
-      if (cudaGetLastError() != cudaSuccess || cudaStreamSynchronize(stream) != cudaSuccess) {
-        set_error("strided chain: CUDA error while waiting for the level counts");
-        st = SCN_ERR_CUDA;
-      }
-    }
-    device_free(lev, stream);
-    if (st != SCN_OK) {
+    SCN_TRY(chain_launch(md, gin, plan, md->mailbox, stream));
+    note_host_wait();
+    if (cudaStreamSynchronize(stream) != cudaSuccess) {
+      set_error("strided chain: CUDA error while waiting for the level counts");
       for (auto &lv : plan) chain_free_level(lv, false, stream);
-      return st;
+      return SCN_ERR_CUDA;
     }
-    const volatile int *host = md->mailbox;
-    int good = 0;
-    while (good < L && host[L + 1 + good] == 0 && host[good + 1] <= plan[good].cap_out) ++good;
-    long long n_in = gin->n_active;
-    const long long batch_size = gin->batch_size;
-    for (int l = 0; l < L; ++l) {
-      ChainLevel &lv = plan[l];
-      if (l < good) {
-        const long long n_out = host[l + 1];
-        lv.gout.n_active = n_out;
-        lv.gout.batch_size = batch_size;
-        lv.rb.n_offsets = (int)lv.K;
-        lv.rb.n_in = n_in;
-        lv.rb.n_out = n_out;
-        lv.rb.built = true;
-        chain_free_level(lv, true, stream);
-        md->grids[make_key(dim, lv.out_size.data())] = lv.gout;
-        md->strided_rules[make_key(dim, lv.in_size.data(), filter_size, filter_stride)] = lv.rb;
-        g_rulebook_builds.fetch_add(1);
-        if (n_built) ++*n_built;
-        n_in = n_out;
-      } else {
-        chain_free_level(lv, false, stream);
-      }
-    }
+    const int good = chain_collect(md, gin->n_active, gin->batch_size, plan, filter, md->mailbox, stream, n_built);
     if (good == L) return SCN_OK;
     // a level shrank less than guessed: that level and the deeper ones again, arrays sized by the input
     start = plan[good].in_size;
     levels = L - good;
     safe = true;
   }
+  return SCN_OK;
+}
+
+// Builds up to `levels` consecutive rulebooks of (filter_size, filter_stride) starting at the grid of
+// `input_size`, each level's output size (in - f) / s + 1.  Does nothing (SCN_OK) where the chain does
+// not apply -- filter != stride, fewer than two levels to build, no grid, rulebooks already there --
+// because the per-level call that follows builds or reports whatever is left.  A chain that was started
+// earlier on the side stream is taken over here.
+int build_strided_chain(scn_metadata *md, const int64_t *input_size, const int64_t *filter_size,
+                        const int64_t *filter_stride, int levels, cudaStream_t stream, int *n_built) {
+  if (n_built) *n_built = 0;
+  SCN_TRY(md_touch(md, stream));
+  SCN_TRY(chain_finalize(md, stream, n_built));
+  if (!chain_applies(md->dim, filter_size, filter_stride)) return SCN_OK;
+  return build_strided_chain_from(md, std::vector<int64_t>(input_size, input_size + md->dim), filter_size,
+                                  std::min(levels, kMaxChain), false, stream, n_built);
+}
+
+// The same chain, started without waiting for it: its kernels go to a side stream of the device behind what
+// `stream` holds now (the input grid), so they run beside whatever the caller enqueues on `stream` next -- the
+// first level's convolutions of a U-Net -- and the host does not wait here.  Whoever first asks for one of those
+// levels (a grid that is not there yet, the rulebook of a level, scn_md_strided_chain) finds the chain finished,
+// reads the counts and makes the levels the object's.  Nothing is started when a chain is already under way.
+int start_strided_chain(scn_metadata *md, const int64_t *input_size, const int64_t *filter_size,
+                        const int64_t *filter_stride, int levels, cudaStream_t stream) {
+  SCN_TRY(md_touch(md, stream));
+  if (md->pending || !chain_applies(md->dim, filter_size, filter_stride)) return SCN_OK;
+  Grid *gin = find_grid_now(md, input_size);
+  if (!gin || gin->n_active >= (1ll << 31)) return SCN_OK;
+  PendingChain *p = new PendingChain();
+  chain_plan(md, gin, std::vector<int64_t>(input_size, input_size + md->dim), filter_size, std::min(levels, kMaxChain),
+             false, p->plan);
+  if (p->plan.size() < 2) {
+    delete p;
+    return SCN_OK;
+  }
+  cudaStream_t side = nullptr;
+  cudaEvent_t ready = nullptr;
+  int st = side_stream(&side);
+  if (st == SCN_OK) st = mailbox_acquire(&p->mailbox);
+  if (st == SCN_OK && (cudaEventCreateWithFlags(&ready, cudaEventDisableTiming) != cudaSuccess ||
+                       cudaEventCreateWithFlags(&p->done, cudaEventDisableTiming) != cudaSuccess ||
+                       cudaEventRecord(ready, stream) != cudaSuccess || cudaStreamWaitEvent(side, ready, 0) != cudaSuccess)) {
+    set_error("strided chain: could not order the side stream behind the caller's");
+    st = SCN_ERR_CUDA;
+  }
+  if (st == SCN_OK) st = chain_launch(md, gin, p->plan, p->mailbox, side);  // frees the plan's arrays on failure
+  if (st == SCN_OK && cudaEventRecord(p->done, side) != cudaSuccess) {
+    cudaStreamSynchronize(side);
+    for (auto &lv : p->plan) chain_free_level(lv, false, stream);
+    set_error("strided chain: could not record the end of the chain");
+    st = SCN_ERR_CUDA;
+  }
+  if (ready) cudaEventDestroy(ready);
+  if (st != SCN_OK) {
+    if (p->done) cudaEventDestroy(p->done);
+    mailbox_release(p->mailbox);
+    delete p;
+    return st;
+  }
+  p->filter.assign(filter_size, filter_size + md->dim);
+  p->n_in = gin->n_active;
+  p->batch_size = gin->batch_size;
+  md->pending = p;
   return SCN_OK;
 }
 
@@ -1370,6 +1535,12 @@ int scn_md_strided_chain(scn_metadata *md, const int64_t *input_size, const int6
                          const int64_t *filter_stride, int levels, void *stream, int *n_built) {
   SCN_REQUIRE(md && input_size && filter_size && filter_stride, SCN_ERR_BAD_ARG, "null argument");
   return build_strided_chain(md, input_size, filter_size, filter_stride, levels, (cudaStream_t)stream, n_built);
+}
+
+int scn_md_strided_chain_start(scn_metadata *md, const int64_t *input_size, const int64_t *filter_size,
+                               const int64_t *filter_stride, int levels, void *stream) {
+  SCN_REQUIRE(md && input_size && filter_size && filter_stride, SCN_ERR_BAD_ARG, "null argument");
+  return start_strided_chain(md, input_size, filter_size, filter_stride, levels, (cudaStream_t)stream);
 }
 
 int scn_md_strided_rulebook(scn_metadata *md, const int64_t *input_size, const int64_t *output_size,

@@ -61,6 +61,8 @@ int rulebook_counts(Rulebook &rb, cudaStream_t stream);         // fills counts_
 int rulebook_counts_async(Rulebook &rb, cudaStream_t stream);
 int rulebook_transposed(Rulebook &rb, cudaStream_t stream);     // builds tnbr if missing
 
+struct PendingChain;  // metadata.cu: levels of a strided chain whose kernels run on the side stream
+
 }  // namespace scn
 
 struct scn_metadata {
@@ -82,6 +84,7 @@ struct scn_metadata {
   int *input_csr_rows = nullptr;   // [n_rows]
 
   scn::CountTicket *last_ticket = nullptr;  // of the last operator that answered "count pending"
+  scn::PendingChain *pending = nullptr;     // a strided chain started with scn_md_strided_chain_start, not yet taken over
 
   int *flags_dev = nullptr;   // device word the kernels OR DeviceFlag bits into
   int *mailbox = nullptr;     // pinned, device-mapped host slot (8 ints) the waited-for integers are posted to

@@ -416,7 +416,9 @@ def _pyramid(cuda, coords, size, levels, chained):
     m = x.metadata
     waits, builds = SCN.host_wait_count(), SCN.lib.scn_rulebook_build_count()
     f = torch.LongTensor([2] * dim)
-    n_chained = SCN.strided_chain(m, x.spatial_size, f, f, levels, cuda) if chained else 0
+    if chained == "started":   # on the side stream, taken over by the first per-level call below
+        SCN.strided_chain_start(m, x.spatial_size, f, f, levels, cuda)
+    n_chained = SCN.strided_chain(m, x.spatial_size, f, f, levels, cuda) if chained is True else 0
     locs, rules, cur = [], [], x.spatial_size.clone()
     for _ in range(levels):
         nxt = (cur - 2) // 2 + 1
@@ -463,6 +465,11 @@ def test_chained_strided_levels_equal_level_by_level(kind, cuda):
     for l in range(levels):
         assert np.array_equal(a[0][l], b[0][l]), "grid of level %d" % l
         _exact_rules(a[1][l], b[1][l], "rulebook of level %d" % l)
+    c = _pyramid(cuda, coords, 1024, levels, chained="started")
+    assert c[3] == levels
+    for l in range(levels):
+        assert np.array_equal(a[0][l], c[0][l]), "grid of level %d (chain started on the side stream)" % l
+        _exact_rules(a[1][l], c[1][l], "rulebook of level %d (chain started on the side stream)" % l)
     if kind == "empty":                                # nothing to count, nothing to wait for level by level
         return
     assert a[2] == levels                              # one wait per level (after the input layer's own)
@@ -470,3 +477,71 @@ def test_chained_strided_levels_equal_level_by_level(kind, cuda):
         assert 2 <= b[2] <= 3                          # the first pass and one or two repeats
     else:
         assert b[2] == 1                               # one wait for the whole chain
+
+
+def test_started_chain_is_dropped_with_its_metadata(cuda):
+    """A chain started on the side stream and never asked for: clearing the Metadata, giving it a new input and
+    destroying it all release it, and the library's pool holds no more than before."""
+    import gc
+    import sparseconvnet_b200 as scn
+    from sparseconvnet_b200 import SCN
+    rng = np.random.default_rng(3)
+    coords = np.concatenate([rng.integers(0, 512, (40000, 3)), np.zeros((40000, 1), np.int64)], 1).astype(np.int64)
+    feats = torch.ones(40000, 1, device=cuda)
+    f = torch.LongTensor([2, 2, 2])
+    inp = scn.InputLayer(3, 512, mode=3)
+    x = inp([torch.from_numpy(coords), feats])      # warm the pool up
+    SCN.strided_chain(x.metadata, x.spatial_size, f, f, 4, cuda)
+    del x
+    gc.collect()
+    torch.cuda.synchronize()
+    used = C_memory_in_use()
+    for what in ("clear", "new input", "destroy"):
+        x = inp([torch.from_numpy(coords), feats])
+        SCN.strided_chain_start(x.metadata, x.spatial_size, f, f, 4, cuda)
+        if what == "clear":
+            x.metadata.clear()
+        elif what == "new input":
+            SCN.InputLayer_updateOutput(x.metadata, x.spatial_size, torch.from_numpy(coords), feats,
+                                        torch.empty(0, device=cuda), 0, 3)
+            assert x.metadata.getNActive(x.spatial_size) > 0
+        del x
+        gc.collect()
+        torch.cuda.synchronize()
+        assert C_memory_in_use() <= used, what
+
+
+def C_memory_in_use():
+    import ctypes as C
+    from sparseconvnet_b200 import SCN
+    reserved, in_use = C.c_uint64(), C.c_uint64()
+    SCN.check(SCN.lib.scn_memory_usage(C.byref(reserved), C.byref(in_use)))
+    return in_use.value
+
+
+def test_unet_prefetches_its_encoder_rulebooks(cuda):
+    """The outermost Sequential starts the encoder's chain on the side stream (Metadata.chain_started), the
+    network's result has the same bits with and without it, and the step has two host waits either way."""
+    import sparseconvnet_b200 as scn
+    from sparseconvnet_b200 import SCN, workloads
+    coords, feats = workloads.batch_config3([0], target_voxels=60000)
+    inp, net, _ = workloads.build_config(3)
+    net.to(cuda).eval()
+    scn.set_precision("tf32x3")
+    try:
+        outs = []
+        for prefetch in (False, True):
+            scn.Sequential.prefetch_rulebooks = prefetch
+            with torch.no_grad():
+                x = inp([torch.from_numpy(coords), torch.from_numpy(feats).to(cuda)])
+                waits = SCN.host_wait_count()
+                y = net(x)
+                waits = SCN.host_wait_count() - waits
+            assert x.metadata.chain_started == prefetch
+            assert waits <= 1, waits          # the chain's counts (often already there when they are asked for)
+            y.metadata.poll_errors()
+            outs.append(y.features.clone())
+    finally:
+        scn.Sequential.prefetch_rulebooks = True
+        scn.set_precision("fp32")
+    assert torch.equal(outs[0], outs[1])
