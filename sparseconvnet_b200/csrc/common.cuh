@@ -200,6 +200,8 @@ int device_free(void *p, cudaStream_t stream);
 
 // Exclusive prefix sum of n int32 values (out may alias in).  total_dev (may be null)
 // receives the sum of all inputs as int32.
-int exclusive_scan_i32(const int *in, int *out, long long n, int *total_dev, cudaStream_t stream);
+int exclusive_scan_i32(const int *in, int *out, long long n, int *total_dev, cudaStream_t stream,
+                       int *scratch = nullptr);
+size_t exclusive_scan_scratch_ints(long long n);  // ints of caller-owned scratch that make the scan allocation-free
 
 }  // namespace scn

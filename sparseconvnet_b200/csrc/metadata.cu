@@ -877,7 +877,7 @@ struct ChainLevel {
   Grid gout;
   Rulebook rb;
   long long bound_in = 0, cap_out = 0;
-  int *slot_of = nullptr, *flag = nullptr, *rank = nullptr;
+  int *slot_of = nullptr, *flag = nullptr, *rank = nullptr, *scan = nullptr;  // scratch of the level's build
 };
 
 __global__ void k_chain_init(int *lev, int n_ints, int n0) {
@@ -893,11 +893,34 @@ static void chain_free_level(ChainLevel &lv, bool keep_result, cudaStream_t stre
   device_free(lv.slot_of, stream);
   device_free(lv.flag, stream);
   device_free(lv.rank, stream);
-  lv.slot_of = lv.flag = lv.rank = nullptr;
+  device_free(lv.scan, stream);
+  lv.slot_of = lv.flag = lv.rank = lv.scan = nullptr;
   if (!keep_result) {
     free_grid(lv.gout, stream);
     free_rulebook(lv.rb, stream);
   }
+}
+
+// Memory first, work second.  Everything the chain needs is allocated on `alloc_stream` (stream-ordered
+// allocation: the blocks may be ones that earlier work of THAT stream is still using), and only then are the
+// memsets and kernels enqueued on `stream`.  With two different streams the caller orders `stream` behind
+// `alloc_stream` between the two calls and frees the scratch later, on a stream that is ordered behind `stream`.
+static int chain_allocate(std::vector<ChainLevel> &plan, cudaStream_t alloc_stream) {
+  for (auto &lv : plan) {
+    const size_t n_ids = (size_t)std::max<long long>(lv.bound_in, 1), cap = (size_t)std::max<long long>(lv.cap_out, 1);
+    SCN_TRY(device_alloc((void **)&lv.slot_of, sizeof(int) * n_ids, alloc_stream));
+    SCN_TRY(device_alloc((void **)&lv.flag, sizeof(int) * n_ids, alloc_stream));
+    SCN_TRY(device_alloc((void **)&lv.rank, sizeof(int) * n_ids, alloc_stream));
+    SCN_TRY(device_alloc((void **)&lv.scan, sizeof(int) * exclusive_scan_scratch_ints(lv.bound_in), alloc_stream));
+    const unsigned long long slots = next_pow2((unsigned long long)std::max<long long>(64, 2 * lv.cap_out));
+    SCN_REQUIRE(slots < (1ull << 31), SCN_ERR_UNSUPPORTED, "site table too large (%llu slots)", slots);
+    lv.gout.table.n_buckets = slots / 2;
+    SCN_TRY(device_alloc((void **)&lv.gout.table.slots, slots * sizeof(Slot), alloc_stream));
+    SCN_TRY(device_alloc((void **)&lv.gout.row_keys, sizeof(unsigned long long) * cap, alloc_stream));
+    SCN_TRY(device_alloc((void **)&lv.rb.nbr, sizeof(int) * (size_t)lv.K * cap, alloc_stream));
+    SCN_TRY(device_alloc((void **)&lv.rb.counts_dev, sizeof(unsigned long long) * (size_t)lv.K, alloc_stream));
+  }
+  return SCN_OK;
 }
 
 static int chain_enqueue(scn_metadata *md, const Grid *gin, std::vector<ChainLevel> &plan, int *lev,
@@ -908,33 +931,22 @@ static int chain_enqueue(scn_metadata *md, const Grid *gin, std::vector<ChainLev
   KeyLayout Lin = gin->layout;
   for (int l = 0; l < L; ++l) {
     ChainLevel &lv = plan[l];
-    const size_t n_ids = (size_t)std::max<long long>(lv.bound_in, 1), cap = (size_t)std::max<long long>(lv.cap_out, 1);
-    SCN_TRY(device_alloc((void **)&lv.slot_of, sizeof(int) * n_ids, stream));
-    SCN_TRY(device_alloc((void **)&lv.flag, sizeof(int) * n_ids, stream));
-    SCN_TRY(device_alloc((void **)&lv.rank, sizeof(int) * n_ids, stream));
-    SCN_TRY(alloc_table(lv.gout.table, lv.cap_out, stream));
-    SCN_TRY(device_alloc((void **)&lv.gout.row_keys, sizeof(unsigned long long) * cap, stream));
-    const size_t nbr_bytes = sizeof(int) * (size_t)lv.K * cap;
-    SCN_TRY(device_alloc((void **)&lv.rb.nbr, nbr_bytes, stream));
-    SCN_CUDA_CHECK(cudaMemsetAsync(lv.rb.nbr, 0xFF, nbr_bytes, stream));
-    SCN_TRY(device_alloc((void **)&lv.rb.counts_dev, sizeof(unsigned long long) * (size_t)lv.K, stream));
+    const size_t cap = (size_t)std::max<long long>(lv.cap_out, 1);
+    // key = all ones (free), row = -1, aux = 0xFFFFFFFF
+    SCN_CUDA_CHECK(cudaMemsetAsync(lv.gout.table.slots, 0xFF, 2 * lv.gout.table.n_buckets * sizeof(Slot), stream));
+    SCN_CUDA_CHECK(cudaMemsetAsync(lv.rb.nbr, 0xFF, sizeof(int) * (size_t)lv.K * cap, stream));
     SCN_CUDA_CHECK(cudaMemsetAsync(lv.rb.counts_dev, 0, sizeof(unsigned long long) * (size_t)lv.K, stream));
     if (lv.bound_in > 0) {
       const unsigned blocks = (unsigned)ceil_div(lv.bound_in, threads);
       int *n_in_dev = lev + l, *n_out_dev = lev + l + 1, *level_flags = lev + L + 1 + l;
       SCN_LAUNCH(k_strided_insert, blocks, threads, 0, stream, Lin, lv.gout.layout, lv.F, lv.gout.table, in_keys, lv.bound_in, n_in_dev, lv.slot_of, level_flags);
       SCN_LAUNCH(k_flag_first, blocks, threads, 0, stream, lv.gout.table.slots, lv.slot_of, lv.bound_in, lv.flag);
-      SCN_TRY(exclusive_scan_i32(lv.flag, lv.rank, lv.bound_in, n_out_dev, stream));
+      SCN_TRY(exclusive_scan_i32(lv.flag, lv.rank, lv.bound_in, n_out_dev, stream, lv.scan));
       const long long n_slots = 2 * (long long)lv.gout.table.n_buckets;
       SCN_LAUNCH(k_number_slots, (unsigned)ceil_div(n_slots, threads), threads, 0, stream, lv.gout.table.slots, n_slots, lv.rank, lv.cap_out, level_flags, lv.gout.row_keys);
       SCN_LAUNCH(k_strided_fill, blocks, threads, 0, stream, Lin, lv.F, lv.gout.table.slots, in_keys, lv.slot_of, lv.bound_in, 0ll, n_out_dev, lv.cap_out, lv.rb.nbr, lv.rb.counts_dev);
       SCN_CUDA_CHECK(cudaGetLastError());
     }
-    // stream-ordered: the scratch goes back behind the level's kernels, before the host waits
-    device_free(lv.slot_of, stream);
-    device_free(lv.flag, stream);
-    device_free(lv.rank, stream);
-    lv.slot_of = lv.flag = lv.rank = nullptr;
     in_keys = lv.gout.row_keys;
     Lin = lv.gout.layout;
   }
@@ -980,26 +992,17 @@ static void chain_plan(scn_metadata *md, const Grid *gin, const std::vector<int6
   }
 }
 
-// launch: every level's kernels and the post of all counts and flags into `mailbox` (pinned, mapped), on `stream`
-static int chain_launch(scn_metadata *md, const Grid *gin, std::vector<ChainLevel> &plan, int *mailbox,
+// launch: every level's kernels and the post of all counts and flags into `mailbox` (pinned, mapped), on `stream`;
+// the plan's arrays and `lev` (2 L + 1 ints) were allocated before
+static int chain_launch(scn_metadata *md, const Grid *gin, std::vector<ChainLevel> &plan, int *lev, int *mailbox,
                         cudaStream_t stream) {
   const int L = (int)plan.size();
   int *mailbox_dev = nullptr;
   SCN_CUDA_CHECK(cudaHostGetDevicePointer((void **)&mailbox_dev, mailbox, 0));
-  int *lev = nullptr;
-  SCN_TRY(device_alloc((void **)&lev, sizeof(int) * (2 * L + 1), stream));
-  int st = chain_enqueue(md, gin, plan, lev, stream);
-  if (st == SCN_OK) {
-    SCN_LAUNCH(k_chain_post, 1, 64, 0, stream, lev, 2 * L + 1, mailbox_dev);
-    if (cudaGetLastError() != cudaSuccess) {
-      set_error("strided chain: launch failed");
-      st = SCN_ERR_CUDA;
-    }
-  }
-  device_free(lev, stream);
-  if (st != SCN_OK)
-    for (auto &lv : plan) chain_free_level(lv, false, stream);
-  return st;
+  SCN_TRY(chain_enqueue(md, gin, plan, lev, stream));
+  SCN_LAUNCH(k_chain_post, 1, 64, 0, stream, lev, 2 * L + 1, mailbox_dev);
+  SCN_CUDA_CHECK(cudaGetLastError());
+  return SCN_OK;
 }
 
 // collect (after the host has seen the mailbox): the levels up to the first that overflowed its arrays become
@@ -1050,6 +1053,7 @@ struct PendingChain {
   long long n_in = 0, batch_size = 0;
   cudaEvent_t done = nullptr;
   int *mailbox = nullptr;
+  int *lev = nullptr;  // the chain's device counters, freed when the chain is taken over
 };
 
 static cudaStream_t g_side_stream[64] = {nullptr};
@@ -1090,6 +1094,7 @@ static int chain_finalize(scn_metadata *md, cudaStream_t stream, int *n_built) {
   } else {
     for (auto &lv : p->plan) chain_free_level(lv, false, stream);
   }
+  device_free(p->lev, stream);
   mailbox_release(p->mailbox);
   std::vector<int64_t> filter = p->filter;
   delete p;
@@ -1105,6 +1110,7 @@ static void chain_abandon(scn_metadata *md, cudaStream_t stream) {
   cudaEventSynchronize(p->done);
   cudaEventDestroy(p->done);
   for (auto &lv : p->plan) chain_free_level(lv, false, stream);
+  device_free(p->lev, stream);
   mailbox_release(p->mailbox);
   delete p;
 }
@@ -1119,12 +1125,21 @@ static int build_strided_chain_from(scn_metadata *md, std::vector<int64_t> start
     const int L = (int)plan.size();
     if (L < 2) return SCN_OK;
     if (!md->mailbox) SCN_TRY(mailbox_acquire(&md->mailbox));
-    SCN_TRY(chain_launch(md, gin, plan, md->mailbox, stream));
-    note_host_wait();
-    if (cudaStreamSynchronize(stream) != cudaSuccess) {
-      set_error("strided chain: CUDA error while waiting for the level counts");
+    int *lev = nullptr;
+    int st = device_alloc((void **)&lev, sizeof(int) * (2 * L + 1), stream);
+    if (st == SCN_OK) st = chain_allocate(plan, stream);
+    if (st == SCN_OK) st = chain_launch(md, gin, plan, lev, md->mailbox, stream);
+    device_free(lev, stream);
+    if (st == SCN_OK) {
+      note_host_wait();
+      if (cudaStreamSynchronize(stream) != cudaSuccess) {
+        set_error("strided chain: CUDA error while waiting for the level counts");
+        st = SCN_ERR_CUDA;
+      }
+    }
+    if (st != SCN_OK) {
       for (auto &lv : plan) chain_free_level(lv, false, stream);
-      return SCN_ERR_CUDA;
+      return st;
     }
     const int good = chain_collect(md, gin->n_active, gin->batch_size, plan, filter, md->mailbox, stream, n_built);
     if (good == L) return SCN_OK;
@@ -1169,25 +1184,36 @@ int start_strided_chain(scn_metadata *md, const int64_t *input_size, const int64
     delete p;
     return SCN_OK;
   }
+  // The chain's memory comes from `stream` (blocks that earlier work of `stream` gave back can be used again at
+  // once; taken on the side stream the pool would have to find blocks nobody can still be using, and grows when it
+  // finds none: single steps of 18-22 ms among 13.6 ms ones).  The side stream starts behind that point of
+  // `stream`; the scratch goes back when the chain is taken over.
   cudaStream_t side = nullptr;
   cudaEvent_t ready = nullptr;
   int st = side_stream(&side);
   if (st == SCN_OK) st = mailbox_acquire(&p->mailbox);
+  if (st == SCN_OK) st = device_alloc((void **)&p->lev, sizeof(int) * (2 * p->plan.size() + 1), stream);
+  if (st == SCN_OK) st = chain_allocate(p->plan, stream);
   if (st == SCN_OK && (cudaEventCreateWithFlags(&ready, cudaEventDisableTiming) != cudaSuccess ||
                        cudaEventCreateWithFlags(&p->done, cudaEventDisableTiming) != cudaSuccess ||
                        cudaEventRecord(ready, stream) != cudaSuccess || cudaStreamWaitEvent(side, ready, 0) != cudaSuccess)) {
     set_error("strided chain: could not order the side stream behind the caller's");
     st = SCN_ERR_CUDA;
   }
-  if (st == SCN_OK) st = chain_launch(md, gin, p->plan, p->mailbox, side);  // frees the plan's arrays on failure
+  bool launched = false;
+  if (st == SCN_OK) {
+    st = chain_launch(md, gin, p->plan, p->lev, p->mailbox, side);
+    launched = true;  // (possibly in part)
+  }
   if (st == SCN_OK && cudaEventRecord(p->done, side) != cudaSuccess) {
-    cudaStreamSynchronize(side);
-    for (auto &lv : p->plan) chain_free_level(lv, false, stream);
     set_error("strided chain: could not record the end of the chain");
     st = SCN_ERR_CUDA;
   }
   if (ready) cudaEventDestroy(ready);
   if (st != SCN_OK) {
+    if (launched) cudaStreamSynchronize(side);  // what was enqueued must not outlive the arrays
+    for (auto &lv : p->plan) chain_free_level(lv, false, stream);
+    device_free(p->lev, stream);
     if (p->done) cudaEventDestroy(p->done);
     mailbox_release(p->mailbox);
     delete p;

@@ -137,8 +137,15 @@ __global__ void __launch_bounds__(kScanThreads) k_scan_tiles(const int *in, int 
 
 __global__ void k_set_zero(int *p) { *p = 0; }
 
-int exclusive_scan_i32(const int *in, int *out, long long n, int *total_dev,
-                       cudaStream_t stream) {
+size_t exclusive_scan_scratch_ints(long long n) {
+  size_t total = 0;
+  for (long long tiles = ceil_div(std::max<long long>(n, 1), kScanTile); tiles > 1; tiles = ceil_div(tiles, kScanTile))
+    total += (size_t)tiles;
+  return total + 1;
+}
+
+// `scratch` (optional): exclusive_scan_scratch_ints(n) ints the caller owns, so that nothing is allocated here
+int exclusive_scan_i32(const int *in, int *out, long long n, int *total_dev, cudaStream_t stream, int *scratch) {
   if (n <= 0) {
     if (total_dev) SCN_LAUNCH(k_set_zero, 1, 1, 0, stream, total_dev);
     return SCN_OK;
@@ -149,14 +156,14 @@ int exclusive_scan_i32(const int *in, int *out, long long n, int *total_dev,
     SCN_CUDA_CHECK(cudaGetLastError());
     return SCN_OK;
   }
-  int *sums = nullptr;
-  SCN_TRY(device_alloc((void **)&sums, sizeof(int) * (size_t)tiles, stream));
+  int *sums = scratch;
+  if (!sums) SCN_TRY(device_alloc((void **)&sums, sizeof(int) * (size_t)tiles, stream));
   SCN_LAUNCH(k_scan_tile_sums, (unsigned)tiles, kScanThreads, 0, stream, in, sums, n);
   SCN_CUDA_CHECK(cudaGetLastError());
-  SCN_TRY(exclusive_scan_i32(sums, sums, tiles, nullptr, stream));
+  SCN_TRY(exclusive_scan_i32(sums, sums, tiles, nullptr, stream, scratch ? scratch + tiles : nullptr));
   SCN_LAUNCH(k_scan_tiles, (unsigned)tiles, kScanThreads, 0, stream, in, out, sums, n, total_dev);
   SCN_CUDA_CHECK(cudaGetLastError());
-  SCN_TRY(device_free(sums, stream));
+  if (!scratch) SCN_TRY(device_free(sums, stream));
   return SCN_OK;
 }
 
