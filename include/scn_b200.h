@@ -198,13 +198,13 @@ SCN_API int scn_md_strided_rulebook(scn_metadata *md, const int64_t *input_size,
                             int64_t *n_rules);
 
 /* Builds, in one enqueued chain, the grids and rulebooks of up to `levels` consecutive levels of the same
- * downsampling (filter_size == filter_stride in every dimension, each level's output size (in - f) / s +
- * 1 being the next level's input size) below the grid of `input_size`: what an encoder's Convolutions
+ * downsampling (the same filter_size and filter_stride, each level's output size (in - f) / s + 1 being the
+ * next level's input size) below the grid of `input_size`: what an encoder's Convolutions
  * would otherwise request one at a time through scn_md_strided_rulebook (Metadata<D>::getRuleBook,
  * Metadata.cpp:492-518), each request ending in a wait for that level's site count.  The chain waits for
  * `stream` once, for all counts together; the per-level calls that follow find their rulebooks built.
  * Grids, row numbering and rulebooks are the ones the per-level calls would have made.  Where the chain
- * does not apply (filter != stride, fewer than two levels left to build, no grid of `input_size`) nothing
+ * does not apply (fewer than two levels left to build, sizes that do not divide, no grid of `input_size`) nothing
  * is built and the result is SCN_OK.  n_built (may be NULL) receives the number of levels built.  The
  * reference has no such call; it is a hint for callers that know the shape of their network. */
 SCN_API int scn_md_strided_chain(scn_metadata *md, const int64_t *input_size, const int64_t *filter_size,

@@ -578,7 +578,7 @@ def SubmanifoldConvolution_updateOutput(inputSize, filterSize, m, input_features
 
 def strided_chain(m, inputSize, filterSize, filterStride, levels, device):
     """Not in the reference: a hint from a caller that knows its network goes `levels` levels down with
-    the same filter = stride downsampling (a U-Net's encoder).  The grids and rulebooks of those levels
+    the same downsampling (a U-Net's or ResNet's encoder).  The grids and rulebooks of those levels
     (Metadata<D>::getRuleBook, Metadata.cpp:492-518, once per level) are built in one enqueued chain with
     a single wait for all the level counts; the Convolutions then find theirs in the cache.  Returns the
     number of levels built (0 when there was nothing to chain)."""

@@ -63,23 +63,29 @@ def SparseResNet(dimension, nInputPlanes, layers):
     n_planes = nInputPlanes
     m = scn.Sequential()
 
-    def shortcut(n_in, n_out, stride):
+    def down(n_in, n_out, stride, index):
+        conv = scn.Convolution(dimension, n_in, n_out, 3, stride, False)
+        # layers from here on that go down by the same stride: their grids and rulebooks can be built together
+        conv.levels_below = sum(1 for layer in layers[index:] if layer[3] == stride)
+        return conv
+
+    def shortcut(n_in, n_out, stride, index):
         if stride > 1:
-            return scn.Convolution(dimension, n_in, n_out, 3, stride, False)
+            return down(n_in, n_out, stride, index)
         if n_in != n_out:
             return scn.NetworkInNetwork(n_in, n_out, False)
         return scn.Identity()
 
-    for block_type, n, reps, stride in layers:
+    for index, (block_type, n, reps, stride) in enumerate(layers):
         for rep in range(reps):
             if block_type[0] == "b":
                 if rep == 0:
                     m.add(scn.BatchNormReLU(n_planes))
                     first = (scn.SubmanifoldConvolution(dimension, n_planes, n, 3, False) if stride == 1
-                             else scn.Convolution(dimension, n_planes, n, 3, stride, False))
+                             else down(n_planes, n, stride, index))
                     main = scn.Sequential().add(first).add(scn.BatchNormReLU(n)).add(
                         scn.SubmanifoldConvolution(dimension, n, n, 3, False))
-                    m.add(scn.ConcatTable().add(main).add(shortcut(n_planes, n, stride)))
+                    m.add(scn.ConcatTable().add(main).add(shortcut(n_planes, n, stride, index)))
                 else:
                     main = scn.Sequential().add(scn.BatchNormReLU(n_planes)).add(
                         scn.SubmanifoldConvolution(dimension, n_planes, n, 3, False)).add(

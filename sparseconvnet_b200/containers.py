@@ -14,13 +14,25 @@ def _flatten(seq, out):
     return out
 
 
+def _keeps_sites(m):
+    """True for a module whose output has the sites and the spatial size of its input."""
+    from . import layers
+    if isinstance(m, (layers.SubmanifoldConvolution, layers.BatchNormalization, layers.Identity, layers.NetworkInNetwork,
+                      AddTable, JoinTable)):
+        return True
+    if type(m) is Sequential:
+        return all(_keeps_sites(c) for c in m._modules.values())
+    if type(m) is ConcatTable:
+        return all(_keeps_sites(c) for c in m._modules.values())
+    return False
+
+
 def _chain_ahead(steps):
     """The first downsampling Convolution that announces further levels (``levels_below > 1``) and is reached
     from the start of `steps` through modules that keep the sites and the spatial size -- so that its input grid
     is the grid of the tensor that enters `steps` -- looking into the branches of a ConcatTable.  None if there
     is none."""
     from . import layers
-    keeps = (layers.SubmanifoldConvolution, layers.BatchNormalization, layers.Identity, layers.NetworkInNetwork)
     for m in steps:
         if isinstance(m, layers.Convolution):
             return m if m.levels_below > 1 else None
@@ -29,8 +41,7 @@ def _chain_ahead(steps):
                 found = _chain_ahead(_flatten(branch, []) if type(branch) is Sequential else [branch])
                 if found is not None:
                     return found
-            return None  # what follows a ConcatTable works on a list of tensors
-        if not isinstance(m, keeps):
+        if not _keeps_sites(m):
             return None
     return None
 

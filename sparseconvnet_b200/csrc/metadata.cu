@@ -858,16 +858,17 @@ int get_strided_rulebook(scn_metadata *md, const int64_t *input_size, const int6
 }
 
 // ---- a chain of strided levels ---------------------------------------------------------------
-// A U-Net asks for the same filter = stride rulebook at every level, each level's input being the last
-// level's output.  Built one call at a time, every level ends with the host waiting for its row count
+// An encoder asks for the same (filter, stride) rulebook at every level (2/2 in a U-Net, 3/2 in a ResNet),
+// each level's input being the last level's output.  Built one call at a time, every level ends with the host waiting for its row count
 // (the next level's arrays and launches are sized by it), the GPU idling through each round trip.
 // Here the whole chain is enqueued at once: level l reads its number of input sites from the device
 // (`lev[l]`), its launches and arrays are sized by a bound the host knows, and one mailbox read at the
 // end fetches every level's count.  With disjoint windows (filter == stride) a level has at most as
 // many sites as its input; the arrays are sized for half of the input bound (surfaces and volumes
-// shrink by 2.5x to 8x per level in 3-D), and a level that shrank less raises its own flag, after
-// which that level and the deeper ones are enqueued again with the safe bound.  Same kernels, same
-// numbering (first touch in input-row order) as one call per level.
+// shrink by 2.5x to 8x per level in 3-D); with overlapping windows they are sized for as many sites as
+// the input has.  A level that needs more raises its own flag, after which that level and the deeper
+// ones are enqueued again with the safe bound (one site per candidate).  Same kernels, same numbering
+// (first touch in input-row order) as one call per level.
 constexpr int kMaxChain = 16;
 
 struct ChainLevel {
@@ -907,11 +908,11 @@ static void chain_free_level(ChainLevel &lv, bool keep_result, cudaStream_t stre
 // `alloc_stream` between the two calls and frees the scratch later, on a stream that is ordered behind `stream`.
 static int chain_allocate(std::vector<ChainLevel> &plan, cudaStream_t alloc_stream) {
   for (auto &lv : plan) {
-    const size_t n_ids = (size_t)std::max<long long>(lv.bound_in, 1), cap = (size_t)std::max<long long>(lv.cap_out, 1);
+    const size_t n_ids = (size_t)std::max<long long>(lv.bound_in * lv.F.tmax, 1), cap = (size_t)std::max<long long>(lv.cap_out, 1);
     SCN_TRY(device_alloc((void **)&lv.slot_of, sizeof(int) * n_ids, alloc_stream));
     SCN_TRY(device_alloc((void **)&lv.flag, sizeof(int) * n_ids, alloc_stream));
     SCN_TRY(device_alloc((void **)&lv.rank, sizeof(int) * n_ids, alloc_stream));
-    SCN_TRY(device_alloc((void **)&lv.scan, sizeof(int) * exclusive_scan_scratch_ints(lv.bound_in), alloc_stream));
+    SCN_TRY(device_alloc((void **)&lv.scan, sizeof(int) * exclusive_scan_scratch_ints((long long)n_ids), alloc_stream));
     const unsigned long long slots = next_pow2((unsigned long long)std::max<long long>(64, 2 * lv.cap_out));
     SCN_REQUIRE(slots < (1ull << 31), SCN_ERR_UNSUPPORTED, "site table too large (%llu slots)", slots);
     lv.gout.table.n_buckets = slots / 2;
@@ -937,11 +938,12 @@ static int chain_enqueue(scn_metadata *md, const Grid *gin, std::vector<ChainLev
     SCN_CUDA_CHECK(cudaMemsetAsync(lv.rb.nbr, 0xFF, sizeof(int) * (size_t)lv.K * cap, stream));
     SCN_CUDA_CHECK(cudaMemsetAsync(lv.rb.counts_dev, 0, sizeof(unsigned long long) * (size_t)lv.K, stream));
     if (lv.bound_in > 0) {
-      const unsigned blocks = (unsigned)ceil_div(lv.bound_in, threads);
+      const long long n_ids = lv.bound_in * lv.F.tmax;  // (site, output it may feed) candidates
+      const unsigned blocks = (unsigned)ceil_div(n_ids, threads);
       int *n_in_dev = lev + l, *n_out_dev = lev + l + 1, *level_flags = lev + L + 1 + l;
       SCN_LAUNCH(k_strided_insert, blocks, threads, 0, stream, Lin, lv.gout.layout, lv.F, lv.gout.table, in_keys, lv.bound_in, n_in_dev, lv.slot_of, level_flags);
-      SCN_LAUNCH(k_flag_first, blocks, threads, 0, stream, lv.gout.table.slots, lv.slot_of, lv.bound_in, lv.flag);
-      SCN_TRY(exclusive_scan_i32(lv.flag, lv.rank, lv.bound_in, n_out_dev, stream, lv.scan));
+      SCN_LAUNCH(k_flag_first, blocks, threads, 0, stream, lv.gout.table.slots, lv.slot_of, n_ids, lv.flag);
+      SCN_TRY(exclusive_scan_i32(lv.flag, lv.rank, n_ids, n_out_dev, stream, lv.scan));
       const long long n_slots = 2 * (long long)lv.gout.table.n_buckets;
       SCN_LAUNCH(k_number_slots, (unsigned)ceil_div(n_slots, threads), threads, 0, stream, lv.gout.table.slots, n_slots, lv.rank, lv.cap_out, level_flags, lv.gout.row_keys);
       SCN_LAUNCH(k_strided_fill, blocks, threads, 0, stream, Lin, lv.F, lv.gout.table.slots, in_keys, lv.slot_of, lv.bound_in, 0ll, n_out_dev, lv.cap_out, lv.rb.nbr, lv.rb.counts_dev);
@@ -957,7 +959,7 @@ static int chain_enqueue(scn_metadata *md, const Grid *gin, std::vector<ChainLev
 // plan: sizes, layouts and bounds of the levels below `start` that can be chained (stops at the first level that
 // is already there, does not divide, or does not fit the key)
 static void chain_plan(scn_metadata *md, const Grid *gin, const std::vector<int64_t> &start, const int64_t *filter,
-                       int levels, bool safe, std::vector<ChainLevel> &plan) {
+                       const int64_t *stride, int levels, bool safe, std::vector<ChainLevel> &plan) {
   const int dim = md->dim;
   std::vector<int64_t> cur = start;
   long long bound = gin->n_active;
@@ -967,25 +969,40 @@ static void chain_plan(scn_metadata *md, const Grid *gin, const std::vector<int6
     lv.out_size.resize(dim);
     bool ok = true;
     lv.F.tmax = 1;
+    long long out_volume = gin->batch_size;
     for (int d = 0; d < dim; ++d) {
-      const int64_t f = filter[d];
-      if (cur[d] < f || (cur[d] - f) % f != 0) ok = false;
-      lv.out_size[d] = ok ? (cur[d] - f) / f + 1 : 1;
+      const int64_t f = filter[d], st = stride[d];
+      if (cur[d] < f || (cur[d] - f) % st != 0) ok = false;
+      lv.out_size[d] = ok ? (cur[d] - f) / st + 1 : 1;
       if (lv.out_size[d] > INT_MAX) ok = false;
-      lv.F.f[d] = lv.F.s[d] = (int)f;
+      lv.F.f[d] = (int)f;
+      lv.F.s[d] = (int)st;
       lv.F.out_size[d] = (int)lv.out_size[d];
-      lv.F.tdim[d] = 1;
+      lv.F.tdim[d] = (int)ceil_div(f, st);
+      lv.F.tmax *= lv.F.tdim[d];
       lv.K *= f;
+      out_volume = out_volume > (1ll << 40) ? out_volume : out_volume * lv.out_size[d];
     }
-    if (!ok || lv.K > 4096) break;
-    auto found = md->strided_rules.find(make_key(dim, cur.data(), filter, filter));
+    if (!ok || lv.K > 4096 || lv.F.tmax > 4096 || bound * lv.F.tmax >= (1ll << 31)) break;
+    auto found = md->strided_rules.find(make_key(dim, cur.data(), filter, stride));
     if (found != md->strided_rules.end() && found->second.built) break;
     if (md->grids.count(make_key(dim, lv.out_size.data()))) break;
     if (make_layout(dim, lv.out_size.data(), lv.gout.layout) != SCN_OK) break;
     if (!(lv.gout.layout.batch_bits >= gin->layout.batch_bits || gin->batch_size <= (1ll << lv.gout.layout.batch_bits)))
       break;
     lv.bound_in = bound;
-    lv.cap_out = safe ? bound : std::max((bound + 1) / 2, std::min<long long>(bound, 4096));
+    // Sites of the level: at most one per candidate (and no more than the output volume).  Disjoint windows
+    // (filter == stride) give at most one site per input site, and the arrays are first sized for half of that;
+    // overlapping windows are first sized for as many sites as the input has.  A level that needs more raises its
+    // flag and is built again from the safe bound.
+    const long long most = std::min(bound * lv.F.tmax, std::max<long long>(out_volume, 1));
+    if (safe)
+      lv.cap_out = most;
+    else if (lv.F.tmax == 1)
+      lv.cap_out = std::max((bound + 1) / 2, std::min<long long>(bound, 4096));
+    else
+      lv.cap_out = std::min(most, std::max<long long>(bound, 4096));
+    if (lv.cap_out >= (1ll << 30)) break;
     bound = lv.cap_out;
     cur = lv.out_size;
     plan.push_back(std::move(lv));
@@ -1008,7 +1025,8 @@ static int chain_launch(scn_metadata *md, const Grid *gin, std::vector<ChainLeve
 // collect (after the host has seen the mailbox): the levels up to the first that overflowed its arrays become
 // grids and rulebooks of the object, the others are freed.  Returns the number of good levels.
 static int chain_collect(scn_metadata *md, long long n_in, long long batch_size, std::vector<ChainLevel> &plan,
-                         const int64_t *filter, const volatile int *host, cudaStream_t stream, int *n_built) {
+                         const int64_t *filter, const int64_t *stride, const volatile int *host, cudaStream_t stream,
+                         int *n_built) {
   const int dim = md->dim, L = (int)plan.size();
   int good = 0;
   while (good < L && host[L + 1 + good] == 0 && host[good + 1] <= plan[good].cap_out) ++good;
@@ -1024,7 +1042,7 @@ static int chain_collect(scn_metadata *md, long long n_in, long long batch_size,
       lv.rb.built = true;
       chain_free_level(lv, true, stream);
       md->grids[make_key(dim, lv.out_size.data())] = lv.gout;
-      md->strided_rules[make_key(dim, lv.in_size.data(), filter, filter)] = lv.rb;
+      md->strided_rules[make_key(dim, lv.in_size.data(), filter, stride)] = lv.rb;
       g_rulebook_builds.fetch_add(1);
       if (n_built) ++*n_built;
       n_in = n_out;
@@ -1037,7 +1055,7 @@ static int chain_collect(scn_metadata *md, long long n_in, long long batch_size,
 
 static bool chain_applies(int dim, const int64_t *filter_size, const int64_t *filter_stride) {
   for (int d = 0; d < dim; ++d)
-    if (filter_size[d] != filter_stride[d] || filter_size[d] < 1 || filter_size[d] > 127) return false;
+    if (filter_size[d] < 1 || filter_size[d] > 127 || filter_stride[d] < 1 || filter_stride[d] > 127) return false;
   return true;
 }
 
@@ -1049,7 +1067,7 @@ static Grid *find_grid_now(scn_metadata *md, const int64_t *spatial_size) {  // 
 // A chain that was started on the side stream and whose counts the host has not looked at yet.
 struct PendingChain {
   std::vector<ChainLevel> plan;
-  std::vector<int64_t> filter;
+  std::vector<int64_t> filter, stride;
   long long n_in = 0, batch_size = 0;
   cudaEvent_t done = nullptr;
   int *mailbox = nullptr;
@@ -1069,8 +1087,8 @@ static int side_stream(cudaStream_t *out) {
   return SCN_OK;
 }
 
-static int build_strided_chain_from(scn_metadata *md, std::vector<int64_t> start, const int64_t *filter, int levels,
-                                    bool safe, cudaStream_t stream, int *n_built);
+static int build_strided_chain_from(scn_metadata *md, std::vector<int64_t> start, const int64_t *filter,
+                                    const int64_t *stride, int levels, bool safe, cudaStream_t stream, int *n_built);
 
 // The host looks at a started chain: waits for its event (usually long past), makes its levels the object's, and
 // builds again, on `stream` and with the safe bounds, whatever overflowed.
@@ -1089,16 +1107,18 @@ static int chain_finalize(scn_metadata *md, cudaStream_t stream, int *n_built) {
   int good = L;
   std::vector<int64_t> rest;
   if (st == SCN_OK) {
-    good = chain_collect(md, p->n_in, p->batch_size, p->plan, p->filter.data(), p->mailbox, stream, n_built);
+    good = chain_collect(md, p->n_in, p->batch_size, p->plan, p->filter.data(), p->stride.data(), p->mailbox, stream,
+                         n_built);
     if (good < L) rest = p->plan[good].in_size;
   } else {
     for (auto &lv : p->plan) chain_free_level(lv, false, stream);
   }
   device_free(p->lev, stream);
   mailbox_release(p->mailbox);
-  std::vector<int64_t> filter = p->filter;
+  std::vector<int64_t> filter = p->filter, stride = p->stride;
   delete p;
-  if (st == SCN_OK && good < L) st = build_strided_chain_from(md, rest, filter.data(), L - good, true, stream, n_built);
+  if (st == SCN_OK && good < L)
+    st = build_strided_chain_from(md, rest, filter.data(), stride.data(), L - good, true, stream, n_built);
   return st;
 }
 
@@ -1115,13 +1135,13 @@ static void chain_abandon(scn_metadata *md, cudaStream_t stream) {
   delete p;
 }
 
-static int build_strided_chain_from(scn_metadata *md, std::vector<int64_t> start, const int64_t *filter, int levels,
-                                    bool safe, cudaStream_t stream, int *n_built) {
+static int build_strided_chain_from(scn_metadata *md, std::vector<int64_t> start, const int64_t *filter,
+                                    const int64_t *stride, int levels, bool safe, cudaStream_t stream, int *n_built) {
   while (levels >= 2) {
     Grid *gin = find_grid_now(md, start.data());
     if (!gin || gin->n_active >= (1ll << 31)) return SCN_OK;
     std::vector<ChainLevel> plan;
-    chain_plan(md, gin, start, filter, levels, safe, plan);
+    chain_plan(md, gin, start, filter, stride, levels, safe, plan);
     const int L = (int)plan.size();
     if (L < 2) return SCN_OK;
     if (!md->mailbox) SCN_TRY(mailbox_acquire(&md->mailbox));
@@ -1141,7 +1161,7 @@ static int build_strided_chain_from(scn_metadata *md, std::vector<int64_t> start
       for (auto &lv : plan) chain_free_level(lv, false, stream);
       return st;
     }
-    const int good = chain_collect(md, gin->n_active, gin->batch_size, plan, filter, md->mailbox, stream, n_built);
+    const int good = chain_collect(md, gin->n_active, gin->batch_size, plan, filter, stride, md->mailbox, stream, n_built);
     if (good == L) return SCN_OK;
     // a level shrank less than guessed: that level and the deeper ones again, arrays sized by the input
     start = plan[good].in_size;
@@ -1153,7 +1173,7 @@ static int build_strided_chain_from(scn_metadata *md, std::vector<int64_t> start
 
 // Builds up to `levels` consecutive rulebooks of (filter_size, filter_stride) starting at the grid of
 // `input_size`, each level's output size (in - f) / s + 1.  Does nothing (SCN_OK) where the chain does
-// not apply -- filter != stride, fewer than two levels to build, no grid, rulebooks already there --
+// not apply -- fewer than two levels to build, sizes that do not divide, no grid, rulebooks already there --
 // because the per-level call that follows builds or reports whatever is left.  A chain that was started
 // earlier on the side stream is taken over here.
 int build_strided_chain(scn_metadata *md, const int64_t *input_size, const int64_t *filter_size,
@@ -1162,7 +1182,7 @@ int build_strided_chain(scn_metadata *md, const int64_t *input_size, const int64
   SCN_TRY(md_touch(md, stream));
   SCN_TRY(chain_finalize(md, stream, n_built));
   if (!chain_applies(md->dim, filter_size, filter_stride)) return SCN_OK;
-  return build_strided_chain_from(md, std::vector<int64_t>(input_size, input_size + md->dim), filter_size,
+  return build_strided_chain_from(md, std::vector<int64_t>(input_size, input_size + md->dim), filter_size, filter_stride,
                                   std::min(levels, kMaxChain), false, stream, n_built);
 }
 
@@ -1178,8 +1198,8 @@ int start_strided_chain(scn_metadata *md, const int64_t *input_size, const int64
   Grid *gin = find_grid_now(md, input_size);
   if (!gin || gin->n_active >= (1ll << 31)) return SCN_OK;
   PendingChain *p = new PendingChain();
-  chain_plan(md, gin, std::vector<int64_t>(input_size, input_size + md->dim), filter_size, std::min(levels, kMaxChain),
-             false, p->plan);
+  chain_plan(md, gin, std::vector<int64_t>(input_size, input_size + md->dim), filter_size, filter_stride,
+             std::min(levels, kMaxChain), false, p->plan);
   if (p->plan.size() < 2) {
     delete p;
     return SCN_OK;
@@ -1220,6 +1240,7 @@ int start_strided_chain(scn_metadata *md, const int64_t *input_size, const int64
     return st;
   }
   p->filter.assign(filter_size, filter_size + md->dim);
+  p->stride.assign(filter_stride, filter_stride + md->dim);
   p->n_in = gin->n_active;
   p->batch_size = gin->batch_size;
   md->pending = p;

@@ -405,9 +405,9 @@ def test_rows_times_small_matrix_refuses_other_shapes(cuda):
     assert out.shape == (10, 33)
 
 
-def _pyramid(cuda, coords, size, levels, chained):
-    """Grids and rulebooks of `levels` f2/s2 levels below an input layer: ([locations], [rulebooks],
-    host waits, rulebooks built), built level by level or, `chained`, in one enqueued chain first."""
+def _pyramid(cuda, coords, size, levels, chained, fsize=2, fstride=2):
+    """Grids and rulebooks of `levels` levels (filter fsize, stride fstride) below an input layer: ([locations],
+    [rulebooks], host waits, rulebooks built), built level by level or, `chained`, in one enqueued chain first."""
     import ctypes as C
     import sparseconvnet_b200 as scn
     from sparseconvnet_b200 import SCN
@@ -415,35 +415,37 @@ def _pyramid(cuda, coords, size, levels, chained):
     x = scn.InputLayer(dim, size, mode=3)([torch.from_numpy(coords), torch.ones(len(coords), 1, device=cuda)])
     m = x.metadata
     waits, builds = SCN.host_wait_count(), SCN.lib.scn_rulebook_build_count()
-    f = torch.LongTensor([2] * dim)
+    f, st = torch.LongTensor([fsize] * dim), torch.LongTensor([fstride] * dim)
     if chained == "started":   # on the side stream, taken over by the first per-level call below
-        SCN.strided_chain_start(m, x.spatial_size, f, f, levels, cuda)
-    n_chained = SCN.strided_chain(m, x.spatial_size, f, f, levels, cuda) if chained is True else 0
+        SCN.strided_chain_start(m, x.spatial_size, f, st, levels, cuda)
+    n_chained = SCN.strided_chain(m, x.spatial_size, f, st, levels, cuda) if chained is True else 0
     locs, rules, cur = [], [], x.spatial_size.clone()
     for _ in range(levels):
-        nxt = (cur - 2) // 2 + 1
+        nxt = (cur - fsize) // fstride + 1
         n_out = C.c_int64()
         with torch.cuda.device(cuda):
             SCN.check(SCN.lib.scn_md_strided_rulebook(m._h, SCN.sizes(cur), SCN.sizes(nxt), SCN.sizes(f),
-                                                      SCN.sizes(f), SCN._stream(), C.byref(n_out), None))
+                                                      SCN.sizes(st), SCN._stream(), C.byref(n_out), None))
         assert n_out.value == m.getNActive(nxt)
         cur = nxt
     waits, builds = SCN.host_wait_count() - waits, SCN.lib.scn_rulebook_build_count() - builds
     cur = x.spatial_size.clone()
     for _ in range(levels):
-        nxt = (cur - 2) // 2 + 1
+        nxt = (cur - fsize) // fstride + 1
         locs.append(m.getSpatialLocations(nxt).numpy())
-        rules.append([t.cpu().numpy() for t in m.rulebook(1, cur, f, f)])
+        rules.append([t.cpu().numpy() for t in m.rulebook(1, cur, f, st)])
         cur = nxt
     return locs, rules, waits, builds, n_chained
 
 
+@pytest.mark.parametrize("fsize,size", [(2, 1024), (3, 1023)])
 @pytest.mark.parametrize("kind", ["surface", "scattered", "empty", "tiny"])
-def test_chained_strided_levels_equal_level_by_level(kind, cuda):
+def test_chained_strided_levels_equal_level_by_level(kind, fsize, size, cuda):
     """scn_md_strided_chain: the same grids (row for row) and rulebooks (rule for rule) as one
-    scn_md_strided_rulebook call per level, with one wait for all levels.  'scattered': isolated sites
-    two apart do not thin out from one level to the next, so the first guess of the level sizes is too
-    small and the chain falls back to the safe sizes for those levels."""
+    scn_md_strided_rulebook call per level, with one wait for all levels, for disjoint (2/2) and overlapping
+    (3/2) windows.  'scattered': isolated sites do not thin out from one level to the next (2/2) or feed
+    eight outputs each (3/2), so the first guess of the level sizes is too small and the chain falls back to
+    the safe sizes for those levels."""
     rng = np.random.default_rng(5)
     if kind == "surface":      # a closed sheet, rows shuffled: shrinks by about four per level
         u = np.stack(np.meshgrid(np.arange(300), np.arange(200), indexing="ij"), -1).reshape(-1, 2)
@@ -458,21 +460,21 @@ def test_chained_strided_levels_equal_level_by_level(kind, cuda):
     else:
         coords = np.array([[5, 6, 7, 0], [1020, 3, 9, 1]], np.int64)
     levels = 5
-    a = _pyramid(cuda, coords, 1024, levels, chained=False)
-    b = _pyramid(cuda, coords, 1024, levels, chained=True)
+    a = _pyramid(cuda, coords, size, levels, chained=False, fsize=fsize)
+    b = _pyramid(cuda, coords, size, levels, chained=True, fsize=fsize)
     assert a[3] == levels and b[3] == levels          # every rulebook built exactly once either way
     assert b[4] == levels                             # ... all of them by the chain
     for l in range(levels):
         assert np.array_equal(a[0][l], b[0][l]), "grid of level %d" % l
         _exact_rules(a[1][l], b[1][l], "rulebook of level %d" % l)
-    c = _pyramid(cuda, coords, 1024, levels, chained="started")
+    c = _pyramid(cuda, coords, size, levels, chained="started", fsize=fsize)
     assert c[3] == levels
     for l in range(levels):
         assert np.array_equal(a[0][l], c[0][l]), "grid of level %d (chain started on the side stream)" % l
         _exact_rules(a[1][l], c[1][l], "rulebook of level %d (chain started on the side stream)" % l)
     if kind == "empty":                                # nothing to count, nothing to wait for level by level
         return
-    assert a[2] == levels                              # one wait per level (after the input layer's own)
+    assert a[2] >= levels                              # one wait per level (more where a table had to grow)
     if kind == "scattered":
         assert 2 <= b[2] <= 3                          # the first pass and one or two repeats
     else:
