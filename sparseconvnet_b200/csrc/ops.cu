@@ -399,14 +399,19 @@ k_dense_to_sparse_grad(KeyLayout L, const unsigned long long *__restrict__ row_k
 // NetworkInNetwork_updateOutput (CPU/NetworkInNetwork.cpp:7-23) and the per-voxel class head of the
 // segmentation networks are this shape: millions of rows, a few dozen columns.  The operation is bound
 // by reading the rows once and writing the scores once; a dense-library GEMM picks a tile shape made for
-// wide outputs and takes several times that.  One thread per row: the row is read in 16-byte pieces, the
-// weights (zero-padded to a multiple of four columns) sit in shared memory and are read as broadcasts,
-// the n_out sums stay in registers (fp32 FMA, plane order -- the order a scalar loop over n_in has).
+// wide outputs and takes several times that.  A warp takes 32 rows at a time: 32 planes of them are read
+// with coalesced 16-byte loads (four rows per instruction) into a padded tile of shared memory, then every
+// lane reads its own row from the tile and adds its products to the n_out sums it keeps in registers
+// (fp32 FMA, plane order -- the order a scalar loop over n_in has); the weights (zero-padded to a multiple
+// of four columns) sit in shared memory and are read as broadcasts.
+constexpr int kAffineChunk = 32;                  // planes per pass through shared memory
+constexpr int kAffineStride = kAffineChunk + 4;   // floats: the 32 lanes' 16-byte reads of their rows do not collide
+
 template <int COUT4>
 __global__ void __launch_bounds__(256)
 k_rows_affine(const float *__restrict__ in, float *__restrict__ out, long long n_rows, int cin, int cout,
               const float *__restrict__ weight, const float *__restrict__ bias) {
-  extern __shared__ float4 sh_w4[];  // [cin][COUT4]
+  extern __shared__ float4 sh_w4[];  // [cin][COUT4], then one [32][kAffineStride] tile per warp
   float *sh_w = reinterpret_cast<float *>(sh_w4);
   constexpr int CP = COUT4 * 4;
   for (int i = threadIdx.x; i < cin * CP; i += blockDim.x) {
@@ -414,38 +419,58 @@ k_rows_affine(const float *__restrict__ in, float *__restrict__ out, long long n
     sh_w[i] = c < cout ? weight[(size_t)k * cout + c] : 0.f;
   }
   __syncthreads();
-  const long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (r >= n_rows) return;
-  float acc[CP];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float *tile = sh_w + (size_t)cin * CP + (size_t)warp * 32 * kAffineStride;
+  const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
+  for (long long row0 = ((long long)blockIdx.x * (blockDim.x >> 5) + warp) * 32; row0 < n_rows; row0 += warps * 32) {
+    float acc[CP];
 #pragma unroll
-  for (int c = 0; c < CP; ++c) acc[c] = (bias && c < cout) ? bias[c] : 0.f;
-  const float4 *row = reinterpret_cast<const float4 *>(in + r * cin);
-  for (int q = 0; q < cin / 4; ++q) {
-    const float4 x = __ldg(row + q);
-    const float xs[4] = {x.x, x.y, x.z, x.w};
+    for (int c = 0; c < CP; ++c) acc[c] = (bias && c < cout) ? bias[c] : 0.f;
+    for (int p0 = 0; p0 < cin; p0 += kAffineChunk) {
+      const int width = min(kAffineChunk, cin - p0);  // a multiple of four
+      // coalesced: lane -> (row lane / 8 + 4 i, 16-byte piece lane % 8)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+      for (int i = 0; i < 8; ++i) {
+        const int r = (lane >> 3) + 4 * i, piece = lane & 7;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (row0 + r < n_rows && piece * 4 < width)
+          v = __ldcs(reinterpret_cast<const float4 *>(in + (row0 + r) * cin + p0 + piece * 4));
+        *reinterpret_cast<float4 *>(tile + r * kAffineStride + piece * 4) = v;
+      }
+      __syncwarp();
+      const float4 *mine = reinterpret_cast<const float4 *>(tile + lane * kAffineStride);
+      for (int q = 0; q < width / 4; ++q) {
+        const float4 x = mine[q];
+        const float xs[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
-      for (int c4 = 0; c4 < COUT4; ++c4) {
-        const float4 w = sh_w4[(q * 4 + j) * COUT4 + c4];
-        acc[c4 * 4 + 0] = fmaf(xs[j], w.x, acc[c4 * 4 + 0]);
-        acc[c4 * 4 + 1] = fmaf(xs[j], w.y, acc[c4 * 4 + 1]);
-        acc[c4 * 4 + 2] = fmaf(xs[j], w.z, acc[c4 * 4 + 2]);
-        acc[c4 * 4 + 3] = fmaf(xs[j], w.w, acc[c4 * 4 + 3]);
+        for (int j = 0; j < 4; ++j) {
+#pragma unroll
+          for (int c4 = 0; c4 < COUT4; ++c4) {
+            const float4 w = sh_w4[(p0 + q * 4 + j) * COUT4 + c4];
+            acc[c4 * 4 + 0] = fmaf(xs[j], w.x, acc[c4 * 4 + 0]);
+            acc[c4 * 4 + 1] = fmaf(xs[j], w.y, acc[c4 * 4 + 1]);
+            acc[c4 * 4 + 2] = fmaf(xs[j], w.z, acc[c4 * 4 + 2]);
+            acc[c4 * 4 + 3] = fmaf(xs[j], w.w, acc[c4 * 4 + 3]);
+          }
+        }
+      }
+      __syncwarp();
+    }
+    const long long r = row0 + lane;
+    if (r < n_rows) {
+      float *o = out + r * cout;
+      if (cout % 4 == 0) {
+#pragma unroll
+        for (int c4 = 0; c4 < COUT4; ++c4)
+          if (c4 * 4 < cout)
+            __stcs(reinterpret_cast<float4 *>(o + c4 * 4),
+                   make_float4(acc[c4 * 4], acc[c4 * 4 + 1], acc[c4 * 4 + 2], acc[c4 * 4 + 3]));
+      } else {
+#pragma unroll
+        for (int c = 0; c < CP; ++c)
+          if (c < cout) o[c] = acc[c];
       }
     }
-  }
-  float *o = out + r * cout;
-  if (cout % 4 == 0) {
-#pragma unroll
-    for (int c4 = 0; c4 < COUT4; ++c4)
-      if (c4 * 4 < cout)
-        *reinterpret_cast<float4 *>(o + c4 * 4) =
-            make_float4(acc[c4 * 4], acc[c4 * 4 + 1], acc[c4 * 4 + 2], acc[c4 * 4 + 3]);
-  } else {
-#pragma unroll
-    for (int c = 0; c < CP; ++c)
-      if (c < cout) o[c] = acc[c];
   }
 }
 
@@ -609,10 +634,18 @@ int scn_rows_affine_forward(const float *in_features, float *out_features, int64
   SCN_REQUIRE((uintptr_t)in_features % 16 == 0 && (uintptr_t)out_features % 16 == 0, SCN_ERR_BAD_ARG,
               "feature matrices must be 16-byte aligned");
   const int c4 = (n_out_planes + 3) / 4;
-  const unsigned blocks = (unsigned)ceil_div(n_rows, 256);
-  const size_t smem = sizeof(float) * 4 * (size_t)c4 * n_in_planes;
+  const unsigned blocks = (unsigned)std::min<long long>(ceil_div(n_rows, 256), 148 * 8);
+  const size_t smem = sizeof(float) * (4 * (size_t)c4 * n_in_planes + 8 * 32 * kAffineStride);
+  // up to 32 KB of weights + 37 KB of tiles: above the 48 KB a kernel gets without asking
+  static bool configured[64] = {false};
+  int dev = 0;
+  SCN_CUDA_CHECK(cudaGetDevice(&dev));
+  const bool configure = dev < 0 || dev >= 64 || !configured[dev];
 #define SCN_AFFINE(N)                                                                                       \
   case N:                                                                                                   \
+    if (configure)                                                                                          \
+      SCN_CUDA_CHECK(cudaFuncSetAttribute(k_rows_affine<N>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
+                                          72 * 1024));                                                      \
     SCN_LAUNCH(k_rows_affine<N>, blocks, 256, smem, stream, in_features, out_features, (long long)n_rows,   \
                n_in_planes, n_out_planes, weight, bias);                                                    \
     break;
