@@ -668,10 +668,10 @@ k_conv_rows_scatter(const float *__restrict__ in, int ld_in, long long n_in, flo
   // With 32 output planes and at most 64 input planes the warp's 32 input rows fit the registers as split
   // fragments (64 registers): they are read and split once and serve every filter offset, instead of being read
   // from the feature matrix and split again for each of the K offsets.
-  constexpr int kHeldChunks = 2;
-  const bool held = (MODE == TC_BF16X3 && NT == 4) && nch <= kHeldChunks;
+  constexpr int kHeldChunks = NT == 4 ? 2 : 3;
+  const bool held = MODE == TC_BF16X3 && nch <= kHeldChunks;
   unsigned ah[2][kHeldChunks][2][4], am[2][kHeldChunks][2][4];  // [tile][chunk][k16 half][fragment register]
-  if (MODE == TC_BF16X3 && NT == 4 && held) {
+  if (MODE == TC_BF16X3 && held) {
 #pragma unroll
     for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
@@ -721,7 +721,7 @@ k_conv_rows_scatter(const float *__restrict__ in, int ld_in, long long n_in, flo
           }
         }
         const int off = c * kRChunk + kp * 16;
-        if constexpr (MODE == TC_BF16X3 && NT == 4) {
+        if constexpr (MODE == TC_BF16X3) {
           if (held) {
 #pragma unroll
             for (int mt = 0; mt < 2; ++mt) {
@@ -730,8 +730,8 @@ k_conv_rows_scatter(const float *__restrict__ in, int ld_in, long long n_in, flo
               unsigned fh[4], fm[4];
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
-                fh[e] = c == 0 ? ah[mt][0][kp][e] : ah[mt][1][kp][e];
-                fm[e] = c == 0 ? am[mt][0][kp][e] : am[mt][1][kp][e];
+                fh[e] = c == 0 ? ah[mt][0][kp][e] : (c == 1 ? ah[mt][1][kp][e] : ah[mt][kHeldChunks - 1][kp][e]);
+                fm[e] = c == 0 ? am[mt][0][kp][e] : (c == 1 ? am[mt][1][kp][e] : am[mt][kHeldChunks - 1][kp][e]);
               }
               rows_mma3<NT>(d[mt], fh, fm, bp);
             }
