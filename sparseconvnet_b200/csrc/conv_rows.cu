@@ -606,6 +606,140 @@ k_conv_rows_thin(const float *__restrict__ in, long long n_in, float *__restrict
     }
 }
 
+// ---- the same in the bf16 three-term form: four offsets per tensor instruction ------------------------------
+// With at most four input planes an m16n8k16 instruction has room for four filter offsets: k = 4 o + p for
+// offset o of a group of four and plane p.  A lane's A fragment is then two planes (2 (t & 1), + 1) of offsets
+// t >> 1 and 2 + (t >> 1) of rows g and g + 8, read straight from the feature matrix and split into the bf16
+// parts h and m; the B fragments come from an image of [group][n-tile][lane] (h pairs, m pairs).  Per 16-row
+// tile and group of four offsets: 3 instructions per 8 output planes, against 12 of m16n8k4 in the tf32 form
+// (which is bound by the issue rate of those: 0.27 ms for 1.59 M rows, 27 offsets, 3 -> 32 planes; this form
+// 0.21 ms, bound by its scalar loads of the input values).
+__global__ void k_rows_thin_prepare_b3(const float *__restrict__ w, uint4 *__restrict__ img, int K, int cin, int cout) {
+  const int nt_n = cout / 8, n_groups = (K + 3) / 4;
+  const long long total = (long long)n_groups * nt_n * 32;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int lane = (int)(i & 31), nt = (int)((i >> 5) % nt_n), grp = (int)((i >> 5) / nt_n);
+  const int g = lane >> 2, t = lane & 3, p0 = 2 * (t & 1);
+  float x[2][2];  // [k half: offsets t >> 1 and 2 + (t >> 1)][plane p0, p0 + 1]
+#pragma unroll
+  for (int e = 0; e < 2; ++e)
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const int k = grp * 4 + 2 * e + (t >> 1), p = p0 + q;
+      x[e][q] = (k < K && p < cin) ? w[((long long)k * cin + p) * cout + nt * 8 + g] : 0.f;
+    }
+  uint4 o;
+  rows_split_bf16(x[0][0], x[0][1], o.x, o.z);
+  rows_split_bf16(x[1][0], x[1][1], o.y, o.w);
+  img[i] = o;  // (b0 h, b1 h, b0 m, b1 m)
+}
+
+template <int NT>
+__global__ void __launch_bounds__(128)
+k_conv_rows_thin_b3(const float *__restrict__ in, long long n_in, float *__restrict__ out, long long n_out,
+                    const uint4 *__restrict__ img, const float *__restrict__ bias, const float *__restrict__ bn_scale,
+                    const float *__restrict__ bn_shift, float leak, const int *__restrict__ nbr, int K, int cin,
+                    int *flags) {
+  constexpr unsigned kFull = 0xffffffffu;
+  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const long long row0 = ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 32;
+  if (row0 >= n_out) return;
+  const long long my_row = row0 + lane;
+  const int p0 = 2 * (t & 1), o_lo = t >> 1;
+  const bool p0_ok = p0 < cin, p1_ok = p0 + 1 < cin;
+  float d[2][NT][4];
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) d[mt][nt][0] = d[mt][nt][1] = d[mt][nt][2] = d[mt][nt][3] = 0.f;
+
+  const int n_groups = (K + 3) / 4;
+  int v[4];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) v[u] = (u < K && my_row < n_out) ? __ldg(nbr + (long long)u * n_out + my_row) : -1;
+  for (int grp = 0; grp < n_groups; ++grp) {
+    int vn[4];  // the next group's rulebook entries, in flight while this group is computed
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int k = (grp + 1) * 4 + u;
+      vn[u] = (k < K && my_row < n_out) ? __ldg(nbr + (long long)k * n_out + my_row) : -1;
+    }
+    unsigned any = 0;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (v[u] >= n_in) {
+        atomicOr(flags, FLAG_BAD_ROW);
+        v[u] = -1;
+      }
+      any |= __ballot_sync(kFull, v[u] >= 0);
+    }
+    if (any != 0) {
+      // this lane's values: [tile][row g / g + 8][k half][plane p0 / p0 + 1]
+      float x[2][2][2][2];
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int src = mt * 16 + h * 8 + g;
+          const int i0 = __shfl_sync(kFull, v[0], src), i1 = __shfl_sync(kFull, v[1], src);
+          const int i2 = __shfl_sync(kFull, v[2], src), i3 = __shfl_sync(kFull, v[3], src);
+          const int idx[2] = {o_lo ? i1 : i0, o_lo ? i3 : i2};
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const float *row = in + (long long)idx[e] * cin + p0;
+            x[mt][h][e][0] = (idx[e] >= 0 && p0_ok) ? __ldg(row) : 0.f;
+            x[mt][h][e][1] = (idx[e] >= 0 && p1_ok) ? __ldg(row + 1) : 0.f;
+          }
+        }
+      unsigned bp[NT][4];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const uint4 q = __ldg(img + ((long long)grp * NT + nt) * 32 + lane);
+        bp[nt][0] = q.x, bp[nt][1] = q.y, bp[nt][2] = q.z, bp[nt][3] = q.w;
+      }
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        if (((mt == 0) ? (any & 0xFFFFu) : (any >> 16)) == 0) continue;
+        unsigned ah[4], am[4];  // a0: row g, k half 0; a1: row g + 8, half 0; a2: row g, half 1; a3: row g + 8, half 1
+        rows_split_bf16(x[mt][0][0][0], x[mt][0][0][1], ah[0], am[0]);
+        rows_split_bf16(x[mt][1][0][0], x[mt][1][0][1], ah[1], am[1]);
+        rows_split_bf16(x[mt][0][1][0], x[mt][0][1][1], ah[2], am[2]);
+        rows_split_bf16(x[mt][1][1][0], x[mt][1][1][1], ah[3], am[3]);
+        rows_mma3<NT>(d[mt], ah, am, bp);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = vn[u];
+  }
+
+  const int t2 = t * 2;
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const long long r = row0 + mt * 16 + h * 8 + g;
+      if (r >= n_out) continue;
+      float *dst = out + r * (NT * 8) + t2;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        float2 y = make_float2(d[mt][nt][h * 2], d[mt][nt][h * 2 + 1]);
+        if (bias) {
+          const float2 b = __ldg(reinterpret_cast<const float2 *>(bias + nt * 8 + t2));
+          y.x += b.x;
+          y.y += b.y;
+        }
+        if (bn_scale) {
+          const float2 sc = __ldg(reinterpret_cast<const float2 *>(bn_scale + nt * 8 + t2));
+          const float2 sh = __ldg(reinterpret_cast<const float2 *>(bn_shift + nt * 8 + t2));
+          y.x = rows_epilogue(y.x, sc.x, sh.x, leak);
+          y.y = rows_epilogue(y.y, sc.y, sh.y, leak);
+        }
+        __stcs(reinterpret_cast<float2 *>(dst + nt * 8), y);
+      }
+    }
+}
+
 bool conv_rows_thin_supported(const float *out, const float *bias, int cin, int cout, int groups) {
   return groups == 1 && cin >= 1 && cin <= 4 && (cout == 16 || cout == 32 || cout == 64) &&
          (uintptr_t)out % 8 == 0 && (uintptr_t)bias % 8 == 0;
@@ -615,6 +749,26 @@ int conv_forward_rows_thin(const float *in, long long n_in, float *out, long lon
                            const float *bias, const float *bn_scale, const float *bn_shift, float leak,
                            const int *table, int K, int cin, int cout, int *flags, cudaStream_t stream) {
   if (n_out == 0) return SCN_OK;
+  if (split_mode_of_env() == TC_BF16X3) {  // the default form of the fp32-class mode
+    const long long total = (long long)((K + 3) / 4) * (cout / 8) * 32;
+    WeightImage wi;
+    bool build = true;
+    SCN_TRY(weight_image_get(WIMG_ROWS_THIN, K, cin, cout, 1, (size_t)total * sizeof(uint4), stream, &wi, &build));
+    uint4 *img = (uint4 *)wi.ptr;
+    if (build)
+      SCN_LAUNCH(k_rows_thin_prepare_b3, (unsigned)ceil_div(total, 256LL), 256, 0, stream, weight, img, K, cin, cout);
+    const unsigned grid = (unsigned)ceil_div(n_out, 128LL);
+    if (cout == 16)
+      SCN_LAUNCH(k_conv_rows_thin_b3<2>, grid, 128, 0, stream, in, n_in, out, n_out, img, bias, bn_scale, bn_shift, leak, table, K, cin, flags);
+    else if (cout == 32)
+      SCN_LAUNCH(k_conv_rows_thin_b3<4>, grid, 128, 0, stream, in, n_in, out, n_out, img, bias, bn_scale, bn_shift, leak, table, K, cin, flags);
+    else
+      SCN_LAUNCH(k_conv_rows_thin_b3<8>, grid, 128, 0, stream, in, n_in, out, n_out, img, bias, bn_scale, bn_shift, leak, table, K, cin, flags);
+    const cudaError_t e = cudaGetLastError();
+    const int rf = weight_image_put(wi, stream);
+    SCN_CUDA_CHECK(e);
+    return rf;
+  }
   const long long total = (long long)K * (cout / 8) * 32;
   WeightImage wi;
   bool build = true;
