@@ -27,10 +27,14 @@
 //
 // Arithmetic modes:
 //   TF32    one pass, operands truncated to tf32 by the tensor core            (1e-2 class)
-//   BF16    operands rounded to bf16 while staging, fp32 accumulate            (1e-2 class)
-//   BF16X3  the fp32-class mode in its default form: a = h + m with h = bf16(a), m = bf16(a - h), both
-//           made in registers while staging; D += W_h*G_h + W_h*G_m + W_m*G_h, fp32 accumulate
-//           (what is dropped is 2^-17 of a product; half the instructions of TF32X3)
+//   BF16    operands rounded to bf16, fp32 accumulate                          (1e-2 class)
+//   BF16X3  the fp32-class mode in its default form: a = h + m with h = bf16(a), m = bf16(a - h);
+//           D += W_h*G_h + W_h*G_m + W_m*G_h, fp32 accumulate (what is dropped is 2^-17 of a product;
+//           half the instructions of TF32X3)
+//           In both bf16 modes the input rows are split once by a pass before the launch and the
+//           producers copy them with cp.async (arrival on completion), as in conv_wide.cu; on the
+//           smallest levels and in the allocation-free entry point they are read as fp32 and split
+//           in the producers' registers instead.
 //   TF32X3  the other form (SCN_X3_FORM=tf32): a = a_hi + a_lo with a_hi the tf32 truncation,
 //           D += W_hi*G_hi + W_hi*G_lo + W_lo*G_hi
 //
@@ -109,6 +113,10 @@ int prepare_weights(const float *w, unsigned char *out, int K, int cin, int cout
 // ---------------------------------------------------------------------------------------------
 struct TcParams {
   const float *in;
+  // bf16 modes, optional: the input rows as bf16 parts (per row and 32-plane block [32 h | 32 m], made by
+  // split_rows_bf16 before the launch).  The producers then only copy (cp.async, arrival on completion)
+  // instead of reading fp32 rows into registers and splitting them for every output row that gathers them.
+  const unsigned char *in_split;
   long long n_in;
   int ld_in;
   float *out;
@@ -196,7 +204,7 @@ __global__ void __launch_bounds__(kTcThreads) k_conv_tc(TcParams P) {
   // ---- prologue: barriers, tensor memory, rulebook columns of this tile ----------------------
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
-      mbar_init(&full_g[s], kAsyncArrive ? kProducerThreads : kProducerThreads / 32);
+      mbar_init(&full_g[s], (kAsyncArrive || (kBf16 && P.in_split)) ? kProducerThreads : kProducerThreads / 32);
       mbar_init(&full_w[s], 1);
       mbar_init(&empty[s], 1);
     }
@@ -253,7 +261,8 @@ __global__ void __launch_bounds__(kTcThreads) k_conv_tc(TcParams P) {
     // and of the step being completed (c = s - L), offset index and slice of step s
     int st = 0, round = 0, ki = 0, slice = 0;
     int st_c = 0;
-    if constexpr (kBf16) {
+    const bool copy_only = kBf16 && P.in_split != nullptr;  // rows split before the launch: see TcParams
+    if (kBf16 && !copy_only) {
       // bf16 operands are made in registers, so the gather cannot run ahead through the ring like the
       // cp.async one.  It runs ahead through registers instead: the loads of step s + 1 are issued
       // before step s is converted and stored (two register buffers, the loop handles two steps per
@@ -354,7 +363,18 @@ __global__ void __launch_bounds__(kTcThreads) k_conv_tc(TcParams P) {
           if (i < n_mine) {
             const int src_row = idx[i * r_step];
             const unsigned off = off_base + i * off_step;
-            if (!kBf16) {
+            if (kBf16 && copy_only) {
+              // plane p = slice * kc + 8 j of the row: block p / 32 of [32 h | 32 m], piece (p % 32) / 8
+              if (src_row >= 0) {
+                const int p = slice * kc + j * kPerPiece;
+                const unsigned char *src = P.in_split + (size_t)src_row * P.ld_in * 4 + (size_t)(p >> 5) * 128 + ((p & 31) >> 3) * 16;
+                cp_async16(sa_u32 + off, src, 16u);
+                if (kSplit) cp_async16(sa_u32 + g_bytes + off, src + 64, 16u);
+              } else {
+                *reinterpret_cast<uint4 *>(sa + off) = make_uint4(0, 0, 0, 0);
+                if (kSplit) *reinterpret_cast<uint4 *>(sa + g_bytes + off) = make_uint4(0, 0, 0, 0);
+              }
+            } else if (!kBf16) {
               // The copy pipe moves one 16-byte lane request per cycle, so a zero-filling copy
               // costs as much as a real one; a missing row is zeroed with a plain 128-bit store
               // (32 lanes per 4 cycles) instead and only real rows go through cp.async.
@@ -379,7 +399,7 @@ __global__ void __launch_bounds__(kTcThreads) k_conv_tc(TcParams P) {
             }
           }
         }
-        if (kAsyncArrive)
+        if (kAsyncArrive || copy_only)
           asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&full_g[st])) : "memory");
         if (++slice == n_slices) {
           slice = 0;
@@ -390,7 +410,7 @@ __global__ void __launch_bounds__(kTcThreads) k_conv_tc(TcParams P) {
           ++round;
         }
       }
-      if (kAsyncArrive) continue;
+      if (kAsyncArrive || copy_only) continue;
       cp_async_commit();
       if (s >= L) {
         // step c = s - L: its rows have landed once only L groups are still pending
@@ -609,6 +629,9 @@ struct TcPlan {
   size_t smem;
 };
 
+// conv_wide.cu: in [n][cin] fp32 -> out, per row and 32-plane block, the 32 h = bf16(x) then the 32 m = bf16(x - h)
+int split_rows_bf16(const float *in, unsigned char *out, long long n_rows, int cin, cudaStream_t stream);
+
 static int env_int(const char *name, int dflt) {
   const char *v = getenv(name);
   return v ? atoi(v) : dflt;
@@ -714,8 +737,22 @@ int conv_forward_tc(const float *in, long long n_in, float *out, long long n_out
   if (build)
     SCN_LAUNCH(k_prepare_weights, (unsigned)ceil_div(total, 256), 256, 0, stream, weight, wprep, K, cin, cout, pl.kc, mode);
 
+  // bf16 modes: the rows are split into their bf16 parts once, before the launch (a row is gathered by up to K
+  // output rows), and the producers copy.  Not for the run the test hook asked for (its dropped arrival is a
+  // warp's, and the copying producers arrive per thread) and not for the smallest levels, where the extra launch
+  // costs more than it saves (224 -> 224 planes: 0.058 ms with register producers against 0.098 at 1.4 k rows, 0.093
+  // against 0.082 at 6.4 k, 0.349 against 0.280 for 320 -> 160 at 23 k).  SCN_TC_COPY=0 / 1 forces the choice.
+  unsigned char *split = nullptr;
+  const int copy_env = env_int("SCN_TC_COPY", -1);
+  const bool copy_only = (mode == TC_BF16 || mode == TC_BF16X3) && cin % 32 == 0 && n_in > 0 && !g_drop_arrival &&
+                         (copy_env < 0 ? n_out >= 4096 : copy_env != 0);
+  if (copy_only) {
+    SCN_TRY(device_alloc((void **)&split, (size_t)n_in * cin * 4, stream));
+    SCN_TRY(split_rows_bf16(in, split, n_in, cin, stream));
+  }
   TcParams P;
   P.in = in;
+  P.in_split = split;
   P.n_in = n_in;
   P.ld_in = cin;
   P.out = out;
@@ -751,7 +788,9 @@ int conv_forward_tc(const float *in, long long n_in, float *out, long long n_out
     SCN_LAUNCH(k_conv_tc<TC_BF16X3>, grid, kTcThreads, pl.smem, stream, P);
   else
     SCN_LAUNCH(k_conv_tc<TC_TF32X3>, grid, kTcThreads, pl.smem, stream, P);
-  SCN_CUDA_CHECK(cudaGetLastError());
+  const cudaError_t launch_err = cudaGetLastError();
+  device_free(split, stream);
+  SCN_CUDA_CHECK(launch_err);
   if (P.n_split > 1) {
     const long long n4 = n_out * cout / 4;  // cout is a multiple of 8
     SCN_LAUNCH(k_sum_partials, (unsigned)ceil_div(n4, 256), 256, 0, stream, reinterpret_cast<const float4 *>(P.partial), P.n_split, n4, bias, bn_scale, bn_shift, leak, cout, reinterpret_cast<float4 *>(out));
@@ -840,6 +879,7 @@ extern "C" int scn_submanifold_convolution_forward_static(scn_metadata *md, cons
              cout, pl.kc, mode);
   TcParams P;
   P.in = in_features;
+  P.in_split = nullptr;  // no allocation here: the producers split in registers
   P.n_in = rb.n_in;
   P.ld_in = cin;
   P.out = out_features;

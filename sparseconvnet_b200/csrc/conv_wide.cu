@@ -439,6 +439,16 @@ constexpr size_t kWideSmemBudget = 226 * 1024;
 
 }  // namespace
 
+// The split pass on its own (also used by the per-tile kernel of conv_tc.cu): cin a multiple of 32, `out` holds
+// n_rows * cin * 4 bytes.
+int split_rows_bf16(const float *in, unsigned char *out, long long n_rows, int cin, cudaStream_t stream) {
+  const long long n_pieces = n_rows * (cin / 8);
+  if (n_pieces <= 0) return SCN_OK;
+  SCN_LAUNCH(k_wide_split_rows, (unsigned)ceil_div(n_pieces, 256LL), 256, 0, stream, in, out, n_pieces, cin);
+  SCN_CUDA_CHECK(cudaGetLastError());
+  return SCN_OK;
+}
+
 bool conv_wide_supported(int K, int cin, int cout, int groups, int precision, long long n_in) {
   (void)K;
   if (precision != SCN_PRECISION_TF32X3 && precision != SCN_PRECISION_BF16) return false;
