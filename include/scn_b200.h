@@ -384,6 +384,20 @@ SCN_API int scn_convolution_bn_forward(scn_metadata *md, const int64_t *input_si
                                        const float *bias, const float *bn_scale, const float *bn_shift,
                                        double leakiness, int n_in_planes, int n_out_planes, int groups,
                                        int precision, void *stream, double *macs);
+/* scn_convolution_bn_forward with a second eval-mode BatchNormalization (+ leaky ReLU), in FRONT of the
+ * convolution: the layer sees act(in * pre_scale[plane] + pre_shift[plane]) (scale / shift [n_in_planes] from
+ * scn_batchnorm_fold, same roundings as the stand-alone operator, so the result has the bits of the separate calls).
+ * bn_scale / bn_shift (the BatchNorm behind) may be NULL.  The tcgen05 kernels apply the one in front in the pass
+ * that splits their input rows; for the other kernels the library normalises into a scratch copy first.  The
+ * reference has no fused form: a BatchNormalization module followed by a Convolution module
+ * (sparseconvnet/networkArchitectures.py:231-238, the way down of a U-Net). */
+SCN_API int scn_convolution_bn_bn_forward(scn_metadata *md, const int64_t *input_size, const int64_t *output_size,
+                                          const int64_t *filter_size, const int64_t *filter_stride,
+                                          const float *in_features, float *out_features, const float *weight,
+                                          const float *bias, const float *pre_scale, const float *pre_shift,
+                                          double pre_leakiness, const float *bn_scale, const float *bn_shift,
+                                          double leakiness, int n_in_planes, int n_out_planes, int groups,
+                                          int precision, void *stream, double *macs);
 SCN_API int scn_deconvolution_bn_forward(scn_metadata *md, const int64_t *input_size, const int64_t *output_size,
                                          const int64_t *filter_size, const int64_t *filter_stride,
                                          const float *in_features, float *out_features, const float *weight,

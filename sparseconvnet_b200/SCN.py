@@ -616,8 +616,9 @@ def strided_chain_start(m, inputSize, filterSize, filterStride, levels, device):
 
 
 def Convolution_updateOutput(inputSize, outputSize, filterSize, filterStride, m, input_features,
-                             output_features, weight, bias, epilogue=None):
-    """sparseconvnet.h:87-92.  `epilogue` (not in the reference): see batchnorm_fold."""
+                             output_features, weight, bias, epilogue=None, prologue=None):
+    """sparseconvnet.h:87-92.  `epilogue` (not in the reference): see batchnorm_fold.  `prologue` (not in the
+    reference): the same triple for an eval-mode BatchNorm in FRONT of the layer (scn_convolution_bn_bn_forward)."""
     f, w, b, groups, cin, cout = _conv_args(input_features, weight, bias)
     macs = C.c_double()
     n_out = C.c_int64()
@@ -634,7 +635,16 @@ def Convolution_updateOutput(inputSize, outputSize, filterSize, filterStride, m,
         output_features.resize_(n_out.value, groups * cout)
         with _timed("conv", dict(op="strided", n_in=f.size(0), n_out=n_out.value, cin=cin, cout=cout,
                                  groups=groups, offsets=w.size(0), precision=_precision)) as info:
-            if epilogue is None:
+            if prologue is not None:
+                psc, psh, pleak = _epilogue_args(prologue, f, groups * cin)
+                sc, sh, leak = _epilogue_args(epilogue, f, groups * cout) if epilogue is not None else (None, None, 1.0)
+                info["fused_bn_in_front"] = True
+                info["fused_bn"] = epilogue is not None
+                check(lib.scn_convolution_bn_bn_forward(
+                    m._h, sizes(inputSize), sizes(outputSize), sizes(filterSize), sizes(filterStride), _ptr(f),
+                    _ptr(output_features), _ptr(w), _ptr(b), psc, psh, pleak, sc, sh, leak, groups * cin,
+                    groups * cout, groups, _precision, _stream(), C.byref(macs)))
+            elif epilogue is None:
                 check(lib.scn_convolution_forward(
                     m._h, sizes(inputSize), sizes(outputSize), sizes(filterSize), sizes(filterStride), _ptr(f),
                     _ptr(output_features), _ptr(w), _ptr(b), groups * cin, groups * cout, groups, _precision,

@@ -83,6 +83,19 @@ class Sequential(torch.nn.Sequential):
                 input = m.forward(input, bn=nxt)  # (no output rows: nothing to apply, as the BatchNorm itself)
                 i += 2
                 continue
+            # an eval-mode BatchNormalization whose result goes straight into a strided Convolution (the way down of a
+            # U-Net): the convolution normalises its input itself (in the pass that splits the rows for the tensor
+            # core, where there is one) -- and the BatchNormalization behind it rides in its store as above
+            nxt2 = steps[i + 2] if i + 2 < n else None
+            if (Sequential.fuse and isinstance(m, layers.BatchNormalization) and type(nxt) is layers.Convolution
+                    and not m._forward_hooks and not m._forward_pre_hooks and not nxt._forward_hooks
+                    and not nxt._forward_pre_hooks and isinstance(input, SparseConvNetTensor)
+                    and input.features.nelement() > 0 and m.fusable(input.features)
+                    and not layers.autograd.needs_grad(input.features, nxt.weight)):
+                post = nxt2 if (isinstance(nxt2, layers.BatchNormalization) and nxt2.fusable(input.features)) else None
+                input = nxt.forward(input, bn=post, pre_bn=m)
+                i += 3 if post is not None else 2
+                continue
             # a JoinTable whose result goes straight into an eval-mode BatchNormalization: every joined tensor is
             # normalised into its columns of the result, the concatenation itself is never written
             if (Sequential.fuse and type(m) is JoinTable and isinstance(nxt, layers.BatchNormalization)

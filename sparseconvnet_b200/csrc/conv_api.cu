@@ -17,8 +17,10 @@ int conv_forward_simt(const float *in, long long n_in, float *out, long long n_o
                       int *flags, cudaStream_t stream);
 int conv_forward_tc(const float *in, long long n_in, float *out, long long n_out, const float *weight,
                     const float *bias, const float *bn_scale, const float *bn_shift, float leak, const int *table,
-                    int K, int cin, int cout, int precision, int *flags, cudaStream_t stream);
+                    int K, int cin, int cout, int precision, int *flags, cudaStream_t stream,
+                    const float *pre_scale = nullptr, const float *pre_shift = nullptr, float pre_leak = 1.f);
 bool conv_tc_supported(int cin, int cout, int groups, int precision);
+bool conv_tc_splits_rows(int precision, int cin, long long n_in, long long n_out);
 int conv_forward_tma(const float *in, long long n_in, float *out, long long n_out, const float *weight,
                      const float *bias, const int *table, int K, int cin, int cout, int precision, int *flags,
                      cudaStream_t stream);
@@ -26,7 +28,8 @@ bool conv_tma_supported(int K, int cin, int cout, int groups, int precision, lon
 bool conv_wide_supported(int K, int cin, int cout, int groups, int precision, long long n_in);
 int conv_forward_wide(const float *in, long long n_in, float *out, long long n_out, const float *weight,
                       const float *bias, const float *bn_scale, const float *bn_shift, float leak, const int *table,
-                      int K, int cin, int cout, int precision, int *flags, cudaStream_t stream);
+                      int K, int cin, int cout, int precision, int *flags, cudaStream_t stream,
+                      const float *pre_scale = nullptr, const float *pre_shift = nullptr, float pre_leak = 1.f);
 bool conv_pipe_supported(const float *in, const float *out, const float *weight, const float *bias, int K, int cin,
                          int cout);
 int conv_forward_pipe(const float *in, long long n_in, float *out, long long n_out, const float *weight,
@@ -120,6 +123,35 @@ __global__ void k_scale_shift_act(float *__restrict__ y, long long n_rows, int p
   }
 }
 
+// the same out of place: the eval-mode BatchNorm in FRONT of a convolution whose kernel has no split pass to take it
+// (planes a multiple of four and 16-byte aligned matrices: four planes per thread; otherwise one)
+__global__ void k_scale_shift_act_to(const float *__restrict__ x, float *__restrict__ y, long long n_rows, int planes,
+                                     const float *__restrict__ scale, const float *__restrict__ shift, float leak, int vec) {
+  if (vec) {
+    const long long total = n_rows * planes / 4;
+    const int pv = planes / 4;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+      const int c = (int)(i % pv) * 4;
+      const float4 v = __ldg(reinterpret_cast<const float4 *>(x) + i);
+      const float4 sc = __ldg(reinterpret_cast<const float4 *>(scale + c)), sh = __ldg(reinterpret_cast<const float4 *>(shift + c));
+      float4 o;
+      o.x = __fadd_rn(__fmul_rn(v.x, sc.x), sh.x), o.y = __fadd_rn(__fmul_rn(v.y, sc.y), sh.y);
+      o.z = __fadd_rn(__fmul_rn(v.z, sc.z), sh.z), o.w = __fadd_rn(__fmul_rn(v.w, sc.w), sh.w);
+      o.x *= (o.x > 0.f) ? 1.f : leak, o.y *= (o.y > 0.f) ? 1.f : leak;
+      o.z *= (o.z > 0.f) ? 1.f : leak, o.w *= (o.w > 0.f) ? 1.f : leak;
+      reinterpret_cast<float4 *>(y)[i] = o;
+    }
+    return;
+  }
+  const long long total = n_rows * planes;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % planes);
+    float v = __fadd_rn(__fmul_rn(x[i], scale[c]), shift[c]);
+    v *= (v > 0.f) ? 1.f : leak;
+    y[i] = v;
+  }
+}
+
 // W, x -> scale = gamma / sqrt(var + eps), shift = beta - mean * scale, with the roundings of the
 // stand-alone BatchNorm kernel (CPU/BatchNormalization.cpp:41-46 of the reference)
 __global__ void k_bn_fold(const float *__restrict__ mean, const float *__restrict__ var, const float *__restrict__ gamma,
@@ -132,9 +164,14 @@ __global__ void k_bn_fold(const float *__restrict__ mean, const float *__restric
   shift[c] = __fadd_rn(__fmul_rn(-mean[c], w), beta ? beta[c] : 0.f);
 }
 
+// pre_scale / pre_shift / pre_leak (optional): an eval-mode BatchNorm and its leaky ReLU in FRONT of the
+// convolution, in[r][p] <- act(in[r][p] * pre_scale[p] + pre_shift[p]).  The tcgen05 kernels that split their input
+// rows before the launch apply it in that pass; for every other kernel it is applied into a scratch copy of the
+// input first (what the stand-alone operator would have done).
 int conv_forward_dispatch(const float *in, long long rows_in, float *out, long long rows_out, const float *weight,
                           const float *bias, const int *table, int K, int cin, int cout, int groups, int precision,
-                          int *flags, cudaStream_t stream, const float *bn_scale, const float *bn_shift, float leak) {
+                          int *flags, cudaStream_t stream, const float *bn_scale, const float *bn_shift, float leak,
+                          const float *pre_scale, const float *pre_shift, float pre_leak) {
   bool fused = true;  // did the kernel apply the optional BatchNorm epilogue itself?
   // TF32X3 is the fp32-accuracy mode: each shape runs whichever fp32-class kernel is fastest.
   // With 32 or 64 output planes (and first layers) that is the row-stationary kernel of
@@ -156,6 +193,21 @@ int conv_forward_dispatch(const float *in, long long rows_in, float *out, long l
   const bool pipe_mma = narrow_x3 && cin % 8 == 0 && conv_pipe_supported(in, out, weight, bias, K, cin, cout);
   // a narrow shape none of the three takes (more than 32 filter offsets, groups ...) goes on to tcgen05
   const bool tensor = precision != SCN_PRECISION_FP32 && !(rows_thin || rows || pipe_mma);
+  const bool to_wide = tensor && !few_tiles && conv_wide_supported(K, cin, cout, groups, precision, rows_in);
+  const bool to_tma = tensor && !to_wide && !few_tiles && conv_tma_supported(K, cin, cout, groups, precision, rows_in);
+  const bool to_tc = tensor && !to_wide && !to_tma && conv_tc_supported(cin, cout, groups, precision);
+  float *pre_copy = nullptr;
+  if (pre_scale && rows_in > 0 && !(to_wide || (to_tc && conv_tc_splits_rows(precision, cin, rows_in, rows_out)))) {
+    const long long total = rows_in * (long long)cin * groups;
+    SCN_TRY(device_alloc((void **)&pre_copy, sizeof(float) * (size_t)total, stream));
+    const int vec = (cin * groups) % 4 == 0 && (uintptr_t)in % 16 == 0 && (uintptr_t)pre_scale % 16 == 0 &&
+                    (uintptr_t)pre_shift % 16 == 0;
+    SCN_LAUNCH(k_scale_shift_act_to, (unsigned)std::min<long long>(ceil_div(total / (vec ? 4 : 1), 256), 148 * 16), 256, 0,
+               stream, in, pre_copy, rows_in, cin * groups, pre_scale, pre_shift, pre_leak, vec);
+    in = pre_copy;
+    pre_scale = pre_shift = nullptr;
+  }
+  const int status = [&]() -> int {
   if (rows_thin) {
     SCN_TRY(conv_forward_rows_thin(in, rows_in, out, rows_out, weight, bias, bn_scale, bn_shift, leak, table, K, cin,
                                    cout, flags, stream));
@@ -169,18 +221,18 @@ int conv_forward_dispatch(const float *in, long long rows_in, float *out, long l
                               flags, stream));
     g_last_kernel = SCN_KERNEL_CONV_PIPE_MMA;
     fused = false;
-  } else if (tensor && !few_tiles && conv_wide_supported(K, cin, cout, groups, precision, rows_in)) {
+  } else if (to_wide) {
     SCN_TRY(conv_forward_wide(in, rows_in, out, rows_out, weight, bias, bn_scale, bn_shift, bn_scale ? leak : 1.f, table,
-                              K, cin, cout, precision, flags, stream));
+                              K, cin, cout, precision, flags, stream, pre_scale, pre_shift, pre_leak));
     g_last_kernel = SCN_KERNEL_CONV_WIDE;
-  } else if (tensor && !few_tiles && conv_tma_supported(K, cin, cout, groups, precision, rows_in)) {
+  } else if (to_tma) {
     SCN_TRY(conv_forward_tma(in, rows_in, out, rows_out, weight, bias, table, K, cin, cout,
                              precision, flags, stream));
     g_last_kernel = SCN_KERNEL_CONV_TC_PERSISTENT;
     fused = false;
-  } else if (tensor && conv_tc_supported(cin, cout, groups, precision)) {
+  } else if (to_tc) {
     SCN_TRY(conv_forward_tc(in, rows_in, out, rows_out, weight, bias, bn_scale, bn_shift, leak, table, K, cin, cout,
-                            precision, flags, stream));
+                            precision, flags, stream, pre_scale, pre_shift, pre_leak));
     g_last_kernel = SCN_KERNEL_CONV_TC;
   } else {
     SCN_TRY(conv_forward_simt(in, rows_in, out, rows_out, weight, bias, table, K, cin, cout,
@@ -188,6 +240,10 @@ int conv_forward_dispatch(const float *in, long long rows_in, float *out, long l
     g_last_kernel = SCN_KERNEL_CONV_SIMT;
     fused = false;
   }
+  return SCN_OK;
+  }();
+  device_free(pre_copy, stream);
+  SCN_TRY(status);
   if (bn_scale && !fused && rows_out > 0) {
     const long long total = rows_out * (long long)cout * groups;
     SCN_LAUNCH(k_scale_shift_act, (unsigned)std::min<long long>(ceil_div(total, 256), 148 * 16), 256, 0, stream, out,
@@ -204,8 +260,10 @@ int conv_forward_dispatch(const float *in, long long rows_in, float *out, long l
 static int run_conv(scn_metadata *md, Rulebook &rb, bool transposed, const float *in, float *out,
                     const float *weight, const float *bias, int n_in_planes, int n_out_planes, int groups,
                     int precision, cudaStream_t stream, double *macs, bool disjoint = false,
-                    const float *bn_scale = nullptr, const float *bn_shift = nullptr, float leak = 1.f) {
-  SCN_REQUIRE(!bn_scale == !bn_shift, SCN_ERR_BAD_ARG, "scale and shift of the fused BatchNorm come together");
+                    const float *bn_scale = nullptr, const float *bn_shift = nullptr, float leak = 1.f,
+                    const float *pre_scale = nullptr, const float *pre_shift = nullptr, float pre_leak = 1.f) {
+  SCN_REQUIRE(!bn_scale == !bn_shift && !pre_scale == !pre_shift, SCN_ERR_BAD_ARG,
+              "scale and shift of a fused BatchNorm come together");
   SCN_REQUIRE(groups >= 1 && n_in_planes >= 1 && n_out_planes >= 1 && n_in_planes % groups == 0 &&
                   n_out_planes % groups == 0,
               SCN_ERR_BAD_ARG, "planes %d -> %d not divisible into %d groups", n_in_planes, n_out_planes, groups);
@@ -238,7 +296,8 @@ static int run_conv(scn_metadata *md, Rulebook &rb, bool transposed, const float
     g_last_kernel = SCN_KERNEL_CONV_ROWS;
   } else if (rows_out > 0) {
     SCN_TRY(conv_forward_dispatch(in, rows_in, out, rows_out, weight, bias, table, rb.n_offsets, cin, cout, groups,
-                                  precision, md->flags_dev, stream, bn_scale, bn_shift, leak));
+                                  precision, md->flags_dev, stream, bn_scale, bn_shift, leak, pre_scale, pre_shift,
+                                  pre_leak));
   }
   if (macs) {  // the reference's return value: rules x ip x op x groups (CPU/Convolution.cpp:141)
     if (g_deferred_counts.load()) {
@@ -402,6 +461,22 @@ int scn_convolution_bn_forward(scn_metadata *md, const int64_t *input_size, cons
   SCN_TRY(get_strided_rulebook(md, input_size, output_size, filter_size, filter_stride, stream, &rb));
   return run_conv(md, *rb, false, in_features, out_features, weight, bias, n_in_planes, n_out_planes, groups,
                   precision, stream, macs, false, bn_scale, bn_shift, (float)leakiness);
+}
+
+int scn_convolution_bn_bn_forward(scn_metadata *md, const int64_t *input_size, const int64_t *output_size,
+                                  const int64_t *filter_size, const int64_t *filter_stride, const float *in_features,
+                                  float *out_features, const float *weight, const float *bias, const float *pre_scale,
+                                  const float *pre_shift, double pre_leakiness, const float *bn_scale,
+                                  const float *bn_shift, double leakiness, int n_in_planes, int n_out_planes, int groups,
+                                  int precision, void *stream_, double *macs) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SCN_REQUIRE(md && input_size && output_size && filter_size && filter_stride && pre_scale && pre_shift, SCN_ERR_BAD_ARG,
+              "null argument");
+  Rulebook *rb = nullptr;
+  SCN_TRY(get_strided_rulebook(md, input_size, output_size, filter_size, filter_stride, stream, &rb));
+  return run_conv(md, *rb, false, in_features, out_features, weight, bias, n_in_planes, n_out_planes, groups,
+                  precision, stream, macs, false, bn_scale, bn_shift, (float)leakiness, pre_scale, pre_shift,
+                  (float)pre_leakiness);
 }
 
 int scn_deconvolution_bn_forward(scn_metadata *md, const int64_t *input_size, const int64_t *output_size,

@@ -630,7 +630,8 @@ struct TcPlan {
 };
 
 // conv_wide.cu: in [n][cin] fp32 -> out, per row and 32-plane block, the 32 h = bf16(x) then the 32 m = bf16(x - h)
-int split_rows_bf16(const float *in, unsigned char *out, long long n_rows, int cin, cudaStream_t stream);
+int split_rows_bf16(const float *in, unsigned char *out, long long n_rows, int cin, cudaStream_t stream,
+                    const float *pre_scale = nullptr, const float *pre_shift = nullptr, float pre_leak = 1.f);
 
 static int env_int(const char *name, int dflt) {
   const char *v = getenv(name);
@@ -717,9 +718,20 @@ static int configure_tc_kernels() {
   return SCN_OK;
 }
 
+// Will conv_forward_tc split the rows before the launch (and so be able to take a BatchNorm in front into that pass)?
+bool conv_tc_splits_rows(int precision, int cin, long long n_in, long long n_out) {
+  const int mode = tc_mode_of(precision);
+  const int copy_env = env_int("SCN_TC_COPY", -1);
+  return (mode == TC_BF16 || mode == TC_BF16X3) && cin % 32 == 0 && n_in > 0 && !g_drop_arrival &&
+         (copy_env < 0 ? n_out >= 4096 : copy_env != 0);
+}
+
+// pre_scale / pre_shift / pre_leak (optional, only where conv_tc_splits_rows says yes): an eval-mode BatchNorm and its
+// leaky ReLU in front of the convolution, applied in the split pass
 int conv_forward_tc(const float *in, long long n_in, float *out, long long n_out, const float *weight,
                     const float *bias, const float *bn_scale, const float *bn_shift, float leak, const int *table,
-                    int K, int cin, int cout, int precision, int *flags, cudaStream_t stream) {
+                    int K, int cin, int cout, int precision, int *flags, cudaStream_t stream, const float *pre_scale,
+                    const float *pre_shift, float pre_leak) {
   if (n_out == 0) return SCN_OK;
   int mode = tc_mode_of(precision);
   SCN_REQUIRE(mode >= 0 && K <= kTcMaxOffsets, SCN_ERR_UNSUPPORTED, "tensor-core path: unsupported precision/filter");
@@ -743,12 +755,11 @@ int conv_forward_tc(const float *in, long long n_in, float *out, long long n_out
   // costs more than it saves (224 -> 224 planes: 0.058 ms with register producers against 0.098 at 1.4 k rows, 0.093
   // against 0.082 at 6.4 k, 0.349 against 0.280 for 320 -> 160 at 23 k).  SCN_TC_COPY=0 / 1 forces the choice.
   unsigned char *split = nullptr;
-  const int copy_env = env_int("SCN_TC_COPY", -1);
-  const bool copy_only = (mode == TC_BF16 || mode == TC_BF16X3) && cin % 32 == 0 && n_in > 0 && !g_drop_arrival &&
-                         (copy_env < 0 ? n_out >= 4096 : copy_env != 0);
+  const bool copy_only = conv_tc_splits_rows(precision, cin, n_in, n_out);
+  SCN_REQUIRE(copy_only || !pre_scale, SCN_ERR_UNSUPPORTED, "a BatchNorm in front needs the split pass");
   if (copy_only) {
     SCN_TRY(device_alloc((void **)&split, (size_t)n_in * cin * 4, stream));
-    SCN_TRY(split_rows_bf16(in, split, n_in, cin, stream));
+    SCN_TRY(split_rows_bf16(in, split, n_in, cin, stream, pre_scale, pre_shift, pre_leak));
   }
   TcParams P;
   P.in = in;

@@ -406,15 +406,32 @@ __global__ void __launch_bounds__((PW + 5) * 32, 1) k_conv_wide(WideParams P) {
 
 // in [n][cin] fp32 -> out, per row and 32-plane slice: the 32 h = bf16(x) then the 32 m = bf16(x - h)
 // (128 bytes, the size of the fp32 slice).  One thread per 8 planes: 32 bytes in, 16 + 16 out.
+// pre_scale / pre_shift (optional): x is first taken through an eval-mode BatchNorm and its leaky ReLU,
+// x <- act(x * scale[plane] + shift[plane]) with the roundings of the stand-alone operator: a BatchNorm in front of
+// the convolution costs no pass of its own.
+__device__ __forceinline__ float wide_pre_bn(float x, float sc, float sh, float leak) {
+  const float y = __fadd_rn(__fmul_rn(x, sc), sh);
+  return y * (y > 0.f ? 1.f : leak);
+}
+
 __global__ void __launch_bounds__(256)
-k_wide_split_rows(const float *__restrict__ in, unsigned char *__restrict__ out, long long n_pieces, int cin) {
+k_wide_split_rows(const float *__restrict__ in, unsigned char *__restrict__ out, long long n_pieces, int cin,
+                  const float *__restrict__ pre_scale, const float *__restrict__ pre_shift, float pre_leak) {
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= n_pieces) return;
   const int ppr = cin / 8;  // pieces per row
   const long long row = idx / ppr;
   const int piece = (int)(idx % ppr), slice = piece >> 2, j = piece & 3;
   const float4 *p = reinterpret_cast<const float4 *>(in + row * cin + piece * 8);
-  const float4 a = __ldg(p), b = __ldg(p + 1);
+  float4 a = __ldg(p), b = __ldg(p + 1);
+  if (pre_scale) {
+    const float4 s0 = __ldg(reinterpret_cast<const float4 *>(pre_scale + piece * 8)), s1 = __ldg(reinterpret_cast<const float4 *>(pre_scale + piece * 8) + 1);
+    const float4 h0 = __ldg(reinterpret_cast<const float4 *>(pre_shift + piece * 8)), h1 = __ldg(reinterpret_cast<const float4 *>(pre_shift + piece * 8) + 1);
+    a.x = wide_pre_bn(a.x, s0.x, h0.x, pre_leak), a.y = wide_pre_bn(a.y, s0.y, h0.y, pre_leak);
+    a.z = wide_pre_bn(a.z, s0.z, h0.z, pre_leak), a.w = wide_pre_bn(a.w, s0.w, h0.w, pre_leak);
+    b.x = wide_pre_bn(b.x, s1.x, h1.x, pre_leak), b.y = wide_pre_bn(b.y, s1.y, h1.y, pre_leak);
+    b.z = wide_pre_bn(b.z, s1.z, h1.z, pre_leak), b.w = wide_pre_bn(b.w, s1.w, h1.w, pre_leak);
+  }
   uint4 h, m;
   split_bf16_pair(a.x, a.y, h.x, m.x);
   split_bf16_pair(a.z, a.w, h.y, m.y);
@@ -441,10 +458,14 @@ constexpr size_t kWideSmemBudget = 226 * 1024;
 
 // The split pass on its own (also used by the per-tile kernel of conv_tc.cu): cin a multiple of 32, `out` holds
 // n_rows * cin * 4 bytes.
-int split_rows_bf16(const float *in, unsigned char *out, long long n_rows, int cin, cudaStream_t stream) {
+int split_rows_bf16(const float *in, unsigned char *out, long long n_rows, int cin, cudaStream_t stream,
+                    const float *pre_scale, const float *pre_shift, float pre_leak) {
   const long long n_pieces = n_rows * (cin / 8);
   if (n_pieces <= 0) return SCN_OK;
-  SCN_LAUNCH(k_wide_split_rows, (unsigned)ceil_div(n_pieces, 256LL), 256, 0, stream, in, out, n_pieces, cin);
+  SCN_REQUIRE(!pre_scale || ((uintptr_t)pre_scale % 16 == 0 && (uintptr_t)pre_shift % 16 == 0), SCN_ERR_BAD_ARG,
+              "scale / shift of the BatchNorm in front must be 16-byte aligned");
+  SCN_LAUNCH(k_wide_split_rows, (unsigned)ceil_div(n_pieces, 256LL), 256, 0, stream, in, out, n_pieces, cin, pre_scale,
+             pre_shift, pre_leak);
   SCN_CUDA_CHECK(cudaGetLastError());
   return SCN_OK;
 }
@@ -463,7 +484,8 @@ bool conv_wide_supported(int K, int cin, int cout, int groups, int precision, lo
 // null (then no scaling and, with leak == 1, no activation: the plain convolution).
 int conv_forward_wide(const float *in, long long n_in, float *out, long long n_out, const float *weight,
                       const float *bias, const float *bn_scale, const float *bn_shift, float leak, const int *table,
-                      int K, int cin, int cout, int precision, int *flags, cudaStream_t stream) {
+                      int K, int cin, int cout, int precision, int *flags, cudaStream_t stream,
+                      const float *pre_scale, const float *pre_shift, float pre_leak) {
   if (n_out == 0) return SCN_OK;
   const int terms = precision == SCN_PRECISION_TF32X3 ? 3 : 1;
   SCN_REQUIRE((uintptr_t)in % 16 == 0, SCN_ERR_BAD_ARG, "tensor-core path needs a 16-byte aligned input matrix");
@@ -486,7 +508,8 @@ int conv_forward_wide(const float *in, long long n_in, float *out, long long n_o
   unsigned char *split = nullptr;
   SCN_TRY(device_alloc((void **)&split, (size_t)n_in * cin * 4, stream));
   const long long n_pieces = n_in * (cin / 8);
-  SCN_LAUNCH(k_wide_split_rows, (unsigned)ceil_div(n_pieces, 256LL), 256, 0, stream, in, split, n_pieces, cin);
+  SCN_LAUNCH(k_wide_split_rows, (unsigned)ceil_div(n_pieces, 256LL), 256, 0, stream, in, split, n_pieces, cin, pre_scale,
+             pre_shift, pre_leak);
   WideParams P;
   P.in = in;
   P.in_split = split;

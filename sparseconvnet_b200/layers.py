@@ -247,7 +247,9 @@ class Convolution(_ConvBase):
         self._init_weight(dimension, nIn, nOut, filter_size, bias, groups)
         self.filter_stride = to_long_tensor(dimension, filter_stride)
 
-    def forward(self, input, bn=None):
+    def forward(self, input, bn=None, pre_bn=None):
+        """`bn` / `pre_bn` (used by Sequential): eval-mode BatchNormalizations behind / in front of this layer that
+        are applied inside the convolution call instead of as passes of their own."""
         assert input.features.nelement() == 0 or input.features.size(1) == self.nIn
         out_size = torch.div(input.spatial_size - self.filter_size, self.filter_stride, rounding_mode="trunc") + 1
         assert ((out_size - 1) * self.filter_stride + self.filter_size == input.spatial_size).all(), \
@@ -267,7 +269,8 @@ class Convolution(_ConvBase):
                 macs = SCN.Convolution_updateOutput(
                     input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata,
                     input.features.detach().contiguous(), output.features, self.weight, bias,
-                    epilogue=bn.folded() if bn is not None else None)
+                    epilogue=bn.folded() if bn is not None else None,
+                    prologue=pre_bn.folded() if pre_bn is not None else None)
         self._count(macs, output.features)
         return output
 
