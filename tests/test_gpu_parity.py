@@ -365,6 +365,47 @@ def test_fused_batchnorm_in_the_persistent_tcgen05_kernel(cout, cuda, monkeypatc
     assert torch.equal(outs[0], outs[1]), float((outs[0] - outs[1]).abs().max())
 
 
+@pytest.mark.parametrize("env,kernel", [({"SCN_TC_PERSISTENT": "1"}, "k_conv_wide"), ({"SCN_TC_COPY": "1"}, "k_conv_tc"),
+                                        ({"SCN_TC_COPY": "0"}, "k_conv_tc"), ({"SCN_X3_MIN_COUT": "999"}, "k_conv_pipe_mma")])
+def test_batchnorm_in_front_of_a_strided_convolution(env, kernel, cuda, monkeypatch):
+    """BatchNorm -> Convolution 2/2 -> BatchNorm as one call (scn_convolution_bn_bn_forward) against the three
+    operators one after the other, bit for bit: in the split pass of both tcgen05 kernels and through the scratch
+    copy (per-tile kernel with register producers, a kernel without any fused store)."""
+    import sparseconvnet_b200 as scn
+    from sparseconvnet_b200 import SCN
+    for k, v in env.items():
+        monkeypatch.setenv(k, v)
+    rng = np.random.default_rng(17)
+    pts = rng.integers(0, 128, (30000, 2))
+    z = (64 + 25 * np.sin(pts[:, 0] / 9.0)).astype(np.int64)
+    coords = np.concatenate([pts, z[:, None], rng.integers(0, 2, (30000, 1))], 1).astype(np.int64)
+    torch.manual_seed(5)
+    net = scn.Sequential().add(scn.BatchNormLeakyReLU(64, leakiness=0.2)).add(
+        scn.Convolution(3, 64, 96, 2, 2, True)).add(scn.BatchNormReLU(96)).to(cuda).eval()
+    for bn in (net[0], net[2]):
+        bn.running_mean.normal_()
+        bn.running_var.uniform_(0.5, 2.0)
+        bn.weight.data.normal_()
+        bn.bias.data.normal_()
+    net[1].bias.data.normal_()
+    feats = torch.randn(30000, 64, device=cuda)
+    scn.set_precision("tf32x3")
+    try:
+        outs = []
+        for fuse in (False, True):
+            scn.Sequential.fuse = fuse
+            with torch.no_grad(), SCN.Profile() as prof:
+                y = net(scn.InputLayer(3, 128, mode=3)([torch.from_numpy(coords), feats]))
+            assert SCN._KERNEL_NAMES[SCN.lib.scn_last_conv_kernel()] == kernel
+            assert sum(r["kind"] == "batchnorm" for r in prof.rows()) == (0 if fuse else 2)
+            y.metadata.poll_errors()
+            outs.append(y.features.clone())
+    finally:
+        scn.Sequential.fuse = True
+        scn.set_precision("fp32")
+    assert torch.equal(outs[0], outs[1]), float((outs[0] - outs[1]).abs().max())
+
+
 @pytest.mark.parametrize("cin,cout", [(4, 1), (32, 20), (32, 3), (64, 32), (256, 17), (96, 8)])
 def test_rows_times_small_matrix(cin, cout, cuda):
     """scn_rows_affine_forward (NetworkInNetwork with few output planes, the per-voxel class head) against
