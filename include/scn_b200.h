@@ -384,6 +384,21 @@ SCN_API int scn_convolution_bn_forward(scn_metadata *md, const int64_t *input_si
                                        const float *bias, const float *bn_scale, const float *bn_shift,
                                        double leakiness, int n_in_planes, int n_out_planes, int groups,
                                        int precision, void *stream, double *macs);
+/* SubmanifoldConvolution of the column-wise concatenation [in_a (planes_a) | in_b (planes_b)] of two matrices over
+ * the same sites -- a JoinTable (sparseconvnet/tables.py:37-49) in front of the layer, as after the skip connection
+ * of a U-Net -- optionally through an eval-mode BatchNormalization (+ leaky ReLU) between the two (pre_scale /
+ * pre_shift [planes_a + planes_b] from scn_batchnorm_fold, may be NULL) and with the one behind the layer in its
+ * store (bn_scale / bn_shift, may be NULL).  groups = 1; planes_a a multiple of eight, planes_b of four.  The
+ * tcgen05 kernels read the two matrices where they lie, in the pass that splits their input rows; for the other
+ * kernels the library writes the (normalised) concatenation to a scratch matrix first.  Same bits as JoinTable,
+ * BatchNormalization, SubmanifoldConvolution, BatchNormalization one after the other.  Not in the reference. */
+SCN_API int scn_submanifold_convolution_joined_forward(scn_metadata *md, const int64_t *spatial_size,
+                                                       const int64_t *filter_size, const float *in_a, int planes_a,
+                                                       const float *in_b, int planes_b, float *out_features,
+                                                       const float *weight, const float *bias, const float *pre_scale,
+                                                       const float *pre_shift, double pre_leakiness,
+                                                       const float *bn_scale, const float *bn_shift, double leakiness,
+                                                       int n_out_planes, int precision, void *stream, double *macs);
 /* scn_convolution_bn_forward with a second eval-mode BatchNormalization (+ leaky ReLU), in FRONT of the
  * convolution: the layer sees act(in * pre_scale[plane] + pre_shift[plane]) (scale / shift [n_in_planes] from
  * scn_batchnorm_fold, same roundings as the stand-alone operator, so the result has the bits of the separate calls).

@@ -603,6 +603,41 @@ def strided_chain(m, inputSize, filterSize, filterStride, levels, device):
     return built.value
 
 
+def SubmanifoldConvolution_joined(inputSize, filterSize, m, inputs, output_features, weight, bias, prologue=None,
+                                  epilogue=None):
+    """SubmanifoldConvolution of the column-wise concatenation of two feature matrices over the same sites (a
+    JoinTable in front of the layer), optionally through an eval-mode BatchNorm in between (`prologue`) and with the
+    one behind in its store (`epilogue`): scn_submanifold_convolution_joined_forward.  Not in the reference.
+    Returns None when the shapes are not ones the call takes (the caller then joins first)."""
+    if len(inputs) != 2 or weight.size(1) != 1:
+        return None
+    fa, fb = (_features(f, "input_features") for f in inputs)
+    ca, cb = fa.size(1), fb.size(1)
+    if fa.size(0) != fb.size(0) or ca % 8 or cb % 4 or fa.device != fb.device or weight.size(2) != ca + cb:
+        return None
+    w = _features(weight.detach(), "weight")
+    b = _optional(bias, fa, "bias")
+    n, cout = fa.size(0), w.size(3)
+    macs = C.c_double()
+    with _on_device(fa.device):
+        if n != m.getNActive(inputSize):
+            raise RuntimeError("features have %d rows, metadata has %d active sites" % (n, m.getNActive(inputSize)))
+        output_features.resize_(n, cout)
+        psc, psh, pleak = _epilogue_args(prologue, fa, ca + cb) if prologue is not None else (None, None, 1.0)
+        sc, sh, leak = _epilogue_args(epilogue, fa, cout) if epilogue is not None else (None, None, 1.0)
+        with _timed("conv", dict(op="submanifold", n_in=n, n_out=n, cin=ca + cb, cout=cout, groups=1, offsets=w.size(0),
+                                 precision=_precision, joined=True, fused_bn=epilogue is not None,
+                                 fused_bn_in_front=prologue is not None)) as info:
+            check(lib.scn_submanifold_convolution_joined_forward(
+                m._h, sizes(inputSize), sizes(filterSize), _ptr(fa), ca, _ptr(fb), cb, _ptr(output_features), _ptr(w),
+                _ptr(b), psc, psh, pleak, sc, sh, leak, cout, _precision, _stream(), C.byref(macs)))
+            result = _macs_result(m, macs)
+            if Profile.active is not None:
+                info["macs"] = float(result)
+                info["kernel"] = _KERNEL_NAMES[lib.scn_last_conv_kernel()]
+    return result
+
+
 def strided_chain_start(m, inputSize, filterSize, filterStride, levels, device):
     """strided_chain without the wait (scn_md_strided_chain_start): the chain's kernels go to the library's side
     stream behind what the current stream holds now and run beside what is enqueued next; the call that first

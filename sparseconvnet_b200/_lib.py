@@ -72,6 +72,9 @@ SIGNATURES = {
     "scn_convolution_bn_forward": (C.c_int, [_vp, _i64p, _i64p, _i64p, _i64p, _vp, _vp, _vp, _vp, _vp, _vp,
                                              C.c_double, C.c_int, C.c_int, C.c_int, C.c_int, _vp,
                                              C.POINTER(C.c_double)]),
+    "scn_submanifold_convolution_joined_forward": (C.c_int, [_vp, _i64p, _i64p, _vp, C.c_int, _vp, C.c_int, _vp, _vp, _vp,
+                                                             _vp, _vp, C.c_double, _vp, _vp, C.c_double, C.c_int,
+                                                             C.c_int, _vp, C.POINTER(C.c_double)]),
     "scn_convolution_bn_bn_forward": (C.c_int, [_vp, _i64p, _i64p, _i64p, _i64p, _vp, _vp, _vp, _vp, _vp, _vp,
                                                 C.c_double, _vp, _vp, C.c_double, C.c_int, C.c_int, C.c_int, C.c_int,
                                                 _vp, C.POINTER(C.c_double)]),

@@ -96,6 +96,23 @@ class Sequential(torch.nn.Sequential):
                 input = nxt.forward(input, bn=post, pre_bn=m)
                 i += 3 if post is not None else 2
                 continue
+            # JoinTable -> eval-mode BatchNormalization -> SubmanifoldConvolution (-> BatchNormalization): the layers
+            # behind the skip connection of a U-Net as one call; the convolution reads the joined tensors where they
+            # lie (in the pass that splits its rows for the tensor core, where the kernel has one)
+            if (Sequential.fuse and type(m) is JoinTable and isinstance(nxt, layers.BatchNormalization)
+                    and type(nxt2) is layers.SubmanifoldConvolution and not m._forward_hooks and not m._forward_pre_hooks
+                    and not nxt2._forward_hooks and not nxt2._forward_pre_hooks and isinstance(input, (list, tuple))
+                    and len(input) == 2 and all(t.features.nelement() > 0 and t.features.dim() == 2 for t in input)
+                    and nxt.fusable(input[0].features) and nxt2.groups == 1
+                    and not any(layers.autograd.needs_grad(t.features) for t in input)
+                    and not layers.autograd.needs_grad(input[0].features, nxt2.weight)):
+                nxt3 = steps[i + 3] if i + 3 < n else None
+                post = nxt3 if (isinstance(nxt3, layers.BatchNormalization) and nxt3.fusable(input[0].features)) else None
+                joined = nxt2.forward_joined(input, pre_bn=nxt, bn=post)
+                if joined is not None:
+                    input = joined
+                    i += 4 if post is not None else 3
+                    continue
             # a JoinTable whose result goes straight into an eval-mode BatchNormalization: every joined tensor is
             # normalised into its columns of the result, the concatenation itself is never written
             if (Sequential.fuse and type(m) is JoinTable and isinstance(nxt, layers.BatchNormalization)

@@ -18,7 +18,8 @@ int conv_forward_simt(const float *in, long long n_in, float *out, long long n_o
 int conv_forward_tc(const float *in, long long n_in, float *out, long long n_out, const float *weight,
                     const float *bias, const float *bn_scale, const float *bn_shift, float leak, const int *table,
                     int K, int cin, int cout, int precision, int *flags, cudaStream_t stream,
-                    const float *pre_scale = nullptr, const float *pre_shift = nullptr, float pre_leak = 1.f);
+                    const float *pre_scale = nullptr, const float *pre_shift = nullptr, float pre_leak = 1.f,
+                    const float *in_b = nullptr, int planes_a = 0);
 bool conv_tc_supported(int cin, int cout, int groups, int precision);
 bool conv_tc_splits_rows(int precision, int cin, long long n_in, long long n_out);
 int conv_forward_tma(const float *in, long long n_in, float *out, long long n_out, const float *weight,
@@ -29,7 +30,8 @@ bool conv_wide_supported(int K, int cin, int cout, int groups, int precision, lo
 int conv_forward_wide(const float *in, long long n_in, float *out, long long n_out, const float *weight,
                       const float *bias, const float *bn_scale, const float *bn_shift, float leak, const int *table,
                       int K, int cin, int cout, int precision, int *flags, cudaStream_t stream,
-                      const float *pre_scale = nullptr, const float *pre_shift = nullptr, float pre_leak = 1.f);
+                      const float *pre_scale = nullptr, const float *pre_shift = nullptr, float pre_leak = 1.f,
+                      const float *in_b = nullptr, int planes_a = 0);
 bool conv_pipe_supported(const float *in, const float *out, const float *weight, const float *bias, int K, int cin,
                          int cout);
 int conv_forward_pipe(const float *in, long long n_in, float *out, long long n_out, const float *weight,
@@ -152,6 +154,29 @@ __global__ void k_scale_shift_act_to(const float *__restrict__ x, float *__restr
   }
 }
 
+// the column-wise concatenation [a (ca planes) | b (cb planes)] through the same BatchNorm into one scratch matrix:
+// a JoinTable and a BatchNorm in front of a convolution whose kernel has no split pass (planes multiples of four)
+__global__ void k_scale_shift_act_join_to(const float *__restrict__ a, int ca, const float *__restrict__ b, int cb,
+                                          float *__restrict__ y, long long n_rows, const float *__restrict__ scale,
+                                          const float *__restrict__ shift, float leak) {
+  const int pv = (ca + cb) / 4, av = ca / 4;
+  const long long total = n_rows * pv;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / pv;
+    const int q = (int)(i % pv), c = q * 4;
+    float4 v = q < av ? __ldg(reinterpret_cast<const float4 *>(a + r * ca + c))
+                      : __ldg(reinterpret_cast<const float4 *>(b + r * cb + (c - ca)));
+    if (scale) {
+      const float4 sc = __ldg(reinterpret_cast<const float4 *>(scale + c)), sh = __ldg(reinterpret_cast<const float4 *>(shift + c));
+      v.x = __fadd_rn(__fmul_rn(v.x, sc.x), sh.x), v.y = __fadd_rn(__fmul_rn(v.y, sc.y), sh.y);
+      v.z = __fadd_rn(__fmul_rn(v.z, sc.z), sh.z), v.w = __fadd_rn(__fmul_rn(v.w, sc.w), sh.w);
+      v.x *= (v.x > 0.f) ? 1.f : leak, v.y *= (v.y > 0.f) ? 1.f : leak;
+      v.z *= (v.z > 0.f) ? 1.f : leak, v.w *= (v.w > 0.f) ? 1.f : leak;
+    }
+    reinterpret_cast<float4 *>(y)[i] = v;
+  }
+}
+
 // W, x -> scale = gamma / sqrt(var + eps), shift = beta - mean * scale, with the roundings of the
 // stand-alone BatchNorm kernel (CPU/BatchNormalization.cpp:41-46 of the reference)
 __global__ void k_bn_fold(const float *__restrict__ mean, const float *__restrict__ var, const float *__restrict__ gamma,
@@ -171,7 +196,8 @@ __global__ void k_bn_fold(const float *__restrict__ mean, const float *__restric
 int conv_forward_dispatch(const float *in, long long rows_in, float *out, long long rows_out, const float *weight,
                           const float *bias, const int *table, int K, int cin, int cout, int groups, int precision,
                           int *flags, cudaStream_t stream, const float *bn_scale, const float *bn_shift, float leak,
-                          const float *pre_scale, const float *pre_shift, float pre_leak) {
+                          const float *pre_scale, const float *pre_shift, float pre_leak, const float *in_b,
+                          int planes_a) {
   bool fused = true;  // did the kernel apply the optional BatchNorm epilogue itself?
   // TF32X3 is the fp32-accuracy mode: each shape runs whichever fp32-class kernel is fastest.
   // With 32 or 64 output planes (and first layers) that is the row-stationary kernel of
@@ -197,7 +223,22 @@ int conv_forward_dispatch(const float *in, long long rows_in, float *out, long l
   const bool to_tma = tensor && !to_wide && !few_tiles && conv_tma_supported(K, cin, cout, groups, precision, rows_in);
   const bool to_tc = tensor && !to_wide && !to_tma && conv_tc_supported(cin, cout, groups, precision);
   float *pre_copy = nullptr;
-  if (pre_scale && rows_in > 0 && !(to_wide || (to_tc && conv_tc_splits_rows(precision, cin, rows_in, rows_out)))) {
+  const bool splits = to_wide || (to_tc && conv_tc_splits_rows(precision, cin, rows_in, rows_out));
+  if (in_b && rows_in > 0 && !splits) {
+    // a joined input (in_b: the input is [in (planes_a) | in_b]; groups == 1) for a kernel without a split pass:
+    // the concatenation, normalised if a BatchNorm comes with it, is written to a scratch matrix first
+    SCN_REQUIRE(groups == 1 && planes_a % 4 == 0 && (cin - planes_a) % 4 == 0 && (uintptr_t)in % 16 == 0 &&
+                    (uintptr_t)in_b % 16 == 0,
+                SCN_ERR_UNSUPPORTED, "joined input: plane counts must be multiples of four");
+    const long long total = rows_in * (long long)cin;
+    SCN_TRY(device_alloc((void **)&pre_copy, sizeof(float) * (size_t)total, stream));
+    SCN_LAUNCH(k_scale_shift_act_join_to, (unsigned)std::min<long long>(ceil_div(total / 4, 256), 148 * 16), 256, 0, stream,
+               in, planes_a, in_b, cin - planes_a, pre_copy, rows_in, pre_scale, pre_shift, pre_leak);
+    in = pre_copy;
+    in_b = nullptr;
+    pre_scale = pre_shift = nullptr;
+  }
+  if (pre_scale && rows_in > 0 && !splits) {
     const long long total = rows_in * (long long)cin * groups;
     SCN_TRY(device_alloc((void **)&pre_copy, sizeof(float) * (size_t)total, stream));
     const int vec = (cin * groups) % 4 == 0 && (uintptr_t)in % 16 == 0 && (uintptr_t)pre_scale % 16 == 0 &&
@@ -223,7 +264,7 @@ int conv_forward_dispatch(const float *in, long long rows_in, float *out, long l
     fused = false;
   } else if (to_wide) {
     SCN_TRY(conv_forward_wide(in, rows_in, out, rows_out, weight, bias, bn_scale, bn_shift, bn_scale ? leak : 1.f, table,
-                              K, cin, cout, precision, flags, stream, pre_scale, pre_shift, pre_leak));
+                              K, cin, cout, precision, flags, stream, pre_scale, pre_shift, pre_leak, in_b, planes_a));
     g_last_kernel = SCN_KERNEL_CONV_WIDE;
   } else if (to_tma) {
     SCN_TRY(conv_forward_tma(in, rows_in, out, rows_out, weight, bias, table, K, cin, cout,
@@ -232,7 +273,7 @@ int conv_forward_dispatch(const float *in, long long rows_in, float *out, long l
     fused = false;
   } else if (to_tc) {
     SCN_TRY(conv_forward_tc(in, rows_in, out, rows_out, weight, bias, bn_scale, bn_shift, leak, table, K, cin, cout,
-                            precision, flags, stream, pre_scale, pre_shift, pre_leak));
+                            precision, flags, stream, pre_scale, pre_shift, pre_leak, in_b, planes_a));
     g_last_kernel = SCN_KERNEL_CONV_TC;
   } else {
     SCN_TRY(conv_forward_simt(in, rows_in, out, rows_out, weight, bias, table, K, cin, cout,
@@ -261,7 +302,8 @@ static int run_conv(scn_metadata *md, Rulebook &rb, bool transposed, const float
                     const float *weight, const float *bias, int n_in_planes, int n_out_planes, int groups,
                     int precision, cudaStream_t stream, double *macs, bool disjoint = false,
                     const float *bn_scale = nullptr, const float *bn_shift = nullptr, float leak = 1.f,
-                    const float *pre_scale = nullptr, const float *pre_shift = nullptr, float pre_leak = 1.f) {
+                    const float *pre_scale = nullptr, const float *pre_shift = nullptr, float pre_leak = 1.f,
+                    const float *in_b = nullptr, int planes_a = 0) {
   SCN_REQUIRE(!bn_scale == !bn_shift && !pre_scale == !pre_shift, SCN_ERR_BAD_ARG,
               "scale and shift of a fused BatchNorm come together");
   SCN_REQUIRE(groups >= 1 && n_in_planes >= 1 && n_out_planes >= 1 && n_in_planes % groups == 0 &&
@@ -297,7 +339,7 @@ static int run_conv(scn_metadata *md, Rulebook &rb, bool transposed, const float
   } else if (rows_out > 0) {
     SCN_TRY(conv_forward_dispatch(in, rows_in, out, rows_out, weight, bias, table, rb.n_offsets, cin, cout, groups,
                                   precision, md->flags_dev, stream, bn_scale, bn_shift, leak, pre_scale, pre_shift,
-                                  pre_leak));
+                                  pre_leak, in_b, planes_a));
   }
   if (macs) {  // the reference's return value: rules x ip x op x groups (CPU/Convolution.cpp:141)
     if (g_deferred_counts.load()) {
@@ -461,6 +503,24 @@ int scn_convolution_bn_forward(scn_metadata *md, const int64_t *input_size, cons
   SCN_TRY(get_strided_rulebook(md, input_size, output_size, filter_size, filter_stride, stream, &rb));
   return run_conv(md, *rb, false, in_features, out_features, weight, bias, n_in_planes, n_out_planes, groups,
                   precision, stream, macs, false, bn_scale, bn_shift, (float)leakiness);
+}
+
+int scn_submanifold_convolution_joined_forward(scn_metadata *md, const int64_t *spatial_size, const int64_t *filter_size,
+                                               const float *in_a, int planes_a, const float *in_b, int planes_b,
+                                               float *out_features, const float *weight, const float *bias,
+                                               const float *pre_scale, const float *pre_shift, double pre_leakiness,
+                                               const float *bn_scale, const float *bn_shift, double leakiness,
+                                               int n_out_planes, int precision, void *stream_, double *macs) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SCN_REQUIRE(md && spatial_size && filter_size, SCN_ERR_BAD_ARG, "null argument");
+  SCN_REQUIRE(planes_a >= 8 && planes_b >= 4 && planes_a % 8 == 0 && planes_b % 4 == 0, SCN_ERR_UNSUPPORTED,
+              "joined input: %d + %d planes unsupported (a multiple of eight, then a multiple of four)", planes_a, planes_b);
+  Rulebook *rb = nullptr;
+  SCN_TRY(get_submanifold_rulebook(md, spatial_size, filter_size, stream, &rb));
+  SCN_REQUIRE(rb->n_in == 0 || (in_a && in_b), SCN_ERR_BAD_ARG, "null features");
+  return run_conv(md, *rb, false, in_a, out_features, weight, bias, planes_a + planes_b, n_out_planes, 1, precision,
+                  stream, macs, false, bn_scale, bn_shift, (float)leakiness, pre_scale, pre_shift, (float)pre_leakiness,
+                  in_b, planes_a);
 }
 
 int scn_convolution_bn_bn_forward(scn_metadata *md, const int64_t *input_size, const int64_t *output_size,

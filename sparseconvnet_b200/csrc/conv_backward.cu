@@ -25,7 +25,8 @@ int conv_forward_dispatch(const float *in, long long rows_in, float *out, long l
                           const float *bias, const int *table, int K, int cin, int cout, int groups, int precision,
                           int *flags, cudaStream_t stream, const float *bn_scale = nullptr,
                           const float *bn_shift = nullptr, float leak = 1.f, const float *pre_scale = nullptr,
-                          const float *pre_shift = nullptr, float pre_leak = 1.f);
+                          const float *pre_shift = nullptr, float pre_leak = 1.f, const float *in_b = nullptr,
+                          int planes_a = 0);
 int conv_forward_simt(const float *in, long long n_in, float *out, long long n_out, const float *weight,
                       const float *bias, const int *table, int K, int cin, int cout, int groups, int *flags,
                       cudaStream_t stream);

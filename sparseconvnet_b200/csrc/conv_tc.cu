@@ -631,7 +631,8 @@ struct TcPlan {
 
 // conv_wide.cu: in [n][cin] fp32 -> out, per row and 32-plane block, the 32 h = bf16(x) then the 32 m = bf16(x - h)
 int split_rows_bf16(const float *in, unsigned char *out, long long n_rows, int cin, cudaStream_t stream,
-                    const float *pre_scale = nullptr, const float *pre_shift = nullptr, float pre_leak = 1.f);
+                    const float *pre_scale = nullptr, const float *pre_shift = nullptr, float pre_leak = 1.f,
+                    const float *in_b = nullptr, int planes_a = 0);
 
 static int env_int(const char *name, int dflt) {
   const char *v = getenv(name);
@@ -731,7 +732,7 @@ bool conv_tc_splits_rows(int precision, int cin, long long n_in, long long n_out
 int conv_forward_tc(const float *in, long long n_in, float *out, long long n_out, const float *weight,
                     const float *bias, const float *bn_scale, const float *bn_shift, float leak, const int *table,
                     int K, int cin, int cout, int precision, int *flags, cudaStream_t stream, const float *pre_scale,
-                    const float *pre_shift, float pre_leak) {
+                    const float *pre_shift, float pre_leak, const float *in_b, int planes_a) {
   if (n_out == 0) return SCN_OK;
   int mode = tc_mode_of(precision);
   SCN_REQUIRE(mode >= 0 && K <= kTcMaxOffsets, SCN_ERR_UNSUPPORTED, "tensor-core path: unsupported precision/filter");
@@ -756,10 +757,15 @@ int conv_forward_tc(const float *in, long long n_in, float *out, long long n_out
   // against 0.082 at 6.4 k, 0.349 against 0.280 for 320 -> 160 at 23 k).  SCN_TC_COPY=0 / 1 forces the choice.
   unsigned char *split = nullptr;
   const bool copy_only = conv_tc_splits_rows(precision, cin, n_in, n_out);
-  SCN_REQUIRE(copy_only || !pre_scale, SCN_ERR_UNSUPPORTED, "a BatchNorm in front needs the split pass");
+  SCN_REQUIRE(copy_only || (!pre_scale && !in_b), SCN_ERR_UNSUPPORTED,
+              "a BatchNorm or a join in front needs the split pass");
   if (copy_only) {
     SCN_TRY(device_alloc((void **)&split, (size_t)n_in * cin * 4, stream));
-    SCN_TRY(split_rows_bf16(in, split, n_in, cin, stream, pre_scale, pre_shift, pre_leak));
+    const int st = split_rows_bf16(in, split, n_in, cin, stream, pre_scale, pre_shift, pre_leak, in_b, planes_a);
+    if (st != SCN_OK) {
+      device_free(split, stream);
+      return st;
+    }
   }
   TcParams P;
   P.in = in;

@@ -414,15 +414,21 @@ __device__ __forceinline__ float wide_pre_bn(float x, float sc, float sh, float 
   return y * (y > 0.f ? 1.f : leak);
 }
 
+// in_b (optional): the input is the column-wise concatenation [in (planes_a) | in_b (cin - planes_a)] of two
+// matrices (a JoinTable in front of the layer), read from where the two lie; planes_a a multiple of eight.
 __global__ void __launch_bounds__(256)
 k_wide_split_rows(const float *__restrict__ in, unsigned char *__restrict__ out, long long n_pieces, int cin,
-                  const float *__restrict__ pre_scale, const float *__restrict__ pre_shift, float pre_leak) {
+                  const float *__restrict__ pre_scale, const float *__restrict__ pre_shift, float pre_leak,
+                  const float *__restrict__ in_b, int planes_a) {
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= n_pieces) return;
   const int ppr = cin / 8;  // pieces per row
   const long long row = idx / ppr;
   const int piece = (int)(idx % ppr), slice = piece >> 2, j = piece & 3;
-  const float4 *p = reinterpret_cast<const float4 *>(in + row * cin + piece * 8);
+  const float *src = !in_b ? in + row * cin + piece * 8
+                           : (piece * 8 < planes_a ? in + row * planes_a + piece * 8
+                                                   : in_b + row * (cin - planes_a) + (piece * 8 - planes_a));
+  const float4 *p = reinterpret_cast<const float4 *>(src);
   float4 a = __ldg(p), b = __ldg(p + 1);
   if (pre_scale) {
     const float4 s0 = __ldg(reinterpret_cast<const float4 *>(pre_scale + piece * 8)), s1 = __ldg(reinterpret_cast<const float4 *>(pre_scale + piece * 8) + 1);
@@ -459,13 +465,15 @@ constexpr size_t kWideSmemBudget = 226 * 1024;
 // The split pass on its own (also used by the per-tile kernel of conv_tc.cu): cin a multiple of 32, `out` holds
 // n_rows * cin * 4 bytes.
 int split_rows_bf16(const float *in, unsigned char *out, long long n_rows, int cin, cudaStream_t stream,
-                    const float *pre_scale, const float *pre_shift, float pre_leak) {
+                    const float *pre_scale, const float *pre_shift, float pre_leak, const float *in_b, int planes_a) {
+  SCN_REQUIRE(!in_b || (planes_a > 0 && planes_a < cin && planes_a % 8 == 0 && (uintptr_t)in_b % 16 == 0),
+              SCN_ERR_BAD_ARG, "joined input: the first part must have a multiple of eight planes");
   const long long n_pieces = n_rows * (cin / 8);
   if (n_pieces <= 0) return SCN_OK;
   SCN_REQUIRE(!pre_scale || ((uintptr_t)pre_scale % 16 == 0 && (uintptr_t)pre_shift % 16 == 0), SCN_ERR_BAD_ARG,
               "scale / shift of the BatchNorm in front must be 16-byte aligned");
   SCN_LAUNCH(k_wide_split_rows, (unsigned)ceil_div(n_pieces, 256LL), 256, 0, stream, in, out, n_pieces, cin, pre_scale,
-             pre_shift, pre_leak);
+             pre_shift, pre_leak, in_b, planes_a);
   SCN_CUDA_CHECK(cudaGetLastError());
   return SCN_OK;
 }
@@ -485,7 +493,7 @@ bool conv_wide_supported(int K, int cin, int cout, int groups, int precision, lo
 int conv_forward_wide(const float *in, long long n_in, float *out, long long n_out, const float *weight,
                       const float *bias, const float *bn_scale, const float *bn_shift, float leak, const int *table,
                       int K, int cin, int cout, int precision, int *flags, cudaStream_t stream,
-                      const float *pre_scale, const float *pre_shift, float pre_leak) {
+                      const float *pre_scale, const float *pre_shift, float pre_leak, const float *in_b, int planes_a) {
   if (n_out == 0) return SCN_OK;
   const int terms = precision == SCN_PRECISION_TF32X3 ? 3 : 1;
   SCN_REQUIRE((uintptr_t)in % 16 == 0, SCN_ERR_BAD_ARG, "tensor-core path needs a 16-byte aligned input matrix");
@@ -507,9 +515,13 @@ int conv_forward_wide(const float *in, long long n_in, float *out, long long n_o
   // the input rows as bf16 parts, made once per call (every row is gathered by up to K output rows)
   unsigned char *split = nullptr;
   SCN_TRY(device_alloc((void **)&split, (size_t)n_in * cin * 4, stream));
-  const long long n_pieces = n_in * (cin / 8);
-  SCN_LAUNCH(k_wide_split_rows, (unsigned)ceil_div(n_pieces, 256LL), 256, 0, stream, in, split, n_pieces, cin, pre_scale,
-             pre_shift, pre_leak);
+  {
+    const int st = split_rows_bf16(in, split, n_in, cin, stream, pre_scale, pre_shift, pre_leak, in_b, planes_a);
+    if (st != SCN_OK) {
+      device_free(split, stream);
+      return st;
+    }
+  }
   WideParams P;
   P.in = in;
   P.in_split = split;

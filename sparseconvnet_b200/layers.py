@@ -224,6 +224,23 @@ class SubmanifoldConvolution(_ConvBase):
         self._count(macs, output.features)
         return output
 
+    def forward_joined(self, inputs, pre_bn=None, bn=None):
+        """This layer applied to the concatenation of `inputs` (what a JoinTable in front of it would produce),
+        through the eval-mode BatchNormalization `pre_bn` between the two if given, without the concatenation and
+        the normalised copy being built as tensors of their own.  None when the shapes do not allow it."""
+        output = SparseConvNetTensor(metadata=inputs[0].metadata, spatial_size=inputs[0].spatial_size)
+        output.features = inputs[0].features.new_empty(0)
+        with SCN.weight_token(self._weight_token()):
+            macs = SCN.SubmanifoldConvolution_joined(
+                inputs[0].spatial_size, self.filter_size, inputs[0].metadata,
+                [i.features.detach().contiguous() for i in inputs], output.features, self.weight,
+                optional_tensor(self, "bias"), prologue=pre_bn.folded() if pre_bn is not None else None,
+                epilogue=bn.folded() if bn is not None else None)
+        if macs is None:
+            return None
+        self._count(macs, output.features)
+        return output
+
     def input_spatial_size(self, out_size):
         return out_size
 

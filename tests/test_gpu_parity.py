@@ -320,12 +320,12 @@ def test_fused_batchnorm_equals_two_passes(precision, cuda):
         scn.Sequential.fuse = True
         scn.set_precision("fp32")
     assert bn_calls[0] == 39 and fused[0] == 0
-    # 27 of the 39 BatchNorms ride in a convolution's store, the 6 behind a JoinTable read the two joined
-    # tensors directly (no concatenation pass), the 6 in front of a strided Convolution are applied by that
-    # convolution to its input (in its split pass, or into a scratch copy where the kernel has none)
-    assert fused[1] == 27 and bn_calls[1] == 6, (bn_calls, fused)
-    assert sum(bool(r.get("joined")) for r in rows if r["kind"] == "batchnorm") == 6
-    assert sum(bool(r.get("fused_bn_in_front")) for r in rows if r["kind"] == "conv") == 6
+    # 27 of the 39 BatchNorms ride in a convolution's store; the 6 behind a JoinTable and the 6 in front of a
+    # strided Convolution are applied by the convolution that follows to its own input (in its split pass, or into
+    # a scratch copy where the kernel has none), the joined tensors read where they lie: no BatchNorm call is left
+    assert fused[1] == 27 and bn_calls[1] == 0, (bn_calls, fused)
+    assert sum(bool(r.get("joined")) for r in rows if r["kind"] == "conv") == 6
+    assert sum(bool(r.get("fused_bn_in_front")) for r in rows if r["kind"] == "conv") == 12
     assert torch.equal(outs[0], outs[1]), float((outs[0] - outs[1]).abs().max())
 
 
