@@ -91,7 +91,7 @@ class Sequential(torch.nn.Sequential):
                     and not m._forward_hooks and not m._forward_pre_hooks and not nxt._forward_hooks
                     and not nxt._forward_pre_hooks and isinstance(input, SparseConvNetTensor)
                     and input.features.nelement() > 0 and m.fusable(input.features)
-                    and not layers.autograd.needs_grad(input.features, nxt.weight)):
+                    and not layers.autograd.needs_grad(input.features, nxt.weight, getattr(nxt, "bias", None))):
                 post = nxt2 if (isinstance(nxt2, layers.BatchNormalization) and nxt2.fusable(input.features)) else None
                 input = nxt.forward(input, bn=post, pre_bn=m)
                 i += 3 if post is not None else 2
@@ -105,7 +105,7 @@ class Sequential(torch.nn.Sequential):
                     and len(input) == 2 and all(t.features.nelement() > 0 and t.features.dim() == 2 for t in input)
                     and nxt.fusable(input[0].features) and nxt2.groups == 1
                     and not any(layers.autograd.needs_grad(t.features) for t in input)
-                    and not layers.autograd.needs_grad(input[0].features, nxt2.weight)):
+                    and not layers.autograd.needs_grad(input[0].features, nxt2.weight, getattr(nxt2, "bias", None))):
                 nxt3 = steps[i + 3] if i + 3 < n else None
                 post = nxt3 if (isinstance(nxt3, layers.BatchNormalization) and nxt3.fusable(input[0].features)) else None
                 joined = nxt2.forward_joined(input, pre_bn=nxt, bn=post)

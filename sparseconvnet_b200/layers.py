@@ -277,6 +277,7 @@ class Convolution(_ConvBase):
             SCN.strided_chain(input.metadata, input.spatial_size, self.filter_size, self.filter_stride,
                               self.levels_below, input.features.device)
         if autograd.needs_grad(input.features, self.weight, bias):
+            assert bn is None and pre_bn is None  # (the fused forms are inference-only; Sequential checks the same)
             output.features, macs = autograd.convolution(
                 autograd.STRIDED, input.features, self.weight, bias.to(self.weight.device), input.metadata,
                 input.spatial_size, out_size, self.filter_size, self.filter_stride)
