@@ -47,11 +47,14 @@ def _chain_ahead(steps):
 
 
 class Sequential(torch.nn.Sequential):
-    """Runs its children in order, like the reference's container.  One peephole: a convolution whose
-    output goes straight into an eval-mode BatchNormalization (possibly across the boundary of a
-    nested Sequential, as in the U-Net's blocks) applies that layer's scale, shift and leaky ReLU in
-    its own store -- same arithmetic, one pass over the activation less.  `Sequential.fuse = False`
-    turns it off.
+    """Runs its children in order, like the reference's container.  Peepholes (inference only, same
+    arithmetic and the same bits as the separate layers; `Sequential.fuse = False` turns them off):
+    a convolution whose output goes straight into an eval-mode BatchNormalization (possibly across
+    the boundary of a nested Sequential, as in the U-Net's blocks) applies that layer's scale, shift
+    and leaky ReLU in its own store; an eval-mode BatchNormalization in front of a strided Convolution
+    is applied by that convolution to its input; JoinTable -> BatchNormalization ->
+    SubmanifoldConvolution is one call on the tensors that would have been joined; a JoinTable
+    followed by a BatchNormalization alone is one pass without the concatenation.
 
     And one look ahead (`Sequential.prefetch_rulebooks = False` turns it off): the first Sequential that sees a
     tensor of a new Metadata looks for the encoder's first downsampling Convolution behind the layers that keep
