@@ -453,8 +453,9 @@ size_t wide_stage_bytes(int terms, int cout, int rows) {
   const size_t w = (size_t)cout * kWSlice * 2 * parts;
   return ((w + 1023) & ~(size_t)1023) + (size_t)4 * (rows * 16 + 32) * parts;
 }
-// Rows per tile.  Measured alternatives that lost: 128-row tiles (N = 128 instructions are as efficient, but the
-// per-group work of the producers doubles: 0.65 against 0.56 ms on 96 -> 96 planes at 154 k rows), 24 producer
+// Rows per tile.  Measured alternatives that lost: 128-row tiles (N = 128 instructions are as efficient, but every
+// tile brings its own weight slabs: a third more operand bytes per row through shared memory; 0.47 against 0.36 ms on
+// 96 -> 96 planes at 154 k rows with the copy-only producers, 0.65 against 0.56 with the earlier ones), 24 producer
 // warps (0.45 against 0.44 ms) and two CTAs per SM with half the ring and one accumulator each (0.45 ms).
 int wide_rows() { return 256; }
 constexpr size_t kWideControlBytes = 4096;  // barriers, step flags, and the rulebook entries of two groups
