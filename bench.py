@@ -347,6 +347,9 @@ def main():
                     help="convolution arithmetic of the headline number (tf32x3 and fp32 meet the fp32 parity bar)")
     ap.add_argument("--no-variants", action="store_true", help="skip timing the other arithmetic modes")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--data-parallel-training", action="store_true",
+                    help="with --gpus N > 1: also time a training step of two rooms per rank with BatchNorm statistics "
+                         "and gradients exchanged between the ranks (`training_step_data_parallel` on the line)")
     ap.add_argument("--no-config1", action="store_true", help="skip the single-convolution (configuration 1) numbers")
     ap.add_argument("--rooms", type=int, default=ROOMS_PER_GPU,
                     help="rooms per GPU; the benchmark is 8, smaller values are for profiler captures of a small case")
@@ -762,6 +765,46 @@ def main():
                     "backward": "input gradients %s, weight gradients fp32" % args.precision, "optimizer": "SGD"}
         del net_t, head_t, params, opt
 
+    # ---- the same training step data-parallel: two rooms per rank, BatchNorm statistics over all ranks, gradients
+    # summed over the ranks before the optimizer step (asked for with --data-parallel-training) -------------------
+    training_dp = None
+    if world > 1 and args.data_parallel_training:
+        inp_t, net_t, head_t = workloads.build_config(CONFIG)
+        net_t.to(dev).train()
+        head_t.to(dev).train()
+        shard.share_batchnorm_statistics(net_t)
+        ct_np, ft_np = workloads.make_batch(CONFIG, [2 * rank, 2 * rank + 1])
+        ct, ft = torch.from_numpy(ct_np), torch.from_numpy(ft_np).to(dev)
+        params = list(net_t.parameters()) + list(head_t.parameters())
+        opt = torch.optim.SGD(params, lr=1e-3)
+        labels = torch.randint(0, 20, (ct_np.shape[0],), device=dev, generator=torch.Generator(dev).manual_seed(1))
+        count = torch.tensor([float(ct_np.shape[0])], device=dev)
+        dist.all_reduce(count)
+        vox_all = int(count.item())
+        reduces = [0]
+
+        def train_step_dp():
+            logits = head_t(net_t(inp_t([ct, ft])).features)
+            loss = torch.nn.functional.cross_entropy(logits, labels[:logits.size(0)], reduction="sum") / vox_all
+            opt.zero_grad(set_to_none=True)
+            loss.backward()
+            reduces[0] = shard.sum_gradients(params)
+            opt.step()
+            return loss
+
+        scn.set_backward_precision(args.precision)
+        try:
+            train_step_dp()
+            ms_t, _ = timed(train_step_dp, 3)
+        finally:
+            scn.set_backward_precision("fp32")
+        n_bn = sum(1 for m in net_t.modules() if isinstance(m, scn.BatchNormalization))
+        training_dp = {"workload": workload_name(2), "voxels_per_step": vox_all, "ms_per_step": ms_t / 3,
+                       "voxels_per_sec": vox_all * 3 / (ms_t / 1e3), "scaling": "weak",
+                       "exchanges_per_step": "%d all-reduces of BatchNorm sums (forward + backward of %d layers), "
+                                             "%d of gradient buckets" % (2 * n_bn, n_bn, reduces[0])}
+        del net_t, head_t, params, opt
+
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -777,6 +820,7 @@ def main():
             "ms_each_step": per_step, "ms_each_step_e2e": measure.per_step_e2e,
             "roofline": roofline, "breakdown_ms_per_step": breakdown, "submanifold_conv": sub, "configs": configs,
             "variants_voxels_per_sec": variants, "training_step": training,
+            "training_step_data_parallel": training_dp,
             "cpu_baseline": cpu, "clocks": clocks,
         }
         if world > 1:

@@ -487,6 +487,44 @@ SCN_API int scn_batchnorm_backward(const float *in_features, float *d_in_feature
                            const float *weight, float *d_weight, float *d_bias, double leakiness,
                            void *stream);
 
+/* Training-mode BatchNorm over rows that live on several GPUs (data-parallel training), in two phases per
+ * direction with the caller's sum over the devices in between.  Not in the reference, which is single-device: its
+ * BatchNormalization_updateOutput / _backward (CPU/BatchNormalization.cpp:12-62, 64-107) take the statistics over
+ * the one matrix they are given; with one device (sums passed on unchanged, n_rows_total = n_rows) the two phases
+ * give what scn_batchnorm_forward / scn_batchnorm_backward give.
+ *
+ * scn_batchnorm_moments: sums[0..C) = sum of x, sums[C..2C) = sum of x^2 over this device's rows (device doubles,
+ * overwritten; n_rows may be 0).  The caller adds the arrays of all devices and the row counts.
+ * scn_batchnorm_forward_moments: mean / biased variance from the summed array and n_rows_total, running statistics
+ * updated as in training mode (every device computes the same values), this device's rows normalised.
+ * n_rows_total = -1 (here and in scn_batchnorm_backward_sums_apply): the total row count is the device double
+ * behind the array, sums[2C] / total_sums[2C], which the caller summed over the devices along with it; the host
+ * then never waits for the count. */
+SCN_API int scn_batchnorm_moments(const float *in_features, int64_t n_rows, int n_planes, int64_t in_stride,
+                                  double *sums, void *stream);
+SCN_API int scn_batchnorm_forward_moments(const float *in_features, float *out_features, int64_t n_rows,
+                                          int64_t n_rows_total, int n_planes, int64_t in_stride,
+                                          int64_t out_stride, const double *sums, float *save_mean,
+                                          float *save_invstd, float *running_mean, float *running_var,
+                                          const float *weight, const float *bias, double eps, double momentum,
+                                          double leakiness, void *stream);
+/* scn_batchnorm_backward_sums: sums[0..C) = sum of d, sums[C..2C) = sum of (x - mean) d over this device's rows,
+ * d = d_out scaled by the leaky ReLU's slope (device doubles, overwritten).
+ * scn_batchnorm_backward_sums_apply: d_in of this device's rows from the sums over all devices (total_sums,
+ * n_rows_total); d_weight / d_bias (may be NULL) from this device's own sums (local_sums), so that adding the
+ * parameter gradients of all devices, as for every other parameter, gives the gradient of the whole batch. */
+SCN_API int scn_batchnorm_backward_sums(const float *in_features, const float *out_features,
+                                        const float *d_out_features, int64_t n_rows, int n_planes,
+                                        int64_t in_stride, int64_t out_stride, const float *save_mean,
+                                        double leakiness, double *sums, void *stream);
+SCN_API int scn_batchnorm_backward_sums_apply(const float *in_features, float *d_in_features,
+                                              const float *out_features, const float *d_out_features,
+                                              int64_t n_rows, int64_t n_rows_total, int n_planes,
+                                              int64_t in_stride, int64_t out_stride, const float *save_mean,
+                                              const float *save_invstd, const float *weight,
+                                              const double *local_sums, const double *total_sums,
+                                              float *d_weight, float *d_bias, double leakiness, void *stream);
+
 /* replaces MaxPooling_updateOutput (sparseconvnet.h:198-201; CPU/MaxPooling.cpp:7-60):
  * out[o] = max(0, max over rules of in[i]) on planes n_features_to_drop .. n_planes_in-1.
  * out [n_active_out, n_planes_in - n_features_to_drop]. */

@@ -946,6 +946,69 @@ def BatchNormalization_backward(input_features, d_input_features, output_feature
             _ptr(w), _ptr(d_weight), _ptr(d_bias), float(leakiness), _stream()))
 
 
+def _sum_over_ranks(t, group):
+    import torch.distributed as dist
+    dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
+
+
+def BatchNormalization_updateOutput_acrossRanks(input_features, output_features, saveMean, saveInvStd, runningMean,
+                                                runningVar, weight, bias, eps, momentum, leakiness, group=None,
+                                                reduce=_sum_over_ranks):
+    """Training-mode BatchNormalization_updateOutput (CPU/BatchNormalization.cpp:12-62) whose statistics cover the
+    rows of every rank of `group`: each rank sums its rows, one all-reduce of 2 x planes + 1 doubles adds the sums
+    and the row counts, every rank normalises its own rows with the shared mean and variance and makes the same
+    update of the running statistics.  Not in the reference (single device).  A rank without rows takes part in
+    the all-reduce.  `reduce(tensor, group)` adds a tensor over the ranks in place.  The host never reads the
+    total row count: it stays on the device, behind the sums.  Returns the summed array (the backward call
+    wants it for the count)."""
+    f = input_features
+    if not f.is_cuda or f.dtype != torch.float32 or f.dim() != 2 or (f.numel() and f.stride(1) != 1):
+        raise RuntimeError("input_features must be a CUDA float32 matrix with unit column stride")
+    n, c = f.size(0), f.size(1)
+    with _on_device(f.device):
+        output_features.resize_(n, c)
+        saveMean.resize_(c)
+        saveInvStd.resize_(c)
+        sums = torch.empty(2 * c + 1, dtype=torch.float64, device=f.device)
+        sums[2 * c] = n
+        check(lib.scn_batchnorm_moments(_ptr(f), n, c, f.stride(0) if n else c, _ptr(sums), _stream()))
+        reduce(sums, group)
+        w = _optional(weight, f, "weight")
+        b = _optional(bias, f, "bias")
+        check(lib.scn_batchnorm_forward_moments(
+            _ptr(f), _ptr(output_features), n, -1, c, f.stride(0) if n else c,
+            output_features.stride(0) if n else c, _ptr(sums), _ptr(saveMean), _ptr(saveInvStd),
+            _ptr(_features(runningMean, "runningMean")), _ptr(_features(runningVar, "runningVar")), _ptr(w), _ptr(b),
+            float(eps), float(momentum), float(leakiness), _stream()))
+    return sums
+
+
+def BatchNormalization_backward_acrossRanks(input_features, d_input_features, output_features, d_output_features,
+                                            saveMean, saveInvStd, weight, d_weight, d_bias, leakiness, forward_sums,
+                                            group=None, reduce=_sum_over_ranks):
+    """Backward of BatchNormalization_updateOutput_acrossRanks (the formula of CPU/BatchNormalization.cpp:64-107
+    with the two sums taken over all ranks).  d_weight / d_bias receive THIS rank's share, so that summing the
+    parameter gradients over the ranks, as for every other parameter, gives the gradient of the whole batch.
+    `forward_sums`: what the forward call returned."""
+    f = input_features
+    n, c = f.size(0), f.size(1)
+    d_input_features.resize_(n, c)
+    w = _optional(weight, f, "weight")
+    with _on_device(f.device):
+        local = torch.empty(2 * c + 1, dtype=torch.float64, device=f.device)
+        check(lib.scn_batchnorm_backward_sums(
+            _ptr(f), _ptr(output_features), _ptr(d_output_features), n, c, f.stride(0) if n else c,
+            output_features.stride(0) if n else c, _ptr(saveMean), float(leakiness), _ptr(local), _stream()))
+        local[2 * c] = 0
+        total = local.clone()
+        reduce(total, group)
+        total[2 * c] = forward_sums[2 * c]
+        check(lib.scn_batchnorm_backward_sums_apply(
+            _ptr(f), _ptr(d_input_features), _ptr(output_features), _ptr(d_output_features), n, -1, c,
+            f.stride(0) if n else c, output_features.stride(0) if n else c, _ptr(saveMean), _ptr(saveInvStd),
+            _ptr(w), _ptr(local), _ptr(total), _ptr(d_weight), _ptr(d_bias), float(leakiness), _stream()))
+
+
 def InputLayer_updateGradInput(m, d_input_features, d_output_features):
     """CPU/IOLayers.cpp:74-93 (and BLInputLayer_updateGradInput, :165-186, reshaped by the caller)."""
     go = _features(d_output_features, "d_output_features")

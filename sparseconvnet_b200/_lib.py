@@ -99,6 +99,14 @@ SIGNATURES = {
     "scn_batchnorm_forward": (C.c_int, [_vp, _vp, C.c_int64, C.c_int, C.c_int64, C.c_int64, _vp, _vp,
                                         _vp, _vp, _vp, _vp, C.c_double, C.c_double, C.c_int,
                                         C.c_double, _vp]),
+    "scn_batchnorm_moments": (C.c_int, [_vp, C.c_int64, C.c_int, C.c_int64, _vp, _vp]),
+    "scn_batchnorm_forward_moments": (C.c_int, [_vp, _vp, C.c_int64, C.c_int64, C.c_int, C.c_int64, C.c_int64, _vp,
+                                                _vp, _vp, _vp, _vp, _vp, _vp, C.c_double, C.c_double, C.c_double,
+                                                _vp]),
+    "scn_batchnorm_backward_sums": (C.c_int, [_vp, _vp, _vp, C.c_int64, C.c_int, C.c_int64, C.c_int64, _vp,
+                                              C.c_double, _vp, _vp]),
+    "scn_batchnorm_backward_sums_apply": (C.c_int, [_vp, _vp, _vp, _vp, C.c_int64, C.c_int64, C.c_int, C.c_int64,
+                                                    C.c_int64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_double, _vp]),
     "scn_max_pooling_forward": (C.c_int, [_vp, _i64p, _i64p, _i64p, _i64p, _vp, _vp, C.c_int, C.c_int,
                                           _vp]),
     "scn_average_pooling_forward": (C.c_int, [_vp, _i64p, _i64p, _i64p, _i64p, _vp, _vp, C.c_int, C.c_int,

@@ -94,6 +94,41 @@ def batchnorm(features, weight, bias, running_mean, running_var, eps, momentum, 
     return _BatchNorm.apply(features, weight, bias, running_mean, running_var, eps, momentum, train, leakiness)
 
 
+class _BatchNormAcrossRanks(torch.autograd.Function):
+    """Training-mode BatchNorm whose statistics cover the rows of every rank of a process group (data-parallel
+    training): one small all-reduce in the forward pass, one in the backward pass."""
+
+    @staticmethod
+    def forward(ctx, features, weight, bias, running_mean, running_var, eps, momentum, leakiness, group):
+        features = features.contiguous()
+        out = features.new_empty(0)
+        save_mean = features.new_empty(features.size(1))
+        save_invstd = features.new_empty(features.size(1))
+        sums = SCN.BatchNormalization_updateOutput_acrossRanks(features, out, save_mean, save_invstd, running_mean,
+                                                               running_var, weight, bias, eps, momentum, leakiness,
+                                                               group)
+        ctx.save_for_backward(features, out, weight, bias, save_mean, save_invstd, sums)
+        ctx.leakiness, ctx.group = leakiness, group
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        features, out, weight, bias, save_mean, save_invstd, sums = ctx.saved_tensors
+        grad_out = grad_out.contiguous()
+        d_in = grad_out.new_empty(0)
+        affine = weight.numel() > 0
+        d_w = torch.empty_like(weight) if affine else None
+        d_b = torch.empty_like(bias) if affine else None
+        SCN.BatchNormalization_backward_acrossRanks(features, d_in, out, grad_out, save_mean, save_invstd,
+                                                    weight.detach(), d_w, d_b, ctx.leakiness, sums, ctx.group)
+        return d_in, d_w, d_b, None, None, None, None, None, None
+
+
+def batchnorm_across_ranks(features, weight, bias, running_mean, running_var, eps, momentum, leakiness, group):
+    return _BatchNormAcrossRanks.apply(features, weight, bias, running_mean, running_var, eps, momentum, leakiness,
+                                       group)
+
+
 class _Pooling(torch.autograd.Function):
     """kind: 'max' | 'avg' | 'unpool'."""
 

@@ -92,9 +92,14 @@ k_bn_stats(const float *__restrict__ in, long long n_rows, int C, long long in_s
 // normalising variance is biased, the running variance unbiased (CPU/BatchNormalization.cpp:32-46).
 __global__ void k_bn_finalize(int C, long long n_rows, const double *__restrict__ sums,
                               float *save_mean, float *save_invstd, float *running_mean,
-                              float *running_var, float eps, float momentum, int train) {
+                              float *running_var, float eps, float momentum, int train,
+                              int count_follows_sums = 0) {
   int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= C) return;
+  if (count_follows_sums) {  // the row count of all devices, summed along with the array
+    n_rows = (long long)sums[2 * C];
+    if (n_rows == 0) return;
+  }
   if (train) {
     double mean = sums[c] / (double)n_rows;
     double ss = sums[C + c] - mean * mean * (double)n_rows;
@@ -235,6 +240,37 @@ __global__ void k_bn_back_finalize(const double *__restrict__ partial, int chunk
   if (d_weight) d_weight[c] = (float)q * is;
   coef[c] = (float)(s / (double)n_rows);                      // gradMean
   coef[C + c] = (float)(q * (double)is * (double)is / (double)n_rows);  // k
+}
+
+// The two-phase form of the backward pass (rows spread over several devices): the chunk sums of one device
+// added in their fixed order ...
+__global__ void k_bn_back_reduce(const double *__restrict__ partial, int chunks, int C, double *__restrict__ sums) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  double s = 0.0, q = 0.0;
+  for (int i = 0; i < chunks; ++i) {
+    s += partial[((long long)i * 2 + 0) * C + c];
+    q += partial[((long long)i * 2 + 1) * C + c];
+  }
+  sums[c] = s;
+  sums[C + c] = q;
+}
+
+// ... and, once the caller has added the devices' sums, the coefficients of k_bn_back_apply from the totals and
+// the parameter gradients from this device's own sums (the same expressions as k_bn_back_finalize).
+__global__ void k_bn_back_coef(const double *__restrict__ local, const double *__restrict__ total, int C,
+                               long long n_rows_total, const float *__restrict__ invstd,
+                               float *__restrict__ d_weight, float *__restrict__ d_bias,
+                               float *__restrict__ coef /* [2][C] */) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  if (n_rows_total < 0) n_rows_total = (long long)total[2 * C];  // summed along with the array
+  if (n_rows_total == 0) n_rows_total = 1;                        // no rows anywhere: all sums are zero
+  const float is = invstd[c];
+  if (d_bias) d_bias[c] = (float)local[c];
+  if (d_weight) d_weight[c] = (float)local[C + c] * is;
+  coef[c] = (float)(total[c] / (double)n_rows_total);
+  coef[C + c] = (float)(total[C + c] * (double)is * (double)is / (double)n_rows_total);
 }
 
 __global__ void __launch_bounds__(256)
@@ -683,6 +719,108 @@ int scn_batchnorm_backward(const float *in_features, float *d_in_features, const
   SCN_CUDA_CHECK(cudaGetLastError());
   SCN_TRY(device_free(partial, stream));
   SCN_TRY(device_free(coef, stream));
+  return SCN_OK;
+}
+
+static void launch_bn_apply(const float *in, float *out, long long n_rows, int n_planes, long long in_stride,
+                            long long out_stride, float *save_mean, float *save_invstd, const float *weight,
+                            const float *bias, float leakiness, cudaStream_t stream) {
+  const bool vec4 = (n_planes % 4 == 0) && (in_stride % 4 == 0) && (out_stride % 4 == 0) &&
+                    ((uintptr_t)in % 16 == 0) && ((uintptr_t)out % 16 == 0);
+  const long long work = n_rows * (vec4 ? n_planes / 4 : n_planes);
+  const unsigned blocks = (unsigned)std::min<long long>(ceil_div(work, 256), 148 * 16);
+  const size_t smem = sizeof(float) * 2 * n_planes;
+  if (vec4)
+    SCN_LAUNCH(k_bn_apply<4>, blocks, 256, smem, stream, in, out, n_rows, n_planes, in_stride, out_stride, save_mean, save_invstd, nullptr, nullptr, 0.f, weight, bias, leakiness);
+  else
+    SCN_LAUNCH(k_bn_apply<1>, blocks, 256, smem, stream, in, out, n_rows, n_planes, in_stride, out_stride, save_mean, save_invstd, nullptr, nullptr, 0.f, weight, bias, leakiness);
+}
+
+int scn_batchnorm_moments(const float *in_features, int64_t n_rows, int n_planes, int64_t in_stride, double *sums,
+                          void *stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SCN_REQUIRE(n_planes >= 1 && n_planes <= 4096, SCN_ERR_UNSUPPORTED, "n_planes %d unsupported", n_planes);
+  SCN_REQUIRE(sums && n_rows >= 0, SCN_ERR_BAD_ARG, "null sums or negative row count");
+  SCN_REQUIRE(in_stride >= n_planes, SCN_ERR_BAD_ARG, "row stride below n_planes");
+  SCN_CUDA_CHECK(cudaMemsetAsync(sums, 0, sizeof(double) * 2 * n_planes, stream));
+  if (n_rows == 0) return SCN_OK;
+  SCN_REQUIRE(in_features, SCN_ERR_BAD_ARG, "null features");
+  const unsigned gy = (unsigned)std::min<long long>(ceil_div(n_rows, 64), 1024);
+  SCN_LAUNCH(k_bn_stats, dim3((unsigned)ceil_div(n_planes, 32), gy), 256, 0, stream, in_features, n_rows, n_planes, in_stride, sums);
+  SCN_CUDA_CHECK(cudaGetLastError());
+  return SCN_OK;
+}
+
+int scn_batchnorm_forward_moments(const float *in_features, float *out_features, int64_t n_rows,
+                                  int64_t n_rows_total, int n_planes, int64_t in_stride, int64_t out_stride,
+                                  const double *sums, float *save_mean, float *save_invstd, float *running_mean,
+                                  float *running_var, const float *weight, const float *bias, double eps,
+                                  double momentum, double leakiness, void *stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SCN_REQUIRE(n_planes >= 1 && n_planes <= 4096, SCN_ERR_UNSUPPORTED, "n_planes %d unsupported", n_planes);
+  SCN_REQUIRE(sums && save_mean && save_invstd && running_mean && running_var, SCN_ERR_BAD_ARG, "null statistics");
+  SCN_REQUIRE(in_stride >= n_planes && out_stride >= n_planes, SCN_ERR_BAD_ARG, "row stride below n_planes");
+  SCN_REQUIRE(n_rows >= 0 && (n_rows_total < 0 || n_rows_total >= n_rows), SCN_ERR_BAD_ARG,
+              "total row count below this device's");
+  if (n_rows_total == 0) return SCN_OK;
+  SCN_LAUNCH(k_bn_finalize, (unsigned)ceil_div(n_planes, 128), 128, 0, stream, n_planes, (long long)n_rows_total, sums, save_mean, save_invstd, running_mean, running_var, (float)eps, (float)momentum, 1, n_rows_total < 0 ? 1 : 0);
+  if (n_rows > 0) {
+    SCN_REQUIRE(in_features && out_features, SCN_ERR_BAD_ARG, "null features");
+    launch_bn_apply(in_features, out_features, n_rows, n_planes, in_stride, out_stride, save_mean, save_invstd, weight, bias, (float)leakiness, stream);
+  }
+  SCN_CUDA_CHECK(cudaGetLastError());
+  return SCN_OK;
+}
+
+int scn_batchnorm_backward_sums(const float *in_features, const float *out_features, const float *d_out_features,
+                                int64_t n_rows, int n_planes, int64_t in_stride, int64_t out_stride,
+                                const float *save_mean, double leakiness, double *sums, void *stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SCN_REQUIRE(n_planes >= 1 && n_planes <= 4096, SCN_ERR_UNSUPPORTED, "n_planes %d unsupported", n_planes);
+  SCN_REQUIRE(sums && save_mean && n_rows >= 0, SCN_ERR_BAD_ARG, "null sums or statistics");
+  SCN_REQUIRE(in_stride >= n_planes && out_stride >= n_planes, SCN_ERR_BAD_ARG, "row stride below n_planes");
+  if (n_rows == 0) {
+    SCN_CUDA_CHECK(cudaMemsetAsync(sums, 0, sizeof(double) * 2 * n_planes, stream));
+    return SCN_OK;
+  }
+  SCN_REQUIRE(in_features && out_features && d_out_features, SCN_ERR_BAD_ARG, "null features");
+  const int chunks = (int)std::max<long long>(1, std::min<long long>(1024, n_rows / 256));
+  const long long chunk_rows = ceil_div(n_rows, chunks);
+  double *partial = nullptr;
+  SCN_TRY(device_alloc((void **)&partial, sizeof(double) * 2 * (size_t)chunks * n_planes, stream));
+  SCN_LAUNCH(k_bn_back_sums, dim3((unsigned)ceil_div(n_planes, 32), (unsigned)chunks), 256, 0, stream, in_features, out_features, d_out_features, (long long)n_rows, n_planes, (long long)in_stride, (long long)out_stride, save_mean, (float)leakiness, chunk_rows, partial);
+  SCN_LAUNCH(k_bn_back_reduce, (unsigned)ceil_div(n_planes, 128), 128, 0, stream, partial, chunks, n_planes, sums);
+  const cudaError_t err = cudaGetLastError();
+  SCN_TRY(device_free(partial, stream));
+  SCN_CUDA_CHECK(err);
+  return SCN_OK;
+}
+
+int scn_batchnorm_backward_sums_apply(const float *in_features, float *d_in_features, const float *out_features,
+                                      const float *d_out_features, int64_t n_rows, int64_t n_rows_total,
+                                      int n_planes, int64_t in_stride, int64_t out_stride, const float *save_mean,
+                                      const float *save_invstd, const float *weight, const double *local_sums,
+                                      const double *total_sums, float *d_weight, float *d_bias, double leakiness,
+                                      void *stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SCN_REQUIRE(n_planes >= 1 && n_planes <= 4096, SCN_ERR_UNSUPPORTED, "n_planes %d unsupported", n_planes);
+  SCN_REQUIRE(save_mean && save_invstd && local_sums && total_sums, SCN_ERR_BAD_ARG, "null statistics or sums");
+  SCN_REQUIRE(in_stride >= n_planes && out_stride >= n_planes, SCN_ERR_BAD_ARG, "row stride below n_planes");
+  SCN_REQUIRE(n_rows >= 0 && (n_rows_total < 0 || (n_rows_total >= n_rows && n_rows_total >= 1)), SCN_ERR_BAD_ARG,
+              "total row count below this device's, or no rows at all");
+  float *coef = nullptr;
+  SCN_TRY(device_alloc((void **)&coef, sizeof(float) * 2 * (size_t)n_planes, stream));
+  SCN_LAUNCH(k_bn_back_coef, (unsigned)ceil_div(n_planes, 128), 128, 0, stream, local_sums, total_sums, n_planes, (long long)n_rows_total, save_invstd, d_weight, d_bias, coef);
+  if (n_rows > 0) {
+    if (!(in_features && d_in_features && out_features && d_out_features)) {
+      device_free(coef, stream);
+      SCN_REQUIRE(false, SCN_ERR_BAD_ARG, "null features");
+    }
+    SCN_LAUNCH(k_bn_back_apply, (unsigned)ceil_div(n_rows * n_planes, 256), 256, 0, stream, in_features, d_in_features, out_features, d_out_features, (long long)n_rows, n_planes, (long long)in_stride, (long long)out_stride, save_mean, save_invstd, weight, coef, (float)leakiness);
+  }
+  const cudaError_t err = cudaGetLastError();
+  SCN_TRY(device_free(coef, stream));
+  SCN_CUDA_CHECK(err);
   return SCN_OK;
 }
 

@@ -385,7 +385,29 @@ class BatchNormalization(Module):
         output.features = features
         return output
 
+    # Data-parallel training: with `across_ranks` the training-mode statistics cover the rows of every rank of
+    # `ranks_group` (shard.share_batchnorm_statistics sets both on all layers of a network).
+    across_ranks = False
+    ranks_group = None
+
+    def _shares_statistics(self):
+        if not (self.training and self.across_ranks):
+            return False
+        import torch.distributed as dist
+        return dist.is_available() and dist.is_initialized() and dist.get_world_size(self.ranks_group) > 1
+
     def forward(self, input):
+        if self._shares_statistics():  # a rank without rows still takes part in the exchange
+            features = input.features
+            if features.dim() != 2:
+                features = features.new_zeros(0, self.nPlanes)
+            assert features.size(1) == self.nPlanes, (self.nPlanes, features.shape)
+            output = SparseConvNetTensor(metadata=input.metadata, spatial_size=input.spatial_size)
+            dev = features.device
+            output.features = autograd.batchnorm_across_ranks(
+                features, optional_tensor(self, "weight").to(dev), optional_tensor(self, "bias").to(dev),
+                self.running_mean, self.running_var, self.eps, self.momentum, self.leakiness, self.ranks_group)
+            return output
         if input.features.nelement() == 0:
             return input
         assert input.features.size(1) == self.nPlanes, (self.nPlanes, input.features.shape)

@@ -1,4 +1,5 @@
-"""Data-parallel inference: the minibatch shards by batch index, one process per GPU.
+"""Data-parallel inference (and, at the end of this file, training): the minibatch shards by batch index, one
+process per GPU.
 
 Each rank keeps a contiguous range of samples, builds its own Metadata (site hash and
 rulebooks never cross ranks: no operator mixes rows of different samples, and inference-mode
@@ -202,3 +203,64 @@ class _PendingBlocks(object):
         if all(c == self.cap for c in counts):
             return self.buf, counts
         return torch.cat(views), counts
+
+
+# ---- data-parallel training ----------------------------------------------------------------------
+#
+# Every rank runs forward and backward on its own samples.  Two things cross ranks: the training-mode
+# BatchNorm statistics (share_batchnorm_statistics: one all-reduce of 2 x planes + 1 doubles per layer and
+# direction) and the parameter gradients (sum_gradients: a few large all-reduces after the backward pass).
+# With a loss that every rank divides by the TOTAL number of rows (or samples), the summed gradients are those
+# of the whole batch on one device.  The reference has no multi-GPU path.
+
+def share_batchnorm_statistics(module, group=None):
+    """Every BatchNormalization layer under `module` takes its training-mode statistics over the rows of all
+    ranks of `group` from now on (eval mode is unchanged: running statistics).  Returns `module`."""
+    from .layers import BatchNormalization
+    for m in module.modules():
+        if isinstance(m, BatchNormalization):
+            m.across_ranks = True
+            m.ranks_group = group
+    return module
+
+
+def sum_gradients(parameters, group=None, bucket_bytes=64 << 20, scale=None):
+    """Adds the gradients of `parameters` over the ranks of `group`, in place, through flat buckets of at most
+    `bucket_bytes` (one all-reduce each, all enqueued before the first result is unpacked).  A parameter without
+    a gradient on this rank (a rank whose shard was empty) counts as zeros and receives the sum, so that every
+    rank packs the same layout; parameters that need no gradient are skipped.  `scale` multiplies the sums
+    (1 / world for an average).  Returns the number of all-reduces."""
+    params = [p for p in parameters if p.requires_grad]
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        if scale is not None:
+            for p in params:
+                if p.grad is not None:
+                    p.grad.mul_(scale)
+        return 0
+    buckets, current, size = [], [], 0
+    for p in params:
+        nbytes = p.numel() * p.element_size()
+        if current and (size + nbytes > bucket_bytes or p.dtype != current[0].dtype or p.device != current[0].device):
+            buckets.append(current)
+            current, size = [], 0
+        current.append(p)
+        size += nbytes
+    if current:
+        buckets.append(current)
+    pending = []
+    for bucket in buckets:
+        flat = torch.cat([(p.grad if p.grad is not None else torch.zeros_like(p)).reshape(-1) for p in bucket])
+        pending.append((bucket, flat, dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group, async_op=True)))
+    for bucket, flat, work in pending:
+        work.wait()
+        if scale is not None:
+            flat.mul_(scale)
+        at = 0
+        for p in bucket:
+            part = flat[at:at + p.numel()].view_as(p)
+            at += p.numel()
+            if p.grad is None:
+                p.grad = part.clone()
+            else:
+                p.grad.copy_(part)
+    return len(buckets)

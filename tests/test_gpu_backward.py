@@ -149,6 +149,81 @@ def test_batchnorm_gradients(ref, cuda, leak, affine, train):
         assert _rel(m.weight.grad, gw) <= TOL and _rel(m.bias.grad, gb) <= TOL
 
 
+@pytest.mark.parametrize("leak,affine", [(0.0, True), (0.333, True), (1.0, False)])
+def test_batchnorm_statistics_over_several_ranks(ref, cuda, leak, affine):
+    """Training-mode BatchNorm with its rows spread over three ranks (one of them without rows): the two-phase
+    entry points with the ranks' sums added in between give what the reference gives for the whole matrix on one
+    device (CPU/BatchNormalization.cpp:12-107) -- outputs, running statistics, d_input, and parameter gradients
+    once the ranks' shares are added.  The ranks run one after the other here; the all-reduce is stood in for by
+    a function that returns the sum of what every rank contributed."""
+    from sparseconvnet_b200 import SCN
+    rng = np.random.default_rng(15)
+    n, c = 1900, 12
+    feats = (rng.standard_normal((n, c)) * 2 + 0.5).astype(np.float32)
+    go = rng.standard_normal((n, c)).astype(np.float32)
+    cuts = [(0, 1200), (1200, 1900), (1900, 1900)]
+    w = torch.from_numpy(rng.uniform(0.5, 1.5, c).astype(np.float32)) if affine else torch.empty(0)
+    b = torch.from_numpy(rng.standard_normal(c).astype(np.float32)) if affine else torch.empty(0)
+    rm0 = torch.from_numpy(rng.standard_normal(c).astype(np.float32))
+    rv0 = torch.from_numpy(rng.uniform(0.5, 2.0, c).astype(np.float32))
+
+    def forward(reduce):
+        res = []
+        for lo, hi in cuts:
+            f = torch.from_numpy(feats[lo:hi]).to(cuda)
+            out, sm, si = f.new_empty(0), f.new_empty(c), f.new_empty(c)
+            rm, rv = rm0.clone().to(cuda), rv0.clone().to(cuda)
+            sums = SCN.BatchNormalization_updateOutput_acrossRanks(f, out, sm, si, rm, rv, w.to(cuda), b.to(cuda), 1e-4,
+                                                                   0.9, leak, reduce=reduce)
+            res.append((f, out, sm, si, rm, rv, sums))
+        return res
+
+    def backward(fwd, reduce):
+        res = []
+        for (lo, hi), (f, out, sm, si, rm, rv, sums) in zip(cuts, fwd):
+            g = torch.from_numpy(go[lo:hi]).to(cuda)
+            d_in = f.new_empty(0)
+            dw = torch.zeros(c, device=cuda) if affine else None
+            db = torch.zeros(c, device=cuda) if affine else None
+            SCN.BatchNormalization_backward_acrossRanks(f, d_in, out, g, sm, si, w.to(cuda), dw, db, leak, sums,
+                                                        reduce=reduce)
+            res.append((d_in, dw, db))
+        return res
+
+    parts = []
+    forward(lambda t, g: parts.append(t.clone()))
+    assert len(parts) == 3 and parts[2][:2 * c].abs().max().item() == 0 and parts[0][2 * c].item() == 1200
+    total = sum(parts)
+    fwd = forward(lambda t, g: t.copy_(total))
+    parts_b = []
+    backward(fwd, lambda t, g: parts_b.append(t.clone()))
+    total_b = sum(parts_b)
+    bwd = backward(fwd, lambda t, g: t.copy_(total_b))
+
+    fin = torch.from_numpy(feats)
+    out, sm, si = torch.empty(0), torch.empty(c), torch.empty(c)
+    rm, rv = rm0.clone(), rv0.clone()
+    ref.BatchNormalization_updateOutput(fin, out, sm, si, rm, rv, w, b, 1e-4, 0.9, True, leak)
+    gi, gw, gb = torch.empty(0), torch.zeros_like(w), torch.zeros_like(b)
+    ref.BatchNormalization_backward(fin, gi, out, torch.from_numpy(go).clone(), sm, si, rm, rv, w, b, gw, gb, leak)
+    assert fwd[2][1].shape == (0, c) and bwd[2][0].shape == (0, c)
+    assert _rel(torch.cat([r[1] for r in fwd]), out) <= TOL
+    assert _rel(torch.cat([r[0] for r in bwd]), gi) <= TOL
+    for r in fwd:   # every rank, the one without rows too, keeps the same running statistics
+        assert _rel(r[4], rm) <= TOL and _rel(r[5], rv) <= TOL and _rel(r[2], sm) <= TOL and _rel(r[3], si) <= TOL
+    if affine:
+        assert _rel(sum(r[1] for r in bwd), gw) <= TOL and _rel(sum(r[2] for r in bwd), gb) <= TOL
+    # one rank holding everything: the two phases are the one-call operator
+    f = torch.from_numpy(feats).to(cuda)
+    one, sm1, si1 = f.new_empty(0), f.new_empty(c), f.new_empty(c)
+    SCN.BatchNormalization_updateOutput(f, one, sm1, si1, rm0.clone().to(cuda), rv0.clone().to(cuda), w.to(cuda),
+                                        b.to(cuda), 1e-4, 0.9, True, leak)
+    two, sm2, si2 = f.new_empty(0), f.new_empty(c), f.new_empty(c)
+    SCN.BatchNormalization_updateOutput_acrossRanks(f, two, sm2, si2, rm0.clone().to(cuda), rv0.clone().to(cuda),
+                                                    w.to(cuda), b.to(cuda), 1e-4, 0.9, leak, reduce=lambda t, g: None)
+    assert _rel(two, one) <= 1e-6 and _rel(sm2, sm1) <= 1e-6 and _rel(si2, si1) <= 1e-6
+
+
 @pytest.mark.parametrize("kind", ["max", "avg", "unpool"])
 @pytest.mark.parametrize("dim,size,f,s", [(2, [17, 17], 3, 2), (3, [16, 16, 16], 2, 2)])
 def test_pooling_gradients(ref, cuda, kind, dim, size, f, s):

@@ -125,3 +125,37 @@ def test_rank_that_dies_gives_a_clean_error(tmp_path):
         outcome = f.read()
     assert outcome.startswith("error after"), outcome
     assert float(outcome.split()[2]) < 30.0
+
+
+def _gradient_worker(rank, world, port_no, tmp):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port_no)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from sparseconvnet_b200 import shard
+    shapes = [(7, 5), (3,), (4, 4, 2), (11,), (2, 3)]
+    params = [torch.nn.Parameter(torch.zeros(s)) for s in shapes]
+    params[3].requires_grad_(False)                       # skipped altogether
+    for i, p in enumerate(params):
+        if p.requires_grad and not (rank == 1 and i == 1):  # rank 1 has no gradient for parameter 1 (empty shard)
+            p.grad = torch.full(p.shape, float(10 * (rank + 1) + i))
+    n = shard.sum_gradients(params, bucket_bytes=100)     # several buckets
+    assert n >= 2
+    for i, p in enumerate(params):
+        if not p.requires_grad:
+            assert p.grad is None
+            continue
+        want = (10 + i) + (0 if i == 1 else 20 + i)
+        assert torch.equal(p.grad, torch.full(p.shape, float(want))), (i, p.grad)
+    shard.sum_gradients(params, scale=0.5)                # one bucket, averaged
+    assert torch.equal(params[0].grad, torch.full((7, 5), 30.0))
+    if rank == 0:
+        np.save(os.path.join(tmp, "grads_ok.npy"), np.array([1.0]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_ranks_sum_their_gradients(tmp_path):
+    port_no = 31500 + os.getpid() % 2000
+    mp.spawn(_gradient_worker, args=(2, port_no, str(tmp_path)), nprocs=2, join=True)
+    assert os.path.exists(os.path.join(str(tmp_path), "grads_ok.npy"))
