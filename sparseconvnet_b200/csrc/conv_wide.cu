@@ -77,6 +77,7 @@ struct WideParams {
   int K, cin, cout;
   int n_stages;
   long long n_tiles;
+  int tile_rows;  // output rows per tile (the MMA's N): a multiple of 16, at most the kernel's ROWS
   int *flags;
 };
 
@@ -146,6 +147,9 @@ __global__ void __launch_bounds__((PW + 5) * 32, 1) k_conv_wide(WideParams P) {
   const unsigned tmem_base = *sh_tmem;
   const long long my_tiles =
       ((long long)blockIdx.x < P.n_tiles) ? (P.n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  // Rows per tile: the shared-memory and TMEM layouts are those of ROWS rows; a launch may use fewer (the host
+  // picks the height that gives every SM the same number of tiles), then the tail of each buffer stays unused.
+  const int TR = P.tile_rows;
 
   if (warp < kWProducerWarps) {
     // =============================== producers: copy the gathered rows ==========================
@@ -170,8 +174,8 @@ __global__ void __launch_bounds__((PW + 5) * 32, 1) k_conv_wide(WideParams P) {
       return __shfl_sync(0xffffffffu, freed, 0) != 0;
     };
     auto entry = [&](long long tile, int k) -> int {
-      const long long r = tile * kWRows + tid;
-      return (tid < kWRows && tile < P.n_tiles && r < P.n_out) ? __ldg(P.nbr + (long long)k * P.n_out + r) : -1;
+      const long long r = tile * TR + tid;
+      return (tid < TR && tile < P.n_tiles && r < P.n_out) ? __ldg(P.nbr + (long long)k * P.n_out + r) : -1;
     };
     // flattened (tile, offset) walk with a two-deep prefetch of the row owner's rulebook entry
     long long tile_a = blockIdx.x;
@@ -217,8 +221,9 @@ __global__ void __launch_bounds__((PW + 5) * 32, 1) k_conv_wide(WideParams P) {
           for (int i = 0; i < kWItems; ++i) {
             const int it = tid + i * kWProducers;
             const int r = (it >> 2) & (kWRows - 1), j = it & 3;
-            const int v = it < kWRows * 4 ? ent[par * kWRows + r] : -1;
-            off[i] = it < kWRows * 4 ? (unsigned)j * kWLbo + (unsigned)r * 16u : 0xFFFFFFFFu;
+            const bool in_tile = it < kWRows * 4 && r < TR;
+            const int v = in_tile ? ent[par * kWRows + r] : -1;
+            off[i] = in_tile ? (unsigned)j * kWLbo + (unsigned)r * 16u : 0xFFFFFFFFu;
             size[i] = v >= 0 ? 16u : 0u;
             src[i] = P.in_split + (v >= 0 ? (size_t)v * P.ld_in * 4 : 0) + j * 16;
           }
@@ -282,7 +287,7 @@ __global__ void __launch_bounds__((PW + 5) * 32, 1) k_conv_wide(WideParams P) {
   } else if (warp == kWMmaWarp) {
     // ==================================== MMA issue (one thread) ===============================
     if (lane == 0) {
-      const unsigned idesc = wide_idesc(kWRows);
+      const unsigned idesc = wide_idesc(TR);
       const unsigned stage0 = smem_u32(smem);
       int st = 0, round = 0;
       bool ok = true;
@@ -364,7 +369,8 @@ __global__ void __launch_bounds__((PW + 5) * 32, 1) k_conv_wide(WideParams P) {
         break;
       }
       tc_fence_after();
-      const long long row0 = (blockIdx.x + t * gridDim.x) * kWRows;
+      const long long row0 = (blockIdx.x + t * gridDim.x) * TR;
+      const long long row_end = min(P.n_out, row0 + TR);
       for (int mt = 0; mt < n_mt; ++mt) {
         const int plane0 = mt * kWPlanes + quad * 32;
         if (plane0 >= P.cout) break;
@@ -374,15 +380,15 @@ __global__ void __launch_bounds__((PW + 5) * 32, 1) k_conv_wide(WideParams P) {
         const float sc = (P.bn_scale && plane_ok) ? P.bn_scale[plane] : 1.f;
         const float sh = (P.bn_scale && plane_ok) ? P.bn_shift[plane] : 0.f;
         const float leak = P.leak;
-        for (int n0 = 0; n0 < kWRows; n0 += 32) {
-          if (row0 + n0 >= P.n_out) break;
+        for (int n0 = 0; n0 < TR; n0 += 32) {
+          if (row0 + n0 >= row_end) break;
           float v[32];
           tmem_ld32(tmem_base + ((unsigned)(quad * 32) << 16) + (unsigned)((ab * n_mt + mt) * kWRows + n0), v);
           if (plane_ok) {
             float *dst = P.out + (row0 + n0) * P.ld_out + plane;
 #pragma unroll
             for (int i = 0; i < 32; ++i)
-              if (row0 + n0 + i < P.n_out) {
+              if (row0 + n0 + i < row_end) {
                 float y = v[i] + b;
                 if (P.bn_scale) {  // separate multiply and add, as the stand-alone BatchNorm kernel rounds them
                   y = __fadd_rn(__fmul_rn(y, sc), sh);
@@ -541,7 +547,6 @@ int conv_forward_wide(const float *in, long long n_in, float *out, long long n_o
   P.cin = cin;
   P.cout = cout;
   P.n_stages = stages;
-  P.n_tiles = ceil_div(n_out, rows);
   P.flags = flags;
   static int n_sm[64] = {0};
   int dev = 0;
@@ -555,6 +560,17 @@ int conv_forward_wide(const float *in, long long n_in, float *out, long long n_o
     SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_wide<3, 256, 12>, cudaFuncAttributeMaxDynamicSharedMemorySize, b));
     n_sm[dev] = sms;
   }
+  // Tile height: with w = the number of tiles of full height the busiest SM would get, the smallest multiple of 16
+  // rows that still covers the level with w tiles per SM -- every SM then gets the same number of tiles (601 tiles
+  // of 256 rows leave 5 on nine SMs and 4 on the rest; 740 tiles of 208 rows are 5 on each, a fifth fewer rows on
+  // the longest SM).  SCN_WIDE_EVEN=0 keeps full-height tiles.
+  P.tile_rows = rows;
+  if (!(getenv("SCN_WIDE_EVEN") && atoi(getenv("SCN_WIDE_EVEN")) == 0)) {
+    const long long waves = ceil_div(ceil_div(n_out, rows), n_sm[dev]);
+    const long long even = ceil_div(ceil_div(n_out, waves * n_sm[dev]), 16) * 16;
+    P.tile_rows = (int)std::max<long long>(64, std::min<long long>(rows, even));
+  }
+  P.n_tiles = ceil_div(n_out, P.tile_rows);
   const unsigned grid = (unsigned)std::min<long long>(P.n_tiles, n_sm[dev]);
   // one CTA per SM by construction: it asks for the whole shared memory and owns all 512 TMEM columns
   if (terms == 3)
