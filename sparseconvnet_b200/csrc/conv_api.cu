@@ -210,7 +210,8 @@ int conv_forward_dispatch(const float *in, long long rows_in, float *out, long l
   // The persistent kernel runs one CTA per SM over whole tiles; with fewer tiles than SMs the
   // per-tile kernel is used instead, which splits a tile's filter offsets over several CTAs.
   const bool force_persistent = getenv("SCN_TC_PERSISTENT") && atoi(getenv("SCN_TC_PERSISTENT")) != 0;
-  const bool few_tiles = rows_out <= 148 * 256 && !force_persistent;
+  const long long wide_min_rows = getenv("SCN_WIDE_MIN_ROWS") ? atoll(getenv("SCN_WIDE_MIN_ROWS")) : 148 * 256;
+  const bool few_tiles = rows_out <= wide_min_rows && !force_persistent;
   const bool use_rows = !(getenv("SCN_X3_ROWS") && atoi(getenv("SCN_X3_ROWS")) == 0);
   const bool rows_thin = narrow_x3 && use_rows && conv_rows_thin_supported(out, bias, cin, cout, groups);
   // the row-stationary kernel also has the single-pass modes (32 / 64 output planes)
