@@ -563,7 +563,8 @@ int conv_forward_wide(const float *in, long long n_in, float *out, long long n_o
 #define SCN_WIDE_ATTR(TRC)                                                                                            \
   SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_wide<1, 256, 12, TRC>, cudaFuncAttributeMaxDynamicSharedMemorySize, b)); \
   SCN_CUDA_CHECK(cudaFuncSetAttribute(k_conv_wide<3, 256, 12, TRC>, cudaFuncAttributeMaxDynamicSharedMemorySize, b));
-    SCN_WIDE_ATTR(0) SCN_WIDE_ATTR(192) SCN_WIDE_ATTR(208) SCN_WIDE_ATTR(224) SCN_WIDE_ATTR(240) SCN_WIDE_ATTR(256)
+    SCN_WIDE_ATTR(0) SCN_WIDE_ATTR(128) SCN_WIDE_ATTR(144) SCN_WIDE_ATTR(160) SCN_WIDE_ATTR(176) SCN_WIDE_ATTR(192)
+    SCN_WIDE_ATTR(208) SCN_WIDE_ATTR(224) SCN_WIDE_ATTR(240) SCN_WIDE_ATTR(256)
 #undef SCN_WIDE_ATTR
     n_sm[dev] = sms;
   }
@@ -580,7 +581,7 @@ int conv_forward_wide(const float *in, long long n_in, float *out, long long n_o
   P.n_tiles = ceil_div(n_out, P.tile_rows);
   const unsigned grid = (unsigned)std::min<long long>(P.n_tiles, n_sm[dev]);
   // one CTA per SM by construction: it asks for the whole shared memory and owns all 512 TMEM columns
-  // the usual heights (four or more tiles per SM give 192 rows or more) have kernels of their own
+  // the heights two or more tiles per SM lead to (128 rows and up) have kernels of their own
 #define SCN_WIDE_LAUNCH(TRC)                                                                 \
   if (terms == 3)                                                                            \
     SCN_LAUNCH((k_conv_wide<3, 256, 12, TRC>), grid, 17 * 32, budget, stream, P);            \
@@ -592,6 +593,10 @@ int conv_forward_wide(const float *in, long long n_in, float *out, long long n_o
     case 224: SCN_WIDE_LAUNCH(224) break;
     case 208: SCN_WIDE_LAUNCH(208) break;
     case 192: SCN_WIDE_LAUNCH(192) break;
+    case 176: SCN_WIDE_LAUNCH(176) break;
+    case 160: SCN_WIDE_LAUNCH(160) break;
+    case 144: SCN_WIDE_LAUNCH(144) break;
+    case 128: SCN_WIDE_LAUNCH(128) break;
     default: SCN_WIDE_LAUNCH(0) break;
   }
 #undef SCN_WIDE_LAUNCH
