@@ -338,12 +338,14 @@ __device__ __forceinline__ void rows_chunk(float (&d)[2][NT][4], const float *a_
   }
 }
 
-template <int NT, int MODE>
+// NCH: the number of 32-plane input chunks as a constant (0: the run-time argument)
+template <int NT, int MODE, int NCH>
 __global__ void __launch_bounds__(32)
 k_conv_rows(const float *__restrict__ in, int ld_in, long long n_in, float *__restrict__ out, int ld_out,
             long long n_out, const uint4 *__restrict__ img, const float *__restrict__ bias,
             const float *__restrict__ bn_scale, const float *__restrict__ bn_shift, float leak,
-            const int *__restrict__ nbr, int K, int nch, int *flags) {
+            const int *__restrict__ nbr, int K, int nch_arg, int *flags) {
+  const int nch = NCH ? NCH : nch_arg;
   constexpr unsigned kFull = 0xffffffffu;
   constexpr int kSlab = (MODE == TC_BF16X3 ? 2 : 4) * NT * 32;  // uint4 per (offset, chunk) slab
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -422,7 +424,8 @@ k_conv_rows(const float *__restrict__ in, int ld_in, long long n_in, float *__re
   int cstage = 0;
   for (unsigned rem = wmask; rem; rem &= rem - 1) {
     const int k = __ffs(rem) - 1;
-    for (int c = 0; c < nch; ++c) {
+#pragma unroll
+    for (int c = 0; c < (NCH ? NCH : nch); ++c) {
       cp_async_wait<kRAStages - 2>();  // the rows of this step have landed (this lane's copies)
       __syncwarp();                    // ... every lane's; and the previous step's reads are done
       issue();
@@ -461,7 +464,7 @@ k_conv_rows(const float *__restrict__ in, int ld_in, long long n_in, float *__re
     }
 }
 
-template <int NT, int MODE>
+template <int NT, int MODE, int NCH = 0>
 static int launch_rows(const float *in, int ld_in, long long n_in, float *out, int ld_out, long long n_out,
                        const uint4 *img, const float *bias, const float *bn_scale, const float *bn_shift, float leak,
                        const int *table, int K, int nch, int *flags, cudaStream_t stream) {
@@ -469,7 +472,7 @@ static int launch_rows(const float *in, int ld_in, long long n_in, float *out, i
   int dev = 0;
   SCN_CUDA_CHECK(cudaGetDevice(&dev));
   const size_t smem = (size_t)kRAStages * kRStageFloats * sizeof(float);
-  auto kernel = k_conv_rows<NT, MODE>;
+  auto kernel = k_conv_rows<NT, MODE, NCH>;
   if (dev >= 64 || !configured[dev]) {
     SCN_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     // 9 KB of shared memory per warp: a carve-out of 80 % holds 20 warps per SM (the registers allow
@@ -998,7 +1001,19 @@ int conv_forward_rows(const float *in, long long n_in, float *out, long long n_o
     rc = cout == 32 ? SCN_ROWS_CALL(4, TC_BF16) : SCN_ROWS_CALL(8, TC_BF16);
   else if (precision == SCN_PRECISION_TF32)
     rc = cout == 32 ? SCN_ROWS_CALL(4, TC_TF32) : SCN_ROWS_CALL(8, TC_TF32);
-  else if (b3)
+  else if (b3 && (nch <= 2 || nch == 4) && !(getenv("SCN_ROWS_NCH") && atoi(getenv("SCN_ROWS_NCH")) == 0)) {
+    // the default mode with 32, 64 or 128 input planes: the chunk count is a constant of the kernel (4 % faster:
+    // 6.94 -> 6.66 ms per U-Net pass over 8 rooms with the first two)
+#define SCN_ROWS_CALL_N(NT, N) \
+  launch_rows<NT, TC_BF16X3, N>(in, cin, n_in, out, cout, n_out, img, bias, bn_scale, bn_shift, leak, table, K, nch, flags, stream)
+    if (nch == 1)
+      rc = cout == 32 ? SCN_ROWS_CALL_N(4, 1) : SCN_ROWS_CALL_N(8, 1);
+    else if (nch == 2)
+      rc = cout == 32 ? SCN_ROWS_CALL_N(4, 2) : SCN_ROWS_CALL_N(8, 2);
+    else
+      rc = cout == 32 ? SCN_ROWS_CALL_N(4, 4) : SCN_ROWS_CALL_N(8, 4);
+#undef SCN_ROWS_CALL_N
+  } else if (b3)
     rc = cout == 32 ? SCN_ROWS_CALL(4, TC_BF16X3) : SCN_ROWS_CALL(8, TC_BF16X3);
   else
     rc = cout == 32 ? SCN_ROWS_CALL(4, TC_TF32X3) : SCN_ROWS_CALL(8, TC_TF32X3);
