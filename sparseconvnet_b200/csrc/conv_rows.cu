@@ -346,6 +346,11 @@ k_conv_rows(const float *__restrict__ in, int ld_in, long long n_in, float *__re
             const float *__restrict__ bn_scale, const float *__restrict__ bn_shift, float leak,
             const int *__restrict__ nbr, int K, int nch_arg, int *flags) {
   const int nch = NCH ? NCH : nch_arg;
+  // the specialised kernels are launched on dense matrices only: the row strides are constants as well
+  if (NCH) {
+    ld_in = NCH * kRChunk;
+    ld_out = NT * 8;
+  }
   constexpr unsigned kFull = 0xffffffffu;
   constexpr int kSlab = (MODE == TC_BF16X3 ? 2 : 4) * NT * 32;  // uint4 per (offset, chunk) slab
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -802,12 +807,18 @@ int conv_forward_rows_thin(const float *in, long long n_in, float *out, long lon
 // 1.59 M fine rows: 0.33 against 0.37 ms; rows sorted by coordinate keep the gather form's tiles to two offsets);
 // with the bf16 three-term form 0.26 ms, and 0.17 ms once the warp's input rows are read and split once and
 // held in registers for all offsets (32 output planes, at most 64 input planes).
-template <int NT, int MODE>
+// NCH: the number of 32-plane input chunks as a constant (0: the run-time argument), as in k_conv_rows.
+template <int NT, int MODE, int NCH>
 __global__ void __launch_bounds__(32)
 k_conv_rows_scatter(const float *__restrict__ in, int ld_in, long long n_in, float *__restrict__ out, int ld_out,
                     long long n_out, const uint4 *__restrict__ img, const float *__restrict__ bias,
                     const float *__restrict__ bn_scale, const float *__restrict__ bn_shift, float leak,
-                    const int *__restrict__ child_of /* [K][n_in] -> output row */, int K, int nch, int *flags) {
+                    const int *__restrict__ child_of /* [K][n_in] -> output row */, int K, int nch_arg, int *flags) {
+  const int nch = NCH ? NCH : nch_arg;
+  if (NCH) {  // dense matrices: constant row strides
+    ld_in = NCH * kRChunk;
+    ld_out = NT * 8;
+  }
   constexpr unsigned kFull = 0xffffffffu;
   constexpr int kSlab = (MODE == TC_BF16X3 ? 2 : 4) * NT * 32;
   const int lane = threadIdx.x, g = lane >> 2, t = lane & 3;
@@ -860,7 +871,8 @@ k_conv_rows_scatter(const float *__restrict__ in, int ld_in, long long n_in, flo
     for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) d[mt][nt][0] = d[mt][nt][1] = d[mt][nt][2] = d[mt][nt][3] = 0.f;
-    for (int c = 0; c < nch; ++c) {
+#pragma unroll
+    for (int c = 0; c < (NCH ? NCH : nch); ++c) {
       const uint4 *w_slab = img + ((long long)k * nch + c) * kSlab;
 #pragma unroll
       for (int kp = 0; kp < 2; ++kp) {
@@ -955,12 +967,17 @@ int conv_forward_rows_scatter(const float *in, long long n_in, float *out, long 
   else if (build)
     SCN_LAUNCH(k_rows_prepare, (unsigned)ceil_div(total, 256LL), 256, 0, stream, weight, img, K, cin, cout);
   const unsigned grid = (unsigned)ceil_div(n_in, 32LL);
-#define SCN_SCATTER_CALL(NT, MODE) \
-  SCN_LAUNCH((k_conv_rows_scatter<NT, MODE>), grid, 32, 0, stream, in, cin, n_in, out, cout, n_out, img, bias, bn_scale, bn_shift, leak, child_of, K, nch, flags)
+#define SCN_SCATTER_CALL(NT, MODE, NCH) \
+  SCN_LAUNCH((k_conv_rows_scatter<NT, MODE, NCH>), grid, 32, 0, stream, in, cin, n_in, out, cout, n_out, img, bias, bn_scale, bn_shift, leak, child_of, K, nch, flags)
+  const bool fixed = !(getenv("SCN_ROWS_NCH") && atoi(getenv("SCN_ROWS_NCH")) == 0);
   if (cout == 32) {
-    if (b3) SCN_SCATTER_CALL(4, TC_BF16X3); else SCN_SCATTER_CALL(4, TC_TF32X3);
+    if (b3 && fixed && nch == 2) SCN_SCATTER_CALL(4, TC_BF16X3, 2);
+    else if (b3) SCN_SCATTER_CALL(4, TC_BF16X3, 0);
+    else SCN_SCATTER_CALL(4, TC_TF32X3, 0);
   } else {
-    if (b3) SCN_SCATTER_CALL(8, TC_BF16X3); else SCN_SCATTER_CALL(8, TC_TF32X3);
+    if (b3 && fixed && nch == 3) SCN_SCATTER_CALL(8, TC_BF16X3, 3);
+    else if (b3) SCN_SCATTER_CALL(8, TC_BF16X3, 0);
+    else SCN_SCATTER_CALL(8, TC_TF32X3, 0);
   }
 #undef SCN_SCATTER_CALL
   const cudaError_t e = cudaGetLastError();
