@@ -95,3 +95,27 @@ def test_precision_switch():
         assert scn.get_precision() == p
     with pytest.raises(ValueError):
         scn.set_precision("fp8")
+
+
+def test_batchnorm_layers_are_switched_to_shared_statistics():
+    """shard.share_batchnorm_statistics marks every BatchNorm layer of a network; without a process group (one
+    process) the layers keep the one-device operator, in training mode too."""
+    import sparseconvnet_b200 as scn
+    from sparseconvnet_b200 import shard
+    net = scn.Sequential().add(scn.SubmanifoldConvolution(3, 3, 8, 3, False)).add(
+        scn.UNet(3, 1, [8, 16], residual_blocks=False)).add(scn.BatchNormReLU(8))
+    layers = [m for m in net.modules() if isinstance(m, scn.BatchNormalization)]
+    assert len(layers) >= 3 and not any(m.across_ranks for m in layers)
+    assert shard.share_batchnorm_statistics(net) is net
+    assert all(m.across_ranks and m.ranks_group is None for m in layers)
+    net.train()
+    assert not any(m._shares_statistics() for m in layers)   # no process group: nothing to share with
+    net.eval()
+    assert not any(m._shares_statistics() for m in layers)
+    # a single process sums nothing and leaves the gradients alone (scaled if asked)
+    p = [m.weight for m in layers]
+    for t in p:
+        t.grad = t.detach().clone() * 0 + 2.0
+    assert shard.sum_gradients(p) == 0 and all(float(t.grad[0]) == 2.0 for t in p)
+    shard.sum_gradients(p, scale=0.5)
+    assert all(float(t.grad[0]) == 1.0 for t in p)
